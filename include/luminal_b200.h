@@ -1,0 +1,244 @@
+/*
+ * luminal_b200.h -- C ABI of libluminal_b200.so, the B200 (sm_100a) execution backend for the
+ * compiled transformer decode path of Luminal.jl.
+ *
+ * The reference has no FFI; its extension seam is Julia multiple dispatch on the device type
+ * (src/Device.jl:9-16, 82-121) and on the array type inside execute_op! (src/Execution.jl:521,
+ * 566, 604).  A `B200Device <: AbstractDevice` shim binds the entry points below with `ccall`;
+ * each declaration names the reference code it stands in for.
+ *
+ * Conventions
+ *  - every function returns 0 on success, a negative LMB200_E* code otherwise, and never aborts,
+ *    traps or blocks without bound; lmb200_last_error() gives the message (thread-local);
+ *  - handles are opaque 64-bit integers; the caller owns host memory, the library owns device
+ *    memory until the matching *_free / *_destroy;
+ *  - "dptr" arguments are device addresses (from lmb200_alloc or any CUDA allocation on the
+ *    context's device); every other pointer is host memory;
+ *  - device tensors are row-major over the LOGICAL shape (last logical dim contiguous).  Julia
+ *    arrays are column-major: pass LMB200_COLMAJOR to upload/download and the library re-lays
+ *    them out, so parity is on logical indices, not on memory images;
+ *  - one host thread per context, calls are synchronous with respect to their host results
+ *    (like the reference: single task, src/Execution.jl:620-665);
+ *  - token ids cross the ABI as int32 (the shim converts from the reference's Float32 ids,
+ *    src/Execution.jl:263).
+ */
+#ifndef LUMINAL_B200_H
+#define LUMINAL_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef uint64_t lmb200_ctx;
+typedef uint64_t lmb200_model;
+typedef uint64_t lmb200_session;
+
+enum { LMB200_F32 = 0, LMB200_BF16 = 1, LMB200_I32 = 2 };
+enum { LMB200_ROWMAJOR = 0, LMB200_COLMAJOR = 1 };
+enum {
+  LMB200_OK = 0,
+  LMB200_EINVAL = -1,    /* bad argument / shape mismatch (reference: error(...), @assert) */
+  LMB200_ECUDA = -2,     /* a CUDA runtime call failed */
+  LMB200_ENOMEM = -3,
+  LMB200_ENCCL = -4,
+  LMB200_ESTATE = -5,    /* call order (e.g. decode past max_ctx) */
+  LMB200_ETIMEOUT = -6   /* a bounded device-side wait gave up */
+};
+
+/* element-wise opcodes of lmb200_ew: the reference's primitive and fused ops
+ * (src/Ops.jl:4-22; executors src/Execution.jl:216-227, 274-285) */
+enum {
+  LMB200_OP_ADD = 0, LMB200_OP_MUL = 1, LMB200_OP_MOD = 2, LMB200_OP_LESSTHAN = 3,
+  LMB200_OP_MAX = 4,
+  LMB200_OP_LOG2 = 8, LMB200_OP_EXP2 = 9, LMB200_OP_SIN = 10, LMB200_OP_COS = 11,
+  LMB200_OP_SQRT = 12, LMB200_OP_RECIP = 13, LMB200_OP_RELU = 14, LMB200_OP_COPY = 15,
+  LMB200_OP_FUSED_MUL_ADD = 16,   /* a*b+c        src/Ops.jl:21, src/Execution.jl:220,278 */
+  LMB200_OP_FUSED_ADD_RELU = 17   /* max(a+b,0)   src/Ops.jl:22, src/Execution.jl:221,279 */
+};
+enum { LMB200_REDUCE_SUM = 0, LMB200_REDUCE_MAX = 1 };
+
+/* ---------------------------------------------------------------------------------------------
+ * Library / context.  Replaces get_device()'s health check and the device structs
+ * (src/Device.jl:9-74): one context per process per GPU.
+ * ------------------------------------------------------------------------------------------ */
+int32_t lmb200_version(void);
+const char* lmb200_last_error(void);
+int32_t lmb200_device_count(int32_t* count);
+int32_t lmb200_init(int32_t device_ordinal, lmb200_ctx* ctx);
+int32_t lmb200_shutdown(lmb200_ctx ctx);
+/* run all later work of this context on an existing cudaStream_t (0 = the context's own) */
+int32_t lmb200_set_stream(lmb200_ctx ctx, void* cuda_stream);
+int32_t lmb200_sync(lmb200_ctx ctx);
+/* number of kernels this context has launched so far (graph replays count their nodes) */
+int32_t lmb200_launch_count(lmb200_ctx ctx, int64_t* count);
+
+/* Tensor-parallel communicator: one rank per process, NCCL over NVLink.  Not in the reference
+ * (single device only, README.md:150-158); defined by the multi-GPU row of the hot-path scope.
+ * Rank 0 creates the id, the launcher broadcasts the 128 bytes, every rank joins. */
+int32_t lmb200_comm_unique_id(uint8_t id_out[128]);
+int32_t lmb200_comm_init(lmb200_ctx ctx, int32_t n_ranks, int32_t rank, const uint8_t id[128]);
+int32_t lmb200_comm_destroy(lmb200_ctx ctx);
+int32_t lmb200_allreduce_sum_f32(lmb200_ctx ctx, void* dptr, int64_t count);
+
+/* ---------------------------------------------------------------------------------------------
+ * Buffers.  Replace to_device / from_device (src/Device.jl:82-105) and the per-node buffers
+ * that compile() allocates (src/Compiler.jl:217-235).
+ * ------------------------------------------------------------------------------------------ */
+int32_t lmb200_alloc(lmb200_ctx ctx, int64_t bytes, void** dptr_out);
+int32_t lmb200_free(lmb200_ctx ctx, void* dptr);
+/* host float32 array of logical shape dims[rank] in `layout` -> row-major device tensor of dtype */
+int32_t lmb200_upload(lmb200_ctx ctx, void* dptr, int32_t dtype, const float* host,
+                      int32_t rank, const int64_t* dims, int32_t layout);
+int32_t lmb200_download(lmb200_ctx ctx, float* host, const void* dptr, int32_t dtype,
+                        int32_t rank, const int64_t* dims, int32_t layout);
+
+/* ---------------------------------------------------------------------------------------------
+ * Primitive ops on float32 row-major device tensors: what execute_op! dispatches to per node.
+ * ------------------------------------------------------------------------------------------ */
+/* Element-wise with the reference's broadcasting (lower rank gets 1-dims PREPENDED,
+ * src/Execution.jl:207-214).  Unused operands are NULL with rank 0.
+ * Replaces src/Execution.jl:216-227 / 274-285. */
+int32_t lmb200_ew(lmb200_ctx ctx, int32_t opcode, float* out_dptr, int32_t out_rank,
+                  const int64_t* out_dims,
+                  const float* a, int32_t a_rank, const int64_t* a_dims,
+                  const float* b, int32_t b_rank, const int64_t* b_dims,
+                  const float* c, int32_t c_rank, const int64_t* c_dims);
+/* SumReduce / MaxReduce over one 0-based axis, axis dropped.  src/Execution.jl:232-233, 306-339 */
+int32_t lmb200_reduce(lmb200_ctx ctx, int32_t kind, float* out_dptr, const float* in_dptr,
+                      int32_t rank, const int64_t* dims, int32_t axis);
+/* batch_matmul cases 2Dx2D, 3Dx2D, 3Dx3D, 4Dx4D.  src/Execution.jl:12-90 */
+int32_t lmb200_matmul(lmb200_ctx ctx, float* out_dptr, const float* a, int32_t a_rank,
+                      const int64_t* a_dims, const float* b, int32_t b_rank, const int64_t* b_dims);
+/* Permute (0-based perm).  src/Execution.jl:229, 298-301 */
+int32_t lmb200_permute(lmb200_ctx ctx, float* out_dptr, const float* in_dptr, int32_t rank,
+                       const int64_t* in_dims, const int32_t* perm);
+/* Reshape keeping the COLUMN-MAJOR linear order of the logical tensor.  src/Execution.jl:228 */
+int32_t lmb200_reshape_colmajor(lmb200_ctx ctx, float* out_dptr, const float* in_dptr,
+                                int32_t in_rank, const int64_t* in_dims,
+                                int32_t out_rank, const int64_t* out_dims);
+/* Expand: new axis of `size` inserted at 0-based `axis`.  src/Execution.jl:238-248, 345-371 */
+int32_t lmb200_expand(lmb200_ctx ctx, float* out_dptr, const float* in_dptr, int32_t in_rank,
+                      const int64_t* in_dims, int32_t axis, int64_t size);
+/* Slice [start, stop) per axis (clamped).  src/Execution.jl:160-181 */
+int32_t lmb200_slice(lmb200_ctx ctx, float* out_dptr, const float* in_dptr, int32_t rank,
+                     const int64_t* in_dims, const int64_t* starts, const int64_t* stops);
+/* Zero padding (left,right) per axis.  src/Execution.jl:183-202 */
+int32_t lmb200_pad(lmb200_ctx ctx, float* out_dptr, const float* in_dptr, int32_t rank,
+                   const int64_t* in_dims, const int64_t* left, const int64_t* right);
+/* Gather rows of table[vocab,dim] by float ids (row Int(id), out-of-range -> 0).
+ * src/Execution.jl:262-264, 580-611 */
+int32_t lmb200_gather(lmb200_ctx ctx, float* out_dptr, const float* table, int64_t vocab,
+                      int64_t dim, const float* ids, int64_t n_ids);
+/* CumSum along the last axis (used by arange).  src/Execution.jl:265-266, 612-613 */
+int32_t lmb200_cumsum_last(lmb200_ctx ctx, float* out_dptr, const float* in_dptr,
+                           int64_t rows, int64_t n);
+/* FlashAttentionOp: softmax(scale*Q K^T [+causal]) V on [B,H,S,D]; dtype F32 or BF16 storage.
+ * src/Ops.jl:104-107, src/Execution.jl:374-479, 565-578 */
+int32_t lmb200_flash_attention(lmb200_ctx ctx, void* out_dptr, const void* q, const void* k,
+                               const void* v, int32_t dtype, int64_t B, int64_t H, int64_t S,
+                               int64_t D, float scale, int32_t causal);
+
+/* ---------------------------------------------------------------------------------------------
+ * Fused layer ops (what the compiled path's fusion groups become, src/Compiler.jl:196-215).
+ * ------------------------------------------------------------------------------------------ */
+/* y = (x * recip(sqrt(mean(x*x)+eps))) * w over the last dim.  src/NN.jl:134-173,
+ * src/HighLevelOps.jl:299-304.  x,y: [rows,n] float32; w: [n] float32. */
+int32_t lmb200_rmsnorm_scale(lmb200_ctx ctx, float* y, const float* x, const float* w,
+                             int64_t rows, int64_t n, float eps);
+/* LayerNorm with mean-centering, optional w / bias (NULL to skip).  src/NN.jl:121-173 */
+int32_t lmb200_layernorm(lmb200_ctx ctx, float* y, const float* x, const float* w,
+                         const float* bias, int64_t rows, int64_t n, float eps);
+/* out = silu(gate) * up, silu via exp2 as in src/HighLevelOps.jl:153-160; src/NN.jl:246-249 */
+int32_t lmb200_silu_gate(lmb200_ctx ctx, float* out, const float* gate, const float* up, int64_t n);
+/* Half-split RoPE on [B,H,S,D] float32 at positions prev_seq..prev_seq+S-1.  src/NN.jl:253-303 */
+int32_t lmb200_rope(lmb200_ctx ctx, float* out, const float* x, int64_t B, int64_t H, int64_t S,
+                    int64_t D, int64_t prev_seq, float base);
+/* argmax over the last dim (first maximum), 0-based ids.  src/Decoding.jl:119-124 */
+int32_t lmb200_argmax(lmb200_ctx ctx, int32_t* out_ids_dptr, const float* x, int64_t rows, int64_t n);
+
+/* ---------------------------------------------------------------------------------------------
+ * Model / session API: the timed decode loop.  A model is the weights of a NN.Llama / NN.Phi3
+ * shaped decoder (src/NN.jl:417-507); a session owns the preallocated GQA KV cache and the
+ * CUDA graph of one decode step, and replaces the per-token graph build + execute of
+ * examples/llama.jl:39-99 and src/Decoding.jl:91-130.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct {
+  int32_t n_layers;
+  int32_t hidden;
+  int32_t n_heads;
+  int32_t n_kv_heads;
+  int32_t head_dim;        /* must equal hidden / n_heads (src/NN.jl:331) */
+  int32_t intermediate;
+  int32_t vocab;
+  float rms_eps;           /* 1e-5 in the reference (src/NN.jl:134) */
+  float rope_base;         /* 500000 Llama (src/NN.jl:451), 10000 Phi-3 (src/NN.jl:503) */
+  int32_t dtype;           /* LMB200_F32: everything float32; LMB200_BF16: weights, KV cache and
+                              GEMV inputs bf16, accumulation and the residual stream float32 */
+  int32_t tp_size;         /* tensor-parallel ranks (1 = single GPU) */
+  int32_t tp_rank;
+  int32_t reserved[4];
+} lmb200_model_config;
+
+int32_t lmb200_model_create(lmb200_ctx ctx, const lmb200_model_config* cfg, lmb200_model* model);
+int32_t lmb200_model_destroy(lmb200_model model);
+/* Set one weight from the FULL logical float32 tensor under its registry name
+ * ("model.layers.3.self_attn.q_proj.weight", "model.embed_tokens.weight", "model.norm.weight",
+ * "lm_head.weight" ...: src/NN.jl:180-225, 433-445).  The library keeps only this rank's shard,
+ * in its own tiled layout.  Replaces graph.tensors / load_weights! (src/Weights.jl:60-114). */
+int32_t lmb200_model_set_weight(lmb200_model model, const char* name, const float* host,
+                                int32_t layout);
+/* Fill every weight on the device from the counter-based generator (seed, tensor id, logical
+ * row-major index) -> Irwin-Hall(12) approximation of N(0,sigma); norm gains get +1. */
+int32_t lmb200_model_init_random(lmb200_model model, uint64_t seed, float sigma);
+int32_t lmb200_model_weight_bytes(lmb200_model model, int64_t* bytes);
+
+int32_t lmb200_session_create(lmb200_model model, int32_t batch, int32_t max_ctx,
+                              lmb200_session* session);
+int32_t lmb200_session_destroy(lmb200_session session);
+int32_t lmb200_session_reset(lmb200_session session);
+int32_t lmb200_session_position(lmb200_session session, int32_t* pos);
+/* Rewind (or move) the position; cache contents at and beyond it are overwritten by later steps. */
+int32_t lmb200_session_set_position(lmb200_session session, int32_t pos);
+/* Synthetic context: fill cache positions [0,n_pos) with generator values (sigma 1 for K and V)
+ * and set the position to n_pos. */
+int32_t lmb200_session_fill_kv_random(lmb200_session session, int32_t n_pos, uint64_t seed);
+/* Keep the residual stream after every layer of the next steps (parity tests). */
+int32_t lmb200_session_set_capture(lmb200_session session, int32_t enable);
+int32_t lmb200_session_read_layer_output(lmb200_session session, int32_t layer, float* host);
+
+/* Prompt: tokens [batch, n] int32 row-major, appended at the current position.  logits_out
+ * (NULL or [batch, vocab] float32) receives the LAST position's logits.
+ * Replaces running the model over the prompt (src/NN.jl:448-455). */
+int32_t lmb200_prefill(lmb200_session session, const int32_t* tokens, int32_t n, float* logits_out);
+/* One token per sequence in, greedy next token out; host buffers, copies inside the call.
+ * Replaces one iteration of the generation loop (src/Decoding.jl:91-130, examples/llama.jl:73-99). */
+int32_t lmb200_decode_step(lmb200_session session, const int32_t* tokens_in,
+                           int32_t* next_tokens_out, float* logits_out);
+/* n_steps greedy steps by CUDA-graph replay with the tokens staying on the device.
+ * first_tokens [batch] host (NULL = continue from the last produced tokens);
+ * tokens_out [n_steps, batch] host (NULL to skip the copy back). */
+int32_t lmb200_decode_n(lmb200_session session, const int32_t* first_tokens, int32_t n_steps,
+                        int32_t* tokens_out);
+/* Same loop, asynchronous on the context's stream: tokens come from and go to device memory
+ * ([batch] int32 in, [n_steps,batch] int32 out, either may be NULL), no host synchronisation. */
+int32_t lmb200_decode_n_device(lmb200_session session, const int32_t* first_tokens_dptr,
+                               int32_t n_steps, int32_t* tokens_out_dptr);
+/* Algorithmic HBM bytes of ONE decode step on this rank at context length T (weights read once
+ * + KV cache read for T keys + KV written for one key). */
+int32_t lmb200_session_step_bytes(lmb200_session session, int32_t T, int64_t* bytes);
+
+/* Stand-alone split-KV decode attention over a cache in the session layout (tests, profiling),
+ * asynchronous on the context's stream (lmb200_sync before reading the result).
+ * q: [batch, n_heads_local, head_dim] in the session dtype (device); out: same shape.
+ * Local q head (kv_local*G + g) is the reference's head kv + KV*g.
+ * Replaces whisper_self_attn_cached's attention over [0, step_pos] (src/Whisper.jl:606-617)
+ * and the S=1 case of SelfAttention (src/NN.jl:369-386). */
+int32_t lmb200_decode_attention_splitkv(lmb200_session session, int32_t layer, const void* q_dptr,
+                                        void* out_dptr, int32_t T);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LUMINAL_B200_H */

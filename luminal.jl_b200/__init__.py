@@ -1,0 +1,13 @@
+"""luminal.jl_b200 -- host side of the B200 backend for Luminal.jl's transformer decode path.
+
+Everything numeric runs in libluminal_b200.so (hand-written sm_100a CUDA behind a C ABI, see
+include/luminal_b200.h).  This package is the Python stand-in for the Julia shim: the same
+device / execute / NN vocabulary as the reference, bound with ctypes instead of ccall.  There
+is no CPU fallback: without the built library or without a B200 every entry point raises."""
+from . import _lib
+from ._lib import BF16, COLMAJOR, F32, ROWMAJOR, LuminalB200Error
+from .device import B200Device, DeviceArray, device_count, from_device, get_device, to_device
+from .session import Model, Session, greedy_generate
+
+__all__ = ["B200Device", "DeviceArray", "Model", "Session", "greedy_generate", "get_device", "to_device",
+           "from_device", "device_count", "LuminalB200Error", "F32", "BF16", "ROWMAJOR", "COLMAJOR"]

@@ -1,0 +1,349 @@
+// Context, error reporting, buffers, host<->device layout conversion and the NCCL binding.
+#include <dlfcn.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "common.cuh"
+#include "gemv.cuh"
+
+namespace lmb {
+
+static thread_local char g_err[1024] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+int32_t fail(int32_t code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+Ctx* ctx_from(lmb200_ctx h) {
+  Ctx* c = reinterpret_cast<Ctx*>(h);
+  if (!c || c->magic != 0x4C4D4231) {
+    set_error("invalid context handle");
+    return nullptr;
+  }
+  return c;
+}
+
+// ---------------------------------------------------------------------------------------------
+// NCCL, resolved at run time so the library loads (and its CPU-side entry points work) on a
+// host without NCCL.  Only the calls below are used; the types are ABI-stable across NCCL 2.x.
+// ---------------------------------------------------------------------------------------------
+namespace {
+struct Id128 { char b[128]; };   // ncclUniqueId: 128 opaque bytes, passed by value
+struct NcclApi {
+  void* lib = nullptr;
+  int (*GetUniqueId)(void*) = nullptr;
+  int (*CommInitRank)(void**, int, Id128, int) = nullptr;
+  int (*CommDestroy)(void*) = nullptr;
+  int (*AllReduce)(const void*, void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+  const char* (*GetErrorString)(int) = nullptr;
+};
+NcclApi g_nccl;
+
+int32_t nccl_load() {
+  if (g_nccl.lib) return LMB200_OK;
+  const char* names[] = {"libnccl.so.2", "libnccl.so"};
+  void* lib = nullptr;
+  for (const char* n : names) {
+    lib = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+    if (lib) break;
+  }
+  if (!lib) return fail(LMB200_ENCCL, "NCCL not found: %s", dlerror());
+  g_nccl.GetUniqueId = reinterpret_cast<decltype(g_nccl.GetUniqueId)>(dlsym(lib, "ncclGetUniqueId"));
+  g_nccl.CommInitRank = reinterpret_cast<decltype(g_nccl.CommInitRank)>(dlsym(lib, "ncclCommInitRank"));
+  g_nccl.CommDestroy = reinterpret_cast<decltype(g_nccl.CommDestroy)>(dlsym(lib, "ncclCommDestroy"));
+  g_nccl.AllReduce = reinterpret_cast<decltype(g_nccl.AllReduce)>(dlsym(lib, "ncclAllReduce"));
+  g_nccl.GetErrorString = reinterpret_cast<decltype(g_nccl.GetErrorString)>(dlsym(lib, "ncclGetErrorString"));
+  if (!g_nccl.GetUniqueId || !g_nccl.CommInitRank || !g_nccl.CommDestroy || !g_nccl.AllReduce)
+    return fail(LMB200_ENCCL, "NCCL library lacks a required symbol");
+  g_nccl.lib = lib;
+  return LMB200_OK;
+}
+const char* nccl_str(int r) { return g_nccl.GetErrorString ? g_nccl.GetErrorString(r) : "?"; }
+}  // namespace
+
+int32_t nccl_allreduce_f32(Ctx* ctx, void* dptr, int64_t count, cudaStream_t stream) {
+  if (!ctx->nccl_comm) return fail(LMB200_ENCCL, "allreduce without a communicator");
+  // ncclFloat32 = 7, ncclSum = 0
+  const int r = g_nccl.AllReduce(dptr, dptr, (size_t)count, 7, 0, ctx->nccl_comm, stream);
+  if (r != 0) return fail(LMB200_ENCCL, "ncclAllReduce: %s", nccl_str(r));
+  return LMB200_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// layout conversion: host float32 (row- or column-major) <-> device row-major tensor
+// ---------------------------------------------------------------------------------------------
+struct Shape8 {
+  int rank;
+  int64_t d[8];
+};
+
+// src is the host image (float32) staged on the device; element (i0..ir) of a column-major
+// array sits at sum i_k * prod_{j<k} d_j.
+template <typename T, bool kToDevice>
+__global__ void relayout_kernel(T* dev, float* stage, Shape8 s, int colmajor, int64_t total) {
+  for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total; o += (int64_t)gridDim.x * blockDim.x) {
+    int64_t src = o;
+    if (colmajor) {
+      int64_t rem = o, stride_total = total;
+      src = 0;
+      // walk the row-major index from the slowest dim, accumulate the column-major offset
+      int64_t cm_stride[8];
+      int64_t acc = 1;
+      for (int k = 0; k < s.rank; ++k) { cm_stride[k] = acc; acc *= s.d[k]; }
+      for (int k = 0; k < s.rank; ++k) {
+        stride_total /= s.d[k];
+        const int64_t ik = rem / stride_total;
+        rem -= ik * stride_total;
+        src += ik * cm_stride[k];
+      }
+    }
+    if (kToDevice) dev[o] = from_f32<T>(stage[src]);
+    else stage[src] = to_f32(dev[o]);
+  }
+}
+
+}  // namespace lmb
+
+using namespace lmb;
+
+extern "C" int32_t lmb200_version(void) { return 100; }
+extern "C" const char* lmb200_last_error(void) { return g_err; }
+
+extern "C" int32_t lmb200_device_count(int32_t* count) {
+  LMB_REQUIRE(count, "device_count: null argument");
+  int n = 0;
+  cudaError_t e = cudaGetDeviceCount(&n);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    *count = 0;
+    return fail(LMB200_ECUDA, "cudaGetDeviceCount: %s", cudaGetErrorString(e));
+  }
+  *count = n;
+  return LMB200_OK;
+}
+
+extern "C" int32_t lmb200_init(int32_t device, lmb200_ctx* out) {
+  LMB_REQUIRE(out, "init: null argument");
+  int n = 0;
+  LMB_TRY(lmb200_device_count(&n));
+  LMB_REQUIRE(device >= 0 && device < n, "init: device %d of %d", device, n);
+  LMB_CUDA(cudaSetDevice(device));
+  cudaDeviceProp prop;
+  LMB_CUDA(cudaGetDeviceProperties(&prop, device));
+  if (prop.major != 10)
+    return fail(LMB200_EINVAL, "init: device %d is sm_%d%d; this library holds sm_100a code only", device,
+                prop.major, prop.minor);
+  Ctx* c = new Ctx();
+  c->device = device;
+  c->sm_count = prop.multiProcessorCount;
+  if (cudaStreamCreateWithFlags(&c->own_stream, cudaStreamNonBlocking) != cudaSuccess) {
+    delete c;
+    return fail(LMB200_ECUDA, "init: stream creation failed");
+  }
+  c->stream = c->own_stream;
+  int32_t rc = gemv_configure();
+  if (rc != LMB200_OK) { cudaStreamDestroy(c->own_stream); delete c; return rc; }
+  *out = reinterpret_cast<lmb200_ctx>(c);
+  return LMB200_OK;
+}
+
+extern "C" int32_t lmb200_shutdown(lmb200_ctx h) {
+  Ctx* c = ctx_from(h);
+  if (!c) return LMB200_EINVAL;
+  cudaSetDevice(c->device);
+  cudaStreamSynchronize(c->stream);
+  if (c->nccl_comm && g_nccl.CommDestroy) g_nccl.CommDestroy(c->nccl_comm);
+  cudaStreamDestroy(c->own_stream);
+  c->magic = 0;
+  delete c;
+  return LMB200_OK;
+}
+
+extern "C" int32_t lmb200_set_stream(lmb200_ctx h, void* stream) {
+  Ctx* c = ctx_from(h);
+  if (!c) return LMB200_EINVAL;
+  c->stream = stream ? reinterpret_cast<cudaStream_t>(stream) : c->own_stream;
+  return LMB200_OK;
+}
+
+extern "C" int32_t lmb200_sync(lmb200_ctx h) {
+  Ctx* c = ctx_from(h);
+  if (!c) return LMB200_EINVAL;
+  LMB_CUDA(cudaSetDevice(c->device));
+  LMB_CUDA(cudaStreamSynchronize(c->stream));
+  return LMB200_OK;
+}
+
+extern "C" int32_t lmb200_launch_count(lmb200_ctx h, int64_t* count) {
+  Ctx* c = ctx_from(h);
+  if (!c || !count) return LMB200_EINVAL;
+  *count = c->launches;
+  return LMB200_OK;
+}
+
+extern "C" int32_t lmb200_comm_unique_id(uint8_t id_out[128]) {
+  LMB_REQUIRE(id_out, "comm_unique_id: null argument");
+  LMB_TRY(nccl_load());
+  Id128 id;
+  memset(&id, 0, sizeof(id));
+  const int r = g_nccl.GetUniqueId(&id);
+  if (r != 0) return fail(LMB200_ENCCL, "ncclGetUniqueId: %s", nccl_str(r));
+  memcpy(id_out, &id, 128);
+  return LMB200_OK;
+}
+
+extern "C" int32_t lmb200_comm_init(lmb200_ctx h, int32_t n_ranks, int32_t rank, const uint8_t id_in[128]) {
+  Ctx* c = ctx_from(h);
+  if (!c) return LMB200_EINVAL;
+  LMB_REQUIRE(id_in && n_ranks >= 1 && rank >= 0 && rank < n_ranks, "comm_init: rank %d of %d", rank, n_ranks);
+  LMB_REQUIRE(!c->nccl_comm, "comm_init: communicator already exists");
+  LMB_TRY(nccl_load());
+  LMB_CUDA(cudaSetDevice(c->device));
+  Id128 id;
+  memcpy(&id, id_in, 128);
+  void* comm = nullptr;
+  const int r = g_nccl.CommInitRank(&comm, n_ranks, id, rank);
+  if (r != 0) return fail(LMB200_ENCCL, "ncclCommInitRank: %s", nccl_str(r));
+  c->nccl_comm = comm;
+  c->tp_size = n_ranks;
+  c->tp_rank = rank;
+  return LMB200_OK;
+}
+
+extern "C" int32_t lmb200_comm_destroy(lmb200_ctx h) {
+  Ctx* c = ctx_from(h);
+  if (!c) return LMB200_EINVAL;
+  if (c->nccl_comm) {
+    cudaSetDevice(c->device);
+    cudaStreamSynchronize(c->stream);
+    g_nccl.CommDestroy(c->nccl_comm);
+    c->nccl_comm = nullptr;
+    c->tp_size = 1;
+    c->tp_rank = 0;
+  }
+  return LMB200_OK;
+}
+
+extern "C" int32_t lmb200_allreduce_sum_f32(lmb200_ctx h, void* dptr, int64_t count) {
+  Ctx* c = ctx_from(h);
+  if (!c) return LMB200_EINVAL;
+  LMB_REQUIRE(dptr && count > 0, "allreduce: bad argument");
+  LMB_CUDA(cudaSetDevice(c->device));
+  LMB_TRY(nccl_allreduce_f32(c, dptr, count, c->stream));
+  LMB_CUDA(cudaStreamSynchronize(c->stream));
+  return LMB200_OK;
+}
+
+extern "C" int32_t lmb200_alloc(lmb200_ctx h, int64_t bytes, void** out) {
+  Ctx* c = ctx_from(h);
+  if (!c) return LMB200_EINVAL;
+  LMB_REQUIRE(out && bytes >= 0, "alloc: bad argument");
+  LMB_CUDA(cudaSetDevice(c->device));
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, (size_t)(bytes > 0 ? bytes : 16));
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(LMB200_ENOMEM, "alloc of %lld bytes failed: %s", (long long)bytes, cudaGetErrorString(e));
+  }
+  *out = p;
+  return LMB200_OK;
+}
+
+extern "C" int32_t lmb200_free(lmb200_ctx h, void* dptr) {
+  Ctx* c = ctx_from(h);
+  if (!c) return LMB200_EINVAL;
+  LMB_CUDA(cudaSetDevice(c->device));
+  LMB_CUDA(cudaStreamSynchronize(c->stream));
+  LMB_CUDA(cudaFree(dptr));
+  return LMB200_OK;
+}
+
+static int32_t shape_of(int32_t rank, const int64_t* dims, Shape8* s, int64_t* total) {
+  LMB_REQUIRE(rank >= 0 && rank <= 8, "rank %d outside 0..8", rank);
+  s->rank = rank;
+  int64_t t = 1;
+  for (int i = 0; i < rank; ++i) {
+    LMB_REQUIRE(dims && dims[i] >= 0, "negative dimension");
+    s->d[i] = dims[i];
+    t *= dims[i];
+  }
+  *total = t;
+  return LMB200_OK;
+}
+
+extern "C" int32_t lmb200_upload(lmb200_ctx h, void* dptr, int32_t dtype, const float* host, int32_t rank,
+                                 const int64_t* dims, int32_t layout) {
+  Ctx* c = ctx_from(h);
+  if (!c) return LMB200_EINVAL;
+  LMB_REQUIRE(dptr && host, "upload: null pointer");
+  LMB_REQUIRE(dtype == LMB200_F32 || dtype == LMB200_BF16, "upload: dtype %d", dtype);
+  Shape8 s;
+  int64_t total;
+  LMB_TRY(shape_of(rank, dims, &s, &total));
+  if (total == 0) return LMB200_OK;
+  LMB_CUDA(cudaSetDevice(c->device));
+  if (dtype == LMB200_F32 && (layout == LMB200_ROWMAJOR || rank <= 1)) {
+    LMB_CUDA(cudaMemcpyAsync(dptr, host, (size_t)total * 4, cudaMemcpyHostToDevice, c->stream));
+    LMB_CUDA(cudaStreamSynchronize(c->stream));
+    return LMB200_OK;
+  }
+  float* stage = nullptr;
+  LMB_CUDA(cudaMalloc(&stage, (size_t)total * 4));
+  cudaError_t e = cudaMemcpyAsync(stage, host, (size_t)total * 4, cudaMemcpyHostToDevice, c->stream);
+  if (e == cudaSuccess) {
+    const int grid = (int)(ceil_div(total, 256) > 4096 ? 4096 : ceil_div(total, 256));
+    if (dtype == LMB200_F32)
+      relayout_kernel<float, true><<<grid, 256, 0, c->stream>>>((float*)dptr, stage, s, layout, total);
+    else
+      relayout_kernel<__nv_bfloat16, true><<<grid, 256, 0, c->stream>>>((__nv_bfloat16*)dptr, stage, s, layout, total);
+    c->launches++;
+    e = cudaGetLastError();
+  }
+  cudaStreamSynchronize(c->stream);
+  cudaFree(stage);
+  if (e != cudaSuccess) return fail(LMB200_ECUDA, "upload: %s", cudaGetErrorString(e));
+  return LMB200_OK;
+}
+
+extern "C" int32_t lmb200_download(lmb200_ctx h, float* host, const void* dptr, int32_t dtype, int32_t rank,
+                                   const int64_t* dims, int32_t layout) {
+  Ctx* c = ctx_from(h);
+  if (!c) return LMB200_EINVAL;
+  LMB_REQUIRE(dptr && host, "download: null pointer");
+  LMB_REQUIRE(dtype == LMB200_F32 || dtype == LMB200_BF16, "download: dtype %d", dtype);
+  Shape8 s;
+  int64_t total;
+  LMB_TRY(shape_of(rank, dims, &s, &total));
+  if (total == 0) return LMB200_OK;
+  LMB_CUDA(cudaSetDevice(c->device));
+  if (dtype == LMB200_F32 && (layout == LMB200_ROWMAJOR || rank <= 1)) {
+    LMB_CUDA(cudaMemcpyAsync(host, dptr, (size_t)total * 4, cudaMemcpyDeviceToHost, c->stream));
+    LMB_CUDA(cudaStreamSynchronize(c->stream));
+    return LMB200_OK;
+  }
+  float* stage = nullptr;
+  LMB_CUDA(cudaMalloc(&stage, (size_t)total * 4));
+  const int grid = (int)(ceil_div(total, 256) > 4096 ? 4096 : ceil_div(total, 256));
+  if (dtype == LMB200_F32)
+    relayout_kernel<float, false><<<grid, 256, 0, c->stream>>>((float*)dptr, stage, s, layout, total);
+  else
+    relayout_kernel<__nv_bfloat16, false><<<grid, 256, 0, c->stream>>>((__nv_bfloat16*)dptr, stage, s, layout, total);
+  c->launches++;
+  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) e = cudaMemcpyAsync(host, stage, (size_t)total * 4, cudaMemcpyDeviceToHost, c->stream);
+  cudaStreamSynchronize(c->stream);
+  cudaFree(stage);
+  if (e != cudaSuccess) return fail(LMB200_ECUDA, "download: %s", cudaGetErrorString(e));
+  return LMB200_OK;
+}

@@ -1,0 +1,148 @@
+// Shared declarations of libluminal_b200: context, error reporting, the tiled ("fragment-major")
+// weight / KV-cache layouts and the counter-based generator.  sm_100a only.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+#include <vector>
+
+#include "../../include/luminal_b200.h"
+
+namespace lmb {
+
+// ---------------------------------------------------------------------------------------------
+// errors
+// ---------------------------------------------------------------------------------------------
+void set_error(const char* fmt, ...);
+int32_t fail(int32_t code, const char* fmt, ...);
+
+#define LMB_CUDA(expr)                                                                       \
+  do {                                                                                       \
+    cudaError_t _e = (expr);                                                                 \
+    if (_e != cudaSuccess)                                                                   \
+      return lmb::fail(LMB200_ECUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), \
+                       __FILE__, __LINE__);                                                  \
+  } while (0)
+
+#define LMB_REQUIRE(cond, ...)                                \
+  do {                                                        \
+    if (!(cond)) return lmb::fail(LMB200_EINVAL, __VA_ARGS__); \
+  } while (0)
+
+#define LMB_TRY(expr)              \
+  do {                             \
+    int32_t _r = (expr);           \
+    if (_r != LMB200_OK) return _r; \
+  } while (0)
+
+// ---------------------------------------------------------------------------------------------
+// context
+// ---------------------------------------------------------------------------------------------
+struct Ctx {
+  uint32_t magic = 0x4C4D4231;
+  int device = 0;
+  int sm_count = 148;
+  cudaStream_t own_stream = nullptr;
+  cudaStream_t stream = nullptr;
+  int64_t launches = 0;
+  // NCCL (resolved with dlopen so that the library loads on hosts without it)
+  void* nccl_comm = nullptr;
+  int tp_size = 1;
+  int tp_rank = 0;
+};
+
+Ctx* ctx_from(lmb200_ctx h);
+int32_t nccl_allreduce_f32(Ctx* ctx, void* dptr, int64_t count, cudaStream_t stream);
+
+static inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+static inline int64_t round_up(int64_t a, int64_t b) { return ceil_div(a, b) * b; }
+
+// ---------------------------------------------------------------------------------------------
+// Counter-based generator, identical on host and device (and in the NumPy oracle):
+//   value = float(2*sum_of_12_uint16_lanes - 12*65535) * (sigma/131072) [+ offset]
+// ---------------------------------------------------------------------------------------------
+__host__ __device__ inline uint64_t splitmix64(uint64_t x) {
+  x += 0x9E3779B97F4A7C15ull;
+  uint64_t z = x;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+__host__ __device__ inline uint64_t stream_key(uint64_t seed, uint64_t tensor_id) {
+  return splitmix64(seed * 0xD1342543DE82EF95ull + tensor_id);
+}
+__host__ __device__ inline float synth_value(uint64_t key, uint64_t idx, float scale /*sigma/131072*/,
+                                             float offset) {
+  int32_t total = 0;
+#pragma unroll
+  for (int r = 0; r < 3; ++r) {
+    uint64_t h = splitmix64(key ^ (idx * 3ull + (uint64_t)r));
+    total += (int32_t)(h & 0xFFFF) + (int32_t)((h >> 16) & 0xFFFF) + (int32_t)((h >> 32) & 0xFFFF) +
+             (int32_t)((h >> 48) & 0xFFFF);
+  }
+  float v = (float)(2 * total - 12 * 65535);
+#ifdef __CUDA_ARCH__
+  v = __fmul_rn(v, scale);
+  if (offset != 0.0f) v = __fadd_rn(v, offset);
+#else
+  v = v * scale;
+  if (offset != 0.0f) v = v + offset;
+#endif
+  return v;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Tiled weight layout.  A matrix [rows, K] is stored as units of 16 rows x 32 k, unit (rb, kc)
+// at ((rb*KC + kc) * 512) elements; inside a unit lane (g = row%8, t = (k%32)/8) owns 16
+// consecutive elements: 8 of row g then 8 of row g+8, k = 8t..8t+7.  This is the operand order
+// of two m16n8k16 MMAs (with the k index permuted identically in the activation operand), so a
+// warp reads one unit with fully contiguous 2 x 16-byte loads per lane.
+// ---------------------------------------------------------------------------------------------
+__host__ __device__ inline int64_t wtile_offset(int64_t row, int64_t k, int64_t KC) {
+  int64_t rb = row >> 4;
+  int r = (int)(row & 15);
+  int g = r & 7, hi = r >> 3;
+  int64_t kc = k >> 5;
+  int kk = (int)(k & 31);
+  int t = kk >> 3, e = kk & 7;
+  return ((rb * KC + kc) * 32 + (g * 4 + t)) * 16 + hi * 8 + e;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Tiled KV cache.  Per (layer, batch, kv head) the keys are grouped in blocks of 16; block kb
+// holds D/16 K-units then D/16 V-units, each unit 16x16 elements in m16n8k16 A-operand order:
+//   K unit dk (M = key, K = d):  lane (g,t): [key g][d 2t,2t+1] [key g+8][d 2t,2t+1]
+//                                            [key g][d 2t+8,+9] [key g+8][d 2t+8,+9]
+//   V unit dm (M = d,   K = key): lane (g,t): [d g][key 2t,2t+1] [d g+8][key 2t,2t+1]
+//                                            [d g][key 2t+8,+9] [d g+8][key 2t+8,+9]
+// with d = 16*unit + local.  One block is 2*16*D elements and fully contiguous.
+// ---------------------------------------------------------------------------------------------
+__host__ __device__ inline int64_t kv_block_elems(int D) { return 32 * (int64_t)D; }
+__host__ __device__ inline int64_t kcache_offset(int64_t key, int d, int D) {
+  int64_t kb = key >> 4;
+  int kk = (int)(key & 15);
+  int dk = d >> 4, dd = d & 15;
+  int g = kk & 7, hik = kk >> 3;
+  int t = (dd & 7) >> 1, e = dd & 1, hid = dd >> 3;
+  return kb * kv_block_elems(D) + (int64_t)dk * 256 + (g * 4 + t) * 8 + (hid * 2 + hik) * 2 + e;
+}
+__host__ __device__ inline int64_t vcache_offset(int64_t key, int d, int D) {
+  int64_t kb = key >> 4;
+  int kk = (int)(key & 15);
+  int dm = d >> 4, dd = d & 15;
+  int g = dd & 7, hid = dd >> 3;
+  int t = (kk & 7) >> 1, e = kk & 1, hik = kk >> 3;
+  return kb * kv_block_elems(D) + (int64_t)(D / 16 + dm) * 256 + (g * 4 + t) * 8 + (hik * 2 + hid) * 2 + e;
+}
+
+// element conversions
+__device__ inline float to_f32(float v) { return v; }
+__device__ inline float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ inline T from_f32(float v);
+template <> __device__ inline float from_f32<float>(float v) { return v; }
+template <> __device__ inline __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+}  // namespace lmb

@@ -1,0 +1,970 @@
+// Model weights (tiled, sharded), the decode session and its CUDA graph.
+#include <math.h>
+#include <string.h>
+
+#include <type_traits>
+
+#include "model.cuh"
+
+namespace lmb {
+
+// ---------------------------------------------------------------------------------------------
+// logical <-> internal index maps
+// ---------------------------------------------------------------------------------------------
+// Internal element (row i, col k) of a tiled matrix -> (slot, logical row, logical col) of the
+// reference tensor it comes from; false for padding.
+__host__ __device__ inline bool wmap_resolve(const WMap& m, int i, int k, int* slot, int* lrow, int* lcol) {
+  if (i >= m.rows || k >= m.K) return false;
+  switch (m.kind) {
+    case MAP_PLAIN:
+      *slot = 0; *lrow = i; *lcol = k;
+      return true;
+    case MAP_QKV: {
+      const int tile = i >> 4, r = i & 15;
+      const int tph = m.D >> 4;
+      const int hs = tile / tph, j = tile - hs * tph;
+      *lcol = k;
+      if (hs < m.Hl) {           // q head: local order (kv-local, group) -> global h = kv + KV*g
+        const int kvl = hs / m.G, g = hs - kvl * m.G;
+        const int h = (m.kv_off + kvl) + m.KV * g;
+        const int d = 8 * j + (r & 7) + (r >> 3) * (m.D >> 1);
+        *slot = 0; *lrow = h + m.H * d;           // feature f = h + H*d
+      } else if (hs < m.Hl + m.KVl) {
+        const int kvh = m.kv_off + (hs - m.Hl);
+        const int d = 8 * j + (r & 7) + (r >> 3) * (m.D >> 1);
+        *slot = 1; *lrow = kvh + m.KV * d;
+      } else {
+        const int kvh = m.kv_off + (hs - m.Hl - m.KVl);
+        const int d = 16 * j + r;
+        *slot = 2; *lrow = kvh + m.KV * d;
+      }
+      return true;
+    }
+    case MAP_O: {                // columns follow the attention output order (local head, d)
+      const int hl = k / m.D, d = k - hl * m.D;
+      const int kvl = hl / m.G, g = hl - kvl * m.G;
+      const int h = (m.kv_off + kvl) + m.KV * g;
+      *slot = 0; *lrow = i; *lcol = h + m.H * d;
+      return true;
+    }
+    case MAP_GATEUP: {           // 16-row tiles: 8 gate rows then the 8 matching up rows
+      const int tile = i >> 4, r = i & 15;
+      const int idx = 8 * tile + (r & 7);
+      if (idx >= m.inter_l) return false;
+      *slot = r >> 3; *lrow = m.inter_off + idx; *lcol = k;
+      return true;
+    }
+    case MAP_DOWN:
+      *slot = 0; *lrow = i; *lcol = m.inter_off + k;
+      return true;
+  }
+  return false;
+}
+
+struct FillSrc {
+  uint64_t key[3];
+  const float* src[3];     // staged logical tensors (NULL -> generator)
+  int colmajor;
+  int only_slot;           // -1: all
+  float scale;             // sigma / 131072
+};
+
+template <typename WT>
+__global__ void fill_tiled_kernel(WT* dst, WMap m, FillSrc f) {
+  const int64_t total = (int64_t)m.RB * m.KC * 512;
+  for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total;
+       o += (int64_t)gridDim.x * blockDim.x) {
+    const int e16 = (int)(o & 15);
+    const int lane = (int)((o >> 4) & 31);
+    const int64_t unit = o >> 9;
+    const int kc = (int)(unit % m.KC);
+    const int rb = (int)(unit / m.KC);
+    const int g = lane >> 2, t = lane & 3;
+    const int i = rb * 16 + g + 8 * (e16 >> 3);
+    const int k = kc * 32 + 8 * t + (e16 & 7);
+    int slot, lrow, lcol;
+    if (!wmap_resolve(m, i, k, &slot, &lrow, &lcol)) {
+      if (f.only_slot < 0) dst[o] = from_f32<WT>(0.f);
+      continue;
+    }
+    if (f.only_slot >= 0 && slot != f.only_slot) continue;
+    float v;
+    if (f.src[slot]) {
+      const int64_t idx = f.colmajor ? (int64_t)lrow + (int64_t)m.src_rows[slot] * lcol
+                                     : (int64_t)lrow * m.src_cols[slot] + lcol;
+      v = f.src[slot][idx];
+    } else {
+      v = synth_value(f.key[slot], (uint64_t)lrow * m.src_cols[slot] + lcol, f.scale, 0.f);
+    }
+    dst[o] = from_f32<WT>(v);
+  }
+}
+
+// plain row-major tensors (embedding table, norm gains)
+template <typename WT>
+__global__ void fill_plain_kernel(WT* dst, int64_t rows, int64_t cols, uint64_t key, const float* src,
+                                  int colmajor, float scale, float offset) {
+  const int64_t total = rows * cols;
+  for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total;
+       o += (int64_t)gridDim.x * blockDim.x) {
+    float v;
+    if (src) {
+      const int64_t r = o / cols, c = o - r * cols;
+      v = src[colmajor ? r + rows * c : o];
+    } else {
+      v = synth_value(key, (uint64_t)o, scale, offset);
+    }
+    dst[o] = from_f32<WT>(v);
+  }
+}
+
+template <typename WT>
+__global__ void fill_kv_kernel(WT* kv, int64_t batch_stride, int64_t head_stride, int B, int KVl,
+                               int KV, int kv_off, int D, int n_pos, int max_ctx, uint64_t key_k,
+                               uint64_t key_v) {
+  const int64_t total = (int64_t)B * KVl * n_pos * D;
+  const float scale = 1.0f / 131072.0f;
+  for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total;
+       o += (int64_t)gridDim.x * blockDim.x) {
+    const int d = (int)(o % D);
+    const int pos = (int)((o / D) % n_pos);
+    const int kvl = (int)((o / ((int64_t)D * n_pos)) % KVl);
+    const int b = (int)(o / ((int64_t)D * n_pos * KVl));
+    // logical index in a [B, KV, max_ctx, D] tensor
+    const uint64_t li = (((uint64_t)b * KV + (kv_off + kvl)) * max_ctx + pos) * D + d;
+    WT* base = kv + b * batch_stride + kvl * head_stride;
+    base[kcache_offset(pos, d, D)] = from_f32<WT>(synth_value(key_k, li, scale, 0.f));
+    base[vcache_offset(pos, d, D)] = from_f32<WT>(synth_value(key_v, li, scale, 0.f));
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// small fused kernels of the decode step
+// ---------------------------------------------------------------------------------------------
+// x <- embedding row (first layer) or x + delta (residual add of the previous projection), then
+// xn = (x * recip(sqrt(mean(x*x) + eps))) * w          src/HighLevelOps.jl:299-304, NN.jl:149-161
+template <typename WT>
+__global__ void __launch_bounds__(256) add_rmsnorm_kernel(float* x, const float* delta, const int* tokens,
+                                                          const WT* embed, int vocab, const float* w,
+                                                          WT* xn, int xn_pitch, int n, float eps,
+                                                          float* capture) {
+  __shared__ float red[8];
+  const int b = blockIdx.x, tid = threadIdx.x;
+  float* xr = x + (int64_t)b * n;
+  float ss = 0.f;
+  if (tokens) {
+    const int tok = tokens[b];
+    const bool ok = tok >= 0 && tok < vocab;     // out of range -> zeros, as _gather_kernel! does
+    const WT* er = embed + (int64_t)(ok ? tok : 0) * n;
+    for (int i = tid; i < n; i += 256) {
+      const float v = ok ? to_f32(er[i]) : 0.f;
+      xr[i] = v;
+      ss += v * v;
+    }
+  } else {
+    const float* dr = delta ? delta + (int64_t)b * n : nullptr;
+    for (int i = tid; i < n; i += 256) {
+      const float v = dr ? xr[i] + dr[i] : xr[i];
+      xr[i] = v;
+      if (capture) capture[(int64_t)b * n + i] = v;
+      ss += v * v;
+    }
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+  if ((tid & 31) == 0) red[tid >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tot += red[i];
+  const float var = tot * (1.0f / (float)n);
+  const float inv = 1.0f / sqrtf(var + eps);
+  if (xn) {
+    WT* o = xn + (int64_t)b * xn_pitch;
+    for (int i = tid; i < n; i += 256) o[i] = from_f32<WT>((xr[i] * inv) * w[i]);
+  }
+}
+
+// greedy token: first maximum of the logits row; also logs it for the device-resident loop
+__global__ void __launch_bounds__(256) argmax_step_kernel(const float* logits, int pitch, int n, int* tokens,
+                                                          int* hist, const int* step_ctr, int B) {
+  __shared__ float sv[256];
+  __shared__ int si[256];
+  const int b = blockIdx.x, tid = threadIdx.x;
+  const float* row = logits + (int64_t)b * pitch;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = tid; i < n; i += 256) {
+    const float v = row[i];
+    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+  }
+  sv[tid] = best;
+  si[tid] = bi;
+  __syncthreads();
+  for (int off = 128; off > 0; off >>= 1) {
+    if (tid < off) {
+      const float v = sv[tid + off];
+      const int i = si[tid + off];
+      if (v > sv[tid] || (v == sv[tid] && i < si[tid])) { sv[tid] = v; si[tid] = i; }
+    }
+    __syncthreads();
+  }
+  if (tid == 0) {
+    tokens[b] = si[0];
+    if (hist) hist[(int64_t)(*step_ctr) * B + b] = si[0];
+  }
+}
+
+__global__ void advance_kernel(int* pos, int* step_ctr) {
+  *pos += 1;
+  *step_ctr += 1;
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+Model* model_from(lmb200_model h) {
+  Model* m = reinterpret_cast<Model*>(h);
+  if (!m || m->magic != 0x4D4F444C) { set_error("invalid model handle"); return nullptr; }
+  return m;
+}
+Session* session_from(lmb200_session h) {
+  Session* s = reinterpret_cast<Session*>(h);
+  if (!s || s->magic != 0x53455353) { set_error("invalid session handle"); return nullptr; }
+  return s;
+}
+
+namespace {
+
+int fill_grid(int64_t total) {
+  int64_t g = ceil_div(total, 256);
+  if (g > 148 * 32) g = 148 * 32;
+  if (g < 1) g = 1;
+  return (int)g;
+}
+
+uint64_t layer_tensor_id(int layer, int slot) { return (uint64_t)16 * layer + slot; }
+enum Slot { S_ATTN_NORM = 0, S_Q = 1, S_K = 2, S_V = 3, S_O = 4, S_FFN_NORM = 5, S_GATE = 6, S_UP = 7, S_DOWN = 8 };
+constexpr uint64_t kIdEmbed = 0xFFFF0, kIdFinalNorm = 0xFFFF1, kIdHead = 0xFFFF2;
+constexpr uint64_t kIdKvBase = 0x100000;
+
+int64_t tiled_elems(const WMap& m) { return (int64_t)m.RB * m.KC * 512; }
+
+template <typename WT>
+int32_t fill_tiled(Ctx* ctx, void* dst, const WMap& m, const FillSrc& f) {
+  fill_tiled_kernel<WT><<<fill_grid(tiled_elems(m)), 256, 0, ctx->stream>>>(reinterpret_cast<WT*>(dst), m, f);
+  ctx->launches++;
+  LMB_CUDA(cudaGetLastError());
+  return LMB200_OK;
+}
+int32_t fill_tiled_dt(Model* M, void* dst, const WMap& m, const FillSrc& f) {
+  return M->cfg.dtype == LMB200_BF16 ? fill_tiled<__nv_bfloat16>(M->ctx, dst, m, f)
+                                     : fill_tiled<float>(M->ctx, dst, m, f);
+}
+template <typename WT>
+int32_t fill_plain(Ctx* ctx, void* dst, int64_t rows, int64_t cols, uint64_t key, const float* src,
+                   int colmajor, float scale, float offset) {
+  fill_plain_kernel<WT><<<fill_grid(rows * cols), 256, 0, ctx->stream>>>(reinterpret_cast<WT*>(dst), rows, cols, key,
+                                                                         src, colmajor, scale, offset);
+  ctx->launches++;
+  LMB_CUDA(cudaGetLastError());
+  return LMB200_OK;
+}
+
+void finish_map(WMap& m) {
+  m.RB = (int)ceil_div(m.rows, 16);
+  m.KC = (int)ceil_div(m.K, 32);
+}
+
+int32_t dmalloc(void** p, int64_t bytes, bool zero, cudaStream_t st) {
+  *p = nullptr;
+  if (bytes <= 0) bytes = 16;
+  cudaError_t e = cudaMalloc(p, (size_t)bytes);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(LMB200_ENOMEM, "cudaMalloc of %lld bytes failed: %s", (long long)bytes, cudaGetErrorString(e));
+  }
+  if (zero) LMB_CUDA(cudaMemsetAsync(*p, 0, (size_t)bytes, st));
+  return LMB200_OK;
+}
+
+}  // namespace
+}  // namespace lmb
+
+using namespace lmb;
+
+// =============================================================================================
+// model
+// =============================================================================================
+extern "C" int32_t lmb200_model_create(lmb200_ctx hctx, const lmb200_model_config* cfg, lmb200_model* out) {
+  Ctx* ctx = ctx_from(hctx);
+  if (!ctx) return LMB200_EINVAL;
+  LMB_REQUIRE(cfg && out, "model_create: null argument");
+  const lmb200_model_config& c = *cfg;
+  LMB_REQUIRE(c.n_layers >= 1 && c.hidden >= 16 && c.n_heads >= 1 && c.n_kv_heads >= 1 && c.vocab >= 1 &&
+                  c.intermediate >= 8, "model_create: non-positive dimension");
+  LMB_REQUIRE(c.head_dim * c.n_heads == c.hidden, "model_create: head_dim %d * n_heads %d != hidden %d",
+              c.head_dim, c.n_heads, c.hidden);
+  LMB_REQUIRE(c.head_dim % 16 == 0, "model_create: head_dim %d must be a multiple of 16", c.head_dim);
+  LMB_REQUIRE(c.n_heads % c.n_kv_heads == 0, "model_create: n_heads %d not a multiple of n_kv_heads %d",
+              c.n_heads, c.n_kv_heads);
+  LMB_REQUIRE(c.dtype == LMB200_F32 || c.dtype == LMB200_BF16, "model_create: dtype %d", c.dtype);
+  LMB_REQUIRE(c.tp_size >= 1 && c.tp_rank >= 0 && c.tp_rank < c.tp_size, "model_create: tp rank %d of %d",
+              c.tp_rank, c.tp_size);
+  LMB_REQUIRE(c.n_kv_heads % c.tp_size == 0, "model_create: tp_size %d does not divide the %d kv heads",
+              c.tp_size, c.n_kv_heads);
+  LMB_REQUIRE(c.intermediate % c.tp_size == 0 && (c.intermediate / c.tp_size) % 8 == 0,
+              "model_create: intermediate %d / tp %d must be a multiple of 8", c.intermediate, c.tp_size);
+  LMB_REQUIRE(c.hidden % 4 == 0, "model_create: hidden %d must be a multiple of 4", c.hidden);
+  if (c.tp_size > 1)
+    LMB_REQUIRE(ctx->nccl_comm && ctx->tp_size == c.tp_size && ctx->tp_rank == c.tp_rank,
+                "model_create: tp_size %d needs lmb200_comm_init with the same ranks first", c.tp_size);
+  LMB_CUDA(cudaSetDevice(ctx->device));
+
+  Model* M = new Model();
+  M->ctx = ctx;
+  M->cfg = c;
+  M->esz = c.dtype == LMB200_BF16 ? 2 : 4;
+  M->D = c.head_dim;
+  M->G = c.n_heads / c.n_kv_heads;
+  M->KVl = c.n_kv_heads / c.tp_size;
+  M->Hl = M->KVl * M->G;
+  M->kv_off = c.tp_rank * M->KVl;
+  M->inter_l = c.intermediate / c.tp_size;
+  M->inter_off = c.tp_rank * M->inter_l;
+
+  auto base = [&](WMap& m, int kind) {
+    m.kind = kind;
+    m.H = c.n_heads; m.KV = c.n_kv_heads; m.D = M->D; m.G = M->G; m.Hl = M->Hl; m.KVl = M->KVl;
+    m.kv_off = M->kv_off; m.inter_l = M->inter_l; m.inter_off = M->inter_off;
+  };
+  base(M->m_qkv, MAP_QKV);
+  M->m_qkv.rows = (M->Hl + 2 * M->KVl) * M->D; M->m_qkv.K = c.hidden;
+  M->m_qkv.src_rows[0] = c.hidden; M->m_qkv.src_rows[1] = M->m_qkv.src_rows[2] = c.n_kv_heads * M->D;
+  M->m_qkv.src_cols[0] = M->m_qkv.src_cols[1] = M->m_qkv.src_cols[2] = c.hidden;
+  finish_map(M->m_qkv);
+  base(M->m_o, MAP_O);
+  M->m_o.rows = c.hidden; M->m_o.K = M->Hl * M->D;
+  M->m_o.src_rows[0] = c.hidden; M->m_o.src_cols[0] = c.n_heads * M->D;
+  finish_map(M->m_o);
+  base(M->m_gu, MAP_GATEUP);
+  M->m_gu.rows = 2 * M->inter_l; M->m_gu.K = c.hidden;
+  M->m_gu.src_rows[0] = M->m_gu.src_rows[1] = c.intermediate;
+  M->m_gu.src_cols[0] = M->m_gu.src_cols[1] = c.hidden;
+  finish_map(M->m_gu);
+  base(M->m_down, MAP_DOWN);
+  M->m_down.rows = c.hidden; M->m_down.K = M->inter_l;
+  M->m_down.src_rows[0] = c.hidden; M->m_down.src_cols[0] = c.intermediate;
+  finish_map(M->m_down);
+  base(M->m_head, MAP_PLAIN);
+  M->m_head.rows = c.vocab; M->m_head.K = c.hidden;
+  M->m_head.src_rows[0] = c.vocab; M->m_head.src_cols[0] = c.hidden;
+  finish_map(M->m_head);
+
+  int32_t rc = LMB200_OK;
+  auto alloc = [&](void** p, int64_t bytes) {
+    if (rc != LMB200_OK) return;
+    rc = dmalloc(p, bytes, true, ctx->stream);
+    if (rc == LMB200_OK) M->weight_bytes += bytes;
+  };
+  M->layers.resize(c.n_layers);
+  for (auto& L : M->layers) {
+    alloc(&L.wqkv, tiled_elems(M->m_qkv) * M->esz);
+    alloc(&L.wo, tiled_elems(M->m_o) * M->esz);
+    alloc(&L.wgu, tiled_elems(M->m_gu) * M->esz);
+    alloc(&L.wdown, tiled_elems(M->m_down) * M->esz);
+    alloc((void**)&L.attn_norm, (int64_t)c.hidden * 4);
+    alloc((void**)&L.ffn_norm, (int64_t)c.hidden * 4);
+  }
+  alloc(&M->embed, (int64_t)c.vocab * c.hidden * M->esz);
+  alloc((void**)&M->final_norm, (int64_t)c.hidden * 4);
+  alloc(&M->lm_head, tiled_elems(M->m_head) * M->esz);
+  alloc((void**)&M->inv_freq, (int64_t)(M->D / 2) * 4);
+  if (rc != LMB200_OK) { lmb200_model_destroy(reinterpret_cast<lmb200_model>(M)); return rc; }
+
+  // inv_freq[i] = recip(exp2((i*2*(1/D)) * log2(base)))              src/NN.jl:261-263
+  std::vector<float> inv(M->D / 2);
+  const float l2b = log2f(c.rope_base);
+  for (int i = 0; i < M->D / 2; ++i) {
+    volatile float f = (float)i * 2.0f;
+    f = f * (1.0f / (float)M->D);
+    f = f * l2b;
+    inv[i] = 1.0f / exp2f(f);
+  }
+  LMB_CUDA(cudaMemcpyAsync(M->inv_freq, inv.data(), inv.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
+  LMB_CUDA(cudaStreamSynchronize(ctx->stream));
+  *out = reinterpret_cast<lmb200_model>(M);
+  return LMB200_OK;
+}
+
+extern "C" int32_t lmb200_model_destroy(lmb200_model h) {
+  Model* M = model_from(h);
+  if (!M) return LMB200_EINVAL;
+  cudaSetDevice(M->ctx->device);
+  for (auto& L : M->layers) {
+    cudaFree(L.wqkv); cudaFree(L.wo); cudaFree(L.wgu); cudaFree(L.wdown);
+    cudaFree(L.attn_norm); cudaFree(L.ffn_norm);
+  }
+  cudaFree(M->embed); cudaFree(M->final_norm); cudaFree(M->lm_head); cudaFree(M->inv_freq);
+  M->magic = 0;
+  delete M;
+  return LMB200_OK;
+}
+
+extern "C" int32_t lmb200_model_weight_bytes(lmb200_model h, int64_t* bytes) {
+  Model* M = model_from(h);
+  if (!M || !bytes) return LMB200_EINVAL;
+  *bytes = M->weight_bytes;
+  return LMB200_OK;
+}
+
+extern "C" int32_t lmb200_model_init_random(lmb200_model h, uint64_t seed, float sigma) {
+  Model* M = model_from(h);
+  if (!M) return LMB200_EINVAL;
+  Ctx* ctx = M->ctx;
+  LMB_CUDA(cudaSetDevice(ctx->device));
+  const float scale = sigma / 131072.0f;
+  const int hid = M->cfg.hidden;
+  for (int l = 0; l < M->cfg.n_layers; ++l) {
+    LayerWeights& L = M->layers[l];
+    FillSrc f{};
+    f.only_slot = -1; f.scale = scale; f.colmajor = 0;
+    f.src[0] = f.src[1] = f.src[2] = nullptr;
+    f.key[0] = stream_key(seed, layer_tensor_id(l, S_Q));
+    f.key[1] = stream_key(seed, layer_tensor_id(l, S_K));
+    f.key[2] = stream_key(seed, layer_tensor_id(l, S_V));
+    LMB_TRY(fill_tiled_dt(M, L.wqkv, M->m_qkv, f));
+    f.key[0] = stream_key(seed, layer_tensor_id(l, S_O));
+    LMB_TRY(fill_tiled_dt(M, L.wo, M->m_o, f));
+    f.key[0] = stream_key(seed, layer_tensor_id(l, S_GATE));
+    f.key[1] = stream_key(seed, layer_tensor_id(l, S_UP));
+    LMB_TRY(fill_tiled_dt(M, L.wgu, M->m_gu, f));
+    f.key[0] = stream_key(seed, layer_tensor_id(l, S_DOWN));
+    LMB_TRY(fill_tiled_dt(M, L.wdown, M->m_down, f));
+    LMB_TRY(fill_plain<float>(ctx, L.attn_norm, 1, hid, stream_key(seed, layer_tensor_id(l, S_ATTN_NORM)), nullptr, 0, scale, 1.0f));
+    LMB_TRY(fill_plain<float>(ctx, L.ffn_norm, 1, hid, stream_key(seed, layer_tensor_id(l, S_FFN_NORM)), nullptr, 0, scale, 1.0f));
+  }
+  if (M->cfg.dtype == LMB200_BF16)
+    LMB_TRY(fill_plain<__nv_bfloat16>(ctx, M->embed, M->cfg.vocab, hid, stream_key(seed, kIdEmbed), nullptr, 0, scale, 0.f));
+  else
+    LMB_TRY(fill_plain<float>(ctx, M->embed, M->cfg.vocab, hid, stream_key(seed, kIdEmbed), nullptr, 0, scale, 0.f));
+  LMB_TRY(fill_plain<float>(ctx, M->final_norm, 1, hid, stream_key(seed, kIdFinalNorm), nullptr, 0, scale, 1.0f));
+  FillSrc f{};
+  f.only_slot = -1; f.scale = scale;
+  f.key[0] = stream_key(seed, kIdHead);
+  LMB_TRY(fill_tiled_dt(M, M->lm_head, M->m_head, f));
+  LMB_CUDA(cudaStreamSynchronize(ctx->stream));
+  return LMB200_OK;
+}
+
+extern "C" int32_t lmb200_model_set_weight(lmb200_model h, const char* name, const float* host, int32_t layout) {
+  Model* M = model_from(h);
+  if (!M) return LMB200_EINVAL;
+  LMB_REQUIRE(name && host, "set_weight: null argument");
+  LMB_REQUIRE(layout == LMB200_ROWMAJOR || layout == LMB200_COLMAJOR, "set_weight: layout %d", layout);
+  Ctx* ctx = M->ctx;
+  LMB_CUDA(cudaSetDevice(ctx->device));
+  const lmb200_model_config& c = M->cfg;
+  const std::string n(name);
+  // resolve the name
+  void* dst = nullptr;
+  const WMap* map = nullptr;
+  int slot = 0;
+  int64_t rows = 0, cols = 0;
+  bool plain_f32 = false, plain_embed = false;
+  if (n == "model.embed_tokens.weight") { dst = M->embed; rows = c.vocab; cols = c.hidden; plain_embed = true; }
+  else if (n == "model.norm.weight") { dst = M->final_norm; rows = 1; cols = c.hidden; plain_f32 = true; }
+  else if (n == "lm_head.weight") { dst = M->lm_head; map = &M->m_head; rows = c.vocab; cols = c.hidden; }
+  else {
+    int layer = -1, used = 0;
+    if (sscanf(name, "model.layers.%d.%n", &layer, &used) < 1 || layer < 0 || layer >= c.n_layers)
+      return fail(LMB200_EINVAL, "set_weight: unknown tensor '%s'", name);
+    const std::string tail(name + used);
+    LayerWeights& L = M->layers[layer];
+    const int kvd = c.n_kv_heads * M->D;
+    if (tail == "input_layernorm.weight") { dst = L.attn_norm; rows = 1; cols = c.hidden; plain_f32 = true; }
+    else if (tail == "post_attention_layernorm.weight") { dst = L.ffn_norm; rows = 1; cols = c.hidden; plain_f32 = true; }
+    else if (tail == "self_attn.q_proj.weight") { dst = L.wqkv; map = &M->m_qkv; slot = 0; rows = c.hidden; cols = c.hidden; }
+    else if (tail == "self_attn.k_proj.weight") { dst = L.wqkv; map = &M->m_qkv; slot = 1; rows = kvd; cols = c.hidden; }
+    else if (tail == "self_attn.v_proj.weight") { dst = L.wqkv; map = &M->m_qkv; slot = 2; rows = kvd; cols = c.hidden; }
+    else if (tail == "self_attn.o_proj.weight") { dst = L.wo; map = &M->m_o; rows = c.hidden; cols = c.hidden; }
+    else if (tail == "mlp.gate_proj.weight") { dst = L.wgu; map = &M->m_gu; slot = 0; rows = c.intermediate; cols = c.hidden; }
+    else if (tail == "mlp.up_proj.weight") { dst = L.wgu; map = &M->m_gu; slot = 1; rows = c.intermediate; cols = c.hidden; }
+    else if (tail == "mlp.down_proj.weight") { dst = L.wdown; map = &M->m_down; rows = c.hidden; cols = c.intermediate; }
+    else return fail(LMB200_EINVAL, "set_weight: unknown tensor '%s'", name);
+  }
+  float* stage = nullptr;
+  const int64_t bytes = rows * cols * 4;
+  LMB_TRY(dmalloc((void**)&stage, bytes, false, ctx->stream));
+  int32_t rc = LMB200_OK;
+  do {
+    if (cudaMemcpyAsync(stage, host, (size_t)bytes, cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess) {
+      rc = fail(LMB200_ECUDA, "set_weight: upload failed"); break;
+    }
+    if (plain_f32) {
+      rc = fill_plain<float>(ctx, dst, rows, cols, 0, stage, 0, 0.f, 0.f);
+    } else if (plain_embed) {
+      rc = c.dtype == LMB200_BF16 ? fill_plain<__nv_bfloat16>(ctx, dst, rows, cols, 0, stage, layout, 0.f, 0.f)
+                                  : fill_plain<float>(ctx, dst, rows, cols, 0, stage, layout, 0.f, 0.f);
+    } else {
+      FillSrc f{};
+      f.only_slot = slot; f.colmajor = layout; f.scale = 0.f;
+      f.src[0] = f.src[1] = f.src[2] = nullptr;
+      f.src[slot] = stage;
+      rc = fill_tiled_dt(M, dst, *map, f);
+    }
+  } while (0);
+  cudaStreamSynchronize(ctx->stream);
+  cudaFree(stage);
+  return rc;
+}
+
+// =============================================================================================
+// session
+// =============================================================================================
+namespace lmb {
+namespace {
+
+template <typename WT>
+int32_t enqueue_step_t(Session* S, cudaStream_t st, bool with_head) {
+  Model* M = S->m;
+  Ctx* ctx = M->ctx;
+  const lmb200_model_config& c = M->cfg;
+  const int dt = c.dtype;
+  const int B = S->B, hid = c.hidden;
+  const int L = c.n_layers;
+  for (int l = 0; l < L; ++l) {
+    LayerWeights& W = M->layers[l];
+    // residual add of the previous MLP (or the embedding gather) + attention RMSNorm
+    add_rmsnorm_kernel<WT><<<B, 256, 0, st>>>(
+        S->x, l == 0 ? nullptr : S->delta, l == 0 ? S->tokens : nullptr, reinterpret_cast<const WT*>(M->embed),
+        c.vocab, W.attn_norm, reinterpret_cast<WT*>(S->xn), S->xn_pitch, hid, c.rms_eps,
+        (S->capture_on && l > 0) ? S->capture + (int64_t)(l - 1) * B * hid : nullptr);
+    ctx->launches++;
+    LMB_CUDA(cudaGetLastError());
+    void* kv_layer = reinterpret_cast<char*>(S->kv) + (int64_t)l * S->kv_layer_stride * M->esz;
+    {  // q/k/v projections + RoPE + KV append
+      GemvParams p;
+      p.W = W.wqkv; p.x = S->xn; p.B = B; p.x_pitch = S->xn_pitch;
+      p.rows = M->m_qkv.rows; p.RB = M->m_qkv.RB; p.KC = M->m_qkv.KC;
+      p.ksplit = S->p_qkv.ksplit; p.kc_per_split = S->p_qkv.kc_per_split;
+      p.partials = S->gemv_partials; p.counters = S->gemv_counters;
+      p.epi = EPI_QKV_ROPE;
+      p.q_out = S->qbuf; p.q_pitch = S->q_pitch;
+      p.kv_layer = kv_layer; p.kv_batch_stride = S->kv_batch_stride; p.kv_head_stride = S->kv_head_stride;
+      p.inv_freq = M->inv_freq; p.pos = S->pos; p.Hl = M->Hl; p.KVl = M->KVl; p.D = M->D;
+      LMB_TRY(gemv_launch(ctx, dt, p, st));
+    }
+    {  // attention over the cache
+      AttnParams a;
+      a.q = S->qbuf; a.q_pitch = S->q_pitch; a.kv_layer = kv_layer;
+      a.kv_batch_stride = S->kv_batch_stride; a.kv_head_stride = S->kv_head_stride;
+      a.B = B; a.KVl = M->KVl; a.G = M->G; a.D = M->D; a.pos = S->pos;
+      a.keys_per_cta = S->keys_per_cta; a.nsplit = S->nsplit;
+      a.scale = 1.0f / sqrtf((float)M->D);
+      a.part_o = S->part_o; a.part_ml = S->part_ml; a.out = S->attn_out; a.out_pitch = S->q_pitch;
+      LMB_TRY(attn_decode_launch(ctx, dt, a, st));
+    }
+    {  // o_proj (row-parallel under TP)
+      GemvParams p;
+      p.W = W.wo; p.x = S->attn_out; p.B = B; p.x_pitch = S->q_pitch;
+      p.rows = M->m_o.rows; p.RB = M->m_o.RB; p.KC = M->m_o.KC;
+      p.ksplit = S->p_o.ksplit; p.kc_per_split = S->p_o.kc_per_split;
+      p.partials = S->gemv_partials; p.counters = S->gemv_counters;
+      p.epi = EPI_STORE_F32; p.out = S->delta; p.out_pitch = hid;
+      LMB_TRY(gemv_launch(ctx, dt, p, st));
+      if (c.tp_size > 1) LMB_TRY(nccl_allreduce_f32(ctx, S->delta, (int64_t)B * hid, st));
+    }
+    add_rmsnorm_kernel<WT><<<B, 256, 0, st>>>(S->x, S->delta, nullptr, nullptr, 0, W.ffn_norm,
+                                              reinterpret_cast<WT*>(S->xn), S->xn_pitch, hid, c.rms_eps, nullptr);
+    ctx->launches++;
+    LMB_CUDA(cudaGetLastError());
+    {  // gate/up + SiLU gate
+      GemvParams p;
+      p.W = W.wgu; p.x = S->xn; p.B = B; p.x_pitch = S->xn_pitch;
+      p.rows = M->m_gu.rows; p.RB = M->m_gu.RB; p.KC = M->m_gu.KC;
+      p.ksplit = S->p_gu.ksplit; p.kc_per_split = S->p_gu.kc_per_split;
+      p.partials = S->gemv_partials; p.counters = S->gemv_counters;
+      p.epi = EPI_SILU_GATE; p.act = S->act; p.act_pitch = S->act_pitch; p.n_act = M->inter_l;
+      LMB_TRY(gemv_launch(ctx, dt, p, st));
+    }
+    {  // down_proj (row-parallel under TP)
+      GemvParams p;
+      p.W = W.wdown; p.x = S->act; p.B = B; p.x_pitch = S->act_pitch;
+      p.rows = M->m_down.rows; p.RB = M->m_down.RB; p.KC = M->m_down.KC;
+      p.ksplit = S->p_down.ksplit; p.kc_per_split = S->p_down.kc_per_split;
+      p.partials = S->gemv_partials; p.counters = S->gemv_counters;
+      p.epi = EPI_STORE_F32; p.out = S->delta; p.out_pitch = hid;
+      LMB_TRY(gemv_launch(ctx, dt, p, st));
+      if (c.tp_size > 1) LMB_TRY(nccl_allreduce_f32(ctx, S->delta, (int64_t)B * hid, st));
+    }
+  }
+  // last residual add (+ final norm); without the head only the add is needed for the capture
+  add_rmsnorm_kernel<WT><<<B, 256, 0, st>>>(S->x, S->delta, nullptr, nullptr, 0, M->final_norm,
+                                            with_head ? reinterpret_cast<WT*>(S->xn) : nullptr, S->xn_pitch, hid,
+                                            c.rms_eps,
+                                            S->capture_on ? S->capture + (int64_t)(L - 1) * B * hid : nullptr);
+  ctx->launches++;
+  LMB_CUDA(cudaGetLastError());
+  if (with_head) {
+    GemvParams p;
+    p.W = M->lm_head; p.x = S->xn; p.B = B; p.x_pitch = S->xn_pitch;
+    p.rows = M->m_head.rows; p.RB = M->m_head.RB; p.KC = M->m_head.KC;
+    p.ksplit = S->p_head.ksplit; p.kc_per_split = S->p_head.kc_per_split;
+    p.partials = S->gemv_partials; p.counters = S->gemv_counters;
+    p.epi = EPI_STORE_F32; p.out = S->logits; p.out_pitch = S->logits_pitch;
+    LMB_TRY(gemv_launch(ctx, dt, p, st));
+    argmax_step_kernel<<<B, 256, 0, st>>>(S->logits, S->logits_pitch, c.vocab, S->tokens, S->tok_hist, S->step_ctr, B);
+    ctx->launches++;
+    LMB_CUDA(cudaGetLastError());
+  }
+  advance_kernel<<<1, 1, 0, st>>>(S->pos, S->step_ctr);
+  ctx->launches++;
+  LMB_CUDA(cudaGetLastError());
+  return LMB200_OK;
+}
+
+int32_t enqueue_step(Session* S, cudaStream_t st, bool with_head) {
+  return S->m->cfg.dtype == LMB200_BF16 ? enqueue_step_t<__nv_bfloat16>(S, st, with_head)
+                                        : enqueue_step_t<float>(S, st, with_head);
+}
+
+void drop_graphs(Session* S) {
+  if (S->graph_full) cudaGraphExecDestroy(S->graph_full);
+  if (S->graph_body) cudaGraphExecDestroy(S->graph_body);
+  S->graph_full = S->graph_body = nullptr;
+  S->graph_stream = nullptr;
+}
+
+int32_t capture_one(Session* S, cudaStream_t st, bool with_head, cudaGraphExec_t* exec, int* nodes) {
+  Ctx* ctx = S->m->ctx;
+  const int64_t before = ctx->launches;
+  LMB_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+  int32_t rc = enqueue_step(S, st, with_head);
+  cudaGraph_t graph = nullptr;
+  cudaError_t e = cudaStreamEndCapture(st, &graph);
+  ctx->launches = before;            // captured, not run
+  if (rc != LMB200_OK) { if (graph) cudaGraphDestroy(graph); return rc; }
+  if (e != cudaSuccess) return fail(LMB200_ECUDA, "graph capture failed: %s", cudaGetErrorString(e));
+  size_t n = 0;
+  cudaGraphGetNodes(graph, nullptr, &n);
+  *nodes = (int)n;
+  e = cudaGraphInstantiate(exec, graph, 0);
+  cudaGraphDestroy(graph);
+  if (e != cudaSuccess) return fail(LMB200_ECUDA, "graph instantiate failed: %s", cudaGetErrorString(e));
+  return LMB200_OK;
+}
+
+// graphs are tied to the stream they were captured on and to the capture flag
+int32_t ensure_graphs(Session* S) {
+  Ctx* ctx = S->m->ctx;
+  if (S->graph_full && S->graph_stream == ctx->stream) return LMB200_OK;
+  drop_graphs(S);
+  LMB_TRY(capture_one(S, ctx->stream, true, &S->graph_full, &S->graph_nodes_full));
+  LMB_TRY(capture_one(S, ctx->stream, false, &S->graph_body, &S->graph_nodes_body));
+  S->graph_stream = ctx->stream;
+  return LMB200_OK;
+}
+
+int32_t run_step(Session* S, bool with_head) {
+  Ctx* ctx = S->m->ctx;
+  LMB_TRY(ensure_graphs(S));
+  LMB_CUDA(cudaGraphLaunch(with_head ? S->graph_full : S->graph_body, ctx->stream));
+  ctx->launches += with_head ? S->graph_nodes_full : S->graph_nodes_body;
+  S->host_pos += 1;
+  return LMB200_OK;
+}
+
+}  // namespace
+}  // namespace lmb
+
+extern "C" int32_t lmb200_session_create(lmb200_model hm, int32_t batch, int32_t max_ctx, lmb200_session* out) {
+  Model* M = model_from(hm);
+  if (!M) return LMB200_EINVAL;
+  LMB_REQUIRE(out, "session_create: null argument");
+  LMB_REQUIRE(batch >= 1 && batch <= 32, "session_create: batch %d outside 1..32", batch);
+  LMB_REQUIRE(max_ctx >= 1, "session_create: max_ctx %d", max_ctx);
+  Ctx* ctx = M->ctx;
+  LMB_CUDA(cudaSetDevice(ctx->device));
+  const lmb200_model_config& c = M->cfg;
+  Session* S = new Session();
+  S->m = M; S->B = batch; S->max_ctx = max_ctx;
+  S->cap = (int)round_up(max_ctx, 64);
+  S->kv_head_stride = (int64_t)(S->cap / 16) * kv_block_elems(M->D);
+  S->kv_batch_stride = S->kv_head_stride * M->KVl;
+  S->kv_layer_stride = S->kv_batch_stride * batch;
+  S->xn_pitch = (int)round_up(c.hidden, 32);
+  S->q_pitch = (int)round_up(M->Hl * M->D, 32);
+  S->act_pitch = (int)round_up(M->inter_l, 32);
+  S->logits_pitch = (int)round_up(c.vocab, 16);
+
+  int64_t max_part = 0;
+  int max_cnt = 0;
+  auto plan = [&](GemvPlan& g, const WMap& m) {
+    int64_t pf; int nc;
+    gemv_plan(ctx, c.dtype, batch, m.RB, m.KC, &g.ksplit, &g.kc_per_split, &pf, &nc);
+    if (pf > max_part) max_part = pf;
+    if (nc > max_cnt) max_cnt = nc;
+  };
+  plan(S->p_qkv, M->m_qkv); plan(S->p_o, M->m_o); plan(S->p_gu, M->m_gu); plan(S->p_down, M->m_down);
+  plan(S->p_head, M->m_head);
+  int64_t po, pml;
+  attn_plan(ctx, batch, M->KVl, M->G, M->D, S->cap, &S->keys_per_cta, &S->nsplit, &po, &pml);
+
+  int32_t rc = LMB200_OK;
+  auto alloc = [&](void** p, int64_t bytes) { if (rc == LMB200_OK) rc = dmalloc(p, bytes, true, ctx->stream); };
+  alloc(&S->kv, S->kv_layer_stride * c.n_layers * M->esz);
+  alloc((void**)&S->x, (int64_t)batch * c.hidden * 4);
+  alloc((void**)&S->delta, (int64_t)batch * c.hidden * 4);
+  alloc((void**)&S->logits, (int64_t)batch * S->logits_pitch * 4);
+  alloc(&S->xn, (int64_t)batch * S->xn_pitch * M->esz);
+  alloc(&S->qbuf, (int64_t)batch * S->q_pitch * M->esz);
+  alloc(&S->attn_out, (int64_t)batch * S->q_pitch * M->esz);
+  alloc(&S->act, (int64_t)batch * S->act_pitch * M->esz);
+  alloc((void**)&S->tokens, (int64_t)batch * 4);
+  alloc((void**)&S->pos, 4);
+  alloc((void**)&S->step_ctr, 4);
+  alloc((void**)&S->tok_hist, (int64_t)(S->cap + 1) * batch * 4);
+  alloc((void**)&S->gemv_partials, max_part * 4);
+  alloc((void**)&S->gemv_counters, (int64_t)max_cnt * 4);
+  alloc((void**)&S->part_o, po * 4);
+  alloc((void**)&S->part_ml, pml * 4);
+  if (rc == LMB200_OK && cudaStreamSynchronize(ctx->stream) != cudaSuccess) rc = fail(LMB200_ECUDA, "session_create: sync failed");
+  if (rc != LMB200_OK) { lmb200_session_destroy(reinterpret_cast<lmb200_session>(S)); return rc; }
+  *out = reinterpret_cast<lmb200_session>(S);
+  return LMB200_OK;
+}
+
+extern "C" int32_t lmb200_session_destroy(lmb200_session h) {
+  Session* S = session_from(h);
+  if (!S) return LMB200_EINVAL;
+  cudaSetDevice(S->m->ctx->device);
+  cudaStreamSynchronize(S->m->ctx->stream);
+  drop_graphs(S);
+  cudaFree(S->kv); cudaFree(S->x); cudaFree(S->delta); cudaFree(S->logits); cudaFree(S->xn); cudaFree(S->qbuf);
+  cudaFree(S->attn_out); cudaFree(S->act); cudaFree(S->tokens); cudaFree(S->pos); cudaFree(S->step_ctr);
+  cudaFree(S->tok_hist); cudaFree(S->prompt); cudaFree(S->gemv_partials); cudaFree(S->gemv_counters);
+  cudaFree(S->part_o); cudaFree(S->part_ml); cudaFree(S->capture);
+  S->magic = 0;
+  delete S;
+  return LMB200_OK;
+}
+
+extern "C" int32_t lmb200_session_reset(lmb200_session h) {
+  Session* S = session_from(h);
+  if (!S) return LMB200_EINVAL;
+  Ctx* ctx = S->m->ctx;
+  LMB_CUDA(cudaSetDevice(ctx->device));
+  LMB_CUDA(cudaMemsetAsync(S->pos, 0, 4, ctx->stream));
+  LMB_CUDA(cudaMemsetAsync(S->step_ctr, 0, 4, ctx->stream));
+  LMB_CUDA(cudaStreamSynchronize(ctx->stream));
+  S->host_pos = 0;
+  return LMB200_OK;
+}
+
+extern "C" int32_t lmb200_session_position(lmb200_session h, int32_t* pos) {
+  Session* S = session_from(h);
+  if (!S || !pos) return LMB200_EINVAL;
+  *pos = S->host_pos;
+  return LMB200_OK;
+}
+
+extern "C" int32_t lmb200_session_set_position(lmb200_session h, int32_t pos) {
+  Session* S = session_from(h);
+  if (!S) return LMB200_EINVAL;
+  LMB_REQUIRE(pos >= 0 && pos <= S->max_ctx, "set_position: %d outside 0..%d", pos, S->max_ctx);
+  Ctx* ctx = S->m->ctx;
+  LMB_CUDA(cudaSetDevice(ctx->device));
+  LMB_CUDA(cudaMemcpyAsync(S->pos, &pos, 4, cudaMemcpyHostToDevice, ctx->stream));
+  LMB_CUDA(cudaStreamSynchronize(ctx->stream));
+  S->host_pos = pos;
+  return LMB200_OK;
+}
+
+extern "C" int32_t lmb200_session_fill_kv_random(lmb200_session h, int32_t n_pos, uint64_t seed) {
+  Session* S = session_from(h);
+  if (!S) return LMB200_EINVAL;
+  Model* M = S->m;
+  Ctx* ctx = M->ctx;
+  LMB_REQUIRE(n_pos >= 0 && n_pos <= S->max_ctx, "fill_kv_random: n_pos %d outside 0..%d", n_pos, S->max_ctx);
+  LMB_CUDA(cudaSetDevice(ctx->device));
+  if (n_pos > 0) {
+    for (int l = 0; l < M->cfg.n_layers; ++l) {
+      const uint64_t kk = stream_key(seed, kIdKvBase + 2 * l), kvv = stream_key(seed, kIdKvBase + 2 * l + 1);
+      const int64_t total = (int64_t)S->B * M->KVl * n_pos * M->D;
+      void* layer = reinterpret_cast<char*>(S->kv) + (int64_t)l * S->kv_layer_stride * M->esz;
+      if (M->cfg.dtype == LMB200_BF16)
+        fill_kv_kernel<__nv_bfloat16><<<fill_grid(total), 256, 0, ctx->stream>>>(
+            reinterpret_cast<__nv_bfloat16*>(layer), S->kv_batch_stride, S->kv_head_stride, S->B, M->KVl,
+            M->cfg.n_kv_heads, M->kv_off, M->D, n_pos, S->max_ctx, kk, kvv);
+      else
+        fill_kv_kernel<float><<<fill_grid(total), 256, 0, ctx->stream>>>(
+            reinterpret_cast<float*>(layer), S->kv_batch_stride, S->kv_head_stride, S->B, M->KVl,
+            M->cfg.n_kv_heads, M->kv_off, M->D, n_pos, S->max_ctx, kk, kvv);
+      ctx->launches++;
+      LMB_CUDA(cudaGetLastError());
+    }
+  }
+  LMB_CUDA(cudaMemcpyAsync(S->pos, &n_pos, 4, cudaMemcpyHostToDevice, ctx->stream));
+  LMB_CUDA(cudaStreamSynchronize(ctx->stream));
+  S->host_pos = n_pos;
+  return LMB200_OK;
+}
+
+extern "C" int32_t lmb200_session_set_capture(lmb200_session h, int32_t enable) {
+  Session* S = session_from(h);
+  if (!S) return LMB200_EINVAL;
+  Ctx* ctx = S->m->ctx;
+  LMB_CUDA(cudaSetDevice(ctx->device));
+  if (enable && !S->capture)
+    LMB_TRY(dmalloc((void**)&S->capture, (int64_t)S->m->cfg.n_layers * S->B * S->m->cfg.hidden * 4, true, ctx->stream));
+  if ((enable != 0) != S->capture_on) {
+    LMB_CUDA(cudaStreamSynchronize(ctx->stream));
+    drop_graphs(S);
+    S->capture_on = enable != 0;
+  }
+  return LMB200_OK;
+}
+
+extern "C" int32_t lmb200_session_read_layer_output(lmb200_session h, int32_t layer, float* host) {
+  Session* S = session_from(h);
+  if (!S) return LMB200_EINVAL;
+  LMB_REQUIRE(S->capture && host, "read_layer_output: capture is not enabled");
+  LMB_REQUIRE(layer >= 0 && layer < S->m->cfg.n_layers, "read_layer_output: layer %d", layer);
+  Ctx* ctx = S->m->ctx;
+  LMB_CUDA(cudaSetDevice(ctx->device));
+  const int64_t n = (int64_t)S->B * S->m->cfg.hidden;
+  LMB_CUDA(cudaMemcpyAsync(host, S->capture + layer * n, n * 4, cudaMemcpyDeviceToHost, ctx->stream));
+  LMB_CUDA(cudaStreamSynchronize(ctx->stream));
+  return LMB200_OK;
+}
+
+static int32_t copy_logits_out(Session* S, float* logits_out) {
+  Ctx* ctx = S->m->ctx;
+  LMB_CUDA(cudaMemcpy2DAsync(logits_out, (size_t)S->m->cfg.vocab * 4, S->logits, (size_t)S->logits_pitch * 4,
+                             (size_t)S->m->cfg.vocab * 4, S->B, cudaMemcpyDeviceToHost, ctx->stream));
+  return LMB200_OK;
+}
+
+extern "C" int32_t lmb200_prefill(lmb200_session h, const int32_t* tokens, int32_t n, float* logits_out) {
+  Session* S = session_from(h);
+  if (!S) return LMB200_EINVAL;
+  LMB_REQUIRE(tokens && n >= 1, "prefill: null tokens or n < 1");
+  if (S->host_pos + n > S->max_ctx)
+    return fail(LMB200_ESTATE, "prefill: %d + %d tokens exceed max_ctx %d", S->host_pos, n, S->max_ctx);
+  Ctx* ctx = S->m->ctx;
+  LMB_CUDA(cudaSetDevice(ctx->device));
+  const int B = S->B;
+  if ((int64_t)n * B > S->prompt_cap) {
+    cudaFree(S->prompt);
+    S->prompt = nullptr;
+    S->prompt_cap = 0;
+    LMB_TRY(dmalloc((void**)&S->prompt, (int64_t)n * B * 4, false, ctx->stream));
+    S->prompt_cap = (int64_t)n * B;
+  }
+  std::vector<int32_t> tr((size_t)n * B);       // [n][B]
+  for (int b = 0; b < B; ++b)
+    for (int i = 0; i < n; ++i) tr[(size_t)i * B + b] = tokens[(size_t)b * n + i];
+  LMB_CUDA(cudaMemcpyAsync(S->prompt, tr.data(), tr.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
+  LMB_CUDA(cudaMemsetAsync(S->step_ctr, 0, 4, ctx->stream));
+  for (int i = 0; i < n; ++i) {
+    LMB_CUDA(cudaMemcpyAsync(S->tokens, S->prompt + (int64_t)i * B, (size_t)B * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+    LMB_TRY(run_step(S, i == n - 1));
+  }
+  if (logits_out) LMB_TRY(copy_logits_out(S, logits_out));
+  LMB_CUDA(cudaStreamSynchronize(ctx->stream));
+  return LMB200_OK;
+}
+
+extern "C" int32_t lmb200_decode_step(lmb200_session h, const int32_t* tokens_in, int32_t* next_tokens_out,
+                                      float* logits_out) {
+  Session* S = session_from(h);
+  if (!S) return LMB200_EINVAL;
+  LMB_REQUIRE(tokens_in, "decode_step: null tokens");
+  if (S->host_pos + 1 > S->max_ctx)
+    return fail(LMB200_ESTATE, "decode_step: position %d is past max_ctx %d", S->host_pos, S->max_ctx);
+  Ctx* ctx = S->m->ctx;
+  LMB_CUDA(cudaSetDevice(ctx->device));
+  LMB_CUDA(cudaMemcpyAsync(S->tokens, tokens_in, (size_t)S->B * 4, cudaMemcpyHostToDevice, ctx->stream));
+  LMB_CUDA(cudaMemsetAsync(S->step_ctr, 0, 4, ctx->stream));
+  LMB_TRY(run_step(S, true));
+  if (next_tokens_out)
+    LMB_CUDA(cudaMemcpyAsync(next_tokens_out, S->tokens, (size_t)S->B * 4, cudaMemcpyDeviceToHost, ctx->stream));
+  if (logits_out) LMB_TRY(copy_logits_out(S, logits_out));
+  LMB_CUDA(cudaStreamSynchronize(ctx->stream));
+  return LMB200_OK;
+}
+
+static int32_t decode_n_common(Session* S, const int32_t* first, bool first_on_device, int32_t n_steps) {
+  LMB_REQUIRE(n_steps >= 1, "decode_n: n_steps %d", n_steps);
+  if (S->host_pos + n_steps > S->max_ctx)
+    return fail(LMB200_ESTATE, "decode_n: %d + %d steps exceed max_ctx %d", S->host_pos, n_steps, S->max_ctx);
+  Ctx* ctx = S->m->ctx;
+  LMB_CUDA(cudaSetDevice(ctx->device));
+  if (first)
+    LMB_CUDA(cudaMemcpyAsync(S->tokens, first, (size_t)S->B * 4,
+                             first_on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, ctx->stream));
+  LMB_CUDA(cudaMemsetAsync(S->step_ctr, 0, 4, ctx->stream));
+  for (int i = 0; i < n_steps; ++i) LMB_TRY(run_step(S, true));
+  return LMB200_OK;
+}
+
+extern "C" int32_t lmb200_decode_n(lmb200_session h, const int32_t* first_tokens, int32_t n_steps, int32_t* tokens_out) {
+  Session* S = session_from(h);
+  if (!S) return LMB200_EINVAL;
+  LMB_TRY(decode_n_common(S, first_tokens, false, n_steps));
+  Ctx* ctx = S->m->ctx;
+  if (tokens_out)
+    LMB_CUDA(cudaMemcpyAsync(tokens_out, S->tok_hist, (size_t)n_steps * S->B * 4, cudaMemcpyDeviceToHost, ctx->stream));
+  LMB_CUDA(cudaStreamSynchronize(ctx->stream));
+  return LMB200_OK;
+}
+
+extern "C" int32_t lmb200_decode_n_device(lmb200_session h, const int32_t* first_dptr, int32_t n_steps, int32_t* out_dptr) {
+  Session* S = session_from(h);
+  if (!S) return LMB200_EINVAL;
+  LMB_TRY(decode_n_common(S, first_dptr, true, n_steps));
+  Ctx* ctx = S->m->ctx;
+  if (out_dptr)
+    LMB_CUDA(cudaMemcpyAsync(out_dptr, S->tok_hist, (size_t)n_steps * S->B * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+  return LMB200_OK;
+}
+
+extern "C" int32_t lmb200_session_step_bytes(lmb200_session h, int32_t T, int64_t* bytes) {
+  Session* S = session_from(h);
+  if (!S || !bytes) return LMB200_EINVAL;
+  Model* M = S->m;
+  const lmb200_model_config& c = M->cfg;
+  const int64_t e = M->esz;
+  int64_t per_layer = ((int64_t)M->m_qkv.rows * c.hidden + (int64_t)c.hidden * M->Hl * M->D +
+                       (int64_t)2 * M->inter_l * c.hidden + (int64_t)c.hidden * M->inter_l) * e +
+                      (int64_t)2 * c.hidden * 4;
+  int64_t w = per_layer * c.n_layers + (int64_t)c.vocab * c.hidden * e + (int64_t)c.hidden * 4 +
+              (int64_t)S->B * c.hidden * e;
+  int64_t kv_read = (int64_t)c.n_layers * S->B * M->KVl * T * M->D * 2 * e;
+  int64_t kv_write = (int64_t)c.n_layers * S->B * M->KVl * M->D * 2 * e;
+  *bytes = w + kv_read + kv_write;
+  return LMB200_OK;
+}
+
+extern "C" int32_t lmb200_decode_attention_splitkv(lmb200_session h, int32_t layer, const void* q_dptr,
+                                                   void* out_dptr, int32_t T) {
+  Session* S = session_from(h);
+  if (!S) return LMB200_EINVAL;
+  Model* M = S->m;
+  LMB_REQUIRE(q_dptr && out_dptr, "decode_attention: null pointer");
+  LMB_REQUIRE(layer >= 0 && layer < M->cfg.n_layers, "decode_attention: layer %d", layer);
+  LMB_REQUIRE(T >= 1 && T <= S->max_ctx, "decode_attention: T %d outside 1..%d", T, S->max_ctx);
+  Ctx* ctx = M->ctx;
+  LMB_CUDA(cudaSetDevice(ctx->device));
+  AttnParams a;
+  a.q = q_dptr; a.q_pitch = M->Hl * M->D;
+  a.kv_layer = reinterpret_cast<char*>(S->kv) + (int64_t)layer * S->kv_layer_stride * M->esz;
+  a.kv_batch_stride = S->kv_batch_stride; a.kv_head_stride = S->kv_head_stride;
+  a.B = S->B; a.KVl = M->KVl; a.G = M->G; a.D = M->D; a.pos = nullptr; a.T_fixed = T;
+  a.keys_per_cta = S->keys_per_cta; a.nsplit = S->nsplit;
+  a.scale = 1.0f / sqrtf((float)M->D);
+  a.part_o = S->part_o; a.part_ml = S->part_ml; a.out = out_dptr; a.out_pitch = M->Hl * M->D;
+  LMB_TRY(attn_decode_launch(ctx, M->cfg.dtype, a, ctx->stream));
+  return LMB200_OK;
+}

@@ -1,0 +1,97 @@
+// Model (weights in the tiled layouts) and session (KV cache, activations, CUDA graph of a step).
+#pragma once
+#include <map>
+#include <string>
+#include <vector>
+
+#include "attention.cuh"
+#include "common.cuh"
+#include "gemv.cuh"
+
+namespace lmb {
+
+enum MapKind { MAP_PLAIN = 0, MAP_QKV = 1, MAP_O = 2, MAP_GATEUP = 3, MAP_DOWN = 4 };
+
+// How one internal (tiled) matrix maps onto up to three logical [out,in] tensors of the
+// reference (src/NN.jl:330-341, 238-244) -- including the head split f = h + H*d that the
+// reference's column-major reshape implies (src/NN.jl:347-354), the GQA mapping q = kv + KV*g
+// (src/NN.jl:305-317), the RoPE pairing (d, d + D/2) (src/NN.jl:274-276) and the tensor-parallel
+// shard of this rank.
+struct WMap {
+  int kind = MAP_PLAIN;
+  int rows = 0, K = 0;       // internal valid extent
+  int RB = 0, KC = 0;        // padded extent in 16-row blocks / 32-k chunks
+  int H = 0, KV = 0, D = 0, G = 0, Hl = 0, KVl = 0, kv_off = 0;
+  int inter_l = 0, inter_off = 0;
+  int src_rows[3] = {0, 0, 0};
+  int src_cols[3] = {0, 0, 0};
+};
+
+struct GemvPlan { int ksplit = 1, kc_per_split = 0; };
+
+struct LayerWeights {
+  void* wqkv = nullptr;
+  void* wo = nullptr;
+  void* wgu = nullptr;
+  void* wdown = nullptr;
+  float* attn_norm = nullptr;
+  float* ffn_norm = nullptr;
+};
+
+struct Model {
+  uint32_t magic = 0x4D4F444C;
+  Ctx* ctx = nullptr;
+  lmb200_model_config cfg{};
+  int esz = 4;
+  int Hl = 0, KVl = 0, G = 0, D = 0, kv_off = 0, inter_l = 0, inter_off = 0;
+  WMap m_qkv, m_o, m_gu, m_down, m_head;
+  std::vector<LayerWeights> layers;
+  void* embed = nullptr;        // [vocab, hidden] row-major, model dtype
+  float* final_norm = nullptr;
+  void* lm_head = nullptr;
+  float* inv_freq = nullptr;    // [D/2]
+  int64_t weight_bytes = 0;
+};
+
+struct Session {
+  uint32_t magic = 0x53455353;
+  Model* m = nullptr;
+  int B = 0, max_ctx = 0, cap = 0;
+  int host_pos = 0;
+  // cache: [L][B][KVl][cap/16][32*D]
+  void* kv = nullptr;
+  int64_t kv_head_stride = 0, kv_batch_stride = 0, kv_layer_stride = 0;
+  // activations
+  float* x = nullptr;
+  float* delta = nullptr;
+  float* logits = nullptr;
+  void* xn = nullptr;
+  void* qbuf = nullptr;
+  void* attn_out = nullptr;
+  void* act = nullptr;
+  int xn_pitch = 0, q_pitch = 0, act_pitch = 0, logits_pitch = 0;
+  int* tokens = nullptr;
+  int* pos = nullptr;
+  int* step_ctr = nullptr;
+  int* tok_hist = nullptr;      // [cap][B]
+  int* prompt = nullptr;        // staging for prefill
+  int64_t prompt_cap = 0;
+  // scratch
+  float* gemv_partials = nullptr;
+  unsigned* gemv_counters = nullptr;
+  float* part_o = nullptr;
+  float* part_ml = nullptr;
+  int keys_per_cta = 0, nsplit = 0;
+  GemvPlan p_qkv, p_o, p_gu, p_down, p_head;
+  float* capture = nullptr;     // [L][B][hidden] when enabled
+  bool capture_on = false;
+  cudaGraphExec_t graph_full = nullptr;
+  cudaGraphExec_t graph_body = nullptr;
+  cudaStream_t graph_stream = nullptr;
+  int graph_nodes_full = 0, graph_nodes_body = 0;
+};
+
+Model* model_from(lmb200_model h);
+Session* session_from(lmb200_session h);
+
+}  // namespace lmb

@@ -1,0 +1,134 @@
+"""The B200 device: the counterpart of the reference's device structs and of
+to_device / from_device (src/Device.jl:9-16, 82-105) for `libluminal_b200.so`."""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+from ._lib import BF16, COLMAJOR, F32, ROWMAJOR, LuminalB200Error
+
+
+class DeviceArray:
+    """A row-major tensor in B200 HBM (what a CuArray is to the reference)."""
+
+    def __init__(self, device, ptr, shape, dtype=F32, owned=True):
+        self.device, self.ptr, self.shape, self.dtype, self._owned = device, ptr, tuple(int(s) for s in shape), dtype, owned
+
+    @property
+    def size(self):
+        return int(np.prod(self.shape)) if self.shape else 1
+
+    def numpy(self, layout=ROWMAJOR):
+        """from_device: float32 NumPy array of the logical shape."""
+        out = np.empty(self.shape, dtype=np.float32, order="F" if layout == COLMAJOR else "C")
+        _lib.call("lmb200_download", self.device.handle, out.ctypes.data_as(C.c_void_p), C.c_void_p(self.ptr),
+                  self.dtype, len(self.shape), _lib.dims(self.shape), layout)
+        return out
+
+    def free(self):
+        if self._owned and self.ptr:
+            _lib.call("lmb200_free", self.device.handle, C.c_void_p(self.ptr))
+            self.ptr = 0
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class B200Device:
+    """One context on one GPU.  Fails loudly when there is no sm_100 GPU or no built library."""
+
+    def __init__(self, ordinal=0, stream=None):
+        h = C.c_uint64(0)
+        _lib.call("lmb200_init", int(ordinal), C.byref(h))
+        self.handle = h
+        self.ordinal = int(ordinal)
+        if stream is not None:
+            self.set_stream(stream)
+
+    def set_stream(self, cuda_stream_ptr):
+        _lib.call("lmb200_set_stream", self.handle, C.c_void_p(int(cuda_stream_ptr or 0)))
+
+    def sync(self):
+        _lib.call("lmb200_sync", self.handle)
+
+    def launch_count(self):
+        n = C.c_int64(0)
+        _lib.call("lmb200_launch_count", self.handle, C.byref(n))
+        return n.value
+
+    def alloc(self, nbytes):
+        p = C.c_void_p(0)
+        _lib.call("lmb200_alloc", self.handle, int(nbytes), C.byref(p))
+        return p.value
+
+    def empty(self, shape, dtype=F32):
+        n = int(np.prod(shape)) if len(shape) else 1
+        return DeviceArray(self, self.alloc(n * (2 if dtype == BF16 else 4)), shape, dtype)
+
+    def upload(self, array, dtype=F32, layout=ROWMAJOR):
+        """to_device: `array` holds the logical tensor; with layout=COLMAJOR its memory image is
+        Julia's (column-major) and the library re-lays it out."""
+        a = np.asarray(array, dtype=np.float32)
+        host = np.asfortranarray(a) if layout == COLMAJOR else np.ascontiguousarray(a)
+        out = self.empty(a.shape, dtype)
+        _lib.call("lmb200_upload", self.handle, C.c_void_p(out.ptr), dtype, host.ctypes.data_as(C.c_void_p),
+                  a.ndim, _lib.dims(a.shape), layout)
+        return out
+
+    # tensor-parallel communicator (one rank per process)
+    @staticmethod
+    def comm_unique_id():
+        buf = (C.c_uint8 * 128)()
+        _lib.call("lmb200_comm_unique_id", buf)
+        return bytes(buf)
+
+    def comm_init(self, n_ranks, rank, unique_id):
+        buf = (C.c_uint8 * 128).from_buffer_copy(unique_id)
+        _lib.call("lmb200_comm_init", self.handle, int(n_ranks), int(rank), buf)
+
+    def comm_destroy(self):
+        _lib.call("lmb200_comm_destroy", self.handle)
+
+    def close(self):
+        if self.handle:
+            _lib.call("lmb200_shutdown", self.handle)
+            self.handle = C.c_uint64(0)
+
+
+def device_count():
+    n = C.c_int32(0)
+    _lib.call("lmb200_device_count", C.byref(n))
+    return n.value
+
+
+_default = None
+
+
+def get_device():
+    """get_device() of src/Device.jl:27-74 for this backend: the B200 or an error, never a CPU
+    fallback."""
+    global _default
+    if _default is None:
+        _default = B200Device(0)
+    return _default
+
+
+def to_device(data, device):
+    if isinstance(data, dict):
+        return {k: to_device(v, device) for k, v in data.items()}
+    if isinstance(data, DeviceArray):
+        return data
+    return device.upload(np.asarray(data, dtype=np.float32))
+
+
+def from_device(data):
+    return data.numpy() if isinstance(data, DeviceArray) else data
+
+
+__all__ = ["B200Device", "DeviceArray", "get_device", "to_device", "from_device", "device_count",
+           "LuminalB200Error", "F32", "BF16", "ROWMAJOR", "COLMAJOR"]

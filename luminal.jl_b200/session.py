@@ -1,0 +1,161 @@
+"""Model and decode session: thin ctypes wrappers over the session API of libluminal_b200.so.
+A `Model` holds the weights of an NN.Llama / NN.Phi3 shaped decoder (src/NN.jl:417-507); a
+`Session` owns the KV cache and replaces the per-token generation loop
+(examples/llama.jl:73-99, src/Decoding.jl:91-130)."""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+from ._lib import BF16, COLMAJOR, F32, ROWMAJOR, ModelConfig
+
+
+def _dtype_code(dtype):
+    if dtype in (F32, "f32", "float32", np.float32):
+        return F32
+    if dtype in (BF16, "bf16", "bfloat16"):
+        return BF16
+    raise ValueError(f"dtype {dtype!r}: expected 'f32' or 'bf16'")
+
+
+class Model:
+    def __init__(self, device, *, n_layers, hidden, n_heads, n_kv_heads, intermediate, vocab,
+                 eps=1e-5, rope_base=10000.0, dtype="f32", tp_size=1, tp_rank=0):
+        self.device = device
+        self.cfg = ModelConfig(n_layers=n_layers, hidden=hidden, n_heads=n_heads, n_kv_heads=n_kv_heads,
+                               head_dim=hidden // n_heads, intermediate=intermediate, vocab=vocab,
+                               rms_eps=eps, rope_base=rope_base, dtype=_dtype_code(dtype),
+                               tp_size=tp_size, tp_rank=tp_rank)
+        h = C.c_uint64(0)
+        _lib.call("lmb200_model_create", device.handle, C.byref(self.cfg), C.byref(h))
+        self.handle = h
+
+    def set_weight(self, name, array, layout=ROWMAJOR):
+        a = np.asarray(array, dtype=np.float32)
+        host = np.asfortranarray(a) if layout == COLMAJOR else np.ascontiguousarray(a)
+        _lib.call("lmb200_model_set_weight", self.handle, name.encode(), host.ctypes.data_as(C.c_void_p), layout)
+
+    def set_weights(self, weights, layout=ROWMAJOR):
+        for name, a in weights.items():
+            self.set_weight(name, a, layout)
+
+    def init_random(self, seed=1234, sigma=0.02):
+        _lib.call("lmb200_model_init_random", self.handle, int(seed), float(sigma))
+
+    def weight_bytes(self):
+        n = C.c_int64(0)
+        _lib.call("lmb200_model_weight_bytes", self.handle, C.byref(n))
+        return n.value
+
+    def close(self):
+        if self.handle:
+            _lib.call("lmb200_model_destroy", self.handle)
+            self.handle = C.c_uint64(0)
+
+
+class Session:
+    def __init__(self, model, batch, max_ctx):
+        self.model, self.batch, self.max_ctx = model, int(batch), int(max_ctx)
+        h = C.c_uint64(0)
+        _lib.call("lmb200_session_create", model.handle, self.batch, self.max_ctx, C.byref(h))
+        self.handle = h
+
+    @property
+    def vocab(self):
+        return self.model.cfg.vocab
+
+    def reset(self):
+        _lib.call("lmb200_session_reset", self.handle)
+
+    def position(self):
+        p = C.c_int32(0)
+        _lib.call("lmb200_session_position", self.handle, C.byref(p))
+        return p.value
+
+    def set_position(self, pos):
+        _lib.call("lmb200_session_set_position", self.handle, int(pos))
+
+    def fill_kv_random(self, n_pos, seed=1234):
+        _lib.call("lmb200_session_fill_kv_random", self.handle, int(n_pos), int(seed))
+
+    def set_capture(self, enable=True):
+        _lib.call("lmb200_session_set_capture", self.handle, int(bool(enable)))
+
+    def layer_output(self, layer):
+        out = np.empty((self.batch, self.model.cfg.hidden), dtype=np.float32)
+        _lib.call("lmb200_session_read_layer_output", self.handle, int(layer), out.ctypes.data_as(C.c_void_p))
+        return out
+
+    def prefill(self, tokens, want_logits=True):
+        t = np.ascontiguousarray(np.asarray(tokens, dtype=np.int32))
+        assert t.ndim == 2 and t.shape[0] == self.batch, "tokens must be [batch, n]"
+        logits = np.empty((self.batch, self.vocab), dtype=np.float32) if want_logits else None
+        _lib.call("lmb200_prefill", self.handle, t.ctypes.data_as(C.c_void_p), t.shape[1],
+                  logits.ctypes.data_as(C.c_void_p) if want_logits else None)
+        return logits
+
+    def decode_step(self, tokens, want_logits=False):
+        t = np.ascontiguousarray(np.asarray(tokens, dtype=np.int32).reshape(self.batch))
+        nxt = np.empty(self.batch, dtype=np.int32)
+        logits = np.empty((self.batch, self.vocab), dtype=np.float32) if want_logits else None
+        _lib.call("lmb200_decode_step", self.handle, t.ctypes.data_as(C.c_void_p), nxt.ctypes.data_as(C.c_void_p),
+                  logits.ctypes.data_as(C.c_void_p) if want_logits else None)
+        return (nxt, logits) if want_logits else nxt
+
+    def decode_step_raw(self, tokens_in_ptr, next_out_ptr):
+        """Host buffers by address (pinned memory of the caller): the end-to-end timed call."""
+        _lib.call("lmb200_decode_step", self.handle, C.c_void_p(tokens_in_ptr), C.c_void_p(next_out_ptr), None)
+
+    def decode_n(self, first_tokens, n_steps):
+        first = None
+        if first_tokens is not None:
+            first = np.ascontiguousarray(np.asarray(first_tokens, dtype=np.int32).reshape(self.batch))
+        out = np.empty((n_steps, self.batch), dtype=np.int32)
+        _lib.call("lmb200_decode_n", self.handle, first.ctypes.data_as(C.c_void_p) if first is not None else None,
+                  int(n_steps), out.ctypes.data_as(C.c_void_p))
+        return out
+
+    def decode_n_device(self, first_tokens_dptr, n_steps, tokens_out_dptr=None):
+        _lib.call("lmb200_decode_n_device", self.handle, C.c_void_p(first_tokens_dptr or 0), int(n_steps),
+                  C.c_void_p(tokens_out_dptr or 0))
+
+    def step_bytes(self, T):
+        n = C.c_int64(0)
+        _lib.call("lmb200_session_step_bytes", self.handle, int(T), C.byref(n))
+        return n.value
+
+    def decode_attention(self, layer, q_dptr, out_dptr, T):
+        _lib.call("lmb200_decode_attention_splitkv", self.handle, int(layer), C.c_void_p(q_dptr),
+                  C.c_void_p(out_dptr), int(T))
+
+    def close(self):
+        if self.handle:
+            _lib.call("lmb200_session_destroy", self.handle)
+            self.handle = C.c_uint64(0)
+
+
+def greedy_generate(session, prompt, n_steps, want_logits=False):
+    """Prompt then n_steps greedy tokens: what examples/llama.jl's generation loop does, with the
+    KV cache the reference lacks for Llama.  Returns tokens [batch, n_steps] (and the logits that
+    produced them, [batch, n_steps, vocab])."""
+    logits = session.prefill(prompt)
+    toks, lgs = [], []
+    for step in range(n_steps):
+        nxt = np.argmax(logits, axis=-1).astype(np.int32)
+        toks.append(nxt)
+        lgs.append(logits)
+        if step + 1 < n_steps:
+            _, logits = _step_logits(session, nxt)
+    t = np.stack(toks, axis=1)
+    return (t, np.stack(lgs, axis=1)) if want_logits else t
+
+
+def _step_logits(session, tokens):
+    # the logits of the step that consumed `tokens`
+    nxt, logits = session.decode_step(tokens, want_logits=True)
+    return nxt, logits
+
+
+__all__ = ["Model", "Session", "greedy_generate"]
