@@ -2,6 +2,7 @@
 #include <dlfcn.h>
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "common.cuh"
@@ -32,6 +33,14 @@ Ctx* ctx_from(lmb200_ctx h) {
     return nullptr;
   }
   return c;
+}
+
+int32_t check_device_error(Ctx* ctx) {
+  if (ctx->dev_err && *reinterpret_cast<volatile int*>(ctx->dev_err) != 0) {
+    *ctx->dev_err = 0;
+    return fail(LMB200_ETIMEOUT, "a kernel gave up a bounded wait (mbarrier / flag): results of the last call are invalid");
+  }
+  return LMB200_OK;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -152,8 +161,17 @@ extern "C" int32_t lmb200_init(int32_t device, lmb200_ctx* out) {
     return fail(LMB200_ECUDA, "init: stream creation failed");
   }
   c->stream = c->own_stream;
+  if (cudaHostAlloc((void**)&c->dev_err, sizeof(int), cudaHostAllocMapped) != cudaSuccess) {
+    cudaStreamDestroy(c->own_stream);
+    delete c;
+    return fail(LMB200_ECUDA, "init: pinned allocation failed");
+  }
+  *c->dev_err = 0;
+  // LMB200_GEMV_KERNEL=ring selects the register-ring bf16 GEMV (for A/B runs); default: stream
+  const char* sel = getenv("LMB200_GEMV_KERNEL");
+  gemv_set_stream_kernel(!(sel && strcmp(sel, "ring") == 0));
   int32_t rc = gemv_configure();
-  if (rc != LMB200_OK) { cudaStreamDestroy(c->own_stream); delete c; return rc; }
+  if (rc != LMB200_OK) { cudaFreeHost(c->dev_err); cudaStreamDestroy(c->own_stream); delete c; return rc; }
   *out = reinterpret_cast<lmb200_ctx>(c);
   return LMB200_OK;
 }
@@ -165,6 +183,7 @@ extern "C" int32_t lmb200_shutdown(lmb200_ctx h) {
   cudaStreamSynchronize(c->stream);
   if (c->nccl_comm && g_nccl.CommDestroy) g_nccl.CommDestroy(c->nccl_comm);
   cudaStreamDestroy(c->own_stream);
+  cudaFreeHost(c->dev_err);
   c->magic = 0;
   delete c;
   return LMB200_OK;
@@ -182,7 +201,7 @@ extern "C" int32_t lmb200_sync(lmb200_ctx h) {
   if (!c) return LMB200_EINVAL;
   LMB_CUDA(cudaSetDevice(c->device));
   LMB_CUDA(cudaStreamSynchronize(c->stream));
-  return LMB200_OK;
+  return check_device_error(c);
 }
 
 extern "C" int32_t lmb200_launch_count(lmb200_ctx h, int64_t* count) {

@@ -248,14 +248,16 @@ __global__ void attn_combine_kernel(const AttnParams p) {
     denom += exp2f(ml[0] - M) * ml[1];
   }
   const float inv = 1.0f / denom;
-  T* out = reinterpret_cast<T*>(p.out) + (int64_t)b * p.out_pitch + hl * p.D;
+  T* out = reinterpret_cast<T*>(p.out);
   for (int d = threadIdx.x; d < p.D; d += blockDim.x) {
     float acc = 0.f;
     for (int s = 0; s < nvalid; ++s) {
       const float w = exp2f(p.part_ml[((slot0 + s) * p.G + h) * 2] - M);
       acc += w * p.part_o[((slot0 + s) * p.G + h) * p.D + d];
     }
-    out[d] = from_f32<T>(acc * inv);
+    const int64_t o = p.out_tiled_bp > 0 ? xtile_offset(b, hl * p.D + d, p.out_tiled_bp)
+                                         : (int64_t)b * p.out_pitch + hl * p.D + d;
+    out[o] = from_f32<T>(acc * inv);
   }
 }
 

@@ -21,8 +21,9 @@ struct AttnParams {
   float scale = 1.f;              // 1/sqrt(D)
   float* part_o = nullptr;        // scratch [B*KVl, nsplit, G, D]
   float* part_ml = nullptr;       // scratch [B*KVl, nsplit, G, 2]  (max, sum)
-  void* out = nullptr;            // [B, out_pitch], same head-major order as q
+  void* out = nullptr;            // [B, out_pitch], same head-major order as q ...
   int out_pitch = 0;
+  int out_tiled_bp = 0;           // ... or, when > 0, a tiled activation buffer (xtile_offset) of that padding
 };
 
 // scratch floats needed: part_o, part_ml

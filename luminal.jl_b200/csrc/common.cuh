@@ -48,6 +48,7 @@ struct Ctx {
   cudaStream_t own_stream = nullptr;
   cudaStream_t stream = nullptr;
   int64_t launches = 0;
+  int* dev_err = nullptr;        // mapped pinned word: a kernel whose bounded wait gave up sets it
   // NCCL (resolved with dlopen so that the library loads on hosts without it)
   void* nccl_comm = nullptr;
   int tp_size = 1;
@@ -55,6 +56,8 @@ struct Ctx {
 };
 
 Ctx* ctx_from(lmb200_ctx h);
+// LMB200_ETIMEOUT (and clears the flag) if a kernel reported a wait that ran out
+int32_t check_device_error(Ctx* ctx);
 int32_t nccl_allreduce_f32(Ctx* ctx, void* dptr, int64_t count, cudaStream_t stream);
 
 static inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
@@ -137,6 +140,17 @@ __host__ __device__ inline int64_t vcache_offset(int64_t key, int d, int D) {
   int t = (kk & 7) >> 1, e = kk & 1, hik = kk >> 3;
   return kb * kv_block_elems(D) + (int64_t)(D / 16 + dm) * 256 + (g * 4 + t) * 8 + (hik * 2 + hid) * 2 + e;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Tiled activations.  A GEMV input x[b, k] (b < Bp = 8, 16 or 32 rows, zero beyond the batch) is
+// stored chunk-major: [k/32][Bp][32].  The slice of any run of k-chunks is contiguous (one bulk
+// copy), and the B-operand read of the MMA -- lane (g,t) takes x[8nt+g][8t..8t+7] -- touches
+// 128 contiguous bytes per quarter-warp, so shared memory needs no padding or swizzle.
+// ---------------------------------------------------------------------------------------------
+__host__ __device__ inline int64_t xtile_offset(int b, int k, int Bp) {
+  return (int64_t)(k >> 5) * (Bp * 32) + b * 32 + (k & 31);
+}
+static inline int batch_pad(int B) { return B <= 8 ? 8 : (B <= 16 ? 16 : 32); }
 
 // element conversions
 __device__ inline float to_f32(float v) { return v; }

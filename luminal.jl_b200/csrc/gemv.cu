@@ -1,13 +1,18 @@
 // Bandwidth-bound decode GEMV with fused epilogues (store / SiLU-gate / RoPE + KV append).
 //
-// One CTA = 8 warps = 2 row groups x 4 k-warps and owns 2*MT 16-row blocks of the tiled weight
-// matrix for one k-split.  The activation slice [B, Ks] is staged in shared memory once; the
-// weights never touch shared memory: every lane streams its own 32 contiguous bytes of each
-// 1 KB unit (evict-first) through a STAGES-deep register ring and feeds them straight to
-// mma.sync m16n8k16 (bf16) or to fp32 FMAs (the float32 parity path).  Partial tiles of the 4
-// k-warps are summed through shared memory; with ksplit > 1 the CTAs of one row group leave
-// their tiles in global scratch and the last one to arrive (a counter) sums them in fixed
-// order, so results do not depend on scheduling.
+// bf16 "stream" kernel (default): stream-K over bulk-TMA.  The weight matrix is cut into units of
+// 128 rows x 128 k (32 KB, eight contiguous 4 KB runs of the tiled layout); the grid is one CTA
+// per SM and CTA c takes the contiguous unit range [c*U/G, (c+1)*U/G), so every SM streams the
+// same number of bytes in a single wave whatever the matrix shape.  A producer warp keeps a ring
+// of STAGES shared-memory stages full with cp.async.bulk copies (weights evict-first, plus the
+// matching slice of the tiled activations) signalled through mbarriers; 8 consumer warps (2 row
+// groups x 4 k-chunks) read their MMA operands from the stage with conflict-free 16-byte loads
+// and issue mma.sync m16n8k16.  When a CTA's range leaves a 128-row group it folds its partial
+// tile: alone -> epilogue; shared -> global scratch + counter, the last contributor sums the
+// parts in CTA order (deterministic) and runs the epilogue.
+//
+// "ring" kernel: weights streamed by plain loads through a register ring; used for float32 (the
+// parity path, fp32 FMAs) and selectable for bf16 (A/B comparison).
 #include <type_traits>
 
 #include "gemv.cuh"
@@ -16,12 +21,11 @@ namespace lmb {
 
 namespace {
 
-constexpr int kThreads = 256;
-constexpr size_t kMaxSmem = 112 * 1024;
 constexpr float kInvLn2 = 1.4426950408889634f;      // Float32(1/log(2)) as the reference rounds it
 constexpr float kHalfPi = 1.5707963267948966f;
+constexpr size_t kMaxSmem = 224 * 1024;
 
-__device__ __forceinline__ uint4 ld_stream(const uint4* p) { return __ldcs(p); }
+bool g_use_stream = true;
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                          uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -32,6 +36,99 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// ---------------------------------------------------------------------------------------------
+// Epilogue over a finished tile in shared memory: tile[r * RP + b], r < RPC rows of the CTA's row
+// group starting at logical internal row row0.
+// ---------------------------------------------------------------------------------------------
+template <typename WT>
+__device__ __forceinline__ void run_epilogue(const GemvParams& p, const float* tile, int RPC, int RP, int Bp,
+                                             int row0, int tid, int nthreads) {
+  if (p.epi == EPI_STORE_F32) {
+    for (int i = tid; i < RPC * Bp; i += nthreads) {
+      const int b = i / RPC, r = i - b * RPC;
+      const int row = row0 + r;
+      if (b < p.B && row < p.rows) p.out[(int64_t)b * p.out_pitch + row] = tile[r * RP + b];
+    }
+  } else if (p.epi == EPI_SILU_GATE) {
+    WT* act = reinterpret_cast<WT*>(p.act);
+    for (int i = tid; i < (RPC / 2) * Bp; i += nthreads) {
+      const int b = i / (RPC / 2), j = i - b * (RPC / 2);
+      const int m = j >> 3, r = j & 7;
+      const int o = row0 / 2 + j;
+      if (b < p.B && o < p.n_act) {
+        const float a = tile[(16 * m + r) * RP + b], u = tile[(16 * m + r + 8) * RP + b];
+        // silu(a) = a * (1 / (1 + exp2((a * -1) * (1/ln2))))     src/HighLevelOps.jl:153-160
+        const float e = exp2f((a * -1.0f) * kInvLn2);
+        const float sg = 1.0f / (1.0f + e);
+        act[xtile_offset(b, o, Bp)] = from_f32<WT>((a * sg) * u);
+      }
+    }
+  } else {  // EPI_QKV_ROPE
+    WT* q_out = reinterpret_cast<WT*>(p.q_out);
+    WT* kv = reinterpret_cast<WT*>(p.kv_layer);
+    const int D = p.D, tiles_per_head = D >> 4, half = D >> 1;
+    const int pos = *p.pos;
+    const float fpos = (float)pos;
+    for (int i = tid; i < (RPC / 2) * Bp; i += nthreads) {
+      const int b = i / (RPC / 2), j = i - b * (RPC / 2);
+      const int m = j >> 3, r = j & 7;
+      const int gt = row0 / 16 + m;                  // global 16-row tile
+      if (b >= p.B || gt >= p.RB) continue;
+      const int hs = gt / tiles_per_head, jj = gt - hs * tiles_per_head;
+      const float v0 = tile[(16 * m + r) * RP + b], v1 = tile[(16 * m + r + 8) * RP + b];
+      if (hs < p.Hl + p.KVl) {
+        // rows r / r+8 of the tile are the RoPE pair (d0, d0 + D/2)      src/NN.jl:253-303
+        const int d0 = 8 * jj + r;
+        const float ang = fpos * p.inv_freq[d0];
+        const float sn = sinf(ang);
+        const float cs = sinf(kHalfPi + ang * -1.0f);   // cos(a) = sin(pi/2 - a)
+        const float o0 = v0 * cs + (v1 * sn) * -1.0f;
+        const float o1 = v0 * sn + v1 * cs;
+        if (hs < p.Hl) {
+          WT* q = q_out + (int64_t)b * p.q_pitch + hs * D;
+          q[d0] = from_f32<WT>(o0);
+          q[d0 + half] = from_f32<WT>(o1);
+        } else {
+          WT* kc = kv + b * p.kv_batch_stride + (hs - p.Hl) * p.kv_head_stride;
+          kc[kcache_offset(pos, d0, D)] = from_f32<WT>(o0);
+          kc[kcache_offset(pos, d0 + half, D)] = from_f32<WT>(o1);
+        }
+      } else {
+        WT* vc = kv + b * p.kv_batch_stride + (hs - p.Hl - p.KVl) * p.kv_head_stride;
+        const int d = 16 * jj + r;
+        vc[vcache_offset(pos, d, D)] = from_f32<WT>(v0);
+        vc[vcache_offset(pos, d + 8, D)] = from_f32<WT>(v1);
+      }
+    }
+  }
+}
+
+// sum `n` partial tiles (dense [RPC*Bp] each, `stride` floats apart) into tile[r*RP+b]
+__device__ __forceinline__ void sum_partials(float* tile, const float* part, int n, int64_t stride, int RPC, int RP,
+                                             int Bp, int tid, int nthreads) {
+  const int total = RPC * Bp;
+  for (int i0 = tid; i0 < total; i0 += nthreads * 4) {
+    float s[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int k = 0; k < n; ++k) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int i = i0 + j * nthreads;
+        if (i < total) s[j] += __ldcg(part + (int64_t)k * stride + i);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int i = i0 + j * nthreads;
+      if (i < total) { const int r = i / Bp, b = i - r * Bp; tile[r * RP + b] = s[j]; }
+    }
+  }
+}
+
+// =============================================================================================
+// ring kernel
+// =============================================================================================
+constexpr int kRingThreads = 256;
+
 template <typename WT> struct Unit;   // 16 rows x 32 k of weights as seen by one lane
 template <> struct Unit<__nv_bfloat16> { uint4 v[2]; };
 template <> struct Unit<float> { uint4 v[4]; };
@@ -41,7 +138,7 @@ __device__ __forceinline__ void load_unit(Unit<WT>& u, const WT* W, int64_t rb, 
   constexpr int N = sizeof(Unit<WT>) / 16;
   const uint4* p = reinterpret_cast<const uint4*>(W + ((rb * KC + kc) * 32 + lane) * 16);
 #pragma unroll
-  for (int i = 0; i < N; ++i) u.v[i] = ld_stream(p + i);
+  for (int i = 0; i < N; ++i) u.v[i] = __ldcs(p + i);
 }
 template <typename WT>
 __device__ __forceinline__ void zero_unit(Unit<WT>& u) {
@@ -51,12 +148,12 @@ __device__ __forceinline__ void zero_unit(Unit<WT>& u) {
 }
 
 template <typename WT, int NB, int MT, int STAGES>
-__global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvParams p) {
+__global__ void __launch_bounds__(kRingThreads, 1) gemv_ring_kernel(const GemvParams p) {
   constexpr int Bp = 8 * NB;
   constexpr int RPC = 2 * MT * 16;
   constexpr bool kBf16 = std::is_same<WT, __nv_bfloat16>::value;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  WT* xs = reinterpret_cast<WT*>(smem_raw);
+  WT* xs = reinterpret_cast<WT*>(smem_raw);           // [chunks][Bp][32], a copy of the global slice
   float* red = reinterpret_cast<float*>(smem_raw);
   __shared__ int s_last;
 
@@ -65,37 +162,26 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvParams p) {
   const int rg = warp >> 2, kw = warp & 3;
   const int kc0 = blockIdx.y * p.kc_per_split;
   const int kc1 = min(p.KC, kc0 + p.kc_per_split);
-  const int Ks = (kc1 - kc0) * 32;
-  const int xs_pitch = kBf16 ? (Ks + ((Ks & 63) == 32 ? 0 : 32)) : Ks + 4;
   const int64_t rb_base = (int64_t)blockIdx.x * (2 * MT) + rg * MT;
   const WT* W = reinterpret_cast<const WT*>(p.W);
 
   // prefetch the first weight units before touching the activations
   Unit<WT> ring[STAGES][MT];
 #pragma unroll
-  for (int s = 0; s < STAGES - 1; ++s) {
+  for (int s = 0; s < STAGES; ++s) {
     const int kc = kc0 + kw + 4 * s;
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
-      if (kc < kc1 && rb_base + mt < p.RB) load_unit<WT>(ring[s][mt], W, rb_base + mt, p.KC, kc, lane);
+      if (s < STAGES - 1 && kc < kc1 && rb_base + mt < p.RB) load_unit<WT>(ring[s][mt], W, rb_base + mt, p.KC, kc, lane);
       else zero_unit<WT>(ring[s][mt]);
     }
   }
-
-#pragma unroll
-  for (int mt = 0; mt < MT; ++mt) zero_unit<WT>(ring[STAGES - 1][mt]);
-
-  // stage x[:, kc0*32 .. kc1*32) into shared memory, rows >= B zero
   {
-    constexpr int EPV = 16 / sizeof(WT);
-    const int vec_per_row = Ks / EPV;
-    const WT* x = reinterpret_cast<const WT*>(p.x);
-    for (int i = tid; i < Bp * vec_per_row; i += kThreads) {
-      const int b = i / vec_per_row, v = i - b * vec_per_row;
-      uint4 val = make_uint4(0, 0, 0, 0);
-      if (b < p.B) val = *reinterpret_cast<const uint4*>(x + (int64_t)b * p.x_pitch + kc0 * 32 + v * EPV);
-      *reinterpret_cast<uint4*>(xs + b * xs_pitch + v * EPV) = val;
-    }
+    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const WT*>(p.x) + (int64_t)kc0 * Bp * 32);
+    uint4* dst = reinterpret_cast<uint4*>(xs);
+    const int nvec = (kc1 - kc0) * Bp * 32 * (int)sizeof(WT) / 16;
+#pragma unroll 8
+    for (int i = tid; i < nvec; i += kRingThreads) dst[i] = src[i];
   }
   __syncthreads();
 
@@ -112,20 +198,17 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvParams p) {
     for (int s = 0; s < STAGES; ++s) {
       const int cur = base + 4 * s;
       if (cur < kc1) {
-        {  // refill the slot freed by the previous iteration
-          const int nxt = cur + 4 * (STAGES - 1);
+        const int nxt = cur + 4 * (STAGES - 1);      // refill the slot freed by the previous iteration
 #pragma unroll
-          for (int mt = 0; mt < MT; ++mt) {
-            if (nxt < kc1 && rb_base + mt < p.RB)
-              load_unit<WT>(ring[(s + STAGES - 1) % STAGES][mt], W, rb_base + mt, p.KC, nxt, lane);
-          }
+        for (int mt = 0; mt < MT; ++mt) {
+          if (nxt < kc1 && rb_base + mt < p.RB)
+            load_unit<WT>(ring[(s + STAGES - 1) % STAGES][mt], W, rb_base + mt, p.KC, nxt, lane);
         }
-        const int koff = (cur - kc0) * 32 + 8 * t;
+        const WT* xc = xs + (cur - kc0) * (Bp * 32) + 8 * t;
         if constexpr (kBf16) {
           uint4 bx[NB];
 #pragma unroll
-          for (int nt = 0; nt < NB; ++nt)
-            bx[nt] = *reinterpret_cast<const uint4*>(xs + (8 * nt + g) * xs_pitch + koff);
+          for (int nt = 0; nt < NB; ++nt) bx[nt] = *reinterpret_cast<const uint4*>(xc + (8 * nt + g) * 32);
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) {
             const uint4 lo = ring[s][mt].v[0], hi = ring[s][mt].v[1];
@@ -144,8 +227,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvParams p) {
             const float4 h1 = *reinterpret_cast<const float4*>(&ring[s][mt].v[3]);
 #pragma unroll
             for (int c = 0; c < Bp; ++c) {
-              const float4 x0 = *reinterpret_cast<const float4*>(xs + c * xs_pitch + koff);
-              const float4 x1 = *reinterpret_cast<const float4*>(xs + c * xs_pitch + koff + 4);
+              const float4 x0 = *reinterpret_cast<const float4*>(xc + c * 32);
+              const float4 x1 = *reinterpret_cast<const float4*>(xc + c * 32 + 4);
               float lo = acc[mt][2 * c][0], hi = acc[mt][2 * c + 1][0];
               lo = fmaf(l0.x, x0.x, lo); lo = fmaf(l0.y, x0.y, lo); lo = fmaf(l0.z, x0.z, lo); lo = fmaf(l0.w, x0.w, lo);
               lo = fmaf(l1.x, x1.x, lo); lo = fmaf(l1.y, x1.y, lo); lo = fmaf(l1.z, x1.z, lo); lo = fmaf(l1.w, x1.w, lo);
@@ -198,15 +281,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvParams p) {
     }
   }
   __syncthreads();
-
   // sum the 4 k-warp slabs into slab 0 (each thread owns its (r,b) positions: no hazard)
-  for (int i = tid; i < RPC * Bp; i += kThreads) {
+  for (int i = tid; i < RPC * Bp; i += kRingThreads) {
     const int r = i / Bp, b = i - r * Bp, o = r * RP + b;
     red[o] = (red[o] + red[SLAB + o]) + (red[2 * SLAB + o] + red[3 * SLAB + o]);
   }
   if (p.ksplit > 1) {
     float* my_part = p.partials + ((int64_t)blockIdx.x * p.ksplit + blockIdx.y) * (RPC * Bp);
-    for (int i = tid; i < RPC * Bp; i += kThreads) {
+    for (int i = tid; i < RPC * Bp; i += kRingThreads) {
       const int r = i / Bp, b = i - r * Bp;
       my_part[i] = red[r * RP + b];
     }
@@ -220,89 +302,254 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const GemvParams p) {
     if (!s_last) return;
     if (tid == 0) p.counters[blockIdx.x] = 0u;   // ready for the next launch
     __threadfence();
-    const float* part = p.partials + (int64_t)blockIdx.x * p.ksplit * (RPC * Bp);
-    for (int i = tid; i < RPC * Bp; i += kThreads) {
-      const int r = i / Bp, b = i - r * Bp;
-      float s = 0.f;
-      for (int k = 0; k < p.ksplit; ++k) s += __ldcg(part + (int64_t)k * (RPC * Bp) + i);
-      red[r * RP + b] = s;
-    }
+    sum_partials(red, p.partials + (int64_t)blockIdx.x * p.ksplit * (RPC * Bp), p.ksplit, RPC * Bp, RPC, RP, Bp, tid,
+                 kRingThreads);
   }
   __syncthreads();
-  auto tile = [&](int r, int b) -> float { return red[r * RP + b]; };
+  run_epilogue<WT>(p, red, RPC, RP, Bp, blockIdx.x * RPC, tid, kRingThreads);
+}
 
-  const int row0 = blockIdx.x * RPC;
-  if (p.epi == EPI_STORE_F32) {
-    for (int i = tid; i < RPC * Bp; i += kThreads) {
-      const int b = i / RPC, r = i - b * RPC;
-      const int row = row0 + r;
-      if (b < p.B && row < p.rows) p.out[(int64_t)b * p.out_pitch + row] = tile(r, b);
-    }
-  } else if (p.epi == EPI_SILU_GATE) {
-    WT* act = reinterpret_cast<WT*>(p.act);
-    for (int i = tid; i < (RPC / 2) * Bp; i += kThreads) {
-      const int b = i / (RPC / 2), j = i - b * (RPC / 2);
-      const int m = j >> 3, r = j & 7;
-      const int o = row0 / 2 + j;
-      if (b < p.B && o < p.n_act) {
-        const float a = tile(16 * m + r, b), u = tile(16 * m + r + 8, b);
-        // silu(a) = a * (1 / (1 + exp2((a * -1) * (1/ln2))))     src/HighLevelOps.jl:153-160
-        const float e = exp2f((a * -1.0f) * kInvLn2);
-        const float sg = 1.0f / (1.0f + e);
-        act[(int64_t)b * p.act_pitch + o] = from_f32<WT>((a * sg) * u);
-      }
-    }
-  } else {  // EPI_QKV_ROPE
-    WT* q_out = reinterpret_cast<WT*>(p.q_out);
-    WT* kv = reinterpret_cast<WT*>(p.kv_layer);
-    const int D = p.D, tiles_per_head = D >> 4, half = D >> 1;
-    const int pos = *p.pos;
-    const float fpos = (float)pos;
-    for (int i = tid; i < (RPC / 2) * Bp; i += kThreads) {
-      const int b = i / (RPC / 2), j = i - b * (RPC / 2);
-      const int m = j >> 3, r = j & 7;
-      const int gt = row0 / 16 + m;                  // global 16-row tile
-      if (b >= p.B || gt >= p.RB) continue;
-      const int hs = gt / tiles_per_head, jj = gt - hs * tiles_per_head;
-      const float v0 = tile(16 * m + r, b), v1 = tile(16 * m + r + 8, b);
-      if (hs < p.Hl + p.KVl) {
-        // rows r / r+8 of the tile are the RoPE pair (d0, d0 + D/2)      src/NN.jl:253-303
-        const int d0 = 8 * jj + r;
-        const float ang = fpos * p.inv_freq[d0];
-        const float sn = sinf(ang);
-        const float cs = sinf(kHalfPi + ang * -1.0f);   // cos(a) = sin(pi/2 - a)
-        const float o0 = v0 * cs + (v1 * sn) * -1.0f;
-        const float o1 = v0 * sn + v1 * cs;
-        if (hs < p.Hl) {
-          WT* q = q_out + (int64_t)b * p.q_pitch + hs * D;
-          q[d0] = from_f32<WT>(o0);
-          q[d0 + half] = from_f32<WT>(o1);
-        } else {
-          WT* kc = kv + b * p.kv_batch_stride + (hs - p.Hl) * p.kv_head_stride;
-          kc[kcache_offset(pos, d0, D)] = from_f32<WT>(o0);
-          kc[kcache_offset(pos, d0 + half, D)] = from_f32<WT>(o1);
-        }
-      } else {
-        WT* vc = kv + b * p.kv_batch_stride + (hs - p.Hl - p.KVl) * p.kv_head_stride;
-        const int d = 16 * jj + r;
-        vc[vcache_offset(pos, d, D)] = from_f32<WT>(v0);
-        vc[vcache_offset(pos, d + 8, D)] = from_f32<WT>(v1);
-      }
+// =============================================================================================
+// stream kernel (bf16)
+// =============================================================================================
+constexpr int kConsumerWarps = 8;
+constexpr int kStreamThreads = (kConsumerWarps + 1) * 32;
+constexpr int kCH = 4;              // k-chunks per stage (one per k-warp)
+constexpr int kRPC = 128;           // rows per row group (8 row blocks)
+constexpr int kStages = 5;
+constexpr int kWStage = 8 * kCH * 1024;
+constexpr long long kWaitLimit = 4000000000LL;   // clock cycles (~2 s) before a wait gives up
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  After a time-out the thread stops waiting for good (`dead`), so control flow --
+// and with it every barrier -- stays the same for all threads; the launch is flagged as failed.
+__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, bool& dead, int* err) {
+  if (dead) return;
+  if (mbar_try_wait(bar, parity)) return;
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (clock64() - t0 > kWaitLimit) {
+      dead = true;
+      if (err) atomicExch(err, 1);
+      return;
     }
   }
 }
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;\n" ::"r"(
+          smem_u32(dst)),
+      "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 256;\n" ::: "memory"); }
+
+template <int NB>
+__global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const GemvParams p, int* err) {
+  constexpr int Bp = 8 * NB;
+  constexpr int kXStage = kCH * Bp * 64;
+  constexpr int kStage = kWStage + kXStage;
+  constexpr int RP = Bp + 1;
+  extern __shared__ __align__(128) unsigned char smem[];
+  float* tile = reinterpret_cast<float*>(smem + kStages * kStage);
+  __shared__ __align__(8) uint64_t full_bar[kStages];
+  __shared__ __align__(8) uint64_t empty_bar[kStages];
+  __shared__ int s_last;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int KS = (p.KC + kCH - 1) / kCH;              // stage units per row group
+  const int nrbg = (p.RB + 7) / 8;
+  const long long U = (long long)nrbg * KS;
+  const long long G = gridDim.x;
+  const int u0 = (int)((long long)blockIdx.x * U / G);
+  const int u1 = (int)((long long)(blockIdx.x + 1) * U / G);
+
+  if (tid == 0) {
+#pragma unroll
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], kConsumerWarps);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  __syncthreads();
+
+  bool dead = false;
+  if (warp == kConsumerWarps) {
+    // ---------------- producer ----------------
+    uint64_t pol_w, pol_x;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;\n" : "=l"(pol_w));
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;\n" : "=l"(pol_x));
+    const __nv_bfloat16* W = reinterpret_cast<const __nv_bfloat16*>(p.W);
+    const __nv_bfloat16* X = reinterpret_cast<const __nv_bfloat16*>(p.x);
+    int it = 0;
+    for (int u = u0; u < u1; ++u, ++it) {
+      const int s = it % kStages, k = it / kStages;
+      mbar_wait(&empty_bar[s], (k & 1) ^ 1, dead, err);
+      const int r = u / KS, ks = u - r * KS;
+      const int chunk0 = ks * kCH;
+      const int nch = min(kCH, p.KC - chunk0);
+      const int nrb = min(8, p.RB - r * 8);
+      unsigned char* st = smem + s * kStage;
+      if (lane == 0) mbar_expect_tx(&full_bar[s], (uint32_t)(nrb * nch * 1024 + nch * Bp * 64));
+      __syncwarp();
+      if (lane < nrb)
+        bulk_g2s(st + lane * (kCH * 1024), W + ((int64_t)(r * 8 + lane) * p.KC + chunk0) * 512, (uint32_t)(nch * 1024),
+                 &full_bar[s], pol_w);
+      else if (lane == 8)
+        bulk_g2s(st + kWStage, X + (int64_t)chunk0 * (Bp * 32), (uint32_t)(nch * Bp * 64), &full_bar[s], pol_x);
+    }
+    return;
+  }
+
+  // ---------------- consumers ----------------
+  const int g = lane >> 2, t = lane & 3;
+  const int rg = warp >> 2, kw = warp & 3;
+  float acc[4][NB][4];
+  auto zero_acc = [&]() {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < NB; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f;
+  };
+  // fold the accumulators of the row group `r` that this CTA's range has just left
+  auto flush = [&](int r) {
+#pragma unroll 1
+    for (int round = 0; round < 4; ++round) {
+      if (kw == round) {
+#pragma unroll
+        for (int mt = 0; mt < 4; ++mt) {
+          const int r0 = (rg * 4 + mt) * 16 + g;
+#pragma unroll
+          for (int nt = 0; nt < NB; ++nt) {
+            const int c = 8 * nt + 2 * t;
+            if (round == 0) {
+              tile[r0 * RP + c] = acc[mt][nt][0];
+              tile[r0 * RP + c + 1] = acc[mt][nt][1];
+              tile[(r0 + 8) * RP + c] = acc[mt][nt][2];
+              tile[(r0 + 8) * RP + c + 1] = acc[mt][nt][3];
+            } else {
+              tile[r0 * RP + c] += acc[mt][nt][0];
+              tile[r0 * RP + c + 1] += acc[mt][nt][1];
+              tile[(r0 + 8) * RP + c] += acc[mt][nt][2];
+              tile[(r0 + 8) * RP + c + 1] += acc[mt][nt][3];
+            }
+          }
+        }
+      }
+      consumer_sync();
+    }
+    // which CTAs share this row group?  CTA of unit u is ceil((u+1)*G/U) - 1
+    const long long ua = (long long)r * KS, ub = ua + KS - 1;
+    const int c_first = (int)(((ua + 1) * G + U - 1) / U) - 1;
+    const int c_last = (int)(((ub + 1) * G + U - 1) / U) - 1;
+    const int n = c_last - c_first + 1;
+    bool do_epilogue = true;
+    if (n > 1) {
+      const int jmax = p.ksplit;      // contributors reserved per row group
+      float* part = p.partials + (int64_t)r * jmax * (kRPC * Bp);
+      float* mine = part + (int64_t)((int)blockIdx.x - c_first) * (kRPC * Bp);
+      for (int i = tid; i < kRPC * Bp; i += 256) {
+        const int rr = i / Bp, b = i - rr * Bp;
+        mine[i] = tile[rr * RP + b];
+      }
+      __threadfence();
+      consumer_sync();
+      if (tid == 0) {
+        const unsigned prev = atomicAdd(&p.counters[r], 1u);
+        s_last = (prev == (unsigned)n - 1u);
+      }
+      consumer_sync();
+      do_epilogue = s_last != 0;
+      if (do_epilogue) {
+        if (tid == 0) p.counters[r] = 0u;
+        __threadfence();
+        sum_partials(tile, part, n, kRPC * Bp, kRPC, RP, Bp, tid, 256);
+        consumer_sync();
+      }
+    }
+    if (do_epilogue) run_epilogue<__nv_bfloat16>(p, tile, kRPC, RP, Bp, r * kRPC, tid, 256);
+    consumer_sync();       // the tile is reused by the next row group
+  };
+
+  zero_acc();
+  int seg_r = u0 < u1 ? u0 / KS : -1;
+  int it = 0;
+  for (int u = u0; u < u1; ++u, ++it) {
+    const int r = u / KS, ks = u - r * KS;
+    if (r != seg_r) {
+      flush(seg_r);
+      zero_acc();
+      seg_r = r;
+    }
+    const int s = it % kStages, k = it / kStages;
+    const int nch = min(kCH, p.KC - ks * kCH);
+    mbar_wait(&full_bar[s], k & 1, dead, err);
+    if (kw < nch) {
+      const unsigned char* st = smem + s * kStage;
+      const unsigned char* xst = st + kWStage + kw * (Bp * 64) + g * 64 + t * 16;
+      uint4 bx[NB];
+#pragma unroll
+      for (int nt = 0; nt < NB; ++nt) bx[nt] = *reinterpret_cast<const uint4*>(xst + nt * 512);
+#pragma unroll
+      for (int mt = 0; mt < 4; ++mt) {
+        if (r * 8 + rg * 4 + mt < p.RB) {
+          const uint4* wp = reinterpret_cast<const uint4*>(st + ((rg * 4 + mt) * kCH + kw) * 1024 + lane * 32);
+          const uint4 lo = wp[0], hi = wp[1];
+#pragma unroll
+          for (int nt = 0; nt < NB; ++nt) {
+            mma_bf16(acc[mt][nt], lo.x, hi.x, lo.y, hi.y, bx[nt].x, bx[nt].y);
+            mma_bf16(acc[mt][nt], lo.z, hi.z, lo.w, hi.w, bx[nt].z, bx[nt].w);
+          }
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty_bar[s]);
+  }
+  if (seg_r >= 0) flush(seg_r);
+}
 
 template <typename WT, int NB, int MT, int STAGES>
-int32_t launch_t(Ctx* ctx, const GemvParams& p, cudaStream_t stream) {
+int32_t launch_ring(Ctx* ctx, const GemvParams& p, cudaStream_t stream) {
   constexpr int Bp = 8 * NB, RPC = 2 * MT * 16;
-  const int Ks = p.kc_per_split * 32;
-  const size_t xs_bytes = (size_t)Bp * (Ks + 32) * sizeof(WT);
+  const size_t xs_bytes = (size_t)p.kc_per_split * Bp * 32 * sizeof(WT);
   const size_t red_bytes = (size_t)4 * RPC * (Bp + 1) * sizeof(float);
   const size_t smem = xs_bytes > red_bytes ? xs_bytes : red_bytes;
-  auto kern = gemv_kernel<WT, NB, MT, STAGES>;
   LMB_REQUIRE(smem <= kMaxSmem, "gemv: %zu bytes of shared memory exceed the configured %zu", smem, kMaxSmem);
   dim3 grid((unsigned)ceil_div(p.RB, 2 * MT), (unsigned)p.ksplit);
-  kern<<<grid, kThreads, smem, stream>>>(p);
+  gemv_ring_kernel<WT, NB, MT, STAGES><<<grid, kRingThreads, smem, stream>>>(p);
+  ctx->launches++;
+  LMB_CUDA(cudaGetLastError());
+  return LMB200_OK;
+}
+
+template <int NB>
+constexpr size_t stream_smem() {
+  return (size_t)kStages * (kWStage + kCH * 8 * NB * 64) + (size_t)kRPC * (8 * NB + 1) * sizeof(float);
+}
+
+template <int NB>
+int32_t launch_stream(Ctx* ctx, const GemvParams& p, cudaStream_t stream) {
+  gemv_stream_kernel<NB><<<p.grid, kStreamThreads, stream_smem<NB>(), stream>>>(p, ctx->dev_err);
   ctx->launches++;
   LMB_CUDA(cudaGetLastError());
   return LMB200_OK;
@@ -314,17 +561,33 @@ constexpr size_t kMaxXsBytes = 96 * 1024;
 
 }  // namespace
 
-void gemv_plan(const Ctx* ctx, int dtype, int B, int RB, int KC, int* ksplit, int* kc_per_split,
-               int64_t* partial_floats, int* n_counters) {
+void gemv_set_stream_kernel(bool on) { g_use_stream = on; }
+
+GemvPlan gemv_plan(const Ctx* ctx, int dtype, int B, int RB, int KC) {
+  GemvPlan pl;
+  const int Bp = batch_pad(B);
+  if (dtype == LMB200_BF16 && g_use_stream) {
+    const int KS = (int)ceil_div(KC, kCH);
+    const int nrbg = (int)ceil_div(RB, 8);
+    const int64_t U = (int64_t)nrbg * KS;
+    int G = ctx->sm_count;
+    if (G > U) G = (int)U;
+    pl.grid = G;
+    const int64_t upc_min = U / G;                       // >= 1
+    pl.ksplit = (int)ceil_div(KS, upc_min) + 1;          // contributors reserved per row group
+    pl.kc_per_split = KC;
+    pl.partial_floats = (int64_t)nrbg * pl.ksplit * kRPC * Bp;
+    pl.n_counters = nrbg;
+    return pl;
+  }
   const int MT = dtype == LMB200_BF16 ? kMtBf16 : kMtF32;
-  const int NB = B <= 8 ? 1 : (B <= 16 ? 2 : 4);
-  const int Bp = 8 * NB, RPC = 2 * MT * 16;
+  const int RPC = 2 * MT * 16;
   const size_t esz = dtype == LMB200_BF16 ? 2 : 4;
   const int nrbg = (int)ceil_div(RB, 2 * MT);
   // One CTA per SM is resident (register ring).  Pick the k-split that minimises
   //   waves * (chunks per CTA + fixed cost of staging x and the epilogue, in chunk units)
   // with the activation slice fitting shared memory and at least one chunk per k-warp.
-  const int per_max = (int)(kMaxXsBytes / (Bp * esz) / 32) - 1;
+  const int per_max = (int)(kMaxXsBytes / (Bp * 32 * esz));
   const int kFixed = 6;
   int best_ks = 1, best_per = KC;
   double best_cost = 1e30;
@@ -337,46 +600,57 @@ void gemv_plan(const Ctx* ctx, int dtype, int B, int RB, int KC, int* ksplit, in
     const double cost = waves * (per_try + kFixed) + 0.02 * ks_eff;
     if (cost < best_cost) { best_cost = cost; best_ks = ks_eff; best_per = per_try; }
   }
-  int ks = best_ks, per = best_per;
-  *ksplit = ks;
-  *kc_per_split = per;
-  *partial_floats = ks > 1 ? (int64_t)nrbg * ks * RPC * Bp : 0;
-  *n_counters = nrbg;
+  pl.ksplit = best_ks;
+  pl.kc_per_split = best_per;
+  pl.grid = nrbg * best_ks;
+  pl.partial_floats = best_ks > 1 ? (int64_t)nrbg * best_ks * RPC * Bp : 0;
+  pl.n_counters = nrbg;
+  return pl;
 }
 
 // Raise the dynamic shared-memory limit of every instantiation once per device, outside any
 // stream capture.
 int32_t gemv_configure() {
-#define LMB_CFG(...)                                                                              \
-  LMB_CUDA(cudaFuncSetAttribute(gemv_kernel<__VA_ARGS__>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                (int)kMaxSmem))
-  LMB_CFG(__nv_bfloat16, 1, kMtBf16, 4);
-  LMB_CFG(__nv_bfloat16, 2, kMtBf16, 4);
-  LMB_CFG(__nv_bfloat16, 4, kMtBf16, 3);
-  LMB_CFG(float, 1, kMtF32, 3);
-  LMB_CFG(float, 2, kMtF32, 3);
-  LMB_CFG(float, 4, kMtF32, 2);
+#define LMB_CFG(KERN, BYTES) \
+  LMB_CUDA(cudaFuncSetAttribute(KERN, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(BYTES)))
+  LMB_CFG((gemv_ring_kernel<__nv_bfloat16, 1, kMtBf16, 4>), kMaxSmem);
+  LMB_CFG((gemv_ring_kernel<__nv_bfloat16, 2, kMtBf16, 4>), kMaxSmem);
+  LMB_CFG((gemv_ring_kernel<__nv_bfloat16, 4, kMtBf16, 3>), kMaxSmem);
+  LMB_CFG((gemv_ring_kernel<float, 1, kMtF32, 3>), kMaxSmem);
+  LMB_CFG((gemv_ring_kernel<float, 2, kMtF32, 3>), kMaxSmem);
+  LMB_CFG((gemv_ring_kernel<float, 4, kMtF32, 2>), kMaxSmem);
+  LMB_CFG(gemv_stream_kernel<1>, stream_smem<1>());
+  LMB_CFG(gemv_stream_kernel<2>, stream_smem<2>());
+  LMB_CFG(gemv_stream_kernel<4>, stream_smem<4>());
 #undef LMB_CFG
   return LMB200_OK;
 }
 
 int32_t gemv_launch(Ctx* ctx, int dtype, GemvParams p, cudaStream_t stream) {
   LMB_REQUIRE(p.B >= 1 && p.B <= 32, "gemv: batch %d outside 1..32", p.B);
+  const int nb = batch_pad(p.B) / 8;
+  if (dtype == LMB200_BF16 && g_use_stream) {
+    LMB_REQUIRE(p.grid >= 1 && p.partials && p.counters, "gemv: stream kernel needs a plan and scratch");
+    switch (nb) {
+      case 1: return launch_stream<1>(ctx, p, stream);
+      case 2: return launch_stream<2>(ctx, p, stream);
+      default: return launch_stream<4>(ctx, p, stream);
+    }
+  }
   LMB_REQUIRE(p.ksplit >= 1 && p.kc_per_split >= 1 && (int64_t)p.ksplit * p.kc_per_split >= p.KC,
               "gemv: bad k split");
   LMB_REQUIRE(p.ksplit == 1 || (p.partials && p.counters), "gemv: split-K needs scratch");
-  const int nb = p.B <= 8 ? 1 : (p.B <= 16 ? 2 : 4);
   if (dtype == LMB200_BF16) {
     switch (nb) {
-      case 1: return launch_t<__nv_bfloat16, 1, kMtBf16, 4>(ctx, p, stream);
-      case 2: return launch_t<__nv_bfloat16, 2, kMtBf16, 4>(ctx, p, stream);
-      default: return launch_t<__nv_bfloat16, 4, kMtBf16, 3>(ctx, p, stream);
+      case 1: return launch_ring<__nv_bfloat16, 1, kMtBf16, 4>(ctx, p, stream);
+      case 2: return launch_ring<__nv_bfloat16, 2, kMtBf16, 4>(ctx, p, stream);
+      default: return launch_ring<__nv_bfloat16, 4, kMtBf16, 3>(ctx, p, stream);
     }
   } else if (dtype == LMB200_F32) {
     switch (nb) {
-      case 1: return launch_t<float, 1, kMtF32, 3>(ctx, p, stream);
-      case 2: return launch_t<float, 2, kMtF32, 3>(ctx, p, stream);
-      default: return launch_t<float, 4, kMtF32, 2>(ctx, p, stream);
+      case 1: return launch_ring<float, 1, kMtF32, 3>(ctx, p, stream);
+      case 2: return launch_ring<float, 2, kMtF32, 3>(ctx, p, stream);
+      default: return launch_ring<float, 4, kMtF32, 2>(ctx, p, stream);
     }
   }
   return fail(LMB200_EINVAL, "gemv: dtype %d", dtype);

@@ -14,23 +14,23 @@ enum GemvEpilogue {
 
 struct GemvParams {
   const void* W = nullptr;   // tiled weights (wtile_offset)
-  const void* x = nullptr;   // activations [B, x_pitch], same element type as W
+  const void* x = nullptr;   // tiled activations (xtile_offset), same element type as W
   int B = 0;
-  int x_pitch = 0;
   int rows = 0;              // valid logical rows (<= 16*RB)
   int RB = 0;                // 16-row blocks
   int KC = 0;                // 32-wide k chunks
-  int ksplit = 1;
+  // work split, filled by gemv_plan
+  int ksplit = 1;            // ring kernel: k-splits (gridDim.y)
   int kc_per_split = 0;
-  float* partials = nullptr;     // split-K scratch [gridDim.x, ksplit, rows_per_cta, 8*NB]
-  unsigned* counters = nullptr;  // one per blockIdx.x, zero between launches
+  int grid = 0;              // stream kernel: number of CTAs
+  float* partials = nullptr;     // split-K scratch
+  unsigned* counters = nullptr;  // one per row group, zero between launches
   int epi = EPI_STORE_F32;
   // EPI_STORE_F32
   float* out = nullptr;
   int out_pitch = 0;
-  // EPI_SILU_GATE
+  // EPI_SILU_GATE: act is a tiled activation buffer of the same batch padding as x
   void* act = nullptr;
-  int act_pitch = 0;
   int n_act = 0;
   // EPI_QKV_ROPE
   void* q_out = nullptr;     // [B, q_pitch], head-major (local head * D + d)
@@ -43,11 +43,17 @@ struct GemvParams {
   int Hl = 0, KVl = 0, D = 0;
 };
 
-// dtype: LMB200_F32 or LMB200_BF16.  Picks tile shape from B and the row count.
-int32_t gemv_launch(Ctx* ctx, int dtype, GemvParams p, cudaStream_t stream);
+struct GemvPlan {
+  int ksplit = 1, kc_per_split = 0, grid = 0;
+  int64_t partial_floats = 0;
+  int n_counters = 0;
+};
+
 int32_t gemv_configure();
-// scratch the launch above needs for the given problem (bytes of partials, number of counters)
-void gemv_plan(const Ctx* ctx, int dtype, int B, int RB, int KC, int* ksplit, int* kc_per_split,
-               int64_t* partial_floats, int* n_counters);
+// bf16 kernel choice: true = bulk-TMA stream-K kernel (default), false = register-ring kernel
+void gemv_set_stream_kernel(bool on);
+GemvPlan gemv_plan(const Ctx* ctx, int dtype, int B, int RB, int KC);
+// dtype: LMB200_F32 or LMB200_BF16
+int32_t gemv_launch(Ctx* ctx, int dtype, GemvParams p, cudaStream_t stream);
 
 }  // namespace lmb

@@ -143,31 +143,47 @@ __global__ void fill_kv_kernel(WT* kv, int64_t batch_stride, int64_t head_stride
 // ---------------------------------------------------------------------------------------------
 // x <- embedding row (first layer) or x + delta (residual add of the previous projection), then
 // xn = (x * recip(sqrt(mean(x*x) + eps))) * w          src/HighLevelOps.jl:299-304, NN.jl:149-161
+// One CTA per sequence; the row stays in shared memory between the two passes and all global
+// accesses are independent float4s, so the kernel costs a couple of memory round trips.
+// xn is a tiled activation buffer (xtile_offset) of batch padding Bp.  n % 4 == 0.
+constexpr int kNormThreads = 512;
 template <typename WT>
-__global__ void __launch_bounds__(256) add_rmsnorm_kernel(float* x, const float* delta, const int* tokens,
-                                                          const WT* embed, int vocab, const float* w,
-                                                          WT* xn, int xn_pitch, int n, float eps,
-                                                          float* capture) {
-  __shared__ float red[8];
+__global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta,
+                                                                   const int* __restrict__ tokens,
+                                                                   const WT* __restrict__ embed, int vocab,
+                                                                   const float* __restrict__ w, WT* __restrict__ xn,
+                                                                   int Bp, int n, float eps,
+                                                                   float* __restrict__ capture) {
+  extern __shared__ __align__(16) float row[];
+  __shared__ float red[kNormThreads / 32];
   const int b = blockIdx.x, tid = threadIdx.x;
-  float* xr = x + (int64_t)b * n;
+  const int n4 = n >> 2;
+  float4* xr = reinterpret_cast<float4*>(x + (int64_t)b * n);
+  float4* rs = reinterpret_cast<float4*>(row);
   float ss = 0.f;
   if (tokens) {
     const int tok = tokens[b];
     const bool ok = tok >= 0 && tok < vocab;     // out of range -> zeros, as _gather_kernel! does
     const WT* er = embed + (int64_t)(ok ? tok : 0) * n;
-    for (int i = tid; i < n; i += 256) {
-      const float v = ok ? to_f32(er[i]) : 0.f;
+#pragma unroll 4
+    for (int i = tid; i < n4; i += kNormThreads) {
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (ok) v = make_float4(to_f32(er[4 * i]), to_f32(er[4 * i + 1]), to_f32(er[4 * i + 2]), to_f32(er[4 * i + 3]));
       xr[i] = v;
-      ss += v * v;
+      rs[i] = v;
+      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
     }
   } else {
-    const float* dr = delta ? delta + (int64_t)b * n : nullptr;
-    for (int i = tid; i < n; i += 256) {
-      const float v = dr ? xr[i] + dr[i] : xr[i];
+    const float4* dr = delta ? reinterpret_cast<const float4*>(delta + (int64_t)b * n) : nullptr;
+    float4* cr = capture ? reinterpret_cast<float4*>(capture + (int64_t)b * n) : nullptr;
+#pragma unroll 4
+    for (int i = tid; i < n4; i += kNormThreads) {
+      float4 v = xr[i];
+      if (dr) { const float4 d = dr[i]; v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w; }
       xr[i] = v;
-      if (capture) capture[(int64_t)b * n + i] = v;
-      ss += v * v;
+      rs[i] = v;
+      if (cr) cr[i] = v;
+      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
     }
   }
 #pragma unroll
@@ -176,12 +192,20 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(float* x, const float*
   __syncthreads();
   float tot = 0.f;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) tot += red[i];
+  for (int i = 0; i < kNormThreads / 32; ++i) tot += red[i];
   const float var = tot * (1.0f / (float)n);
   const float inv = 1.0f / sqrtf(var + eps);
   if (xn) {
-    WT* o = xn + (int64_t)b * xn_pitch;
-    for (int i = tid; i < n; i += 256) o[i] = from_f32<WT>((xr[i] * inv) * w[i]);
+    const float4* w4 = reinterpret_cast<const float4*>(w);
+#pragma unroll 4
+    for (int i = tid; i < n4; i += kNormThreads) {
+      const float4 v = rs[i], g = w4[i];
+      WT* o = xn + xtile_offset(b, 4 * i, Bp);       // 4 consecutive k never straddle a 32-chunk
+      o[0] = from_f32<WT>((v.x * inv) * g.x);
+      o[1] = from_f32<WT>((v.y * inv) * g.y);
+      o[2] = from_f32<WT>((v.z * inv) * g.z);
+      o[3] = from_f32<WT>((v.w * inv) * g.w);
+    }
   }
 }
 
@@ -525,6 +549,15 @@ extern "C" int32_t lmb200_model_set_weight(lmb200_model h, const char* name, con
 namespace lmb {
 namespace {
 
+GemvParams gemv_params(Session* S, const void* W, const WMap& m, const GemvPlan& pl, const void* x) {
+  GemvParams p;
+  p.W = W; p.x = x; p.B = S->B;
+  p.rows = m.rows; p.RB = m.RB; p.KC = m.KC;
+  p.ksplit = pl.ksplit; p.kc_per_split = pl.kc_per_split; p.grid = pl.grid;
+  p.partials = S->gemv_partials; p.counters = S->gemv_counters;
+  return p;
+}
+
 template <typename WT>
 int32_t enqueue_step_t(Session* S, cudaStream_t st, bool with_head) {
   Model* M = S->m;
@@ -533,85 +566,66 @@ int32_t enqueue_step_t(Session* S, cudaStream_t st, bool with_head) {
   const int dt = c.dtype;
   const int B = S->B, hid = c.hidden;
   const int L = c.n_layers;
+  const size_t norm_smem = (size_t)hid * sizeof(float);
   for (int l = 0; l < L; ++l) {
     LayerWeights& W = M->layers[l];
     // residual add of the previous MLP (or the embedding gather) + attention RMSNorm
-    add_rmsnorm_kernel<WT><<<B, 256, 0, st>>>(
+    add_rmsnorm_kernel<WT><<<B, kNormThreads, norm_smem, st>>>(
         S->x, l == 0 ? nullptr : S->delta, l == 0 ? S->tokens : nullptr, reinterpret_cast<const WT*>(M->embed),
-        c.vocab, W.attn_norm, reinterpret_cast<WT*>(S->xn), S->xn_pitch, hid, c.rms_eps,
+        c.vocab, W.attn_norm, reinterpret_cast<WT*>(S->xn), S->Bp, hid, c.rms_eps,
         (S->capture_on && l > 0) ? S->capture + (int64_t)(l - 1) * B * hid : nullptr);
     ctx->launches++;
     LMB_CUDA(cudaGetLastError());
     void* kv_layer = reinterpret_cast<char*>(S->kv) + (int64_t)l * S->kv_layer_stride * M->esz;
     {  // q/k/v projections + RoPE + KV append
-      GemvParams p;
-      p.W = W.wqkv; p.x = S->xn; p.B = B; p.x_pitch = S->xn_pitch;
-      p.rows = M->m_qkv.rows; p.RB = M->m_qkv.RB; p.KC = M->m_qkv.KC;
-      p.ksplit = S->p_qkv.ksplit; p.kc_per_split = S->p_qkv.kc_per_split;
-      p.partials = S->gemv_partials; p.counters = S->gemv_counters;
+      GemvParams p = gemv_params(S, W.wqkv, M->m_qkv, S->p_qkv, S->xn);
       p.epi = EPI_QKV_ROPE;
       p.q_out = S->qbuf; p.q_pitch = S->q_pitch;
       p.kv_layer = kv_layer; p.kv_batch_stride = S->kv_batch_stride; p.kv_head_stride = S->kv_head_stride;
       p.inv_freq = M->inv_freq; p.pos = S->pos; p.Hl = M->Hl; p.KVl = M->KVl; p.D = M->D;
       LMB_TRY(gemv_launch(ctx, dt, p, st));
     }
-    {  // attention over the cache
+    {  // attention over the cache; the result is the tiled input of o_proj
       AttnParams a;
       a.q = S->qbuf; a.q_pitch = S->q_pitch; a.kv_layer = kv_layer;
       a.kv_batch_stride = S->kv_batch_stride; a.kv_head_stride = S->kv_head_stride;
       a.B = B; a.KVl = M->KVl; a.G = M->G; a.D = M->D; a.pos = S->pos;
       a.keys_per_cta = S->keys_per_cta; a.nsplit = S->nsplit;
       a.scale = 1.0f / sqrtf((float)M->D);
-      a.part_o = S->part_o; a.part_ml = S->part_ml; a.out = S->attn_out; a.out_pitch = S->q_pitch;
+      a.part_o = S->part_o; a.part_ml = S->part_ml; a.out = S->attn_out; a.out_tiled_bp = S->Bp;
       LMB_TRY(attn_decode_launch(ctx, dt, a, st));
     }
     {  // o_proj (row-parallel under TP)
-      GemvParams p;
-      p.W = W.wo; p.x = S->attn_out; p.B = B; p.x_pitch = S->q_pitch;
-      p.rows = M->m_o.rows; p.RB = M->m_o.RB; p.KC = M->m_o.KC;
-      p.ksplit = S->p_o.ksplit; p.kc_per_split = S->p_o.kc_per_split;
-      p.partials = S->gemv_partials; p.counters = S->gemv_counters;
+      GemvParams p = gemv_params(S, W.wo, M->m_o, S->p_o, S->attn_out);
       p.epi = EPI_STORE_F32; p.out = S->delta; p.out_pitch = hid;
       LMB_TRY(gemv_launch(ctx, dt, p, st));
       if (c.tp_size > 1) LMB_TRY(nccl_allreduce_f32(ctx, S->delta, (int64_t)B * hid, st));
     }
-    add_rmsnorm_kernel<WT><<<B, 256, 0, st>>>(S->x, S->delta, nullptr, nullptr, 0, W.ffn_norm,
-                                              reinterpret_cast<WT*>(S->xn), S->xn_pitch, hid, c.rms_eps, nullptr);
+    add_rmsnorm_kernel<WT><<<B, kNormThreads, norm_smem, st>>>(S->x, S->delta, nullptr, nullptr, 0, W.ffn_norm,
+                                                               reinterpret_cast<WT*>(S->xn), S->Bp, hid, c.rms_eps,
+                                                               nullptr);
     ctx->launches++;
     LMB_CUDA(cudaGetLastError());
     {  // gate/up + SiLU gate
-      GemvParams p;
-      p.W = W.wgu; p.x = S->xn; p.B = B; p.x_pitch = S->xn_pitch;
-      p.rows = M->m_gu.rows; p.RB = M->m_gu.RB; p.KC = M->m_gu.KC;
-      p.ksplit = S->p_gu.ksplit; p.kc_per_split = S->p_gu.kc_per_split;
-      p.partials = S->gemv_partials; p.counters = S->gemv_counters;
-      p.epi = EPI_SILU_GATE; p.act = S->act; p.act_pitch = S->act_pitch; p.n_act = M->inter_l;
+      GemvParams p = gemv_params(S, W.wgu, M->m_gu, S->p_gu, S->xn);
+      p.epi = EPI_SILU_GATE; p.act = S->act; p.n_act = M->inter_l;
       LMB_TRY(gemv_launch(ctx, dt, p, st));
     }
     {  // down_proj (row-parallel under TP)
-      GemvParams p;
-      p.W = W.wdown; p.x = S->act; p.B = B; p.x_pitch = S->act_pitch;
-      p.rows = M->m_down.rows; p.RB = M->m_down.RB; p.KC = M->m_down.KC;
-      p.ksplit = S->p_down.ksplit; p.kc_per_split = S->p_down.kc_per_split;
-      p.partials = S->gemv_partials; p.counters = S->gemv_counters;
+      GemvParams p = gemv_params(S, W.wdown, M->m_down, S->p_down, S->act);
       p.epi = EPI_STORE_F32; p.out = S->delta; p.out_pitch = hid;
       LMB_TRY(gemv_launch(ctx, dt, p, st));
       if (c.tp_size > 1) LMB_TRY(nccl_allreduce_f32(ctx, S->delta, (int64_t)B * hid, st));
     }
   }
   // last residual add (+ final norm); without the head only the add is needed for the capture
-  add_rmsnorm_kernel<WT><<<B, 256, 0, st>>>(S->x, S->delta, nullptr, nullptr, 0, M->final_norm,
-                                            with_head ? reinterpret_cast<WT*>(S->xn) : nullptr, S->xn_pitch, hid,
-                                            c.rms_eps,
-                                            S->capture_on ? S->capture + (int64_t)(L - 1) * B * hid : nullptr);
+  add_rmsnorm_kernel<WT><<<B, kNormThreads, norm_smem, st>>>(
+      S->x, S->delta, nullptr, nullptr, 0, M->final_norm, with_head ? reinterpret_cast<WT*>(S->xn) : nullptr, S->Bp,
+      hid, c.rms_eps, S->capture_on ? S->capture + (int64_t)(L - 1) * B * hid : nullptr);
   ctx->launches++;
   LMB_CUDA(cudaGetLastError());
   if (with_head) {
-    GemvParams p;
-    p.W = M->lm_head; p.x = S->xn; p.B = B; p.x_pitch = S->xn_pitch;
-    p.rows = M->m_head.rows; p.RB = M->m_head.RB; p.KC = M->m_head.KC;
-    p.ksplit = S->p_head.ksplit; p.kc_per_split = S->p_head.kc_per_split;
-    p.partials = S->gemv_partials; p.counters = S->gemv_counters;
+    GemvParams p = gemv_params(S, M->lm_head, M->m_head, S->p_head, S->xn);
     p.epi = EPI_STORE_F32; p.out = S->logits; p.out_pitch = S->logits_pitch;
     LMB_TRY(gemv_launch(ctx, dt, p, st));
     argmax_step_kernel<<<B, 256, 0, st>>>(S->logits, S->logits_pitch, c.vocab, S->tokens, S->tok_hist, S->step_ctr, B);
@@ -693,18 +707,16 @@ extern "C" int32_t lmb200_session_create(lmb200_model hm, int32_t batch, int32_t
   S->kv_head_stride = (int64_t)(S->cap / 16) * kv_block_elems(M->D);
   S->kv_batch_stride = S->kv_head_stride * M->KVl;
   S->kv_layer_stride = S->kv_batch_stride * batch;
-  S->xn_pitch = (int)round_up(c.hidden, 32);
-  S->q_pitch = (int)round_up(M->Hl * M->D, 32);
-  S->act_pitch = (int)round_up(M->inter_l, 32);
+  S->Bp = batch_pad(batch);
+  S->q_pitch = M->Hl * M->D;
   S->logits_pitch = (int)round_up(c.vocab, 16);
 
   int64_t max_part = 0;
   int max_cnt = 0;
   auto plan = [&](GemvPlan& g, const WMap& m) {
-    int64_t pf; int nc;
-    gemv_plan(ctx, c.dtype, batch, m.RB, m.KC, &g.ksplit, &g.kc_per_split, &pf, &nc);
-    if (pf > max_part) max_part = pf;
-    if (nc > max_cnt) max_cnt = nc;
+    g = gemv_plan(ctx, c.dtype, batch, m.RB, m.KC);
+    if (g.partial_floats > max_part) max_part = g.partial_floats;
+    if (g.n_counters > max_cnt) max_cnt = g.n_counters;
   };
   plan(S->p_qkv, M->m_qkv); plan(S->p_o, M->m_o); plan(S->p_gu, M->m_gu); plan(S->p_down, M->m_down);
   plan(S->p_head, M->m_head);
@@ -717,10 +729,11 @@ extern "C" int32_t lmb200_session_create(lmb200_model hm, int32_t batch, int32_t
   alloc((void**)&S->x, (int64_t)batch * c.hidden * 4);
   alloc((void**)&S->delta, (int64_t)batch * c.hidden * 4);
   alloc((void**)&S->logits, (int64_t)batch * S->logits_pitch * 4);
-  alloc(&S->xn, (int64_t)batch * S->xn_pitch * M->esz);
+  // tiled GEMV inputs: [k chunks][Bp][32], zero in the padding rows and columns
+  alloc(&S->xn, (int64_t)M->m_qkv.KC * S->Bp * 32 * M->esz);
   alloc(&S->qbuf, (int64_t)batch * S->q_pitch * M->esz);
-  alloc(&S->attn_out, (int64_t)batch * S->q_pitch * M->esz);
-  alloc(&S->act, (int64_t)batch * S->act_pitch * M->esz);
+  alloc(&S->attn_out, (int64_t)M->m_o.KC * S->Bp * 32 * M->esz);
+  alloc(&S->act, (int64_t)M->m_down.KC * S->Bp * 32 * M->esz);
   alloc((void**)&S->tokens, (int64_t)batch * 4);
   alloc((void**)&S->pos, 4);
   alloc((void**)&S->step_ctr, 4);
@@ -873,7 +886,7 @@ extern "C" int32_t lmb200_prefill(lmb200_session h, const int32_t* tokens, int32
   }
   if (logits_out) LMB_TRY(copy_logits_out(S, logits_out));
   LMB_CUDA(cudaStreamSynchronize(ctx->stream));
-  return LMB200_OK;
+  return check_device_error(ctx);
 }
 
 extern "C" int32_t lmb200_decode_step(lmb200_session h, const int32_t* tokens_in, int32_t* next_tokens_out,
@@ -892,7 +905,7 @@ extern "C" int32_t lmb200_decode_step(lmb200_session h, const int32_t* tokens_in
     LMB_CUDA(cudaMemcpyAsync(next_tokens_out, S->tokens, (size_t)S->B * 4, cudaMemcpyDeviceToHost, ctx->stream));
   if (logits_out) LMB_TRY(copy_logits_out(S, logits_out));
   LMB_CUDA(cudaStreamSynchronize(ctx->stream));
-  return LMB200_OK;
+  return check_device_error(ctx);
 }
 
 static int32_t decode_n_common(Session* S, const int32_t* first, bool first_on_device, int32_t n_steps) {
@@ -917,7 +930,7 @@ extern "C" int32_t lmb200_decode_n(lmb200_session h, const int32_t* first_tokens
   if (tokens_out)
     LMB_CUDA(cudaMemcpyAsync(tokens_out, S->tok_hist, (size_t)n_steps * S->B * 4, cudaMemcpyDeviceToHost, ctx->stream));
   LMB_CUDA(cudaStreamSynchronize(ctx->stream));
-  return LMB200_OK;
+  return check_device_error(ctx);
 }
 
 extern "C" int32_t lmb200_decode_n_device(lmb200_session h, const int32_t* first_dptr, int32_t n_steps, int32_t* out_dptr) {

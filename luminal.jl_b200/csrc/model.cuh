@@ -27,8 +27,6 @@ struct WMap {
   int src_cols[3] = {0, 0, 0};
 };
 
-struct GemvPlan { int ksplit = 1, kc_per_split = 0; };
-
 struct LayerWeights {
   void* wqkv = nullptr;
   void* wo = nullptr;
@@ -69,7 +67,8 @@ struct Session {
   void* qbuf = nullptr;
   void* attn_out = nullptr;
   void* act = nullptr;
-  int xn_pitch = 0, q_pitch = 0, act_pitch = 0, logits_pitch = 0;
+  int Bp = 0;                   // batch padding of the tiled activation buffers (8, 16 or 32)
+  int q_pitch = 0, logits_pitch = 0;
   int* tokens = nullptr;
   int* pos = nullptr;
   int* step_ctr = nullptr;

@@ -62,7 +62,8 @@ def test_small_llama_fp32_greedy_matches_oracle(lib_built, device):
     sess.close(); model.close()
 
 
-@pytest.mark.parametrize("name,batch", [("tiny_gqa128", 3), ("tiny_gqa96", 2), ("small_llama", 9), ("tiny_gqa128", 17)])
+@pytest.mark.parametrize("name,batch", [("tiny_gqa128", 3), ("tiny_gqa96", 2), ("small_llama", 9), ("tiny_gqa128", 17),
+                                        ("mid_gqa", 2)])
 def test_gqa_fp32_matches_oracle(lib_built, device, name, batch):
     """Reduced shapes of the Llama-3-8B (head_dim 128, GQA) and Phi-3 (head_dim 96) paths and
     the three batch tilings (<=8, <=16, <=32)."""
@@ -80,7 +81,8 @@ def test_gqa_fp32_matches_oracle(lib_built, device, name, batch):
     sess.close(); model.close()
 
 
-@pytest.mark.parametrize("name,batch", [("tiny_gqa128", 4), ("tiny_gqa96", 16), ("small_llama", 32)])
+@pytest.mark.parametrize("name,batch", [("tiny_gqa128", 4), ("tiny_gqa96", 16), ("small_llama", 32),
+                                        ("mid_gqa", 32), ("mid_gqa", 5)])
 def test_bf16_layer_outputs_within_tolerance(lib_built, device, name, batch):
     L = lib_built
     cfg = O.CONFIGS[name]
