@@ -5,11 +5,13 @@
 // per SM and CTA c takes the contiguous unit range [c*U/G, (c+1)*U/G), so every SM streams the
 // same number of bytes in a single wave whatever the matrix shape.  A producer warp keeps a ring
 // of STAGES shared-memory stages full with cp.async.bulk copies (weights evict-first, plus the
-// matching slice of the tiled activations) signalled through mbarriers; 8 consumer warps (2 row
-// groups x 4 k-chunks) read their MMA operands from the stage with conflict-free 16-byte loads
-// and issue mma.sync m16n8k16.  When a CTA's range leaves a 128-row group it folds its partial
-// tile: alone -> epilogue; shared -> global scratch + counter, the last contributor sums the
-// parts in CTA order (deterministic) and runs the epilogue.
+// matching slice of the tiled activations) signalled through mbarriers; 8 consumer warps read
+// their MMA operands from the stage with conflict-free 16-byte loads
+// and issue mma.sync m16n8k16; each consumer warp owns one 16-row block of the group, so nothing
+// is reduced across warps and the fused epilogue runs from the accumulator registers.  When a
+// CTA's range leaves a row group its warps fold their fragments: alone -> epilogue; shared ->
+// global scratch + a per-row-block counter, the last contributing warp sums the fragments in CTA
+// order (deterministic) and runs the epilogue.  No CTA-wide barrier after start-up.
 //
 // "ring" kernel: weights streamed by plain loads through a register ring; used for float32 (the
 // parity path, fp32 FMAs) and selectable for bf16 (A/B comparison).
@@ -360,19 +362,98 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
       "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
       : "memory");
 }
-__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 256;\n" ::: "memory"); }
+
+// Epilogue of one 16-row block straight from the accumulator fragments of the warp that owns it:
+// lane (g,t) holds, per batch tile nt, rows g (c0,c1) and g+8 (c2,c3) at columns 8nt+2t, +1 --
+// and rows g / g+8 are exactly the pairs the fused epilogues combine.
+template <int NB>
+__device__ __forceinline__ void fragment_epilogue(const GemvParams& p, const float (&acc)[NB][4], int rb, int g, int t) {
+  constexpr int Bp = 8 * NB;
+  if (p.epi == EPI_STORE_F32) {
+    const int row = rb * 16 + g;
+#pragma unroll
+    for (int nt = 0; nt < NB; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int b = 8 * nt + 2 * t + e;
+        if (b < p.B) {
+          if (row < p.rows) p.out[(int64_t)b * p.out_pitch + row] = acc[nt][e];
+          if (row + 8 < p.rows) p.out[(int64_t)b * p.out_pitch + row + 8] = acc[nt][2 + e];
+        }
+      }
+    }
+  } else if (p.epi == EPI_SILU_GATE) {
+    __nv_bfloat16* act = reinterpret_cast<__nv_bfloat16*>(p.act);
+    const int o = rb * 8 + g;
+    if (o < p.n_act) {
+#pragma unroll
+      for (int nt = 0; nt < NB; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int b = 8 * nt + 2 * t + e;
+          if (b < p.B) {
+            const float a = acc[nt][e], u = acc[nt][2 + e];
+            // silu(a) = a * (1 / (1 + exp2((a * -1) * (1/ln2))))     src/HighLevelOps.jl:153-160
+            const float ex = exp2f((a * -1.0f) * kInvLn2);
+            const float sg = 1.0f / (1.0f + ex);
+            act[xtile_offset(b, o, Bp)] = __float2bfloat16_rn((a * sg) * u);
+          }
+        }
+      }
+    }
+  } else {  // EPI_QKV_ROPE
+    __nv_bfloat16* q_out = reinterpret_cast<__nv_bfloat16*>(p.q_out);
+    __nv_bfloat16* kv = reinterpret_cast<__nv_bfloat16*>(p.kv_layer);
+    const int D = p.D, tiles_per_head = D >> 4, half = D >> 1;
+    const int pos = *p.pos;
+    const int hs = rb / tiles_per_head, jj = rb - hs * tiles_per_head;
+    float sn = 0.f, cs = 1.f;
+    const bool rope = hs < p.Hl + p.KVl;
+    const int d0 = 8 * jj + g;
+    if (rope) {
+      // rows g / g+8 of the block are the RoPE pair (d0, d0 + D/2)      src/NN.jl:253-303
+      const float ang = (float)pos * p.inv_freq[d0];
+      sn = sinf(ang);
+      cs = sinf(kHalfPi + ang * -1.0f);   // cos(a) = sin(pi/2 - a)
+    }
+#pragma unroll
+    for (int nt = 0; nt < NB; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int b = 8 * nt + 2 * t + e;
+        if (b >= p.B) continue;
+        const float v0 = acc[nt][e], v1 = acc[nt][2 + e];
+        if (rope) {
+          const float o0 = v0 * cs + (v1 * sn) * -1.0f;
+          const float o1 = v0 * sn + v1 * cs;
+          if (hs < p.Hl) {
+            __nv_bfloat16* q = q_out + (int64_t)b * p.q_pitch + hs * D;
+            q[d0] = __float2bfloat16_rn(o0);
+            q[d0 + half] = __float2bfloat16_rn(o1);
+          } else {
+            __nv_bfloat16* kc = kv + b * p.kv_batch_stride + (hs - p.Hl) * p.kv_head_stride;
+            kc[kcache_offset(pos, d0, D)] = __float2bfloat16_rn(o0);
+            kc[kcache_offset(pos, d0 + half, D)] = __float2bfloat16_rn(o1);
+          }
+        } else {
+          __nv_bfloat16* vc = kv + b * p.kv_batch_stride + (hs - p.Hl - p.KVl) * p.kv_head_stride;
+          const int d = 16 * jj + g;
+          vc[vcache_offset(pos, d, D)] = __float2bfloat16_rn(v0);
+          vc[vcache_offset(pos, d + 8, D)] = __float2bfloat16_rn(v1);
+        }
+      }
+    }
+  }
+}
 
 template <int NB>
 __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const GemvParams p, int* err) {
   constexpr int Bp = 8 * NB;
   constexpr int kXStage = kCH * Bp * 64;
   constexpr int kStage = kWStage + kXStage;
-  constexpr int RP = Bp + 1;
   extern __shared__ __align__(128) unsigned char smem[];
-  float* tile = reinterpret_cast<float*>(smem + kStages * kStage);
   __shared__ __align__(8) uint64_t full_bar[kStages];
   __shared__ __align__(8) uint64_t empty_bar[kStages];
-  __shared__ int s_last;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int KS = (p.KC + kCH - 1) / kCH;              // stage units per row group
@@ -420,74 +501,54 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const Ge
     return;
   }
 
-  // ---------------- consumers ----------------
+  // ---------------- consumers: warp w owns row block 8r + w of the current row group ----------------
   const int g = lane >> 2, t = lane & 3;
-  const int rg = warp >> 2, kw = warp & 3;
-  float acc[4][NB][4];
+  float acc[NB][4];
   auto zero_acc = [&]() {
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-      for (int j = 0; j < NB; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f;
+    for (int j = 0; j < NB; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
   };
-  // fold the accumulators of the row group `r` that this CTA's range has just left
+  // Fold the accumulators of row group r, which this CTA's unit range has just left.  Everything
+  // is warp-local: alone -> epilogue; shared -> fragment to scratch, per-row-block counter, the
+  // last contributor sums the fragments in CTA order and runs the epilogue.
   auto flush = [&](int r) {
-#pragma unroll 1
-    for (int round = 0; round < 4; ++round) {
-      if (kw == round) {
-#pragma unroll
-        for (int mt = 0; mt < 4; ++mt) {
-          const int r0 = (rg * 4 + mt) * 16 + g;
-#pragma unroll
-          for (int nt = 0; nt < NB; ++nt) {
-            const int c = 8 * nt + 2 * t;
-            if (round == 0) {
-              tile[r0 * RP + c] = acc[mt][nt][0];
-              tile[r0 * RP + c + 1] = acc[mt][nt][1];
-              tile[(r0 + 8) * RP + c] = acc[mt][nt][2];
-              tile[(r0 + 8) * RP + c + 1] = acc[mt][nt][3];
-            } else {
-              tile[r0 * RP + c] += acc[mt][nt][0];
-              tile[r0 * RP + c + 1] += acc[mt][nt][1];
-              tile[(r0 + 8) * RP + c] += acc[mt][nt][2];
-              tile[(r0 + 8) * RP + c + 1] += acc[mt][nt][3];
-            }
-          }
-        }
-      }
-      consumer_sync();
-    }
-    // which CTAs share this row group?  CTA of unit u is ceil((u+1)*G/U) - 1
+    const int rb = r * 8 + warp;
+    if (rb >= p.RB) return;
     const long long ua = (long long)r * KS, ub = ua + KS - 1;
-    const int c_first = (int)(((ua + 1) * G + U - 1) / U) - 1;
+    const int c_first = (int)(((ua + 1) * G + U - 1) / U) - 1;     // CTA of unit u: ceil((u+1)G/U) - 1
     const int c_last = (int)(((ub + 1) * G + U - 1) / U) - 1;
     const int n = c_last - c_first + 1;
-    bool do_epilogue = true;
     if (n > 1) {
-      const int jmax = p.ksplit;      // contributors reserved per row group
-      float* part = p.partials + (int64_t)r * jmax * (kRPC * Bp);
-      float* mine = part + (int64_t)((int)blockIdx.x - c_first) * (kRPC * Bp);
-      for (int i = tid; i < kRPC * Bp; i += 256) {
-        const int rr = i / Bp, b = i - rr * Bp;
-        mine[i] = tile[rr * RP + b];
-      }
+      float4* part = reinterpret_cast<float4*>(p.partials) + (int64_t)rb * p.ksplit * (32 * NB);
+      float4* mine = part + (int64_t)((int)blockIdx.x - c_first) * (32 * NB) + lane * NB;
+#pragma unroll
+      for (int nt = 0; nt < NB; ++nt) mine[nt] = make_float4(acc[nt][0], acc[nt][1], acc[nt][2], acc[nt][3]);
       __threadfence();
-      consumer_sync();
-      if (tid == 0) {
-        const unsigned prev = atomicAdd(&p.counters[r], 1u);
-        s_last = (prev == (unsigned)n - 1u);
-      }
-      consumer_sync();
-      do_epilogue = s_last != 0;
-      if (do_epilogue) {
-        if (tid == 0) p.counters[r] = 0u;
-        __threadfence();
-        sum_partials(tile, part, n, kRPC * Bp, kRPC, RP, Bp, tid, 256);
-        consumer_sync();
+      __syncwarp();
+      unsigned prev = 0;
+      if (lane == 0) prev = atomicAdd(&p.counters[rb], 1u);
+      prev = __shfl_sync(0xffffffffu, prev, 0);
+      if (prev != (unsigned)n - 1u) return;
+      if (lane == 0) p.counters[rb] = 0u;          // ready for the next launch
+      __threadfence();
+      zero_acc();
+      for (int k0 = 0; k0 < n; k0 += 4) {
+        float4 v[4][NB];
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+#pragma unroll
+          for (int nt = 0; nt < NB; ++nt)
+            v[kk][nt] = (k0 + kk < n) ? __ldcg(part + (int64_t)(k0 + kk) * (32 * NB) + lane * NB + nt)
+                                      : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+#pragma unroll
+          for (int nt = 0; nt < NB; ++nt) {
+            acc[nt][0] += v[kk][nt].x; acc[nt][1] += v[kk][nt].y; acc[nt][2] += v[kk][nt].z; acc[nt][3] += v[kk][nt].w;
+          }
       }
     }
-    if (do_epilogue) run_epilogue<__nv_bfloat16>(p, tile, kRPC, RP, Bp, r * kRPC, tid, 256);
-    consumer_sync();       // the tile is reused by the next row group
+    fragment_epilogue<NB>(p, acc, rb, g, t);
   };
 
   zero_acc();
@@ -503,21 +564,20 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const Ge
     const int s = it % kStages, k = it / kStages;
     const int nch = min(kCH, p.KC - ks * kCH);
     mbar_wait(&full_bar[s], k & 1, dead, err);
-    if (kw < nch) {
+    if (r * 8 + warp < p.RB) {
       const unsigned char* st = smem + s * kStage;
-      const unsigned char* xst = st + kWStage + kw * (Bp * 64) + g * 64 + t * 16;
-      uint4 bx[NB];
+      const unsigned char* xst = st + kWStage + g * 64 + t * 16;
+      const unsigned char* wst = st + warp * (kCH * 1024) + lane * 32;
 #pragma unroll
-      for (int nt = 0; nt < NB; ++nt) bx[nt] = *reinterpret_cast<const uint4*>(xst + nt * 512);
-#pragma unroll
-      for (int mt = 0; mt < 4; ++mt) {
-        if (r * 8 + rg * 4 + mt < p.RB) {
-          const uint4* wp = reinterpret_cast<const uint4*>(st + ((rg * 4 + mt) * kCH + kw) * 1024 + lane * 32);
-          const uint4 lo = wp[0], hi = wp[1];
+      for (int c = 0; c < kCH; ++c) {
+        if (c < nch) {
+          const uint4 lo = *reinterpret_cast<const uint4*>(wst + c * 1024);
+          const uint4 hi = *reinterpret_cast<const uint4*>(wst + c * 1024 + 16);
 #pragma unroll
           for (int nt = 0; nt < NB; ++nt) {
-            mma_bf16(acc[mt][nt], lo.x, hi.x, lo.y, hi.y, bx[nt].x, bx[nt].y);
-            mma_bf16(acc[mt][nt], lo.z, hi.z, lo.w, hi.w, bx[nt].z, bx[nt].w);
+            const uint4 bx = *reinterpret_cast<const uint4*>(xst + c * (Bp * 64) + nt * 512);
+            mma_bf16(acc[nt], lo.x, hi.x, lo.y, hi.y, bx.x, bx.y);
+            mma_bf16(acc[nt], lo.z, hi.z, lo.w, hi.w, bx.z, bx.w);
           }
         }
       }
@@ -544,7 +604,7 @@ int32_t launch_ring(Ctx* ctx, const GemvParams& p, cudaStream_t stream) {
 
 template <int NB>
 constexpr size_t stream_smem() {
-  return (size_t)kStages * (kWStage + kCH * 8 * NB * 64) + (size_t)kRPC * (8 * NB + 1) * sizeof(float);
+  return (size_t)kStages * (kWStage + kCH * 8 * NB * 64);
 }
 
 template <int NB>
@@ -576,8 +636,8 @@ GemvPlan gemv_plan(const Ctx* ctx, int dtype, int B, int RB, int KC) {
     const int64_t upc_min = U / G;                       // >= 1
     pl.ksplit = (int)ceil_div(KS, upc_min) + 1;          // contributors reserved per row group
     pl.kc_per_split = KC;
-    pl.partial_floats = (int64_t)nrbg * pl.ksplit * kRPC * Bp;
-    pl.n_counters = nrbg;
+    pl.partial_floats = (int64_t)nrbg * pl.ksplit * kRPC * Bp;    // [row block][contributor][16 x Bp fragment]
+    pl.n_counters = nrbg * 8;
     return pl;
   }
   const int MT = dtype == LMB200_BF16 ? kMtBf16 : kMtF32;
