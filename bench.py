@@ -163,6 +163,7 @@ def run_reference(args):
 
 
 def main():
+    global BATCH
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=256)
@@ -170,7 +171,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--layers", type=int, default=CFG["n_layers"], help="debug only: fewer layers (invalid as a result)")
+    ap.add_argument("--batch", type=int, default=BATCH, help="debug only: another batch size (invalid as a result)")
     args = ap.parse_args()
+    BATCH = args.batch
     if args.impl == "reference":
         run_reference(args)
         return

@@ -7,6 +7,7 @@
 
 #include "common.cuh"
 #include "gemv.cuh"
+#include "model.cuh"
 
 namespace lmb {
 
@@ -171,6 +172,8 @@ extern "C" int32_t lmb200_init(int32_t device, lmb200_ctx* out) {
   const char* sel = getenv("LMB200_GEMV_KERNEL");
   gemv_set_stream_kernel(!(sel && strcmp(sel, "ring") == 0));
   int32_t rc = gemv_configure();
+  if (rc == LMB200_OK) rc = attn_configure();
+  if (rc == LMB200_OK) rc = step_kernels_configure();
   if (rc != LMB200_OK) { cudaFreeHost(c->dev_err); cudaStreamDestroy(c->own_stream); delete c; return rc; }
   *out = reinterpret_cast<lmb200_ctx>(c);
   return LMB200_OK;

@@ -12,6 +12,7 @@
 //
 // float32 path (parity configs): same cache layout and the same scratch format, CUDA cores.
 #include <math_constants.h>
+#include <stdlib.h>
 
 #include "attention.cuh"
 
@@ -262,6 +263,18 @@ __global__ void attn_combine_kernel(const AttnParams p) {
 }
 
 }  // namespace
+
+// The decode-attention kernels keep their operands in flight through L1 (streaming loads), so
+// they want the largest L1 split; the tiny combine kernel follows the GEMV's split instead.
+int32_t attn_configure() {
+  const char* e = getenv("LMB200_CARVEOUT");
+  if (e && atoi(e) == 0) return LMB200_OK;
+  LMB_CUDA(cudaFuncSetAttribute(attn_combine_kernel<float>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                cudaSharedmemCarveoutMaxShared));
+  LMB_CUDA(cudaFuncSetAttribute(attn_combine_kernel<__nv_bfloat16>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                cudaSharedmemCarveoutMaxShared));
+  return LMB200_OK;
+}
 
 void attn_plan(const Ctx* ctx, int B, int KVl, int G, int D, int ctx_capacity, int* keys_per_cta,
                int* nsplit, int64_t* part_o_floats, int64_t* part_ml_floats) {

@@ -26,6 +26,7 @@ struct AttnParams {
   int out_tiled_bp = 0;           // ... or, when > 0, a tiled activation buffer (xtile_offset) of that padding
 };
 
+int32_t attn_configure();
 // scratch floats needed: part_o, part_ml
 void attn_plan(const Ctx* ctx, int B, int KVl, int G, int D, int ctx_capacity, int* keys_per_cta,
                int* nsplit, int64_t* part_o_floats, int64_t* part_ml_floats);

@@ -671,8 +671,9 @@ GemvPlan gemv_plan(const Ctx* ctx, int dtype, int B, int RB, int KC) {
 // Raise the dynamic shared-memory limit of every instantiation once per device, outside any
 // stream capture.
 int32_t gemv_configure() {
-#define LMB_CFG(KERN, BYTES) \
-  LMB_CUDA(cudaFuncSetAttribute(KERN, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(BYTES)))
+#define LMB_CFG(KERN, BYTES)                                                                           \
+  LMB_CUDA(cudaFuncSetAttribute(KERN, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(BYTES)));     \
+  LMB_CUDA(cudaFuncSetAttribute(KERN, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared))
   LMB_CFG((gemv_ring_kernel<__nv_bfloat16, 1, kMtBf16, 4>), kMaxSmem);
   LMB_CFG((gemv_ring_kernel<__nv_bfloat16, 2, kMtBf16, 4>), kMaxSmem);
   LMB_CFG((gemv_ring_kernel<__nv_bfloat16, 4, kMtBf16, 3>), kMaxSmem);

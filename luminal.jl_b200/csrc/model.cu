@@ -1,5 +1,6 @@
 // Model weights (tiled, sharded), the decode session and its CUDA graph.
 #include <math.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <type_traits>
@@ -242,6 +243,23 @@ __global__ void __launch_bounds__(256) argmax_step_kernel(const float* logits, i
 __global__ void advance_kernel(int* pos, int* step_ctr) {
   *pos += 1;
   *step_ctr += 1;
+}
+
+static int g_debug_skip = 0;   // LMB200_DEBUG_SKIP bit mask (timing experiments only): 1 attention, 2 gemv, 4 norm
+
+int32_t step_kernels_configure() {
+  const char* sk = getenv("LMB200_DEBUG_SKIP");
+  g_debug_skip = sk ? atoi(sk) : 0;
+  const char* e = getenv("LMB200_CARVEOUT");
+  if (e && atoi(e) == 0) return LMB200_OK;
+#define LMB_CARVE(KERN) \
+  LMB_CUDA(cudaFuncSetAttribute(KERN, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared))
+  LMB_CARVE(add_rmsnorm_kernel<float>);
+  LMB_CARVE(add_rmsnorm_kernel<__nv_bfloat16>);
+  LMB_CARVE(argmax_step_kernel);
+  LMB_CARVE(advance_kernel);
+#undef LMB_CARVE
+  return LMB200_OK;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -570,7 +588,7 @@ int32_t enqueue_step_t(Session* S, cudaStream_t st, bool with_head) {
   for (int l = 0; l < L; ++l) {
     LayerWeights& W = M->layers[l];
     // residual add of the previous MLP (or the embedding gather) + attention RMSNorm
-    add_rmsnorm_kernel<WT><<<B, kNormThreads, norm_smem, st>>>(
+    if (!(g_debug_skip & 4) || l == 0) add_rmsnorm_kernel<WT><<<B, kNormThreads, norm_smem, st>>>(
         S->x, l == 0 ? nullptr : S->delta, l == 0 ? S->tokens : nullptr, reinterpret_cast<const WT*>(M->embed),
         c.vocab, W.attn_norm, reinterpret_cast<WT*>(S->xn), S->Bp, hid, c.rms_eps,
         (S->capture_on && l > 0) ? S->capture + (int64_t)(l - 1) * B * hid : nullptr);
@@ -583,7 +601,7 @@ int32_t enqueue_step_t(Session* S, cudaStream_t st, bool with_head) {
       p.q_out = S->qbuf; p.q_pitch = S->q_pitch;
       p.kv_layer = kv_layer; p.kv_batch_stride = S->kv_batch_stride; p.kv_head_stride = S->kv_head_stride;
       p.inv_freq = M->inv_freq; p.pos = S->pos; p.Hl = M->Hl; p.KVl = M->KVl; p.D = M->D;
-      LMB_TRY(gemv_launch(ctx, dt, p, st));
+      if (!(g_debug_skip & 2)) LMB_TRY(gemv_launch(ctx, dt, p, st));
     }
     {  // attention over the cache; the result is the tiled input of o_proj
       AttnParams a;
@@ -593,15 +611,15 @@ int32_t enqueue_step_t(Session* S, cudaStream_t st, bool with_head) {
       a.keys_per_cta = S->keys_per_cta; a.nsplit = S->nsplit;
       a.scale = 1.0f / sqrtf((float)M->D);
       a.part_o = S->part_o; a.part_ml = S->part_ml; a.out = S->attn_out; a.out_tiled_bp = S->Bp;
-      LMB_TRY(attn_decode_launch(ctx, dt, a, st));
+      if (!(g_debug_skip & 1)) LMB_TRY(attn_decode_launch(ctx, dt, a, st));
     }
     {  // o_proj (row-parallel under TP)
       GemvParams p = gemv_params(S, W.wo, M->m_o, S->p_o, S->attn_out);
       p.epi = EPI_STORE_F32; p.out = S->delta; p.out_pitch = hid;
-      LMB_TRY(gemv_launch(ctx, dt, p, st));
+      if (!(g_debug_skip & 2)) LMB_TRY(gemv_launch(ctx, dt, p, st));
       if (c.tp_size > 1) LMB_TRY(nccl_allreduce_f32(ctx, S->delta, (int64_t)B * hid, st));
     }
-    add_rmsnorm_kernel<WT><<<B, kNormThreads, norm_smem, st>>>(S->x, S->delta, nullptr, nullptr, 0, W.ffn_norm,
+    if (!(g_debug_skip & 4)) add_rmsnorm_kernel<WT><<<B, kNormThreads, norm_smem, st>>>(S->x, S->delta, nullptr, nullptr, 0, W.ffn_norm,
                                                                reinterpret_cast<WT*>(S->xn), S->Bp, hid, c.rms_eps,
                                                                nullptr);
     ctx->launches++;
@@ -609,12 +627,12 @@ int32_t enqueue_step_t(Session* S, cudaStream_t st, bool with_head) {
     {  // gate/up + SiLU gate
       GemvParams p = gemv_params(S, W.wgu, M->m_gu, S->p_gu, S->xn);
       p.epi = EPI_SILU_GATE; p.act = S->act; p.n_act = M->inter_l;
-      LMB_TRY(gemv_launch(ctx, dt, p, st));
+      if (!(g_debug_skip & 2)) LMB_TRY(gemv_launch(ctx, dt, p, st));
     }
     {  // down_proj (row-parallel under TP)
       GemvParams p = gemv_params(S, W.wdown, M->m_down, S->p_down, S->act);
       p.epi = EPI_STORE_F32; p.out = S->delta; p.out_pitch = hid;
-      LMB_TRY(gemv_launch(ctx, dt, p, st));
+      if (!(g_debug_skip & 2)) LMB_TRY(gemv_launch(ctx, dt, p, st));
       if (c.tp_size > 1) LMB_TRY(nccl_allreduce_f32(ctx, S->delta, (int64_t)B * hid, st));
     }
   }
@@ -627,7 +645,7 @@ int32_t enqueue_step_t(Session* S, cudaStream_t st, bool with_head) {
   if (with_head) {
     GemvParams p = gemv_params(S, M->lm_head, M->m_head, S->p_head, S->xn);
     p.epi = EPI_STORE_F32; p.out = S->logits; p.out_pitch = S->logits_pitch;
-    LMB_TRY(gemv_launch(ctx, dt, p, st));
+    if (!(g_debug_skip & 2)) LMB_TRY(gemv_launch(ctx, dt, p, st));
     argmax_step_kernel<<<B, 256, 0, st>>>(S->logits, S->logits_pitch, c.vocab, S->tokens, S->tok_hist, S->step_ctr, B);
     ctx->launches++;
     LMB_CUDA(cudaGetLastError());

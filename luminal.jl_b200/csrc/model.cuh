@@ -90,6 +90,7 @@ struct Session {
   int graph_nodes_full = 0, graph_nodes_body = 0;
 };
 
+int32_t step_kernels_configure();
 Model* model_from(lmb200_model h);
 Session* session_from(lmb200_session h);
 
