@@ -238,6 +238,30 @@ int32_t lmb200_session_step_bytes(lmb200_session session, int32_t T, int64_t* by
 int32_t lmb200_decode_attention_splitkv(lmb200_session session, int32_t layer, const void* q_dptr,
                                         void* out_dptr, int32_t T);
 
+/* Address and strides (in elements) of one layer of the session's tiled KV cache, for callers that
+ * run the attention kernels on it themselves.  The cache belongs to the session. */
+int32_t lmb200_session_kv_layer(lmb200_session session, int32_t layer, void** kv_dptr,
+                                int64_t* batch_stride, int64_t* head_stride);
+
+/* Split-KV decode attention that allocates nothing.  It has no counterpart in the reference.
+ * Some callers cannot call cudaMalloc: a host runtime that already owns all device memory in a
+ * pool of its own (CUDA.jl, a serving arena), or a loop that cannot take the synchronisation an
+ * allocation may cause.  The kernel's per-split partial results therefore go to an 8 MiB array
+ * built into the library (one per GPU that loads it, kept until exit) instead of session scratch.
+ *  - q, out: [batch, n_kv_heads*group, head_dim] device tensors of `dtype`, heads ordered
+ *    (kv head, group member); kv_layer: a tiled cache layer as lmb200_session_kv_layer returns.
+ *  - Shapes whose partial results exceed the array (more than 2 Mi floats: roughly
+ *    batch * n_kv_heads * group * splits * (head_dim + 2)) are rejected with LMB200_EINVAL.
+ *  - The first call on a device looks up the array's device address; make that call outside any
+ *    stream capture.  Asynchronous on the context's stream like lmb200_decode_attention_splitkv.
+ *  - All calls share the array: calls whose kernels overlap on the GPU race.  Nothing in it
+ *    needs clearing between calls. */
+int32_t lmb200_decode_attention_noalloc(lmb200_ctx ctx, int32_t dtype, const void* q_dptr,
+                                        void* out_dptr, const void* kv_layer_dptr,
+                                        int64_t kv_batch_stride, int64_t kv_head_stride,
+                                        int32_t batch, int32_t n_kv_heads, int32_t group,
+                                        int32_t head_dim, int32_t T);
+
 #ifdef __cplusplus
 }
 #endif

@@ -88,6 +88,8 @@ SIGNATURES = {
     "lmb200_decode_n_device": [_u64, _vp, _i32, _vp],
     "lmb200_session_step_bytes": [_u64, _i32, _pi64],
     "lmb200_decode_attention_splitkv": [_u64, _i32, _vp, _vp, _i32],
+    "lmb200_session_kv_layer": [_u64, _i32, C.POINTER(_vp), _pi64, _pi64],
+    "lmb200_decode_attention_noalloc": [_u64, _i32, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _i32, _i32, _i32],
 }
 
 _lib = None

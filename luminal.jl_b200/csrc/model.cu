@@ -978,6 +978,18 @@ extern "C" int32_t lmb200_session_step_bytes(lmb200_session h, int32_t T, int64_
   return LMB200_OK;
 }
 
+extern "C" int32_t lmb200_session_kv_layer(lmb200_session h, int32_t layer, void** kv_dptr, int64_t* batch_stride,
+                                           int64_t* head_stride) {
+  Session* S = session_from(h);
+  if (!S) return LMB200_EINVAL;
+  LMB_REQUIRE(kv_dptr && batch_stride && head_stride, "session_kv_layer: null argument");
+  LMB_REQUIRE(layer >= 0 && layer < S->m->cfg.n_layers, "session_kv_layer: layer %d", layer);
+  *kv_dptr = reinterpret_cast<char*>(S->kv) + (int64_t)layer * S->kv_layer_stride * S->m->esz;
+  *batch_stride = S->kv_batch_stride;
+  *head_stride = S->kv_head_stride;
+  return LMB200_OK;
+}
+
 extern "C" int32_t lmb200_decode_attention_splitkv(lmb200_session h, int32_t layer, const void* q_dptr,
                                                    void* out_dptr, int32_t T) {
   Session* S = session_from(h);

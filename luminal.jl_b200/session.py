@@ -130,6 +130,12 @@ class Session:
         _lib.call("lmb200_decode_attention_splitkv", self.handle, int(layer), C.c_void_p(q_dptr),
                   C.c_void_p(out_dptr), int(T))
 
+    def kv_layer(self, layer):
+        """(device address, batch stride, head stride) of one layer of the tiled KV cache."""
+        p, bs, hs = C.c_void_p(0), C.c_int64(0), C.c_int64(0)
+        _lib.call("lmb200_session_kv_layer", self.handle, int(layer), C.byref(p), C.byref(bs), C.byref(hs))
+        return p.value, bs.value, hs.value
+
     def close(self):
         if self.handle:
             _lib.call("lmb200_session_destroy", self.handle)
@@ -152,10 +158,19 @@ def greedy_generate(session, prompt, n_steps, want_logits=False):
     return (t, np.stack(lgs, axis=1)) if want_logits else t
 
 
+def decode_attention_noalloc(device, dtype, q_dptr, out_dptr, kv_layer_dptr, kv_batch_stride, kv_head_stride,
+                             batch, n_kv_heads, group, head_dim, T):
+    """Split-KV decode attention whose scratch is an array inside the library: for callers that
+    cannot let the library allocate device memory.  Asynchronous; see include/luminal_b200.h."""
+    _lib.call("lmb200_decode_attention_noalloc", device.handle, _dtype_code(dtype), C.c_void_p(q_dptr),
+              C.c_void_p(out_dptr), C.c_void_p(kv_layer_dptr), int(kv_batch_stride), int(kv_head_stride),
+              int(batch), int(n_kv_heads), int(group), int(head_dim), int(T))
+
+
 def _step_logits(session, tokens):
     # the logits of the step that consumed `tokens`
     nxt, logits = session.decode_step(tokens, want_logits=True)
     return nxt, logits
 
 
-__all__ = ["Model", "Session", "greedy_generate"]
+__all__ = ["Model", "Session", "greedy_generate", "decode_attention_noalloc"]
