@@ -1,0 +1,159 @@
+"""execute() and compile() on the B200 device: the Python stand-in for the interpreter of
+src/Execution.jl:620-665 and for src/Compiler.jl:75-100, 181-364, dispatching every node to one
+C entry point of libluminal_b200.so (what `execute_op!` methods on a B200 array type do through
+ccall).  No node is computed on the host."""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+from . import graph as G
+from .device import DeviceArray, get_device
+
+_EW = {G.Add: "add", G.Mul: "mul", G.Mod: "mod", G.LessThan: "less_than", G.Max: "max", G.Log2: "log2",
+       G.Exp2: "exp2", G.Sin: "sin", G.Cos: "cos", G.Sqrt: "sqrt", G.Recip: "recip", G.ReLU: "relu",
+       G.Contiguous: "copy", G.FusedMulAdd: "fused_mul_add", G.FusedAddReLU: "fused_add_relu"}
+
+
+def _p(a):
+    return C.c_void_p(a.ptr)
+
+
+def _ew(dev, name, out, ins):
+    args = []
+    for k in range(3):
+        if k < len(ins):
+            args += [_p(ins[k]), len(ins[k].shape), _lib.dims(ins[k].shape)]
+        else:
+            args += [None, 0, _lib.dims(())]
+    _lib.call("lmb200_ew", dev.handle, _lib.OP[name], _p(out), len(out.shape), _lib.dims(out.shape), *args)
+
+
+def execute_op(dev, op, out_shape, ins):
+    """One node on the device; returns a new DeviceArray (the functional execute_op of
+    src/Execution.jl:216-270)."""
+    out = dev.empty(out_shape)
+    run_op(dev, op, out, ins)
+    return out
+
+
+def run_op(dev, op, out, ins):
+    """In-place form (execute_op!, src/Execution.jl:274-371, 565-618)."""
+    t = type(op)
+    h = dev.handle
+    if t in _EW:
+        _ew(dev, _EW[t], out, ins)
+    elif t in (G.SumReduce, G.MaxReduce):
+        a = ins[0]
+        _lib.call("lmb200_reduce", h, _lib.REDUCE_SUM if t is G.SumReduce else _lib.REDUCE_MAX, _p(out), _p(a),
+                  len(a.shape), _lib.dims(a.shape), op.dim - 1)
+    elif t is G.MatMul:
+        a, b = ins
+        _lib.call("lmb200_matmul", h, _p(out), _p(a), len(a.shape), _lib.dims(a.shape), _p(b), len(b.shape),
+                  _lib.dims(b.shape))
+    elif t is G.Permute:
+        a = ins[0]
+        perm = (C.c_int32 * len(op.dims))(*[d - 1 for d in op.dims])
+        _lib.call("lmb200_permute", h, _p(out), _p(a), len(a.shape), _lib.dims(a.shape), perm)
+    elif t is G.Reshape:
+        a = ins[0]
+        _lib.call("lmb200_reshape_colmajor", h, _p(out), _p(a), len(a.shape), _lib.dims(a.shape), len(op.shape),
+                  _lib.dims(op.shape))
+    elif t is G.Expand:
+        a = ins[0]
+        _lib.call("lmb200_expand", h, _p(out), _p(a), len(a.shape), _lib.dims(a.shape), op.dim - 1, op.size)
+    elif t is G.Slice:
+        a = ins[0]
+        starts = _lib.dims([s for s, _ in op.ranges])
+        stops = _lib.dims([min(e, d) for (_, e), d in zip(op.ranges, a.shape)])
+        _lib.call("lmb200_slice", h, _p(out), _p(a), len(a.shape), _lib.dims(a.shape), starts, stops)
+    elif t is G.Pad:
+        a = ins[0]
+        _lib.call("lmb200_pad", h, _p(out), _p(a), len(a.shape), _lib.dims(a.shape),
+                  _lib.dims([l for l, _ in op.padding]), _lib.dims([r for _, r in op.padding]))
+    elif t is G.FlashAttentionOp:
+        q, k, v = ins
+        B, H, S, D = q.shape
+        _lib.call("lmb200_flash_attention", h, _p(out), _p(q), _p(k), _p(v), _lib.F32, B, H, S, D, op.scale,
+                  int(op.causal))
+    elif t is G.Function and op.name == "Gather":
+        table, ids = ins
+        _lib.call("lmb200_gather", h, _p(out), _p(table), table.shape[0], table.shape[1], _p(ids),
+                  int(np.prod(ids.shape)))
+    elif t is G.Function and op.name == "CumSum":
+        a = ins[0]
+        n = a.shape[-1]
+        _lib.call("lmb200_cumsum_last", h, _p(out), _p(a), int(np.prod(a.shape)) // n, n)
+    else:
+        raise NotImplementedError(f"Function op with name {getattr(op, 'name', t.__name__)} not implemented.")
+
+
+def execute(graph, output_ids, initial_inputs, device=None):
+    """execute(graph, ids, inputs, device) of src/Execution.jl:620-670: inputs are host arrays keyed
+    by node id, results come back as host arrays keyed by node id."""
+    dev = device or get_device()
+    single = isinstance(output_ids, int)
+    ids = [output_ids] if single else list(output_ids)
+    results = {k: (v if isinstance(v, DeviceArray) else dev.upload(np.asarray(v, dtype=np.float32)))
+               for k, v in initial_inputs.items()}
+    for (node_id, out_idx), data in graph.tensors.items():       # pre-loaded weights
+        if node_id not in results and out_idx == 1:
+            results[node_id] = data if isinstance(data, DeviceArray) else dev.upload(np.asarray(data, np.float32))
+    for node_id, node in enumerate(graph.nodes, start=1):
+        if node_id in results:
+            continue
+        op = node.op
+        if isinstance(op, G.Constant):
+            results[node_id] = dev.upload(np.asarray(op.value, dtype=np.float32))
+        elif isinstance(op, G.Function) and op.name == "InputTensor":
+            raise KeyError(f"input tensor node {node_id} has no data")
+        else:
+            ins = [results[i] for i, _, _ in node.inputs]
+            results[node_id] = execute_op(dev, op, graph.shapes[node_id - 1], ins)
+    out = {i: results[i].numpy() for i in ids}
+    return out[output_ids] if single else out
+
+
+class CompiledGraph:
+    """compile(graph): one preallocated device buffer per node and a list of steps
+    (src/Compiler.jl:75-100, 217-361).  Calling it copies the inputs in and runs the steps;
+    it returns the per-node device buffers (index by node id, as the reference does)."""
+
+    def __init__(self, graph, device=None):
+        self.graph, self.dev = graph, device or get_device()
+        self.results = {}
+        self.steps = []
+        for node_id, node in enumerate(graph.nodes, start=1):
+            shape = graph.shapes[node_id - 1]
+            buf = self.dev.empty(shape)
+            self.results[node_id] = buf
+            op = node.op
+            if isinstance(op, G.Constant):
+                _lib.call("lmb200_upload", self.dev.handle, C.c_void_p(buf.ptr), _lib.F32,
+                          np.asarray([op.value], np.float32).ctypes.data_as(C.c_void_p), 0, _lib.dims(()), 0)
+            elif isinstance(op, G.Function) and op.name == "InputTensor":
+                pass
+            else:
+                ins = [self.results[i] for i, _, _ in node.inputs]
+                self.steps.append((op, buf, ins))
+
+    def __call__(self, inputs, device=None):
+        for node_id, data in inputs.items():
+            buf = self.results[node_id]
+            a = np.ascontiguousarray(np.asarray(data, dtype=np.float32))
+            if a.size != buf.size:
+                raise ValueError(f"Input size mismatch for node {node_id}: expected {buf.size}, got {a.size}")
+            _lib.call("lmb200_upload", self.dev.handle, C.c_void_p(buf.ptr), _lib.F32, a.ctypes.data_as(C.c_void_p),
+                      len(buf.shape), _lib.dims(buf.shape), 0)
+        for op, out, ins in self.steps:
+            run_op(self.dev, op, out, ins)
+        return self.results
+
+
+def compile(graph, device=None):     # noqa: A001  (the reference's name)
+    return CompiledGraph(graph, device)
+
+
+__all__ = ["execute", "execute_op", "run_op", "compile", "CompiledGraph"]

@@ -42,6 +42,13 @@ def test_small_llama_fp32_greedy_matches_oracle(lib_built, device):
     tok, log = L.greedy_generate(sess, prompt, 64, want_logits=True)
     assert np.array_equal(tok, ref_tok)
     assert np.abs(log - ref_log).max() <= LOGIT_TOL
+    # ... and against the committed fixture of the same run (tests/golden/make_golden.py)
+    import os
+    gold = np.load(os.path.join(os.path.dirname(__file__), "golden", "small_llama_golden.npz"))
+    assert np.array_equal(prompt, gold["prompt"])
+    assert np.array_equal(tok, gold["tokens"])
+    assert np.abs(log[:, 0] - gold["logits_first"]).max() <= LOGIT_TOL
+    assert np.abs(log[:, -1] - gold["logits_last"]).max() <= LOGIT_TOL
 
     # the same weights pushed through set_weight (row-major and Julia column-major images)
     for layout in (L.ROWMAJOR, L.COLMAJOR):
