@@ -182,6 +182,14 @@ typedef struct {
 } lmb200_model_config;
 
 int32_t lmb200_model_create(lmb200_ctx ctx, const lmb200_model_config* cfg, lmb200_model* model);
+/* Host-only view of the weight re-layout and tensor-parallel sharding (no GPU needed): the extent
+ * of this rank's fused matrix `matrix` (0 qkv, 1 o_proj, 2 gate/up, 3 down_proj, 4 lm_head) and, for
+ * one of its elements, which logical tensor (slot: q/k/v = 0/1/2, gate/up = 0/1, else 0) and which
+ * [out, in] element of it sits there (-1 for padding).  Encodes src/NN.jl:305-317, 347-354
+ * (q = kv + KV*g, feature f = h + H*d) and the RoPE pairing of src/NN.jl:274-276. */
+int32_t lmb200_shard_extent(const lmb200_model_config* cfg, int32_t matrix, int32_t* rows, int32_t* cols);
+int32_t lmb200_shard_map(const lmb200_model_config* cfg, int32_t matrix, int32_t row, int32_t col,
+                         int32_t* slot, int32_t* logical_row, int32_t* logical_col);
 int32_t lmb200_model_destroy(lmb200_model model);
 /* Set one weight from the FULL logical float32 tensor under its registry name
  * ("model.layers.3.self_attn.q_proj.weight", "model.embed_tokens.weight", "model.norm.weight",

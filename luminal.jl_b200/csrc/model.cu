@@ -338,11 +338,9 @@ using namespace lmb;
 // =============================================================================================
 // model
 // =============================================================================================
-extern "C" int32_t lmb200_model_create(lmb200_ctx hctx, const lmb200_model_config* cfg, lmb200_model* out) {
-  Ctx* ctx = ctx_from(hctx);
-  if (!ctx) return LMB200_EINVAL;
-  LMB_REQUIRE(cfg && out, "model_create: null argument");
-  const lmb200_model_config& c = *cfg;
+// Validates a configuration and derives this rank's shard extents and index maps.  Host
+// arithmetic only (no CUDA call), so the sharding can be checked without a GPU.
+static int32_t derive_model(const lmb200_model_config& c, Model* M) {
   LMB_REQUIRE(c.n_layers >= 1 && c.hidden >= 16 && c.n_heads >= 1 && c.n_kv_heads >= 1 && c.vocab >= 1 &&
                   c.intermediate >= 8, "model_create: non-positive dimension");
   LMB_REQUIRE(c.head_dim * c.n_heads == c.hidden, "model_create: head_dim %d * n_heads %d != hidden %d",
@@ -358,13 +356,6 @@ extern "C" int32_t lmb200_model_create(lmb200_ctx hctx, const lmb200_model_confi
   LMB_REQUIRE(c.intermediate % c.tp_size == 0 && (c.intermediate / c.tp_size) % 8 == 0,
               "model_create: intermediate %d / tp %d must be a multiple of 8", c.intermediate, c.tp_size);
   LMB_REQUIRE(c.hidden % 4 == 0, "model_create: hidden %d must be a multiple of 4", c.hidden);
-  if (c.tp_size > 1)
-    LMB_REQUIRE(ctx->nccl_comm && ctx->tp_size == c.tp_size && ctx->tp_rank == c.tp_rank,
-                "model_create: tp_size %d needs lmb200_comm_init with the same ranks first", c.tp_size);
-  LMB_CUDA(cudaSetDevice(ctx->device));
-
-  Model* M = new Model();
-  M->ctx = ctx;
   M->cfg = c;
   M->esz = c.dtype == LMB200_BF16 ? 2 : 4;
   M->D = c.head_dim;
@@ -402,6 +393,49 @@ extern "C" int32_t lmb200_model_create(lmb200_ctx hctx, const lmb200_model_confi
   M->m_head.rows = c.vocab; M->m_head.K = c.hidden;
   M->m_head.src_rows[0] = c.vocab; M->m_head.src_cols[0] = c.hidden;
   finish_map(M->m_head);
+  return LMB200_OK;
+}
+
+extern "C" int32_t lmb200_shard_extent(const lmb200_model_config* cfg, int32_t matrix, int32_t* rows, int32_t* cols) {
+  LMB_REQUIRE(cfg && rows && cols, "shard_extent: null argument");
+  Model M;
+  LMB_TRY(derive_model(*cfg, &M));
+  const WMap* maps[5] = {&M.m_qkv, &M.m_o, &M.m_gu, &M.m_down, &M.m_head};
+  LMB_REQUIRE(matrix >= 0 && matrix < 5, "shard_extent: matrix %d", matrix);
+  *rows = maps[matrix]->rows;
+  *cols = maps[matrix]->K;
+  return LMB200_OK;
+}
+
+extern "C" int32_t lmb200_shard_map(const lmb200_model_config* cfg, int32_t matrix, int32_t row, int32_t col,
+                                    int32_t* slot, int32_t* logical_row, int32_t* logical_col) {
+  LMB_REQUIRE(cfg && slot && logical_row && logical_col, "shard_map: null argument");
+  Model M;
+  LMB_TRY(derive_model(*cfg, &M));
+  const WMap* maps[5] = {&M.m_qkv, &M.m_o, &M.m_gu, &M.m_down, &M.m_head};
+  LMB_REQUIRE(matrix >= 0 && matrix < 5, "shard_map: matrix %d", matrix);
+  int s = -1, r = -1, c = -1;
+  if (!wmap_resolve(*maps[matrix], row, col, &s, &r, &c)) { s = -1; r = -1; c = -1; }   // padding
+  *slot = s; *logical_row = r; *logical_col = c;
+  return LMB200_OK;
+}
+
+extern "C" int32_t lmb200_model_create(lmb200_ctx hctx, const lmb200_model_config* cfg, lmb200_model* out) {
+  Ctx* ctx = ctx_from(hctx);
+  if (!ctx) return LMB200_EINVAL;
+  LMB_REQUIRE(cfg && out, "model_create: null argument");
+  const lmb200_model_config& c = *cfg;
+  Model* M = new Model();
+  M->ctx = ctx;
+  {
+    const int32_t rc0 = derive_model(c, M);
+    if (rc0 != LMB200_OK) { delete M; return rc0; }
+  }
+  if (c.tp_size > 1 && !(ctx->nccl_comm && ctx->tp_size == c.tp_size && ctx->tp_rank == c.tp_rank)) {
+    delete M;
+    return fail(LMB200_EINVAL, "model_create: tp_size %d needs lmb200_comm_init with the same ranks first", c.tp_size);
+  }
+  if (cudaSetDevice(ctx->device) != cudaSuccess) { delete M; return fail(LMB200_ECUDA, "model_create: cudaSetDevice failed"); }
 
   int32_t rc = LMB200_OK;
   auto alloc = [&](void** p, int64_t bytes) {

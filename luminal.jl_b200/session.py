@@ -173,4 +173,26 @@ def _step_logits(session, tokens):
     return nxt, logits
 
 
-__all__ = ["Model", "Session", "greedy_generate", "decode_attention_noalloc"]
+__all__ = ["Model", "Session", "greedy_generate", "decode_attention_noalloc", "shard_layout"]
+
+
+def shard_layout(cfg_kwargs, matrix, tp_size=1, tp_rank=0):
+    """Host-only: (rows, cols, row_map, col_map) of this rank's fused matrix `matrix`
+    ('qkv', 'o', 'gate_up', 'down', 'head').  row_map[i] = (slot, logical row), col_map[k] =
+    logical column; -1 marks padding.  Needs no GPU."""
+    idx = {"qkv": 0, "o": 1, "gate_up": 2, "down": 3, "head": 4}[matrix]
+    cfg = ModelConfig(n_layers=cfg_kwargs["n_layers"], hidden=cfg_kwargs["hidden"], n_heads=cfg_kwargs["n_heads"],
+                      n_kv_heads=cfg_kwargs["n_kv_heads"], head_dim=cfg_kwargs["hidden"] // cfg_kwargs["n_heads"],
+                      intermediate=cfg_kwargs["intermediate"], vocab=cfg_kwargs["vocab"], rms_eps=1e-5,
+                      rope_base=10000.0, dtype=F32, tp_size=tp_size, tp_rank=tp_rank)
+    rows, cols = C.c_int32(0), C.c_int32(0)
+    _lib.call("lmb200_shard_extent", C.byref(cfg), idx, C.byref(rows), C.byref(cols))
+    s, r, c = C.c_int32(0), C.c_int32(0), C.c_int32(0)
+    row_map, col_map = [], []
+    for i in range(rows.value):
+        _lib.call("lmb200_shard_map", C.byref(cfg), idx, i, 0, C.byref(s), C.byref(r), C.byref(c))
+        row_map.append((s.value, r.value))
+    for k in range(cols.value):
+        _lib.call("lmb200_shard_map", C.byref(cfg), idx, 0, k, C.byref(s), C.byref(r), C.byref(c))
+        col_map.append(c.value)
+    return rows.value, cols.value, row_map, col_map
