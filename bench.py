@@ -304,7 +304,11 @@ def main():
             "clocks": clocks,
             "roofline": {"kernel": "attn_decode_bf16_kernel<128> + attn_combine_kernel (per layer)", "bound": "hbm",
                          "achieved": attn_gbs, "peak": peak, "unit": "GB/s", "frac": attn_gbs / peak,
-                         "peak_kind": peak_kind, "traffic": None, "bytes_per_launch": attn_bytes,
+                         "peak_kind": peak_kind,
+                         # dram__bytes_read + write of one launch from the ncu capture in
+                         # profiles/attn_decode_bf16_llama3_8b_b32_ctx8190.md, scaled by keys x local kv heads
+                         "traffic": int(1.0841e9 * (KVl * T_mid) / (8 * 8190.0)) if cfg["n_heads"] == 32 else None,
+                         "bytes_per_launch": attn_bytes,
                          "ms_per_launch": attn_ms},
             "step_hbm": {"bytes_per_step_per_gpu": step_bytes, "achieved": step_gbs, "peak": peak, "unit": "GB/s",
                          "frac": step_gbs / peak},
