@@ -155,6 +155,13 @@ int32_t lmb200_silu_gate(lmb200_ctx ctx, float* out, const float* gate, const fl
 /* Half-split RoPE on [B,H,S,D] float32 at positions prev_seq..prev_seq+S-1.  src/NN.jl:253-303 */
 int32_t lmb200_rope(lmb200_ctx ctx, float* out, const float* x, int64_t B, int64_t H, int64_t S,
                     int64_t D, int64_t prev_seq, float base);
+/* One Linear on host data: out[b, o] = sum_i x[b, i] * W[o, i]; W [rows, K], x [batch <= 32, K],
+ * out [batch, rows], all float32 row-major on the host.  dtype selects the float32 or the bf16
+ * (float32-accumulate) decode GEMV; variant (bf16 only) 0 = tcgen05 / TMEM, 1 = mma.sync.
+ * The decode session runs the same kernels on resident weights; this entry uploads, runs once and
+ * downloads (tests, comparisons).  Replaces NN.Linear for a single position, src/NN.jl:22-35. */
+int32_t lmb200_linear_gemv(lmb200_ctx ctx, int32_t dtype, int32_t variant, int32_t rows, int32_t K,
+                           int32_t batch, const float* w_host, const float* x_host, float* out_host);
 /* argmax over the last dim (first maximum), 0-based ids.  src/Decoding.jl:119-124 */
 int32_t lmb200_argmax(lmb200_ctx ctx, int32_t* out_ids_dptr, const float* x, int64_t rows, int64_t n);
 

@@ -168,9 +168,9 @@ extern "C" int32_t lmb200_init(int32_t device, lmb200_ctx* out) {
     return fail(LMB200_ECUDA, "init: pinned allocation failed");
   }
   *c->dev_err = 0;
-  // LMB200_GEMV_KERNEL=ring selects the register-ring bf16 GEMV (for A/B runs); default: stream
+  // LMB200_GEMV_KERNEL=mma selects the mma.sync bf16 GEMV (for A/B runs); default: tcgen05
   const char* sel = getenv("LMB200_GEMV_KERNEL");
-  gemv_set_stream_kernel(!(sel && strcmp(sel, "ring") == 0));
+  gemv_set_variant((sel && strcmp(sel, "mma") == 0) ? GEMV_MMA_SYNC : GEMV_TCGEN05);
   int32_t rc = gemv_configure();
   if (rc == LMB200_OK) rc = attn_configure();
   if (rc == LMB200_OK) rc = step_kernels_configure();

@@ -256,7 +256,7 @@ __global__ void attn_combine_kernel(const AttnParams p) {
       const float w = exp2f(p.part_ml[((slot0 + s) * p.G + h) * 2] - M);
       acc += w * p.part_o[((slot0 + s) * p.G + h) * p.D + d];
     }
-    const int64_t o = p.out_tiled_bp > 0 ? xtile_offset(b, hl * p.D + d, p.out_tiled_bp)
+    const int64_t o = p.out_tiled_bp > 0 ? Layout<T>::x_offset(b, hl * p.D + d, p.out_tiled_bp)
                                          : (int64_t)b * p.out_pitch + hl * p.D + d;
     out[o] = from_f32<T>(acc * inv);
   }

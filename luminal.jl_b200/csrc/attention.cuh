@@ -23,7 +23,7 @@ struct AttnParams {
   float* part_ml = nullptr;       // scratch [B*KVl, nsplit, G, 2]  (max, sum)
   void* out = nullptr;            // [B, out_pitch], same head-major order as q ...
   int out_pitch = 0;
-  int out_tiled_bp = 0;           // ... or, when > 0, a tiled activation buffer (xtile_offset) of that padding
+  int out_tiled_bp = 0;           // ... or, when > 0, a GEMV activation buffer (Layout<T>::x_offset) of that padding
 };
 
 int32_t attn_configure();

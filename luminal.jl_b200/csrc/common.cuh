@@ -152,6 +152,47 @@ __host__ __device__ inline int64_t xtile_offset(int b, int k, int Bp) {
 }
 static inline int batch_pad(int B) { return B <= 8 ? 8 : (B <= 16 ? 16 : 32); }
 
+// ---------------------------------------------------------------------------------------------
+// bf16 GEMV operands: the tensor-core ("UMMA") canonical K-major layout without swizzle, so that
+// one contiguous bulk copy lands a stage in shared memory exactly as tcgen05.mma reads it through
+// a shared-memory descriptor -- and as ldmatrix reads it for mma.sync.
+//   core matrix = 8 rows x 8 k (bf16) = 128 contiguous bytes, rows 16 bytes apart.
+//   weights: unit = 128 rows x 128 k = 32 KB at ((row/128)*KS + k/128) * 16384 elements, inside it
+//            [k8 = (k%128)/8][m8 = (row%128)/8][row%8][k%8]
+//            -> A descriptor: K-direction core-matrix stride (LBO) 2048 B, M-direction (SBO) 128 B.
+//   activations x[b, k], b < Bp (16 or 32), zero beyond the batch and beyond K:
+//            [k/8][b/8][b%8][k%8]  -> B descriptor: LBO = Bp*16 B, SBO = 128 B; the slice of one
+//            128-k stage is Bp*256 contiguous bytes.
+// K is padded to a multiple of 128 (KS stages), rows to a multiple of 128.
+// ---------------------------------------------------------------------------------------------
+__host__ __device__ inline int64_t wcanon_offset(int64_t row, int64_t k, int64_t KS) {
+  const int64_t r = row >> 7, ks = k >> 7;
+  const int m8 = (int)((row & 127) >> 3), rr = (int)(row & 7);
+  const int k8 = (int)((k & 127) >> 3), kk = (int)(k & 7);
+  return (r * KS + ks) * 16384 + k8 * 1024 + m8 * 64 + rr * 8 + kk;
+}
+__host__ __device__ inline int64_t xcanon_offset(int b, int k, int Bp) {
+  return (int64_t)(k >> 3) * (Bp * 8) + (b >> 3) * 64 + (b & 7) * 8 + (k & 7);
+}
+
+// Per-dtype operand layouts of the decode GEMV: float32 uses the lane-ordered tiles of the
+// register-ring kernel, bf16 the canonical tensor-core layout above.
+template <typename WT> struct Layout;
+template <> struct Layout<float> {
+  __host__ __device__ static int batch_pad(int B) { return B <= 8 ? 8 : (B <= 16 ? 16 : 32); }
+  __host__ __device__ static int64_t w_elems(int rows, int K) { return (int64_t)((rows + 15) / 16) * ((K + 31) / 32) * 512; }
+  __host__ __device__ static int64_t w_offset(int row, int k, int K) { return wtile_offset(row, k, (K + 31) / 32); }
+  __host__ __device__ static int64_t x_elems(int K, int Bp) { return (int64_t)((K + 31) / 32) * Bp * 32; }
+  __host__ __device__ static int64_t x_offset(int b, int k, int Bp) { return xtile_offset(b, k, Bp); }
+};
+template <> struct Layout<__nv_bfloat16> {
+  __host__ __device__ static int batch_pad(int B) { return B <= 16 ? 16 : 32; }
+  __host__ __device__ static int64_t w_elems(int rows, int K) { return (int64_t)((rows + 127) / 128) * ((K + 127) / 128) * 16384; }
+  __host__ __device__ static int64_t w_offset(int row, int k, int K) { return wcanon_offset(row, k, (K + 127) / 128); }
+  __host__ __device__ static int64_t x_elems(int K, int Bp) { return (int64_t)((K + 127) / 128) * 128 * Bp; }
+  __host__ __device__ static int64_t x_offset(int b, int k, int Bp) { return xcanon_offset(b, k, Bp); }
+};
+
 // element conversions
 __device__ inline float to_f32(float v) { return v; }
 __device__ inline float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }

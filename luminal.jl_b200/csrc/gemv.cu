@@ -1,20 +1,25 @@
 // Bandwidth-bound decode GEMV with fused epilogues (store / SiLU-gate / RoPE + KV append).
 //
-// bf16 "stream" kernel (default): stream-K over bulk-TMA.  The weight matrix is cut into units of
-// 128 rows x 128 k (32 KB, eight contiguous 4 KB runs of the tiled layout); the grid is one CTA
-// per SM and CTA c takes the contiguous unit range [c*U/G, (c+1)*U/G), so every SM streams the
-// same number of bytes in a single wave whatever the matrix shape.  A producer warp keeps a ring
-// of STAGES shared-memory stages full with cp.async.bulk copies (weights evict-first, plus the
-// matching slice of the tiled activations) signalled through mbarriers; 8 consumer warps read
-// their MMA operands from the stage with conflict-free 16-byte loads
-// and issue mma.sync m16n8k16; each consumer warp owns one 16-row block of the group, so nothing
-// is reduced across warps and the fused epilogue runs from the accumulator registers.  When a
-// CTA's range leaves a row group its warps fold their fragments: alone -> epilogue; shared ->
-// global scratch + a per-row-block counter, the last contributing warp sums the fragments in CTA
-// order (deterministic) and runs the epilogue.  No CTA-wide barrier after start-up.
+// bf16 kernels: stream-K over bulk-TMA.  Weights and activations sit in HBM in the tensor-core
+// canonical K-major layout (common.cuh), cut into units of 128 rows x 128 k = one contiguous
+// 32 KB block; the grid is one CTA per SM and CTA c takes the contiguous unit range
+// [c*U/G, (c+1)*U/G), so every SM streams the same number of bytes in a single wave whatever the
+// matrix shape.  A producer warp keeps a ring of 5 shared-memory stages full with cp.async.bulk
+// copies (one 32 KB copy of weights, evict-first, + the matching activation slice) signalled
+// through mbarriers.  Two consumers of the ring:
+//   tcgen05 (default): one thread issues tcgen05.mma (M = 128 rows, N = batch padding, K = 16)
+//     straight from the stage through shared-memory descriptors, accumulators double-buffered in
+//     TMEM; tcgen05.commit hands the stage back to the producer; four epilogue warps read the
+//     accumulators with tcgen05.ld (one row per thread) and run the fused epilogue while the next
+//     row group is already being multiplied.
+//   mma.sync: 8 consumer warps, one 16-row block each, operands via ldmatrix.  At batch 32 this
+//     path is limited by the legacy tensor pipe (one m16n8k16 per ~9 SM cycles, ~5.5 needed);
+//     kept selectable for comparison.
+// When a CTA's range leaves a row group its partial result is folded: alone -> epilogue; shared
+// -> global scratch + counter, the last contributor sums the parts in CTA order (deterministic).
 //
-// "ring" kernel: weights streamed by plain loads through a register ring; used for float32 (the
-// parity path, fp32 FMAs) and selectable for bf16 (A/B comparison).
+// float32 ("ring") kernel: weights streamed by plain loads through a register ring, fp32 FMAs --
+// the parity path.
 #include <type_traits>
 
 #include "gemv.cuh"
@@ -27,7 +32,7 @@ constexpr float kInvLn2 = 1.4426950408889634f;      // Float32(1/log(2)) as the 
 constexpr float kHalfPi = 1.5707963267948966f;
 constexpr size_t kMaxSmem = 224 * 1024;
 
-bool g_use_stream = true;
+int g_variant = GEMV_TCGEN05;
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                          uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -62,7 +67,7 @@ __device__ __forceinline__ void run_epilogue(const GemvParams& p, const float* t
         // silu(a) = a * (1 / (1 + exp2((a * -1) * (1/ln2))))     src/HighLevelOps.jl:153-160
         const float e = exp2f((a * -1.0f) * kInvLn2);
         const float sg = 1.0f / (1.0f + e);
-        act[xtile_offset(b, o, Bp)] = from_f32<WT>((a * sg) * u);
+        act[Layout<WT>::x_offset(b, o, Bp)] = from_f32<WT>((a * sg) * u);
       }
     }
   } else {  // EPI_QKV_ROPE
@@ -312,14 +317,10 @@ __global__ void __launch_bounds__(kRingThreads, 1) gemv_ring_kernel(const GemvPa
 }
 
 // =============================================================================================
-// stream kernel (bf16)
+// bf16 stream-K kernels
 // =============================================================================================
-constexpr int kConsumerWarps = 8;
-constexpr int kStreamThreads = (kConsumerWarps + 1) * 32;
-constexpr int kCH = 4;              // k-chunks per stage (one per k-warp)
-constexpr int kRPC = 128;           // rows per row group (8 row blocks)
 constexpr int kStages = 5;
-constexpr int kWStage = 8 * kCH * 1024;
+constexpr int kWStage = 32768;                   // 128 rows x 128 k, bf16
 constexpr long long kWaitLimit = 4000000000LL;   // clock cycles (~2 s) before a wait gives up
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -363,12 +364,73 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
       : "memory");
 }
 
+struct UnitRange {
+  int KS, nrbg, u0, u1;
+  long long U, G;
+};
+__device__ __forceinline__ UnitRange unit_range(const GemvParams& p) {
+  UnitRange ur;
+  ur.KS = (p.K + 127) >> 7;
+  ur.nrbg = (p.rows + 127) >> 7;
+  ur.U = (long long)ur.nrbg * ur.KS;
+  ur.G = gridDim.x;
+  ur.u0 = (int)((long long)blockIdx.x * ur.U / ur.G);
+  ur.u1 = (int)((long long)(blockIdx.x + 1) * ur.U / ur.G);
+  return ur;
+}
+// CTAs that share row group r: CTA of unit u is ceil((u+1)*G/U) - 1
+__device__ __forceinline__ void contributors(const UnitRange& ur, int r, int* c_first, int* n) {
+  const long long ua = (long long)r * ur.KS, ub = ua + ur.KS - 1;
+  *c_first = (int)(((ua + 1) * ur.G + ur.U - 1) / ur.U) - 1;
+  const int c_last = (int)(((ub + 1) * ur.G + ur.U - 1) / ur.U) - 1;
+  *n = c_last - *c_first + 1;
+}
+
+// producer loop shared by both kernels: one 32 KB weight copy + one activation copy per unit
+template <int Bp>
+__device__ __forceinline__ void produce(const GemvParams& p, const UnitRange& ur, unsigned char* smem,
+                                        uint64_t* full_bar, uint64_t* empty_bar, int lane, int* err) {
+  constexpr int kXStage = Bp * 256;
+  constexpr int kStage = kWStage + kXStage;
+  uint64_t pol_w, pol_x;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;\n" : "=l"(pol_w));
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;\n" : "=l"(pol_x));
+  const __nv_bfloat16* W = reinterpret_cast<const __nv_bfloat16*>(p.W);
+  const __nv_bfloat16* X = reinterpret_cast<const __nv_bfloat16*>(p.x);
+  bool dead = false;
+  int it = 0;
+  for (int u = ur.u0; u < ur.u1; ++u, ++it) {
+    const int s = it % kStages, k = it / kStages;
+    mbar_wait(&empty_bar[s], (k & 1) ^ 1, dead, err);
+    const int r = u / ur.KS, ks = u - r * ur.KS;
+    if (lane == 0) {
+      unsigned char* st = smem + s * kStage;
+      mbar_expect_tx(&full_bar[s], (uint32_t)kStage);
+      bulk_g2s(st, W + ((int64_t)r * ur.KS + ks) * 16384, (uint32_t)kWStage, &full_bar[s], pol_w);
+      bulk_g2s(st + kWStage, X + (int64_t)ks * (128 * Bp), (uint32_t)kXStage, &full_bar[s], pol_x);
+    }
+    __syncwarp();
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// mma.sync variant: 8 consumer warps, warp w owns row block 8r + w
+// ---------------------------------------------------------------------------------------------
+constexpr int kMmaThreads = 9 * 32;
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+
 // Epilogue of one 16-row block straight from the accumulator fragments of the warp that owns it:
 // lane (g,t) holds, per batch tile nt, rows g (c0,c1) and g+8 (c2,c3) at columns 8nt+2t, +1 --
 // and rows g / g+8 are exactly the pairs the fused epilogues combine.
 template <int NB>
 __device__ __forceinline__ void fragment_epilogue(const GemvParams& p, const float (&acc)[NB][4], int rb, int g, int t) {
   constexpr int Bp = 8 * NB;
+  typedef Layout<__nv_bfloat16> LY;
   if (p.epi == EPI_STORE_F32) {
     const int row = rb * 16 + g;
 #pragma unroll
@@ -396,7 +458,7 @@ __device__ __forceinline__ void fragment_epilogue(const GemvParams& p, const flo
             // silu(a) = a * (1 / (1 + exp2((a * -1) * (1/ln2))))     src/HighLevelOps.jl:153-160
             const float ex = exp2f((a * -1.0f) * kInvLn2);
             const float sg = 1.0f / (1.0f + ex);
-            act[xtile_offset(b, o, Bp)] = __float2bfloat16_rn((a * sg) * u);
+            act[LY::x_offset(b, o, Bp)] = __float2bfloat16_rn((a * sg) * u);
           }
         }
       }
@@ -447,77 +509,44 @@ __device__ __forceinline__ void fragment_epilogue(const GemvParams& p, const flo
 }
 
 template <int NB>
-__global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const GemvParams p, int* err) {
+__global__ void __launch_bounds__(kMmaThreads, 1) gemv_mma_kernel(const GemvParams p, int* err) {
   constexpr int Bp = 8 * NB;
-  constexpr int kXStage = kCH * Bp * 64;
-  constexpr int kStage = kWStage + kXStage;
-  extern __shared__ __align__(128) unsigned char smem[];
+  constexpr int kStage = kWStage + Bp * 256;
+  extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ __align__(8) uint64_t full_bar[kStages];
   __shared__ __align__(8) uint64_t empty_bar[kStages];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int KS = (p.KC + kCH - 1) / kCH;              // stage units per row group
-  const int nrbg = (p.RB + 7) / 8;
-  const long long U = (long long)nrbg * KS;
-  const long long G = gridDim.x;
-  const int u0 = (int)((long long)blockIdx.x * U / G);
-  const int u1 = (int)((long long)(blockIdx.x + 1) * U / G);
-
+  const UnitRange ur = unit_range(p);
   if (tid == 0) {
 #pragma unroll
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], kConsumerWarps);
+      mbar_init(&empty_bar[s], 8);
     }
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   __syncthreads();
 
-  bool dead = false;
-  if (warp == kConsumerWarps) {
-    // ---------------- producer ----------------
-    uint64_t pol_w, pol_x;
-    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;\n" : "=l"(pol_w));
-    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;\n" : "=l"(pol_x));
-    const __nv_bfloat16* W = reinterpret_cast<const __nv_bfloat16*>(p.W);
-    const __nv_bfloat16* X = reinterpret_cast<const __nv_bfloat16*>(p.x);
-    int it = 0;
-    for (int u = u0; u < u1; ++u, ++it) {
-      const int s = it % kStages, k = it / kStages;
-      mbar_wait(&empty_bar[s], (k & 1) ^ 1, dead, err);
-      const int r = u / KS, ks = u - r * KS;
-      const int chunk0 = ks * kCH;
-      const int nch = min(kCH, p.KC - chunk0);
-      const int nrb = min(8, p.RB - r * 8);
-      unsigned char* st = smem + s * kStage;
-      if (lane == 0) mbar_expect_tx(&full_bar[s], (uint32_t)(nrb * nch * 1024 + nch * Bp * 64));
-      __syncwarp();
-      if (lane < nrb)
-        bulk_g2s(st + lane * (kCH * 1024), W + ((int64_t)(r * 8 + lane) * p.KC + chunk0) * 512, (uint32_t)(nch * 1024),
-                 &full_bar[s], pol_w);
-      else if (lane == 8)
-        bulk_g2s(st + kWStage, X + (int64_t)chunk0 * (Bp * 32), (uint32_t)(nch * Bp * 64), &full_bar[s], pol_x);
-    }
+  if (warp == 8) {
+    produce<Bp>(p, ur, smem, full_bar, empty_bar, lane, err);
     return;
   }
 
-  // ---------------- consumers: warp w owns row block 8r + w of the current row group ----------------
   const int g = lane >> 2, t = lane & 3;
   float acc[NB][4];
   auto zero_acc = [&]() {
 #pragma unroll
     for (int j = 0; j < NB; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
   };
-  // Fold the accumulators of row group r, which this CTA's unit range has just left.  Everything
-  // is warp-local: alone -> epilogue; shared -> fragment to scratch, per-row-block counter, the
-  // last contributor sums the fragments in CTA order and runs the epilogue.
+  // Fold the accumulators of row group r, which this CTA's unit range has just left.  Warp-local:
+  // alone -> epilogue; shared -> fragment to scratch, per-row-block counter, the last contributor
+  // sums the fragments in CTA order and runs the epilogue.
   auto flush = [&](int r) {
     const int rb = r * 8 + warp;
-    if (rb >= p.RB) return;
-    const long long ua = (long long)r * KS, ub = ua + KS - 1;
-    const int c_first = (int)(((ua + 1) * G + U - 1) / U) - 1;     // CTA of unit u: ceil((u+1)G/U) - 1
-    const int c_last = (int)(((ub + 1) * G + U - 1) / U) - 1;
-    const int n = c_last - c_first + 1;
+    if (rb * 16 >= p.rows) return;
+    int c_first, n;
+    contributors(ur, r, &c_first, &n);
     if (n > 1) {
       float4* part = reinterpret_cast<float4*>(p.partials) + (int64_t)rb * p.ksplit * (32 * NB);
       float4* mine = part + (int64_t)((int)blockIdx.x - c_first) * (32 * NB) + lane * NB;
@@ -551,34 +580,35 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const Ge
     fragment_epilogue<NB>(p, acc, rb, g, t);
   };
 
+  bool dead = false;
   zero_acc();
-  int seg_r = u0 < u1 ? u0 / KS : -1;
+  int seg_r = ur.u0 < ur.u1 ? ur.u0 / ur.KS : -1;
   int it = 0;
-  for (int u = u0; u < u1; ++u, ++it) {
-    const int r = u / KS, ks = u - r * KS;
+  // ldmatrix lane addressing: matrix mi = lane/8, row lane%8
+  const int mi = lane >> 3, lr = lane & 7;
+  const uint32_t a_lane = (uint32_t)((mi >> 1) * 2048 + (2 * warp + (mi & 1)) * 128 + lr * 16);
+  const uint32_t b_lane = (uint32_t)((mi & 1) * (Bp * 16) + (mi >> 1) * 128 + lr * 16);
+  for (int u = ur.u0; u < ur.u1; ++u, ++it) {
+    const int r = u / ur.KS;
     if (r != seg_r) {
       flush(seg_r);
       zero_acc();
       seg_r = r;
     }
     const int s = it % kStages, k = it / kStages;
-    const int nch = min(kCH, p.KC - ks * kCH);
     mbar_wait(&full_bar[s], k & 1, dead, err);
-    if (r * 8 + warp < p.RB) {
-      const unsigned char* st = smem + s * kStage;
-      const unsigned char* xst = st + kWStage + g * 64 + t * 16;
-      const unsigned char* wst = st + warp * (kCH * 1024) + lane * 32;
+    if ((r * 8 + warp) * 16 < p.rows) {
+      const uint32_t st = smem_u32(smem + s * kStage);
 #pragma unroll
-      for (int c = 0; c < kCH; ++c) {
-        if (c < nch) {
-          const uint4 lo = *reinterpret_cast<const uint4*>(wst + c * 1024);
-          const uint4 hi = *reinterpret_cast<const uint4*>(wst + c * 1024 + 16);
+      for (int j = 0; j < 8; ++j) {            // 8 k-steps of 16
+        uint32_t a[4];
+        ldmatrix_x4(a, st + a_lane + j * 4096);
 #pragma unroll
-          for (int nt = 0; nt < NB; ++nt) {
-            const uint4 bx = *reinterpret_cast<const uint4*>(xst + c * (Bp * 64) + nt * 512);
-            mma_bf16(acc[nt], lo.x, hi.x, lo.y, hi.y, bx.x, bx.y);
-            mma_bf16(acc[nt], lo.z, hi.z, lo.w, hi.w, bx.z, bx.w);
-          }
+        for (int np = 0; np < NB / 2; ++np) {  // two batch tiles per ldmatrix.x4
+          uint32_t b[4];
+          ldmatrix_x4(b, st + kWStage + b_lane + j * (2 * Bp * 16) + np * 256);
+          mma_bf16(acc[2 * np], a[0], a[1], a[2], a[3], b[0], b[1]);
+          mma_bf16(acc[2 * np + 1], a[0], a[1], a[2], a[3], b[2], b[3]);
         }
       }
     }
@@ -586,6 +616,260 @@ __global__ void __launch_bounds__(kStreamThreads, 1) gemv_stream_kernel(const Ge
     if (lane == 0) mbar_arrive(&empty_bar[s]);
   }
   if (seg_r >= 0) flush(seg_r);
+}
+
+// ---------------------------------------------------------------------------------------------
+// tcgen05 variant
+// ---------------------------------------------------------------------------------------------
+constexpr int kTcThreads = 6 * 32;    // warp 0 producer, warp 1 MMA issue + TMEM, warps 2..5 epilogue
+
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  // K-major, no swizzle: start address, leading (K-direction) and stride (M/N-direction) byte
+  // offsets between 8x8 core matrices, all in 16-byte units; bit 46 = descriptor version 1.
+  return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) |
+         ((uint64_t)(sbo_bytes >> 4) << 32) | (1ull << 46);
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+
+template <int N> __device__ __forceinline__ void tmem_load_row(float (&v)[N], uint32_t taddr);
+template <>
+__device__ __forceinline__ void tmem_load_row<32>(float (&v)[32], uint32_t taddr) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+template <>
+__device__ __forceinline__ void tmem_load_row<16>(float (&v)[16], uint32_t taddr) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Epilogue of one accumulator row held by one thread (v[b], b < N).  Rows g and g+8 of a 16-row
+// block -- the pairs the fused epilogues combine -- are 8 lanes apart in the same warp.
+template <int N>
+__device__ __forceinline__ void row_epilogue(const GemvParams& p, float (&v)[N], int row) {
+  typedef Layout<__nv_bfloat16> LY;
+  const int rb = row >> 4, rr = row & 15, g = rr & 7, hi = rr >> 3;
+  if (p.epi == EPI_STORE_F32) {
+    if (row < p.rows) {
+#pragma unroll
+      for (int b = 0; b < N; ++b)
+        if (b < p.B) p.out[(int64_t)b * p.out_pitch + row] = v[b];
+    }
+    return;
+  }
+  float w[N];                                   // the partner row's values
+#pragma unroll
+  for (int b = 0; b < N; ++b) w[b] = __shfl_xor_sync(0xffffffffu, v[b], 8);
+  if (row >= p.rows) return;
+  if (p.epi == EPI_SILU_GATE) {
+    const int o = rb * 8 + g;
+    if (hi == 0 && o < p.n_act) {
+      __nv_bfloat16* act = reinterpret_cast<__nv_bfloat16*>(p.act);
+#pragma unroll
+      for (int b = 0; b < N; ++b) {
+        if (b < p.B) {
+          const float a = v[b], u = w[b];
+          // silu(a) = a * (1 / (1 + exp2((a * -1) * (1/ln2))))     src/HighLevelOps.jl:153-160
+          const float ex = exp2f((a * -1.0f) * kInvLn2);
+          const float sg = 1.0f / (1.0f + ex);
+          act[LY::x_offset(b, o, N)] = __float2bfloat16_rn((a * sg) * u);
+        }
+      }
+    }
+    return;
+  }
+  // EPI_QKV_ROPE
+  __nv_bfloat16* kv = reinterpret_cast<__nv_bfloat16*>(p.kv_layer);
+  const int D = p.D, tiles_per_head = D >> 4, half = D >> 1;
+  const int pos = *p.pos;
+  const int hs = rb / tiles_per_head, jj = rb - hs * tiles_per_head;
+  if (hs < p.Hl + p.KVl) {
+    // rows g / g+8 of the block are the RoPE pair (d0, d0 + D/2)      src/NN.jl:253-303
+    const int d0 = 8 * jj + g;
+    const float ang = (float)pos * p.inv_freq[d0];
+    const float sn = sinf(ang);
+    const float cs = sinf(kHalfPi + ang * -1.0f);   // cos(a) = sin(pi/2 - a)
+    const int d = hi ? d0 + half : d0;
+#pragma unroll
+    for (int b = 0; b < N; ++b) {
+      if (b < p.B) {
+        // low row: x0*cos - x1*sin; high row: x0*sin + x1*cos (x0 = the low row's value)
+        const float o = hi ? (w[b] * sn + v[b] * cs) : (v[b] * cs + (w[b] * sn) * -1.0f);
+        if (hs < p.Hl) {
+          reinterpret_cast<__nv_bfloat16*>(p.q_out)[(int64_t)b * p.q_pitch + hs * D + d] = __float2bfloat16_rn(o);
+        } else {
+          kv[b * p.kv_batch_stride + (hs - p.Hl) * p.kv_head_stride + kcache_offset(pos, d, D)] = __float2bfloat16_rn(o);
+        }
+      }
+    }
+  } else {
+    const int d = 16 * jj + rr;
+#pragma unroll
+    for (int b = 0; b < N; ++b)
+      if (b < p.B)
+        kv[b * p.kv_batch_stride + (hs - p.Hl - p.KVl) * p.kv_head_stride + vcache_offset(pos, d, D)] =
+            __float2bfloat16_rn(v[b]);
+  }
+}
+
+template <int N>
+__global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const GemvParams p, int* err) {
+  constexpr int kXStage = N * 256;
+  constexpr int kStage = kWStage + kXStage;
+  constexpr uint32_t kTmemCols = 2 * N;       // two accumulator buffers (32 or 64 columns)
+  // instruction descriptor, kind::f16: D = f32 (bit 4), A = B = bf16 (bits 7, 10), both K-major,
+  // N >> 3 at bit 17, M >> 4 at bit 24
+  constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((128u >> 4) << 24);
+  extern __shared__ __align__(1024) unsigned char smem[];
+  __shared__ __align__(8) uint64_t full_bar[kStages];
+  __shared__ __align__(8) uint64_t empty_bar[kStages];
+  __shared__ __align__(8) uint64_t acc_full[2];
+  __shared__ __align__(8) uint64_t acc_empty[2];
+  __shared__ uint32_t tmem_base_slot;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const UnitRange ur = unit_range(p);
+  if (tid == 0) {
+#pragma unroll
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&acc_full[0], 1); mbar_init(&acc_full[1], 1);
+    mbar_init(&acc_empty[0], 4); mbar_init(&acc_empty[1], 4);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_base_slot)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+  bool dead = false;
+
+  if (warp == 0) {
+    produce<N>(p, ur, smem, full_bar, empty_bar, lane, err);
+  } else if (warp == 1) {
+    // ---------------- MMA issue ----------------
+    int it = 0, seg = 0;
+    for (int u = ur.u0; u < ur.u1; ++u, ++it) {
+      const int ks = u % ur.KS;
+      const bool first = (u == ur.u0) || ks == 0;
+      const bool last = (u == ur.u1 - 1) || ks == ur.KS - 1;
+      const int buf = seg & 1;
+      if (first) mbar_wait(&acc_empty[buf], ((seg >> 1) & 1) ^ 1, dead, err);   // epilogue has drained this buffer
+      const int s = it % kStages, k = it / kStages;
+      mbar_wait(&full_bar[s], k & 1, dead, err);
+      tc_fence_after();
+      if (lane == 0) {
+        const uint32_t st = smem_u32(smem + s * kStage);
+        const uint64_t adesc = smem_desc(st, 2048, 128);
+        const uint64_t bdesc = smem_desc(st + kWStage, N * 16, 128);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)     // 8 k-steps of 16: two core matrices along K each
+          tc_mma_f16(tmem_base + buf * N, adesc + (uint64_t)(j * (4096 >> 4)), bdesc + (uint64_t)(j * ((2 * N * 16) >> 4)),
+                     kIdesc, (first && j == 0) ? 0u : 1u);
+        tc_commit(&empty_bar[s]);       // stage free once these MMAs have read it
+        if (last) tc_commit(&acc_full[buf]);
+      }
+      __syncwarp();
+      if (last) ++seg;
+    }
+  } else {
+    // ---------------- epilogue: warp quarter q owns TMEM lanes / rows 32q .. 32q+31 ----------------
+    const int q = warp & 3;
+    int seg = 0;
+    for (int u = ur.u0; u < ur.u1; ++seg) {
+      const int r = u / ur.KS;
+      const int u_end = min(ur.u1, (r + 1) * ur.KS);
+      u = u_end;
+      const int buf = seg & 1;
+      mbar_wait(&acc_full[buf], (seg >> 1) & 1, dead, err);
+      tc_fence_after();
+      float v[N];
+      tmem_load_row<N>(v, tmem_base + ((uint32_t)(32 * q) << 16) + (uint32_t)(buf * N));
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+      const int row_in_group = 32 * q + lane;
+      int c_first, n;
+      contributors(ur, r, &c_first, &n);
+      bool run = true;
+      if (n > 1) {
+        float4* part = reinterpret_cast<float4*>(p.partials) + (int64_t)r * p.ksplit * (128 * N / 4);
+        float4* mine = part + (int64_t)((int)blockIdx.x - c_first) * (128 * N / 4) + row_in_group * (N / 4);
+#pragma unroll
+        for (int i = 0; i < N / 4; ++i) mine[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        __threadfence();
+        __syncwarp();
+        unsigned prev = 0;
+        if (lane == 0) prev = atomicAdd(&p.counters[r * 4 + q], 1u);
+        prev = __shfl_sync(0xffffffffu, prev, 0);
+        run = prev == (unsigned)n - 1u;
+        if (run) {
+          if (lane == 0) p.counters[r * 4 + q] = 0u;     // ready for the next launch
+          __threadfence();
+#pragma unroll
+          for (int i = 0; i < N; ++i) v[i] = 0.f;
+          for (int k0 = 0; k0 < n; k0 += 2) {
+            float4 t0[N / 4], t1[N / 4];
+            const float4* pa = part + (int64_t)k0 * (128 * N / 4) + row_in_group * (N / 4);
+            const bool two = k0 + 1 < n;
+#pragma unroll
+            for (int i = 0; i < N / 4; ++i) {
+              t0[i] = __ldcg(pa + i);
+              t1[i] = two ? __ldcg(pa + (128 * N / 4) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int i = 0; i < N / 4; ++i) {
+              v[4 * i] += t0[i].x; v[4 * i + 1] += t0[i].y; v[4 * i + 2] += t0[i].z; v[4 * i + 3] += t0[i].w;
+              v[4 * i] += t1[i].x; v[4 * i + 1] += t1[i].y; v[4 * i + 2] += t1[i].z; v[4 * i + 3] += t1[i].w;
+            }
+          }
+        }
+      }
+      // every lane of the warp takes the same branch here (the counter is per warp quarter)
+      if (run) row_epilogue<N>(p, v, r * 128 + row_in_group);
+    }
+  }
+  // all roles meet before the accumulator memory is given back
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
 }
 
 template <typename WT, int NB, int MT, int STAGES>
@@ -602,47 +886,52 @@ int32_t launch_ring(Ctx* ctx, const GemvParams& p, cudaStream_t stream) {
   return LMB200_OK;
 }
 
-template <int NB>
+template <int Bp>
 constexpr size_t stream_smem() {
-  return (size_t)kStages * (kWStage + kCH * 8 * NB * 64);
+  return (size_t)kStages * (kWStage + Bp * 256) + 1024;
 }
 
-template <int NB>
-int32_t launch_stream(Ctx* ctx, const GemvParams& p, cudaStream_t stream) {
-  gemv_stream_kernel<NB><<<p.grid, kStreamThreads, stream_smem<NB>(), stream>>>(p, ctx->dev_err);
+template <int Bp>
+int32_t launch_bf16(Ctx* ctx, const GemvParams& p, cudaStream_t stream) {
+  if (g_variant == GEMV_MMA_SYNC)
+    gemv_mma_kernel<Bp / 8><<<p.grid, kMmaThreads, stream_smem<Bp>(), stream>>>(p, ctx->dev_err);
+  else
+    gemv_tc_kernel<Bp><<<p.grid, kTcThreads, stream_smem<Bp>(), stream>>>(p, ctx->dev_err);
   ctx->launches++;
   LMB_CUDA(cudaGetLastError());
   return LMB200_OK;
 }
 
-constexpr int kMtBf16 = 4;
 constexpr int kMtF32 = 1;
 constexpr size_t kMaxXsBytes = 96 * 1024;
 
 }  // namespace
 
-void gemv_set_stream_kernel(bool on) { g_use_stream = on; }
+void gemv_set_variant(int variant) { g_variant = variant == GEMV_MMA_SYNC ? GEMV_MMA_SYNC : GEMV_TCGEN05; }
+int gemv_variant() { return g_variant; }
 
-GemvPlan gemv_plan(const Ctx* ctx, int dtype, int B, int RB, int KC) {
+GemvPlan gemv_plan(const Ctx* ctx, int dtype, int B, int rows, int K) {
   GemvPlan pl;
-  const int Bp = batch_pad(B);
-  if (dtype == LMB200_BF16 && g_use_stream) {
-    const int KS = (int)ceil_div(KC, kCH);
-    const int nrbg = (int)ceil_div(RB, 8);
+  if (dtype == LMB200_BF16) {
+    const int Bp = Layout<__nv_bfloat16>::batch_pad(B);
+    const int KS = (int)ceil_div(K, 128);
+    const int nrbg = (int)ceil_div(rows, 128);
     const int64_t U = (int64_t)nrbg * KS;
     int G = ctx->sm_count;
     if (G > U) G = (int)U;
     pl.grid = G;
     const int64_t upc_min = U / G;                       // >= 1
     pl.ksplit = (int)ceil_div(KS, upc_min) + 1;          // contributors reserved per row group
-    pl.kc_per_split = KC;
-    pl.partial_floats = (int64_t)nrbg * pl.ksplit * kRPC * Bp;    // [row block][contributor][16 x Bp fragment]
+    pl.kc_per_split = KS;
+    pl.partial_floats = (int64_t)nrbg * pl.ksplit * 128 * Bp;   // [row group][contributor][128 x Bp]
     pl.n_counters = nrbg * 8;
     return pl;
   }
-  const int MT = dtype == LMB200_BF16 ? kMtBf16 : kMtF32;
+  const int Bp = Layout<float>::batch_pad(B);
+  const int RB = (int)ceil_div(rows, 16), KC = (int)ceil_div(K, 32);
+  const int MT = kMtF32;
   const int RPC = 2 * MT * 16;
-  const size_t esz = dtype == LMB200_BF16 ? 2 : 4;
+  const size_t esz = 4;
   const int nrbg = (int)ceil_div(RB, 2 * MT);
   // One CTA per SM is resident (register ring).  Pick the k-split that minimises
   //   waves * (chunks per CTA + fixed cost of staging x and the epilogue, in chunk units)
@@ -671,50 +960,34 @@ GemvPlan gemv_plan(const Ctx* ctx, int dtype, int B, int RB, int KC) {
 // Raise the dynamic shared-memory limit of every instantiation once per device, outside any
 // stream capture.
 int32_t gemv_configure() {
-#define LMB_CFG(KERN, BYTES)                                                                           \
-  LMB_CUDA(cudaFuncSetAttribute(KERN, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(BYTES)));     \
-  LMB_CUDA(cudaFuncSetAttribute(KERN, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared))
-  LMB_CFG((gemv_ring_kernel<__nv_bfloat16, 1, kMtBf16, 4>), kMaxSmem);
-  LMB_CFG((gemv_ring_kernel<__nv_bfloat16, 2, kMtBf16, 4>), kMaxSmem);
-  LMB_CFG((gemv_ring_kernel<__nv_bfloat16, 4, kMtBf16, 3>), kMaxSmem);
+#define LMB_CFG(KERN, BYTES) \
+  LMB_CUDA(cudaFuncSetAttribute(KERN, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(BYTES)))
   LMB_CFG((gemv_ring_kernel<float, 1, kMtF32, 3>), kMaxSmem);
   LMB_CFG((gemv_ring_kernel<float, 2, kMtF32, 3>), kMaxSmem);
   LMB_CFG((gemv_ring_kernel<float, 4, kMtF32, 2>), kMaxSmem);
-  LMB_CFG(gemv_stream_kernel<1>, stream_smem<1>());
-  LMB_CFG(gemv_stream_kernel<2>, stream_smem<2>());
-  LMB_CFG(gemv_stream_kernel<4>, stream_smem<4>());
+  LMB_CFG(gemv_mma_kernel<2>, stream_smem<16>());
+  LMB_CFG(gemv_mma_kernel<4>, stream_smem<32>());
+  LMB_CFG(gemv_tc_kernel<16>, stream_smem<16>());
+  LMB_CFG(gemv_tc_kernel<32>, stream_smem<32>());
 #undef LMB_CFG
   return LMB200_OK;
 }
 
 int32_t gemv_launch(Ctx* ctx, int dtype, GemvParams p, cudaStream_t stream) {
   LMB_REQUIRE(p.B >= 1 && p.B <= 32, "gemv: batch %d outside 1..32", p.B);
-  const int nb = batch_pad(p.B) / 8;
-  if (dtype == LMB200_BF16 && g_use_stream) {
-    LMB_REQUIRE(p.grid >= 1 && p.partials && p.counters, "gemv: stream kernel needs a plan and scratch");
-    switch (nb) {
-      case 1: return launch_stream<1>(ctx, p, stream);
-      case 2: return launch_stream<2>(ctx, p, stream);
-      default: return launch_stream<4>(ctx, p, stream);
-    }
+  if (dtype == LMB200_BF16) {
+    LMB_REQUIRE(p.grid >= 1 && p.partials && p.counters, "gemv: the bf16 kernels need a plan and scratch");
+    return Layout<__nv_bfloat16>::batch_pad(p.B) == 16 ? launch_bf16<16>(ctx, p, stream) : launch_bf16<32>(ctx, p, stream);
   }
+  LMB_REQUIRE(dtype == LMB200_F32, "gemv: dtype %d", dtype);
   LMB_REQUIRE(p.ksplit >= 1 && p.kc_per_split >= 1 && (int64_t)p.ksplit * p.kc_per_split >= p.KC,
               "gemv: bad k split");
   LMB_REQUIRE(p.ksplit == 1 || (p.partials && p.counters), "gemv: split-K needs scratch");
-  if (dtype == LMB200_BF16) {
-    switch (nb) {
-      case 1: return launch_ring<__nv_bfloat16, 1, kMtBf16, 4>(ctx, p, stream);
-      case 2: return launch_ring<__nv_bfloat16, 2, kMtBf16, 4>(ctx, p, stream);
-      default: return launch_ring<__nv_bfloat16, 4, kMtBf16, 3>(ctx, p, stream);
-    }
-  } else if (dtype == LMB200_F32) {
-    switch (nb) {
-      case 1: return launch_ring<float, 1, kMtF32, 3>(ctx, p, stream);
-      case 2: return launch_ring<float, 2, kMtF32, 3>(ctx, p, stream);
-      default: return launch_ring<float, 4, kMtF32, 2>(ctx, p, stream);
-    }
+  switch (Layout<float>::batch_pad(p.B) / 8) {
+    case 1: return launch_ring<float, 1, kMtF32, 3>(ctx, p, stream);
+    case 2: return launch_ring<float, 2, kMtF32, 3>(ctx, p, stream);
+    default: return launch_ring<float, 4, kMtF32, 2>(ctx, p, stream);
   }
-  return fail(LMB200_EINVAL, "gemv: dtype %d", dtype);
 }
 
 }  // namespace lmb

@@ -12,24 +12,31 @@ enum GemvEpilogue {
   EPI_QKV_ROPE = 2     // RoPE on q and k, q -> q_out, k/v appended to the cache at *pos
 };
 
+// bf16 kernel variants (float32 always runs the register-ring kernel)
+enum GemvVariant {
+  GEMV_TCGEN05 = 0,    // tcgen05.mma, accumulators in TMEM (default)
+  GEMV_MMA_SYNC = 1    // mma.sync m16n8k16 from ldmatrix
+};
+
 struct GemvParams {
-  const void* W = nullptr;   // tiled weights (wtile_offset)
-  const void* x = nullptr;   // tiled activations (xtile_offset), same element type as W
+  const void* W = nullptr;   // weights in Layout<WT>::w_offset order
+  const void* x = nullptr;   // activations in Layout<WT>::x_offset order, same element type as W
   int B = 0;
-  int rows = 0;              // valid logical rows (<= 16*RB)
-  int RB = 0;                // 16-row blocks
-  int KC = 0;                // 32-wide k chunks
-  // work split, filled by gemv_plan
-  int ksplit = 1;            // ring kernel: k-splits (gridDim.y)
+  int rows = 0;              // valid internal rows
+  int K = 0;                 // valid reduction length
+  int RB = 0;                // float32 ring kernel: 16-row blocks
+  int KC = 0;                //                      32-wide k chunks
+  // work split, filled from gemv_plan
+  int ksplit = 1;            // ring: k-splits (gridDim.y); bf16: contributors reserved per row group
   int kc_per_split = 0;
-  int grid = 0;              // stream kernel: number of CTAs
+  int grid = 0;              // bf16 kernels: number of CTAs
   float* partials = nullptr;     // split-K scratch
-  unsigned* counters = nullptr;  // one per row group, zero between launches
+  unsigned* counters = nullptr;  // zero between launches
   int epi = EPI_STORE_F32;
   // EPI_STORE_F32
   float* out = nullptr;
   int out_pitch = 0;
-  // EPI_SILU_GATE: act is a tiled activation buffer of the same batch padding as x
+  // EPI_SILU_GATE: act is a GEMV activation buffer of the same batch padding as x
   void* act = nullptr;
   int n_act = 0;
   // EPI_QKV_ROPE
@@ -50,9 +57,9 @@ struct GemvPlan {
 };
 
 int32_t gemv_configure();
-// bf16 kernel choice: true = bulk-TMA stream-K kernel (default), false = register-ring kernel
-void gemv_set_stream_kernel(bool on);
-GemvPlan gemv_plan(const Ctx* ctx, int dtype, int B, int RB, int KC);
+void gemv_set_variant(int variant);
+int gemv_variant();
+GemvPlan gemv_plan(const Ctx* ctx, int dtype, int B, int rows, int K);
 // dtype: LMB200_F32 or LMB200_BF16
 int32_t gemv_launch(Ctx* ctx, int dtype, GemvParams p, cudaStream_t stream);
 

@@ -72,20 +72,16 @@ struct FillSrc {
 
 template <typename WT>
 __global__ void fill_tiled_kernel(WT* dst, WMap m, FillSrc f) {
-  const int64_t total = (int64_t)m.RB * m.KC * 512;
+  // every valid (internal row, k); the padding of the layout stays zero from the allocation
+  const int64_t total = (int64_t)m.rows * m.K;
   for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total;
        o += (int64_t)gridDim.x * blockDim.x) {
-    const int e16 = (int)(o & 15);
-    const int lane = (int)((o >> 4) & 31);
-    const int64_t unit = o >> 9;
-    const int kc = (int)(unit % m.KC);
-    const int rb = (int)(unit / m.KC);
-    const int g = lane >> 2, t = lane & 3;
-    const int i = rb * 16 + g + 8 * (e16 >> 3);
-    const int k = kc * 32 + 8 * t + (e16 & 7);
+    const int i = (int)(o / m.K);
+    const int k = (int)(o - (int64_t)i * m.K);
     int slot, lrow, lcol;
+    const int64_t at = Layout<WT>::w_offset(i, k, m.K);
     if (!wmap_resolve(m, i, k, &slot, &lrow, &lcol)) {
-      if (f.only_slot < 0) dst[o] = from_f32<WT>(0.f);
+      if (f.only_slot < 0) dst[at] = from_f32<WT>(0.f);
       continue;
     }
     if (f.only_slot >= 0 && slot != f.only_slot) continue;
@@ -97,7 +93,7 @@ __global__ void fill_tiled_kernel(WT* dst, WMap m, FillSrc f) {
     } else {
       v = synth_value(f.key[slot], (uint64_t)lrow * m.src_cols[slot] + lcol, f.scale, 0.f);
     }
-    dst[o] = from_f32<WT>(v);
+    dst[at] = from_f32<WT>(v);
   }
 }
 
@@ -146,7 +142,7 @@ __global__ void fill_kv_kernel(WT* kv, int64_t batch_stride, int64_t head_stride
 // xn = (x * recip(sqrt(mean(x*x) + eps))) * w          src/HighLevelOps.jl:299-304, NN.jl:149-161
 // One CTA per sequence; the row stays in shared memory between the two passes and all global
 // accesses are independent float4s, so the kernel costs a couple of memory round trips.
-// xn is a tiled activation buffer (xtile_offset) of batch padding Bp.  n % 4 == 0.
+// xn is a GEMV activation buffer (Layout<WT>::x_offset) of batch padding Bp.  n % 4 == 0.
 constexpr int kNormThreads = 512;
 template <typename WT>
 __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta,
@@ -201,7 +197,7 @@ __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(float* __rest
 #pragma unroll 4
     for (int i = tid; i < n4; i += kNormThreads) {
       const float4 v = rs[i], g = w4[i];
-      WT* o = xn + xtile_offset(b, 4 * i, Bp);       // 4 consecutive k never straddle a 32-chunk
+      WT* o = xn + Layout<WT>::x_offset(b, 4 * i, Bp);   // 4 consecutive k stay inside one 8-k group
       o[0] = from_f32<WT>((v.x * inv) * g.x);
       o[1] = from_f32<WT>((v.y * inv) * g.y);
       o[2] = from_f32<WT>((v.z * inv) * g.z);
@@ -290,11 +286,13 @@ enum Slot { S_ATTN_NORM = 0, S_Q = 1, S_K = 2, S_V = 3, S_O = 4, S_FFN_NORM = 5,
 constexpr uint64_t kIdEmbed = 0xFFFF0, kIdFinalNorm = 0xFFFF1, kIdHead = 0xFFFF2;
 constexpr uint64_t kIdKvBase = 0x100000;
 
-int64_t tiled_elems(const WMap& m) { return (int64_t)m.RB * m.KC * 512; }
+int64_t tiled_elems(const WMap& m, int dtype) {
+  return dtype == LMB200_BF16 ? Layout<__nv_bfloat16>::w_elems(m.rows, m.K) : Layout<float>::w_elems(m.rows, m.K);
+}
 
 template <typename WT>
 int32_t fill_tiled(Ctx* ctx, void* dst, const WMap& m, const FillSrc& f) {
-  fill_tiled_kernel<WT><<<fill_grid(tiled_elems(m)), 256, 0, ctx->stream>>>(reinterpret_cast<WT*>(dst), m, f);
+  fill_tiled_kernel<WT><<<fill_grid((int64_t)m.rows * m.K), 256, 0, ctx->stream>>>(reinterpret_cast<WT*>(dst), m, f);
   ctx->launches++;
   LMB_CUDA(cudaGetLastError());
   return LMB200_OK;
@@ -445,16 +443,16 @@ extern "C" int32_t lmb200_model_create(lmb200_ctx hctx, const lmb200_model_confi
   };
   M->layers.resize(c.n_layers);
   for (auto& L : M->layers) {
-    alloc(&L.wqkv, tiled_elems(M->m_qkv) * M->esz);
-    alloc(&L.wo, tiled_elems(M->m_o) * M->esz);
-    alloc(&L.wgu, tiled_elems(M->m_gu) * M->esz);
-    alloc(&L.wdown, tiled_elems(M->m_down) * M->esz);
+    alloc(&L.wqkv, tiled_elems(M->m_qkv, c.dtype) * M->esz);
+    alloc(&L.wo, tiled_elems(M->m_o, c.dtype) * M->esz);
+    alloc(&L.wgu, tiled_elems(M->m_gu, c.dtype) * M->esz);
+    alloc(&L.wdown, tiled_elems(M->m_down, c.dtype) * M->esz);
     alloc((void**)&L.attn_norm, (int64_t)c.hidden * 4);
     alloc((void**)&L.ffn_norm, (int64_t)c.hidden * 4);
   }
   alloc(&M->embed, (int64_t)c.vocab * c.hidden * M->esz);
   alloc((void**)&M->final_norm, (int64_t)c.hidden * 4);
-  alloc(&M->lm_head, tiled_elems(M->m_head) * M->esz);
+  alloc(&M->lm_head, tiled_elems(M->m_head, c.dtype) * M->esz);
   alloc((void**)&M->inv_freq, (int64_t)(M->D / 2) * 4);
   if (rc != LMB200_OK) { lmb200_model_destroy(reinterpret_cast<lmb200_model>(M)); return rc; }
 
@@ -604,7 +602,7 @@ namespace {
 GemvParams gemv_params(Session* S, const void* W, const WMap& m, const GemvPlan& pl, const void* x) {
   GemvParams p;
   p.W = W; p.x = x; p.B = S->B;
-  p.rows = m.rows; p.RB = m.RB; p.KC = m.KC;
+  p.rows = m.rows; p.K = m.K; p.RB = m.RB; p.KC = m.KC;
   p.ksplit = pl.ksplit; p.kc_per_split = pl.kc_per_split; p.grid = pl.grid;
   p.partials = S->gemv_partials; p.counters = S->gemv_counters;
   return p;
@@ -759,14 +757,14 @@ extern "C" int32_t lmb200_session_create(lmb200_model hm, int32_t batch, int32_t
   S->kv_head_stride = (int64_t)(S->cap / 16) * kv_block_elems(M->D);
   S->kv_batch_stride = S->kv_head_stride * M->KVl;
   S->kv_layer_stride = S->kv_batch_stride * batch;
-  S->Bp = batch_pad(batch);
+  S->Bp = c.dtype == LMB200_BF16 ? Layout<__nv_bfloat16>::batch_pad(batch) : Layout<float>::batch_pad(batch);
   S->q_pitch = M->Hl * M->D;
   S->logits_pitch = (int)round_up(c.vocab, 16);
 
   int64_t max_part = 0;
   int max_cnt = 0;
   auto plan = [&](GemvPlan& g, const WMap& m) {
-    g = gemv_plan(ctx, c.dtype, batch, m.RB, m.KC);
+    g = gemv_plan(ctx, c.dtype, batch, m.rows, m.K);
     if (g.partial_floats > max_part) max_part = g.partial_floats;
     if (g.n_counters > max_cnt) max_cnt = g.n_counters;
   };
@@ -782,10 +780,13 @@ extern "C" int32_t lmb200_session_create(lmb200_model hm, int32_t batch, int32_t
   alloc((void**)&S->delta, (int64_t)batch * c.hidden * 4);
   alloc((void**)&S->logits, (int64_t)batch * S->logits_pitch * 4);
   // tiled GEMV inputs: [k chunks][Bp][32], zero in the padding rows and columns
-  alloc(&S->xn, (int64_t)M->m_qkv.KC * S->Bp * 32 * M->esz);
+  auto x_elems = [&](int K) {
+    return c.dtype == LMB200_BF16 ? Layout<__nv_bfloat16>::x_elems(K, S->Bp) : Layout<float>::x_elems(K, S->Bp);
+  };
+  alloc(&S->xn, x_elems(M->m_qkv.K) * M->esz);
   alloc(&S->qbuf, (int64_t)batch * S->q_pitch * M->esz);
-  alloc(&S->attn_out, (int64_t)M->m_o.KC * S->Bp * 32 * M->esz);
-  alloc(&S->act, (int64_t)M->m_down.KC * S->Bp * 32 * M->esz);
+  alloc(&S->attn_out, x_elems(M->m_o.K) * M->esz);
+  alloc(&S->act, x_elems(M->m_down.K) * M->esz);
   alloc((void**)&S->tokens, (int64_t)batch * 4);
   alloc((void**)&S->pos, 4);
   alloc((void**)&S->step_ctr, 4);
@@ -1010,6 +1011,84 @@ extern "C" int32_t lmb200_session_step_bytes(lmb200_session h, int32_t T, int64_
   int64_t kv_write = (int64_t)c.n_layers * S->B * M->KVl * M->D * 2 * e;
   *bytes = w + kv_read + kv_write;
   return LMB200_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// stand-alone Linear for one batch of rows (tests, A/B of the GEMV kernels)
+// ---------------------------------------------------------------------------------------------
+namespace lmb {
+namespace {
+template <typename WT>
+__global__ void fill_x_kernel(WT* dst, const float* src, int B, int K, int Bp) {
+  const int64_t total = (int64_t)B * K;
+  for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total; o += (int64_t)gridDim.x * blockDim.x) {
+    const int b = (int)(o / K), k = (int)(o - (int64_t)b * K);
+    dst[Layout<WT>::x_offset(b, k, Bp)] = from_f32<WT>(src[o]);
+  }
+}
+}  // namespace
+}  // namespace lmb
+
+extern "C" int32_t lmb200_linear_gemv(lmb200_ctx hctx, int32_t dtype, int32_t variant, int32_t rows, int32_t K,
+                                      int32_t batch, const float* w_host, const float* x_host, float* out_host) {
+  Ctx* ctx = ctx_from(hctx);
+  if (!ctx) return LMB200_EINVAL;
+  LMB_REQUIRE(w_host && x_host && out_host, "linear_gemv: null pointer");
+  LMB_REQUIRE(dtype == LMB200_F32 || dtype == LMB200_BF16, "linear_gemv: dtype %d", dtype);
+  LMB_REQUIRE(rows >= 1 && K >= 1 && batch >= 1 && batch <= 32, "linear_gemv: rows %d, K %d, batch %d", rows, K, batch);
+  LMB_CUDA(cudaSetDevice(ctx->device));
+  const bool bf = dtype == LMB200_BF16;
+  const int esz = bf ? 2 : 4;
+  const int Bp = bf ? Layout<__nv_bfloat16>::batch_pad(batch) : Layout<float>::batch_pad(batch);
+  WMap m;
+  m.kind = MAP_PLAIN; m.rows = rows; m.K = K; m.src_rows[0] = rows; m.src_cols[0] = K;
+  finish_map(m);
+  const int saved = gemv_variant();
+  if (bf) gemv_set_variant(variant);
+  const GemvPlan pl = gemv_plan(ctx, dtype, batch, rows, K);
+  void *W = nullptr, *X = nullptr;
+  float *ws = nullptr, *xs = nullptr, *out = nullptr, *partials = nullptr;
+  unsigned* counters = nullptr;
+  int32_t rc = LMB200_OK;
+  auto alloc = [&](void** p, int64_t bytes) { if (rc == LMB200_OK) rc = dmalloc(p, bytes, true, ctx->stream); };
+  alloc(&W, tiled_elems(m, dtype) * esz);
+  alloc(&X, (bf ? Layout<__nv_bfloat16>::x_elems(K, Bp) : Layout<float>::x_elems(K, Bp)) * esz);
+  alloc((void**)&ws, (int64_t)rows * K * 4);
+  alloc((void**)&xs, (int64_t)batch * K * 4);
+  alloc((void**)&out, (int64_t)batch * rows * 4);
+  alloc((void**)&partials, pl.partial_floats * 4);
+  alloc((void**)&counters, (int64_t)pl.n_counters * 4);
+  do {
+    if (rc != LMB200_OK) break;
+    if (cudaMemcpyAsync(ws, w_host, (size_t)rows * K * 4, cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess ||
+        cudaMemcpyAsync(xs, x_host, (size_t)batch * K * 4, cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess) {
+      rc = fail(LMB200_ECUDA, "linear_gemv: upload failed"); break;
+    }
+    FillSrc f{};
+    f.only_slot = -1; f.src[0] = ws;
+    Model tmp; tmp.ctx = ctx; tmp.cfg.dtype = dtype;
+    rc = fill_tiled_dt(&tmp, W, m, f);
+    if (rc != LMB200_OK) break;
+    if (bf) fill_x_kernel<__nv_bfloat16><<<fill_grid((int64_t)batch * K), 256, 0, ctx->stream>>>((__nv_bfloat16*)X, xs, batch, K, Bp);
+    else fill_x_kernel<float><<<fill_grid((int64_t)batch * K), 256, 0, ctx->stream>>>((float*)X, xs, batch, K, Bp);
+    ctx->launches++;
+    GemvParams p;
+    p.W = W; p.x = X; p.B = batch; p.rows = rows; p.K = K; p.RB = m.RB; p.KC = m.KC;
+    p.ksplit = pl.ksplit; p.kc_per_split = pl.kc_per_split; p.grid = pl.grid;
+    p.partials = partials; p.counters = counters;
+    p.epi = EPI_STORE_F32; p.out = out; p.out_pitch = rows;
+    rc = gemv_launch(ctx, dtype, p, ctx->stream);
+    if (rc != LMB200_OK) break;
+    if (cudaMemcpyAsync(out_host, out, (size_t)batch * rows * 4, cudaMemcpyDeviceToHost, ctx->stream) != cudaSuccess) {
+      rc = fail(LMB200_ECUDA, "linear_gemv: download failed"); break;
+    }
+  } while (0);
+  cudaError_t se = cudaStreamSynchronize(ctx->stream);
+  if (rc == LMB200_OK && se != cudaSuccess) rc = fail(LMB200_ECUDA, "linear_gemv: %s", cudaGetErrorString(se));
+  if (rc == LMB200_OK) rc = check_device_error(ctx);
+  cudaFree(W); cudaFree(X); cudaFree(ws); cudaFree(xs); cudaFree(out); cudaFree(partials); cudaFree(counters);
+  gemv_set_variant(saved);
+  return rc;
 }
 
 extern "C" int32_t lmb200_session_kv_layer(lmb200_session h, int32_t layer, void** kv_dptr, int64_t* batch_stride,

@@ -173,7 +173,7 @@ def _step_logits(session, tokens):
     return nxt, logits
 
 
-__all__ = ["Model", "Session", "greedy_generate", "decode_attention_noalloc", "shard_layout"]
+__all__ = ["Model", "Session", "greedy_generate", "decode_attention_noalloc", "shard_layout", "linear_gemv"]
 
 
 def shard_layout(cfg_kwargs, matrix, tp_size=1, tp_rank=0):
@@ -196,3 +196,17 @@ def shard_layout(cfg_kwargs, matrix, tp_size=1, tp_rank=0):
         _lib.call("lmb200_shard_map", C.byref(cfg), idx, 0, k, C.byref(s), C.byref(r), C.byref(c))
         col_map.append(c.value)
     return rows.value, cols.value, row_map, col_map
+
+
+def linear_gemv(device, w, x, dtype="bf16", variant=0):
+    """out[b, o] = sum_i x[b, i] * w[o, i] through the decode GEMV kernel (host arrays in and out).
+    variant (bf16): 0 = tcgen05/TMEM, 1 = mma.sync."""
+    w = np.ascontiguousarray(np.asarray(w, dtype=np.float32))
+    x = np.ascontiguousarray(np.asarray(x, dtype=np.float32))
+    rows, K = w.shape
+    batch = x.shape[0]
+    assert x.shape[1] == K
+    out = np.empty((batch, rows), dtype=np.float32)
+    _lib.call("lmb200_linear_gemv", device.handle, _dtype_code(dtype), int(variant), rows, K, batch,
+              w.ctypes.data_as(C.c_void_p), x.ctypes.data_as(C.c_void_p), out.ctypes.data_as(C.c_void_p))
+    return out
