@@ -8,6 +8,7 @@
 #include "common.cuh"
 #include "gemv.cuh"
 #include "model.cuh"
+#include "pdl.cuh"
 
 namespace lmb {
 
@@ -35,6 +36,10 @@ Ctx* ctx_from(lmb200_ctx h) {
   }
   return c;
 }
+
+static bool g_pdl = true;
+bool pdl_enabled() { return g_pdl; }
+void pdl_set_enabled(bool on) { g_pdl = on; }
 
 int32_t check_device_error(Ctx* ctx) {
   if (ctx->dev_err && *reinterpret_cast<volatile int*>(ctx->dev_err) != 0) {
@@ -169,6 +174,8 @@ extern "C" int32_t lmb200_init(int32_t device, lmb200_ctx* out) {
   }
   *c->dev_err = 0;
   // LMB200_GEMV_KERNEL=mma selects the mma.sync bf16 GEMV (for A/B runs); default: tcgen05
+  const char* pdl = getenv("LMB200_PDL");      // LMB200_PDL=0: plain stream-ordered launches
+  pdl_set_enabled(!(pdl && atoi(pdl) == 0));
   const char* sel = getenv("LMB200_GEMV_KERNEL");
   gemv_set_variant((sel && strcmp(sel, "mma") == 0) ? GEMV_MMA_SYNC : GEMV_TCGEN05);
   int32_t rc = gemv_configure();

@@ -23,6 +23,7 @@
 #include <type_traits>
 
 #include "gemv.cuh"
+#include "pdl.cuh"
 
 namespace lmb {
 
@@ -172,6 +173,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) gemv_ring_kernel(const GemvPa
   const int64_t rb_base = (int64_t)blockIdx.x * (2 * MT) + rg * MT;
   const WT* W = reinterpret_cast<const WT*>(p.W);
 
+  pdl_launch_dependents();
   // prefetch the first weight units before touching the activations
   Unit<WT> ring[STAGES][MT];
 #pragma unroll
@@ -183,6 +185,7 @@ __global__ void __launch_bounds__(kRingThreads, 1) gemv_ring_kernel(const GemvPa
       else zero_unit<WT>(ring[s][mt]);
     }
   }
+  pdl_wait();      // everything below reads or writes what earlier kernels produced
   {
     const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const WT*>(p.x) + (int64_t)kc0 * Bp * 32);
     uint4* dst = reinterpret_cast<uint4*>(xs);
@@ -398,8 +401,28 @@ __device__ __forceinline__ void produce(const GemvParams& p, const UnitRange& ur
   const __nv_bfloat16* W = reinterpret_cast<const __nv_bfloat16*>(p.W);
   const __nv_bfloat16* X = reinterpret_cast<const __nv_bfloat16*>(p.x);
   bool dead = false;
-  int it = 0;
-  for (int u = ur.u0; u < ur.u1; ++u, ++it) {
+  // The weights never change: the first stages' weight copies go out before this kernel waits for
+  // its predecessor; the activation copies (and everything else) come after the wait.
+  const int n_units = ur.u1 - ur.u0;
+  const int n_pre = n_units < kStages ? n_units : kStages;
+  if (lane == 0) {
+    for (int it = 0; it < n_pre; ++it) {
+      const int u = ur.u0 + it;
+      const int r = u / ur.KS, ks = u - r * ur.KS;
+      mbar_expect_tx(&full_bar[it], (uint32_t)kStage);
+      bulk_g2s(smem + it * kStage, W + ((int64_t)r * ur.KS + ks) * 16384, (uint32_t)kWStage, &full_bar[it], pol_w);
+    }
+  }
+  pdl_wait();
+  if (lane == 0) {
+    for (int it = 0; it < n_pre; ++it) {
+      const int ks = (ur.u0 + it) % ur.KS;
+      bulk_g2s(smem + it * kStage + kWStage, X + (int64_t)ks * (128 * Bp), (uint32_t)kXStage, &full_bar[it], pol_x);
+    }
+  }
+  __syncwarp();
+  int it = n_pre;
+  for (int u = ur.u0 + n_pre; u < ur.u1; ++u, ++it) {
     const int s = it % kStages, k = it / kStages;
     mbar_wait(&empty_bar[s], (k & 1) ^ 1, dead, err);
     const int r = u / ur.KS, ks = u - r * ur.KS;
@@ -527,11 +550,13 @@ __global__ void __launch_bounds__(kMmaThreads, 1) gemv_mma_kernel(const GemvPara
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   __syncthreads();
+  pdl_launch_dependents();
 
   if (warp == 8) {
     produce<Bp>(p, ur, smem, full_bar, empty_bar, lane, err);
     return;
   }
+  pdl_wait();
 
   const int g = lane >> 2, t = lane & 3;
   float acc[NB][4];
@@ -777,10 +802,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const GemvParams
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
   bool dead = false;
+  pdl_launch_dependents();
 
   if (warp == 0) {
     produce<N>(p, ur, smem, full_bar, empty_bar, lane, err);
   } else if (warp == 1) {
+    pdl_wait();
     // ---------------- MMA issue ----------------
     int it = 0, seg = 0;
     for (int u = ur.u0; u < ur.u1; ++u, ++it) {
@@ -808,6 +835,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const GemvParams
     }
   } else {
     // ---------------- epilogue: warp quarter q owns TMEM lanes / rows 32q .. 32q+31 ----------------
+    pdl_wait();
     const int q = warp & 3;
     int seg = 0;
     for (int u = ur.u0; u < ur.u1; ++seg) {
@@ -880,9 +908,8 @@ int32_t launch_ring(Ctx* ctx, const GemvParams& p, cudaStream_t stream) {
   const size_t smem = xs_bytes > red_bytes ? xs_bytes : red_bytes;
   LMB_REQUIRE(smem <= kMaxSmem, "gemv: %zu bytes of shared memory exceed the configured %zu", smem, kMaxSmem);
   dim3 grid((unsigned)ceil_div(p.RB, 2 * MT), (unsigned)p.ksplit);
-  gemv_ring_kernel<WT, NB, MT, STAGES><<<grid, kRingThreads, smem, stream>>>(p);
+  LMB_CUDA(launch_k(gemv_ring_kernel<WT, NB, MT, STAGES>, grid, dim3(kRingThreads), smem, stream, p));
   ctx->launches++;
-  LMB_CUDA(cudaGetLastError());
   return LMB200_OK;
 }
 
@@ -894,11 +921,10 @@ constexpr size_t stream_smem() {
 template <int Bp>
 int32_t launch_bf16(Ctx* ctx, const GemvParams& p, cudaStream_t stream) {
   if (g_variant == GEMV_MMA_SYNC)
-    gemv_mma_kernel<Bp / 8><<<p.grid, kMmaThreads, stream_smem<Bp>(), stream>>>(p, ctx->dev_err);
+    LMB_CUDA(launch_k(gemv_mma_kernel<Bp / 8>, dim3(p.grid), dim3(kMmaThreads), stream_smem<Bp>(), stream, p, ctx->dev_err));
   else
-    gemv_tc_kernel<Bp><<<p.grid, kTcThreads, stream_smem<Bp>(), stream>>>(p, ctx->dev_err);
+    LMB_CUDA(launch_k(gemv_tc_kernel<Bp>, dim3(p.grid), dim3(kTcThreads), stream_smem<Bp>(), stream, p, ctx->dev_err));
   ctx->launches++;
-  LMB_CUDA(cudaGetLastError());
   return LMB200_OK;
 }
 

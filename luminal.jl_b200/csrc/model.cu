@@ -6,6 +6,7 @@
 #include <type_traits>
 
 #include "model.cuh"
+#include "pdl.cuh"
 
 namespace lmb {
 
@@ -153,6 +154,8 @@ __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(float* __rest
                                                                    float* __restrict__ capture) {
   extern __shared__ __align__(16) float row[];
   __shared__ float red[kNormThreads / 32];
+  pdl_launch_dependents();
+  pdl_wait();
   const int b = blockIdx.x, tid = threadIdx.x;
   const int n4 = n >> 2;
   float4* xr = reinterpret_cast<float4*>(x + (int64_t)b * n);
@@ -211,6 +214,8 @@ __global__ void __launch_bounds__(256) argmax_step_kernel(const float* logits, i
                                                           int* hist, const int* step_ctr, int B) {
   __shared__ float sv[256];
   __shared__ int si[256];
+  pdl_launch_dependents();
+  pdl_wait();
   const int b = blockIdx.x, tid = threadIdx.x;
   const float* row = logits + (int64_t)b * pitch;
   float best = -INFINITY;
@@ -237,6 +242,8 @@ __global__ void __launch_bounds__(256) argmax_step_kernel(const float* logits, i
 }
 
 __global__ void advance_kernel(int* pos, int* step_ctr) {
+  pdl_launch_dependents();
+  pdl_wait();
   *pos += 1;
   *step_ctr += 1;
 }
@@ -620,12 +627,13 @@ int32_t enqueue_step_t(Session* S, cudaStream_t st, bool with_head) {
   for (int l = 0; l < L; ++l) {
     LayerWeights& W = M->layers[l];
     // residual add of the previous MLP (or the embedding gather) + attention RMSNorm
-    if (!(g_debug_skip & 4) || l == 0) add_rmsnorm_kernel<WT><<<B, kNormThreads, norm_smem, st>>>(
-        S->x, l == 0 ? nullptr : S->delta, l == 0 ? S->tokens : nullptr, reinterpret_cast<const WT*>(M->embed),
-        c.vocab, W.attn_norm, reinterpret_cast<WT*>(S->xn), S->Bp, hid, c.rms_eps,
-        (S->capture_on && l > 0) ? S->capture + (int64_t)(l - 1) * B * hid : nullptr);
+    if (!(g_debug_skip & 4) || l == 0)
+      LMB_CUDA(launch_k(add_rmsnorm_kernel<WT>, dim3(B), dim3(kNormThreads), norm_smem, st, S->x,
+                        l == 0 ? (const float*)nullptr : (const float*)S->delta, l == 0 ? (const int*)S->tokens : (const int*)nullptr,
+                        reinterpret_cast<const WT*>(M->embed), c.vocab, (const float*)W.attn_norm,
+                        reinterpret_cast<WT*>(S->xn), S->Bp, hid, c.rms_eps,
+                        (S->capture_on && l > 0) ? S->capture + (int64_t)(l - 1) * B * hid : (float*)nullptr));
     ctx->launches++;
-    LMB_CUDA(cudaGetLastError());
     void* kv_layer = reinterpret_cast<char*>(S->kv) + (int64_t)l * S->kv_layer_stride * M->esz;
     {  // q/k/v projections + RoPE + KV append
       GemvParams p = gemv_params(S, W.wqkv, M->m_qkv, S->p_qkv, S->xn);
@@ -651,11 +659,11 @@ int32_t enqueue_step_t(Session* S, cudaStream_t st, bool with_head) {
       if (!(g_debug_skip & 2)) LMB_TRY(gemv_launch(ctx, dt, p, st));
       if (c.tp_size > 1) LMB_TRY(nccl_allreduce_f32(ctx, S->delta, (int64_t)B * hid, st));
     }
-    if (!(g_debug_skip & 4)) add_rmsnorm_kernel<WT><<<B, kNormThreads, norm_smem, st>>>(S->x, S->delta, nullptr, nullptr, 0, W.ffn_norm,
-                                                               reinterpret_cast<WT*>(S->xn), S->Bp, hid, c.rms_eps,
-                                                               nullptr);
+    if (!(g_debug_skip & 4))
+      LMB_CUDA(launch_k(add_rmsnorm_kernel<WT>, dim3(B), dim3(kNormThreads), norm_smem, st, S->x, (const float*)S->delta,
+                        (const int*)nullptr, (const WT*)nullptr, 0, (const float*)W.ffn_norm,
+                        reinterpret_cast<WT*>(S->xn), S->Bp, hid, c.rms_eps, (float*)nullptr));
     ctx->launches++;
-    LMB_CUDA(cudaGetLastError());
     {  // gate/up + SiLU gate
       GemvParams p = gemv_params(S, W.wgu, M->m_gu, S->p_gu, S->xn);
       p.epi = EPI_SILU_GATE; p.act = S->act; p.n_act = M->inter_l;
@@ -669,22 +677,21 @@ int32_t enqueue_step_t(Session* S, cudaStream_t st, bool with_head) {
     }
   }
   // last residual add (+ final norm); without the head only the add is needed for the capture
-  add_rmsnorm_kernel<WT><<<B, kNormThreads, norm_smem, st>>>(
-      S->x, S->delta, nullptr, nullptr, 0, M->final_norm, with_head ? reinterpret_cast<WT*>(S->xn) : nullptr, S->Bp,
-      hid, c.rms_eps, S->capture_on ? S->capture + (int64_t)(L - 1) * B * hid : nullptr);
+  LMB_CUDA(launch_k(add_rmsnorm_kernel<WT>, dim3(B), dim3(kNormThreads), norm_smem, st, S->x, (const float*)S->delta,
+                    (const int*)nullptr, (const WT*)nullptr, 0, (const float*)M->final_norm,
+                    with_head ? reinterpret_cast<WT*>(S->xn) : (WT*)nullptr, S->Bp, hid, c.rms_eps,
+                    S->capture_on ? S->capture + (int64_t)(L - 1) * B * hid : (float*)nullptr));
   ctx->launches++;
-  LMB_CUDA(cudaGetLastError());
   if (with_head) {
     GemvParams p = gemv_params(S, M->lm_head, M->m_head, S->p_head, S->xn);
     p.epi = EPI_STORE_F32; p.out = S->logits; p.out_pitch = S->logits_pitch;
     if (!(g_debug_skip & 2)) LMB_TRY(gemv_launch(ctx, dt, p, st));
-    argmax_step_kernel<<<B, 256, 0, st>>>(S->logits, S->logits_pitch, c.vocab, S->tokens, S->tok_hist, S->step_ctr, B);
+    LMB_CUDA(launch_k(argmax_step_kernel, dim3(B), dim3(256), 0, st, (const float*)S->logits, S->logits_pitch, c.vocab,
+                      S->tokens, S->tok_hist, (const int*)S->step_ctr, B));
     ctx->launches++;
-    LMB_CUDA(cudaGetLastError());
   }
-  advance_kernel<<<1, 1, 0, st>>>(S->pos, S->step_ctr);
+  LMB_CUDA(launch_k(advance_kernel, dim3(1), dim3(1), 0, st, S->pos, S->step_ctr));
   ctx->launches++;
-  LMB_CUDA(cudaGetLastError());
   return LMB200_OK;
 }
 
