@@ -12,6 +12,8 @@
 
 namespace lmb {
 
+int32_t flash_tc_configure();
+
 static thread_local char g_err[1024] = "";
 
 void set_error(const char* fmt, ...) {
@@ -180,6 +182,7 @@ extern "C" int32_t lmb200_init(int32_t device, lmb200_ctx* out) {
   gemv_set_variant((sel && strcmp(sel, "mma") == 0) ? GEMV_MMA_SYNC : GEMV_TCGEN05);
   int32_t rc = gemv_configure();
   if (rc == LMB200_OK) rc = attn_configure();
+  if (rc == LMB200_OK) rc = flash_tc_configure();
   if (rc == LMB200_OK) rc = step_kernels_configure();
   if (rc != LMB200_OK) { cudaFreeHost(c->dev_err); cudaStreamDestroy(c->own_stream); delete c; return rc; }
   *out = reinterpret_cast<lmb200_ctx>(c);

@@ -6,10 +6,16 @@
 // are staged in shared memory as float32 and every key updates the running (max, sum, output)
 // exactly like the reference's scalar online softmax; causal skips keys j > i.
 #include <math_constants.h>
+#include <stdlib.h>
+#include <string.h>
 
 #include "common.cuh"
 
 namespace lmb {
+// tensor-core kernel (flash_tc.cu)
+bool flash_tc_supported(int64_t D);
+int32_t flash_tc_launch(Ctx* ctx, void* out, const void* q, const void* k, const void* v, int64_t BH, int64_t S, int64_t D,
+                        float scale, int causal);
 namespace {
 
 constexpr int kBQ = 64, kBK = 32, kThreads = 256;
@@ -124,6 +130,12 @@ extern "C" int32_t lmb200_flash_attention(lmb200_ctx h, void* out, const void* q
   LMB_REQUIRE(B >= 1 && H >= 1 && S >= 1 && B * H <= 65535, "flash_attention: bad shape");
   LMB_CUDA(cudaSetDevice(ctx->device));
   if (dtype == LMB200_F32) return launch<float>(ctx, out, q, k, v, B * H, S, D, scale, causal);
-  if (dtype == LMB200_BF16) return launch<__nv_bfloat16>(ctx, out, q, k, v, B * H, S, D, scale, causal);
+  if (dtype == LMB200_BF16) {
+    // LMB200_FLASH_KERNEL=simple keeps the CUDA-core kernel (comparison runs)
+    const char* sel = getenv("LMB200_FLASH_KERNEL");
+    if (flash_tc_supported(D) && !(sel && strcmp(sel, "simple") == 0))
+      return flash_tc_launch(ctx, out, q, k, v, B * H, S, D, scale, causal);
+    return launch<__nv_bfloat16>(ctx, out, q, k, v, B * H, S, D, scale, causal);
+  }
   return fail(LMB200_EINVAL, "flash_attention: dtype %d", dtype);
 }
