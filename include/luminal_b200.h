@@ -185,8 +185,16 @@ typedef struct {
                               GEMV inputs bf16, accumulation and the residual stream float32 */
   int32_t tp_size;         /* tensor-parallel ranks (1 = single GPU) */
   int32_t tp_rank;
-  int32_t reserved[4];
+  int32_t arch;            /* LMB200_ARCH_LLAMA (NN.Llama / NN.Phi3) or LMB200_ARCH_WHISPER_DECODER
+                              (TextDecoder with cached self attention and cross attention,
+                              src/Whisper.jl:449-502, 584-742): LayerNorm, biases, GELU MLP, tied
+                              embedding head, learned positions, no RoPE, n_kv_heads == n_heads,
+                              tp_size 1 */
+  int32_t max_positions;   /* Whisper: rows of embed_positions (448, src/Whisper.jl:206) */
+  int32_t cross_len;       /* Whisper: encoder positions the cross attention reads (1500) */
+  int32_t reserved;
 } lmb200_model_config;
+enum { LMB200_ARCH_LLAMA = 0, LMB200_ARCH_WHISPER_DECODER = 1 };
 
 int32_t lmb200_model_create(lmb200_ctx ctx, const lmb200_model_config* cfg, lmb200_model* model);
 /* Host-only view of the weight re-layout and tensor-parallel sharding (no GPU needed): the extent
@@ -222,6 +230,13 @@ int32_t lmb200_session_fill_kv_random(lmb200_session session, int32_t n_pos, uin
 /* Keep the residual stream after every layer of the next steps (parity tests). */
 int32_t lmb200_session_set_capture(lmb200_session session, int32_t enable);
 int32_t lmb200_session_read_layer_output(lmb200_session session, int32_t layer, float* host);
+
+/* Whisper: the cross-attention keys and values of one decoder layer, as project_cross_kv computes
+ * them (src/Whisper.jl:809-831; K already scaled by head_dim^-0.25): float32 [batch, heads,
+ * cross_len, head_dim] in `layout`.  Stands in for the cross_kv_arrays that decode_step! feeds as
+ * inputs at every step (src/Whisper.jl:770-778): here they are uploaded once. */
+int32_t lmb200_session_set_cross_kv(lmb200_session session, int32_t layer, const float* k_host,
+                                    const float* v_host, int32_t layout);
 
 /* Prompt: tokens [batch, n] int32 row-major, appended at the current position.  logits_out
  * (NULL or [batch, vocab] float32) receives the LAST position's logits.

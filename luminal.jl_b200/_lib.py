@@ -28,7 +28,8 @@ class ModelConfig(C.Structure):
                 ("n_kv_heads", C.c_int32), ("head_dim", C.c_int32), ("intermediate", C.c_int32),
                 ("vocab", C.c_int32), ("rms_eps", C.c_float), ("rope_base", C.c_float),
                 ("dtype", C.c_int32), ("tp_size", C.c_int32), ("tp_rank", C.c_int32),
-                ("reserved", C.c_int32 * 4)]
+                ("arch", C.c_int32), ("max_positions", C.c_int32), ("cross_len", C.c_int32),
+                ("reserved", C.c_int32)]
 
 
 _i32, _i64, _u64, _f32, _vp = C.c_int32, C.c_int64, C.c_uint64, C.c_float, C.c_void_p
@@ -85,6 +86,7 @@ SIGNATURES = {
     "lmb200_session_fill_kv_random": [_u64, _i32, _u64],
     "lmb200_session_set_capture": [_u64, _i32],
     "lmb200_session_read_layer_output": [_u64, _i32, _vp],
+    "lmb200_session_set_cross_kv": [_u64, _i32, _vp, _vp, _i32],
     "lmb200_prefill": [_u64, _vp, _i32, _vp],
     "lmb200_decode_step": [_u64, _vp, _vp, _vp],
     "lmb200_decode_n": [_u64, _vp, _i32, _vp],

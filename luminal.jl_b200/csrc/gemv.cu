@@ -44,6 +44,16 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// gelu(a) = a*0.5*(1 + tanh(0.7978845608*a*(1 + 0.044715*a*a))), tanh(z) = sigmoid(2z)*2 - 1,
+// sigmoid through exp2 -- the reference's decomposition, src/HighLevelOps.jl:153-168
+__device__ __forceinline__ float gelu_ref(float a) {
+  const float inner = (0.7978845608f * a) * (1.0f + (0.044715f * a) * a);
+  const float z = inner * 2.0f;
+  const float sg = 1.0f / (1.0f + exp2f((z * -1.0f) * kInvLn2));
+  const float th = sg * 2.0f + -1.0f;
+  return (a * 0.5f) * (1.0f + th);
+}
+
 // ---------------------------------------------------------------------------------------------
 // Epilogue over a finished tile in shared memory: tile[r * RP + b], r < RPC rows of the CTA's row
 // group starting at logical internal row row0.
@@ -55,7 +65,16 @@ __device__ __forceinline__ void run_epilogue(const GemvParams& p, const float* t
     for (int i = tid; i < RPC * Bp; i += nthreads) {
       const int b = i / RPC, r = i - b * RPC;
       const int row = row0 + r;
-      if (b < p.B && row < p.rows) p.out[(int64_t)b * p.out_pitch + row] = tile[r * RP + b];
+      if (b < p.B && row < p.rows)
+        p.out[(int64_t)b * p.out_pitch + row] = tile[r * RP + b] + (p.bias ? p.bias[row] : 0.f);
+    }
+  } else if (p.epi == EPI_GELU_ACT) {
+    WT* act = reinterpret_cast<WT*>(p.act);
+    for (int i = tid; i < RPC * Bp; i += nthreads) {
+      const int b = i / RPC, r = i - b * RPC;
+      const int row = row0 + r;
+      if (b < p.B && row < p.n_act)
+        act[Layout<WT>::x_offset(b, row, Bp)] = from_f32<WT>(gelu_ref(tile[r * RP + b] + (p.bias ? p.bias[row] : 0.f)));
     }
   } else if (p.epi == EPI_SILU_GATE) {
     WT* act = reinterpret_cast<WT*>(p.act);
@@ -83,15 +102,22 @@ __device__ __forceinline__ void run_epilogue(const GemvParams& p, const float* t
       const int gt = row0 / 16 + m;                  // global 16-row tile
       if (b >= p.B || gt >= p.RB) continue;
       const int hs = gt / tiles_per_head, jj = gt - hs * tiles_per_head;
-      const float v0 = tile[(16 * m + r) * RP + b], v1 = tile[(16 * m + r + 8) * RP + b];
+      float v0 = tile[(16 * m + r) * RP + b], v1 = tile[(16 * m + r + 8) * RP + b];
+      if (p.bias) { v0 += p.bias[gt * 16 + r]; v1 += p.bias[gt * 16 + r + 8]; }
       if (hs < p.Hl + p.KVl) {
         // rows r / r+8 of the tile are the RoPE pair (d0, d0 + D/2)      src/NN.jl:253-303
         const int d0 = 8 * jj + r;
-        const float ang = fpos * p.inv_freq[d0];
-        const float sn = sinf(ang);
-        const float cs = sinf(kHalfPi + ang * -1.0f);   // cos(a) = sin(pi/2 - a)
-        const float o0 = v0 * cs + (v1 * sn) * -1.0f;
-        const float o1 = v0 * sn + v1 * cs;
+        float o0, o1;
+        if (p.rope) {
+          const float ang = fpos * p.inv_freq[d0];
+          const float sn = sinf(ang);
+          const float cs = sinf(kHalfPi + ang * -1.0f);   // cos(a) = sin(pi/2 - a)
+          o0 = v0 * cs + (v1 * sn) * -1.0f;
+          o1 = v0 * sn + v1 * cs;
+        } else {
+          o0 = v0 * p.qk_scale;
+          o1 = v1 * p.qk_scale;
+        }
         if (hs < p.Hl) {
           WT* q = q_out + (int64_t)b * p.q_pitch + hs * D;
           q[d0] = from_f32<WT>(o0);
@@ -451,9 +477,31 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
 // lane (g,t) holds, per batch tile nt, rows g (c0,c1) and g+8 (c2,c3) at columns 8nt+2t, +1 --
 // and rows g / g+8 are exactly the pairs the fused epilogues combine.
 template <int NB>
-__device__ __forceinline__ void fragment_epilogue(const GemvParams& p, const float (&acc)[NB][4], int rb, int g, int t) {
+__device__ __forceinline__ void fragment_epilogue(const GemvParams& p, float (&acc)[NB][4], int rb, int g, int t) {
   constexpr int Bp = 8 * NB;
   typedef Layout<__nv_bfloat16> LY;
+  if (p.bias) {
+    const float b0 = rb * 16 + g < p.rows ? p.bias[rb * 16 + g] : 0.f;
+    const float b1 = rb * 16 + g + 8 < p.rows ? p.bias[rb * 16 + g + 8] : 0.f;
+#pragma unroll
+    for (int nt = 0; nt < NB; ++nt) { acc[nt][0] += b0; acc[nt][1] += b0; acc[nt][2] += b1; acc[nt][3] += b1; }
+  }
+  if (p.epi == EPI_GELU_ACT) {
+    __nv_bfloat16* act = reinterpret_cast<__nv_bfloat16*>(p.act);
+    const int row = rb * 16 + g;
+#pragma unroll
+    for (int nt = 0; nt < NB; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int b = 8 * nt + 2 * t + e;
+        if (b < p.B) {
+          if (row < p.n_act) act[LY::x_offset(b, row, Bp)] = __float2bfloat16_rn(gelu_ref(acc[nt][e]));
+          if (row + 8 < p.n_act) act[LY::x_offset(b, row + 8, Bp)] = __float2bfloat16_rn(gelu_ref(acc[nt][2 + e]));
+        }
+      }
+    }
+    return;
+  }
   if (p.epi == EPI_STORE_F32) {
     const int row = rb * 16 + g;
 #pragma unroll
@@ -495,11 +543,13 @@ __device__ __forceinline__ void fragment_epilogue(const GemvParams& p, const flo
     float sn = 0.f, cs = 1.f;
     const bool rope = hs < p.Hl + p.KVl;
     const int d0 = 8 * jj + g;
-    if (rope) {
+    if (rope && p.rope) {
       // rows g / g+8 of the block are the RoPE pair (d0, d0 + D/2)      src/NN.jl:253-303
       const float ang = (float)pos * p.inv_freq[d0];
       sn = sinf(ang);
       cs = sinf(kHalfPi + ang * -1.0f);   // cos(a) = sin(pi/2 - a)
+    } else if (rope) {
+      cs = p.qk_scale;                    // no rotation: q and k rows are only scaled
     }
 #pragma unroll
     for (int nt = 0; nt < NB; ++nt) {
@@ -701,11 +751,25 @@ template <int N>
 __device__ __forceinline__ void row_epilogue(const GemvParams& p, float (&v)[N], int row) {
   typedef Layout<__nv_bfloat16> LY;
   const int rb = row >> 4, rr = row & 15, g = rr & 7, hi = rr >> 3;
+  if (p.bias) {
+    const float bias = row < p.rows ? p.bias[row] : 0.f;
+#pragma unroll
+    for (int b = 0; b < N; ++b) v[b] += bias;
+  }
   if (p.epi == EPI_STORE_F32) {
     if (row < p.rows) {
 #pragma unroll
       for (int b = 0; b < N; ++b)
         if (b < p.B) p.out[(int64_t)b * p.out_pitch + row] = v[b];
+    }
+    return;
+  }
+  if (p.epi == EPI_GELU_ACT) {
+    if (row < p.n_act) {
+      __nv_bfloat16* act = reinterpret_cast<__nv_bfloat16*>(p.act);
+#pragma unroll
+      for (int b = 0; b < N; ++b)
+        if (b < p.B) act[LY::x_offset(b, row, N)] = __float2bfloat16_rn(gelu_ref(v[b]));
     }
     return;
   }
@@ -738,9 +802,12 @@ __device__ __forceinline__ void row_epilogue(const GemvParams& p, float (&v)[N],
   if (hs < p.Hl + p.KVl) {
     // rows g / g+8 of the block are the RoPE pair (d0, d0 + D/2)      src/NN.jl:253-303
     const int d0 = 8 * jj + g;
-    const float ang = (float)pos * p.inv_freq[d0];
-    const float sn = sinf(ang);
-    const float cs = sinf(kHalfPi + ang * -1.0f);   // cos(a) = sin(pi/2 - a)
+    float sn = 0.f, cs = p.qk_scale;                // no rotation: q and k rows are only scaled
+    if (p.rope) {
+      const float ang = (float)pos * p.inv_freq[d0];
+      sn = sinf(ang);
+      cs = sinf(kHalfPi + ang * -1.0f);             // cos(a) = sin(pi/2 - a)
+    }
     const int d = hi ? d0 + half : d0;
 #pragma unroll
     for (int b = 0; b < N; ++b) {

@@ -9,7 +9,8 @@ namespace lmb {
 enum GemvEpilogue {
   EPI_STORE_F32 = 0,   // out[b, row] = acc                       (o_proj, down_proj, lm_head)
   EPI_SILU_GATE = 1,   // act[b, i] = silu(gate_i) * up_i         (rows interleaved 8 gate / 8 up)
-  EPI_QKV_ROPE = 2     // RoPE on q and k, q -> q_out, k/v appended to the cache at *pos
+  EPI_QKV_ROPE = 2,    // RoPE on q and k (if `rope`), q -> q_out, k/v appended to the cache at *pos
+  EPI_GELU_ACT = 3     // act[b, row] = gelu(acc)                  (Whisper fc1)
 };
 
 // bf16 kernel variants (float32 always runs the register-ring kernel)
@@ -48,6 +49,10 @@ struct GemvParams {
   const float* inv_freq = nullptr;   // [D/2]
   const int* pos = nullptr;          // device scalar: position the new key is written at
   int Hl = 0, KVl = 0, D = 0;
+  int rope = 1;                      // 0: no rotation (Whisper), q and k rows are only scaled
+  float qk_scale = 1.f;              // multiplies q and k rows (Whisper: head_dim^-0.25, src/Whisper.jl:257)
+  // every epilogue: added to the accumulator first, one value per internal row (NULL: none)
+  const float* bias = nullptr;
 };
 
 struct GemvPlan {

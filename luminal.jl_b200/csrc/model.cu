@@ -209,6 +209,91 @@ __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(float* __rest
   }
 }
 
+// Whisper decoder: x <- embedding row + positional row (first layer) or x + delta, then LayerNorm
+// with mean-centering, gain and bias:  xc = x + mean*(-1);  y = (xc * recip(sqrt(mean(xc*xc) + eps))) * w + b
+// (src/NN.jl:138-173, src/HighLevelOps.jl:292-304; positions src/Whisper.jl:699-701).
+template <typename WT>
+__global__ void __launch_bounds__(kNormThreads) add_layernorm_kernel(float* __restrict__ x, const float* __restrict__ delta,
+                                                                     const float* __restrict__ delta_bias,
+                                                                     const int* __restrict__ tokens,
+                                                                     const WT* __restrict__ embed, int vocab,
+                                                                     const float* __restrict__ pos_emb,
+                                                                     const int* __restrict__ pos,
+                                                                     const float* __restrict__ w,
+                                                                     const float* __restrict__ bias, WT* __restrict__ xn,
+                                                                     int Bp, int n, float eps, float* __restrict__ capture) {
+  extern __shared__ __align__(16) float row[];
+  __shared__ float red[kNormThreads / 32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int b = blockIdx.x, tid = threadIdx.x;
+  float* xr = x + (int64_t)b * n;
+  auto block_sum = [&](float v) -> float {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    __syncthreads();
+    if ((tid & 31) == 0) red[tid >> 5] = v;
+    __syncthreads();
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < kNormThreads / 32; ++i) t += red[i];
+    return t;
+  };
+  float s1 = 0.f;
+  if (tokens) {
+    const int tok = tokens[b];
+    const bool ok = tok >= 0 && tok < vocab;
+    const WT* er = embed + (int64_t)(ok ? tok : 0) * n;
+    const float* pr = pos_emb + (int64_t)(*pos) * n;
+    for (int i = tid; i < n; i += kNormThreads) {
+      const float v = (ok ? to_f32(er[i]) : 0.f) + pr[i];
+      xr[i] = v; row[i] = v; s1 += v;
+    }
+  } else {
+    const float* dr = delta ? delta + (int64_t)b * n : nullptr;
+    for (int i = tid; i < n; i += kNormThreads) {
+      float v = xr[i];
+      if (dr) v += dr[i];
+      (void)delta_bias;
+      xr[i] = v; row[i] = v; s1 += v;
+      if (capture) capture[(int64_t)b * n + i] = v;
+    }
+  }
+  const float mean = block_sum(s1) * (1.0f / (float)n);
+  float s2 = 0.f;
+  for (int i = tid; i < n; i += kNormThreads) { const float c = row[i] + mean * -1.0f; row[i] = c; s2 += c * c; }
+  const float var = block_sum(s2) * (1.0f / (float)n);
+  const float inv = 1.0f / sqrtf(var + eps);
+  if (xn)
+    for (int i = tid; i < n; i += kNormThreads)
+      xn[Layout<WT>::x_offset(b, i, Bp)] = from_f32<WT>((row[i] * inv) * w[i] + bias[i]);
+}
+
+// bias of a fused matrix in internal row order: dst[i] = src[logical row] for rows of `slot`
+__global__ void fill_bias_kernel(float* dst, WMap m, const float* src, int slot) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < m.rows; i += gridDim.x * blockDim.x) {
+    int s, lrow, lcol;
+    if (wmap_resolve(m, i, 0, &s, &lrow, &lcol) && s == slot) dst[i] = src[lrow];
+  }
+}
+
+// scatter a logical [B, H, T, D] float32 tensor pair into a tiled cache layer
+template <typename WT>
+__global__ void scatter_kv_kernel(WT* kv, int64_t batch_stride, int64_t head_stride, int B, int H, int T, int D,
+                                  const float* ksrc, const float* vsrc, int colmajor) {
+  const int64_t total = (int64_t)B * H * T * D;
+  for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total; o += (int64_t)gridDim.x * blockDim.x) {
+    const int d = (int)(o % D);
+    const int t = (int)((o / D) % T);
+    const int h = (int)((o / ((int64_t)D * T)) % H);
+    const int b = (int)(o / ((int64_t)D * T * H));
+    const int64_t src = colmajor ? (int64_t)b + (int64_t)B * (h + (int64_t)H * (t + (int64_t)T * d)) : o;
+    WT* base = kv + b * batch_stride + h * head_stride;
+    base[kcache_offset(t, d, D)] = from_f32<WT>(ksrc[src]);
+    base[vcache_offset(t, d, D)] = from_f32<WT>(vsrc[src]);
+  }
+}
+
 // greedy token: first maximum of the logits row; also logs it for the device-resident loop
 __global__ void __launch_bounds__(256) argmax_step_kernel(const float* logits, int pitch, int n, int* tokens,
                                                           int* hist, const int* step_ctr, int B) {
@@ -257,6 +342,8 @@ int32_t step_kernels_configure() {
   if (e && atoi(e) == 0) return LMB200_OK;
 #define LMB_CARVE(KERN) \
   LMB_CUDA(cudaFuncSetAttribute(KERN, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared))
+  LMB_CARVE(add_layernorm_kernel<float>);
+  LMB_CARVE(add_layernorm_kernel<__nv_bfloat16>);
   LMB_CARVE(add_rmsnorm_kernel<float>);
   LMB_CARVE(add_rmsnorm_kernel<__nv_bfloat16>);
   LMB_CARVE(argmax_step_kernel);
@@ -361,6 +448,11 @@ static int32_t derive_model(const lmb200_model_config& c, Model* M) {
   LMB_REQUIRE(c.intermediate % c.tp_size == 0 && (c.intermediate / c.tp_size) % 8 == 0,
               "model_create: intermediate %d / tp %d must be a multiple of 8", c.intermediate, c.tp_size);
   LMB_REQUIRE(c.hidden % 4 == 0, "model_create: hidden %d must be a multiple of 4", c.hidden);
+  LMB_REQUIRE(c.arch == LMB200_ARCH_LLAMA || c.arch == LMB200_ARCH_WHISPER_DECODER, "model_create: arch %d", c.arch);
+  if (c.arch == LMB200_ARCH_WHISPER_DECODER) {
+    LMB_REQUIRE(c.n_kv_heads == c.n_heads && c.tp_size == 1, "model_create: the Whisper decoder has no GQA and no tensor parallelism");
+    LMB_REQUIRE(c.max_positions >= 1 && c.cross_len >= 1, "model_create: Whisper needs max_positions and cross_len");
+  }
   M->cfg = c;
   M->esz = c.dtype == LMB200_BF16 ? 2 : 4;
   M->D = c.head_dim;
@@ -398,6 +490,18 @@ static int32_t derive_model(const lmb200_model_config& c, Model* M) {
   M->m_head.rows = c.vocab; M->m_head.K = c.hidden;
   M->m_head.src_rows[0] = c.vocab; M->m_head.src_cols[0] = c.hidden;
   finish_map(M->m_head);
+  if (c.arch == LMB200_ARCH_WHISPER_DECODER) {
+    // fc1 / fc2 are plain matrices; the cross-attention q projection is a q-only head-ordered matrix
+    M->m_gu.kind = MAP_PLAIN; M->m_gu.rows = c.intermediate; M->m_gu.K = c.hidden;
+    M->m_gu.src_rows[0] = c.intermediate; M->m_gu.src_cols[0] = c.hidden;
+    finish_map(M->m_gu);
+    M->m_down.kind = MAP_PLAIN; M->m_down.rows = c.hidden; M->m_down.K = c.intermediate;
+    M->m_down.src_rows[0] = c.hidden; M->m_down.src_cols[0] = c.intermediate;
+    finish_map(M->m_down);
+    M->m_qc = M->m_qkv;
+    M->m_qc.KVl = 0; M->m_qc.rows = M->Hl * M->D;
+    finish_map(M->m_qc);
+  }
   return LMB200_OK;
 }
 
@@ -457,9 +561,28 @@ extern "C" int32_t lmb200_model_create(lmb200_ctx hctx, const lmb200_model_confi
     alloc((void**)&L.attn_norm, (int64_t)c.hidden * 4);
     alloc((void**)&L.ffn_norm, (int64_t)c.hidden * 4);
   }
+  if (c.arch == LMB200_ARCH_WHISPER_DECODER) {
+    for (auto& L : M->layers) {
+      alloc(&L.wq_cross, tiled_elems(M->m_qc, c.dtype) * M->esz);
+      alloc(&L.wo_cross, tiled_elems(M->m_o, c.dtype) * M->esz);
+      alloc((void**)&L.attn_norm_b, (int64_t)c.hidden * 4);
+      alloc((void**)&L.ffn_norm_b, (int64_t)c.hidden * 4);
+      alloc((void**)&L.cross_norm, (int64_t)c.hidden * 4);
+      alloc((void**)&L.cross_norm_b, (int64_t)c.hidden * 4);
+      alloc((void**)&L.b_qkv, (int64_t)M->m_qkv.rows * 4);
+      alloc((void**)&L.b_o, (int64_t)c.hidden * 4);
+      alloc((void**)&L.b_q_cross, (int64_t)M->m_qc.rows * 4);
+      alloc((void**)&L.b_o_cross, (int64_t)c.hidden * 4);
+      alloc((void**)&L.b_fc1, (int64_t)c.intermediate * 4);
+      alloc((void**)&L.b_fc2, (int64_t)c.hidden * 4);
+    }
+    alloc((void**)&M->final_norm_b, (int64_t)c.hidden * 4);
+    alloc((void**)&M->pos_emb, (int64_t)c.max_positions * c.hidden * 4);
+    alloc(&M->embed_tiled, tiled_elems(M->m_head, c.dtype) * M->esz);
+  }
   alloc(&M->embed, (int64_t)c.vocab * c.hidden * M->esz);
   alloc((void**)&M->final_norm, (int64_t)c.hidden * 4);
-  alloc(&M->lm_head, tiled_elems(M->m_head, c.dtype) * M->esz);
+  if (c.arch == LMB200_ARCH_LLAMA) alloc(&M->lm_head, tiled_elems(M->m_head, c.dtype) * M->esz);
   alloc((void**)&M->inv_freq, (int64_t)(M->D / 2) * 4);
   if (rc != LMB200_OK) { lmb200_model_destroy(reinterpret_cast<lmb200_model>(M)); return rc; }
 
@@ -485,7 +608,11 @@ extern "C" int32_t lmb200_model_destroy(lmb200_model h) {
   for (auto& L : M->layers) {
     cudaFree(L.wqkv); cudaFree(L.wo); cudaFree(L.wgu); cudaFree(L.wdown);
     cudaFree(L.attn_norm); cudaFree(L.ffn_norm);
+    cudaFree(L.wq_cross); cudaFree(L.wo_cross); cudaFree(L.attn_norm_b); cudaFree(L.ffn_norm_b);
+    cudaFree(L.cross_norm); cudaFree(L.cross_norm_b); cudaFree(L.b_qkv); cudaFree(L.b_o); cudaFree(L.b_q_cross);
+    cudaFree(L.b_o_cross); cudaFree(L.b_fc1); cudaFree(L.b_fc2);
   }
+  cudaFree(M->final_norm_b); cudaFree(M->pos_emb); cudaFree(M->embed_tiled);
   cudaFree(M->embed); cudaFree(M->final_norm); cudaFree(M->lm_head); cudaFree(M->inv_freq);
   M->magic = 0;
   delete M;
@@ -502,6 +629,7 @@ extern "C" int32_t lmb200_model_weight_bytes(lmb200_model h, int64_t* bytes) {
 extern "C" int32_t lmb200_model_init_random(lmb200_model h, uint64_t seed, float sigma) {
   Model* M = model_from(h);
   if (!M) return LMB200_EINVAL;
+  LMB_REQUIRE(M->cfg.arch == LMB200_ARCH_LLAMA, "init_random: only for Llama-shaped models; set Whisper weights by name");
   Ctx* ctx = M->ctx;
   LMB_CUDA(cudaSetDevice(ctx->device));
   const float scale = sigma / 131072.0f;
@@ -552,8 +680,52 @@ extern "C" int32_t lmb200_model_set_weight(lmb200_model h, const char* name, con
   const WMap* map = nullptr;
   int slot = 0;
   int64_t rows = 0, cols = 0;
-  bool plain_f32 = false, plain_embed = false;
-  if (n == "model.embed_tokens.weight") { dst = M->embed; rows = c.vocab; cols = c.hidden; plain_embed = true; }
+  bool plain_f32 = false, plain_embed = false, is_bias = false;
+  void* also_tiled = nullptr;          // Whisper: the embedding doubles as the head matrix
+  if (c.arch == LMB200_ARCH_WHISPER_DECODER) {
+    // registry names of TextDecoder (src/Whisper.jl:464-481, 423-431)
+    const int hid = c.hidden;
+    if (n.rfind("model.encoder.", 0) == 0) return LMB200_OK;            // the encoder is not part of this model
+    if (n == "model.decoder.embed_tokens.weight") { dst = M->embed; rows = c.vocab; cols = hid; plain_embed = true; also_tiled = M->embed_tiled; }
+    else if (n == "model.decoder.embed_positions.weight") { dst = M->pos_emb; rows = c.max_positions; cols = hid; plain_f32 = true; }
+    else if (n == "model.decoder.layer_norm.weight") { dst = M->final_norm; rows = 1; cols = hid; plain_f32 = true; }
+    else if (n == "model.decoder.layer_norm.bias") { dst = M->final_norm_b; rows = 1; cols = hid; plain_f32 = true; }
+    else {
+      int layer = -1, used = 0;
+      if (sscanf(name, "model.decoder.layers.%d.%n", &layer, &used) < 1 || layer < 0 || layer >= c.n_layers)
+        return fail(LMB200_EINVAL, "set_weight: unknown tensor '%s'", name);
+      const std::string tail(name + used);
+      LayerWeights& L = M->layers[layer];
+      auto vec = [&](float* d, int len) { dst = d; rows = 1; cols = len; plain_f32 = true; };
+      auto mat = [&](void* d, const WMap* m, int sl, int r_, int c_) { dst = d; map = m; slot = sl; rows = r_; cols = c_; };
+      auto bia = [&](float* d, const WMap* m, int sl, int len) { dst = d; map = m; slot = sl; rows = 1; cols = len; is_bias = true; };
+      if (tail == "self_attn.q_proj.weight") mat(L.wqkv, &M->m_qkv, 0, hid, hid);
+      else if (tail == "self_attn.k_proj.weight") mat(L.wqkv, &M->m_qkv, 1, hid, hid);
+      else if (tail == "self_attn.v_proj.weight") mat(L.wqkv, &M->m_qkv, 2, hid, hid);
+      else if (tail == "self_attn.q_proj.bias") bia(L.b_qkv, &M->m_qkv, 0, hid);
+      else if (tail == "self_attn.v_proj.bias") bia(L.b_qkv, &M->m_qkv, 2, hid);
+      else if (tail == "self_attn.out_proj.weight") mat(L.wo, &M->m_o, 0, hid, hid);
+      else if (tail == "self_attn.out_proj.bias") vec(L.b_o, hid);
+      else if (tail == "self_attn_layer_norm.weight") vec(L.attn_norm, hid);
+      else if (tail == "self_attn_layer_norm.bias") vec(L.attn_norm_b, hid);
+      else if (tail == "encoder_attn.q_proj.weight") mat(L.wq_cross, &M->m_qc, 0, hid, hid);
+      else if (tail == "encoder_attn.q_proj.bias") bia(L.b_q_cross, &M->m_qc, 0, hid);
+      else if (tail == "encoder_attn.out_proj.weight") mat(L.wo_cross, &M->m_o, 0, hid, hid);
+      else if (tail == "encoder_attn.out_proj.bias") vec(L.b_o_cross, hid);
+      // k_proj / v_proj of the cross attention act on the encoder output once (project_cross_kv);
+      // their result is handed to the session with lmb200_session_set_cross_kv
+      else if (tail.rfind("encoder_attn.k_proj", 0) == 0 || tail.rfind("encoder_attn.v_proj", 0) == 0) return LMB200_OK;
+      else if (tail == "encoder_attn_layer_norm.weight") vec(L.cross_norm, hid);
+      else if (tail == "encoder_attn_layer_norm.bias") vec(L.cross_norm_b, hid);
+      else if (tail == "fc1.weight") mat(L.wgu, &M->m_gu, 0, c.intermediate, hid);
+      else if (tail == "fc1.bias") vec(L.b_fc1, c.intermediate);
+      else if (tail == "fc2.weight") mat(L.wdown, &M->m_down, 0, hid, c.intermediate);
+      else if (tail == "fc2.bias") vec(L.b_fc2, hid);
+      else if (tail == "final_layer_norm.weight") vec(L.ffn_norm, hid);
+      else if (tail == "final_layer_norm.bias") vec(L.ffn_norm_b, hid);
+      else return fail(LMB200_EINVAL, "set_weight: unknown tensor '%s'", name);
+    }
+  } else if (n == "model.embed_tokens.weight") { dst = M->embed; rows = c.vocab; cols = c.hidden; plain_embed = true; }
   else if (n == "model.norm.weight") { dst = M->final_norm; rows = 1; cols = c.hidden; plain_f32 = true; }
   else if (n == "lm_head.weight") { dst = M->lm_head; map = &M->m_head; rows = c.vocab; cols = c.hidden; }
   else {
@@ -582,11 +754,21 @@ extern "C" int32_t lmb200_model_set_weight(lmb200_model h, const char* name, con
     if (cudaMemcpyAsync(stage, host, (size_t)bytes, cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess) {
       rc = fail(LMB200_ECUDA, "set_weight: upload failed"); break;
     }
-    if (plain_f32) {
-      rc = fill_plain<float>(ctx, dst, rows, cols, 0, stage, 0, 0.f, 0.f);
+    if (is_bias) {
+      fill_bias_kernel<<<fill_grid(map->rows), 256, 0, ctx->stream>>>(reinterpret_cast<float*>(dst), *map, stage, slot);
+      ctx->launches++;
+      if (cudaGetLastError() != cudaSuccess) rc = fail(LMB200_ECUDA, "set_weight: bias fill failed");
+    } else if (plain_f32) {
+      rc = fill_plain<float>(ctx, dst, rows, cols, 0, stage, rows > 1 ? layout : 0, 0.f, 0.f);
     } else if (plain_embed) {
       rc = c.dtype == LMB200_BF16 ? fill_plain<__nv_bfloat16>(ctx, dst, rows, cols, 0, stage, layout, 0.f, 0.f)
                                   : fill_plain<float>(ctx, dst, rows, cols, 0, stage, layout, 0.f, 0.f);
+      if (rc == LMB200_OK && also_tiled) {
+        FillSrc f{};
+        f.only_slot = 0; f.colmajor = layout; f.scale = 0.f;
+        f.src[0] = stage; f.src[1] = f.src[2] = nullptr;
+        rc = fill_tiled_dt(M, also_tiled, M->m_head, f);
+      }
     } else {
       FillSrc f{};
       f.only_slot = slot; f.colmajor = layout; f.scale = 0.f;
@@ -695,7 +877,103 @@ int32_t enqueue_step_t(Session* S, cudaStream_t st, bool with_head) {
   return LMB200_OK;
 }
 
+// One decode step of the Whisper TextDecoder with cached self attention and cross attention
+// (build_decode_step!, src/Whisper.jl:679-742): per layer LayerNorm -> q/k/v (bias, head_dim^-0.25
+// on q and k, no RoPE) + cache append -> attention over [0, pos] -> out_proj -> LayerNorm ->
+// cross q -> attention over the fixed cross K/V -> out_proj -> LayerNorm -> fc1 + GELU -> fc2;
+// then the final LayerNorm and the tied-embedding head.
+template <typename WT>
+int32_t enqueue_whisper_step_t(Session* S, cudaStream_t st, bool with_head) {
+  Model* M = S->m;
+  Ctx* ctx = M->ctx;
+  const lmb200_model_config& c = M->cfg;
+  const int dt = c.dtype;
+  const int B = S->B, hid = c.hidden, L = c.n_layers;
+  const size_t norm_smem = (size_t)hid * sizeof(float);
+  const float qk_scale = powf((float)hid / (float)c.n_heads, -0.25f);
+  auto norm = [&](const float* delta, bool first, const float* w, const float* b, bool write_xn, float* cap) -> int32_t {
+    LMB_CUDA(launch_k(add_layernorm_kernel<WT>, dim3(B), dim3(kNormThreads), norm_smem, st, S->x, delta,
+                      (const float*)nullptr, first ? (const int*)S->tokens : (const int*)nullptr,
+                      reinterpret_cast<const WT*>(M->embed), c.vocab, (const float*)M->pos_emb, (const int*)S->pos, w, b,
+                      write_xn ? reinterpret_cast<WT*>(S->xn) : (WT*)nullptr, S->Bp, hid, c.rms_eps, cap));
+    ctx->launches++;
+    return LMB200_OK;
+  };
+  auto attention = [&](void* kv_layer, int64_t bs, int64_t hs, const int* pos, int T_fixed, int kpc, int nsplit) -> int32_t {
+    AttnParams a;
+    a.q = S->qbuf; a.q_pitch = S->q_pitch; a.kv_layer = kv_layer; a.kv_batch_stride = bs; a.kv_head_stride = hs;
+    a.B = B; a.KVl = M->KVl; a.G = 1; a.D = M->D; a.pos = pos; a.T_fixed = T_fixed;
+    a.keys_per_cta = kpc; a.nsplit = nsplit;
+    a.scale = 1.0f;                      // the scale is already in q and k
+    a.part_o = S->part_o; a.part_ml = S->part_ml; a.out = S->attn_out; a.out_tiled_bp = S->Bp;
+    return attn_decode_launch(ctx, dt, a, st);
+  };
+  for (int l = 0; l < L; ++l) {
+    LayerWeights& W = M->layers[l];
+    LMB_TRY(norm(l == 0 ? nullptr : S->delta, l == 0, W.attn_norm, W.attn_norm_b, true,
+                 (S->capture_on && l > 0) ? S->capture + (int64_t)(l - 1) * B * hid : nullptr));
+    void* kv_layer = reinterpret_cast<char*>(S->kv) + (int64_t)l * S->kv_layer_stride * M->esz;
+    {
+      GemvParams p = gemv_params(S, W.wqkv, M->m_qkv, S->p_qkv, S->xn);
+      p.epi = EPI_QKV_ROPE; p.rope = 0; p.qk_scale = qk_scale; p.bias = W.b_qkv;
+      p.q_out = S->qbuf; p.q_pitch = S->q_pitch;
+      p.kv_layer = kv_layer; p.kv_batch_stride = S->kv_batch_stride; p.kv_head_stride = S->kv_head_stride;
+      p.inv_freq = M->inv_freq; p.pos = S->pos; p.Hl = M->Hl; p.KVl = M->KVl; p.D = M->D;
+      LMB_TRY(gemv_launch(ctx, dt, p, st));
+    }
+    LMB_TRY(attention(kv_layer, S->kv_batch_stride, S->kv_head_stride, S->pos, 0, S->keys_per_cta, S->nsplit));
+    {
+      GemvParams p = gemv_params(S, W.wo, M->m_o, S->p_o, S->attn_out);
+      p.epi = EPI_STORE_F32; p.out = S->delta; p.out_pitch = hid; p.bias = W.b_o;
+      LMB_TRY(gemv_launch(ctx, dt, p, st));
+    }
+    LMB_TRY(norm(S->delta, false, W.cross_norm, W.cross_norm_b, true, nullptr));
+    {  // cross-attention query: q rows only, nothing is appended to a cache
+      GemvParams p = gemv_params(S, W.wq_cross, M->m_qc, S->p_qc, S->xn);
+      p.epi = EPI_QKV_ROPE; p.rope = 0; p.qk_scale = qk_scale; p.bias = W.b_q_cross;
+      p.q_out = S->qbuf; p.q_pitch = S->q_pitch;
+      p.kv_layer = nullptr; p.inv_freq = M->inv_freq; p.pos = S->pos; p.Hl = M->Hl; p.KVl = 0; p.D = M->D;
+      LMB_TRY(gemv_launch(ctx, dt, p, st));
+    }
+    void* cross_layer = reinterpret_cast<char*>(S->cross_kv) + (int64_t)l * S->cross_layer_stride * M->esz;
+    LMB_TRY(attention(cross_layer, S->cross_batch_stride, S->cross_head_stride, nullptr, c.cross_len,
+                      S->cross_keys_per_cta, S->cross_nsplit));
+    {
+      GemvParams p = gemv_params(S, W.wo_cross, M->m_o, S->p_o, S->attn_out);
+      p.epi = EPI_STORE_F32; p.out = S->delta; p.out_pitch = hid; p.bias = W.b_o_cross;
+      LMB_TRY(gemv_launch(ctx, dt, p, st));
+    }
+    LMB_TRY(norm(S->delta, false, W.ffn_norm, W.ffn_norm_b, true, nullptr));
+    {
+      GemvParams p = gemv_params(S, W.wgu, M->m_gu, S->p_gu, S->xn);
+      p.epi = EPI_GELU_ACT; p.act = S->act; p.n_act = c.intermediate; p.bias = W.b_fc1;
+      LMB_TRY(gemv_launch(ctx, dt, p, st));
+    }
+    {
+      GemvParams p = gemv_params(S, W.wdown, M->m_down, S->p_down, S->act);
+      p.epi = EPI_STORE_F32; p.out = S->delta; p.out_pitch = hid; p.bias = W.b_fc2;
+      LMB_TRY(gemv_launch(ctx, dt, p, st));
+    }
+  }
+  LMB_TRY(norm(S->delta, false, M->final_norm, M->final_norm_b, with_head,
+               S->capture_on ? S->capture + (int64_t)(L - 1) * B * hid : nullptr));
+  if (with_head) {
+    GemvParams p = gemv_params(S, M->embed_tiled, M->m_head, S->p_head, S->xn);     // logits = out * E^T
+    p.epi = EPI_STORE_F32; p.out = S->logits; p.out_pitch = S->logits_pitch;
+    LMB_TRY(gemv_launch(ctx, dt, p, st));
+    LMB_CUDA(launch_k(argmax_step_kernel, dim3(B), dim3(256), 0, st, (const float*)S->logits, S->logits_pitch, c.vocab,
+                      S->tokens, S->tok_hist, (const int*)S->step_ctr, B));
+    ctx->launches++;
+  }
+  LMB_CUDA(launch_k(advance_kernel, dim3(1), dim3(1), 0, st, S->pos, S->step_ctr));
+  ctx->launches++;
+  return LMB200_OK;
+}
+
 int32_t enqueue_step(Session* S, cudaStream_t st, bool with_head) {
+  if (S->m->cfg.arch == LMB200_ARCH_WHISPER_DECODER)
+    return S->m->cfg.dtype == LMB200_BF16 ? enqueue_whisper_step_t<__nv_bfloat16>(S, st, with_head)
+                                          : enqueue_whisper_step_t<float>(S, st, with_head);
   return S->m->cfg.dtype == LMB200_BF16 ? enqueue_step_t<__nv_bfloat16>(S, st, with_head)
                                         : enqueue_step_t<float>(S, st, with_head);
 }
@@ -758,6 +1036,10 @@ extern "C" int32_t lmb200_session_create(lmb200_model hm, int32_t batch, int32_t
   Ctx* ctx = M->ctx;
   LMB_CUDA(cudaSetDevice(ctx->device));
   const lmb200_model_config& c = M->cfg;
+  const bool whisper = c.arch == LMB200_ARCH_WHISPER_DECODER;
+  if (whisper)
+    LMB_REQUIRE(max_ctx <= c.max_positions, "session_create: max_ctx %d exceeds the %d learned positions", max_ctx,
+                c.max_positions);
   Session* S = new Session();
   S->m = M; S->B = batch; S->max_ctx = max_ctx;
   S->cap = (int)round_up(max_ctx, 64);
@@ -779,10 +1061,22 @@ extern "C" int32_t lmb200_session_create(lmb200_model hm, int32_t batch, int32_t
   plan(S->p_head, M->m_head);
   int64_t po, pml;
   attn_plan(ctx, batch, M->KVl, M->G, M->D, S->cap, &S->keys_per_cta, &S->nsplit, &po, &pml);
+  if (whisper) {
+    plan(S->p_qc, M->m_qc);
+    S->cross_cap = (int)round_up(c.cross_len, 64);
+    S->cross_head_stride = (int64_t)(S->cross_cap / 16) * kv_block_elems(M->D);
+    S->cross_batch_stride = S->cross_head_stride * M->KVl;
+    S->cross_layer_stride = S->cross_batch_stride * batch;
+    int64_t po2, pml2;
+    attn_plan(ctx, batch, M->KVl, M->G, M->D, S->cross_cap, &S->cross_keys_per_cta, &S->cross_nsplit, &po2, &pml2);
+    if (po2 > po) po = po2;
+    if (pml2 > pml) pml = pml2;
+  }
 
   int32_t rc = LMB200_OK;
   auto alloc = [&](void** p, int64_t bytes) { if (rc == LMB200_OK) rc = dmalloc(p, bytes, true, ctx->stream); };
   alloc(&S->kv, S->kv_layer_stride * c.n_layers * M->esz);
+  if (whisper) alloc(&S->cross_kv, S->cross_layer_stride * c.n_layers * M->esz);
   alloc((void**)&S->x, (int64_t)batch * c.hidden * 4);
   alloc((void**)&S->delta, (int64_t)batch * c.hidden * 4);
   alloc((void**)&S->logits, (int64_t)batch * S->logits_pitch * 4);
@@ -814,6 +1108,7 @@ extern "C" int32_t lmb200_session_destroy(lmb200_session h) {
   cudaSetDevice(S->m->ctx->device);
   cudaStreamSynchronize(S->m->ctx->stream);
   drop_graphs(S);
+  cudaFree(S->cross_kv);
   cudaFree(S->kv); cudaFree(S->x); cudaFree(S->delta); cudaFree(S->logits); cudaFree(S->xn); cudaFree(S->qbuf);
   cudaFree(S->attn_out); cudaFree(S->act); cudaFree(S->tokens); cudaFree(S->pos); cudaFree(S->step_ctr);
   cudaFree(S->tok_hist); cudaFree(S->prompt); cudaFree(S->gemv_partials); cudaFree(S->gemv_counters);
@@ -852,6 +1147,43 @@ extern "C" int32_t lmb200_session_set_position(lmb200_session h, int32_t pos) {
   LMB_CUDA(cudaStreamSynchronize(ctx->stream));
   S->host_pos = pos;
   return LMB200_OK;
+}
+
+extern "C" int32_t lmb200_session_set_cross_kv(lmb200_session h, int32_t layer, const float* k_host, const float* v_host,
+                                               int32_t layout) {
+  Session* S = session_from(h);
+  if (!S) return LMB200_EINVAL;
+  Model* M = S->m;
+  const lmb200_model_config& c = M->cfg;
+  LMB_REQUIRE(c.arch == LMB200_ARCH_WHISPER_DECODER && S->cross_kv, "set_cross_kv: not a Whisper decoder session");
+  LMB_REQUIRE(k_host && v_host, "set_cross_kv: null pointer");
+  LMB_REQUIRE(layer >= 0 && layer < c.n_layers, "set_cross_kv: layer %d", layer);
+  LMB_REQUIRE(layout == LMB200_ROWMAJOR || layout == LMB200_COLMAJOR, "set_cross_kv: layout %d", layout);
+  Ctx* ctx = M->ctx;
+  LMB_CUDA(cudaSetDevice(ctx->device));
+  const int64_t n = (int64_t)S->B * M->KVl * c.cross_len * M->D;
+  float *ks = nullptr, *vs = nullptr;
+  LMB_TRY(dmalloc((void**)&ks, n * 4, false, ctx->stream));
+  int32_t rc = dmalloc((void**)&vs, n * 4, false, ctx->stream);
+  if (rc == LMB200_OK) {
+    cudaMemcpyAsync(ks, k_host, (size_t)n * 4, cudaMemcpyHostToDevice, ctx->stream);
+    cudaMemcpyAsync(vs, v_host, (size_t)n * 4, cudaMemcpyHostToDevice, ctx->stream);
+    void* dst = reinterpret_cast<char*>(S->cross_kv) + (int64_t)layer * S->cross_layer_stride * M->esz;
+    if (c.dtype == LMB200_BF16)
+      scatter_kv_kernel<__nv_bfloat16><<<fill_grid(n), 256, 0, ctx->stream>>>(
+          reinterpret_cast<__nv_bfloat16*>(dst), S->cross_batch_stride, S->cross_head_stride, S->B, M->KVl, c.cross_len,
+          M->D, ks, vs, layout);
+    else
+      scatter_kv_kernel<float><<<fill_grid(n), 256, 0, ctx->stream>>>(reinterpret_cast<float*>(dst), S->cross_batch_stride,
+                                                                      S->cross_head_stride, S->B, M->KVl, c.cross_len,
+                                                                      M->D, ks, vs, layout);
+    ctx->launches++;
+    if (cudaGetLastError() != cudaSuccess || cudaStreamSynchronize(ctx->stream) != cudaSuccess)
+      rc = fail(LMB200_ECUDA, "set_cross_kv: upload failed");
+  }
+  cudaStreamSynchronize(ctx->stream);
+  cudaFree(ks); cudaFree(vs);
+  return rc;
 }
 
 extern "C" int32_t lmb200_session_fill_kv_random(lmb200_session h, int32_t n_pos, uint64_t seed) {

@@ -34,6 +34,19 @@ struct LayerWeights {
   void* wdown = nullptr;
   float* attn_norm = nullptr;
   float* ffn_norm = nullptr;
+  // Whisper decoder layers only
+  void* wq_cross = nullptr;      // encoder_attn.q_proj
+  void* wo_cross = nullptr;      // encoder_attn.out_proj
+  float* attn_norm_b = nullptr;  // LayerNorm biases
+  float* ffn_norm_b = nullptr;
+  float* cross_norm = nullptr;
+  float* cross_norm_b = nullptr;
+  float* b_qkv = nullptr;        // biases in internal row order (k rows zero)
+  float* b_o = nullptr;
+  float* b_q_cross = nullptr;
+  float* b_o_cross = nullptr;
+  float* b_fc1 = nullptr;
+  float* b_fc2 = nullptr;
 };
 
 struct Model {
@@ -43,6 +56,10 @@ struct Model {
   int esz = 4;
   int Hl = 0, KVl = 0, G = 0, D = 0, kv_off = 0, inter_l = 0, inter_off = 0;
   WMap m_qkv, m_o, m_gu, m_down, m_head;
+  WMap m_qc;                    // Whisper: cross-attention q projection (q rows only)
+  float* final_norm_b = nullptr;
+  float* pos_emb = nullptr;     // Whisper: [max_positions, hidden] float32
+  void* embed_tiled = nullptr;  // Whisper: the embedding table in GEMV layout (tied head)
   std::vector<LayerWeights> layers;
   void* embed = nullptr;        // [vocab, hidden] row-major, model dtype
   float* final_norm = nullptr;
@@ -81,7 +98,12 @@ struct Session {
   float* part_o = nullptr;
   float* part_ml = nullptr;
   int keys_per_cta = 0, nsplit = 0;
-  GemvPlan p_qkv, p_o, p_gu, p_down, p_head;
+  GemvPlan p_qkv, p_o, p_gu, p_down, p_head, p_qc;
+  // Whisper: cross-attention cache [L][B][H][cross_cap/16][32*D] and its split plan
+  void* cross_kv = nullptr;
+  int cross_cap = 0;
+  int64_t cross_head_stride = 0, cross_batch_stride = 0, cross_layer_stride = 0;
+  int cross_keys_per_cta = 0, cross_nsplit = 0;
   float* capture = nullptr;     // [L][B][hidden] when enabled
   bool capture_on = false;
   cudaGraphExec_t graph_full = nullptr;

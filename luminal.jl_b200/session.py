@@ -22,12 +22,14 @@ def _dtype_code(dtype):
 
 class Model:
     def __init__(self, device, *, n_layers, hidden, n_heads, n_kv_heads, intermediate, vocab,
-                 eps=1e-5, rope_base=10000.0, dtype="f32", tp_size=1, tp_rank=0):
+                 eps=1e-5, rope_base=10000.0, dtype="f32", tp_size=1, tp_rank=0, arch=0, max_positions=0,
+                 cross_len=0):
         self.device = device
         self.cfg = ModelConfig(n_layers=n_layers, hidden=hidden, n_heads=n_heads, n_kv_heads=n_kv_heads,
                                head_dim=hidden // n_heads, intermediate=intermediate, vocab=vocab,
                                rms_eps=eps, rope_base=rope_base, dtype=_dtype_code(dtype),
-                               tp_size=tp_size, tp_rank=tp_rank)
+                               tp_size=tp_size, tp_rank=tp_rank, arch=arch, max_positions=max_positions,
+                               cross_len=cross_len)
         h = C.c_uint64(0)
         _lib.call("lmb200_model_create", device.handle, C.byref(self.cfg), C.byref(h))
         self.handle = h
@@ -55,6 +57,15 @@ class Model:
             self.handle = C.c_uint64(0)
 
 
+def WhisperDecoderModel(device, *, d_model, heads, layers, ffn, vocab, max_positions, cross_len, dtype="f32"):
+    """The Whisper TextDecoder (src/Whisper.jl:449-502) for cached decoding: LayerNorm, biases, GELU
+    MLP, learned positions, tied-embedding head.  Weights by their registry names
+    (model.decoder.*); the cross K/V of every layer go to Session.set_cross_kv."""
+    return Model(device, n_layers=layers, hidden=d_model, n_heads=heads, n_kv_heads=heads, intermediate=ffn,
+                 vocab=vocab, eps=1e-5, rope_base=10000.0, dtype=dtype, arch=1, max_positions=max_positions,
+                 cross_len=cross_len)
+
+
 class Session:
     def __init__(self, model, batch, max_ctx):
         self.model, self.batch, self.max_ctx = model, int(batch), int(max_ctx)
@@ -79,6 +90,17 @@ class Session:
 
     def fill_kv_random(self, n_pos, seed=1234):
         _lib.call("lmb200_session_fill_kv_random", self.handle, int(n_pos), int(seed))
+
+    def set_cross_kv(self, layer, k, v, layout=ROWMAJOR):
+        """Whisper: cross-attention K (already scaled) and V of one layer, [batch, heads, T, head_dim]."""
+        k = np.asarray(k, dtype=np.float32)
+        v = np.asarray(v, dtype=np.float32)
+        if layout == COLMAJOR:
+            k, v = np.asfortranarray(k), np.asfortranarray(v)
+        else:
+            k, v = np.ascontiguousarray(k), np.ascontiguousarray(v)
+        _lib.call("lmb200_session_set_cross_kv", self.handle, int(layer), k.ctypes.data_as(C.c_void_p),
+                  v.ctypes.data_as(C.c_void_p), layout)
 
     def set_capture(self, enable=True):
         _lib.call("lmb200_session_set_capture", self.handle, int(bool(enable)))
@@ -173,7 +195,8 @@ def _step_logits(session, tokens):
     return nxt, logits
 
 
-__all__ = ["Model", "Session", "greedy_generate", "decode_attention_noalloc", "shard_layout", "linear_gemv"]
+__all__ = ["Model", "Session", "greedy_generate", "decode_attention_noalloc", "shard_layout", "linear_gemv",
+           "WhisperDecoderModel"]
 
 
 def shard_layout(cfg_kwargs, matrix, tp_size=1, tp_rank=0):
