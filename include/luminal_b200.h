@@ -131,6 +131,10 @@ int32_t lmb200_pad(lmb200_ctx ctx, float* out_dptr, const float* in_dptr, int32_
  * src/Execution.jl:262-264, 580-611 */
 int32_t lmb200_gather(lmb200_ctx ctx, float* out_dptr, const float* table, int64_t vocab,
                       int64_t dim, const float* ids, int64_t n_ids);
+/* Unfold of the last axis (Conv1D's im2col): in [rows, length] -> out [rows, O, kernel] with
+ * O = (length - dilation*(kernel-1) - 1) / stride + 1.  src/Execution.jl:481-550 */
+int32_t lmb200_unfold1d(lmb200_ctx ctx, float* out_dptr, const float* in_dptr, int64_t rows,
+                        int64_t length, int64_t kernel, int64_t stride, int64_t dilation);
 /* CumSum along the last axis (used by arange).  src/Execution.jl:265-266, 612-613 */
 int32_t lmb200_cumsum_last(lmb200_ctx ctx, float* out_dptr, const float* in_dptr,
                            int64_t rows, int64_t n);

@@ -64,6 +64,7 @@ SIGNATURES = {
     "lmb200_pad": [_u64, _vp, _vp, _i32, _pi64, _pi64, _pi64],
     "lmb200_gather": [_u64, _vp, _vp, _i64, _i64, _vp, _i64],
     "lmb200_cumsum_last": [_u64, _vp, _vp, _i64, _i64],
+    "lmb200_unfold1d": [_u64, _vp, _vp, _i64, _i64, _i64, _i64, _i64],
     "lmb200_flash_attention": [_u64, _vp, _vp, _vp, _vp, _i32, _i64, _i64, _i64, _i64, _f32, _i32],
     "lmb200_rmsnorm_scale": [_u64, _vp, _vp, _vp, _i64, _i64, _f32],
     "lmb200_layernorm": [_u64, _vp, _vp, _vp, _vp, _i64, _i64, _f32],

@@ -157,6 +157,16 @@ __global__ void gather_kernel(float* out, const float* table, int64_t vocab, int
   }
 }
 
+// im2col of the last axis: out[bc, o, k] = a[bc, o*stride + k*dilation]   (src/Execution.jl:481-504)
+__global__ void unfold1d_kernel(float* out, const float* a, int64_t BC, int64_t Lin, int64_t O, int64_t K, int64_t stride,
+                                int64_t dilation) {
+  const int64_t total = BC * O * K;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t k = i % K, o = (i / K) % O, bc = i / (K * O);
+    out[i] = a[bc * Lin + o * stride + k * dilation];
+  }
+}
+
 __global__ void cumsum_kernel(float* out, const float* in, int64_t rows, int64_t n) {
   const int64_t r = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
   if (r >= rows) return;
@@ -486,6 +496,17 @@ extern "C" int32_t lmb200_gather(lmb200_ctx h, float* out, const float* table, i
   CTX_OR_FAIL();
   LMB_REQUIRE(out && table && ids && vocab >= 1 && dim >= 1 && n_ids >= 1, "gather: bad argument");
   gather_kernel<<<grid_for(n_ids * dim), 256, 0, ctx->stream>>>(out, table, vocab, dim, ids, n_ids);
+  LAUNCHED();
+  return LMB200_OK;
+}
+
+extern "C" int32_t lmb200_unfold1d(lmb200_ctx h, float* out, const float* in, int64_t rows, int64_t length, int64_t kernel,
+                                   int64_t stride, int64_t dilation) {
+  CTX_OR_FAIL();
+  LMB_REQUIRE(out && in && rows >= 1 && kernel >= 1 && stride >= 1 && dilation >= 1, "unfold: bad argument");
+  const int64_t O = (length - dilation * (kernel - 1) - 1) / stride + 1;
+  LMB_REQUIRE(O >= 1, "unfold: length %lld too short for kernel %lld", (long long)length, (long long)kernel);
+  unfold1d_kernel<<<grid_for(rows * O * kernel), 256, 0, ctx->stream>>>(out, in, rows, length, O, kernel, stride, dilation);
   LAUNCHED();
   return LMB200_OK;
 }

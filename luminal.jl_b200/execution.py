@@ -73,6 +73,10 @@ def run_op(dev, op, out, ins):
         a = ins[0]
         _lib.call("lmb200_pad", h, _p(out), _p(a), len(a.shape), _lib.dims(a.shape),
                   _lib.dims([l for l, _ in op.padding]), _lib.dims([r for _, r in op.padding]))
+    elif t is G.Unfold:
+        a = ins[0]
+        _lib.call("lmb200_unfold1d", h, _p(out), _p(a), int(np.prod(a.shape[:-1])), a.shape[-1], op.kernel_shape[0],
+                  op.stride_shape[0], op.dilation_shape[0])
     elif t is G.FlashAttentionOp:
         q, k, v = ins
         B, H, S, D = q.shape

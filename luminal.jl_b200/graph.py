@@ -66,6 +66,13 @@ class Pad(Op):
 
 
 @dataclass(frozen=True)
+class Unfold(Op):
+    kernel_shape: Tuple[int, ...]
+    stride_shape: Tuple[int, ...]
+    dilation_shape: Tuple[int, ...]
+
+
+@dataclass(frozen=True)
 class Constant(Op):
     value: float
 
@@ -298,6 +305,15 @@ def triu(graph, size, diagonal=0):
 def gather(matrix, indexes):
     return add_op(matrix.graph_ref, Function("Gather"), [_inp(matrix), _inp(indexes)],
                   tuple(indexes.shape) + (matrix.shape[1],))
+
+
+def unfold(a, kernel_shape, stride_shape, dilation_shape):      # src/HighLevelOps.jl:390-420
+    spatial = len(kernel_shape)
+    assert spatial == 1 and len(a.shape) > 1, "Unfold > 1D not implemented"
+    s_i, k_i, d_i, st_i = a.shape[-1], kernel_shape[0], dilation_shape[0], stride_shape[0]
+    o_i = (s_i - d_i * (k_i - 1) - 1) // st_i + 1
+    return add_op(a.graph_ref, Unfold(tuple(kernel_shape), tuple(stride_shape), tuple(dilation_shape)), [_inp(a)],
+                  tuple(a.shape[:-1]) + (o_i, k_i))
 
 
 def flash_attention(q, k, v, scale=None, causal=False):

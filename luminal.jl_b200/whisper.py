@@ -1,0 +1,170 @@
+"""Whisper as graph builders: the Python stand-in for src/Whisper.jl:208-404, 809-831 and for
+NN.Conv1D (src/NN.jl:38-104) -- sinusoids, self attention, encoder blocks, AudioEncoder and
+project_cross_kv -- with the model sizes as arguments instead of the reference's hard-coded
+whisper-tiny constants (src/Whisper.jl:195-206).  The encoder and the cross-K/V projection run
+once per utterance through execute() (one device call per node); the per-token decoder runs in
+the fused session (session.WhisperDecoderModel).
+
+One deliberate difference: a Linear bias on a [batch, seq, out] tensor is added as a broadcast
+over the last dim.  The reference expands it along dim 1 to the batch size, which only has the
+right shape for batch 1 (src/NN.jl:27-33; greedy_decode asserts batch == 1, src/Decoding.jl:43)."""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+
+from . import graph as G
+
+F32 = np.float32
+
+
+class WLinear:
+    def __init__(self, in_features, out_features, graph, reg, prefix, bias=True):
+        self.weight = G.tensor(graph, [out_features, in_features])
+        reg[f"{prefix}.weight"] = self.weight
+        self.bias = None
+        if bias:
+            self.bias = G.tensor(graph, [out_features])
+            reg[f"{prefix}.bias"] = self.bias
+
+    def __call__(self, x):
+        out = G.matmul(x, G.permute(self.weight, [2, 1]))
+        return out + self.bias if self.bias is not None else out
+
+
+class WLayerNorm:
+    def __init__(self, dim, graph, reg, prefix, epsilon=1e-5):
+        self.weight = G.tensor(graph, [dim])
+        self.bias = G.tensor(graph, [dim])
+        reg[f"{prefix}.weight"], reg[f"{prefix}.bias"] = self.weight, self.bias
+        self.epsilon = epsilon
+
+    def __call__(self, x):            # src/NN.jl:138-173
+        axis = len(x.shape)
+        out = G.std_norm(G.mean_norm(x, axis), axis, self.epsilon)
+        w, b = self.weight, self.bias
+        for i in range(1, len(out.shape)):
+            w = G.expand(w, i, out.shape[i - 1])
+            b = G.expand(b, i, out.shape[i - 1])
+        return out * w + b
+
+
+class Conv1D:                          # src/NN.jl:38-104
+    def __init__(self, ch_in, ch_out, kernel, graph, reg, prefix, stride=1, padding=0):
+        self.weight = G.tensor(graph, [ch_out, ch_in * kernel])
+        self.bias = G.tensor(graph, [ch_out])
+        reg[f"{prefix}.weight"], reg[f"{prefix}.bias"] = self.weight, self.bias
+        self.kernel, self.stride, self.padding = kernel, stride, padding
+
+    def __call__(self, x):             # x: [batch, channels, length]
+        rank = len(x.shape)
+        padded = G.pad_along(x, rank, self.padding, self.padding) if self.padding > 0 else x
+        unfolded = G.unfold(padded, [self.kernel], [self.stride], [1])           # [B, C, O, K]
+        perm = G.permute(unfolded, [1, 3, 2, 4])                                 # [B, O, C, K]
+        B, O, C, K = perm.shape
+        merged = G.reshape(perm, [B, O, C * K])                                  # column-major: c + C*k
+        out = G.matmul(merged, G.permute(self.weight, [2, 1]))                   # [B, O, ch_out]
+        out = G.permute(out, [1, 3, 2])                                          # [B, ch_out, O]
+        b = G.expand(G.expand(self.bias, 1, out.shape[0]), 3, out.shape[2])
+        return out + b
+
+
+def sinusoids(channels, length, graph):          # src/Whisper.jl:208-231
+    inc = math.log(10000.0) / (channels / 2 - 1)
+    inv_ts = np.array([math.exp(-inc * i) for i in range(channels // 2)], dtype=F32)
+    inv = G.tensor(graph, [channels // 2])
+    graph.tensors[(inv.id, 1)] = inv_ts
+    scaled = G.expand(G.arange(graph, length), 2, channels // 2) * G.expand(inv, 1, length)
+    return G.concat_along(G.sin(scaled), G.cos(scaled), 2)
+
+
+class WhisperSelfAttention:                      # src/Whisper.jl:238-276
+    def __init__(self, hidden, heads, graph, reg, prefix):
+        self.q_proj = WLinear(hidden, hidden, graph, reg, f"{prefix}.q_proj", bias=True)
+        self.k_proj = WLinear(hidden, hidden, graph, reg, f"{prefix}.k_proj", bias=False)
+        self.v_proj = WLinear(hidden, hidden, graph, reg, f"{prefix}.v_proj", bias=True)
+        self.o_proj = WLinear(hidden, hidden, graph, reg, f"{prefix}.out_proj", bias=True)
+        self.heads = heads
+
+    def __call__(self, x, mask):
+        batch, seq, hidden = x.shape
+        H, D = self.heads, hidden // self.heads
+        scale = F32(F32(F32(hidden) / F32(H)) ** F32(-0.25))
+        q = G.permute(G.reshape(self.q_proj(x) * scale, [batch, seq, H, D]), [1, 3, 2, 4])
+        k = G.permute(G.reshape(self.k_proj(x) * scale, [batch, seq, H, D]), [1, 3, 4, 2])
+        v = G.permute(G.reshape(self.v_proj(x), [batch, seq, H, D]), [1, 3, 2, 4])
+        weights = G.matmul(q, k)
+        if mask:
+            m = G.triu(x.graph_ref, seq, 1) * F32(-1e9)
+            weights = weights + G.expand(G.expand(m, 1, H), 1, batch)
+        out = G.matmul(G.softmax(weights, 4), v)
+        return self.o_proj(G.reshape(G.permute(out, [1, 3, 2, 4]), [batch, seq, hidden]))
+
+
+class EncoderTransformerBlock:                   # src/Whisper.jl:322-352
+    def __init__(self, hidden, heads, ff, graph, reg, prefix):
+        self.attn = WhisperSelfAttention(hidden, heads, graph, reg, f"{prefix}.self_attn")
+        self.attn_norm = WLayerNorm(hidden, graph, reg, f"{prefix}.self_attn_layer_norm")
+        self.ff1 = WLinear(hidden, ff, graph, reg, f"{prefix}.fc1")
+        self.ff2 = WLinear(ff, hidden, graph, reg, f"{prefix}.fc2")
+        self.ff_norm = WLayerNorm(hidden, graph, reg, f"{prefix}.final_layer_norm")
+
+    def __call__(self, x):
+        x = x + self.attn(self.attn_norm(x), False)
+        return x + self.ff2(G.gelu(self.ff1(self.ff_norm(x))))
+
+
+class AudioEncoder:                              # src/Whisper.jl:354-404
+    def __init__(self, graph, reg, *, d_model, heads, layers, ffn, n_mels):
+        pfx = "model.encoder"
+        self.d_model = d_model
+        self.conv1 = Conv1D(n_mels, d_model, 3, graph, reg, f"{pfx}.conv1", stride=1, padding=1)
+        self.conv2 = Conv1D(d_model, d_model, 3, graph, reg, f"{pfx}.conv2", stride=2, padding=1)
+        self.layers = [EncoderTransformerBlock(d_model, heads, ffn, graph, reg, f"{pfx}.layers.{i}") for i in range(layers)]
+        self.post_ln = WLayerNorm(d_model, graph, reg, f"{pfx}.layer_norm")
+
+    def __call__(self, x):                       # x: [batch, n_mels, frames]
+        x = G.gelu(self.conv1(x))
+        x = G.gelu(self.conv2(x))
+        x = G.permute(x, [1, 3, 2])
+        x = x + G.expand(sinusoids(self.d_model, x.shape[1], x.graph_ref), 1, x.shape[0])
+        for layer in self.layers:
+            x = layer(x)
+        return self.post_ln(x)
+
+
+def project_cross_kv(graph, reg, enc_output, *, d_model, heads, layers):     # src/Whisper.jl:809-831
+    """[(K, V)] per decoder layer, each [batch, heads, seq, head_dim]; K carries head_dim^-0.25."""
+    batch, seq, _ = enc_output.shape
+    D = d_model // heads
+    scale = F32(F32(F32(d_model) / F32(heads)) ** F32(-0.25))
+    out = []
+    for i in range(layers):
+        p = f"model.decoder.layers.{i}.encoder_attn"
+        k_proj = WLinear(d_model, d_model, graph, reg, f"{p}.k_proj", bias=False)
+        v_proj = WLinear(d_model, d_model, graph, reg, f"{p}.v_proj", bias=True)
+        k = G.permute(G.reshape(k_proj(enc_output) * scale, [batch, seq, heads, D]), [1, 3, 2, 4])
+        v = G.permute(G.reshape(v_proj(enc_output), [batch, seq, heads, D]), [1, 3, 2, 4])
+        out.append((k, v))
+    return out
+
+
+def encode_cross_kv(device, weights, mel, *, d_model, heads, enc_layers, dec_layers, ffn, n_mels):
+    """Runs AudioEncoder + project_cross_kv node by node on the device (execute()).  Returns the
+    encoder output and the per-layer cross (K, V) as host arrays, ready for Session.set_cross_kv."""
+    from .execution import execute
+    g, reg = G.Graph(), {}
+    mel = np.asarray(mel, dtype=F32)
+    inp = G.tensor(g, mel.shape)
+    enc = AudioEncoder(g, reg, d_model=d_model, heads=heads, layers=enc_layers, ffn=ffn, n_mels=n_mels)(inp)
+    kv = project_cross_kv(g, reg, enc, d_model=d_model, heads=heads, layers=dec_layers)
+    inputs = {t.id: weights[name] for name, t in reg.items()}
+    inputs[inp.id] = mel
+    ids = [enc.id] + [t.id for pair in kv for t in pair]
+    res = execute(g, ids, inputs, device)
+    return res[enc.id], [(res[k.id], res[v.id]) for k, v in kv]
+
+
+__all__ = ["AudioEncoder", "Conv1D", "WhisperSelfAttention", "EncoderTransformerBlock", "sinusoids", "project_cross_kv",
+           "encode_cross_kv"]

@@ -67,3 +67,46 @@ def test_whisper_decode_bf16_layer_outputs(lib_built, device):
         assert np.linalg.norm(logits - ref_logits) / np.linalg.norm(ref_logits) <= 4e-2
         tok = ref_logits.argmax(-1)          # teacher forcing with the oracle's tokens
     sess.close(); model.close()
+
+
+def test_unfold_matches_oracle(lib_built, device):
+    L = lib_built
+    x = O.synth_normal(2, 1, (2, 3, 23), 1.0)
+    for k, st, dil in [(3, 1, 1), (3, 2, 1), (4, 3, 2), (1, 1, 1)]:
+        g = L.Graph()
+        t = L.tensor(g, x.shape)
+        u = L.graph.unfold(t, [k], [st], [dil])
+        got = L.execute(g, u.id, {t.id: x}, device)
+        o = (23 - dil * (k - 1) - 1) // st + 1
+        ref = np.stack([x[..., dil * j: dil * j + st * (o - 1) + 1: st] for j in range(k)], -1)
+        assert got.shape == ref.shape and np.array_equal(got, ref)
+
+
+def test_whisper_encoder_graph_matches_oracle(lib_built, device):
+    """AudioEncoder + project_cross_kv built as a graph and run node by node on the device against
+    the oracle's encoder; then the whole chain encoder -> cross K/V upload -> greedy decode."""
+    L = lib_built
+    cfg = W.CONFIGS["whisper_test"]
+    batch, frames = 2, 60
+    w = W.synth_weights(cfg, seed=13)
+    mel = O.synth_normal(13, 5, (batch, cfg["n_mels"], frames), 1.0)
+    ref_enc = W.encoder(mel, w, cfg)
+    ref_kv = W.project_cross_kv(ref_enc, w, cfg)
+    enc, kv = L.whisper.encode_cross_kv(device, w, mel, d_model=cfg["d_model"], heads=cfg["heads"],
+                                        enc_layers=cfg["enc_layers"], dec_layers=cfg["dec_layers"], ffn=cfg["ffn"],
+                                        n_mels=cfg["n_mels"])
+    assert enc.shape == ref_enc.shape
+    assert np.abs(enc - ref_enc).max() <= 1e-3
+    for (k, v), (rk, rv) in zip(kv, ref_kv):
+        assert np.abs(k - rk).max() <= 1e-3 and np.abs(v - rv).max() <= 1e-3
+    first = O.synth_tokens(13, 6, (batch,), cfg["vocab"])
+    ref_tok, ref_log = W.CachedDecoder(w, cfg, batch, ref_kv).greedy(first, 10)
+    model, sess = build(L, device, cfg, w, batch, kv, "f32", enc.shape[1])
+    tok = first.astype(np.int32)
+    toks, logs = [], []
+    for _ in range(10):
+        tok, lg = sess.decode_step(tok, want_logits=True)
+        toks.append(tok.copy()); logs.append(lg)
+    assert np.abs(np.stack(logs, 1) - ref_log).max() <= 1e-3
+    assert np.array_equal(np.stack(toks, 1), ref_tok)
+    sess.close(); model.close()
