@@ -606,7 +606,16 @@ def _stream_key(seed, tensor_id):
 def synth_normal(seed, tensor_id, shape, sigma, offset=0.0):
     """Row-major linear index -> value.  `offset` is added after the multiply (norm gains)."""
     n = int(np.prod(shape))
-    idx = np.arange(n, dtype=np.uint64)
+    return synth_normal_at(seed, tensor_id, np.arange(n, dtype=np.uint64), sigma, offset).reshape(shape)
+
+
+def synth_normal_at(seed, tensor_id, linear_index, sigma, offset=0.0):
+    """The generator's values at the given row-major linear indices (any shape of indices), so a
+    slice of a tensor too large to build on the host can be regenerated."""
+    idx = np.asarray(linear_index).astype(np.uint64)
+    shape = idx.shape
+    idx = idx.reshape(-1)
+    n = idx.size
     with np.errstate(over="ignore"):
         key = _stream_key(seed, tensor_id)
         total = np.zeros(n, dtype=np.int64)
