@@ -5,6 +5,9 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <chrono>
+#include <thread>
+
 #include "common.cuh"
 #include "gemv.cuh"
 #include "model.cuh"
@@ -63,6 +66,7 @@ struct NcclApi {
   int (*CommInitRank)(void**, int, Id128, int) = nullptr;
   int (*CommDestroy)(void*) = nullptr;
   int (*AllReduce)(const void*, void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+  int (*AllGather)(const void*, void*, size_t, int, void*, cudaStream_t) = nullptr;
   const char* (*GetErrorString)(int) = nullptr;
 };
 NcclApi g_nccl;
@@ -80,6 +84,7 @@ int32_t nccl_load() {
   g_nccl.CommInitRank = reinterpret_cast<decltype(g_nccl.CommInitRank)>(dlsym(lib, "ncclCommInitRank"));
   g_nccl.CommDestroy = reinterpret_cast<decltype(g_nccl.CommDestroy)>(dlsym(lib, "ncclCommDestroy"));
   g_nccl.AllReduce = reinterpret_cast<decltype(g_nccl.AllReduce)>(dlsym(lib, "ncclAllReduce"));
+  g_nccl.AllGather = reinterpret_cast<decltype(g_nccl.AllGather)>(dlsym(lib, "ncclAllGather"));
   g_nccl.GetErrorString = reinterpret_cast<decltype(g_nccl.GetErrorString)>(dlsym(lib, "ncclGetErrorString"));
   if (!g_nccl.GetUniqueId || !g_nccl.CommInitRank || !g_nccl.CommDestroy || !g_nccl.AllReduce)
     return fail(LMB200_ENCCL, "NCCL library lacks a required symbol");
@@ -87,6 +92,110 @@ int32_t nccl_load() {
   return LMB200_OK;
 }
 const char* nccl_str(int r) { return g_nccl.GetErrorString ? g_nccl.GetErrorString(r) : "?"; }
+
+// What the ranks tell each other while the peer exchange region is set up.
+struct PeerHello {
+  cudaIpcMemHandle_t handle;
+  int32_t ok;
+  int32_t pad[15];
+};
+
+// Waits for the stream, but not forever: a rank whose peers never arrive gives up after `seconds`.
+bool stream_done_within(cudaStream_t st, double seconds) {
+  const auto t0 = std::chrono::steady_clock::now();
+  for (;;) {
+    const cudaError_t e = cudaStreamQuery(st);
+    if (e == cudaSuccess) return true;
+    if (e != cudaErrorNotReady) { cudaGetLastError(); return false; }
+    if (std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count() > seconds) return false;
+    std::this_thread::sleep_for(std::chrono::microseconds(200));
+  }
+}
+
+int32_t gather_hello(Ctx* c, const PeerHello& mine, PeerHello* all, void* dsend, void* drecv) {
+  LMB_CUDA(cudaMemcpyAsync(dsend, &mine, sizeof(PeerHello), cudaMemcpyHostToDevice, c->own_stream));
+  const int r = g_nccl.AllGather(dsend, drecv, sizeof(PeerHello), 0 /* ncclInt8 */, c->nccl_comm, c->own_stream);
+  if (r != 0) return fail(LMB200_ENCCL, "ncclAllGather: %s", nccl_str(r));
+  LMB_CUDA(cudaMemcpyAsync(all, drecv, sizeof(PeerHello) * c->tp_size, cudaMemcpyDeviceToHost, c->own_stream));
+  LMB_CUDA(cudaStreamSynchronize(c->own_stream));
+  return LMB200_OK;
+}
+
+// Maps one exchange region per rank into every rank (CUDA IPC inside one node) for the all-reduce
+// that the decode step's norm kernels do themselves.  Every decision is taken on gathered data, so
+// all ranks end up with the same answer; any failure leaves peer_n == 0 and NCCL does the sums.
+int32_t peer_setup(Ctx* c) {
+  const char* sel = getenv("LMB200_TP_ALLREDUCE");          // "nccl": keep ncclAllReduce (A/B runs)
+  if ((sel && strcmp(sel, "nccl") == 0) || c->tp_size < 2 || c->tp_size > 8 || !g_nccl.AllGather) return LMB200_OK;
+  const int n = c->tp_size;
+  void *region = nullptr, *dsend = nullptr, *drecv = nullptr;
+  PeerHello mine, all[8];
+  memset(&mine, 0, sizeof(mine));
+  bool ok = cudaMalloc(&region, kPeerRegionBytes) == cudaSuccess && cudaMemset(region, 0, kPeerRegionBytes) == cudaSuccess &&
+            cudaMalloc((void**)&c->peer_step, 8) == cudaSuccess && cudaMemset(c->peer_step, 0, 8) == cudaSuccess &&
+            cudaMalloc((void**)&c->peer_scratch, 4) == cudaSuccess && cudaMemset(c->peer_scratch, 0, 4) == cudaSuccess &&
+            cudaDeviceSynchronize() == cudaSuccess && cudaIpcGetMemHandle(&mine.handle, region) == cudaSuccess;
+  cudaGetLastError();
+  mine.ok = ok ? 1 : 0;
+  int32_t rc = LMB200_OK;
+  if (cudaMalloc(&dsend, sizeof(PeerHello)) != cudaSuccess || cudaMalloc(&drecv, sizeof(PeerHello) * 8) != cudaSuccess) {
+    cudaGetLastError();
+    rc = fail(LMB200_ENOMEM, "comm_init: staging allocation failed");
+  }
+  void* mapped[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  if (rc == LMB200_OK) rc = gather_hello(c, mine, all, dsend, drecv);
+  if (rc == LMB200_OK) {
+    for (int r = 0; r < n; ++r) ok = ok && all[r].ok;
+    if (ok) {
+      for (int r = 0; r < n; ++r) {
+        if (r == c->tp_rank) { mapped[r] = region; continue; }
+        if (cudaIpcOpenMemHandle(&mapped[r], all[r].handle, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+          cudaGetLastError();
+          mapped[r] = nullptr;
+          ok = false;
+        }
+      }
+    }
+    mine.ok = ok ? 1 : 0;
+    rc = gather_hello(c, mine, all, dsend, drecv);       // second round: did every rank map every peer?
+    if (rc == LMB200_OK)
+      for (int r = 0; r < n; ++r) ok = ok && all[r].ok;
+  }
+  cudaFree(dsend);
+  cudaFree(drecv);
+  if (rc == LMB200_OK && ok) {
+    for (int r = 0; r < n; ++r) c->peer_base[r] = mapped[r];
+    c->peer_n = n;
+    return LMB200_OK;
+  }
+  for (int r = 0; r < n; ++r)
+    if (mapped[r] && r != c->tp_rank) cudaIpcCloseMemHandle(mapped[r]);
+  cudaFree(region);
+  cudaFree(c->peer_step); c->peer_step = nullptr;
+  cudaFree(c->peer_scratch); c->peer_scratch = nullptr;
+  cudaGetLastError();
+  return rc;
+}
+
+// Peers may still be reading this rank's region (their last norm kernel), so all ranks meet in one
+// NCCL all-reduce first.  If the others never come, the region is left allocated rather than freed
+// under a reader.
+void peer_teardown(Ctx* c) {
+  if (c->peer_n == 0) return;
+  cudaStreamSynchronize(c->stream);
+  bool met = g_nccl.AllReduce(c->peer_scratch, c->peer_scratch, 1, 7, 0, c->nccl_comm, c->own_stream) == 0 &&
+             stream_done_within(c->own_stream, 5.0);
+  for (int r = 0; r < c->peer_n; ++r) {
+    if (r != c->tp_rank && c->peer_base[r]) cudaIpcCloseMemHandle(c->peer_base[r]);
+    else if (r == c->tp_rank && met) cudaFree(c->peer_base[r]);
+    c->peer_base[r] = nullptr;
+  }
+  if (met) { cudaFree(c->peer_step); cudaFree(c->peer_scratch); }
+  c->peer_step = nullptr;
+  c->peer_scratch = nullptr;
+  c->peer_n = 0;
+  cudaGetLastError();
+}
 }  // namespace
 
 int32_t nccl_allreduce_f32(Ctx* ctx, void* dptr, int64_t count, cudaStream_t stream) {
@@ -194,6 +303,7 @@ extern "C" int32_t lmb200_shutdown(lmb200_ctx h) {
   if (!c) return LMB200_EINVAL;
   cudaSetDevice(c->device);
   cudaStreamSynchronize(c->stream);
+  peer_teardown(c);
   if (c->nccl_comm && g_nccl.CommDestroy) g_nccl.CommDestroy(c->nccl_comm);
   cudaStreamDestroy(c->own_stream);
   cudaFreeHost(c->dev_err);
@@ -250,7 +360,7 @@ extern "C" int32_t lmb200_comm_init(lmb200_ctx h, int32_t n_ranks, int32_t rank,
   c->nccl_comm = comm;
   c->tp_size = n_ranks;
   c->tp_rank = rank;
-  return LMB200_OK;
+  return peer_setup(c);
 }
 
 extern "C" int32_t lmb200_comm_destroy(lmb200_ctx h) {
@@ -259,6 +369,7 @@ extern "C" int32_t lmb200_comm_destroy(lmb200_ctx h) {
   if (c->nccl_comm) {
     cudaSetDevice(c->device);
     cudaStreamSynchronize(c->stream);
+    peer_teardown(c);
     g_nccl.CommDestroy(c->nccl_comm);
     c->nccl_comm = nullptr;
     c->tp_size = 1;

@@ -53,7 +53,69 @@ struct Ctx {
   void* nccl_comm = nullptr;
   int tp_size = 1;
   int tp_rank = 0;
+  // Peer exchange region of the in-kernel all-reduce, one per communicator, mapped into every rank
+  // with CUDA IPC: two partial buffers of kPeerBufFloats floats, then one 64-bit flag per source
+  // rank.  peer_n == 0: not set up, the NCCL all-reduce is used instead.
+  int peer_n = 0;
+  void* peer_base[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  unsigned long long* peer_step = nullptr;   // device counter: decode steps enqueued on this communicator
+  float* peer_scratch = nullptr;             // 1 float for the teardown barrier
 };
+
+constexpr int64_t kPeerBufFloats = 1 << 20;
+constexpr int64_t kPeerFlagsOffset = 2 * kPeerBufFloats * 4;          // bytes
+constexpr int64_t kPeerRegionBytes = kPeerFlagsOffset + 4096;
+constexpr unsigned long long kPeerEpochStride = 4096;                 // reductions per step < this
+constexpr long long kPeerWaitCycles = 20000000000ll;                  // about 10 s of SM clock
+
+// What a kernel needs to sum the ranks' partial results of one row-parallel projection: every rank
+// wrote its partial into its own region; the consumer signals the peers, waits (bounded) for their
+// signals and adds the partials in rank order, so every rank gets the same bits.
+struct PeerReduce {
+  int n = 0, rank = 0;
+  const float* part[8];                    // rank r's partial buffer of this reduction
+  unsigned long long* remote_flag[8];      // this rank's slot in rank r's flag array
+  const unsigned long long* local_flag;    // this rank's flag array, one slot per source rank
+  const unsigned long long* step;          // steps completed so far
+  unsigned phase = 0;                      // 1 + index of the reduction inside the step
+  int* dev_err = nullptr;
+};
+
+#ifdef __CUDACC__
+// All threads of the block call this once the kernel that produced this rank's partial is complete.
+// CTA 0 publishes "rank `rank` has written reduction `epoch`" into every peer's flag array; every
+// CTA then waits until all peers have published the same epoch.  A wait that runs out (or finds an
+// earlier failure recorded) sets the error word and returns, so nothing spins forever.
+__device__ __forceinline__ void peer_exchange_wait(const PeerReduce& pr) {
+  const unsigned long long epoch = *pr.step * kPeerEpochStride + pr.phase;
+  const int t = threadIdx.x;
+  if (t < pr.n && t != pr.rank) {
+    if (blockIdx.x == 0) {
+      __threadfence_system();
+      asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(pr.remote_flag[t]), "l"(epoch) : "memory");
+    }
+    const long long t0 = clock64();
+    unsigned spins = 0;
+    for (;;) {
+      unsigned long long v;
+      asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(pr.local_flag + t) : "memory");
+      if (v >= epoch) break;
+      if ((++spins & 1023u) == 0u) {
+        volatile int* err = pr.dev_err;
+        if (*err != 0) break;
+        if (clock64() - t0 > kPeerWaitCycles) { *err = 1; break; }
+      }
+    }
+  }
+  __syncthreads();
+}
+
+__device__ __forceinline__ float4 peer_load4(const float* p) {
+  float4 v;
+  asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+  return v;
+}
+#endif
 
 Ctx* ctx_from(lmb200_ctx h);
 // LMB200_ETIMEOUT (and clears the flag) if a kernel reported a wait that ran out

@@ -747,9 +747,12 @@ __device__ __forceinline__ void tmem_load_row<16>(float (&v)[16], uint32_t taddr
 
 // Epilogue of one accumulator row held by one thread (v[b], b < N).  Rows g and g+8 of a 16-row
 // block -- the pairs the fused epilogues combine -- are 8 lanes apart in the same warp.
-template <int N>
-__device__ __forceinline__ void row_epilogue(const GemvParams& p, float (&v)[N], int row) {
+// The thread holds batch columns b0 .. b0+NV-1 of the row (the whole row when NV == BP); BP is the
+// batch padding of the activation buffers.
+template <int NV, int BP>
+__device__ __forceinline__ void row_epilogue(const GemvParams& p, float (&v)[NV], int row, int b0) {
   typedef Layout<__nv_bfloat16> LY;
+  constexpr int N = NV;
   const int rb = row >> 4, rr = row & 15, g = rr & 7, hi = rr >> 3;
   if (p.bias) {
     const float bias = row < p.rows ? p.bias[row] : 0.f;
@@ -760,7 +763,7 @@ __device__ __forceinline__ void row_epilogue(const GemvParams& p, float (&v)[N],
     if (row < p.rows) {
 #pragma unroll
       for (int b = 0; b < N; ++b)
-        if (b < p.B) p.out[(int64_t)b * p.out_pitch + row] = v[b];
+        if (b0 + b < p.B) p.out[(int64_t)(b0 + b) * p.out_pitch + row] = v[b];
     }
     return;
   }
@@ -769,7 +772,7 @@ __device__ __forceinline__ void row_epilogue(const GemvParams& p, float (&v)[N],
       __nv_bfloat16* act = reinterpret_cast<__nv_bfloat16*>(p.act);
 #pragma unroll
       for (int b = 0; b < N; ++b)
-        if (b < p.B) act[LY::x_offset(b, row, N)] = __float2bfloat16_rn(gelu_ref(v[b]));
+        if (b0 + b < p.B) act[LY::x_offset(b0 + b, row, BP)] = __float2bfloat16_rn(gelu_ref(v[b]));
     }
     return;
   }
@@ -783,12 +786,12 @@ __device__ __forceinline__ void row_epilogue(const GemvParams& p, float (&v)[N],
       __nv_bfloat16* act = reinterpret_cast<__nv_bfloat16*>(p.act);
 #pragma unroll
       for (int b = 0; b < N; ++b) {
-        if (b < p.B) {
+        if (b0 + b < p.B) {
           const float a = v[b], u = w[b];
           // silu(a) = a * (1 / (1 + exp2((a * -1) * (1/ln2))))     src/HighLevelOps.jl:153-160
           const float ex = exp2f((a * -1.0f) * kInvLn2);
           const float sg = 1.0f / (1.0f + ex);
-          act[LY::x_offset(b, o, N)] = __float2bfloat16_rn((a * sg) * u);
+          act[LY::x_offset(b0 + b, o, BP)] = __float2bfloat16_rn((a * sg) * u);
         }
       }
     }
@@ -811,13 +814,13 @@ __device__ __forceinline__ void row_epilogue(const GemvParams& p, float (&v)[N],
     const int d = hi ? d0 + half : d0;
 #pragma unroll
     for (int b = 0; b < N; ++b) {
-      if (b < p.B) {
+      if (b0 + b < p.B) {
         // low row: x0*cos - x1*sin; high row: x0*sin + x1*cos (x0 = the low row's value)
         const float o = hi ? (w[b] * sn + v[b] * cs) : (v[b] * cs + (w[b] * sn) * -1.0f);
         if (hs < p.Hl) {
-          reinterpret_cast<__nv_bfloat16*>(p.q_out)[(int64_t)b * p.q_pitch + hs * D + d] = __float2bfloat16_rn(o);
+          reinterpret_cast<__nv_bfloat16*>(p.q_out)[(int64_t)(b0 + b) * p.q_pitch + hs * D + d] = __float2bfloat16_rn(o);
         } else {
-          kv[b * p.kv_batch_stride + (hs - p.Hl) * p.kv_head_stride + kcache_offset(pos, d, D)] = __float2bfloat16_rn(o);
+          kv[(b0 + b) * p.kv_batch_stride + (hs - p.Hl) * p.kv_head_stride + kcache_offset(pos, d, D)] = __float2bfloat16_rn(o);
         }
       }
     }
@@ -825,11 +828,27 @@ __device__ __forceinline__ void row_epilogue(const GemvParams& p, float (&v)[N],
     const int d = 16 * jj + rr;
 #pragma unroll
     for (int b = 0; b < N; ++b)
-      if (b < p.B)
-        kv[b * p.kv_batch_stride + (hs - p.Hl - p.KVl) * p.kv_head_stride + vcache_offset(pos, d, D)] =
+      if (b0 + b < p.B)
+        kv[(b0 + b) * p.kv_batch_stride + (hs - p.Hl - p.KVl) * p.kv_head_stride + vcache_offset(pos, d, D)] =
             __float2bfloat16_rn(v[b]);
   }
 }
+
+// Optional per-CTA phase stamps (SM clock) for tuning; compiled in only with -DLMB_GEMV_TRACE.
+#ifdef LMB_GEMV_TRACE
+__device__ long long g_gemv_trace[160 * 16];
+__device__ __forceinline__ long long gtime_ns() { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+}  // namespace
+int32_t gemv_trace_copy(long long* out) {
+  return cudaMemcpyFromSymbol(out, g_gemv_trace, sizeof(g_gemv_trace)) == cudaSuccess ? 0 : -3;
+}
+namespace {
+#define LMB_TRACE(slot) (g_gemv_trace[blockIdx.x * 16 + (slot)] = clock64())
+#define LMB_TRACE_NS(slot) (g_gemv_trace[blockIdx.x * 16 + (slot)] = gtime_ns())
+#else
+#define LMB_TRACE(slot) ((void)0)
+#define LMB_TRACE_NS(slot) ((void)0)
+#endif
 
 template <int N>
 __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const GemvParams p, int* err) {
@@ -849,6 +868,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const GemvParams
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const UnitRange ur = unit_range(p);
   if (tid == 0) {
+    LMB_TRACE(0); LMB_TRACE_NS(10);
 #pragma unroll
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&full_bar[s], 1);
@@ -870,11 +890,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const GemvParams
   const uint32_t tmem_base = tmem_base_slot;
   bool dead = false;
   pdl_launch_dependents();
+  if (tid == 0) LMB_TRACE(1);
 
   if (warp == 0) {
     produce<N>(p, ur, smem, full_bar, empty_bar, lane, err);
   } else if (warp == 1) {
     pdl_wait();
+    if (lane == 0) LMB_TRACE(2);
     // ---------------- MMA issue ----------------
     int it = 0, seg = 0;
     for (int u = ur.u0; u < ur.u1; ++u, ++it) {
@@ -886,6 +908,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const GemvParams
       const int s = it % kStages, k = it / kStages;
       mbar_wait(&full_bar[s], k & 1, dead, err);
       tc_fence_after();
+      if (lane == 0 && it == 0) LMB_TRACE(3);
       if (lane == 0) {
         const uint32_t st = smem_u32(smem + s * kStage);
         const uint64_t adesc = smem_desc(st, 2048, 128);
@@ -900,11 +923,19 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const GemvParams
       __syncwarp();
       if (last) ++seg;
     }
+    if (lane == 0) LMB_TRACE(4);
   } else {
     // ---------------- epilogue: warp quarter q owns TMEM lanes / rows 32q .. 32q+31 ----------------
+    // A row group whose k range is shared by n > 1 CTAs is folded by all of them together: each
+    // stores its partial accumulator and counts itself in; once this CTA has finished its own
+    // units it waits until every contributor of the group has arrived and then sums, in contributor
+    // order, the 16-row blocks that fall to it (block j goes to contributor j mod n) and runs
+    // their epilogue.  The sum order is fixed, so results do not depend on timing.
     pdl_wait();
     const int q = warp & 3;
+    const int e = tid - 64;                      // 0..127 inside the epilogue group
     int seg = 0;
+    int pend_r[2], pend_first[2], pend_n[2], n_pend = 0;
     for (int u = ur.u0; u < ur.u1; ++seg) {
       const int r = u / ur.KS;
       const int u_end = min(ur.u1, (r + 1) * ur.KS);
@@ -917,46 +948,127 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const GemvParams
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[buf]);
+      if (tid == 64) LMB_TRACE(5);
       const int row_in_group = 32 * q + lane;
       int c_first, n;
       contributors(ur, r, &c_first, &n);
-      bool run = true;
-      if (n > 1) {
-        float4* part = reinterpret_cast<float4*>(p.partials) + (int64_t)r * p.ksplit * (128 * N / 4);
-        float4* mine = part + (int64_t)((int)blockIdx.x - c_first) * (128 * N / 4) + row_in_group * (N / 4);
+      if (n == 1) {
+        row_epilogue<N, N>(p, v, r * 128 + row_in_group, 0);
+        continue;
+      }
+      float4* part = reinterpret_cast<float4*>(p.partials) + (int64_t)r * p.ksplit * (128 * N / 4);
+      float4* mine = part + (int64_t)((int)blockIdx.x - c_first) * (128 * N / 4) + row_in_group * (N / 4);
 #pragma unroll
-        for (int i = 0; i < N / 4; ++i) mine[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-        __threadfence();
-        __syncwarp();
-        unsigned prev = 0;
-        if (lane == 0) prev = atomicAdd(&p.counters[r * 4 + q], 1u);
-        prev = __shfl_sync(0xffffffffu, prev, 0);
-        run = prev == (unsigned)n - 1u;
-        if (run) {
-          if (lane == 0) p.counters[r * 4 + q] = 0u;     // ready for the next launch
-          __threadfence();
-#pragma unroll
-          for (int i = 0; i < N; ++i) v[i] = 0.f;
-          for (int k0 = 0; k0 < n; k0 += 2) {
-            float4 t0[N / 4], t1[N / 4];
-            const float4* pa = part + (int64_t)k0 * (128 * N / 4) + row_in_group * (N / 4);
-            const bool two = k0 + 1 < n;
-#pragma unroll
-            for (int i = 0; i < N / 4; ++i) {
-              t0[i] = __ldcg(pa + i);
-              t1[i] = two ? __ldcg(pa + (128 * N / 4) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-#pragma unroll
-            for (int i = 0; i < N / 4; ++i) {
-              v[4 * i] += t0[i].x; v[4 * i + 1] += t0[i].y; v[4 * i + 2] += t0[i].z; v[4 * i + 3] += t0[i].w;
-              v[4 * i] += t1[i].x; v[4 * i + 1] += t1[i].y; v[4 * i + 2] += t1[i].z; v[4 * i + 3] += t1[i].w;
-            }
-          }
+      for (int i = 0; i < N / 4; ++i) mine[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+      __threadfence();
+      asm volatile("bar.sync 1, 128;\n" ::: "memory");
+      if (e == 0) atomicAdd(&p.counters[r * 8], 1u);
+      if (tid == 64) LMB_TRACE(6);
+      if (n_pend < 2) { pend_r[n_pend] = r; pend_first[n_pend] = c_first; pend_n[n_pend] = n; ++n_pend; }
+    }
+    // wait for every contributor of the shared row groups.  The last segment is shared with CTAs
+    // that finished it long ago, the first one with a CTA that ends on it about now.
+    if (e == 0) {
+      const long long t0 = clock64();
+      for (int ip = n_pend - 1; ip >= 0; --ip) {
+        for (;;) {
+          unsigned seen;
+          asm volatile("ld.acquire.gpu.global.u32 %0, [%1];\n" : "=r"(seen) : "l"(p.counters + pend_r[ip] * 8) : "memory");
+          if (seen >= (unsigned)pend_n[ip] || dead) break;
+          if (clock64() - t0 > kWaitLimit) { dead = true; if (err) atomicExch(err, 1); break; }
         }
       }
-      // every lane of the warp takes the same branch here (the counter is per warp quarter)
-      if (run) row_epilogue<N>(p, v, r * 128 + row_in_group);
     }
+    asm volatile("bar.sync 1, 128;\n" ::: "memory");
+    if (tid == 64) LMB_TRACE(7);
+    const int row16 = lane & 15, cg = e >> 4;               // one float4 (4 batch columns) per thread
+    if (cg < N / 4 && n_pend > 0) {                          // warp-uniform: whole warps drop out for N = 16
+      // Per shared row group this contributor owns the 16-row blocks ci, ci + n, ... (at most 4) and
+      // sums each over the contributors in ascending order.  A round trip to L2 at the end of a
+      // kernel costs microseconds, so every partial this thread needs is fetched with one wave of
+      // cp.async into the (now idle) pipeline stages, slot s of thread e at byte s * 2048 + e * 16,
+      // and summed from shared memory afterwards.
+      constexpr int kSlots = (kStages * kStage) / 2048;
+      constexpr int64_t kPartStride = 128 * N / 4;           // float4s per contributor
+      const uint32_t fs = smem_u32(smem) + (uint32_t)e * 16u;
+      int n_[2], ci_[2], nj_[2];
+      const float4* part_[2];
+#pragma unroll
+      for (int ip = 0; ip < 2; ++ip) {
+        const bool on = ip < n_pend;
+        n_[ip] = on ? pend_n[ip] : 1;
+        ci_[ip] = on ? (int)blockIdx.x - pend_first[ip] : 8;
+        nj_[ip] = ci_[ip] < 8 ? (8 - ci_[ip] + n_[ip] - 1) / n_[ip] : 0;
+        part_[ip] = reinterpret_cast<const float4*>(p.partials) + (int64_t)(on ? pend_r[ip] : 0) * p.ksplit * kPartStride +
+                    row16 * (N / 4) + cg;
+      }
+      auto issue = [&](int ip, int slot, int k0, int k1) -> int {
+        for (int jj = 0; jj < nj_[ip]; ++jj) {
+          const float4* src = part_[ip] + 16 * (ci_[ip] + jj * n_[ip]) * (N / 4);
+          for (int k = k0; k < k1; ++k, ++slot)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(fs + (uint32_t)slot * 2048u), "l"(src + k * kPartStride) : "memory");
+        }
+        return slot;
+      };
+      auto lds4 = [&](int slot) -> float4 {
+        float4 t;
+        asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];\n" : "=f"(t.x), "=f"(t.y), "=f"(t.z), "=f"(t.w) : "r"(fs + (uint32_t)slot * 2048u));
+        return t;
+      };
+      auto consume = [&](int ip, int slot) -> int {
+        for (int jj = 0; jj < nj_[ip]; ++jj) {
+          float v4[4] = {0.f, 0.f, 0.f, 0.f};
+          for (int k = 0; k < n_[ip]; ++k, ++slot) {
+            const float4 t = lds4(slot);
+            v4[0] += t.x; v4[1] += t.y; v4[2] += t.z; v4[3] += t.w;
+          }
+          row_epilogue<4, N>(p, v4, pend_r[ip] * 128 + 16 * (ci_[ip] + jj * n_[ip]) + row16, 4 * cg);
+        }
+        return slot;
+      };
+      const int cnt0 = nj_[0] * n_[0], cnt1 = nj_[1] * n_[1];
+      if (cnt0 + cnt1 <= kSlots) {
+        const int s1 = issue(0, 0, 0, n_[0]);
+        issue(1, s1, 0, n_[1]);
+        asm volatile("cp.async.wait_all;\n" ::: "memory");
+        if (tid == 64) LMB_TRACE(12);
+        consume(1, consume(0, 0));
+      } else {
+        // a row group shared by more CTAs than there are slots (tiny matrices): waves over k
+#pragma unroll 1
+        for (int ip = 0; ip < 2; ++ip) {
+          if (nj_[ip] == 0) continue;
+          if (nj_[ip] * n_[ip] <= kSlots) {
+            issue(ip, 0, 0, n_[ip]);
+            asm volatile("cp.async.wait_all;\n" ::: "memory");
+            consume(ip, 0);
+            continue;
+          }
+          float v4[4] = {0.f, 0.f, 0.f, 0.f};          // n > kSlots > 8, so there is one block
+          for (int k0 = 0; k0 < n_[ip]; k0 += kSlots) {
+            const int k1 = min(n_[ip], k0 + kSlots);
+            issue(ip, 0, k0, k1);
+            asm volatile("cp.async.wait_all;\n" ::: "memory");
+            for (int sl = 0; sl < k1 - k0; ++sl) {
+              const float4 t = lds4(sl);
+              v4[0] += t.x; v4[1] += t.y; v4[2] += t.z; v4[3] += t.w;
+            }
+          }
+          row_epilogue<4, N>(p, v4, pend_r[ip] * 128 + 16 * ci_[ip] + row16, 4 * cg);
+        }
+      }
+      if (tid == 64) LMB_TRACE(13);
+    }
+    asm volatile("bar.sync 1, 128;\n" ::: "memory");
+    if (e < n_pend) {
+      const int r = pend_r[e], n = pend_n[e];
+      const unsigned prev = atomicAdd(&p.counters[r * 8 + 1], 1u);
+      if (prev == (unsigned)n - 1u) {                       // every contributor has read: ready for the next launch
+        p.counters[r * 8] = 0u;
+        p.counters[r * 8 + 1] = 0u;
+      }
+    }
+    if (tid == 64) LMB_TRACE(8);
   }
   // all roles meet before the accumulator memory is given back
   tc_fence_before();
@@ -965,6 +1077,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const GemvParams
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
   }
+  if (tid == 0) { LMB_TRACE(9); LMB_TRACE_NS(11); }
 }
 
 template <typename WT, int NB, int MT, int STAGES>
@@ -1084,3 +1197,9 @@ int32_t gemv_launch(Ctx* ctx, int dtype, GemvParams p, cudaStream_t stream) {
 }
 
 }  // namespace lmb
+
+#ifdef LMB_GEMV_TRACE
+extern "C" int32_t lmb200_debug_gemv_trace(long long* out) {
+  return lmb::gemv_trace_copy(out);
+}
+#endif

@@ -151,13 +151,17 @@ __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(float* __rest
                                                                    const WT* __restrict__ embed, int vocab,
                                                                    const float* __restrict__ w, WT* __restrict__ xn,
                                                                    int Bp, int n, float eps,
-                                                                   float* __restrict__ capture) {
+                                                                   float* __restrict__ capture, PeerReduce pr) {
   extern __shared__ __align__(16) float row[];
   __shared__ float red[kNormThreads / 32];
   pdl_launch_dependents();
   pdl_wait();
   const int b = blockIdx.x, tid = threadIdx.x;
   const int n4 = n >> 2;
+  // tensor parallel: delta is the sum of every rank's partial projection, read from the ranks'
+  // exchange regions once all of them have signalled (all-reduce folded into this kernel)
+  const bool peers = pr.n > 1 && !tokens;
+  if (peers) peer_exchange_wait(pr);
   float4* xr = reinterpret_cast<float4*>(x + (int64_t)b * n);
   float4* rs = reinterpret_cast<float4*>(row);
   float ss = 0.f;
@@ -179,7 +183,14 @@ __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(float* __rest
 #pragma unroll 4
     for (int i = tid; i < n4; i += kNormThreads) {
       float4 v = xr[i];
-      if (dr) { const float4 d = dr[i]; v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w; }
+      if (peers) {
+        float4 d = peer_load4(pr.part[0] + (int64_t)b * n + 4 * i);
+        for (int r = 1; r < pr.n; ++r) {
+          const float4 e = peer_load4(pr.part[r] + (int64_t)b * n + 4 * i);
+          d.x += e.x; d.y += e.y; d.z += e.z; d.w += e.w;
+        }
+        v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+      } else if (dr) { const float4 d = dr[i]; v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w; }
       xr[i] = v;
       rs[i] = v;
       if (cr) cr[i] = v;
@@ -326,18 +337,16 @@ __global__ void __launch_bounds__(256) argmax_step_kernel(const float* logits, i
   }
 }
 
-__global__ void advance_kernel(int* pos, int* step_ctr) {
+__global__ void advance_kernel(int* pos, int* step_ctr, unsigned long long* peer_step) {
   pdl_launch_dependents();
   pdl_wait();
   *pos += 1;
   *step_ctr += 1;
+  if (peer_step) *peer_step += 1;     // epoch base of the next step's in-kernel all-reduces
 }
 
-static int g_debug_skip = 0;   // LMB200_DEBUG_SKIP bit mask (timing experiments only): 1 attention, 2 gemv, 4 norm
 
 int32_t step_kernels_configure() {
-  const char* sk = getenv("LMB200_DEBUG_SKIP");
-  g_debug_skip = sk ? atoi(sk) : 0;
   const char* e = getenv("LMB200_CARVEOUT");
   if (e && atoi(e) == 0) return LMB200_OK;
 #define LMB_CARVE(KERN) \
@@ -540,7 +549,11 @@ extern "C" int32_t lmb200_model_create(lmb200_ctx hctx, const lmb200_model_confi
     const int32_t rc0 = derive_model(c, M);
     if (rc0 != LMB200_OK) { delete M; return rc0; }
   }
-  if (c.tp_size > 1 && !(ctx->nccl_comm && ctx->tp_size == c.tp_size && ctx->tp_rank == c.tp_rank)) {
+  // LMB200_TP_SOLO=1 (profiling aid): one rank's shard without its peers.  The partial sums are
+  // never reduced, so the results are not the model's; the kernels and their sizes are the rank's.
+  const char* solo = getenv("LMB200_TP_SOLO");
+  M->tp_solo = c.tp_size > 1 && !ctx->nccl_comm && solo && atoi(solo) == 1;
+  if (c.tp_size > 1 && !M->tp_solo && !(ctx->nccl_comm && ctx->tp_size == c.tp_size && ctx->tp_rank == c.tp_rank)) {
     delete M;
     return fail(LMB200_EINVAL, "model_create: tp_size %d needs lmb200_comm_init with the same ranks first", c.tp_size);
   }
@@ -797,6 +810,43 @@ GemvParams gemv_params(Session* S, const void* W, const WMap& m, const GemvPlan&
   return p;
 }
 
+// Partial-sum exchange of the two row-parallel projections of a layer (index 2l: o_proj, 2l + 1:
+// down_proj).  With the peer regions mapped, the projection writes this rank's partial into its
+// region (buffers alternate, so a buffer is rewritten only after every peer has passed the next
+// reduction) and the following norm kernel sums all ranks' partials itself; otherwise the partial
+// goes through ncclAllReduce in place.
+struct RowParallelOut {
+  float* out;          // where the GEMV stores its [B, hidden] result
+  bool nccl;           // all-reduce `out` in place afterwards
+  PeerReduce pr;       // for the consuming norm kernel (n == 0: read `out` as is)
+};
+
+RowParallelOut row_parallel_out(Session* S, int index) {
+  Ctx* ctx = S->m->ctx;
+  RowParallelOut r;
+  r.out = S->delta;
+  r.nccl = false;
+  const int n = S->m->cfg.tp_size;
+  if (n <= 1 || S->m->tp_solo) return r;
+  if (ctx->peer_n != n || (int64_t)S->B * S->m->cfg.hidden > kPeerBufFloats || (unsigned long long)index + 1 >= kPeerEpochStride) {
+    r.nccl = true;
+    return r;
+  }
+  const int64_t buf = (int64_t)(index & 1) * kPeerBufFloats;
+  r.out = reinterpret_cast<float*>(ctx->peer_base[ctx->tp_rank]) + buf;
+  r.pr.n = n;
+  r.pr.rank = ctx->tp_rank;
+  for (int k = 0; k < n; ++k) {
+    r.pr.part[k] = reinterpret_cast<const float*>(ctx->peer_base[k]) + buf;
+    r.pr.remote_flag[k] = reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(ctx->peer_base[k]) + kPeerFlagsOffset) + ctx->tp_rank;
+  }
+  r.pr.local_flag = reinterpret_cast<const unsigned long long*>(reinterpret_cast<char*>(ctx->peer_base[ctx->tp_rank]) + kPeerFlagsOffset);
+  r.pr.step = ctx->peer_step;
+  r.pr.phase = (unsigned)index + 1;
+  r.pr.dev_err = ctx->dev_err;
+  return r;
+}
+
 template <typename WT>
 int32_t enqueue_step_t(Session* S, cudaStream_t st, bool with_head) {
   Model* M = S->m;
@@ -806,15 +856,17 @@ int32_t enqueue_step_t(Session* S, cudaStream_t st, bool with_head) {
   const int B = S->B, hid = c.hidden;
   const int L = c.n_layers;
   const size_t norm_smem = (size_t)hid * sizeof(float);
+  RowParallelOut prev;             // the down_proj of the previous layer
+  prev.out = S->delta; prev.nccl = false;
   for (int l = 0; l < L; ++l) {
     LayerWeights& W = M->layers[l];
     // residual add of the previous MLP (or the embedding gather) + attention RMSNorm
-    if (!(g_debug_skip & 4) || l == 0)
-      LMB_CUDA(launch_k(add_rmsnorm_kernel<WT>, dim3(B), dim3(kNormThreads), norm_smem, st, S->x,
-                        l == 0 ? (const float*)nullptr : (const float*)S->delta, l == 0 ? (const int*)S->tokens : (const int*)nullptr,
-                        reinterpret_cast<const WT*>(M->embed), c.vocab, (const float*)W.attn_norm,
-                        reinterpret_cast<WT*>(S->xn), S->Bp, hid, c.rms_eps,
-                        (S->capture_on && l > 0) ? S->capture + (int64_t)(l - 1) * B * hid : (float*)nullptr));
+    LMB_CUDA(launch_k(add_rmsnorm_kernel<WT>, dim3(B), dim3(kNormThreads), norm_smem, st, S->x,
+                      l == 0 ? (const float*)nullptr : (const float*)prev.out, l == 0 ? (const int*)S->tokens : (const int*)nullptr,
+                      reinterpret_cast<const WT*>(M->embed), c.vocab, (const float*)W.attn_norm,
+                      reinterpret_cast<WT*>(S->xn), S->Bp, hid, c.rms_eps,
+                      (S->capture_on && l > 0) ? S->capture + (int64_t)(l - 1) * B * hid : (float*)nullptr,
+                      l == 0 ? PeerReduce() : prev.pr));
     ctx->launches++;
     void* kv_layer = reinterpret_cast<char*>(S->kv) + (int64_t)l * S->kv_layer_stride * M->esz;
     {  // q/k/v projections + RoPE + KV append
@@ -823,7 +875,7 @@ int32_t enqueue_step_t(Session* S, cudaStream_t st, bool with_head) {
       p.q_out = S->qbuf; p.q_pitch = S->q_pitch;
       p.kv_layer = kv_layer; p.kv_batch_stride = S->kv_batch_stride; p.kv_head_stride = S->kv_head_stride;
       p.inv_freq = M->inv_freq; p.pos = S->pos; p.Hl = M->Hl; p.KVl = M->KVl; p.D = M->D;
-      if (!(g_debug_skip & 2)) LMB_TRY(gemv_launch(ctx, dt, p, st));
+      LMB_TRY(gemv_launch(ctx, dt, p, st));
     }
     {  // attention over the cache; the result is the tiled input of o_proj
       AttnParams a;
@@ -833,46 +885,47 @@ int32_t enqueue_step_t(Session* S, cudaStream_t st, bool with_head) {
       a.keys_per_cta = S->keys_per_cta; a.nsplit = S->nsplit;
       a.scale = 1.0f / sqrtf((float)M->D);
       a.part_o = S->part_o; a.part_ml = S->part_ml; a.out = S->attn_out; a.out_tiled_bp = S->Bp;
-      if (!(g_debug_skip & 1)) LMB_TRY(attn_decode_launch(ctx, dt, a, st));
+      LMB_TRY(attn_decode_launch(ctx, dt, a, st));
     }
+    RowParallelOut ro = row_parallel_out(S, 2 * l);
     {  // o_proj (row-parallel under TP)
       GemvParams p = gemv_params(S, W.wo, M->m_o, S->p_o, S->attn_out);
-      p.epi = EPI_STORE_F32; p.out = S->delta; p.out_pitch = hid;
-      if (!(g_debug_skip & 2)) LMB_TRY(gemv_launch(ctx, dt, p, st));
-      if (c.tp_size > 1) LMB_TRY(nccl_allreduce_f32(ctx, S->delta, (int64_t)B * hid, st));
+      p.epi = EPI_STORE_F32; p.out = ro.out; p.out_pitch = hid;
+      LMB_TRY(gemv_launch(ctx, dt, p, st));
+      if (ro.nccl) LMB_TRY(nccl_allreduce_f32(ctx, ro.out, (int64_t)B * hid, st));
     }
-    if (!(g_debug_skip & 4))
-      LMB_CUDA(launch_k(add_rmsnorm_kernel<WT>, dim3(B), dim3(kNormThreads), norm_smem, st, S->x, (const float*)S->delta,
-                        (const int*)nullptr, (const WT*)nullptr, 0, (const float*)W.ffn_norm,
-                        reinterpret_cast<WT*>(S->xn), S->Bp, hid, c.rms_eps, (float*)nullptr));
+    LMB_CUDA(launch_k(add_rmsnorm_kernel<WT>, dim3(B), dim3(kNormThreads), norm_smem, st, S->x, (const float*)ro.out,
+                      (const int*)nullptr, (const WT*)nullptr, 0, (const float*)W.ffn_norm,
+                      reinterpret_cast<WT*>(S->xn), S->Bp, hid, c.rms_eps, (float*)nullptr, ro.pr));
     ctx->launches++;
     {  // gate/up + SiLU gate
       GemvParams p = gemv_params(S, W.wgu, M->m_gu, S->p_gu, S->xn);
       p.epi = EPI_SILU_GATE; p.act = S->act; p.n_act = M->inter_l;
-      if (!(g_debug_skip & 2)) LMB_TRY(gemv_launch(ctx, dt, p, st));
+      LMB_TRY(gemv_launch(ctx, dt, p, st));
     }
+    prev = row_parallel_out(S, 2 * l + 1);
     {  // down_proj (row-parallel under TP)
       GemvParams p = gemv_params(S, W.wdown, M->m_down, S->p_down, S->act);
-      p.epi = EPI_STORE_F32; p.out = S->delta; p.out_pitch = hid;
-      if (!(g_debug_skip & 2)) LMB_TRY(gemv_launch(ctx, dt, p, st));
-      if (c.tp_size > 1) LMB_TRY(nccl_allreduce_f32(ctx, S->delta, (int64_t)B * hid, st));
+      p.epi = EPI_STORE_F32; p.out = prev.out; p.out_pitch = hid;
+      LMB_TRY(gemv_launch(ctx, dt, p, st));
+      if (prev.nccl) LMB_TRY(nccl_allreduce_f32(ctx, prev.out, (int64_t)B * hid, st));
     }
   }
   // last residual add (+ final norm); without the head only the add is needed for the capture
-  LMB_CUDA(launch_k(add_rmsnorm_kernel<WT>, dim3(B), dim3(kNormThreads), norm_smem, st, S->x, (const float*)S->delta,
+  LMB_CUDA(launch_k(add_rmsnorm_kernel<WT>, dim3(B), dim3(kNormThreads), norm_smem, st, S->x, (const float*)prev.out,
                     (const int*)nullptr, (const WT*)nullptr, 0, (const float*)M->final_norm,
                     with_head ? reinterpret_cast<WT*>(S->xn) : (WT*)nullptr, S->Bp, hid, c.rms_eps,
-                    S->capture_on ? S->capture + (int64_t)(L - 1) * B * hid : (float*)nullptr));
+                    S->capture_on ? S->capture + (int64_t)(L - 1) * B * hid : (float*)nullptr, prev.pr));
   ctx->launches++;
   if (with_head) {
     GemvParams p = gemv_params(S, M->lm_head, M->m_head, S->p_head, S->xn);
     p.epi = EPI_STORE_F32; p.out = S->logits; p.out_pitch = S->logits_pitch;
-    if (!(g_debug_skip & 2)) LMB_TRY(gemv_launch(ctx, dt, p, st));
+    LMB_TRY(gemv_launch(ctx, dt, p, st));
     LMB_CUDA(launch_k(argmax_step_kernel, dim3(B), dim3(256), 0, st, (const float*)S->logits, S->logits_pitch, c.vocab,
                       S->tokens, S->tok_hist, (const int*)S->step_ctr, B));
     ctx->launches++;
   }
-  LMB_CUDA(launch_k(advance_kernel, dim3(1), dim3(1), 0, st, S->pos, S->step_ctr));
+  LMB_CUDA(launch_k(advance_kernel, dim3(1), dim3(1), 0, st, S->pos, S->step_ctr, ctx->peer_n > 1 ? ctx->peer_step : (unsigned long long*)nullptr));
   ctx->launches++;
   return LMB200_OK;
 }
@@ -965,7 +1018,7 @@ int32_t enqueue_whisper_step_t(Session* S, cudaStream_t st, bool with_head) {
                       S->tokens, S->tok_hist, (const int*)S->step_ctr, B));
     ctx->launches++;
   }
-  LMB_CUDA(launch_k(advance_kernel, dim3(1), dim3(1), 0, st, S->pos, S->step_ctr));
+  LMB_CUDA(launch_k(advance_kernel, dim3(1), dim3(1), 0, st, S->pos, S->step_ctr, (unsigned long long*)nullptr));
   ctx->launches++;
   return LMB200_OK;
 }

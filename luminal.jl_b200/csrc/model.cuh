@@ -50,6 +50,7 @@ struct LayerWeights {
 };
 
 struct Model {
+  bool tp_solo = false;        // profiling aid: shard of one rank, no all-reduce
   uint32_t magic = 0x4D4F444C;
   Ctx* ctx = nullptr;
   lmb200_model_config cfg{};
