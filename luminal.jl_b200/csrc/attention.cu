@@ -169,6 +169,46 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_bf16_kernel(const At
       p.part_ml[(slot * G + h) * 2 + 1] = lsum;
     }
   }
+  if (!p.counters) return;          // the splits are merged by attn_combine_kernel
+  // The CTA that finishes last for this (sequence, kv head) merges the splits itself: same
+  // arithmetic and order as attn_combine_kernel, without another launch.
+  __shared__ int is_last;
+  const int nvalid = (T + p.keys_per_cta - 1) / p.keys_per_cta;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const unsigned prev = atomicAdd(&p.counters[bk], 1u);
+    is_last = prev == (unsigned)nvalid - 1u;
+    if (is_last) p.counters[bk] = 0u;          // ready for the next launch
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  float* w_m = &sm_o[0][0][0];                  // [nvalid][G] maxima, then [nvalid][G] sums
+  float* w_l = w_m + p.nsplit * G;
+  const int64_t slot0 = (int64_t)bk * p.nsplit;
+  for (int i = tid; i < nvalid * G; i += kAttnThreads) {
+    w_m[i] = __ldcg(p.part_ml + (slot0 * G + i) * 2);
+    w_l[i] = __ldcg(p.part_ml + (slot0 * G + i) * 2 + 1);
+  }
+  __syncthreads();
+  __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out);
+  for (int i = tid; i < G * D; i += kAttnThreads) {
+    const int h = i / D, d = i - h * D;
+    float Mx = -CUDART_INF_F;
+    for (int sp = 0; sp < nvalid; ++sp) Mx = fmaxf(Mx, w_m[sp * G + h]);
+    float denom = 0.f;
+    for (int sp = 0; sp < nvalid; ++sp) denom += exp2f(w_m[sp * G + h] - Mx) * w_l[sp * G + h];
+    const float inv = 1.0f / denom;
+    float acc = 0.f;
+    const float* po = p.part_o + (slot0 * G + h) * D + d;
+#pragma unroll 8
+    for (int sp = 0; sp < nvalid; ++sp) acc += exp2f(w_m[sp * G + h] - Mx) * __ldcg(po + (int64_t)sp * G * D);
+    const int hl = kvl * G + h;
+    const int64_t o = p.out_tiled_bp > 0 ? Layout<__nv_bfloat16>::x_offset(b, hl * D + d, p.out_tiled_bp)
+                                         : (int64_t)b * p.out_pitch + hl * D + d;
+    out[o] = __float2bfloat16_rn(acc * inv);
+  }
 }
 
 // float32 path: one CTA per (sequence, kv head, split, q head of the group).
@@ -294,7 +334,10 @@ void attn_plan(const Ctx* ctx, int B, int KVl, int G, int D, int ctx_capacity, i
   *part_ml_floats = (int64_t)B * KVl * (*nsplit) * G * 2;
 }
 
-int32_t attn_decode_launch(Ctx* ctx, int dtype, const AttnParams& p, cudaStream_t stream) {
+int32_t attn_decode_launch(Ctx* ctx, int dtype, const AttnParams& p_in, cudaStream_t stream) {
+  AttnParams p = p_in;
+  // the in-kernel merge keeps the splits' (max, sum) pairs in the shared memory of the O tiles
+  if (dtype != LMB200_BF16 || 2 * p.nsplit * p.G > 32 * p.D) p.counters = nullptr;
   LMB_REQUIRE(p.keys_per_cta >= 64 && p.keys_per_cta % 64 == 0, "attention: keys_per_cta %d", p.keys_per_cta);
   LMB_REQUIRE(p.D % 16 == 0 && p.D >= 16 && p.D <= 256, "attention: head_dim %d", p.D);
   dim3 grid((unsigned)(p.B * p.KVl), (unsigned)p.nsplit, 1);
@@ -312,6 +355,7 @@ int32_t attn_decode_launch(Ctx* ctx, int dtype, const AttnParams& p, cudaStream_
     }
     ctx->launches++;
     LMB_CUDA(cudaGetLastError());
+    if (p.counters) return LMB200_OK;        // merged by the last CTA of each (sequence, kv head)
     LMB_CUDA(launch_k(attn_combine_kernel<__nv_bfloat16>, dim3(p.B * p.KVl * p.G), dim3(128), 0, stream, p));
   } else {
     grid.z = (unsigned)p.G;

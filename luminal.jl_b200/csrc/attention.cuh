@@ -24,6 +24,7 @@ struct AttnParams {
   void* out = nullptr;            // [B, out_pitch], same head-major order as q ...
   int out_pitch = 0;
   int out_tiled_bp = 0;           // ... or, when > 0, a GEMV activation buffer (Layout<T>::x_offset) of that padding
+  unsigned* counters = nullptr;   // [B*KVl] zeros: the last CTA of a (sequence, kv head) merges the splits (bf16); NULL: separate kernel
 };
 
 int32_t attn_configure();

@@ -145,6 +145,17 @@ __global__ void fill_kv_kernel(WT* kv, int64_t batch_stride, int64_t head_stride
 // accesses are independent float4s, so the kernel costs a couple of memory round trips.
 // xn is a GEMV activation buffer (Layout<WT>::x_offset) of batch padding Bp.  n % 4 == 0.
 constexpr int kNormThreads = 512;
+// four consecutive activation elements (inside one 8-k group, so 8- or 16-byte aligned) in one store
+__device__ __forceinline__ void store4(float* o, float a, float b, float c, float d) {
+  *reinterpret_cast<float4*>(o) = make_float4(a, b, c, d);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* o, float a, float b, float c, float d) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+  uint2 u;
+  u.x = *reinterpret_cast<const uint32_t*>(&lo);
+  u.y = *reinterpret_cast<const uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(o) = u;
+}
 template <typename WT>
 __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta,
                                                                    const int* __restrict__ tokens,
@@ -154,10 +165,17 @@ __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(float* __rest
                                                                    float* __restrict__ capture, PeerReduce pr) {
   extern __shared__ __align__(16) float row[];
   __shared__ float red[kNormThreads / 32];
-  pdl_launch_dependents();
-  pdl_wait();
   const int b = blockIdx.x, tid = threadIdx.x;
   const int n4 = n >> 2;
+  // the gains never change: they are fetched before this kernel waits for its producer
+  const float4* w4 = reinterpret_cast<const float4*>(w);
+  float4 g0 = make_float4(0.f, 0.f, 0.f, 0.f), g1 = g0;
+  if (xn) {
+    if (tid < n4) g0 = w4[tid];
+    if (tid + kNormThreads < n4) g1 = w4[tid + kNormThreads];
+  }
+  pdl_launch_dependents();
+  pdl_wait();
   // tensor parallel: delta is the sum of every rank's partial projection, read from the ranks'
   // exchange regions once all of them have signalled (all-reduce folded into this kernel)
   const bool peers = pr.n > 1 && !tokens;
@@ -184,11 +202,14 @@ __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(float* __rest
     for (int i = tid; i < n4; i += kNormThreads) {
       float4 v = xr[i];
       if (peers) {
-        float4 d = peer_load4(pr.part[0] + (int64_t)b * n + 4 * i);
-        for (int r = 1; r < pr.n; ++r) {
-          const float4 e = peer_load4(pr.part[r] + (int64_t)b * n + 4 * i);
-          d.x += e.x; d.y += e.y; d.z += e.z; d.w += e.w;
-        }
+        float4 e[8];                       // every rank's partial in flight at once, summed in rank order
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+          if (r < pr.n) e[r] = peer_load4(pr.part[r] + (int64_t)b * n + 4 * i);
+        float4 d = e[0];
+#pragma unroll
+        for (int r = 1; r < 8; ++r)
+          if (r < pr.n) { d.x += e[r].x; d.y += e[r].y; d.z += e[r].z; d.w += e[r].w; }
         v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
       } else if (dr) { const float4 d = dr[i]; v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w; }
       xr[i] = v;
@@ -207,15 +228,12 @@ __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(float* __rest
   const float var = tot * (1.0f / (float)n);
   const float inv = 1.0f / sqrtf(var + eps);
   if (xn) {
-    const float4* w4 = reinterpret_cast<const float4*>(w);
 #pragma unroll 4
     for (int i = tid; i < n4; i += kNormThreads) {
-      const float4 v = rs[i], g = w4[i];
+      const float4 v = rs[i];
+      const float4 g = i == tid ? g0 : (i == tid + kNormThreads ? g1 : w4[i]);
       WT* o = xn + Layout<WT>::x_offset(b, 4 * i, Bp);   // 4 consecutive k stay inside one 8-k group
-      o[0] = from_f32<WT>((v.x * inv) * g.x);
-      o[1] = from_f32<WT>((v.y * inv) * g.y);
-      o[2] = from_f32<WT>((v.z * inv) * g.z);
-      o[3] = from_f32<WT>((v.w * inv) * g.w);
+      store4(o, (v.x * inv) * g.x, (v.y * inv) * g.y, (v.z * inv) * g.z, (v.w * inv) * g.w);
     }
   }
 }
@@ -885,6 +903,7 @@ int32_t enqueue_step_t(Session* S, cudaStream_t st, bool with_head) {
       a.keys_per_cta = S->keys_per_cta; a.nsplit = S->nsplit;
       a.scale = 1.0f / sqrtf((float)M->D);
       a.part_o = S->part_o; a.part_ml = S->part_ml; a.out = S->attn_out; a.out_tiled_bp = S->Bp;
+      a.counters = S->attn_counters;
       LMB_TRY(attn_decode_launch(ctx, dt, a, st));
     }
     RowParallelOut ro = row_parallel_out(S, 2 * l);
@@ -959,6 +978,7 @@ int32_t enqueue_whisper_step_t(Session* S, cudaStream_t st, bool with_head) {
     a.keys_per_cta = kpc; a.nsplit = nsplit;
     a.scale = 1.0f;                      // the scale is already in q and k
     a.part_o = S->part_o; a.part_ml = S->part_ml; a.out = S->attn_out; a.out_tiled_bp = S->Bp;
+      a.counters = S->attn_counters;
     return attn_decode_launch(ctx, dt, a, st);
   };
   for (int l = 0; l < L; ++l) {
@@ -1149,6 +1169,7 @@ extern "C" int32_t lmb200_session_create(lmb200_model hm, int32_t batch, int32_t
   alloc((void**)&S->gemv_counters, (int64_t)max_cnt * 4);
   alloc((void**)&S->part_o, po * 4);
   alloc((void**)&S->part_ml, pml * 4);
+  alloc((void**)&S->attn_counters, (int64_t)S->B * M->KVl * 4);
   if (rc == LMB200_OK && cudaStreamSynchronize(ctx->stream) != cudaSuccess) rc = fail(LMB200_ECUDA, "session_create: sync failed");
   if (rc != LMB200_OK) { lmb200_session_destroy(reinterpret_cast<lmb200_session>(S)); return rc; }
   *out = reinterpret_cast<lmb200_session>(S);
@@ -1165,7 +1186,7 @@ extern "C" int32_t lmb200_session_destroy(lmb200_session h) {
   cudaFree(S->kv); cudaFree(S->x); cudaFree(S->delta); cudaFree(S->logits); cudaFree(S->xn); cudaFree(S->qbuf);
   cudaFree(S->attn_out); cudaFree(S->act); cudaFree(S->tokens); cudaFree(S->pos); cudaFree(S->step_ctr);
   cudaFree(S->tok_hist); cudaFree(S->prompt); cudaFree(S->gemv_partials); cudaFree(S->gemv_counters);
-  cudaFree(S->part_o); cudaFree(S->part_ml); cudaFree(S->capture);
+  cudaFree(S->part_o); cudaFree(S->part_ml); cudaFree(S->attn_counters); cudaFree(S->capture);
   S->magic = 0;
   delete S;
   return LMB200_OK;
@@ -1513,6 +1534,7 @@ extern "C" int32_t lmb200_decode_attention_splitkv(lmb200_session h, int32_t lay
   a.keys_per_cta = S->keys_per_cta; a.nsplit = S->nsplit;
   a.scale = 1.0f / sqrtf((float)M->D);
   a.part_o = S->part_o; a.part_ml = S->part_ml; a.out = out_dptr; a.out_pitch = M->Hl * M->D;
+  a.counters = S->attn_counters;
   LMB_TRY(attn_decode_launch(ctx, M->cfg.dtype, a, ctx->stream));
   return LMB200_OK;
 }

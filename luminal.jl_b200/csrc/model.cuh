@@ -98,6 +98,7 @@ struct Session {
   unsigned* gemv_counters = nullptr;
   float* part_o = nullptr;
   float* part_ml = nullptr;
+  unsigned* attn_counters = nullptr;   // [B*KVl], zero between launches
   int keys_per_cta = 0, nsplit = 0;
   GemvPlan p_qkv, p_o, p_gu, p_down, p_head, p_qc;
   // Whisper: cross-attention cache [L][B][H][cross_cap/16][32*D] and its split plan
