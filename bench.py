@@ -302,12 +302,12 @@ def main():
                     "h2d_bytes_per_step": BATCH * 4, "d2h_bytes_per_step": BATCH * 4, "ms_per_step": e2e_ms / e2e_steps},
             "gpu_launches": int(launches),
             "clocks": clocks,
-            "roofline": {"kernel": "attn_decode_bf16_kernel<128> + attn_combine_kernel (per layer)", "bound": "hbm",
+            "roofline": {"kernel": "attn_decode_bf16_kernel<128> (per layer; the last CTA of each sequence and kv head merges the splits)", "bound": "hbm",
                          "achieved": attn_gbs, "peak": peak, "unit": "GB/s", "frac": attn_gbs / peak,
                          "peak_kind": peak_kind,
                          # dram__bytes_read + write of one launch from the ncu capture in
                          # profiles/attn_decode_bf16_llama3_8b_b32_ctx8190.md, scaled by keys x local kv heads
-                         "traffic": int(1.0841e9 * (KVl * T_mid) / (8 * 8190.0)) if cfg["n_heads"] == 32 else None,
+                         "traffic": int(1.0793e9 * (KVl * T_mid) / (8 * 8190.0)) if cfg["n_heads"] == 32 else None,
                          "bytes_per_launch": attn_bytes,
                          "ms_per_launch": attn_ms},
             "step_hbm": {"bytes_per_step_per_gpu": step_bytes, "achieved": step_gbs, "peak": peak, "unit": "GB/s",
