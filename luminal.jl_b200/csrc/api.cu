@@ -293,6 +293,7 @@ extern "C" int32_t lmb200_init(int32_t device, lmb200_ctx* out) {
   if (rc == LMB200_OK) rc = attn_configure();
   if (rc == LMB200_OK) rc = flash_tc_configure();
   if (rc == LMB200_OK) rc = step_kernels_configure();
+  if (rc == LMB200_OK) rc = prefill_configure();
   if (rc != LMB200_OK) { cudaFreeHost(c->dev_err); cudaStreamDestroy(c->own_stream); delete c; return rc; }
   *out = reinterpret_cast<lmb200_ctx>(c);
   return LMB200_OK;

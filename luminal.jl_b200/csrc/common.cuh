@@ -122,6 +122,13 @@ Ctx* ctx_from(lmb200_ctx h);
 int32_t check_device_error(Ctx* ctx);
 int32_t nccl_allreduce_f32(Ctx* ctx, void* dptr, int64_t count, cudaStream_t stream);
 
+// Strided view of the tensors of a tensor-core flash attention launch (elements, bf16)
+struct FlashView {
+  int H = 1, G = 1;                 // query heads per batch entry; query heads per kv head
+  int64_t q_b = 0, q_h = 0, q_s = 0;    // q and out: batch, head, position strides
+  int64_t k_b = 0, k_h = 0, k_s = 0;    // k and v
+};
+
 static inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 static inline int64_t round_up(int64_t a, int64_t b) { return ceil_div(a, b) * b; }
 

@@ -47,7 +47,7 @@ __device__ __forceinline__ uint32_t canon(int row, int c8, int rows) {
 template <int D>
 __global__ void __launch_bounds__(kThreads, 1)
 flash_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
-                const __nv_bfloat16* __restrict__ v, int S, float scale, int causal, int* err) {
+                const __nv_bfloat16* __restrict__ v, const FlashView fv, int S, float scale, int causal, int* err) {
   using namespace tc;
   typedef Smem<D> SM;
   extern __shared__ __align__(1024) unsigned char smem[];
@@ -60,10 +60,13 @@ flash_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;      // heavy (late) causal tiles first
   const int q0 = qt * kBM;
-  const int64_t bh = blockIdx.y;
-  const __nv_bfloat16* qb = q + bh * (int64_t)S * D;
-  const __nv_bfloat16* kb = k + bh * (int64_t)S * D;
-  const __nv_bfloat16* vb = v + bh * (int64_t)S * D;
+  // blockIdx.y = batch * H + head; query head h reads kv head h / G (G = 1: an op with H kv heads)
+  const int bi = (int)blockIdx.y / fv.H, hi = (int)blockIdx.y - bi * fv.H;
+  const __nv_bfloat16* qb = q + bi * fv.q_b + hi * fv.q_h;
+  const __nv_bfloat16* kb = k + bi * fv.k_b + (hi / fv.G) * fv.k_h;
+  const __nv_bfloat16* vb = v + bi * fv.k_b + (hi / fv.G) * fv.k_h;
+  __nv_bfloat16* ob_base = out + bi * fv.q_b + hi * fv.q_h;
+  const int64_t q_s = fv.q_s, k_s = fv.k_s;
   const int k_stop = causal ? min(S, q0 + kBM) : S;
   const int n_tiles = (k_stop + kBN - 1) / kBN;
 
@@ -91,7 +94,7 @@ flash_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict
     for (int i = lt; i < kBM * (D / 8); i += 128) {
       const int row = i / (D / 8), c8 = i - row * (D / 8);
       const int qi = q0 + row;
-      cp_async16(sQ + canon(row, c8, kBM), qb + (int64_t)min(qi, S - 1) * D + c8 * 8, qi < S ? 16u : 0u);
+      cp_async16(sQ + canon(row, c8, kBM), qb + (int64_t)min(qi, S - 1) * q_s + c8 * 8, qi < S ? 16u : 0u);
     }
     cp_async_commit();
     auto signal_oldest = [&](int j) {               // tile j has landed in its stage
@@ -107,7 +110,7 @@ flash_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict
       for (int i = lt; i < kBN * (D / 8); i += 128) {
         const int row = i / (D / 8), c8 = i - row * (D / 8);
         const int key = j * kBN + row;
-        const int64_t src = (int64_t)min(key, S - 1) * D + c8 * 8;
+        const int64_t src = (int64_t)min(key, S - 1) * k_s + c8 * 8;
         const uint32_t nb = key < S ? 16u : 0u;
         cp_async16(sK + canon(row, c8, kBN), kb + src, nb);
         cp_async16(sV + canon(row, c8, kBN), vb + src, nb);
@@ -253,7 +256,7 @@ flash_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict
     if (n_tiles >= 1) accumulate(n_tiles - 1, alpha_pending);
     if (qi < S) {
       const float inv = 1.0f / l;
-      __nv_bfloat16* ob = out + bh * (int64_t)S * D + (int64_t)qi * D;
+      __nv_bfloat16* ob = ob_base + (int64_t)qi * q_s;
 #pragma unroll
       for (int i = 0; i < D; i += 8) {
         uint4 w;
@@ -277,26 +280,37 @@ flash_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict
 
 int32_t flash_tc_configure() {
   LMB_CUDA(cudaFuncSetAttribute(flash_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<128>::total + 1024));
+  LMB_CUDA(cudaFuncSetAttribute(flash_tc_kernel<96>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<96>::total + 1024));
   LMB_CUDA(cudaFuncSetAttribute(flash_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<64>::total + 1024));
   return LMB200_OK;
 }
 
-bool flash_tc_supported(int64_t D) { return D == 64 || D == 128; }
+bool flash_tc_supported(int64_t D) { return D == 64 || D == 96 || D == 128; }
 
-int32_t flash_tc_launch(Ctx* ctx, void* out, const void* q, const void* k, const void* v, int64_t BH, int64_t S, int64_t D,
-                        float scale, int causal) {
-  dim3 grid((unsigned)ceil_div(S, kBM), (unsigned)BH);
-  if (D == 128)
-    flash_tc_kernel<128><<<grid, kThreads, Smem<128>::total + 1024, ctx->stream>>>(
-        (__nv_bfloat16*)out, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (int)S, scale, causal,
-        ctx->dev_err);
-  else
-    flash_tc_kernel<64><<<grid, kThreads, Smem<64>::total + 1024, ctx->stream>>>(
-        (__nv_bfloat16*)out, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (int)S, scale, causal,
-        ctx->dev_err);
+// q, out: element (b, h, s, d) at b * q_b + h * q_h + s * q_s + d; k, v likewise with the k strides
+int32_t flash_tc_launch_view(Ctx* ctx, void* out, const void* q, const void* k, const void* v, const FlashView& fv, int64_t B,
+                             int64_t S, int64_t D, float scale, int causal, cudaStream_t stream) {
+  dim3 grid((unsigned)ceil_div(S, kBM), (unsigned)(B * fv.H));
+#define LMB_FLASH(DD)                                                                                                   \
+  flash_tc_kernel<DD><<<grid, kThreads, Smem<DD>::total + 1024, stream>>>(                                             \
+      (__nv_bfloat16*)out, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, fv, (int)S, scale, causal, \
+      ctx->dev_err)
+  if (D == 128) LMB_FLASH(128);
+  else if (D == 96) LMB_FLASH(96);
+  else if (D == 64) LMB_FLASH(64);
+  else return fail(LMB200_EINVAL, "flash attention: head_dim %lld has no tensor-core kernel", (long long)D);
+#undef LMB_FLASH
   ctx->launches++;
   LMB_CUDA(cudaGetLastError());
   return LMB200_OK;
+}
+
+int32_t flash_tc_launch(Ctx* ctx, void* out, const void* q, const void* k, const void* v, int64_t BH, int64_t S, int64_t D,
+                        float scale, int causal) {
+  FlashView fv;                       // [B*H, S, D] contiguous, as the op's tensors are
+  fv.H = 1; fv.G = 1;
+  fv.q_b = fv.k_b = S * D; fv.q_h = fv.k_h = 0; fv.q_s = fv.k_s = D;
+  return flash_tc_launch_view(ctx, out, q, k, v, fv, BH, S, D, scale, causal, ctx->stream);
 }
 
 }  // namespace lmb

@@ -1051,6 +1051,25 @@ int32_t enqueue_step(Session* S, cudaStream_t st, bool with_head) {
                                         : enqueue_step_t<float>(S, st, with_head);
 }
 
+// Final norm + head + greedy token on the residual rows already in S->x (after the GEMM prefill).
+int32_t enqueue_head_bf16(Session* S, cudaStream_t st) {
+  Model* M = S->m;
+  Ctx* ctx = M->ctx;
+  const lmb200_model_config& c = M->cfg;
+  const int B = S->B, hid = c.hidden;
+  LMB_CUDA(launch_k(add_rmsnorm_kernel<__nv_bfloat16>, dim3(B), dim3(kNormThreads), (size_t)hid * sizeof(float), st, S->x,
+                    (const float*)nullptr, (const int*)nullptr, (const __nv_bfloat16*)nullptr, 0, (const float*)M->final_norm,
+                    reinterpret_cast<__nv_bfloat16*>(S->xn), S->Bp, hid, c.rms_eps, (float*)nullptr, PeerReduce()));
+  ctx->launches++;
+  GemvParams p = gemv_params(S, M->lm_head, M->m_head, S->p_head, S->xn);
+  p.epi = EPI_STORE_F32; p.out = S->logits; p.out_pitch = S->logits_pitch;
+  LMB_TRY(gemv_launch(ctx, c.dtype, p, st));
+  LMB_CUDA(launch_k(argmax_step_kernel, dim3(B), dim3(256), 0, st, (const float*)S->logits, S->logits_pitch, c.vocab,
+                    S->tokens, S->tok_hist, (const int*)S->step_ctr, B));
+  ctx->launches++;
+  return LMB200_OK;
+}
+
 void drop_graphs(Session* S) {
   if (S->graph_full) cudaGraphExecDestroy(S->graph_full);
   if (S->graph_body) cudaGraphExecDestroy(S->graph_body);
@@ -1340,6 +1359,20 @@ extern "C" int32_t lmb200_prefill(lmb200_session h, const int32_t* tokens, int32
     S->prompt_cap = 0;
     LMB_TRY(dmalloc((void**)&S->prompt, (int64_t)n * B * 4, false, ctx->stream));
     S->prompt_cap = (int64_t)n * B;
+  }
+  if (prefill_gemm_ok(S, n)) {
+    // every position at once: GEMMs + flash attention, then the head on the last position
+    LMB_CUDA(cudaMemcpyAsync(S->prompt, tokens, (size_t)n * B * 4, cudaMemcpyHostToDevice, ctx->stream));
+    LMB_TRY(prefill_gemm(S, S->prompt, n, ctx->stream));
+    LMB_CUDA(cudaMemsetAsync(S->step_ctr, 0, 4, ctx->stream));
+    LMB_TRY(enqueue_head_bf16(S, ctx->stream));
+    const int new_pos = S->host_pos + n;
+    LMB_CUDA(cudaMemcpyAsync(S->pos, &new_pos, 4, cudaMemcpyHostToDevice, ctx->stream));
+    LMB_CUDA(cudaStreamSynchronize(ctx->stream));
+    S->host_pos = new_pos;
+    if (logits_out) LMB_TRY(copy_logits_out(S, logits_out));
+    LMB_CUDA(cudaStreamSynchronize(ctx->stream));
+    return check_device_error(ctx);
   }
   std::vector<int32_t> tr((size_t)n * B);       // [n][B]
   for (int b = 0; b < B; ++b)

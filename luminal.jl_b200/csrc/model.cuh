@@ -115,6 +115,10 @@ struct Session {
 };
 
 int32_t step_kernels_configure();
+// prompt phase as GEMMs + flash attention (csrc/prefill.cu)
+int32_t prefill_configure();
+bool prefill_gemm_ok(const Session* S, int n);
+int32_t prefill_gemm(Session* S, const int* tokens_dev, int n, cudaStream_t st);
 Model* model_from(lmb200_model h);
 Session* session_from(lmb200_session h);
 

@@ -1,0 +1,398 @@
+// Prompt phase of the Llama / Phi-3 path (bf16): all positions of all sequences at once.
+//
+// The reference runs the model over the whole prompt as one graph -- Linear on [B, S, hidden]
+// through batch_matmul (src/Execution.jl:12-54), SelfAttention with a materialised [B, H, S, S]
+// score tensor and a -1e9 mask (src/NN.jl:343-387).  Here the Linears are one tensor-core GEMM
+// each (tcgen05.mma, accumulators in TMEM) and attention is the tensor-core flash kernel with
+// grouped kv heads; K and V are also appended to the decode cache.
+//
+// gemm_tc_kernel: acc[row, token] = sum_k W[row, k] * X[token, k]
+//   one CTA = 128 weight rows x 128 tokens, k in steps of 128 through a 3-stage ring:
+//   warp 5      : bulk copies of 32 KB weight units (already in the tensor core's layout),
+//   warps 6..9  : cp.async 16-byte chunks of the row-major activations into the same layout,
+//   warp 4      : one thread issues tcgen05.mma 128 x 128 x 16,
+//   warps 0..3  : epilogue, one weight row per thread, tcgen05.ld 32 tokens at a time:
+//                 store float32 / SiLU(gate) * up / RoPE + q, k, v (and the cache).
+#include <math_constants.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include "model.cuh"
+#include "tc.cuh"
+
+namespace lmb {
+
+int32_t flash_tc_launch_view(Ctx* ctx, void* out, const void* q, const void* k, const void* v, const FlashView& fv, int64_t B,
+                             int64_t S, int64_t D, float scale, int causal, cudaStream_t stream);
+bool flash_tc_supported(int64_t D);
+
+namespace {
+
+constexpr int kGemmBN = 128;
+constexpr int kGemmStages = 3;
+constexpr int kGemmThreads = 10 * 32;
+constexpr int kUnitBytes = 32768;
+constexpr float kInvLn2 = 1.4426950408889634f;
+constexpr float kHalfPi = 1.5707963267948966f;
+
+enum GemmEpilogue { GEMM_STORE_F32 = 0, GEMM_SILU_GATE = 1, GEMM_QKV_ROPE = 2 };
+
+struct GemmParams {
+  const __nv_bfloat16* W = nullptr;     // canonical 128 x 128 units, unit (row group, k step) at (rg * KS + ks) * 16384
+  const __nv_bfloat16* X = nullptr;     // [T, ldx] row-major
+  int ldx = 0, T = 0, rows = 0, K = 0;
+  int epi = GEMM_STORE_F32;
+  float* out = nullptr;                 // GEMM_STORE_F32: out[token * ldo + row]
+  int ldo = 0;
+  __nv_bfloat16* act = nullptr;         // GEMM_SILU_GATE: act[token * ld_act + i], rows interleaved 8 gate / 8 up
+  int ld_act = 0, n_act = 0;
+  // GEMM_QKV_ROPE: token t = b * n_seq + s sits at position pos0 + s of sequence b
+  __nv_bfloat16* q = nullptr;           // [T, ldq]: local head * D + d
+  __nv_bfloat16* kbuf = nullptr;        // [T, ldkv]: local kv head * D + d
+  __nv_bfloat16* vbuf = nullptr;
+  int ldq = 0, ldkv = 0;
+  __nv_bfloat16* kv_layer = nullptr;    // the decode cache of this layer
+  int64_t kv_batch_stride = 0, kv_head_stride = 0;
+  const float* inv_freq = nullptr;
+  int pos0 = 0, n_seq = 1, Hl = 0, KVl = 0, D = 0;
+};
+
+__device__ __forceinline__ uint32_t canon(int row, int c8, int rows) {
+  return (uint32_t)(c8 * (rows * 16) + (row >> 3) * 128 + (row & 7) * 16);
+}
+
+// v[i] = accumulator of (row, token t0 + i).  Rows g and g+8 of a 16-row block, which the fused
+// epilogues combine, are 8 lanes apart.
+__device__ __forceinline__ void gemm_epilogue(const GemmParams& p, float (&v)[32], int row, int t0) {
+  const int rb = row >> 4, rr = row & 15, g = rr & 7, hi = rr >> 3;
+  if (p.epi == GEMM_STORE_F32) {
+    if (row < p.rows) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (t0 + i < p.T) p.out[(int64_t)(t0 + i) * p.ldo + row] = v[i];
+    }
+    return;
+  }
+  float w[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) w[i] = __shfl_xor_sync(0xffffffffu, v[i], 8);
+  if (row >= p.rows) return;
+  if (p.epi == GEMM_SILU_GATE) {
+    const int o = rb * 8 + g;
+    if (hi == 0 && o < p.n_act) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        if (t0 + i < p.T) {
+          const float a = v[i], u = w[i];
+          const float ex = exp2f((a * -1.0f) * kInvLn2);          // src/HighLevelOps.jl:153-160
+          const float sg = 1.0f / (1.0f + ex);
+          p.act[(int64_t)(t0 + i) * p.ld_act + o] = __float2bfloat16_rn((a * sg) * u);
+        }
+      }
+    }
+    return;
+  }
+  // GEMM_QKV_ROPE
+  const int D = p.D, tiles_per_head = D >> 4, half = D >> 1;
+  const int hs = rb / tiles_per_head, jj = rb - hs * tiles_per_head;
+  if (hs < p.Hl + p.KVl) {
+    const int d0 = 8 * jj + g;                         // rows g / g+8 are the pair (d0, d0 + D/2), src/NN.jl:253-303
+    const int d = hi ? d0 + half : d0;
+    const float f = p.inv_freq[d0];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const int t = t0 + i;
+      if (t < p.T) {
+        const int b = t / p.n_seq, pos = p.pos0 + (t - b * p.n_seq);
+        const float ang = (float)pos * f;
+        const float sn = sinf(ang), cs = sinf(kHalfPi + ang * -1.0f);
+        const float o = hi ? (w[i] * sn + v[i] * cs) : (v[i] * cs + (w[i] * sn) * -1.0f);
+        const __nv_bfloat16 ob = __float2bfloat16_rn(o);
+        if (hs < p.Hl) {
+          p.q[(int64_t)t * p.ldq + hs * D + d] = ob;
+        } else {
+          const int kvh = hs - p.Hl;
+          p.kbuf[(int64_t)t * p.ldkv + kvh * D + d] = ob;
+          p.kv_layer[b * p.kv_batch_stride + kvh * p.kv_head_stride + kcache_offset(pos, d, D)] = ob;
+        }
+      }
+    }
+  } else {
+    const int kvh = hs - p.Hl - p.KVl, d = 16 * jj + rr;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const int t = t0 + i;
+      if (t < p.T) {
+        const int b = t / p.n_seq, pos = p.pos0 + (t - b * p.n_seq);
+        const __nv_bfloat16 ob = __float2bfloat16_rn(v[i]);
+        p.vbuf[(int64_t)t * p.ldkv + kvh * D + d] = ob;
+        p.kv_layer[b * p.kv_batch_stride + kvh * p.kv_head_stride + vcache_offset(pos, d, D)] = ob;
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const GemmParams p, int* err) {
+  using namespace tc;
+  constexpr int kBBytes = kGemmBN * 256;                  // 128 tokens x 128 k, bf16
+  constexpr int kStage = kUnitBytes + kBBytes;
+  extern __shared__ __align__(1024) unsigned char smem[];
+  __shared__ __align__(8) uint64_t full_a[kGemmStages], full_b[kGemmStages], empty[kGemmStages], acc_full;
+  __shared__ uint32_t tmem_slot;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int rg = blockIdx.x, t0 = blockIdx.y * kGemmBN;
+  const int KS = (p.K + 127) >> 7;
+  if (tid == 0) {
+    for (int s = 0; s < kGemmStages; ++s) { mbar_init(&full_a[s], 1); mbar_init(&full_b[s], 4); mbar_init(&empty[s], 1); }
+    mbar_init(&acc_full, 1);
+    mbar_init_fence();
+  }
+  if (warp == 4) tmem_alloc(&tmem_slot, kGemmBN);
+  fence_before();
+  __syncthreads();
+  fence_after();
+  const uint32_t tmem = tmem_slot;
+  bool dead = false;
+
+  if (warp >= 6) {
+    // activations: row-major [token, k] -> K-major core matrices
+    const int lt = tid - 6 * 32;
+    for (int ks = 0; ks < KS; ++ks) {
+      const int s = ks % kGemmStages;
+      mbar_wait(&empty[s], ((ks / kGemmStages) & 1) ^ 1, dead, err);
+      const uint32_t sB = smem_u32(smem + s * kStage + kUnitBytes);
+      for (int i = lt; i < kGemmBN * 16; i += 128) {
+        const int tok = i >> 4, c8 = i & 15;
+        const int t = t0 + tok, k = ks * 128 + c8 * 8;
+        const bool ok = t < p.T && k < p.K;
+        cp_async16(sB + canon(tok, c8, kGemmBN), p.X + (int64_t)(ok ? t : 0) * p.ldx + (ok ? k : 0), ok ? 16u : 0u);
+      }
+      cp_async_commit();
+      if (ks >= 1) {                               // the previous step's chunks have landed
+        cp_async_wait<1>();
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&full_b[(ks - 1) % kGemmStages]);
+      }
+    }
+    cp_async_wait<0>();
+    fence_async_smem();
+    __syncwarp();
+    if (lane == 0 && KS >= 1) mbar_arrive(&full_b[(KS - 1) % kGemmStages]);
+  } else if (warp == 5) {
+    // weights: one contiguous unit per k step
+    for (int ks = 0; ks < KS; ++ks) {
+      const int s = ks % kGemmStages;
+      mbar_wait(&empty[s], ((ks / kGemmStages) & 1) ^ 1, dead, err);
+      if (lane == 0) {
+        mbar_expect_tx(&full_a[s], (uint32_t)kUnitBytes);
+        bulk_g2s(smem + s * kStage, p.W + ((int64_t)rg * KS + ks) * 16384, (uint32_t)kUnitBytes, &full_a[s]);
+      }
+      __syncwarp();
+    }
+  } else if (warp == 4) {
+    constexpr uint32_t kIdesc = idesc_bf16(128, kGemmBN, false, false);
+    for (int ks = 0; ks < KS; ++ks) {
+      const int s = ks % kGemmStages;
+      mbar_wait(&full_a[s], (ks / kGemmStages) & 1, dead, err);
+      mbar_wait(&full_b[s], (ks / kGemmStages) & 1, dead, err);
+      fence_after();
+      if (lane == 0) {
+        const uint32_t sa = smem_u32(smem + s * kStage);
+        const uint64_t adesc = smem_desc(sa, 2048, 128);
+        const uint64_t bdesc = smem_desc(sa + kUnitBytes, kGemmBN * 16, 128);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          mma_f16(tmem, adesc + (uint64_t)(j * (4096 >> 4)), bdesc + (uint64_t)(j * ((2 * kGemmBN * 16) >> 4)), kIdesc,
+                  (ks == 0 && j == 0) ? 0u : 1u);
+        commit(&empty[s]);
+        if (ks == KS - 1) commit(&acc_full);
+      }
+      __syncwarp();
+    }
+  } else {
+    mbar_wait(&acc_full, 0, dead, err);
+    fence_after();
+    const uint32_t lane_base = (uint32_t)(32 * warp) << 16;
+    const int row = rg * 128 + 32 * warp + lane;
+#pragma unroll 1
+    for (int ch = 0; ch < kGemmBN / 32; ++ch) {
+      float v[32];
+      tmem_ld32(v, tmem + lane_base + ch * 32);
+      gemm_epilogue(p, v, row, t0 + ch * 32);
+    }
+    fence_before();
+  }
+  fence_before();
+  __syncthreads();
+  if (warp == 4) {
+    fence_after();
+    tmem_dealloc(tmem, kGemmBN);
+  }
+}
+
+constexpr size_t kGemmSmem = (size_t)kGemmStages * (kUnitBytes + kGemmBN * 256) + 1024;
+
+int32_t gemm_launch(Ctx* ctx, const GemmParams& p, cudaStream_t st) {
+  dim3 grid((unsigned)ceil_div(p.rows, 128), (unsigned)ceil_div(p.T, kGemmBN));
+  gemm_tc_kernel<<<grid, kGemmThreads, kGemmSmem, st>>>(p, ctx->dev_err);
+  ctx->launches++;
+  LMB_CUDA(cudaGetLastError());
+  return LMB200_OK;
+}
+
+// x[t, :] = embedding row of token t (zeros when the id is out of range, as _gather_kernel! does)
+__global__ void embed_rows_kernel(float* __restrict__ x, const int* __restrict__ tokens, const __nv_bfloat16* __restrict__ embed,
+                                  int vocab, int n) {
+  const int t = blockIdx.x;
+  const int tok = tokens[t];
+  const bool ok = tok >= 0 && tok < vocab;
+  const __nv_bfloat16* er = embed + (int64_t)(ok ? tok : 0) * n;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) x[(int64_t)t * n + i] = ok ? __bfloat162float(er[i]) : 0.f;
+}
+
+// x[t, :] += delta[t, :] (if given); xn[t, :] = bf16((x * recip(sqrt(mean(x*x) + eps))) * w)
+__global__ void __launch_bounds__(256) rmsnorm_rows_kernel(float* __restrict__ x, const float* __restrict__ delta,
+                                                           const float* __restrict__ w, __nv_bfloat16* __restrict__ xn, int n,
+                                                           float eps) {
+  extern __shared__ float row[];
+  __shared__ float red[8];
+  const int t = blockIdx.x, tid = threadIdx.x;
+  float* xr = x + (int64_t)t * n;
+  float ss = 0.f;
+  for (int i = tid; i < n; i += 256) {
+    float v = xr[i];
+    if (delta) { v += delta[(int64_t)t * n + i]; xr[i] = v; }
+    row[i] = v;
+    ss += v * v;
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+  if ((tid & 31) == 0) red[tid >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tot += red[i];
+  const float inv = 1.0f / sqrtf(tot * (1.0f / (float)n) + eps);
+  if (xn)
+    for (int i = tid; i < n; i += 256) xn[(int64_t)t * n + i] = __float2bfloat16_rn((row[i] * inv) * w[i]);
+}
+
+// the residual rows of each sequence's last prompt position -> the decode step's [B, n] buffer
+__global__ void last_rows_kernel(float* __restrict__ dst, const float* __restrict__ x, const float* __restrict__ delta, int n_seq,
+                                 int n) {
+  const int b = blockIdx.x;
+  const int64_t t = (int64_t)b * n_seq + n_seq - 1;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) dst[(int64_t)b * n + i] = x[t * n + i] + (delta ? delta[t * n + i] : 0.f);
+}
+
+struct Scratch {
+  void* p[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  int n = 0;
+  ~Scratch() { for (int i = 0; i < n; ++i) cudaFree(p[i]); }
+  template <typename T>
+  int32_t get(T** out, int64_t elems) {
+    void* q = nullptr;
+    if (cudaMalloc(&q, (size_t)elems * sizeof(T)) != cudaSuccess) {
+      cudaGetLastError();
+      return fail(LMB200_ENOMEM, "prefill: scratch allocation of %lld bytes failed", (long long)(elems * (int64_t)sizeof(T)));
+    }
+    p[n++] = q;
+    *out = reinterpret_cast<T*>(q);
+    return LMB200_OK;
+  }
+};
+
+}  // namespace
+
+int32_t prefill_configure() {
+  LMB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmem));
+  return LMB200_OK;
+}
+
+bool prefill_gemm_ok(const Session* S, int n) {
+  const Model* M = S->m;
+  const lmb200_model_config& c = M->cfg;
+  const char* e = getenv("LMB200_PREFILL");          // "steps": feed the prompt through the decode step
+  if (e && strcmp(e, "steps") == 0) return false;
+  return c.arch == LMB200_ARCH_LLAMA && c.dtype == LMB200_BF16 && S->host_pos == 0 && !S->capture_on && n >= 8 && flash_tc_supported(M->D) &&
+         c.hidden % 8 == 0 && M->inter_l % 8 == 0;
+}
+
+// tokens_dev: [B, n] int32, sequence-major.  On return the cache holds positions 0..n-1 of every
+// sequence and S->x the residual rows of the last position (the caller runs the final norm + head).
+int32_t prefill_gemm(Session* S, const int* tokens_dev, int n, cudaStream_t st) {
+  Model* M = S->m;
+  Ctx* ctx = M->ctx;
+  const lmb200_model_config& c = M->cfg;
+  const int B = S->B, hid = c.hidden, L = c.n_layers, D = M->D;
+  const int T = B * n;
+  const int qw = M->Hl * D, kvw = M->KVl * D;
+  Scratch sc;
+  float *x, *delta;
+  __nv_bfloat16 *xn, *q, *kb, *vb, *attn, *act;
+  LMB_TRY(sc.get(&x, (int64_t)T * hid));
+  LMB_TRY(sc.get(&delta, (int64_t)T * hid));
+  LMB_TRY(sc.get(&xn, (int64_t)T * hid));
+  LMB_TRY(sc.get(&q, (int64_t)T * qw));
+  LMB_TRY(sc.get(&kb, (int64_t)T * kvw));
+  LMB_TRY(sc.get(&vb, (int64_t)T * kvw));
+  LMB_TRY(sc.get(&attn, (int64_t)T * qw));
+  LMB_TRY(sc.get(&act, (int64_t)T * M->inter_l));
+  embed_rows_kernel<<<T, 256, 0, st>>>(x, tokens_dev, reinterpret_cast<const __nv_bfloat16*>(M->embed), c.vocab, hid);
+  ctx->launches++;
+  const size_t norm_smem = (size_t)hid * sizeof(float);
+  auto reduce = [&](float* buf) -> int32_t {          // row-parallel projection under tensor parallelism
+    if (c.tp_size > 1 && !M->tp_solo) return nccl_allreduce_f32(ctx, buf, (int64_t)T * hid, st);
+    return LMB200_OK;
+  };
+  FlashView fv;
+  fv.H = M->Hl; fv.G = M->G;
+  fv.q_b = (int64_t)n * qw; fv.q_h = D; fv.q_s = qw;
+  fv.k_b = (int64_t)n * kvw; fv.k_h = D; fv.k_s = kvw;
+  for (int l = 0; l < L; ++l) {
+    LayerWeights& W = M->layers[l];
+    rmsnorm_rows_kernel<<<T, 256, norm_smem, st>>>(x, l == 0 ? nullptr : delta, (const float*)W.attn_norm, xn, hid, c.rms_eps);
+    ctx->launches++;
+    {
+      GemmParams p;
+      p.W = reinterpret_cast<const __nv_bfloat16*>(W.wqkv); p.X = xn; p.ldx = hid; p.T = T; p.rows = M->m_qkv.rows; p.K = hid;
+      p.epi = GEMM_QKV_ROPE;
+      p.q = q; p.kbuf = kb; p.vbuf = vb; p.ldq = qw; p.ldkv = kvw;
+      p.kv_layer = reinterpret_cast<__nv_bfloat16*>(S->kv) + (int64_t)l * S->kv_layer_stride;
+      p.kv_batch_stride = S->kv_batch_stride; p.kv_head_stride = S->kv_head_stride;
+      p.inv_freq = M->inv_freq; p.pos0 = 0; p.n_seq = n; p.Hl = M->Hl; p.KVl = M->KVl; p.D = D;
+      LMB_TRY(gemm_launch(ctx, p, st));
+    }
+    LMB_TRY(flash_tc_launch_view(ctx, attn, q, kb, vb, fv, B, n, D, 1.0f / sqrtf((float)D), 1, st));
+    {
+      GemmParams p;
+      p.W = reinterpret_cast<const __nv_bfloat16*>(W.wo); p.X = attn; p.ldx = qw; p.T = T; p.rows = hid; p.K = qw;
+      p.epi = GEMM_STORE_F32; p.out = delta; p.ldo = hid;
+      LMB_TRY(gemm_launch(ctx, p, st));
+      LMB_TRY(reduce(delta));
+    }
+    rmsnorm_rows_kernel<<<T, 256, norm_smem, st>>>(x, delta, (const float*)W.ffn_norm, xn, hid, c.rms_eps);
+    ctx->launches++;
+    {
+      GemmParams p;
+      p.W = reinterpret_cast<const __nv_bfloat16*>(W.wgu); p.X = xn; p.ldx = hid; p.T = T; p.rows = M->m_gu.rows; p.K = hid;
+      p.epi = GEMM_SILU_GATE; p.act = act; p.ld_act = M->inter_l; p.n_act = M->inter_l;
+      LMB_TRY(gemm_launch(ctx, p, st));
+    }
+    {
+      GemmParams p;
+      p.W = reinterpret_cast<const __nv_bfloat16*>(W.wdown); p.X = act; p.ldx = M->inter_l; p.T = T; p.rows = hid; p.K = M->inter_l;
+      p.epi = GEMM_STORE_F32; p.out = delta; p.ldo = hid;
+      LMB_TRY(gemm_launch(ctx, p, st));
+      LMB_TRY(reduce(delta));
+    }
+  }
+  last_rows_kernel<<<B, 256, 0, st>>>(S->x, x, delta, n, hid);
+  ctx->launches++;
+  LMB_CUDA(cudaGetLastError());
+  LMB_CUDA(cudaStreamSynchronize(st));           // the scratch is freed on return
+  return LMB200_OK;
+}
+
+}  // namespace lmb
