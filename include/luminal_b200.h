@@ -166,6 +166,13 @@ int32_t lmb200_rope(lmb200_ctx ctx, float* out, const float* x, int64_t B, int64
  * downloads (tests, comparisons).  Replaces NN.Linear for a single position, src/NN.jl:22-35. */
 int32_t lmb200_linear_gemv(lmb200_ctx ctx, int32_t dtype, int32_t variant, int32_t rows, int32_t K,
                            int32_t batch, const float* w_host, const float* x_host, float* out_host);
+
+/* out[t, o] = sum_i x[t, i] * w[o, i] for many rows t at once (the prompt phase) through the
+ * tensor-core GEMM (bf16 operands, float32 accumulation): w [rows, K], x [n_tokens, K] and out
+ * [n_tokens, rows] are float32 row-major host arrays; K must be a multiple of 8.  Replaces
+ * NN.Linear -> batch_matmul on [B, S, in] (src/NN.jl:22-35, src/Execution.jl:12-54). */
+int32_t lmb200_prefill_gemm(lmb200_ctx ctx, int32_t rows, int32_t K, int32_t n_tokens, const float* w_host,
+                            const float* x_host, float* out_host);
 /* argmax over the last dim (first maximum), 0-based ids.  src/Decoding.jl:119-124 */
 int32_t lmb200_argmax(lmb200_ctx ctx, int32_t* out_ids_dptr, const float* x, int64_t rows, int64_t n);
 

@@ -10,8 +10,8 @@ from .device import B200Device, DeviceArray, device_count, from_device, get_devi
 from . import graph, nn, whisper
 from .execution import CompiledGraph, compile, execute
 from .graph import Graph, GraphTensor, constant, tensor
-from .session import Model, Session, WhisperDecoderModel, decode_attention_noalloc, greedy_generate, linear_gemv, shard_layout
+from .session import Model, Session, WhisperDecoderModel, decode_attention_noalloc, greedy_generate, linear_gemv, prefill_gemm, shard_layout
 
 __all__ = ["Graph", "GraphTensor", "tensor", "constant", "execute", "compile", "CompiledGraph", "graph", "nn", "whisper",
-           "B200Device", "DeviceArray", "Model", "Session", "WhisperDecoderModel", "greedy_generate", "decode_attention_noalloc", "shard_layout", "linear_gemv", "get_device", "to_device",
+           "B200Device", "DeviceArray", "Model", "Session", "WhisperDecoderModel", "greedy_generate", "decode_attention_noalloc", "shard_layout", "linear_gemv", "prefill_gemm", "get_device", "to_device",
            "from_device", "device_count", "LuminalB200Error", "F32", "BF16", "ROWMAJOR", "COLMAJOR"]

@@ -72,6 +72,7 @@ SIGNATURES = {
     "lmb200_rope": [_u64, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _f32],
     "lmb200_argmax": [_u64, _vp, _vp, _i64, _i64],
     "lmb200_linear_gemv": [_u64, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp],
+    "lmb200_prefill_gemm": [_u64, _i32, _i32, _i32, _vp, _vp, _vp],
     "lmb200_model_create": [_u64, C.POINTER(ModelConfig), C.POINTER(_u64)],
     "lmb200_shard_extent": [C.POINTER(ModelConfig), _i32, _pi32, _pi32],
     "lmb200_shard_map": [C.POINTER(ModelConfig), _i32, _i32, _i32, _pi32, _pi32, _pi32],

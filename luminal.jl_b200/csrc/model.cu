@@ -1537,6 +1537,48 @@ extern "C" int32_t lmb200_linear_gemv(lmb200_ctx hctx, int32_t dtype, int32_t va
   return rc;
 }
 
+extern "C" int32_t lmb200_prefill_gemm(lmb200_ctx hctx, int32_t rows, int32_t K, int32_t n_tokens, const float* w_host,
+                                       const float* x_host, float* out_host) {
+  Ctx* ctx = ctx_from(hctx);
+  if (!ctx) return LMB200_EINVAL;
+  LMB_REQUIRE(w_host && x_host && out_host, "prefill_gemm: null pointer");
+  LMB_REQUIRE(rows >= 1 && K >= 8 && K % 8 == 0 && n_tokens >= 1, "prefill_gemm: rows %d, K %d, tokens %d", rows, K, n_tokens);
+  LMB_CUDA(cudaSetDevice(ctx->device));
+  WMap m;
+  m.kind = MAP_PLAIN; m.rows = rows; m.K = K; m.src_rows[0] = rows; m.src_cols[0] = K;
+  finish_map(m);
+  void* W = nullptr;
+  float *ws = nullptr, *xs = nullptr, *out = nullptr;
+  int32_t rc = LMB200_OK;
+  auto alloc = [&](void** p, int64_t bytes) { if (rc == LMB200_OK) rc = dmalloc(p, bytes, true, ctx->stream); };
+  alloc(&W, tiled_elems(m, LMB200_BF16) * 2);
+  alloc((void**)&ws, (int64_t)rows * K * 4);
+  alloc((void**)&xs, (int64_t)n_tokens * K * 4);
+  alloc((void**)&out, (int64_t)n_tokens * rows * 4);
+  do {
+    if (rc != LMB200_OK) break;
+    if (cudaMemcpyAsync(ws, w_host, (size_t)rows * K * 4, cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess ||
+        cudaMemcpyAsync(xs, x_host, (size_t)n_tokens * K * 4, cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess) {
+      rc = fail(LMB200_ECUDA, "prefill_gemm: upload failed"); break;
+    }
+    FillSrc f{};
+    f.only_slot = -1; f.src[0] = ws;
+    Model tmp; tmp.ctx = ctx; tmp.cfg.dtype = LMB200_BF16;
+    rc = fill_tiled_dt(&tmp, W, m, f);
+    if (rc != LMB200_OK) break;
+    rc = prefill_linear(ctx, W, xs, n_tokens, rows, K, out, ctx->stream);
+    if (rc != LMB200_OK) break;
+    if (cudaMemcpyAsync(out_host, out, (size_t)n_tokens * rows * 4, cudaMemcpyDeviceToHost, ctx->stream) != cudaSuccess) {
+      rc = fail(LMB200_ECUDA, "prefill_gemm: download failed"); break;
+    }
+  } while (0);
+  cudaError_t se = cudaStreamSynchronize(ctx->stream);
+  if (rc == LMB200_OK && se != cudaSuccess) rc = fail(LMB200_ECUDA, "prefill_gemm: %s", cudaGetErrorString(se));
+  if (rc == LMB200_OK) rc = check_device_error(ctx);
+  cudaFree(W); cudaFree(ws); cudaFree(xs); cudaFree(out);
+  return rc;
+}
+
 extern "C" int32_t lmb200_session_kv_layer(lmb200_session h, int32_t layer, void** kv_dptr, int64_t* batch_stride,
                                            int64_t* head_stride) {
   Session* S = session_from(h);

@@ -119,6 +119,7 @@ int32_t step_kernels_configure();
 int32_t prefill_configure();
 bool prefill_gemm_ok(const Session* S, int n);
 int32_t prefill_gemm(Session* S, const int* tokens_dev, int n, cudaStream_t st);
+int32_t prefill_linear(Ctx* ctx, const void* W, const float* x_dev, int T, int rows, int K, float* out_dev, cudaStream_t st);
 Model* model_from(lmb200_model h);
 Session* session_from(lmb200_session h);
 

@@ -17,6 +17,8 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <algorithm>
+
 #include "model.cuh"
 #include "tc.cuh"
 
@@ -304,6 +306,31 @@ struct Scratch {
 };
 
 }  // namespace
+
+namespace {
+__global__ void f32_to_bf16_kernel(__nv_bfloat16* __restrict__ dst, const float* __restrict__ src, int64_t n) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+    dst[i] = __float2bfloat16_rn(src[i]);
+}
+}  // namespace
+
+// out[t, row] = sum_k x[t, k] * W[row, k]: W in the bf16 weight layout, x float32 row-major on the
+// device (rounded to bf16 here), out float32 [T, rows].
+int32_t prefill_linear(Ctx* ctx, const void* W, const float* x_dev, int T, int rows, int K, float* out_dev, cudaStream_t st) {
+  LMB_REQUIRE(K % 8 == 0, "prefill_gemm: K %d must be a multiple of 8", K);
+  Scratch sc;
+  __nv_bfloat16* xb;
+  LMB_TRY(sc.get(&xb, (int64_t)T * K));
+  const int64_t n = (int64_t)T * K;
+  f32_to_bf16_kernel<<<(unsigned)std::min<int64_t>(ceil_div(n, 256), 4096), 256, 0, st>>>(xb, x_dev, n);
+  ctx->launches++;
+  GemmParams p;
+  p.W = reinterpret_cast<const __nv_bfloat16*>(W); p.X = xb; p.ldx = K; p.T = T; p.rows = rows; p.K = K;
+  p.epi = GEMM_STORE_F32; p.out = out_dev; p.ldo = rows;
+  LMB_TRY(gemm_launch(ctx, p, st));
+  LMB_CUDA(cudaStreamSynchronize(st));
+  return LMB200_OK;
+}
 
 int32_t prefill_configure() {
   LMB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmem));

@@ -233,3 +233,15 @@ def linear_gemv(device, w, x, dtype="bf16", variant=0):
     _lib.call("lmb200_linear_gemv", device.handle, _dtype_code(dtype), int(variant), rows, K, batch,
               w.ctypes.data_as(C.c_void_p), x.ctypes.data_as(C.c_void_p), out.ctypes.data_as(C.c_void_p))
     return out
+
+
+def prefill_gemm(device, w, x):
+    """out[t, o] = sum_i x[t, i] * w[o, i] through the tensor-core prompt GEMM (bf16 operands)."""
+    w = np.ascontiguousarray(np.asarray(w, dtype=np.float32))
+    x = np.ascontiguousarray(np.asarray(x, dtype=np.float32))
+    rows, K = w.shape
+    assert x.shape[1] == K
+    out = np.empty((x.shape[0], rows), dtype=np.float32)
+    _lib.call("lmb200_prefill_gemm", device.handle, rows, K, x.shape[0], w.ctypes.data_as(C.c_void_p),
+              x.ctypes.data_as(C.c_void_p), out.ctypes.data_as(C.c_void_p))
+    return out

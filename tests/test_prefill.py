@@ -77,3 +77,15 @@ def test_gemm_prefill_phi3_width(lib_built, device):
         if not np.array_equal(fast[i].argmax(-1), slow[i].argmax(-1)):
             break
     sess.close(); model.close()
+
+
+@pytest.mark.parametrize("rows,K,tokens", [(128, 128, 128), (100, 72, 37), (384, 1024, 300), (1000, 2816, 129), (4608, 3072, 512)])
+def test_prefill_gemm_matches_float64(lib_built, device, rows, K, tokens):
+    L = lib_built
+    rng = np.random.default_rng(rows + tokens)
+    w = O.bf16_round(rng.standard_normal((rows, K), dtype=np.float32) * np.float32(0.05))
+    x = O.bf16_round(rng.standard_normal((tokens, K), dtype=np.float32))
+    got = L.prefill_gemm(device, w, x)
+    ref = x.astype(np.float64) @ w.astype(np.float64).T
+    assert got.shape == ref.shape
+    assert np.abs(got - ref).max() <= 2e-5 * max(1.0, np.abs(ref).max()) * np.sqrt(K / 32.0)
