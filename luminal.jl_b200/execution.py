@@ -161,3 +161,27 @@ def compile(graph, device=None):     # noqa: A001  (the reference's name)
 
 
 __all__ = ["execute", "execute_op", "run_op", "compile", "CompiledGraph"]
+
+
+def compile_fused(model, reg, inputs, device=None, batch=1, max_ctx=2048, dtype="f32", eps=1e-5):
+    """The fused counterpart of compile() for a whole nn.Llama / nn.Phi3: instead of one kernel per
+    primitive node, the model's registered weights (the same `reg` name -> tensor map and the same
+    node-id -> array `inputs` that execute() takes) fill a device-resident model with a KV cache, and
+    the returned Session runs prefill / decode_step / decode_n on it.  What the reference reaches by
+    re-running the graph over the growing prefix (examples/llama.jl:39-99) becomes one cached step."""
+    from .session import Model, Session
+    dev = device or get_device()
+    cfg = model.config
+    m = Model(dev, n_layers=cfg["n_layers"], hidden=cfg["hidden"], n_heads=cfg["n_heads"], n_kv_heads=cfg["n_kv_heads"],
+              intermediate=cfg["intermediate"], vocab=cfg["vocab"], eps=eps, rope_base=model.ROPE_BASE, dtype=dtype)
+    for name, t in reg.items():
+        data = inputs.get(t.id, model_graph_tensor(t))
+        if data is None:
+            raise KeyError(f"weight {name} (node {t.id}) has no data")
+        m.set_weight(name, data.numpy() if isinstance(data, DeviceArray) else np.asarray(data, dtype=np.float32))
+    return Session(m, batch, max_ctx)
+
+
+def model_graph_tensor(t):
+    """Data pre-loaded into the graph for tensor t (graph.tensors, as load_weights! fills it), or None."""
+    return t.graph_ref.tensors.get((t.id, 1))

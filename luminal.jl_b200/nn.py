@@ -154,6 +154,8 @@ class Llama:                                    # src/NN.jl:417-455
 
     def __init__(self, graph, reg=None, vocab_size=128256, hidden=4096, n_layers=32, n_heads=32, n_kv_heads=8,
                  intermediate=14336):
+        self.config = dict(n_layers=n_layers, hidden=hidden, n_heads=n_heads, n_kv_heads=n_kv_heads,
+                           intermediate=intermediate, vocab=vocab_size)
         self.layers = [TransformerBlock(hidden, n_heads, n_kv_heads, intermediate, graph, reg, f"model.layers.{i}")
                        for i in range(n_layers)]
         self.embedding = Embedding(vocab_size, hidden, graph, reg, "model.embed_tokens")

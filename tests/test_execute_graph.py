@@ -235,3 +235,37 @@ def test_flash_attention_op(lib_built, device, dtype, tol, shape, causal):
     ref = O.flash_attn_fast(q, k, v, scale, causal)
     got = out.float().cpu().numpy()
     assert np.abs(got - ref).max() / np.abs(ref).max() <= tol
+
+
+def test_fused_session_from_the_same_graph_inputs(lib_built, device):
+    """One nn.Llama, one registry, one input dict: run op by op with execute() (recomputing the whole
+    prefix per token, as the reference generates) and through compile_fused() with the KV cache."""
+    L = lib_built
+    cfg = O.CONFIGS["tiny_gqa128"]
+    w = O.synth_llama_weights(cfg, seed=8)
+    batch, seq, steps = 2, 6, 3
+    toks = O.synth_tokens(8, 1000, (batch, seq), cfg["vocab"])
+    g, reg = L.Graph(), {}
+    model = L.nn.Llama(g, reg, vocab_size=cfg["vocab"], hidden=cfg["hidden"], n_layers=cfg["n_layers"],
+                       n_heads=cfg["n_heads"], n_kv_heads=cfg["n_kv_heads"], intermediate=cfg["intermediate"])
+    model.ROPE_BASE = cfg["rope_base"]
+    weights = {t.id: w[n] for n, t in reg.items()}
+    sess = L.compile_fused(model, reg, weights, device, batch=batch, max_ctx=32)
+    logits = sess.prefill(toks.astype(np.int32))
+    seqs = toks.copy()
+    for step in range(steps):
+        gi, ri = L.Graph(), {}
+        mi = L.nn.Llama(gi, ri, vocab_size=cfg["vocab"], hidden=cfg["hidden"], n_layers=cfg["n_layers"],
+                        n_heads=cfg["n_heads"], n_kv_heads=cfg["n_kv_heads"], intermediate=cfg["intermediate"])
+        mi.ROPE_BASE = cfg["rope_base"]
+        inp = L.tensor(gi, list(seqs.shape))
+        out = mi(inp, 0)
+        inputs = {t.id: w[n] for n, t in ri.items()}
+        inputs[inp.id] = seqs.astype(np.float32)
+        full = L.execute(gi, out.id, inputs, device)[:, -1, :]
+        assert np.abs(full - logits).max() <= 1e-3
+        nxt = full.argmax(-1)
+        assert np.array_equal(nxt, logits.argmax(-1))
+        seqs = np.concatenate([seqs, nxt[:, None]], axis=1)
+        _, logits = sess.decode_step(nxt.astype(np.int32), want_logits=True)
+    sess.close()
