@@ -325,9 +325,19 @@ int32_t attn_configure() {
 
 void attn_plan(const Ctx* ctx, int B, int KVl, int G, int D, int ctx_capacity, int* keys_per_cta,
                int* nsplit, int64_t* part_o_floats, int64_t* part_ml_floats) {
-  int64_t want = round_up(ceil_div((int64_t)ctx_capacity * B * KVl, (int64_t)ctx->sm_count * 8), 64);
-  if (want < 64) want = 64;
-  if (want > 1024) want = 1024;
+  // Two CTAs are resident per SM (registers).  Pick the split whose CTAs fill whole waves of
+  // 2 x #SMs: cost = waves x (keys per CTA + a fixed per-CTA cost, about 96 keys' worth of q load,
+  // merge and partial store).  Few (sequence, kv head) pairs -- tensor-parallel shards -- want few,
+  // long splits in a single wave; many pairs want about 1024 keys per CTA.
+  const int64_t pairs = (int64_t)B * KVl, resident = (int64_t)ctx->sm_count * 2;
+  int64_t best_k = 64, best_cost = -1;
+  for (int64_t k = 64; k <= 2048; k += 64) {
+    const int64_t ns = ceil_div(ctx_capacity, k);
+    if (k > 64 && ceil_div(ctx_capacity, k - 64) == ns) continue;      // same split count with shorter CTAs exists
+    const int64_t cost = ceil_div(pairs * ns, resident) * (k + 96);
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best_k = k; }
+  }
+  const int64_t want = best_k;
   *keys_per_cta = (int)want;
   *nsplit = (int)ceil_div(ctx_capacity, want);
   *part_o_floats = (int64_t)B * KVl * (*nsplit) * G * D;
