@@ -1080,6 +1080,231 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const GemvParams
   if (tid == 0) { LMB_TRACE(9); LMB_TRACE_NS(11); }
 }
 
+// =============================================================================================
+// Cluster variant for small matrices.  The stream-K kernel folds a shared row group through
+// global scratch: store, fence, count, wait, fetch -- about 6 us after the last MMA, more than
+// the streaming itself once a matrix is a few tens of MB (tensor-parallel shards, q/k/v, o_proj).
+// Here a thread-block cluster of C CTAs owns one 128-row group, CTA c streams the c-th share of
+// its k range, and the partial accumulators are exchanged through distributed shared memory:
+// every CTA sends each peer the rows that peer finalises (128 / C of them), one cluster barrier,
+// then every CTA sums its rows over the C sources in rank order and runs their epilogue.
+// =============================================================================================
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_nctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;\n" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t dsmem_addr(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void dsmem_store4(uint32_t addr, float a, float b, float c, float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1,%2,%3,%4};\n" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+
+template <int N>
+__global__ void __launch_bounds__(kTcThreads, 1) gemv_cl_kernel(const GemvParams p, int* err) {
+  constexpr int kXStage = N * 256;
+  constexpr int kStage = kWStage + kXStage;
+  constexpr uint32_t kTmemCols = N < 32 ? 32 : N;     // an allocation is at least 32 columns
+  constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((128u >> 4) << 24);
+  extern __shared__ __align__(1024) unsigned char smem[];       // kStages stages, then recv[C][128 / C][N] floats
+  __shared__ __align__(8) uint64_t full_bar[kStages];
+  __shared__ __align__(8) uint64_t empty_bar[kStages];
+  __shared__ __align__(8) uint64_t acc_full;
+  __shared__ uint32_t tmem_base_slot;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int C = (int)cluster_nctarank(), c = (int)cluster_ctarank();
+  const int r = (int)blockIdx.x / C;                              // row group of this cluster
+  const int KS = (p.K + 127) >> 7;
+  const int ks0 = (int)((long long)c * KS / C), ks1 = (int)((long long)(c + 1) * KS / C);
+  const int n_steps = ks1 - ks0;
+  if (tid == 0) {
+#pragma unroll
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&acc_full, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_base_slot)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+  bool dead = false;
+  pdl_launch_dependents();
+
+  if (warp == 0) {
+    // ---------------- producer: weights before the dependency wait, activations after ----------------
+    uint64_t pol_w, pol_x;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;\n" : "=l"(pol_w));
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;\n" : "=l"(pol_x));
+    const __nv_bfloat16* W = reinterpret_cast<const __nv_bfloat16*>(p.W) + ((int64_t)r * KS + ks0) * 16384;
+    const __nv_bfloat16* X = reinterpret_cast<const __nv_bfloat16*>(p.x) + (int64_t)ks0 * (128 * N);
+    const int n_pre = n_steps < kStages ? n_steps : kStages;
+    if (lane == 0) {
+      for (int i = 0; i < n_pre; ++i) {
+        mbar_expect_tx(&full_bar[i], (uint32_t)kStage);
+        bulk_g2s(smem + i * kStage, W + (int64_t)i * 16384, (uint32_t)kWStage, &full_bar[i], pol_w);
+      }
+    }
+    pdl_wait();
+    if (lane == 0) {
+      for (int i = 0; i < n_pre; ++i)
+        bulk_g2s(smem + i * kStage + kWStage, X + (int64_t)i * (128 * N), (uint32_t)kXStage, &full_bar[i], pol_x);
+    }
+    __syncwarp();
+    for (int i = n_pre; i < n_steps; ++i) {
+      const int s = i % kStages, k = i / kStages;
+      mbar_wait(&empty_bar[s], (k & 1) ^ 1, dead, err);
+      if (lane == 0) {
+        unsigned char* sp = smem + s * kStage;
+        mbar_expect_tx(&full_bar[s], (uint32_t)kStage);
+        bulk_g2s(sp, W + (int64_t)i * 16384, (uint32_t)kWStage, &full_bar[s], pol_w);
+        bulk_g2s(sp + kWStage, X + (int64_t)i * (128 * N), (uint32_t)kXStage, &full_bar[s], pol_x);
+      }
+      __syncwarp();
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issue ----------------
+    pdl_wait();
+    for (int i = 0; i < n_steps; ++i) {
+      const int s = i % kStages, k = i / kStages;
+      mbar_wait(&full_bar[s], k & 1, dead, err);
+      tc_fence_after();
+      if (lane == 0) {
+        const uint32_t sa = smem_u32(smem + s * kStage);
+        const uint64_t adesc = smem_desc(sa, 2048, 128);
+        const uint64_t bdesc = smem_desc(sa + kWStage, N * 16, 128);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          tc_mma_f16(tmem_base, adesc + (uint64_t)(j * (4096 >> 4)), bdesc + (uint64_t)(j * ((2 * N * 16) >> 4)), kIdesc,
+                     (i == 0 && j == 0) ? 0u : 1u);
+        tc_commit(&empty_bar[s]);
+        if (i == n_steps - 1) tc_commit(&acc_full);
+      }
+      __syncwarp();
+    }
+  } else {
+    // ---------------- epilogue warps: send every row to the CTA that finalises it ----------------
+    pdl_wait();
+    const int q = warp & 3;
+    float v[N];
+    if (n_steps > 0) {
+      mbar_wait(&acc_full, 0, dead, err);
+      tc_fence_after();
+      tmem_load_row<N>(v, tmem_base + ((uint32_t)(32 * q) << 16));
+      tc_fence_before();
+    } else {
+#pragma unroll
+      for (int i = 0; i < N; ++i) v[i] = 0.f;
+    }
+    const int rows_per = 128 / C;
+    const int row = 32 * q + lane;
+    const int owner = row / rows_per, row_local = row - owner * rows_per;
+    const uint32_t recv_local = smem_u32(smem + kStages * kStage) + (uint32_t)(((c * rows_per + row_local) * N) * 4);
+    const uint32_t dst = dsmem_addr(recv_local, (uint32_t)owner);
+#pragma unroll
+    for (int i = 0; i < N / 4; ++i) dsmem_store4(dst + 16u * i, v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+  }
+  // every partial row is in its owner's shared memory once all CTAs of the cluster are here
+  cluster_sync_all();
+  if (warp >= 2) {
+    const int e = tid - 64;
+    const int rows_per = 128 / C;
+    const int row16 = lane & 15, cg = e >> 4;               // one float4 (4 batch columns) per thread
+    if (cg < N / 4) {
+      const float4* recv = reinterpret_cast<const float4*>(smem + kStages * kStage);
+      for (int j = 0; j < rows_per / 16; ++j) {
+        float v4[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int src = 0; src < C; ++src) {
+          const float4 t = recv[((src * rows_per + 16 * j + row16) * N) / 4 + cg];
+          v4[0] += t.x; v4[1] += t.y; v4[2] += t.z; v4[3] += t.w;
+        }
+        row_epilogue<4, N>(p, v4, r * 128 + c * rows_per + 16 * j + row16, 4 * cg);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+template <int Bp>
+constexpr size_t cluster_smem() {
+  return (size_t)kStages * (kWStage + Bp * 256) + 128 * Bp * 4 + 1024;
+}
+
+template <int Bp>
+int32_t launch_cluster(Ctx* ctx, const GemvParams& p, cudaStream_t stream) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(ceil_div(p.rows, 128) * p.cluster));
+  cfg.blockDim = dim3(kTcThreads);
+  cfg.dynamicSmemBytes = cluster_smem<Bp>();
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)p.cluster;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
+  LMB_CUDA(cudaLaunchKernelEx(&cfg, gemv_cl_kernel<Bp>, p, ctx->dev_err));
+  ctx->launches++;
+  return LMB200_OK;
+}
+
+// The largest cluster size (8, 4, 2) that keeps rows/128 x C CTAs on the device in one wave and
+// gives every CTA at least one k step; 0: use the stream-K kernel.
+template <int Bp>
+int cluster_choice(const Ctx* ctx, int rows, int K) {
+  const int nrbg = (int)ceil_div(rows, 128), KS = (int)ceil_div(K, 128);
+  for (int C = 8; C >= 2; C >>= 1) {
+    if (C > KS || (int64_t)nrbg * C > ctx->sm_count) continue;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(nrbg * C));
+    cfg.blockDim = dim3(kTcThreads);
+    cfg.dynamicSmemBytes = cluster_smem<Bp>();
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)C;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n_clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&n_clusters, gemv_cl_kernel<Bp>, &cfg) != cudaSuccess) {
+      cudaGetLastError();
+      continue;
+    }
+    if (n_clusters >= nrbg) return C;
+  }
+  return 0;
+}
+
 template <typename WT, int NB, int MT, int STAGES>
 int32_t launch_ring(Ctx* ctx, const GemvParams& p, cudaStream_t stream) {
   constexpr int Bp = 8 * NB, RPC = 2 * MT * 16;
@@ -1102,6 +1327,8 @@ template <int Bp>
 int32_t launch_bf16(Ctx* ctx, const GemvParams& p, cudaStream_t stream) {
   if (g_variant == GEMV_MMA_SYNC)
     LMB_CUDA(launch_k(gemv_mma_kernel<Bp / 8>, dim3(p.grid), dim3(kMmaThreads), stream_smem<Bp>(), stream, p, ctx->dev_err));
+  else if (p.cluster > 1)
+    return launch_cluster<Bp>(ctx, p, stream);
   else
     LMB_CUDA(launch_k(gemv_tc_kernel<Bp>, dim3(p.grid), dim3(kTcThreads), stream_smem<Bp>(), stream, p, ctx->dev_err));
   ctx->launches++;
@@ -1131,6 +1358,11 @@ GemvPlan gemv_plan(const Ctx* ctx, int dtype, int B, int rows, int K) {
     pl.kc_per_split = KS;
     pl.partial_floats = (int64_t)nrbg * pl.ksplit * 128 * Bp;   // [row group][contributor][128 x Bp]
     pl.n_counters = nrbg * 8;
+    // small matrices: a cluster per row group, partials through distributed shared memory
+    const char* ce = getenv("LMB200_GEMV_CLUSTER");             // 0: never; N (MB): size limit, default 64
+    const int64_t limit_mb = ce ? atoi(ce) : 64;
+    if (g_variant == GEMV_TCGEN05 && (int64_t)rows * K * 2 <= limit_mb * 1000000)
+      pl.cluster = Bp == 16 ? cluster_choice<16>(ctx, rows, K) : cluster_choice<32>(ctx, rows, K);
     return pl;
   }
   const int Bp = Layout<float>::batch_pad(B);
@@ -1175,6 +1407,8 @@ int32_t gemv_configure() {
   LMB_CFG(gemv_mma_kernel<4>, stream_smem<32>());
   LMB_CFG(gemv_tc_kernel<16>, stream_smem<16>());
   LMB_CFG(gemv_tc_kernel<32>, stream_smem<32>());
+  LMB_CFG(gemv_cl_kernel<16>, cluster_smem<16>());
+  LMB_CFG(gemv_cl_kernel<32>, cluster_smem<32>());
 #undef LMB_CFG
   return LMB200_OK;
 }

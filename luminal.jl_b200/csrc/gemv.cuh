@@ -31,6 +31,7 @@ struct GemvParams {
   int ksplit = 1;            // ring: k-splits (gridDim.y); bf16: contributors reserved per row group
   int kc_per_split = 0;
   int grid = 0;              // bf16 kernels: number of CTAs
+  int cluster = 0;           // > 1: one thread-block cluster of this size per 128-row group (small matrices)
   float* partials = nullptr;     // split-K scratch
   unsigned* counters = nullptr;  // zero between launches
   int epi = EPI_STORE_F32;
@@ -56,7 +57,7 @@ struct GemvParams {
 };
 
 struct GemvPlan {
-  int ksplit = 1, kc_per_split = 0, grid = 0;
+  int ksplit = 1, kc_per_split = 0, grid = 0, cluster = 0;
   int64_t partial_floats = 0;
   int n_counters = 0;
 };

@@ -823,7 +823,7 @@ GemvParams gemv_params(Session* S, const void* W, const WMap& m, const GemvPlan&
   GemvParams p;
   p.W = W; p.x = x; p.B = S->B;
   p.rows = m.rows; p.K = m.K; p.RB = m.RB; p.KC = m.KC;
-  p.ksplit = pl.ksplit; p.kc_per_split = pl.kc_per_split; p.grid = pl.grid;
+  p.ksplit = pl.ksplit; p.kc_per_split = pl.kc_per_split; p.grid = pl.grid; p.cluster = pl.cluster;
   p.partials = S->gemv_partials; p.counters = S->gemv_counters;
   return p;
 }
@@ -1520,7 +1520,7 @@ extern "C" int32_t lmb200_linear_gemv(lmb200_ctx hctx, int32_t dtype, int32_t va
     ctx->launches++;
     GemvParams p;
     p.W = W; p.x = X; p.B = batch; p.rows = rows; p.K = K; p.RB = m.RB; p.KC = m.KC;
-    p.ksplit = pl.ksplit; p.kc_per_split = pl.kc_per_split; p.grid = pl.grid;
+    p.ksplit = pl.ksplit; p.kc_per_split = pl.kc_per_split; p.grid = pl.grid; p.cluster = pl.cluster;
     p.partials = partials; p.counters = counters;
     p.epi = EPI_STORE_F32; p.out = out; p.out_pitch = rows;
     rc = gemv_launch(ctx, dtype, p, ctx->stream);
