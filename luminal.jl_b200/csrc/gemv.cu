@@ -1359,8 +1359,8 @@ GemvPlan gemv_plan(const Ctx* ctx, int dtype, int B, int rows, int K) {
     pl.partial_floats = (int64_t)nrbg * pl.ksplit * 128 * Bp;   // [row group][contributor][128 x Bp]
     pl.n_counters = nrbg * 8;
     // small matrices: a cluster per row group, partials through distributed shared memory
-    const char* ce = getenv("LMB200_GEMV_CLUSTER");             // 0: never; N (MB): size limit, default 64
-    const int64_t limit_mb = ce ? atoi(ce) : 64;
+    const char* ce = getenv("LMB200_GEMV_CLUSTER");             // 0: never; N (MB): size limit, default 128
+    const int64_t limit_mb = ce ? atoi(ce) : 128;
     if (g_variant == GEMV_TCGEN05 && (int64_t)rows * K * 2 <= limit_mb * 1000000)
       pl.cluster = Bp == 16 ? cluster_choice<16>(ctx, rows, K) : cluster_choice<32>(ctx, rows, K);
     return pl;
