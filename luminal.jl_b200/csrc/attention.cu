@@ -23,6 +23,13 @@ namespace {
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr int kAttnThreads = 128;
 
+// Keys per CTA for a context of T keys: the launch has nsplit CTAs per (sequence, kv head), planned
+// for the cache capacity; a shorter context is divided evenly among the same CTAs (multiples of 64).
+__device__ __forceinline__ int keys_per_cta_for(const AttnParams& p, int T) {
+  const int even = (((T + p.nsplit - 1) / p.nsplit + 63) >> 6) << 6;
+  return even < p.keys_per_cta ? even : p.keys_per_cta;
+}
+
 __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                          uint32_t a3, uint32_t b0, uint32_t b1) {
   asm volatile(
@@ -51,7 +58,8 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_bf16_kernel(const At
   pdl_launch_dependents();
   pdl_wait();
   const int T = p.pos ? (*p.pos + 1) : p.T_fixed;
-  const int k_begin = blockIdx.y * p.keys_per_cta;
+  const int kpc = keys_per_cta_for(p, T);
+  const int k_begin = blockIdx.y * kpc;
   if (k_begin >= T) return;
   const int bk = blockIdx.x;
   const int b = bk / p.KVl, kvl = bk - b * p.KVl;
@@ -72,7 +80,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_bf16_kernel(const At
     }
   }
 
-  const int kpw = p.keys_per_cta / 4;
+  const int kpw = kpc / 4;
   const int wb = k_begin + warp * kpw;
   const int we = min(T, wb + kpw);
   const int kb_begin = wb >> 4, kb_end = (we + 15) >> 4;     // empty when wb >= T
@@ -173,7 +181,7 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_bf16_kernel(const At
   // The CTA that finishes last for this (sequence, kv head) merges the splits itself: same
   // arithmetic and order as attn_combine_kernel, without another launch.
   __shared__ int is_last;
-  const int nvalid = (T + p.keys_per_cta - 1) / p.keys_per_cta;
+  const int nvalid = (T + kpc - 1) / kpc;
   __threadfence();
   __syncthreads();
   if (tid == 0) {
@@ -222,9 +230,10 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_simple_kernel(const 
   pdl_launch_dependents();
   pdl_wait();
   const int Tctx = p.pos ? (*p.pos + 1) : p.T_fixed;
-  const int k_begin = blockIdx.y * p.keys_per_cta;
+  const int kpc = keys_per_cta_for(p, Tctx);
+  const int k_begin = blockIdx.y * kpc;
   if (k_begin >= Tctx) return;
-  const int k_end = min(Tctx, k_begin + p.keys_per_cta);
+  const int k_end = min(Tctx, k_begin + kpc);
   const int n = k_end - k_begin;
   const int bk = blockIdx.x, h = blockIdx.z;
   const int b = bk / p.KVl, kvl = bk - b * p.KVl;
@@ -283,7 +292,8 @@ __global__ void attn_combine_kernel(const AttnParams p) {
   pdl_launch_dependents();
   pdl_wait();
   const int Tctx = p.pos ? (*p.pos + 1) : p.T_fixed;
-  const int nvalid = (Tctx + p.keys_per_cta - 1) / p.keys_per_cta;
+  const int kpc = keys_per_cta_for(p, Tctx);
+  const int nvalid = (Tctx + kpc - 1) / kpc;
   const int b = blockIdx.x / (p.KVl * p.G);
   const int hl = blockIdx.x - b * (p.KVl * p.G);
   const int kvl = hl / p.G, h = hl - kvl * p.G;

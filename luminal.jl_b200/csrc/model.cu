@@ -324,34 +324,53 @@ __global__ void scatter_kv_kernel(WT* kv, int64_t batch_stride, int64_t head_str
 }
 
 // greedy token: first maximum of the logits row; also logs it for the device-resident loop
-__global__ void __launch_bounds__(256) argmax_step_kernel(const float* logits, int pitch, int n, int* tokens,
-                                                          int* hist, const int* step_ctr, int B) {
-  __shared__ float sv[256];
-  __shared__ int si[256];
+constexpr int kArgmaxThreads = 1024;
+__global__ void __launch_bounds__(kArgmaxThreads) argmax_step_kernel(const float* logits, int pitch, int n, int* tokens,
+                                                                     int* hist, const int* step_ctr, int B) {
+  __shared__ float sv[kArgmaxThreads / 32];
+  __shared__ int si[kArgmaxThreads / 32];
   pdl_launch_dependents();
   pdl_wait();
   const int b = blockIdx.x, tid = threadIdx.x;
   const float* row = logits + (int64_t)b * pitch;
   float best = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = tid; i < n; i += 256) {
-    const float v = row[i];
+  auto take = [&](float v, int i) {
     if (v > best || (v == best && i < bi)) { best = v; bi = i; }
-  }
-  sv[tid] = best;
-  si[tid] = bi;
-  __syncthreads();
-  for (int off = 128; off > 0; off >>= 1) {
-    if (tid < off) {
-      const float v = sv[tid + off];
-      const int i = si[tid + off];
-      if (v > sv[tid] || (v == sv[tid] && i < si[tid])) { sv[tid] = v; si[tid] = i; }
+  };
+  if ((pitch & 3) == 0) {              // rows are 16-byte aligned: four logits per load
+    const float4* row4 = reinterpret_cast<const float4*>(row);
+    const int n4 = n >> 2;
+#pragma unroll 4
+    for (int i = tid; i < n4; i += kArgmaxThreads) {
+      const float4 v = row4[i];
+      take(v.x, 4 * i); take(v.y, 4 * i + 1); take(v.z, 4 * i + 2); take(v.w, 4 * i + 3);
     }
-    __syncthreads();
+    for (int i = 4 * n4 + tid; i < n; i += kArgmaxThreads) take(row[i], i);
+  } else {
+    for (int i = tid; i < n; i += kArgmaxThreads) take(row[i], i);
   }
-  if (tid == 0) {
-    tokens[b] = si[0];
-    if (hist) hist[(int64_t)(*step_ctr) * B + b] = si[0];
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    const float v = __shfl_xor_sync(0xffffffffu, best, off);
+    const int i = __shfl_xor_sync(0xffffffffu, bi, off);
+    take(v, i);
+  }
+  if ((tid & 31) == 0) { sv[tid >> 5] = best; si[tid >> 5] = bi; }
+  __syncthreads();
+  if (tid < 32) {
+    best = sv[tid];
+    bi = si[tid];
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      const float v = __shfl_xor_sync(0xffffffffu, best, off);
+      const int i = __shfl_xor_sync(0xffffffffu, bi, off);
+      take(v, i);
+    }
+    if (tid == 0) {
+      tokens[b] = bi;
+      if (hist) hist[(int64_t)(*step_ctr) * B + b] = bi;
+    }
   }
 }
 
@@ -940,7 +959,7 @@ int32_t enqueue_step_t(Session* S, cudaStream_t st, bool with_head) {
     GemvParams p = gemv_params(S, M->lm_head, M->m_head, S->p_head, S->xn);
     p.epi = EPI_STORE_F32; p.out = S->logits; p.out_pitch = S->logits_pitch;
     LMB_TRY(gemv_launch(ctx, dt, p, st));
-    LMB_CUDA(launch_k(argmax_step_kernel, dim3(B), dim3(256), 0, st, (const float*)S->logits, S->logits_pitch, c.vocab,
+    LMB_CUDA(launch_k(argmax_step_kernel, dim3(B), dim3(kArgmaxThreads), 0, st, (const float*)S->logits, S->logits_pitch, c.vocab,
                       S->tokens, S->tok_hist, (const int*)S->step_ctr, B));
     ctx->launches++;
   }
@@ -1034,7 +1053,7 @@ int32_t enqueue_whisper_step_t(Session* S, cudaStream_t st, bool with_head) {
     GemvParams p = gemv_params(S, M->embed_tiled, M->m_head, S->p_head, S->xn);     // logits = out * E^T
     p.epi = EPI_STORE_F32; p.out = S->logits; p.out_pitch = S->logits_pitch;
     LMB_TRY(gemv_launch(ctx, dt, p, st));
-    LMB_CUDA(launch_k(argmax_step_kernel, dim3(B), dim3(256), 0, st, (const float*)S->logits, S->logits_pitch, c.vocab,
+    LMB_CUDA(launch_k(argmax_step_kernel, dim3(B), dim3(kArgmaxThreads), 0, st, (const float*)S->logits, S->logits_pitch, c.vocab,
                       S->tokens, S->tok_hist, (const int*)S->step_ctr, B));
     ctx->launches++;
   }
@@ -1064,7 +1083,7 @@ int32_t enqueue_head_bf16(Session* S, cudaStream_t st) {
   GemvParams p = gemv_params(S, M->lm_head, M->m_head, S->p_head, S->xn);
   p.epi = EPI_STORE_F32; p.out = S->logits; p.out_pitch = S->logits_pitch;
   LMB_TRY(gemv_launch(ctx, c.dtype, p, st));
-  LMB_CUDA(launch_k(argmax_step_kernel, dim3(B), dim3(256), 0, st, (const float*)S->logits, S->logits_pitch, c.vocab,
+  LMB_CUDA(launch_k(argmax_step_kernel, dim3(B), dim3(kArgmaxThreads), 0, st, (const float*)S->logits, S->logits_pitch, c.vocab,
                     S->tokens, S->tok_hist, (const int*)S->step_ctr, B));
   ctx->launches++;
   return LMB200_OK;
