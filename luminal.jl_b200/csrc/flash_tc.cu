@@ -1,20 +1,24 @@
 // FlashAttentionOp on the tensor cores (bf16): out = softmax(scale * Q K^T [+ causal]) V.
 // Replaces flash_attn_fwd_kernel (src/Execution.jl:374-450, one query row per block, keys in
-// series, no tensor cores) for bf16 tensors of head_dim 64 or 128.
+// series, no tensor cores) for bf16 tensors of head_dim 64, 96 or 128.
 //
-// One CTA = 128 query rows of one (batch, head), keys in tiles of 64:
-//   4 loader warps : cp.async 16-byte chunks of Q / K / V from row-major global memory into the
+// One CTA = two tiles of 128 query rows of one (batch, head) sharing the key/value stream, keys in
+// tiles of 64:
+//   2 loader warps : cp.async 16-byte chunks of Q / K / V from row-major global memory into the
 //                    canonical core-matrix layout (8 rows x 16 bytes) the tensor core reads, 3 K/V
 //                    stages in flight;
-//   1 MMA warp     : one thread issues tcgen05.mma -- S = Q K^T (M 128, N 64, K = D) into a
-//                    double-buffered TMEM tile, then PV = P V (M 128, N = D, K 64; V read MN-major
-//                    from the same tile layout as K) into another; tcgen05.commit signals mbarriers;
-//   4 softmax warps: one query row per thread: tcgen05.ld the S row, online softmax (exp2 with the
-//                    scale folded in), write P as bf16 straight into the A-operand layout, and fold
-//                    the previous tile's PV into the row's float32 output registers
-//                    (O = O * alpha + PV), so the softmax of tile j+1 overlaps the PV MMA of tile j.
-// Causal: key tiles beyond the diagonal are never loaded; inside the diagonal tile keys j > i are
-// masked -- the reference's `if causal && j > i continue`.
+//   1 MMA warp     : one thread issues tcgen05.mma for both query tiles -- S = Q K^T (M 128, N 64,
+//                    K = D) into a double-buffered TMEM tile, then O += P V (M 128, N = D, K 64; V
+//                    read MN-major from the same tile layout as K) accumulating in TMEM over all
+//                    key tiles; tcgen05.commit signals mbarriers;
+//   2 x 4 softmax warps, one group per query tile, one query row per thread: tcgen05.ld the S row,
+//                    exp2 with the scale folded in, write P as bf16 straight into the A-operand
+//                    layout.  The running maximum is only raised -- and O in TMEM rescaled -- when
+//                    it grows by more than 2^8 (p stays <= 256, exact in the final O / l), so in the
+//                    steady state a softmax thread never touches O and the two groups keep the
+//                    tensor core busy in turn.
+// Causal: key tiles beyond a query tile's diagonal are never computed; inside the diagonal tile
+// keys j > i are masked -- the reference's `if causal && j > i continue`.
 #include <math_constants.h>
 
 #include "common.cuh"
@@ -24,20 +28,28 @@ namespace lmb {
 namespace {
 
 constexpr int kBM = 128, kBN = 64, kKvStages = 3;
-constexpr int kThreads = 9 * 32;         // warps 0-3 softmax, 4 MMA, 5-8 loaders
+constexpr int kLoaders = 2 * 32;          // loader threads
+constexpr int kThreads = 9 * 32 + kLoaders;   // warps 0-3 / 4-7 softmax of query tile 0 / 1, 8 MMA, 9.. loaders
 constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kRescaleStep = 8.0f;     // log2 units the maximum may lag behind before O is rescaled
 
 template <int D>
 struct Smem {
   static constexpr int kQ = kBM * D * 2;
   static constexpr int kKV = kBN * D * 2;
   static constexpr int kP = kBM * kBN * 2;
-  static constexpr int offQ = 0;
-  static constexpr int offK = offQ + kQ;
+  static constexpr int offQ = 0;                              // two query tiles
+  static constexpr int offK = offQ + 2 * kQ;
   static constexpr int offV = offK + kKvStages * kKV;
-  static constexpr int offP = offV + kKvStages * kKV;
-  static constexpr int total = offP + 2 * kP;
+  static constexpr int offP = offV + kKvStages * kKV;          // [tile][buffer]
+  static constexpr int total = offP + 4 * kP;
 };
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
 
 // chunk (row, d8) of a [rows x D] row-major tile -> canonical offset [d8][row/8][row%8][16 B]
 __device__ __forceinline__ uint32_t canon(int row, int c8, int rows) {
@@ -52,14 +64,14 @@ flash_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict
   typedef Smem<D> SM;
   extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ __align__(8) uint64_t q_full, kv_full[kKvStages], kv_empty[kKvStages];
-  __shared__ __align__(8) uint64_t s_full[2], s_empty[2], p_full[2], p_empty[2], pv_full[2], pv_empty[2];
+  __shared__ __align__(8) uint64_t s_full[2][2], s_empty[2][2], p_full[2][2], p_empty[2][2], pv_done[2];
   __shared__ uint32_t tmem_slot;
   constexpr uint32_t kTmemCols = 512;
-  constexpr uint32_t kColS = 0, kColPV = 128;               // S: 2 x 64 columns, PV: 2 x D columns
+  constexpr uint32_t kColS = 0, kColO = 256;                 // S: [tile][buffer] x 64 columns, O: [tile] x D columns
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;      // heavy (late) causal tiles first
-  const int q0 = qt * kBM;
+  const int qp = (int)gridDim.x - 1 - (int)blockIdx.x;        // heavy (late) causal tiles first
+  const int q0 = qp * 2 * kBM;
   // blockIdx.y = batch * H + head; query head h reads kv head h / G (G = 1: an op with H kv heads)
   const int bi = (int)blockIdx.y / fv.H, hi = (int)blockIdx.y - bi * fv.H;
   const __nv_bfloat16* qb = q + bi * fv.q_b + hi * fv.q_h;
@@ -67,34 +79,42 @@ flash_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict
   const __nv_bfloat16* vb = v + bi * fv.k_b + (hi / fv.G) * fv.k_h;
   __nv_bfloat16* ob_base = out + bi * fv.q_b + hi * fv.q_h;
   const int64_t q_s = fv.q_s, k_s = fv.k_s;
-  const int k_stop = causal ? min(S, q0 + kBM) : S;
-  const int n_tiles = (k_stop + kBN - 1) / kBN;
+  int n_tiles[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int qt0 = q0 + t * kBM;
+    const int k_stop = qt0 >= S ? 0 : (causal ? min(S, qt0 + kBM) : S);
+    n_tiles[t] = (k_stop + kBN - 1) / kBN;
+  }
+  const int n_max = max(n_tiles[0], n_tiles[1]);
 
   if (tid == 0) {
-    mbar_init(&q_full, 4);
-    for (int s = 0; s < kKvStages; ++s) { mbar_init(&kv_full[s], 4); mbar_init(&kv_empty[s], 1); }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4);
-      mbar_init(&p_full[i], 4); mbar_init(&p_empty[i], 1);
-      mbar_init(&pv_full[i], 1); mbar_init(&pv_empty[i], 4);
+    mbar_init(&q_full, kLoaders / 32);
+    for (int s = 0; s < kKvStages; ++s) { mbar_init(&kv_full[s], kLoaders / 32); mbar_init(&kv_empty[s], 1); }
+    for (int t = 0; t < 2; ++t) {
+      for (int i = 0; i < 2; ++i) {
+        mbar_init(&s_full[t][i], 1); mbar_init(&s_empty[t][i], 4);
+        mbar_init(&p_full[t][i], 4); mbar_init(&p_empty[t][i], 1);
+      }
+      mbar_init(&pv_done[t], 1);
     }
     mbar_init_fence();
   }
-  if (warp == 4) tmem_alloc(&tmem_slot, kTmemCols);
+  if (warp == 8) tmem_alloc(&tmem_slot, kTmemCols);
   fence_before();
   __syncthreads();
   fence_after();
   const uint32_t tmem = tmem_slot;
   bool dead = false;
 
-  if (warp >= 5) {
+  if (warp >= 9) {
     // ------------------------------ loaders ------------------------------
-    const int lt = tid - 5 * 32;                    // 0..127
+    const int lt = tid - 9 * 32;                    // 0..kLoaders-1
     const uint32_t sQ = smem_u32(smem + SM::offQ);
-    for (int i = lt; i < kBM * (D / 8); i += 128) {
-      const int row = i / (D / 8), c8 = i - row * (D / 8);
+    for (int i = lt; i < 2 * kBM * (D / 8); i += kLoaders) {
+      const int row = i / (D / 8), c8 = i - row * (D / 8);      // row 0..255 over both tiles
       const int qi = q0 + row;
-      cp_async16(sQ + canon(row, c8, kBM), qb + (int64_t)min(qi, S - 1) * q_s + c8 * 8, qi < S ? 16u : 0u);
+      cp_async16(sQ + (row >> 7) * SM::kQ + canon(row & 127, c8, kBM), qb + (int64_t)min(qi, S - 1) * q_s + c8 * 8, qi < S ? 16u : 0u);
     }
     cp_async_commit();
     auto signal_oldest = [&](int j) {               // tile j has landed in its stage
@@ -103,17 +123,31 @@ flash_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict
       if (lane == 0) mbar_arrive(&kv_full[j % kKvStages]);
     };
     bool q_signalled = false;
-    for (int j = 0; j < n_tiles; ++j) {
+    for (int j = 0; j < n_max; ++j) {
       const int s = j % kKvStages;
       mbar_wait(&kv_empty[s], ((j / kKvStages) & 1) ^ 1, dead, err);
       const uint32_t sK = smem_u32(smem + SM::offK + s * SM::kKV), sV = smem_u32(smem + SM::offV + s * SM::kKV);
-      for (int i = lt; i < kBN * (D / 8); i += 128) {
-        const int row = i / (D / 8), c8 = i - row * (D / 8);
-        const int key = j * kBN + row;
-        const int64_t src = (int64_t)min(key, S - 1) * k_s + c8 * 8;
-        const uint32_t nb = key < S ? 16u : 0u;
-        cp_async16(sK + canon(row, c8, kBN), kb + src, nb);
-        cp_async16(sV + canon(row, c8, kBN), vb + src, nb);
+      if ((kLoaders % (D / 8)) == 0 && (j + 1) * kBN <= S) {
+        // tile inside the sequence, and a thread keeps its 16-byte column: rows advance by kLoaders / (D/8)
+        constexpr int kCols = D / 8, kRowStep = kLoaders / kCols;
+        const int c8 = lt % kCols, row0 = lt / kCols;
+        const __nv_bfloat16* ks = kb + (int64_t)(j * kBN + row0) * k_s + c8 * 8;
+        const __nv_bfloat16* vs = vb + (int64_t)(j * kBN + row0) * k_s + c8 * 8;
+#pragma unroll
+        for (int it = 0; it < kBN / kRowStep; ++it) {
+          const uint32_t off = canon(row0 + it * kRowStep, c8, kBN);
+          cp_async16(sK + off, ks + (int64_t)it * kRowStep * k_s, 16u);
+          cp_async16(sV + off, vs + (int64_t)it * kRowStep * k_s, 16u);
+        }
+      } else {
+        for (int i = lt; i < kBN * (D / 8); i += kLoaders) {
+          const int row = i / (D / 8), c8 = i - row * (D / 8);
+          const int key = j * kBN + row;
+          const int64_t src = (int64_t)min(key, S - 1) * k_s + c8 * 8;
+          const uint32_t nb = key < S ? 16u : 0u;
+          cp_async16(sK + canon(row, c8, kBN), kb + src, nb);
+          cp_async16(sV + canon(row, c8, kBN), vb + src, nb);
+        }
       }
       cp_async_commit();
       // groups in flight: Q (until signalled), tiles j-1 and j at most
@@ -135,142 +169,163 @@ flash_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict
       __syncwarp();
       if (lane == 0) mbar_arrive(&q_full);
     }
-    if (n_tiles >= 1) signal_oldest(n_tiles - 1);
-  } else if (warp == 4) {
+    if (n_max >= 1) signal_oldest(n_max - 1);
+  } else if (warp == 8) {
     // ------------------------------ MMA issue ------------------------------
     constexpr uint32_t kIdescS = idesc_bf16(kBM, kBN, false, false);
     constexpr uint32_t kIdescPV = idesc_bf16(kBM, D, false, true);          // V is read MN-major
-    const uint32_t sQ = smem_u32(smem + SM::offQ);
     mbar_wait(&q_full, 0, dead, err);
-    auto issue_pv = [&](int j) {
+    auto issue_pv = [&](int j) {                     // O[t] += P[t](j) V(j) for the tiles that reach key tile j
       const int pb = j & 1, s = j % kKvStages;
-      mbar_wait(&p_full[pb], (j >> 1) & 1, dead, err);
-      mbar_wait(&pv_empty[pb], ((j >> 1) & 1) ^ 1, dead, err);
-      fence_after();
-      if (lane == 0) {
-        // A = P [128 x 64] K-major: lbo (between key groups of 8) = 128*16, sbo = 128
-        // B = V tile [64 keys x D] read as N = d (contiguous), K = key: sbo (between d groups) =
-        //     64*16 = 1024, lbo (between key groups) = 128
-        const uint64_t adesc = smem_desc(smem_u32(smem + SM::offP + pb * SM::kP), kBM * 16, 128);
-        const uint64_t bdesc = smem_desc(smem_u32(smem + SM::offV + s * SM::kKV), 128, kBN * 16);
 #pragma unroll
-        for (int ks = 0; ks < kBN / 16; ++ks)
-          mma_f16(tmem + kColPV + pb * D, adesc + (uint64_t)(ks * ((2 * kBM * 16) >> 4)), bdesc + (uint64_t)(ks * (256 >> 4)),
-                  kIdescPV, ks ? 1u : 0u);
-        commit(&pv_full[pb]);
-        commit(&p_empty[pb]);
-        commit(&kv_empty[s]);
+      for (int t = 0; t < 2; ++t) {
+        if (j >= n_tiles[t]) continue;
+        mbar_wait(&p_full[t][pb], (j >> 1) & 1, dead, err);
+        fence_after();
+        if (lane == 0) {
+          // A = P [128 x 64] K-major: lbo (between key groups of 8) = 128*16, sbo = 128
+          // B = V tile [64 keys x D] read as N = d (contiguous), K = key: sbo (between d groups) =
+          //     64*16 = 1024, lbo (between key groups) = 128
+          const uint64_t adesc = smem_desc(smem_u32(smem + SM::offP + (t * 2 + pb) * SM::kP), kBM * 16, 128);
+          const uint64_t bdesc = smem_desc(smem_u32(smem + SM::offV + s * SM::kKV), 128, kBN * 16);
+#pragma unroll
+          for (int ks = 0; ks < kBN / 16; ++ks)
+            mma_f16(tmem + kColO + t * D, adesc + (uint64_t)(ks * ((2 * kBM * 16) >> 4)), bdesc + (uint64_t)(ks * (256 >> 4)),
+                    kIdescPV, (j > 0 || ks > 0) ? 1u : 0u);
+          commit(&pv_done[t]);
+          commit(&p_empty[t][pb]);
+        }
+        __syncwarp();
       }
+      if (lane == 0) commit(&kv_empty[s]);
       __syncwarp();
     };
-    for (int j = 0; j < n_tiles; ++j) {
+    for (int j = 0; j < n_max; ++j) {
       const int sb = j & 1, s = j % kKvStages;
       mbar_wait(&kv_full[s], (j / kKvStages) & 1, dead, err);
-      mbar_wait(&s_empty[sb], ((j >> 1) & 1) ^ 1, dead, err);
-      fence_after();
-      if (lane == 0) {
-        // A = Q [128 x D] K-major: lbo = 128*16, sbo = 128;  B = K tile [64 x D] K-major: lbo = 64*16
-        const uint64_t adesc = smem_desc(sQ, kBM * 16, 128);
-        const uint64_t bdesc = smem_desc(smem_u32(smem + SM::offK + s * SM::kKV), kBN * 16, 128);
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks)
-          mma_f16(tmem + kColS + sb * kBN, adesc + (uint64_t)(ks * ((2 * kBM * 16) >> 4)),
-                  bdesc + (uint64_t)(ks * ((2 * kBN * 16) >> 4)), kIdescS, ks ? 1u : 0u);
-        commit(&s_full[sb]);
+      for (int t = 0; t < 2; ++t) {
+        if (j >= n_tiles[t]) continue;
+        mbar_wait(&s_empty[t][sb], ((j >> 1) & 1) ^ 1, dead, err);
+        fence_after();
+        if (lane == 0) {
+          // A = Q [128 x D] K-major: lbo = 128*16, sbo = 128;  B = K tile [64 x D] K-major: lbo = 64*16
+          const uint64_t adesc = smem_desc(smem_u32(smem + SM::offQ + t * SM::kQ), kBM * 16, 128);
+          const uint64_t bdesc = smem_desc(smem_u32(smem + SM::offK + s * SM::kKV), kBN * 16, 128);
+#pragma unroll
+          for (int ks = 0; ks < D / 16; ++ks)
+            mma_f16(tmem + kColS + (t * 2 + sb) * kBN, adesc + (uint64_t)(ks * ((2 * kBM * 16) >> 4)),
+                    bdesc + (uint64_t)(ks * ((2 * kBN * 16) >> 4)), kIdescS, ks ? 1u : 0u);
+          commit(&s_full[t][sb]);
+        }
+        __syncwarp();
       }
-      __syncwarp();
       if (j >= 1) issue_pv(j - 1);
     }
-    if (n_tiles >= 1) issue_pv(n_tiles - 1);
+    if (n_max >= 1) issue_pv(n_max - 1);
   } else {
     // ------------------------------ softmax + output: one query row per thread ------------------------------
-    const int r = 32 * warp + lane;
-    const int qi = q0 + r;
-    const uint32_t lane_base = (uint32_t)(32 * warp) << 16;
+    const int t = warp >> 2, wq = warp & 3;
+    const int r = 32 * wq + lane;
+    const int qi = q0 + t * kBM + r;
+    const uint32_t lane_base = (uint32_t)(32 * wq) << 16;
+    const uint32_t colO = kColO + t * D;
     const float c = scale * kLog2e;
+    const int nt = n_tiles[t];
     float m = -CUDART_INF_F, l = 0.f;
-    float o[D];
-#pragma unroll
-    for (int i = 0; i < D; ++i) o[i] = 0.f;
-    float alpha_pending = 1.f;
-    auto accumulate = [&](int j, float alpha) {       // O = O * alpha + P_j V_j
-      const int pb = j & 1;
-      mbar_wait(&pv_full[pb], (j >> 1) & 1, dead, err);
-      fence_after();
-#pragma unroll
-      for (int ch = 0; ch < D / 32; ++ch) {
-        float t[32];
-        tmem_ld32(t, tmem + lane_base + kColPV + pb * D + ch * 32);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[ch * 32 + i] = fmaf(o[ch * 32 + i], alpha, t[i]);
-      }
-      fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&pv_empty[pb]);
-    };
-    for (int j = 0; j < n_tiles; ++j) {
+    for (int j = 0; j < nt; ++j) {
       const int sb = j & 1;
-      mbar_wait(&s_full[sb], (j >> 1) & 1, dead, err);
+      mbar_wait(&s_full[t][sb], (j >> 1) & 1, dead, err);
       fence_after();
       float sv[2][32];
-      tmem_ld32(sv[0], tmem + lane_base + kColS + sb * kBN);
-      tmem_ld32(sv[1], tmem + lane_base + kColS + sb * kBN + 32);
+      tmem_ld32(sv[0], tmem + lane_base + kColS + (t * 2 + sb) * kBN);
+      tmem_ld32(sv[1], tmem + lane_base + kColS + (t * 2 + sb) * kBN + 32);
       fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&s_empty[sb]);
+      if (lane == 0) mbar_arrive(&s_empty[t][sb]);
+      // scores stay unscaled in registers; the scale (c > 0) enters through the exp2 argument
       float mx = -CUDART_INF_F;
+      const bool inside = (j + 1) * kBN <= S && (!causal || (j + 1) * kBN - 1 <= q0 + t * kBM);   // no key of the tile is masked
+      if (inside) {
 #pragma unroll
-      for (int i = 0; i < kBN; ++i) {
-        const int key = j * kBN + i;
-        const bool masked = key >= S || (causal && key > qi);
-        sv[i >> 5][i & 31] = masked ? -CUDART_INF_F : sv[i >> 5][i & 31] * c;
-        mx = fmaxf(mx, sv[i >> 5][i & 31]);
+        for (int i = 0; i < kBN; ++i) mx = fmaxf(mx, sv[i >> 5][i & 31]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < kBN; ++i) {
+          const int key = j * kBN + i;
+          if (key >= S || (causal && key > qi)) sv[i >> 5][i & 31] = -CUDART_INF_F;
+          mx = fmaxf(mx, sv[i >> 5][i & 31]);
+        }
       }
-      const float m_new = fmaxf(m, mx);
-      const float m_use = m_new == -CUDART_INF_F ? 0.f : m_new;     // row fully masked so far
-      const float alpha = exp2f(m - m_use);
+      mx *= c;
+      // raise the reference maximum only when it lags by more than kRescaleStep; O and l follow it
+      const bool first = m == -CUDART_INF_F && mx > -CUDART_INF_F;
+      const bool raise = m > -CUDART_INF_F && mx > m + kRescaleStep;
+      if (__any_sync(0xffffffffu, raise) && j > 0) {
+        const float alpha = raise ? exp2f(m - mx) : 1.0f;
+        mbar_wait(&pv_done[t], (j - 1) & 1, dead, err);          // every P V issued so far has landed in O
+        fence_after();
+#pragma unroll
+        for (int ch = 0; ch < D / 32; ++ch) {
+          float o[32];
+          tmem_ld32(o, tmem + lane_base + colO + ch * 32);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] *= alpha;
+          tmem_st32(tmem + lane_base + colO + ch * 32, o);
+        }
+        fence_before();
+      }
+      if (raise) { l *= exp2f(m - mx); m = mx; }
+      if (first) m = mx;
+      const float neg_m = m == -CUDART_INF_F ? 0.f : -m;             // row fully masked so far: p = exp2(-inf) = 0
       float sum = 0.f;
       uint32_t packed[kBN / 2];
 #pragma unroll
       for (int i = 0; i < kBN; i += 2) {
-        const float p0 = exp2f(sv[i >> 5][i & 31] - m_use), p1 = exp2f(sv[i >> 5][(i & 31) + 1] - m_use);
-        // the row sum uses the same bf16-rounded values the tensor core multiplies with V
+        const float p0 = ex2_approx(fmaf(sv[i >> 5][i & 31], c, neg_m)), p1 = ex2_approx(fmaf(sv[i >> 5][(i & 31) + 1], c, neg_m));
+        sum += p0 + p1;
         const __nv_bfloat162 pb2 = __floats2bfloat162_rn(p0, p1);
-        sum += __low2float(pb2) + __high2float(pb2);
         packed[i / 2] = *reinterpret_cast<const uint32_t*>(&pb2);
       }
-      l = l * alpha + sum;
-      m = m_new;
-      mbar_wait(&p_empty[sb], ((j >> 1) & 1) ^ 1, dead, err);
-      unsigned char* pt = smem + SM::offP + sb * SM::kP;
+      l += sum;
+      mbar_wait(&p_empty[t][sb], ((j >> 1) & 1) ^ 1, dead, err);
+      unsigned char* pt = smem + SM::offP + (t * 2 + sb) * SM::kP;
 #pragma unroll
       for (int c8 = 0; c8 < kBN / 8; ++c8)
         *reinterpret_cast<uint4*>(pt + canon(r, c8, kBM)) =
             make_uint4(packed[4 * c8], packed[4 * c8 + 1], packed[4 * c8 + 2], packed[4 * c8 + 3]);
       fence_async_smem();
+      fence_before();                    // orders a rescale's tcgen05.st before the MMA that the arrive releases
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full[sb]);
-      if (j >= 1) accumulate(j - 1, alpha_pending);
-      alpha_pending = alpha;
+      if (lane == 0) mbar_arrive(&p_full[t][sb]);
     }
-    if (n_tiles >= 1) accumulate(n_tiles - 1, alpha_pending);
-    if (qi < S) {
+    if (nt >= 1) {
+      mbar_wait(&pv_done[t], (nt - 1) & 1, dead, err);
+      fence_after();
       const float inv = 1.0f / l;
       __nv_bfloat16* ob = ob_base + (int64_t)qi * q_s;
 #pragma unroll
-      for (int i = 0; i < D; i += 8) {
-        uint4 w;
-        __nv_bfloat162 a0 = __floats2bfloat162_rn(o[i] * inv, o[i + 1] * inv), a1 = __floats2bfloat162_rn(o[i + 2] * inv, o[i + 3] * inv);
-        __nv_bfloat162 a2 = __floats2bfloat162_rn(o[i + 4] * inv, o[i + 5] * inv), a3 = __floats2bfloat162_rn(o[i + 6] * inv, o[i + 7] * inv);
-        w.x = *reinterpret_cast<uint32_t*>(&a0); w.y = *reinterpret_cast<uint32_t*>(&a1);
-        w.z = *reinterpret_cast<uint32_t*>(&a2); w.w = *reinterpret_cast<uint32_t*>(&a3);
-        *reinterpret_cast<uint4*>(ob + i) = w;
+      for (int ch = 0; ch < D / 32; ++ch) {
+        float o[32];
+        tmem_ld32(o, tmem + lane_base + colO + ch * 32);
+        if (qi < S) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 w;
+            __nv_bfloat162 a0 = __floats2bfloat162_rn(o[i] * inv, o[i + 1] * inv), a1 = __floats2bfloat162_rn(o[i + 2] * inv, o[i + 3] * inv);
+            __nv_bfloat162 a2 = __floats2bfloat162_rn(o[i + 4] * inv, o[i + 5] * inv), a3 = __floats2bfloat162_rn(o[i + 6] * inv, o[i + 7] * inv);
+            w.x = *reinterpret_cast<uint32_t*>(&a0); w.y = *reinterpret_cast<uint32_t*>(&a1);
+            w.z = *reinterpret_cast<uint32_t*>(&a2); w.w = *reinterpret_cast<uint32_t*>(&a3);
+            *reinterpret_cast<uint4*>(ob + ch * 32 + i) = w;
+          }
+        }
       }
+      fence_before();
     }
   }
   fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == 8) {
     fence_after();
     tmem_dealloc(tmem, kTmemCols);
   }
@@ -290,7 +345,7 @@ bool flash_tc_supported(int64_t D) { return D == 64 || D == 96 || D == 128; }
 // q, out: element (b, h, s, d) at b * q_b + h * q_h + s * q_s + d; k, v likewise with the k strides
 int32_t flash_tc_launch_view(Ctx* ctx, void* out, const void* q, const void* k, const void* v, const FlashView& fv, int64_t B,
                              int64_t S, int64_t D, float scale, int causal, cudaStream_t stream) {
-  dim3 grid((unsigned)ceil_div(S, kBM), (unsigned)(B * fv.H));
+  dim3 grid((unsigned)ceil_div(S, 2 * kBM), (unsigned)(B * fv.H));
 #define LMB_FLASH(DD)                                                                                                   \
   flash_tc_kernel<DD><<<grid, kThreads, Smem<DD>::total + 1024, stream>>>(                                             \
       (__nv_bfloat16*)out, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, fv, (int)S, scale, causal, \
