@@ -33,6 +33,16 @@ constexpr int kThreads = 9 * 32 + kLoaders;   // warps 0-3 / 4-7 softmax of quer
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleStep = 8.0f;     // log2 units the maximum may lag behind before O is rescaled
 
+// Optional phase stamps (SM clock) of CTA (0, 0) for tuning; compiled in only with -DLMB_FLASH_TRACE.
+#ifdef LMB_FLASH_TRACE
+}  // namespace
+__device__ long long g_flash_trace[64 * 16];
+namespace {
+#define FL_TRACE(tile, slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (tile) < 64) g_flash_trace[(tile) * 16 + (slot)] = clock64(); } while (0)
+#else
+#define FL_TRACE(tile, slot) ((void)0)
+#endif
+
 template <int D>
 struct Smem {
   static constexpr int kQ = kBM * D * 2;
@@ -90,7 +100,7 @@ flash_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict
 
   if (tid == 0) {
     mbar_init(&q_full, kLoaders / 32);
-    for (int s = 0; s < kKvStages; ++s) { mbar_init(&kv_full[s], kLoaders / 32); mbar_init(&kv_empty[s], 1); }
+    for (int s = 0; s < kKvStages; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
     for (int t = 0; t < 2; ++t) {
       for (int i = 0; i < 2; ++i) {
         mbar_init(&s_full[t][i], 1); mbar_init(&s_empty[t][i], 4);
@@ -109,7 +119,11 @@ flash_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict
 
   if (warp >= 9) {
     // ------------------------------ loaders ------------------------------
-    const int lt = tid - 9 * 32;                    // 0..kLoaders-1
+    // The loader warps take the key tiles in turn (warp w: tiles w, w + 2, ...), each waiting for
+    // its own tile to land before it signals it, so one warp's wait never holds back the other's
+    // next issue.
+    const int lw = warp - 9, lt = tid - 9 * 32;     // lt: 0..kLoaders-1
+    constexpr int kLw = kLoaders / 32;
     const uint32_t sQ = smem_u32(smem + SM::offQ);
     for (int i = lt; i < 2 * kBM * (D / 8); i += kLoaders) {
       const int row = i / (D / 8), c8 = i - row * (D / 8);      // row 0..255 over both tiles
@@ -117,30 +131,25 @@ flash_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict
       cp_async16(sQ + (row >> 7) * SM::kQ + canon(row & 127, c8, kBM), qb + (int64_t)min(qi, S - 1) * q_s + c8 * 8, qi < S ? 16u : 0u);
     }
     cp_async_commit();
-    auto signal_oldest = [&](int j) {               // tile j has landed in its stage
-      fence_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&kv_full[j % kKvStages]);
-    };
     bool q_signalled = false;
-    for (int j = 0; j < n_max; ++j) {
+    for (int j = lw; j < n_max; j += kLw) {
       const int s = j % kKvStages;
       mbar_wait(&kv_empty[s], ((j / kKvStages) & 1) ^ 1, dead, err);
       const uint32_t sK = smem_u32(smem + SM::offK + s * SM::kKV), sV = smem_u32(smem + SM::offV + s * SM::kKV);
-      if ((kLoaders % (D / 8)) == 0 && (j + 1) * kBN <= S) {
-        // tile inside the sequence, and a thread keeps its 16-byte column: rows advance by kLoaders / (D/8)
-        constexpr int kCols = D / 8, kRowStep = kLoaders / kCols;
-        const int c8 = lt % kCols, row0 = lt / kCols;
+      if ((32 % (D / 8)) == 0 && (j + 1) * kBN <= S) {
+        // tile inside the sequence, and a lane keeps its 16-byte column: rows advance by 32 / (D/8)
+        constexpr int kCols = D / 8, kRowStep = 32 / kCols;
+        const int c8 = lane % kCols, row0 = lane / kCols;
         const __nv_bfloat16* ks = kb + (int64_t)(j * kBN + row0) * k_s + c8 * 8;
         const __nv_bfloat16* vs = vb + (int64_t)(j * kBN + row0) * k_s + c8 * 8;
-#pragma unroll
+#pragma unroll 8
         for (int it = 0; it < kBN / kRowStep; ++it) {
           const uint32_t off = canon(row0 + it * kRowStep, c8, kBN);
           cp_async16(sK + off, ks + (int64_t)it * kRowStep * k_s, 16u);
           cp_async16(sV + off, vs + (int64_t)it * kRowStep * k_s, 16u);
         }
       } else {
-        for (int i = lt; i < kBN * (D / 8); i += kLoaders) {
+        for (int i = lane; i < kBN * (D / 8); i += 32) {
           const int row = i / (D / 8), c8 = i - row * (D / 8);
           const int key = j * kBN + row;
           const int64_t src = (int64_t)min(key, S - 1) * k_s + c8 * 8;
@@ -150,26 +159,24 @@ flash_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict
         }
       }
       cp_async_commit();
-      // groups in flight: Q (until signalled), tiles j-1 and j at most
       if (!q_signalled) {
-        cp_async_wait<1>();                          // Q (and everything before tile j) has landed
+        cp_async_wait<1>();                          // this warp's share of Q has landed
         fence_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(&q_full);
         q_signalled = true;
       }
-      if (j >= 1) {
-        cp_async_wait<1>();                          // tile j-1 has landed
-        signal_oldest(j - 1);
-      }
+      cp_async_wait<0>();                            // tile j has landed
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&kv_full[s]);
     }
-    cp_async_wait<0>();
     if (!q_signalled) {
+      cp_async_wait<0>();
       fence_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&q_full);
     }
-    if (n_max >= 1) signal_oldest(n_max - 1);
   } else if (warp == 8) {
     // ------------------------------ MMA issue ------------------------------
     constexpr uint32_t kIdescS = idesc_bf16(kBM, kBN, false, false);
@@ -182,6 +189,7 @@ flash_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict
         if (j >= n_tiles[t]) continue;
         mbar_wait(&p_full[t][pb], (j >> 1) & 1, dead, err);
         fence_after();
+        if (lane == 0) FL_TRACE(j, 8 + t);
         if (lane == 0) {
           // A = P [128 x 64] K-major: lbo (between key groups of 8) = 128*16, sbo = 128
           // B = V tile [64 keys x D] read as N = d (contiguous), K = key: sbo (between d groups) =
@@ -203,11 +211,13 @@ flash_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict
     for (int j = 0; j < n_max; ++j) {
       const int sb = j & 1, s = j % kKvStages;
       mbar_wait(&kv_full[s], (j / kKvStages) & 1, dead, err);
+      if (lane == 0) FL_TRACE(j, 10);
 #pragma unroll
       for (int t = 0; t < 2; ++t) {
         if (j >= n_tiles[t]) continue;
         mbar_wait(&s_empty[t][sb], ((j >> 1) & 1) ^ 1, dead, err);
         fence_after();
+        if (lane == 0) FL_TRACE(j, 11 + t);
         if (lane == 0) {
           // A = Q [128 x D] K-major: lbo = 128*16, sbo = 128;  B = K tile [64 x D] K-major: lbo = 64*16
           const uint64_t adesc = smem_desc(smem_u32(smem + SM::offQ + t * SM::kQ), kBM * 16, 128);
@@ -235,28 +245,30 @@ flash_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict
     float m = -CUDART_INF_F, l = 0.f;
     for (int j = 0; j < nt; ++j) {
       const int sb = j & 1;
+      if (wq == 0 && lane == 0) FL_TRACE(j, 0 + 4 * t);
       mbar_wait(&s_full[t][sb], (j >> 1) & 1, dead, err);
       fence_after();
-      float sv[2][32];
-      tmem_ld32(sv[0], tmem + lane_base + kColS + (t * 2 + sb) * kBN);
-      tmem_ld32(sv[1], tmem + lane_base + kColS + (t * 2 + sb) * kBN + 32);
+      if (wq == 0 && lane == 0) FL_TRACE(j, 1 + 4 * t);
+      float sv[kBN];
+      tmem_ld64(sv, tmem + lane_base + kColS + (t * 2 + sb) * kBN);
       fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_empty[t][sb]);
       // scores stay unscaled in registers; the scale (c > 0) enters through the exp2 argument
-      float mx = -CUDART_INF_F;
+      float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};     // four chains, not one of 64
       const bool inside = (j + 1) * kBN <= S && (!causal || (j + 1) * kBN - 1 <= q0 + t * kBM);   // no key of the tile is masked
       if (inside) {
 #pragma unroll
-        for (int i = 0; i < kBN; ++i) mx = fmaxf(mx, sv[i >> 5][i & 31]);
+        for (int i = 0; i < kBN; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], sv[i]);
       } else {
 #pragma unroll
         for (int i = 0; i < kBN; ++i) {
           const int key = j * kBN + i;
-          if (key >= S || (causal && key > qi)) sv[i >> 5][i & 31] = -CUDART_INF_F;
-          mx = fmaxf(mx, sv[i >> 5][i & 31]);
+          if (key >= S || (causal && key > qi)) sv[i] = -CUDART_INF_F;
+          mx4[i & 3] = fmaxf(mx4[i & 3], sv[i]);
         }
       }
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       mx *= c;
       // raise the reference maximum only when it lags by more than kRescaleStep; O and l follow it
       const bool first = m == -CUDART_INF_F && mx > -CUDART_INF_F;
@@ -278,16 +290,17 @@ flash_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict
       if (raise) { l *= exp2f(m - mx); m = mx; }
       if (first) m = mx;
       const float neg_m = m == -CUDART_INF_F ? 0.f : -m;             // row fully masked so far: p = exp2(-inf) = 0
-      float sum = 0.f;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t packed[kBN / 2];
 #pragma unroll
       for (int i = 0; i < kBN; i += 2) {
-        const float p0 = ex2_approx(fmaf(sv[i >> 5][i & 31], c, neg_m)), p1 = ex2_approx(fmaf(sv[i >> 5][(i & 31) + 1], c, neg_m));
-        sum += p0 + p1;
+        const float p0 = ex2_approx(fmaf(sv[i], c, neg_m)), p1 = ex2_approx(fmaf(sv[i + 1], c, neg_m));
+        sum4[(i >> 1) & 3] += p0 + p1;
         const __nv_bfloat162 pb2 = __floats2bfloat162_rn(p0, p1);
         packed[i / 2] = *reinterpret_cast<const uint32_t*>(&pb2);
       }
-      l += sum;
+      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      if (wq == 0 && lane == 0) FL_TRACE(j, 2 + 4 * t);
       mbar_wait(&p_empty[t][sb], ((j >> 1) & 1) ^ 1, dead, err);
       unsigned char* pt = smem + SM::offP + (t * 2 + sb) * SM::kP;
 #pragma unroll
@@ -298,6 +311,7 @@ flash_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict
       fence_before();                    // orders a rescale's tcgen05.st before the MMA that the arrive releases
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[t][sb]);
+      if (wq == 0 && lane == 0) FL_TRACE(j, 3 + 4 * t);
     }
     if (nt >= 1) {
       mbar_wait(&pv_done[t], (nt - 1) & 1, dead, err);
@@ -369,3 +383,9 @@ int32_t flash_tc_launch(Ctx* ctx, void* out, const void* q, const void* k, const
 }
 
 }  // namespace lmb
+
+#ifdef LMB_FLASH_TRACE
+extern "C" int32_t lmb200_debug_flash_trace(long long* out) {
+  return cudaMemcpyFromSymbol(out, lmb::g_flash_trace, sizeof(lmb::g_flash_trace)) == cudaSuccess ? 0 : -3;
+}
+#endif
