@@ -7,9 +7,10 @@
 // grouped kv heads; K and V are also appended to the decode cache.
 //
 // gemm_tc_kernel: acc[row, token] = sum_k W[row, k] * X[token, k]
-//   one CTA = 128 weight rows x 128 tokens, k in steps of 128 through a 3-stage ring:
-//   warp 5      : bulk copies of 32 KB weight units (already in the tensor core's layout),
-//   warps 6..9  : cp.async 16-byte chunks of the row-major activations into the same layout,
+//   one CTA = 128 weight rows x 128 tokens, k in steps of 64 through a 6-stage ring:
+//   warp 5      : bulk copies of half weight units (16 KB, already in the tensor core's layout),
+//   warps 6..9  : cp.async 16-byte chunks of the row-major activations into the same layout, the
+//                 warps taking the steps in turn,
 //   warp 4      : one thread issues tcgen05.mma 128 x 128 x 16,
 //   warps 0..3  : epilogue, one weight row per thread, tcgen05.ld 32 tokens at a time:
 //                 store float32 / SiLU(gate) * up / RoPE + q, k, v (and the cache).
@@ -31,7 +32,7 @@ bool flash_tc_supported(int64_t D);
 namespace {
 
 constexpr int kGemmBN = 128;
-constexpr int kGemmStages = 3;
+constexpr int kGemmStages = 6;
 constexpr int kGemmThreads = 10 * 32;
 constexpr int kUnitBytes = 32768;
 constexpr float kInvLn2 = 1.4426950408889634f;
@@ -136,16 +137,18 @@ __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, float (&v)[32
 
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const GemmParams p, int* err) {
   using namespace tc;
-  constexpr int kBBytes = kGemmBN * 256;                  // 128 tokens x 128 k, bf16
-  constexpr int kStage = kUnitBytes + kBBytes;
+  constexpr int kABytes = kUnitBytes / 2;                 // 128 rows x 64 k: half a weight unit (its first / last 8 k-groups)
+  constexpr int kBBytes = kGemmBN * 128;                  // 128 tokens x 64 k, bf16
+  constexpr int kStage = kABytes + kBBytes;
   extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ __align__(8) uint64_t full_a[kGemmStages], full_b[kGemmStages], empty[kGemmStages], acc_full;
   __shared__ uint32_t tmem_slot;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int rg = blockIdx.x, t0 = blockIdx.y * kGemmBN;
-  const int KS = (p.K + 127) >> 7;
+  const int KS = (p.K + 127) >> 7;                        // weight units along k
+  const int NS = (p.K + 63) >> 6;                         // pipeline steps of 64 k
   if (tid == 0) {
-    for (int s = 0; s < kGemmStages; ++s) { mbar_init(&full_a[s], 1); mbar_init(&full_b[s], 4); mbar_init(&empty[s], 1); }
+    for (int s = 0; s < kGemmStages; ++s) { mbar_init(&full_a[s], 1); mbar_init(&full_b[s], 1); mbar_init(&empty[s], 1); }
     mbar_init(&acc_full, 1);
     mbar_init_fence();
   }
@@ -157,58 +160,56 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const GemmPara
   bool dead = false;
 
   if (warp >= 6) {
-    // activations: row-major [token, k] -> K-major core matrices
-    const int lt = tid - 6 * 32;
-    for (int ks = 0; ks < KS; ++ks) {
-      const int s = ks % kGemmStages;
-      mbar_wait(&empty[s], ((ks / kGemmStages) & 1) ^ 1, dead, err);
-      const uint32_t sB = smem_u32(smem + s * kStage + kUnitBytes);
-      for (int i = lt; i < kGemmBN * 16; i += 128) {
-        const int tok = i >> 4, c8 = i & 15;
-        const int t = t0 + tok, k = ks * 128 + c8 * 8;
-        const bool ok = t < p.T && k < p.K;
+    // activations: row-major [token, k] -> K-major core matrices.  The four loader warps take the
+    // steps in turn and each waits for its own step to land, so up to four steps are in flight.
+    const int lw = warp - 6;
+    for (int st = lw; st < NS; st += 4) {
+      const int s = st % kGemmStages;
+      mbar_wait(&empty[s], ((st / kGemmStages) & 1) ^ 1, dead, err);
+      const uint32_t sB = smem_u32(smem + s * kStage + kABytes);
+      const int c8 = lane & 7, tok0 = lane >> 3;            // a lane keeps its 16-byte column; tokens advance by 4
+      const int k = st * 64 + c8 * 8;
+      const bool k_ok = k < p.K;
+#pragma unroll 8
+      for (int it = 0; it < kGemmBN / 4; ++it) {
+        const int tok = tok0 + 4 * it, t = t0 + tok;
+        const bool ok = k_ok && t < p.T;
         cp_async16(sB + canon(tok, c8, kGemmBN), p.X + (int64_t)(ok ? t : 0) * p.ldx + (ok ? k : 0), ok ? 16u : 0u);
       }
       cp_async_commit();
-      if (ks >= 1) {                               // the previous step's chunks have landed
-        cp_async_wait<1>();
-        fence_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&full_b[(ks - 1) % kGemmStages]);
-      }
+      cp_async_wait<0>();
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&full_b[s]);
     }
-    cp_async_wait<0>();
-    fence_async_smem();
-    __syncwarp();
-    if (lane == 0 && KS >= 1) mbar_arrive(&full_b[(KS - 1) % kGemmStages]);
   } else if (warp == 5) {
-    // weights: one contiguous unit per k step
-    for (int ks = 0; ks < KS; ++ks) {
-      const int s = ks % kGemmStages;
-      mbar_wait(&empty[s], ((ks / kGemmStages) & 1) ^ 1, dead, err);
+    // weights: half a contiguous unit per step
+    for (int st = 0; st < NS; ++st) {
+      const int s = st % kGemmStages;
+      mbar_wait(&empty[s], ((st / kGemmStages) & 1) ^ 1, dead, err);
       if (lane == 0) {
-        mbar_expect_tx(&full_a[s], (uint32_t)kUnitBytes);
-        bulk_g2s(smem + s * kStage, p.W + ((int64_t)rg * KS + ks) * 16384, (uint32_t)kUnitBytes, &full_a[s]);
+        mbar_expect_tx(&full_a[s], (uint32_t)kABytes);
+        bulk_g2s(smem + s * kStage, p.W + ((int64_t)rg * KS + (st >> 1)) * 16384 + (st & 1) * 8192, (uint32_t)kABytes, &full_a[s]);
       }
       __syncwarp();
     }
   } else if (warp == 4) {
     constexpr uint32_t kIdesc = idesc_bf16(128, kGemmBN, false, false);
-    for (int ks = 0; ks < KS; ++ks) {
-      const int s = ks % kGemmStages;
-      mbar_wait(&full_a[s], (ks / kGemmStages) & 1, dead, err);
-      mbar_wait(&full_b[s], (ks / kGemmStages) & 1, dead, err);
+    for (int st = 0; st < NS; ++st) {
+      const int s = st % kGemmStages;
+      mbar_wait(&full_a[s], (st / kGemmStages) & 1, dead, err);
+      mbar_wait(&full_b[s], (st / kGemmStages) & 1, dead, err);
       fence_after();
       if (lane == 0) {
         const uint32_t sa = smem_u32(smem + s * kStage);
         const uint64_t adesc = smem_desc(sa, 2048, 128);
-        const uint64_t bdesc = smem_desc(sa + kUnitBytes, kGemmBN * 16, 128);
+        const uint64_t bdesc = smem_desc(sa + kABytes, kGemmBN * 16, 128);
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
+        for (int j = 0; j < 4; ++j)
           mma_f16(tmem, adesc + (uint64_t)(j * (4096 >> 4)), bdesc + (uint64_t)(j * ((2 * kGemmBN * 16) >> 4)), kIdesc,
-                  (ks == 0 && j == 0) ? 0u : 1u);
+                  (st == 0 && j == 0) ? 0u : 1u);
         commit(&empty[s]);
-        if (ks == KS - 1) commit(&acc_full);
+        if (st == NS - 1) commit(&acc_full);
       }
       __syncwarp();
     }
@@ -233,7 +234,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const GemmPara
   }
 }
 
-constexpr size_t kGemmSmem = (size_t)kGemmStages * (kUnitBytes + kGemmBN * 256) + 1024;
+constexpr size_t kGemmSmem = (size_t)kGemmStages * (kUnitBytes / 2 + kGemmBN * 128) + 1024;
 
 int32_t gemm_launch(Ctx* ctx, const GemmParams& p, cudaStream_t st) {
   dim3 grid((unsigned)ceil_div(p.rows, 128), (unsigned)ceil_div(p.T, kGemmBN));
