@@ -56,7 +56,7 @@ struct GemmParams {
   int ldq = 0, ldkv = 0;
   __nv_bfloat16* kv_layer = nullptr;    // the decode cache of this layer
   int64_t kv_batch_stride = 0, kv_head_stride = 0;
-  const float* inv_freq = nullptr;
+  const float2* rope = nullptr;         // [n_seq, D/2]: (sin, cos) of position pos0 + s times inv_freq[d0]
   int pos0 = 0, n_seq = 1, Hl = 0, KVl = 0, D = 0;
 };
 
@@ -101,14 +101,13 @@ __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, float (&v)[32
   if (hs < p.Hl + p.KVl) {
     const int d0 = 8 * jj + g;                         // rows g / g+8 are the pair (d0, d0 + D/2), src/NN.jl:253-303
     const int d = hi ? d0 + half : d0;
-    const float f = p.inv_freq[d0];
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
       const int t = t0 + i;
       if (t < p.T) {
-        const int b = t / p.n_seq, pos = p.pos0 + (t - b * p.n_seq);
-        const float ang = (float)pos * f;
-        const float sn = sinf(ang), cs = sinf(kHalfPi + ang * -1.0f);
+        const int b = t / p.n_seq, sq = t - b * p.n_seq, pos = p.pos0 + sq;
+        const float2 sc = p.rope[(int64_t)sq * half + d0];
+        const float sn = sc.x, cs = sc.y;
         const float o = hi ? (w[i] * sn + v[i] * cs) : (v[i] * cs + (w[i] * sn) * -1.0f);
         const __nv_bfloat16 ob = __float2bfloat16_rn(o);
         if (hs < p.Hl) {
@@ -135,24 +134,47 @@ __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, float (&v)[32
   }
 }
 
+// Tile order: groups of `gt` token tiles (their activations, about 64 MB, stay in L2); inside a
+// group the row groups follow one another and the token tile is the fast index, so the CTAs running
+// at one time share a few weight row groups and the weights stream from HBM once per group.
+struct TileOrder {
+  int n_tt, n_rg, gt;
+  __device__ __forceinline__ void decode(int tile, int* rg, int* tt) const {
+    const int per_group = gt * n_rg;
+    const int grp = tile / per_group, within = tile - grp * per_group;
+    const int tt0 = grp * gt;
+    const int width = min(gt, n_tt - tt0);          // the last group may be narrower
+    // tiles of the last group are numbered with its own width
+    const int w_rg = within / width;
+    *rg = w_rg;
+    *tt = tt0 + (within - w_rg * width);
+  }
+};
+
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const GemmParams p, int* err) {
   using namespace tc;
   constexpr int kABytes = kUnitBytes / 2;                 // 128 rows x 64 k: half a weight unit (its first / last 8 k-groups)
   constexpr int kBBytes = kGemmBN * 128;                  // 128 tokens x 64 k, bf16
   constexpr int kStage = kABytes + kBBytes;
   extern __shared__ __align__(1024) unsigned char smem[];
-  __shared__ __align__(8) uint64_t full_a[kGemmStages], full_b[kGemmStages], empty[kGemmStages], acc_full;
+  __shared__ __align__(8) uint64_t full_a[kGemmStages], full_b[kGemmStages], empty[kGemmStages], acc_full[2], acc_empty[2];
   __shared__ uint32_t tmem_slot;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int rg = blockIdx.x, t0 = blockIdx.y * kGemmBN;
   const int KS = (p.K + 127) >> 7;                        // weight units along k
-  const int NS = (p.K + 63) >> 6;                         // pipeline steps of 64 k
+  const int NS = (p.K + 63) >> 6;                         // pipeline steps of 64 k per tile
+  // Persistent CTAs walk the tiles with the token tile as the fast index: the CTAs running at one
+  // time share a few weight row groups (L2 hits) and the activations fit L2 as a whole.
+  const int n_tt = (p.T + kGemmBN - 1) / kGemmBN, n_rg = (p.rows + 127) >> 7;
+  const int n_tiles = n_tt * n_rg;
+  TileOrder order;
+  order.n_tt = n_tt; order.n_rg = n_rg;
+  order.gt = max(8, min(n_tt, (64 << 20) / (kGemmBN * p.K * 2)));
   if (tid == 0) {
     for (int s = 0; s < kGemmStages; ++s) { mbar_init(&full_a[s], 1); mbar_init(&full_b[s], 1); mbar_init(&empty[s], 1); }
-    mbar_init(&acc_full, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
     mbar_init_fence();
   }
-  if (warp == 4) tmem_alloc(&tmem_slot, kGemmBN);
+  if (warp == 4) tmem_alloc(&tmem_slot, 2 * kGemmBN);
   fence_before();
   __syncthreads();
   fence_after();
@@ -163,85 +185,123 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const GemmPara
     // activations: row-major [token, k] -> K-major core matrices.  The four loader warps take the
     // steps in turn and each waits for its own step to land, so up to four steps are in flight.
     const int lw = warp - 6;
-    for (int st = lw; st < NS; st += 4) {
-      const int s = st % kGemmStages;
-      mbar_wait(&empty[s], ((st / kGemmStages) & 1) ^ 1, dead, err);
-      const uint32_t sB = smem_u32(smem + s * kStage + kABytes);
-      const int c8 = lane & 7, tok0 = lane >> 3;            // a lane keeps its 16-byte column; tokens advance by 4
-      const int k = st * 64 + c8 * 8;
-      const bool k_ok = k < p.K;
+    const int c8 = lane & 7, tok0 = lane >> 3;              // a lane keeps its 16-byte column; tokens advance by 4
+    int g = 0;                                              // steps issued by all loader warps so far
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+      int rg_, tt_;
+      order.decode(tile, &rg_, &tt_);
+      const int t0 = tt_ * kGemmBN;
+      for (int st = 0; st < NS; ++st, ++g) {
+        if ((g & 3) != lw) continue;
+        const int s = g % kGemmStages;
+        mbar_wait(&empty[s], ((g / kGemmStages) & 1) ^ 1, dead, err);
+        const uint32_t sB = smem_u32(smem + s * kStage + kABytes);
+        const int k = st * 64 + c8 * 8;
+        const bool k_ok = k < p.K;
 #pragma unroll 8
-      for (int it = 0; it < kGemmBN / 4; ++it) {
-        const int tok = tok0 + 4 * it, t = t0 + tok;
-        const bool ok = k_ok && t < p.T;
-        cp_async16(sB + canon(tok, c8, kGemmBN), p.X + (int64_t)(ok ? t : 0) * p.ldx + (ok ? k : 0), ok ? 16u : 0u);
+        for (int it = 0; it < kGemmBN / 4; ++it) {
+          const int tok = tok0 + 4 * it, t = t0 + tok;
+          const bool ok = k_ok && t < p.T;
+          cp_async16(sB + canon(tok, c8, kGemmBN), p.X + (int64_t)(ok ? t : 0) * p.ldx + (ok ? k : 0), ok ? 16u : 0u);
+        }
+        cp_async_commit();
+        cp_async_wait<0>();
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&full_b[s]);
       }
-      cp_async_commit();
-      cp_async_wait<0>();
-      fence_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&full_b[s]);
     }
   } else if (warp == 5) {
     // weights: half a contiguous unit per step
-    for (int st = 0; st < NS; ++st) {
-      const int s = st % kGemmStages;
-      mbar_wait(&empty[s], ((st / kGemmStages) & 1) ^ 1, dead, err);
-      if (lane == 0) {
-        mbar_expect_tx(&full_a[s], (uint32_t)kABytes);
-        bulk_g2s(smem + s * kStage, p.W + ((int64_t)rg * KS + (st >> 1)) * 16384 + (st & 1) * 8192, (uint32_t)kABytes, &full_a[s]);
+    int g = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+      int rg, tt_;
+      order.decode(tile, &rg, &tt_);
+      for (int st = 0; st < NS; ++st, ++g) {
+        const int s = g % kGemmStages;
+        mbar_wait(&empty[s], ((g / kGemmStages) & 1) ^ 1, dead, err);
+        if (lane == 0) {
+          mbar_expect_tx(&full_a[s], (uint32_t)kABytes);
+          bulk_g2s(smem + s * kStage, p.W + ((int64_t)rg * KS + (st >> 1)) * 16384 + (st & 1) * 8192, (uint32_t)kABytes, &full_a[s]);
+        }
+        __syncwarp();
       }
-      __syncwarp();
     }
   } else if (warp == 4) {
     constexpr uint32_t kIdesc = idesc_bf16(128, kGemmBN, false, false);
-    for (int st = 0; st < NS; ++st) {
-      const int s = st % kGemmStages;
-      mbar_wait(&full_a[s], (st / kGemmStages) & 1, dead, err);
-      mbar_wait(&full_b[s], (st / kGemmStages) & 1, dead, err);
+    int g = 0, n = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++n) {
+      const int buf = n & 1;
+      mbar_wait(&acc_empty[buf], ((n >> 1) & 1) ^ 1, dead, err);        // the epilogue has drained this accumulator
       fence_after();
-      if (lane == 0) {
-        const uint32_t sa = smem_u32(smem + s * kStage);
-        const uint64_t adesc = smem_desc(sa, 2048, 128);
-        const uint64_t bdesc = smem_desc(sa + kABytes, kGemmBN * 16, 128);
+      for (int st = 0; st < NS; ++st, ++g) {
+        const int s = g % kGemmStages;
+        mbar_wait(&full_a[s], (g / kGemmStages) & 1, dead, err);
+        mbar_wait(&full_b[s], (g / kGemmStages) & 1, dead, err);
+        fence_after();
+        if (lane == 0) {
+          const uint32_t sa = smem_u32(smem + s * kStage);
+          const uint64_t adesc = smem_desc(sa, 2048, 128);
+          const uint64_t bdesc = smem_desc(sa + kABytes, kGemmBN * 16, 128);
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-          mma_f16(tmem, adesc + (uint64_t)(j * (4096 >> 4)), bdesc + (uint64_t)(j * ((2 * kGemmBN * 16) >> 4)), kIdesc,
-                  (st == 0 && j == 0) ? 0u : 1u);
-        commit(&empty[s]);
-        if (st == NS - 1) commit(&acc_full);
+          for (int j = 0; j < 4; ++j)
+            mma_f16(tmem + buf * kGemmBN, adesc + (uint64_t)(j * (4096 >> 4)), bdesc + (uint64_t)(j * ((2 * kGemmBN * 16) >> 4)),
+                    kIdesc, (st == 0 && j == 0) ? 0u : 1u);
+          commit(&empty[s]);
+          if (st == NS - 1) commit(&acc_full[buf]);
+        }
+        __syncwarp();
       }
-      __syncwarp();
     }
   } else {
-    mbar_wait(&acc_full, 0, dead, err);
-    fence_after();
+    // epilogue of tile n while the MMAs of tile n + 1 fill the other accumulator
     const uint32_t lane_base = (uint32_t)(32 * warp) << 16;
-    const int row = rg * 128 + 32 * warp + lane;
+    int n = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++n) {
+      const int buf = n & 1;
+      int rg_, tt_;
+      order.decode(tile, &rg_, &tt_);
+      const int t0 = tt_ * kGemmBN, row = rg_ * 128 + 32 * warp + lane;
+      mbar_wait(&acc_full[buf], (n >> 1) & 1, dead, err);
+      fence_after();
 #pragma unroll 1
-    for (int ch = 0; ch < kGemmBN / 32; ++ch) {
-      float v[32];
-      tmem_ld32(v, tmem + lane_base + ch * 32);
-      gemm_epilogue(p, v, row, t0 + ch * 32);
+      for (int ch = 0; ch < kGemmBN / 32; ++ch) {
+        float v[32];
+        tmem_ld32(v, tmem + lane_base + buf * kGemmBN + ch * 32);
+        if (ch == kGemmBN / 32 - 1) {                  // the whole accumulator is in registers or done with
+          fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        }
+        gemm_epilogue(p, v, row, t0 + ch * 32);
+      }
     }
-    fence_before();
   }
   fence_before();
   __syncthreads();
   if (warp == 4) {
     fence_after();
-    tmem_dealloc(tmem, kGemmBN);
+    tmem_dealloc(tmem, 2 * kGemmBN);
   }
 }
 
 constexpr size_t kGemmSmem = (size_t)kGemmStages * (kUnitBytes / 2 + kGemmBN * 128) + 1024;
 
 int32_t gemm_launch(Ctx* ctx, const GemmParams& p, cudaStream_t st) {
-  dim3 grid((unsigned)ceil_div(p.rows, 128), (unsigned)ceil_div(p.T, kGemmBN));
-  gemm_tc_kernel<<<grid, kGemmThreads, kGemmSmem, st>>>(p, ctx->dev_err);
+  const int64_t tiles = ceil_div(p.rows, 128) * ceil_div(p.T, kGemmBN);
+  gemm_tc_kernel<<<(unsigned)std::min<int64_t>(tiles, ctx->sm_count), kGemmThreads, kGemmSmem, st>>>(p, ctx->dev_err);
   ctx->launches++;
   LMB_CUDA(cudaGetLastError());
   return LMB200_OK;
+}
+
+// (sin, cos) of every prompt position, with the decode step's expressions (src/NN.jl:253-303)
+__global__ void rope_table_kernel(float2* __restrict__ tab, const float* __restrict__ inv_freq, int pos0, int n_seq, int half) {
+  const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (i >= (int64_t)n_seq * half) return;
+  const int sq = (int)(i / half), d0 = (int)(i - (int64_t)sq * half);
+  const float ang = (float)(pos0 + sq) * inv_freq[d0];
+  tab[i] = make_float2(sinf(ang), sinf(kHalfPi + ang * -1.0f));
 }
 
 // x[t, :] = embedding row of token t (zeros when the id is out of range, as _gather_kernel! does)
@@ -290,7 +350,7 @@ __global__ void last_rows_kernel(float* __restrict__ dst, const float* __restric
 }
 
 struct Scratch {
-  void* p[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  void* p[12] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
   int n = 0;
   ~Scratch() { for (int i = 0; i < n; ++i) cudaFree(p[i]); }
   template <typename T>
@@ -367,6 +427,10 @@ int32_t prefill_gemm(Session* S, const int* tokens_dev, int n, cudaStream_t st) 
   LMB_TRY(sc.get(&vb, (int64_t)T * kvw));
   LMB_TRY(sc.get(&attn, (int64_t)T * qw));
   LMB_TRY(sc.get(&act, (int64_t)T * M->inter_l));
+  float2* rope;
+  LMB_TRY(sc.get(&rope, (int64_t)n * (D / 2)));
+  rope_table_kernel<<<(unsigned)ceil_div((int64_t)n * (D / 2), 256), 256, 0, st>>>(rope, M->inv_freq, 0, n, D / 2);
+  ctx->launches++;
   embed_rows_kernel<<<T, 256, 0, st>>>(x, tokens_dev, reinterpret_cast<const __nv_bfloat16*>(M->embed), c.vocab, hid);
   ctx->launches++;
   const size_t norm_smem = (size_t)hid * sizeof(float);
@@ -389,7 +453,7 @@ int32_t prefill_gemm(Session* S, const int* tokens_dev, int n, cudaStream_t st) 
       p.q = q; p.kbuf = kb; p.vbuf = vb; p.ldq = qw; p.ldkv = kvw;
       p.kv_layer = reinterpret_cast<__nv_bfloat16*>(S->kv) + (int64_t)l * S->kv_layer_stride;
       p.kv_batch_stride = S->kv_batch_stride; p.kv_head_stride = S->kv_head_stride;
-      p.inv_freq = M->inv_freq; p.pos0 = 0; p.n_seq = n; p.Hl = M->Hl; p.KVl = M->KVl; p.D = D;
+      p.rope = rope; p.pos0 = 0; p.n_seq = n; p.Hl = M->Hl; p.KVl = M->KVl; p.D = D;
       LMB_TRY(gemm_launch(ctx, p, st));
     }
     LMB_TRY(flash_tc_launch_view(ctx, attn, q, kb, vb, fv, B, n, D, 1.0f / sqrtf((float)D), 1, st));
