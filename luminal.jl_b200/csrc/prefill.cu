@@ -8,12 +8,13 @@
 //
 // gemm_tc_kernel: acc[row, token] = sum_k W[row, k] * X[token, k]
 //   one CTA = 128 weight rows x 128 tokens, k in steps of 64 through a 6-stage ring:
-//   warp 5      : bulk copies of half weight units (16 KB, already in the tensor core's layout),
-//   warps 6..9  : cp.async 16-byte chunks of the row-major activations into the same layout, the
-//                 warps taking the steps in turn,
+//   warp 5      : one thread issues, per step, a bulk copy of half a weight unit (16 KB, already in
+//                 the tensor core's layout) and a 3-D TMA box of the row-major activations that lands
+//                 in the same layout,
 //   warp 4      : one thread issues tcgen05.mma 128 x 128 x 16,
 //   warps 0..3  : epilogue, one weight row per thread, tcgen05.ld 32 tokens at a time:
 //                 store float32 / SiLU(gate) * up / RoPE + q, k, v (and the cache).
+#include <cuda.h>
 #include <math_constants.h>
 #include <stdlib.h>
 #include <string.h>
@@ -33,7 +34,7 @@ namespace {
 
 constexpr int kGemmBN = 128;
 constexpr int kGemmStages = 6;
-constexpr int kGemmThreads = 10 * 32;
+constexpr int kGemmThreads = 6 * 32;
 constexpr int kUnitBytes = 32768;
 constexpr float kInvLn2 = 1.4426950408889634f;
 constexpr float kHalfPi = 1.5707963267948966f;
@@ -151,13 +152,14 @@ struct TileOrder {
   }
 };
 
-__global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const GemmParams p, int* err) {
+__global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap,
+                                                                  int* err) {
   using namespace tc;
   constexpr int kABytes = kUnitBytes / 2;                 // 128 rows x 64 k: half a weight unit (its first / last 8 k-groups)
   constexpr int kBBytes = kGemmBN * 128;                  // 128 tokens x 64 k, bf16
   constexpr int kStage = kABytes + kBBytes;
   extern __shared__ __align__(1024) unsigned char smem[];
-  __shared__ __align__(8) uint64_t full_a[kGemmStages], full_b[kGemmStages], empty[kGemmStages], acc_full[2], acc_empty[2];
+  __shared__ __align__(8) uint64_t full[kGemmStages], empty[kGemmStages], acc_full[2], acc_empty[2];
   __shared__ uint32_t tmem_slot;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int KS = (p.K + 127) >> 7;                        // weight units along k
@@ -170,7 +172,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const GemmPara
   order.n_tt = n_tt; order.n_rg = n_rg;
   order.gt = max(8, min(n_tt, (64 << 20) / (kGemmBN * p.K * 2)));
   if (tid == 0) {
-    for (int s = 0; s < kGemmStages; ++s) { mbar_init(&full_a[s], 1); mbar_init(&full_b[s], 1); mbar_init(&empty[s], 1); }
+    for (int s = 0; s < kGemmStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
     mbar_init_fence();
   }
@@ -181,38 +183,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const GemmPara
   const uint32_t tmem = tmem_slot;
   bool dead = false;
 
-  if (warp >= 6) {
-    // activations: row-major [token, k] -> K-major core matrices.  The four loader warps take the
-    // steps in turn and each waits for its own step to land, so up to four steps are in flight.
-    const int lw = warp - 6;
-    const int c8 = lane & 7, tok0 = lane >> 3;              // a lane keeps its 16-byte column; tokens advance by 4
-    int g = 0;                                              // steps issued by all loader warps so far
-    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-      int rg_, tt_;
-      order.decode(tile, &rg_, &tt_);
-      const int t0 = tt_ * kGemmBN;
-      for (int st = 0; st < NS; ++st, ++g) {
-        if ((g & 3) != lw) continue;
-        const int s = g % kGemmStages;
-        mbar_wait(&empty[s], ((g / kGemmStages) & 1) ^ 1, dead, err);
-        const uint32_t sB = smem_u32(smem + s * kStage + kABytes);
-        const int k = st * 64 + c8 * 8;
-        const bool k_ok = k < p.K;
-#pragma unroll 8
-        for (int it = 0; it < kGemmBN / 4; ++it) {
-          const int tok = tok0 + 4 * it, t = t0 + tok;
-          const bool ok = k_ok && t < p.T;
-          cp_async16(sB + canon(tok, c8, kGemmBN), p.X + (int64_t)(ok ? t : 0) * p.ldx + (ok ? k : 0), ok ? 16u : 0u);
-        }
-        cp_async_commit();
-        cp_async_wait<0>();
-        fence_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&full_b[s]);
-      }
-    }
-  } else if (warp == 5) {
-    // weights: half a contiguous unit per step
+  if (warp == 5) {
+    // producer: per step half a weight unit (bulk copy, already in the tensor core's layout) and the
+    // activations of 128 tokens x 64 k through a 3-D tensor map over the row-major [T, K] matrix seen
+    // as [k/8][token][8]: the box {8, 128, 8} lands as K-major core matrices, rows past T as zeros
     int g = 0;
     for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
       int rg, tt_;
@@ -221,8 +195,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const GemmPara
         const int s = g % kGemmStages;
         mbar_wait(&empty[s], ((g / kGemmStages) & 1) ^ 1, dead, err);
         if (lane == 0) {
-          mbar_expect_tx(&full_a[s], (uint32_t)kABytes);
-          bulk_g2s(smem + s * kStage, p.W + ((int64_t)rg * KS + (st >> 1)) * 16384 + (st & 1) * 8192, (uint32_t)kABytes, &full_a[s]);
+          mbar_expect_tx(&full[s], (uint32_t)kStage);
+          bulk_g2s(smem + s * kStage, p.W + ((int64_t)rg * KS + (st >> 1)) * 16384 + (st & 1) * 8192, (uint32_t)kABytes, &full[s]);
+          asm volatile(
+              "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n" ::"r"(
+                  smem_u32(smem + s * kStage + kABytes)),
+              "l"(reinterpret_cast<uint64_t>(&xmap)), "r"(0), "r"(tt_ * kGemmBN), "r"(st * 8), "r"(smem_u32(&full[s]))
+              : "memory");
         }
         __syncwarp();
       }
@@ -236,8 +215,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const GemmPara
       fence_after();
       for (int st = 0; st < NS; ++st, ++g) {
         const int s = g % kGemmStages;
-        mbar_wait(&full_a[s], (g / kGemmStages) & 1, dead, err);
-        mbar_wait(&full_b[s], (g / kGemmStages) & 1, dead, err);
+        mbar_wait(&full[s], (g / kGemmStages) & 1, dead, err);
         fence_after();
         if (lane == 0) {
           const uint32_t sa = smem_u32(smem + s * kStage);
@@ -287,9 +265,40 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const GemmPara
 
 constexpr size_t kGemmSmem = (size_t)kGemmStages * (kUnitBytes / 2 + kGemmBN * 128) + 1024;
 
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// cuTensorMapEncodeTiled, resolved through the runtime so the library does not link libcuda
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    else
+      cudaGetLastError();
+  }
+  return fn;
+}
+
 int32_t gemm_launch(Ctx* ctx, const GemmParams& p, cudaStream_t st) {
+  LMB_REQUIRE(p.K % 8 == 0 && p.ldx % 8 == 0 && (reinterpret_cast<uintptr_t>(p.X) & 15) == 0, "prefill gemm: K %d, row pitch %d", p.K, p.ldx);
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return fail(LMB200_ECUDA, "prefill gemm: cuTensorMapEncodeTiled is not available");
+  CUtensorMap xmap;
+  const cuuint64_t dims[3] = {8, (cuuint64_t)p.T, (cuuint64_t)(p.K / 8)};
+  const cuuint64_t strides[2] = {(cuuint64_t)p.ldx * 2, 16};          // bytes, dims 1 and 2
+  const cuuint32_t box[3] = {8, (cuuint32_t)kGemmBN, 8};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = enc(&xmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<__nv_bfloat16*>(p.X), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(LMB200_ECUDA, "prefill gemm: cuTensorMapEncodeTiled failed (%d)", (int)r);
   const int64_t tiles = ceil_div(p.rows, 128) * ceil_div(p.T, kGemmBN);
-  gemm_tc_kernel<<<(unsigned)std::min<int64_t>(tiles, ctx->sm_count), kGemmThreads, kGemmSmem, st>>>(p, ctx->dev_err);
+  gemm_tc_kernel<<<(unsigned)std::min<int64_t>(tiles, ctx->sm_count), kGemmThreads, kGemmSmem, st>>>(p, xmap, ctx->dev_err);
   ctx->launches++;
   LMB_CUDA(cudaGetLastError());
   return LMB200_OK;
