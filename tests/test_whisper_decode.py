@@ -110,3 +110,54 @@ def test_whisper_encoder_graph_matches_oracle(lib_built, device):
     assert np.abs(np.stack(logs, 1) - ref_log).max() <= 1e-3
     assert np.array_equal(np.stack(toks, 1), ref_tok)
     sess.close(); model.close()
+
+
+def _fast_weights(cfg, seed):
+    """Whisper-base is 70 M parameters: a NumPy generator instead of the counter-based one."""
+    rng = np.random.default_rng(seed)
+    w = {}
+    for name, shape in sorted(W.weight_shapes(cfg).items()):
+        a = rng.standard_normal(shape, dtype=np.float32) * np.float32(0.02)
+        w[name] = a + np.float32(1.0) if name.endswith("layer_norm.weight") else a
+    return w
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_whisper_base_full_size_decoder(lib_built, device, dtype):
+    """The Whisper-base decoder at its full size (d_model 512, 8 heads, 6 layers, FFN 2048, vocab
+    51865, batch 8, 1500 encoder positions): the oracle is small enough to run it whole."""
+    L = lib_built
+    cfg = W.CONFIGS["whisper_base"]
+    batch, T, steps = 8, 1500, 5
+    w = _fast_weights(cfg, 17)
+    if dtype == "bf16":
+        w = {k: (O.bf16_round(v) if v.ndim == 2 and "embed_positions" not in k else v) for k, v in w.items()}
+    rng = np.random.default_rng(3)
+    D = cfg["d_model"] // cfg["heads"]
+    kv = [(rng.standard_normal((batch, cfg["heads"], T, D), dtype=np.float32) * np.float32(0.5),
+           rng.standard_normal((batch, cfg["heads"], T, D), dtype=np.float32)) for _ in range(cfg["dec_layers"])]
+    if dtype == "bf16":
+        kv = [(O.bf16_round(k), O.bf16_round(v)) for k, v in kv]
+    first = O.synth_tokens(17, 6, (batch,), cfg["vocab"])
+    ref = W.CachedDecoder(w, cfg, batch, kv)
+    model, sess = build(L, device, cfg, w, batch, kv, dtype, T)
+    tok = first.astype(np.int32)
+    for step in range(steps):
+        ref_logits = ref.step(tok)
+        nxt, logits = sess.decode_step(tok, want_logits=True)
+        if dtype == "f32":
+            assert np.abs(logits - ref_logits).max() <= 1e-3, step
+            assert np.array_equal(nxt, ref_logits.argmax(-1)), step
+        else:
+            assert np.linalg.norm(logits - ref_logits) / np.linalg.norm(ref_logits) <= 4e-2, step
+        tok = ref_logits.argmax(-1).astype(np.int32)          # teacher forcing with the oracle's tokens
+    # the CUDA-graph loop reproduces the stepwise tokens
+    sess.reset()
+    tok = first.astype(np.int32)
+    stepwise = []
+    for _ in range(steps):
+        tok = sess.decode_step(tok)
+        stepwise.append(tok.copy())
+    sess.reset()
+    assert np.array_equal(sess.decode_n(first, steps), np.stack(stepwise, 0))
+    sess.close(); model.close()
