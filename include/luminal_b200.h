@@ -167,6 +167,26 @@ int32_t lmb200_rope(lmb200_ctx ctx, float* out, const float* x, int64_t B, int64
 int32_t lmb200_linear_gemv(lmb200_ctx ctx, int32_t dtype, int32_t variant, int32_t rows, int32_t K,
                            int32_t batch, const float* w_host, const float* x_host, float* out_host);
 
+/* ------------------------------------------------------------------------------------------
+ * Whisper AudioEncoder + cross-K/V projection on the tensor cores (bf16 operands, float32
+ * accumulation and residual stream).  Replaces running AudioEncoder (src/Whisper.jl:354-404; Conv1D
+ * src/NN.jl:55-104; WhisperSelfAttention src/Whisper.jl:238-276) and project_cross_kv
+ * (src/Whisper.jl:809-831) node by node.  Weights are set by the reference's registry names
+ * (model.encoder.*, model.decoder.layers.{i}.encoder_attn.{k,v}_proj.*), full logical tensors.
+ * ------------------------------------------------------------------------------------------ */
+typedef uint64_t lmb200_whisper_encoder;
+int32_t lmb200_whisper_encoder_create(lmb200_ctx ctx, int32_t d_model, int32_t heads, int32_t layers, int32_t ffn,
+                                      int32_t n_mels, int32_t dec_layers, lmb200_whisper_encoder* out);
+int32_t lmb200_whisper_encoder_destroy(lmb200_whisper_encoder enc);
+int32_t lmb200_whisper_encoder_set_weight(lmb200_whisper_encoder enc, const char* name, const float* host, int32_t layout);
+/* mel [batch, n_mels, frames] float32 row-major on the host; out_host NULL or [batch, (frames - 1) / 2 + 1, d_model].
+ * The output also stays on the device for lmb200_whisper_encoder_cross_kv. */
+int32_t lmb200_whisper_encoder_run(lmb200_whisper_encoder enc, const float* mel_host, int32_t batch, int32_t frames,
+                                   float* out_host);
+/* Cross K/V of every decoder layer from the last encoder output, written into the (bf16 Whisper) session's
+ * cross cache: project_cross_kv + lmb200_session_set_cross_kv without the trip through the host. */
+int32_t lmb200_whisper_encoder_cross_kv(lmb200_whisper_encoder enc, lmb200_session session);
+
 /* out[t, o] = sum_i x[t, i] * w[o, i] for many rows t at once (the prompt phase) through the
  * tensor-core GEMM (bf16 operands, float32 accumulation): w [rows, K], x [n_tokens, K] and out
  * [n_tokens, rows] are float32 row-major host arrays; K must be a multiple of 8.  Replaces

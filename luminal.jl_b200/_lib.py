@@ -73,6 +73,11 @@ SIGNATURES = {
     "lmb200_argmax": [_u64, _vp, _vp, _i64, _i64],
     "lmb200_linear_gemv": [_u64, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp],
     "lmb200_prefill_gemm": [_u64, _i32, _i32, _i32, _vp, _vp, _vp],
+    "lmb200_whisper_encoder_create": [_u64, _i32, _i32, _i32, _i32, _i32, _i32, C.POINTER(_u64)],
+    "lmb200_whisper_encoder_destroy": [_u64],
+    "lmb200_whisper_encoder_set_weight": [_u64, C.c_char_p, _vp, _i32],
+    "lmb200_whisper_encoder_run": [_u64, _vp, _i32, _i32, _vp],
+    "lmb200_whisper_encoder_cross_kv": [_u64, _u64],
     "lmb200_model_create": [_u64, C.POINTER(ModelConfig), C.POINTER(_u64)],
     "lmb200_shard_extent": [C.POINTER(ModelConfig), _i32, _pi32, _pi32],
     "lmb200_shard_map": [C.POINTER(ModelConfig), _i32, _i32, _i32, _pi32, _pi32, _pi32],

@@ -39,7 +39,7 @@ constexpr int kUnitBytes = 32768;
 constexpr float kInvLn2 = 1.4426950408889634f;
 constexpr float kHalfPi = 1.5707963267948966f;
 
-enum GemmEpilogue { GEMM_STORE_F32 = 0, GEMM_SILU_GATE = 1, GEMM_QKV_ROPE = 2 };
+enum GemmEpilogue { GEMM_STORE_F32 = 0, GEMM_SILU_GATE = 1, GEMM_QKV_ROPE = 2, GEMM_AFFINE = 3, GEMM_CROSS_KV = 4 };
 
 struct GemmParams {
   const __nv_bfloat16* W = nullptr;     // canonical 128 x 128 units, unit (row group, k step) at (rg * KS + ks) * 16384
@@ -57,9 +57,24 @@ struct GemmParams {
   int ldq = 0, ldkv = 0;
   __nv_bfloat16* kv_layer = nullptr;    // the decode cache of this layer
   int64_t kv_batch_stride = 0, kv_head_stride = 0;
+  // GEMM_AFFINE: y = (acc + bias[row]) -> gelu? -> * out_scale, stored float32 or bf16 at out_any[token * ldo + row]
+  // GEMM_CROSS_KV: the same y as bf16 into a tiled cache layer: row = head * D + d, token = b * n_seq + position
+  const float* bias = nullptr;
+  float out_scale = 1.f;
+  int gelu = 0, out_bf16 = 0, is_v = 0;
+  void* out_any = nullptr;
   const float2* rope = nullptr;         // [n_seq, D/2]: (sin, cos) of position pos0 + s times inv_freq[d0]
   int pos0 = 0, n_seq = 1, Hl = 0, KVl = 0, D = 0;
 };
+
+// GELU with the reference's tanh (src/HighLevelOps.jl:162-168): tanh z = sigmoid(2z) * 2 - 1
+__device__ __forceinline__ float gelu_ref(float a) {
+  const float inner = (0.7978845608f * a) * (1.0f + (0.044715f * a) * a);
+  const float z = inner * 2.0f;
+  const float sg = 1.0f / (1.0f + exp2f((z * -1.0f) * kInvLn2));
+  const float th = sg * 2.0f + -1.0f;
+  return (a * 0.5f) * (1.0f + th);
+}
 
 __device__ __forceinline__ uint32_t canon(int row, int c8, int rows) {
   return (uint32_t)(c8 * (rows * 16) + (row >> 3) * 128 + (row & 7) * 16);
@@ -74,6 +89,29 @@ __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, float (&v)[32
 #pragma unroll
       for (int i = 0; i < 32; ++i)
         if (t0 + i < p.T) p.out[(int64_t)(t0 + i) * p.ldo + row] = v[i];
+    }
+    return;
+  }
+  if (p.epi == GEMM_AFFINE || p.epi == GEMM_CROSS_KV) {
+    if (row >= p.rows) return;
+    const float bias = p.bias ? p.bias[row] : 0.f;
+    const int h = p.epi == GEMM_CROSS_KV ? row / p.D : 0, d = p.epi == GEMM_CROSS_KV ? row - h * p.D : 0;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const int t = t0 + i;
+      if (t >= p.T) continue;
+      float y = v[i] + bias;
+      if (p.gelu) y = gelu_ref(y);
+      y *= p.out_scale;
+      if (p.epi == GEMM_CROSS_KV) {
+        const int b = t / p.n_seq, pos = t - b * p.n_seq;
+        p.kv_layer[b * p.kv_batch_stride + h * p.kv_head_stride + (p.is_v ? vcache_offset(pos, d, p.D) : kcache_offset(pos, d, p.D))] =
+            __float2bfloat16_rn(y);
+      } else if (p.out_bf16) {
+        reinterpret_cast<__nv_bfloat16*>(p.out_any)[(int64_t)t * p.ldo + row] = __float2bfloat16_rn(y);
+      } else {
+        reinterpret_cast<float*>(p.out_any)[(int64_t)t * p.ldo + row] = y;
+      }
     }
     return;
   }
@@ -400,6 +438,26 @@ int32_t prefill_linear(Ctx* ctx, const void* W, const float* x_dev, int T, int r
   LMB_TRY(gemm_launch(ctx, p, st));
   LMB_CUDA(cudaStreamSynchronize(st));
   return LMB200_OK;
+}
+
+// y[t, row] = ((sum_k x[t, k] W[row, k]) + bias[row]) -> gelu? -> * scale, float32 or bf16 at out[t * ldo + row]
+int32_t gemm_affine(Ctx* ctx, const void* W, const __nv_bfloat16* X, int ldx, int T, int rows, int K, const float* bias, float scale,
+                    int gelu, void* out, int ldo, int out_bf16, cudaStream_t st) {
+  GemmParams p;
+  p.W = reinterpret_cast<const __nv_bfloat16*>(W); p.X = X; p.ldx = ldx; p.T = T; p.rows = rows; p.K = K;
+  p.epi = GEMM_AFFINE; p.bias = bias; p.out_scale = scale; p.gelu = gelu; p.out_bf16 = out_bf16; p.out_any = out; p.ldo = ldo;
+  return gemm_launch(ctx, p, st);
+}
+
+// the same product written as bf16 into a tiled cache layer (rows = heads * D in head-major order)
+int32_t gemm_cross_kv(Ctx* ctx, const void* W, const __nv_bfloat16* X, int ldx, int T, int rows, int K, const float* bias, float scale,
+                      void* kv_layer, int64_t batch_stride, int64_t head_stride, int n_seq, int D, int is_v, cudaStream_t st) {
+  GemmParams p;
+  p.W = reinterpret_cast<const __nv_bfloat16*>(W); p.X = X; p.ldx = ldx; p.T = T; p.rows = rows; p.K = K;
+  p.epi = GEMM_CROSS_KV; p.bias = bias; p.out_scale = scale; p.is_v = is_v;
+  p.kv_layer = reinterpret_cast<__nv_bfloat16*>(kv_layer); p.kv_batch_stride = batch_stride; p.kv_head_stride = head_stride;
+  p.n_seq = n_seq; p.D = D;
+  return gemm_launch(ctx, p, st);
 }
 
 int32_t prefill_configure() {

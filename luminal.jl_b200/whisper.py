@@ -166,5 +166,50 @@ def encode_cross_kv(device, weights, mel, *, d_model, heads, enc_layers, dec_lay
     return res[enc.id], [(res[k.id], res[v.id]) for k, v in kv]
 
 
-__all__ = ["AudioEncoder", "Conv1D", "WhisperSelfAttention", "EncoderTransformerBlock", "sinusoids", "project_cross_kv",
+class FusedEncoder:
+    """AudioEncoder + project_cross_kv on the tensor cores (bf16): the fused counterpart of
+    encode_cross_kv.  Weights by the reference's registry names; names it does not use are skipped."""
+
+    def __init__(self, device, *, d_model, heads, enc_layers, dec_layers, ffn, n_mels):
+        import ctypes as C
+        from . import _lib
+        self._lib, self._C = _lib, C
+        self.device, self.d_model = device, d_model
+        h = C.c_uint64(0)
+        _lib.call("lmb200_whisper_encoder_create", device.handle, d_model, heads, enc_layers, ffn, n_mels, dec_layers, C.byref(h))
+        self.handle = h
+
+    def set_weights(self, weights):
+        C = self._C
+        used = []
+        for name, a in weights.items():
+            if not (name.startswith("model.encoder.") or ".encoder_attn.k_proj." in name or ".encoder_attn.v_proj." in name):
+                continue
+            host = np.ascontiguousarray(np.asarray(a, dtype=np.float32))
+            self._lib.call("lmb200_whisper_encoder_set_weight", self.handle, name.encode(), host.ctypes.data_as(C.c_void_p), 0)
+            used.append(name)
+        return used
+
+    def run(self, mel, want_output=True):
+        """mel [batch, n_mels, frames] -> encoder output [batch, frames // 2 (rounded up), d_model] (or None)."""
+        C = self._C
+        mel = np.ascontiguousarray(np.asarray(mel, dtype=np.float32))
+        batch, _, frames = mel.shape
+        seq = (frames - 1) // 2 + 1
+        out = np.empty((batch, seq, self.d_model), dtype=np.float32) if want_output else None
+        self._lib.call("lmb200_whisper_encoder_run", self.handle, mel.ctypes.data_as(C.c_void_p), batch, frames,
+                       out.ctypes.data_as(C.c_void_p) if want_output else None)
+        return out
+
+    def cross_kv_into(self, session):
+        """Projects the last output to every decoder layer's cross K/V, straight into the session's cache."""
+        self._lib.call("lmb200_whisper_encoder_cross_kv", self.handle, session.handle)
+
+    def close(self):
+        if self.handle:
+            self._lib.call("lmb200_whisper_encoder_destroy", self.handle)
+            self.handle = None
+
+
+__all__ = ["FusedEncoder", "AudioEncoder", "Conv1D", "WhisperSelfAttention", "EncoderTransformerBlock", "sinusoids", "project_cross_kv",
            "encode_cross_kv"]

@@ -161,3 +161,36 @@ def test_whisper_base_full_size_decoder(lib_built, device, dtype):
     sess.reset()
     assert np.array_equal(sess.decode_n(first, steps), np.stack(stepwise, 0))
     sess.close(); model.close()
+
+
+@pytest.mark.parametrize("batch,frames", [(2, 60), (3, 301)])
+def test_fused_encoder_matches_oracle(lib_built, device, batch, frames):
+    """AudioEncoder + cross K/V projection on the tensor cores (bf16) against the float32 oracle, then
+    the decoder on the cross cache the fused path wrote."""
+    L = lib_built
+    cfg = W.CONFIGS["whisper_test"]
+    w = W.synth_weights(cfg, seed=23)
+    mel = O.synth_normal(23, 5, (batch, cfg["n_mels"], frames), 1.0)
+    ref_enc = W.encoder(mel, w, cfg)
+    ref_kv = W.project_cross_kv(ref_enc, w, cfg)
+    enc = L.whisper.FusedEncoder(device, d_model=cfg["d_model"], heads=cfg["heads"], enc_layers=cfg["enc_layers"],
+                                 dec_layers=cfg["dec_layers"], ffn=cfg["ffn"], n_mels=cfg["n_mels"])
+    enc.set_weights(w)
+    out = enc.run(mel)
+    assert out.shape == ref_enc.shape
+    assert np.linalg.norm(out - ref_enc) / np.linalg.norm(ref_enc) <= 2e-2
+    T = ref_enc.shape[1]
+    model = L.WhisperDecoderModel(device, d_model=cfg["d_model"], heads=cfg["heads"], layers=cfg["dec_layers"], ffn=cfg["ffn"],
+                                  vocab=cfg["vocab"], max_positions=cfg["max_positions"], cross_len=T, dtype="bf16")
+    for name, a in w.items():
+        model.set_weight(name, a)
+    sess = L.Session(model, batch, cfg["max_positions"])
+    enc.cross_kv_into(sess)
+    ref = W.CachedDecoder(w, cfg, batch, ref_kv)
+    tok = O.synth_tokens(23, 6, (batch,), cfg["vocab"])
+    for step in range(5):
+        ref_logits = ref.step(tok)
+        _, logits = sess.decode_step(tok, want_logits=True)
+        assert np.linalg.norm(logits - ref_logits) / np.linalg.norm(ref_logits) <= 4e-2, step
+        tok = ref_logits.argmax(-1)
+    sess.close(); model.close(); enc.close()
