@@ -35,6 +35,24 @@ namespace {
 
 constexpr float kHalfPi = 1.5707963267948966f;
 
+struct Bufs {
+  std::vector<void*> p;
+  ~Bufs() { release(); }
+  void release() { for (void* q : p) cudaFree(q); p.clear(); }
+  template <typename T>
+  int32_t get(T** out, int64_t elems) {
+    void* q = nullptr;
+    if (cudaMalloc(&q, (size_t)(elems * (int64_t)sizeof(T))) != cudaSuccess) {
+      cudaGetLastError();
+      return fail(LMB200_ENOMEM, "whisper encoder: scratch allocation failed");
+    }
+    p.push_back(q);
+    *out = reinterpret_cast<T*>(q);
+    return LMB200_OK;
+  }
+};
+
+
 struct EncLinear {
   void* W = nullptr;        // bf16, tensor-core weight layout
   float* bias = nullptr;    // [rows] or NULL
@@ -56,6 +74,12 @@ struct WhisperEncoder {
   __nv_bfloat16* enc_b = nullptr;       // last output, bf16 [B * S, d]
   float* enc_f = nullptr;               // last output, float32
   int out_B = 0, out_S = 0;
+  // scratch of the last run, kept while the input shape stays the same
+  Bufs scratch;
+  int scratch_B = 0, scratch_frames = 0;
+  float *mel = nullptr, *x = nullptr, *delta = nullptr;
+  __nv_bfloat16 *col1 = nullptr, *h1 = nullptr, *col2 = nullptr, *xn = nullptr, *qb = nullptr, *kb = nullptr, *vb = nullptr, *attn = nullptr,
+                *act = nullptr;
 };
 
 WhisperEncoder* enc_from(uint64_t h) {
@@ -193,19 +217,6 @@ int32_t upload_vector(WhisperEncoder* E, float** dst, const float* host, int n, 
 
 void free_linear(EncLinear& l) { cudaFree(l.W); cudaFree(l.bias); l.W = nullptr; l.bias = nullptr; }
 
-struct Bufs {
-  std::vector<void*> p;
-  ~Bufs() { for (void* q : p) cudaFree(q); }
-  template <typename T>
-  int32_t get(T** out, int64_t elems) {
-    void* q = nullptr;
-    LMB_TRY(dev_alloc(&q, elems * (int64_t)sizeof(T)));
-    p.push_back(q);
-    *out = reinterpret_cast<T*>(q);
-    return LMB200_OK;
-  }
-};
-
 }  // namespace
 }  // namespace lmb
 
@@ -252,6 +263,7 @@ extern "C" int32_t lmb200_whisper_encoder_destroy(uint64_t h) {
   for (EncLinear& l : E->cross_k) free_linear(l);
   for (EncLinear& l : E->cross_v) free_linear(l);
   cudaFree(E->post_w); cudaFree(E->post_b); cudaFree(E->inv_ts); cudaFree(E->enc_b); cudaFree(E->enc_f);
+  E->scratch.release();
   E->magic = 0;
   delete E;
   return LMB200_OK;
@@ -331,21 +343,27 @@ extern "C" int32_t lmb200_whisper_encoder_run(uint64_t h, const float* mel_host,
   const int L1 = frames;                         // conv1: kernel 3, stride 1, padding 1
   const int S = (frames + 2 - 3) / 2 + 1;        // conv2: kernel 3, stride 2, padding 1
   const int64_t T1 = (int64_t)batch * L1, T = (int64_t)batch * S;
-  Bufs sc;
-  float *mel, *x, *delta;
-  __nv_bfloat16 *col1, *h1, *col2, *xn, *qb, *kb, *vb, *attn, *act;
-  LMB_TRY(sc.get(&mel, (int64_t)batch * C1 * frames));
-  LMB_TRY(sc.get(&col1, T1 * C1 * 3));
-  LMB_TRY(sc.get(&h1, T1 * d));
-  LMB_TRY(sc.get(&col2, T * d * 3));
-  LMB_TRY(sc.get(&x, T * d));
-  LMB_TRY(sc.get(&delta, T * d));
-  LMB_TRY(sc.get(&xn, T * d));
-  LMB_TRY(sc.get(&qb, T * d));
-  LMB_TRY(sc.get(&kb, T * d));
-  LMB_TRY(sc.get(&vb, T * d));
-  LMB_TRY(sc.get(&attn, T * d));
-  LMB_TRY(sc.get(&act, T * E->ffn));
+  if (E->scratch_B != batch || E->scratch_frames != frames) {
+    E->scratch.release();
+    E->scratch_B = E->scratch_frames = 0;
+    Bufs& sc = E->scratch;
+    LMB_TRY(sc.get(&E->mel, (int64_t)batch * C1 * frames));
+    LMB_TRY(sc.get(&E->col1, T1 * C1 * 3));
+    LMB_TRY(sc.get(&E->h1, T1 * d));
+    LMB_TRY(sc.get(&E->col2, T * d * 3));
+    LMB_TRY(sc.get(&E->x, T * d));
+    LMB_TRY(sc.get(&E->delta, T * d));
+    LMB_TRY(sc.get(&E->xn, T * d));
+    LMB_TRY(sc.get(&E->qb, T * d));
+    LMB_TRY(sc.get(&E->kb, T * d));
+    LMB_TRY(sc.get(&E->vb, T * d));
+    LMB_TRY(sc.get(&E->attn, T * d));
+    LMB_TRY(sc.get(&E->act, T * E->ffn));
+    E->scratch_B = batch; E->scratch_frames = frames;
+  }
+  float *mel = E->mel, *x = E->x, *delta = E->delta;
+  __nv_bfloat16 *col1 = E->col1, *h1 = E->h1, *col2 = E->col2, *xn = E->xn, *qb = E->qb, *kb = E->kb, *vb = E->vb, *attn = E->attn,
+                *act = E->act;
   if (E->out_B * E->out_S != T) {
     cudaFree(E->enc_b); cudaFree(E->enc_f);
     E->enc_b = nullptr; E->enc_f = nullptr;
