@@ -198,24 +198,50 @@ __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(float* __rest
   } else {
     const float4* dr = delta ? reinterpret_cast<const float4*>(delta + (int64_t)b * n) : nullptr;
     float4* cr = capture ? reinterpret_cast<float4*>(capture + (int64_t)b * n) : nullptr;
+    if (peers) {
+      // two row elements per pass, every rank's partial of both in flight at once (one NVLink round
+      // trip for a row of up to 2 x kNormThreads float4s), summed in rank order
+      for (int i0 = tid; i0 < n4; i0 += 2 * kNormThreads) {
+        const int i1 = i0 + kNormThreads;
+        const bool two = i1 < n4;
+        float4 e0[8], e1[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          if (r < pr.n) {
+            e0[r] = peer_load4(pr.part[r] + (int64_t)b * n + 4 * i0);
+            if (two) e1[r] = peer_load4(pr.part[r] + (int64_t)b * n + 4 * i1);
+          }
+        }
+        float4 v0 = xr[i0], v1 = two ? xr[i1] : make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 d0 = e0[0], d1 = two ? e1[0] : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int r = 1; r < 8; ++r) {
+          if (r < pr.n) {
+            d0.x += e0[r].x; d0.y += e0[r].y; d0.z += e0[r].z; d0.w += e0[r].w;
+            if (two) { d1.x += e1[r].x; d1.y += e1[r].y; d1.z += e1[r].z; d1.w += e1[r].w; }
+          }
+        }
+        v0.x += d0.x; v0.y += d0.y; v0.z += d0.z; v0.w += d0.w;
+        xr[i0] = v0; rs[i0] = v0;
+        if (cr) cr[i0] = v0;
+        ss += v0.x * v0.x + v0.y * v0.y + v0.z * v0.z + v0.w * v0.w;
+        if (two) {
+          v1.x += d1.x; v1.y += d1.y; v1.z += d1.z; v1.w += d1.w;
+          xr[i1] = v1; rs[i1] = v1;
+          if (cr) cr[i1] = v1;
+          ss += v1.x * v1.x + v1.y * v1.y + v1.z * v1.z + v1.w * v1.w;
+        }
+      }
+    } else {
 #pragma unroll 4
-    for (int i = tid; i < n4; i += kNormThreads) {
-      float4 v = xr[i];
-      if (peers) {
-        float4 e[8];                       // every rank's partial in flight at once, summed in rank order
-#pragma unroll
-        for (int r = 0; r < 8; ++r)
-          if (r < pr.n) e[r] = peer_load4(pr.part[r] + (int64_t)b * n + 4 * i);
-        float4 d = e[0];
-#pragma unroll
-        for (int r = 1; r < 8; ++r)
-          if (r < pr.n) { d.x += e[r].x; d.y += e[r].y; d.z += e[r].z; d.w += e[r].w; }
-        v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
-      } else if (dr) { const float4 d = dr[i]; v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w; }
-      xr[i] = v;
-      rs[i] = v;
-      if (cr) cr[i] = v;
-      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+      for (int i = tid; i < n4; i += kNormThreads) {
+        float4 v = xr[i];
+        if (dr) { const float4 d = dr[i]; v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w; }
+        xr[i] = v;
+        rs[i] = v;
+        if (cr) cr[i] = v;
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+      }
     }
   }
 #pragma unroll
