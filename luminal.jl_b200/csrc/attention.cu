@@ -324,8 +324,6 @@ __global__ void attn_combine_kernel(const AttnParams p) {
 // The decode-attention kernels keep their operands in flight through L1 (streaming loads), so
 // they want the largest L1 split; the tiny combine kernel follows the GEMV's split instead.
 int32_t attn_configure() {
-  const char* e = getenv("LMB200_CARVEOUT");
-  if (e && atoi(e) == 0) return LMB200_OK;
   LMB_CUDA(cudaFuncSetAttribute(attn_combine_kernel<float>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                 cudaSharedmemCarveoutMaxShared));
   LMB_CUDA(cudaFuncSetAttribute(attn_combine_kernel<__nv_bfloat16>, cudaFuncAttributePreferredSharedMemoryCarveout,

@@ -410,8 +410,6 @@ __global__ void advance_kernel(int* pos, int* step_ctr, unsigned long long* peer
 
 
 int32_t step_kernels_configure() {
-  const char* e = getenv("LMB200_CARVEOUT");
-  if (e && atoi(e) == 0) return LMB200_OK;
 #define LMB_CARVE(KERN) \
   LMB_CUDA(cudaFuncSetAttribute(KERN, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared))
   LMB_CARVE(add_layernorm_kernel<float>);
