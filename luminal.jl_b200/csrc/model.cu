@@ -1248,7 +1248,7 @@ extern "C" int32_t lmb200_session_destroy(lmb200_session h) {
   cudaFree(S->kv); cudaFree(S->x); cudaFree(S->delta); cudaFree(S->logits); cudaFree(S->xn); cudaFree(S->qbuf);
   cudaFree(S->attn_out); cudaFree(S->act); cudaFree(S->tokens); cudaFree(S->pos); cudaFree(S->step_ctr);
   cudaFree(S->tok_hist); cudaFree(S->prompt); cudaFree(S->gemv_partials); cudaFree(S->gemv_counters);
-  cudaFree(S->part_o); cudaFree(S->part_ml); cudaFree(S->attn_counters); cudaFree(S->capture);
+  cudaFree(S->part_o); cudaFree(S->part_ml); cudaFree(S->attn_counters); cudaFree(S->prefill_buf); cudaFree(S->capture);
   S->magic = 0;
   delete S;
   return LMB200_OK;

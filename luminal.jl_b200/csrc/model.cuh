@@ -99,6 +99,8 @@ struct Session {
   float* part_o = nullptr;
   float* part_ml = nullptr;
   unsigned* attn_counters = nullptr;   // [B*KVl], zero between launches
+  void* prefill_buf = nullptr;         // scratch of the GEMM prompt phase, kept between prompts
+  int64_t prefill_bytes = 0;
   int keys_per_cta = 0, nsplit = 0;
   GemvPlan p_qkv, p_o, p_gu, p_down, p_head, p_qc;
   // Whisper: cross-attention cache [L][B][H][cross_cap/16][32*D] and its split plan

@@ -140,21 +140,25 @@ __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, float (&v)[32
   if (hs < p.Hl + p.KVl) {
     const int d0 = 8 * jj + g;                         // rows g / g+8 are the pair (d0, d0 + D/2), src/NN.jl:253-303
     const int d = hi ? d0 + half : d0;
+    // all table reads of the chunk first: between stores the compiler could not move them
+    float2 sc[32];
+    int sq = t0 % p.n_seq;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      sc[i] = (t0 + i < p.T) ? __ldg(p.rope + (int64_t)sq * half + d0) : make_float2(0.f, 1.f);
+      if (++sq == p.n_seq) sq = 0;
+    }
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
       const int t = t0 + i;
       if (t < p.T) {
-        const int b = t / p.n_seq, sq = t - b * p.n_seq, pos = p.pos0 + sq;
-        const float2 sc = p.rope[(int64_t)sq * half + d0];
-        const float sn = sc.x, cs = sc.y;
+        const float sn = sc[i].x, cs = sc[i].y;
         const float o = hi ? (w[i] * sn + v[i] * cs) : (v[i] * cs + (w[i] * sn) * -1.0f);
         const __nv_bfloat16 ob = __float2bfloat16_rn(o);
         if (hs < p.Hl) {
           p.q[(int64_t)t * p.ldq + hs * D + d] = ob;
         } else {
-          const int kvh = hs - p.Hl;
-          p.kbuf[(int64_t)t * p.ldkv + kvh * D + d] = ob;
-          p.kv_layer[b * p.kv_batch_stride + kvh * p.kv_head_stride + kcache_offset(pos, d, D)] = ob;
+          p.kbuf[(int64_t)t * p.ldkv + (hs - p.Hl) * D + d] = ob;
         }
       }
     }
@@ -164,10 +168,7 @@ __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, float (&v)[32
     for (int i = 0; i < 32; ++i) {
       const int t = t0 + i;
       if (t < p.T) {
-        const int b = t / p.n_seq, pos = p.pos0 + (t - b * p.n_seq);
-        const __nv_bfloat16 ob = __float2bfloat16_rn(v[i]);
-        p.vbuf[(int64_t)t * p.ldkv + kvh * D + d] = ob;
-        p.kv_layer[b * p.kv_batch_stride + kvh * p.kv_head_stride + vcache_offset(pos, d, D)] = ob;
+        p.vbuf[(int64_t)t * p.ldkv + kvh * D + d] = __float2bfloat16_rn(v[i]);
       }
     }
   }
@@ -342,6 +343,25 @@ int32_t gemm_launch(Ctx* ctx, const GemmParams& p, cudaStream_t st) {
   return LMB200_OK;
 }
 
+// K and V of the prompt, token-major [B * n_seq, KVl * D], into the decode cache of one layer: one CTA
+// per (sequence, kv head, 16-key block) reads 16 rows of D elements and writes the block's 32 * D
+// contiguous elements (K units then V units, the layout of kcache_offset / vcache_offset).
+__global__ void __launch_bounds__(256) cache_fill_kernel(__nv_bfloat16* __restrict__ kv_layer, int64_t batch_stride, int64_t head_stride,
+                                                         const __nv_bfloat16* __restrict__ kbuf, const __nv_bfloat16* __restrict__ vbuf,
+                                                         int ldkv, int n_seq, int pos0, int KVl, int D) {
+  const int blk = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  __nv_bfloat16* base = kv_layer + b * batch_stride + kvh * head_stride;
+  for (int i = threadIdx.x; i < 16 * D; i += 256) {
+    const int key = i / D, d = i - key * D;
+    const int sq = blk * 16 + key - (pos0 & 15);                 // position pos0 + sq sits in block (pos0 >> 4) + blk
+    if (sq < 0 || sq >= n_seq) continue;
+    const int pos = pos0 + sq;
+    const int64_t src = ((int64_t)b * n_seq + sq) * ldkv + kvh * D + d;
+    base[kcache_offset(pos, d, D)] = kbuf[src];
+    base[vcache_offset(pos, d, D)] = vbuf[src];
+  }
+}
+
 // (sin, cos) of every prompt position, with the decode step's expressions (src/NN.jl:253-303)
 __global__ void rope_table_kernel(float2* __restrict__ tab, const float* __restrict__ inv_freq, int pos0, int n_seq, int half) {
   const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
@@ -483,19 +503,31 @@ int32_t prefill_gemm(Session* S, const int* tokens_dev, int n, cudaStream_t st) 
   const int B = S->B, hid = c.hidden, L = c.n_layers, D = M->D;
   const int T = B * n;
   const int qw = M->Hl * D, kvw = M->KVl * D;
-  Scratch sc;
-  float *x, *delta;
-  __nv_bfloat16 *xn, *q, *kb, *vb, *attn, *act;
-  LMB_TRY(sc.get(&x, (int64_t)T * hid));
-  LMB_TRY(sc.get(&delta, (int64_t)T * hid));
-  LMB_TRY(sc.get(&xn, (int64_t)T * hid));
-  LMB_TRY(sc.get(&q, (int64_t)T * qw));
-  LMB_TRY(sc.get(&kb, (int64_t)T * kvw));
-  LMB_TRY(sc.get(&vb, (int64_t)T * kvw));
-  LMB_TRY(sc.get(&attn, (int64_t)T * qw));
-  LMB_TRY(sc.get(&act, (int64_t)T * M->inter_l));
-  float2* rope;
-  LMB_TRY(sc.get(&rope, (int64_t)n * (D / 2)));
+  // one scratch block per session, kept for the next prompt of the same or a smaller size
+  const int64_t sizes[9] = {(int64_t)T * hid * 4, (int64_t)T * hid * 4, (int64_t)T * hid * 2, (int64_t)T * qw * 2, (int64_t)T * kvw * 2,
+                            (int64_t)T * kvw * 2, (int64_t)T * qw * 2, (int64_t)T * M->inter_l * 2, (int64_t)n * (D / 2) * 8};
+  int64_t offs[9], total = 0;
+  for (int i = 0; i < 9; ++i) { offs[i] = total; total += round_up(sizes[i], 256); }
+  if (total > S->prefill_bytes) {
+    cudaFree(S->prefill_buf);
+    S->prefill_buf = nullptr;
+    S->prefill_bytes = 0;
+    if (cudaMalloc(&S->prefill_buf, (size_t)total) != cudaSuccess) {
+      cudaGetLastError();
+      return fail(LMB200_ENOMEM, "prefill: scratch allocation of %lld bytes failed", (long long)total);
+    }
+    S->prefill_bytes = total;
+  }
+  char* base = reinterpret_cast<char*>(S->prefill_buf);
+  float* x = reinterpret_cast<float*>(base + offs[0]);
+  float* delta = reinterpret_cast<float*>(base + offs[1]);
+  __nv_bfloat16* xn = reinterpret_cast<__nv_bfloat16*>(base + offs[2]);
+  __nv_bfloat16* q = reinterpret_cast<__nv_bfloat16*>(base + offs[3]);
+  __nv_bfloat16* kb = reinterpret_cast<__nv_bfloat16*>(base + offs[4]);
+  __nv_bfloat16* vb = reinterpret_cast<__nv_bfloat16*>(base + offs[5]);
+  __nv_bfloat16* attn = reinterpret_cast<__nv_bfloat16*>(base + offs[6]);
+  __nv_bfloat16* act = reinterpret_cast<__nv_bfloat16*>(base + offs[7]);
+  float2* rope = reinterpret_cast<float2*>(base + offs[8]);
   rope_table_kernel<<<(unsigned)ceil_div((int64_t)n * (D / 2), 256), 256, 0, st>>>(rope, M->inv_freq, 0, n, D / 2);
   ctx->launches++;
   embed_rows_kernel<<<T, 256, 0, st>>>(x, tokens_dev, reinterpret_cast<const __nv_bfloat16*>(M->embed), c.vocab, hid);
@@ -522,6 +554,9 @@ int32_t prefill_gemm(Session* S, const int* tokens_dev, int n, cudaStream_t st) 
       p.kv_batch_stride = S->kv_batch_stride; p.kv_head_stride = S->kv_head_stride;
       p.rope = rope; p.pos0 = 0; p.n_seq = n; p.Hl = M->Hl; p.KVl = M->KVl; p.D = D;
       LMB_TRY(gemm_launch(ctx, p, st));
+      cache_fill_kernel<<<dim3((unsigned)ceil_div(n, 16), (unsigned)M->KVl, (unsigned)B), 256, 0, st>>>(
+          p.kv_layer, p.kv_batch_stride, p.kv_head_stride, kb, vb, kvw, n, 0, M->KVl, D);
+      ctx->launches++;
     }
     LMB_TRY(flash_tc_launch_view(ctx, attn, q, kb, vb, fv, B, n, D, 1.0f / sqrtf((float)D), 1, st));
     {
@@ -550,7 +585,7 @@ int32_t prefill_gemm(Session* S, const int* tokens_dev, int n, cudaStream_t st) 
   last_rows_kernel<<<B, 256, 0, st>>>(S->x, x, delta, n, hid);
   ctx->launches++;
   LMB_CUDA(cudaGetLastError());
-  LMB_CUDA(cudaStreamSynchronize(st));           // the scratch is freed on return
+  LMB_CUDA(cudaStreamSynchronize(st));
   return LMB200_OK;
 }
 
