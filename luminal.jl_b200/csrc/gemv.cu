@@ -1131,6 +1131,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_cl_kernel(const GemvParams
   const int ks0 = (int)((long long)c * KS / C), ks1 = (int)((long long)(c + 1) * KS / C);
   const int n_steps = ks1 - ks0;
   if (tid == 0) {
+    LMB_TRACE(0); LMB_TRACE_NS(10);
 #pragma unroll
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&full_bar[s], 1);
@@ -1151,6 +1152,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_cl_kernel(const GemvParams
   const uint32_t tmem_base = tmem_base_slot;
   bool dead = false;
   pdl_launch_dependents();
+  if (tid == 0) LMB_TRACE(1);
 
   if (warp == 0) {
     // ---------------- producer: weights before the dependency wait, activations after ----------------
@@ -1186,10 +1188,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_cl_kernel(const GemvParams
   } else if (warp == 1) {
     // ---------------- MMA issue ----------------
     pdl_wait();
+    if (lane == 0) LMB_TRACE(2);
     for (int i = 0; i < n_steps; ++i) {
       const int s = i % kStages, k = i / kStages;
       mbar_wait(&full_bar[s], k & 1, dead, err);
       tc_fence_after();
+      if (lane == 0 && i == 0) LMB_TRACE(3);
       if (lane == 0) {
         const uint32_t sa = smem_u32(smem + s * kStage);
         const uint64_t adesc = smem_desc(sa, 2048, 128);
@@ -1203,6 +1207,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_cl_kernel(const GemvParams
       }
       __syncwarp();
     }
+    if (lane == 0) LMB_TRACE(4);
   } else {
     // ---------------- epilogue warps: send every row to the CTA that finalises it ----------------
     pdl_wait();
@@ -1213,6 +1218,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_cl_kernel(const GemvParams
       tc_fence_after();
       tmem_load_row<N>(v, tmem_base + ((uint32_t)(32 * q) << 16));
       tc_fence_before();
+      if (tid == 64) LMB_TRACE(5);
     } else {
 #pragma unroll
       for (int i = 0; i < N; ++i) v[i] = 0.f;
@@ -1224,9 +1230,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_cl_kernel(const GemvParams
     const uint32_t dst = dsmem_addr(recv_local, (uint32_t)owner);
 #pragma unroll
     for (int i = 0; i < N / 4; ++i) dsmem_store4(dst + 16u * i, v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    if (tid == 64) LMB_TRACE(6);
   }
   // every partial row is in its owner's shared memory once all CTAs of the cluster are here
   cluster_sync_all();
+  if (tid == 64) LMB_TRACE(7);
   if (warp >= 2) {
     const int e = tid - 64;
     const int rows_per = 128 / C;
@@ -1243,12 +1251,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_cl_kernel(const GemvParams
       }
     }
   }
+  if (tid == 64) LMB_TRACE(8);
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
   }
+  if (tid == 0) { LMB_TRACE(9); LMB_TRACE_NS(11); }
 }
 
 template <int Bp>
