@@ -128,6 +128,8 @@ int32_t peer_setup(Ctx* c) {
   const char* sel = getenv("LMB200_TP_ALLREDUCE");          // "nccl": keep ncclAllReduce (A/B runs)
   if ((sel && strcmp(sel, "nccl") == 0) || c->tp_size < 2 || c->tp_size > 8 || !g_nccl.AllGather) return LMB200_OK;
   const int n = c->tp_size;
+  const char* wms = getenv("LMB200_PEER_WAIT_MS");          // how long a kernel waits for a peer's signal
+  c->peer_wait_cycles = wms && atoll(wms) > 0 ? atoll(wms) * 1900000ll : kPeerWaitCycles;
   void *region = nullptr, *dsend = nullptr, *drecv = nullptr;
   PeerHello mine, all[8];
   memset(&mine, 0, sizeof(mine));

@@ -60,6 +60,7 @@ struct Ctx {
   void* peer_base[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
   unsigned long long* peer_step = nullptr;   // device counter: decode steps enqueued on this communicator
   float* peer_scratch = nullptr;             // 1 float for the teardown barrier
+  long long peer_wait_cycles = 0;            // SM cycles a kernel waits for a peer's signal (LMB200_PEER_WAIT_MS, default 10 s)
 };
 
 constexpr int64_t kPeerBufFloats = 1 << 20;
@@ -79,6 +80,7 @@ struct PeerReduce {
   const unsigned long long* step;          // steps completed so far
   unsigned phase = 0;                      // 1 + index of the reduction inside the step
   int* dev_err = nullptr;
+  long long wait_cycles = kPeerWaitCycles;
 };
 
 #ifdef __CUDACC__
@@ -103,7 +105,7 @@ __device__ __forceinline__ void peer_exchange_wait(const PeerReduce& pr) {
       if ((++spins & 1023u) == 0u) {
         volatile int* err = pr.dev_err;
         if (*err != 0) break;
-        if (clock64() - t0 > kPeerWaitCycles) { *err = 1; break; }
+        if (clock64() - t0 > pr.wait_cycles) { *err = 1; break; }
       }
     }
   }

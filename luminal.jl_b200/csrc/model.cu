@@ -905,6 +905,7 @@ RowParallelOut row_parallel_out(Session* S, int index) {
   r.pr.step = ctx->peer_step;
   r.pr.phase = (unsigned)index + 1;
   r.pr.dev_err = ctx->dev_err;
+  r.pr.wait_cycles = ctx->peer_wait_cycles > 0 ? ctx->peer_wait_cycles : kPeerWaitCycles;
   return r;
 }
 

@@ -86,3 +86,72 @@ def test_tp2_decode_matches_oracle(lib_built, name, dtype, tol):
         assert same_ref and err <= tol
     else:
         assert err / scale <= tol
+
+
+def _missing_peer_main(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    os.environ["LMB200_PEER_WAIT_MS"] = "300"
+    import time
+    import torch
+    import torch.distributed as dist
+    import luminal_jl_b200 as L
+    import luminal_oracle as O
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    cfg = O.CONFIGS["tiny_gqa128"]
+    w = O.synth_llama_weights(cfg, seed=31)
+    dev = L.B200Device(rank)
+    uid = [L.B200Device.comm_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(uid, src=0)
+    dev.comm_init(world, rank, uid[0])
+    model = L.Model(dev, n_layers=cfg["n_layers"], hidden=cfg["hidden"], n_heads=cfg["n_heads"],
+                    n_kv_heads=cfg["n_kv_heads"], intermediate=cfg["intermediate"], vocab=cfg["vocab"],
+                    eps=cfg["eps"], rope_base=cfg["rope_base"], dtype="bf16", tp_size=world, tp_rank=rank)
+    model.set_weights(w)
+    sess = L.Session(model, 2, 32)
+    tok = np.array([1, 2], np.int32)
+    sess.decode_step(tok)                        # both ranks: works
+    dist.barrier()
+    if rank == 0:
+        # the peer never joins this step: every wait for its signal runs out (between steps, nothing in
+        # flight on the peer), the call reports it and the context stays usable
+        t0 = time.time()
+        code = 0
+        try:
+            sess.decode_step(tok)
+        except L.LuminalB200Error as e:
+            code = e.code
+        waited = time.time() - t0
+        a = O.bf16_round(O.synth_normal(1, 1, (256, 256), 0.05))
+        x = O.bf16_round(O.synth_normal(1, 2, (4, 256), 1.0))
+        y = L.linear_gemv(dev, a, x, "bf16")
+        ok = bool(np.abs(y - x.astype(np.float64) @ a.astype(np.float64).T).max() <= 1e-3)
+        q.put((code, waited, ok))
+    dist.barrier()
+    sess.close(); model.close(); dev.comm_destroy()
+    dist.destroy_process_group()
+
+
+def test_tp2_missing_peer_times_out(lib_built):
+    """Failure made on the host: one rank skips a step.  The other rank's kernels stop waiting after the
+    (shortened) limit, the call returns LMB200_ETIMEOUT and later calls on the context work."""
+    L = lib_built
+    if L.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 31500 + os.getpid() % 2000
+    procs = [ctx.Process(target=_missing_peer_main, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    code, waited, ok = q.get(timeout=300)
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    assert code == -6                            # LMB200_ETIMEOUT
+    assert waited < 30.0
+    assert ok
