@@ -264,6 +264,75 @@ __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(float* __rest
   }
 }
 
+// Tensor-parallel form of the residual add + RMSNorm: a cluster of kTpSplit CTAs per sequence, each
+// summing one slice of the row over every rank's partial (peer loads issued from four times as
+// many SMs as one CTA per row would use), the slices' sums of squares exchanged through
+// distributed shared memory and added in CTA order, so every rank still gets the same bits.
+constexpr int kTpSplit = 4, kTpThreads = 256;
+template <typename WT>
+__global__ void __launch_bounds__(kTpThreads) add_rmsnorm_tp_kernel(float* __restrict__ x, const float* __restrict__ w,
+                                                                    WT* __restrict__ xn, int Bp, int n, float eps,
+                                                                    float* __restrict__ capture, PeerReduce pr) {
+  extern __shared__ __align__(16) float row[];          // this CTA's slice
+  __shared__ float red[kTpThreads / 32];
+  __shared__ float ss_part[kTpSplit];
+  uint32_t c;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(c));
+  const int b = blockIdx.x / kTpSplit, tid = threadIdx.x;
+  const int q4 = (n >> 2) / kTpSplit, col0 = (int)c * q4;      // float4s per slice, first float4 of this slice
+  const float4* w4 = reinterpret_cast<const float4*>(w);
+  float4 g0 = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (xn && tid < q4) g0 = w4[col0 + tid];                     // the gains never change: before the wait
+  pdl_launch_dependents();
+  pdl_wait();
+  peer_exchange_wait(pr);
+  float4* xr = reinterpret_cast<float4*>(x + (int64_t)b * n);
+  float4* rs = reinterpret_cast<float4*>(row);
+  float4* cr = capture ? reinterpret_cast<float4*>(capture + (int64_t)b * n) : nullptr;
+  float ss = 0.f;
+  for (int i = tid; i < q4; i += kTpThreads) {
+    const int idx = col0 + i;
+    float4 e[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r)
+      if (r < pr.n) e[r] = peer_load4(pr.part[r] + (int64_t)b * n + 4 * idx);
+    float4 v = xr[idx];
+    float4 d = e[0];
+#pragma unroll
+    for (int r = 1; r < 8; ++r)
+      if (r < pr.n) { d.x += e[r].x; d.y += e[r].y; d.z += e[r].z; d.w += e[r].w; }
+    v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+    xr[idx] = v;
+    rs[i] = v;
+    if (cr) cr[idx] = v;
+    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+  if ((tid & 31) == 0) red[tid >> 5] = ss;
+  __syncthreads();
+  float mine = 0.f;
+#pragma unroll
+  for (int i = 0; i < kTpThreads / 32; ++i) mine += red[i];
+  if (tid < kTpSplit) {                                        // this slice's sum into slot c of every CTA of the cluster
+    uint32_t local = (uint32_t)__cvta_generic_to_shared(&ss_part[c]), remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(local), "r"((uint32_t)tid));
+    asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(remote), "f"(mine) : "memory");
+  }
+  asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+  const float tot = ((ss_part[0] + ss_part[1]) + ss_part[2]) + ss_part[3];
+  const float inv = 1.0f / sqrtf(tot * (1.0f / (float)n) + eps);
+  if (xn) {
+    for (int i = tid; i < q4; i += kTpThreads) {
+      const float4 v = rs[i];
+      const float4 g = i == tid ? g0 : w4[col0 + i];
+      WT* o = xn + Layout<WT>::x_offset(b, 4 * (col0 + i), Bp);
+      store4(o, (v.x * inv) * g.x, (v.y * inv) * g.y, (v.z * inv) * g.z, (v.w * inv) * g.w);
+    }
+  }
+}
+
 // Whisper decoder: x <- embedding row + positional row (first layer) or x + delta, then LayerNorm
 // with mean-centering, gain and bias:  xc = x + mean*(-1);  y = (xc * recip(sqrt(mean(xc*xc) + eps))) * w + b
 // (src/NN.jl:138-173, src/HighLevelOps.jl:292-304; positions src/Whisper.jl:699-701).
@@ -920,16 +989,36 @@ int32_t enqueue_step_t(Session* S, cudaStream_t st, bool with_head) {
   const size_t norm_smem = (size_t)hid * sizeof(float);
   RowParallelOut prev;             // the down_proj of the previous layer
   prev.out = S->delta; prev.nccl = false;
+  // residual add + RMSNorm; with the ranks' partials in peer regions the clustered kernel does the all-reduce
+  auto launch_norm = [&](const float* delta, const int* tokens, const float* w, WT* xn, float* capture, const PeerReduce& pr) -> int32_t {
+    if (pr.n > 1 && !tokens && hid % (16 * kTpSplit) == 0) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3((unsigned)(B * kTpSplit));
+      cfg.blockDim = dim3(kTpThreads);
+      cfg.dynamicSmemBytes = norm_smem / kTpSplit;
+      cfg.stream = st;
+      cudaLaunchAttribute attr[2];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = kTpSplit; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+      attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[1].val.programmaticStreamSerializationAllowed = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = pdl_enabled() ? 2 : 1;
+      LMB_CUDA(cudaLaunchKernelEx(&cfg, add_rmsnorm_tp_kernel<WT>, S->x, w, xn, S->Bp, hid, c.rms_eps, capture, pr));
+    } else {
+      LMB_CUDA(launch_k(add_rmsnorm_kernel<WT>, dim3(B), dim3(kNormThreads), norm_smem, st, S->x, delta, tokens,
+                        reinterpret_cast<const WT*>(M->embed), c.vocab, w, xn, S->Bp, hid, c.rms_eps, capture, pr));
+    }
+    ctx->launches++;
+    return LMB200_OK;
+  };
   for (int l = 0; l < L; ++l) {
     LayerWeights& W = M->layers[l];
     // residual add of the previous MLP (or the embedding gather) + attention RMSNorm
-    LMB_CUDA(launch_k(add_rmsnorm_kernel<WT>, dim3(B), dim3(kNormThreads), norm_smem, st, S->x,
-                      l == 0 ? (const float*)nullptr : (const float*)prev.out, l == 0 ? (const int*)S->tokens : (const int*)nullptr,
-                      reinterpret_cast<const WT*>(M->embed), c.vocab, (const float*)W.attn_norm,
-                      reinterpret_cast<WT*>(S->xn), S->Bp, hid, c.rms_eps,
-                      (S->capture_on && l > 0) ? S->capture + (int64_t)(l - 1) * B * hid : (float*)nullptr,
-                      l == 0 ? PeerReduce() : prev.pr));
-    ctx->launches++;
+    LMB_TRY(launch_norm(l == 0 ? (const float*)nullptr : (const float*)prev.out, l == 0 ? (const int*)S->tokens : (const int*)nullptr,
+                        (const float*)W.attn_norm, reinterpret_cast<WT*>(S->xn),
+                        (S->capture_on && l > 0) ? S->capture + (int64_t)(l - 1) * B * hid : (float*)nullptr,
+                        l == 0 ? PeerReduce() : prev.pr));
     void* kv_layer = reinterpret_cast<char*>(S->kv) + (int64_t)l * S->kv_layer_stride * M->esz;
     {  // q/k/v projections + RoPE + KV append
       GemvParams p = gemv_params(S, W.wqkv, M->m_qkv, S->p_qkv, S->xn);
@@ -957,10 +1046,8 @@ int32_t enqueue_step_t(Session* S, cudaStream_t st, bool with_head) {
       LMB_TRY(gemv_launch(ctx, dt, p, st));
       if (ro.nccl) LMB_TRY(nccl_allreduce_f32(ctx, ro.out, (int64_t)B * hid, st));
     }
-    LMB_CUDA(launch_k(add_rmsnorm_kernel<WT>, dim3(B), dim3(kNormThreads), norm_smem, st, S->x, (const float*)ro.out,
-                      (const int*)nullptr, (const WT*)nullptr, 0, (const float*)W.ffn_norm,
-                      reinterpret_cast<WT*>(S->xn), S->Bp, hid, c.rms_eps, (float*)nullptr, ro.pr));
-    ctx->launches++;
+    LMB_TRY(launch_norm((const float*)ro.out, (const int*)nullptr, (const float*)W.ffn_norm, reinterpret_cast<WT*>(S->xn),
+                        (float*)nullptr, ro.pr));
     {  // gate/up + SiLU gate
       GemvParams p = gemv_params(S, W.wgu, M->m_gu, S->p_gu, S->xn);
       p.epi = EPI_SILU_GATE; p.act = S->act; p.n_act = M->inter_l;
@@ -975,11 +1062,9 @@ int32_t enqueue_step_t(Session* S, cudaStream_t st, bool with_head) {
     }
   }
   // last residual add (+ final norm); without the head only the add is needed for the capture
-  LMB_CUDA(launch_k(add_rmsnorm_kernel<WT>, dim3(B), dim3(kNormThreads), norm_smem, st, S->x, (const float*)prev.out,
-                    (const int*)nullptr, (const WT*)nullptr, 0, (const float*)M->final_norm,
-                    with_head ? reinterpret_cast<WT*>(S->xn) : (WT*)nullptr, S->Bp, hid, c.rms_eps,
-                    S->capture_on ? S->capture + (int64_t)(L - 1) * B * hid : (float*)nullptr, prev.pr));
-  ctx->launches++;
+  LMB_TRY(launch_norm((const float*)prev.out, (const int*)nullptr, (const float*)M->final_norm,
+                      with_head ? reinterpret_cast<WT*>(S->xn) : (WT*)nullptr,
+                      S->capture_on ? S->capture + (int64_t)(L - 1) * B * hid : (float*)nullptr, prev.pr));
   if (with_head) {
     GemvParams p = gemv_params(S, M->lm_head, M->m_head, S->p_head, S->xn);
     p.epi = EPI_STORE_F32; p.out = S->logits; p.out_pitch = S->logits_pitch;
