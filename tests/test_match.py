@@ -1,0 +1,134 @@
+"""The node-list text form and the structural matcher: a graph built by the nn mirror of src/NN.jl is
+exported, read back with no model object or weight names, and recognised; graphs that deviate are refused.
+The GPU case runs the recognised graph through the fused session and op by op, and compares."""
+import json
+
+import numpy as np
+import pytest
+
+import luminal_jl_b200 as L
+from luminal_jl_b200 import graph as G, match as M, nn
+
+
+def build(cls=nn.Llama, seq=4, batch=2, kv=2, layers=3, prev_seq=0, hidden=32, heads=4, inter=48, vocab=64, base=None):
+    g, reg = G.Graph(), {}
+    model = cls(g, reg, vocab_size=vocab, hidden=hidden, n_layers=layers, n_heads=heads, n_kv_heads=kv, intermediate=inter)
+    if base is not None:
+        model.ROPE_BASE = base
+    tok = G.tensor(g, [batch, seq])
+    out = model(tok, prev_seq)
+    return g, reg, tok, out
+
+
+@pytest.mark.parametrize("cls,seq,kv,base", [(nn.Llama, 5, 2, 500000.0), (nn.Phi3, 1, 4, 10000.0), (nn.Llama, 3, 1, 500000.0),
+                                             (nn.Llama, 2, 4, 1000000.0)])
+def test_roundtrip_and_match(cls, seq, kv, base):
+    g, reg, tok, out = build(cls, seq=seq, kv=kv, base=base)
+    text = json.dumps(M.export_graph(g))
+    g2 = M.import_graph(text)
+    assert g2.nodes == g.nodes and g2.shapes == g.shapes
+    m = M.match_decoder(g2, out.id)
+    assert (m.n_layers, m.hidden, m.n_heads, m.n_kv_heads, m.head_dim, m.intermediate, m.vocab) == (3, 32, 4, kv, 8, 48, 64)
+    assert (m.batch, m.seq, m.prev_seq, m.tokens) == (2, seq, 0, tok.id)
+    assert m.rope_base == base and np.float32(m.eps) == np.float32(1e-5)
+    assert m.weights == {name: t.id for name, t in reg.items()}
+
+
+def test_prev_seq_is_recovered_and_refused_by_compile():
+    g, _, _, out = build(seq=2, prev_seq=7)
+    assert M.match_decoder(g, out.id).prev_seq == 7
+    with pytest.raises(M.MatchError, match="prev_seq"):
+        M.compile_b200(g, out.id, {})
+
+
+def test_import_rejects_malformed_lists():
+    g, _, _, _ = build(layers=1)
+    doc = M.export_graph(g)
+    bad = json.loads(json.dumps(doc))
+    bad["nodes"][5]["op"] = "Tanh"
+    with pytest.raises(ValueError, match="unknown op"):
+        M.import_graph(bad)
+    bad = json.loads(json.dumps(doc))
+    k = next(i for i, n in enumerate(bad["nodes"]) if n["inputs"])
+    bad["nodes"][k]["inputs"][0][0] = len(bad["nodes"]) + 3
+    with pytest.raises(ValueError, match="earlier node"):
+        M.import_graph(bad)
+    with pytest.raises(ValueError, match="node list"):
+        M.import_graph({"nodes": []})
+
+
+def _mutate(g, pick, new_op):
+    """Replaces the op of the first node (searching from the end) for which pick(op) is true."""
+    for i in range(len(g.nodes) - 1, -1, -1):
+        if pick(g.nodes[i].op):
+            g.nodes[i] = G.Node(new_op(g.nodes[i].op), g.nodes[i].inputs)
+            return i + 1
+    raise AssertionError("nothing to mutate")
+
+
+@pytest.mark.parametrize("pick,new_op", [
+    (lambda o: isinstance(o, G.Exp2), lambda o: G.Log2()),                                       # another activation / softmax
+    (lambda o: isinstance(o, G.Constant) and o.value == -1e9, lambda o: G.Constant(-1e4)),       # another mask value
+    (lambda o: isinstance(o, G.Sin), lambda o: G.Cos()),                                         # another rotation
+    (lambda o: isinstance(o, G.SumReduce) and o.dim == 3, lambda o: G.MaxReduce(3)),             # not an RMS
+    (lambda o: isinstance(o, G.Permute) and o.dims == (2, 1), lambda o: G.Permute((1, 2))),      # weight not transposed
+    (lambda o: isinstance(o, G.Constant) and abs(o.value - 8 ** -0.5) < 1e-6, lambda o: G.Constant(0.5)),   # another score scale
+    (lambda o: isinstance(o, G.Slice), lambda o: G.Slice(o.ranges[:-1] + ((0, 2),))),            # another pair split
+])
+def test_deviating_graphs_are_refused(pick, new_op):
+    g, _, _, out = build(seq=3)
+    _mutate(g, pick, new_op)
+    with pytest.raises(M.MatchError, match="node "):
+        M.match_decoder(g, out.id)
+
+
+def test_other_structures_are_refused():
+    # a bias on the head; a mean-centring LayerNorm instead of the final RMSNorm
+    g = G.Graph()
+    x = G.tensor(g, [2, 16])
+    with pytest.raises(M.MatchError):
+        M.match_decoder(g, nn.Linear(16, 8, g, bias=True)(x).id)
+    g = G.Graph()
+    x = G.tensor(g, [2, 3, 16])
+    head = nn.Linear(16, 8, g, bias=False)
+    with pytest.raises(M.MatchError, match="Linear's MatMul"):      # the centred tensor is a sum, but not a block's
+        M.match_decoder(g, head(nn.LayerNorm(16, g, bias=False)(x)).id)
+    with pytest.raises(M.MatchError, match="no node"):
+        M.match_decoder(g, 10 ** 6)
+
+
+def test_layers_must_agree():
+    g, reg = G.Graph(), {}
+    a = nn.Llama(g, reg, vocab_size=64, hidden=32, n_layers=1, n_heads=4, n_kv_heads=2, intermediate=48)
+    odd = nn.TransformerBlock(32, 4, 4, 48, g, reg, "model.layers.1")        # other kv head count
+    tok = G.tensor(g, [1, 2])
+    x = a.embedding(tok)
+    x = odd(a.layers[0](x, 0, rope_base=500000.0), 0, rope_base=500000.0)
+    with pytest.raises(M.MatchError, match="block 1 differs"):
+        M.match_decoder(g, a.head(a.norm(x)).id)
+
+
+@pytest.mark.gpu
+def test_compile_b200_from_a_node_list(lib_built, device):
+    """Node list as text -> import -> match -> fused session; against execute() of the same graph."""
+    import luminal_oracle as O
+    cfg = O.CONFIGS["tiny_gqa128"]
+    w = O.synth_llama_weights(cfg, seed=21)
+    batch, seq = 2, 5
+    toks = O.synth_tokens(21, 1000, (batch, seq), cfg["vocab"])
+    g, reg = G.Graph(), {}
+    model = nn.Llama(g, reg, vocab_size=cfg["vocab"], hidden=cfg["hidden"], n_layers=cfg["n_layers"], n_heads=cfg["n_heads"],
+                     n_kv_heads=cfg["n_kv_heads"], intermediate=cfg["intermediate"])
+    model.ROPE_BASE = cfg["rope_base"]
+    inp = G.tensor(g, [batch, seq])
+    out = model(inp, 0)
+    by_id = {t.id: w[n] for n, t in reg.items()}
+    g2 = M.import_graph(json.dumps(M.export_graph(g)))
+    sess, m = M.compile_b200(g2, out.id, by_id, device, max_ctx=16)
+    assert m.rope_base == cfg["rope_base"] and m.n_layers == cfg["n_layers"]
+    logits = sess.prefill(toks.astype(np.int32))
+    full = L.execute(g, out.id, {**by_id, inp.id: toks.astype(np.float32)}, device)[:, -1, :]
+    ref = O.llama_forward(toks, w, cfg)[:, -1, :]
+    assert np.abs(full - logits).max() <= 1e-3 and np.abs(ref - logits).max() <= 1e-3
+    assert np.array_equal(full.argmax(-1), logits.argmax(-1))
+    sess.close()
