@@ -393,6 +393,20 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
       : "memory");
 }
 
+// The producer warp's last act: one 32 KB L2 prefetch per lane and round over this CTA's share of the
+// next GEMV's weight heads (see GemvParams::pf_base).
+__device__ __forceinline__ void prefetch_next_weights(const GemvParams& p, int lane) {
+  if (!p.pf_base) return;
+  const long long total = (long long)p.pf_parts * p.pf_chunk;
+  const int n0 = (int)((long long)blockIdx.x * total / gridDim.x), n1 = (int)((long long)(blockIdx.x + 1) * total / gridDim.x);
+  for (int n = n0 + lane; n < n1; n += 32) {
+    const int part = n / p.pf_chunk, within = n - part * p.pf_chunk;
+    const long long unit = (long long)part * p.pf_units / p.pf_parts + within;
+    const char* a = reinterpret_cast<const char*>(p.pf_base) + unit * 32768;
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(a), "r"(32768u) : "memory");
+  }
+}
+
 struct UnitRange {
   int KS, nrbg, u0, u1;
   long long U, G;
@@ -460,6 +474,7 @@ __device__ __forceinline__ void produce(const GemvParams& p, const UnitRange& ur
     }
     __syncwarp();
   }
+  prefetch_next_weights(p, lane);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1185,6 +1200,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_cl_kernel(const GemvParams
       }
       __syncwarp();
     }
+    prefetch_next_weights(p, lane);
   } else if (warp == 1) {
     // ---------------- MMA issue ----------------
     pdl_wait();
@@ -1352,6 +1368,21 @@ constexpr size_t kMaxXsBytes = 96 * 1024;
 
 void gemv_set_variant(int variant) { g_variant = variant == GEMV_MMA_SYNC ? GEMV_MMA_SYNC : GEMV_TCGEN05; }
 int gemv_variant() { return g_variant; }
+
+void gemv_prefetch_next(GemvParams& p, const Ctx* ctx, int dtype, const void* next_W, int next_rows, int next_K,
+                        const GemvPlan& next_plan) {
+  (void)ctx;
+  static const int budget_mb = [] { const char* e = getenv("LMB200_L2_PREFETCH_MB"); return e ? atoi(e) : 24; }();
+  if (dtype != LMB200_BF16 || g_variant != GEMV_TCGEN05 || budget_mb <= 0 || !next_W) return;
+  const int KS = (int)ceil_div(next_K, 128), nrbg = (int)ceil_div(next_rows, 128);
+  const int64_t U = (int64_t)nrbg * KS;
+  const int parts = next_plan.cluster > 1 ? nrbg * next_plan.cluster : next_plan.grid;
+  if (parts <= 0 || U / parts < 1) return;
+  int64_t chunk = ((int64_t)budget_mb * 1000000 / 32768) / parts;
+  if (chunk < 1) chunk = 1;
+  if (chunk > U / parts) chunk = U / parts;
+  p.pf_base = next_W; p.pf_units = (int)U; p.pf_parts = parts; p.pf_chunk = (int)chunk;
+}
 
 GemvPlan gemv_plan(const Ctx* ctx, int dtype, int B, int rows, int K) {
   GemvPlan pl;

@@ -54,7 +54,14 @@ struct GemvParams {
   float qk_scale = 1.f;              // multiplies q and k rows (Whisper: head_dim^-0.25, src/Whisper.jl:257)
   // every epilogue: added to the accumulator first, one value per internal row (NULL: none)
   const float* bias = nullptr;
+  // L2 prefetch for the GEMV that runs next (bf16 tensor-core kernels): once a CTA's producer has issued
+  // its last copy, HBM would idle through this kernel's fold, epilogue and drain; instead it pulls the
+  // head of every next-kernel CTA's weight range into L2.  The next matrix has pf_units 32 KB units;
+  // CTA i of its pf_parts CTAs starts at unit i * pf_units / pf_parts; pf_chunk units are fetched per part.
+  const void* pf_base = nullptr;
+  int pf_units = 0, pf_parts = 0, pf_chunk = 0;
 };
+
 
 struct GemvPlan {
   int ksplit = 1, kc_per_split = 0, grid = 0, cluster = 0;
@@ -66,6 +73,9 @@ int32_t gemv_configure();
 void gemv_set_variant(int variant);
 int gemv_variant();
 GemvPlan gemv_plan(const Ctx* ctx, int dtype, int B, int rows, int K);
+// Fills the prefetch fields of `p` from the matrix (and plan) of the GEMV that follows it.
+void gemv_prefetch_next(GemvParams& p, const Ctx* ctx, int dtype, const void* next_W, int next_rows, int next_K,
+                        const GemvPlan& next_plan);
 // dtype: LMB200_F32 or LMB200_BF16
 int32_t gemv_launch(Ctx* ctx, int dtype, GemvParams p, cudaStream_t stream);
 

@@ -1043,6 +1043,7 @@ int32_t enqueue_step_t(Session* S, cudaStream_t st, bool with_head) {
     {  // o_proj (row-parallel under TP)
       GemvParams p = gemv_params(S, W.wo, M->m_o, S->p_o, S->attn_out);
       p.epi = EPI_STORE_F32; p.out = ro.out; p.out_pitch = hid;
+      gemv_prefetch_next(p, ctx, dt, W.wgu, M->m_gu.rows, M->m_gu.K, S->p_gu);
       LMB_TRY(gemv_launch(ctx, dt, p, st));
       if (ro.nccl) LMB_TRY(nccl_allreduce_f32(ctx, ro.out, (int64_t)B * hid, st));
     }
@@ -1051,12 +1052,15 @@ int32_t enqueue_step_t(Session* S, cudaStream_t st, bool with_head) {
     {  // gate/up + SiLU gate
       GemvParams p = gemv_params(S, W.wgu, M->m_gu, S->p_gu, S->xn);
       p.epi = EPI_SILU_GATE; p.act = S->act; p.n_act = M->inter_l;
+      gemv_prefetch_next(p, ctx, dt, W.wdown, M->m_down.rows, M->m_down.K, S->p_down);
       LMB_TRY(gemv_launch(ctx, dt, p, st));
     }
     prev = row_parallel_out(S, 2 * l + 1);
     {  // down_proj (row-parallel under TP)
       GemvParams p = gemv_params(S, W.wdown, M->m_down, S->p_down, S->act);
       p.epi = EPI_STORE_F32; p.out = prev.out; p.out_pitch = hid;
+      if (l + 1 < L) gemv_prefetch_next(p, ctx, dt, M->layers[l + 1].wqkv, M->m_qkv.rows, M->m_qkv.K, S->p_qkv);
+      else if (with_head) gemv_prefetch_next(p, ctx, dt, M->lm_head, M->m_head.rows, M->m_head.K, S->p_head);
       LMB_TRY(gemv_launch(ctx, dt, p, st));
       if (prev.nccl) LMB_TRY(nccl_allreduce_f32(ctx, prev.out, (int64_t)B * hid, st));
     }
