@@ -68,14 +68,23 @@ def _rank_main(rank, world, port, q, name, dtype, P=6):
 # the 20-token bf16 prompt goes through the GEMM prompt phase (row-parallel outputs reduced with NCCL)
 @pytest.mark.parametrize("name,dtype,tol,P", [("tiny_gqa128", "f32", 1e-3, 6), ("mid_gqa", "bf16", 4e-2, 6), ("mid_gqa", "bf16", 4e-2, 20)])
 def test_tp2_decode_matches_oracle(lib_built, name, dtype, tol, P):
-    L = lib_built
-    if L.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
+    _run_tp(lib_built, 2, name, dtype, tol, P)
+
+
+# four ranks: a cluster of CTAs per sequence in the norm kernel sums four peers' partials
+@pytest.mark.parametrize("name,dtype,tol,P", [("mid_gqa_kv4", "f32", 1e-3, 6), ("mid_gqa_kv4", "bf16", 4e-2, 6)])
+def test_tp4_decode_matches_oracle(lib_built, name, dtype, tol, P):
+    _run_tp(lib_built, 4, name, dtype, tol, P)
+
+
+def _run_tp(L, world, name, dtype, tol, P):
+    if L.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29500 + (os.getpid() + 7 * P) % 2000
-    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, q, name, dtype, P)) for r in range(2)]
+    port = 29500 + (os.getpid() + 7 * P + 13 * world) % 2000
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, q, name, dtype, P)) for r in range(world)]
     for p in procs:
         p.start()
     same_ref, same_loop, err, scale = q.get(timeout=600)
