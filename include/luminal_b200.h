@@ -44,7 +44,9 @@ enum {
   LMB200_ENOMEM = -3,
   LMB200_ENCCL = -4,
   LMB200_ESTATE = -5,    /* call order (e.g. decode past max_ctx) */
-  LMB200_ETIMEOUT = -6   /* a bounded device-side wait gave up */
+  LMB200_ETIMEOUT = -6,  /* a bounded device-side wait gave up */
+  LMB200_ENOTFOUND = -7  /* a tensor name the model does not have (the reference skips tensors that
+                            are not registered, src/Weights.jl:76-91) */
 };
 
 /* element-wise opcodes of lmb200_ew: the reference's primitive and fused ops
@@ -178,7 +180,8 @@ typedef uint64_t lmb200_whisper_encoder;
 int32_t lmb200_whisper_encoder_create(lmb200_ctx ctx, int32_t d_model, int32_t heads, int32_t layers, int32_t ffn,
                                       int32_t n_mels, int32_t dec_layers, lmb200_whisper_encoder* out);
 int32_t lmb200_whisper_encoder_destroy(lmb200_whisper_encoder enc);
-int32_t lmb200_whisper_encoder_set_weight(lmb200_whisper_encoder enc, const char* name, const float* host, int32_t layout);
+int32_t lmb200_whisper_encoder_set_weight(lmb200_whisper_encoder enc, const char* name, const float* host, int32_t rank,
+                                          const int64_t* dims, int32_t layout);
 /* mel [batch, n_mels, frames] float32 row-major on the host; out_host NULL or [batch, (frames - 1) / 2 + 1, d_model].
  * The output also stays on the device for lmb200_whisper_encoder_cross_kv. */
 int32_t lmb200_whisper_encoder_run(lmb200_whisper_encoder enc, const float* mel_host, int32_t batch, int32_t frames,
@@ -239,10 +242,19 @@ int32_t lmb200_shard_map(const lmb200_model_config* cfg, int32_t matrix, int32_t
 int32_t lmb200_model_destroy(lmb200_model model);
 /* Set one weight from the FULL logical float32 tensor under its registry name
  * ("model.layers.3.self_attn.q_proj.weight", "model.embed_tokens.weight", "model.norm.weight",
- * "lm_head.weight" ...: src/NN.jl:180-225, 433-445).  The library keeps only this rank's shard,
- * in its own tiled layout.  Replaces graph.tensors / load_weights! (src/Weights.jl:60-114). */
+ * "lm_head.weight" ...: src/NN.jl:180-225, 433-445).  dims[rank] is the shape of `host` (rank 1 or
+ * 2); it must equal the logical shape the configuration gives that tensor ([out, in] for a
+ * Linear, [n] for gains and biases), else LMB200_EINVAL names both shapes and nothing is read.
+ * A name the model does not have returns LMB200_ENOTFOUND.  The library keeps only this rank's
+ * shard, in its own tiled layout.  Replaces graph.tensors / load_weights! (src/Weights.jl:60-114). */
 int32_t lmb200_model_set_weight(lmb200_model model, const char* name, const float* host,
-                                int32_t layout);
+                                int32_t rank, const int64_t* dims, int32_t layout);
+/* Which of the model's tensors have not been set yet: their count, and their names separated by
+ * '\n' into names_out (as many as fit in `capacity` bytes, NUL-terminated; names_out may be NULL
+ * with capacity 0).  Stands in for the warning load_weights! prints for missing keys
+ * (src/Weights.jl:86-91). */
+int32_t lmb200_model_missing_weights(lmb200_model model, char* names_out, int64_t capacity,
+                                     int32_t* n_missing);
 /* Fill every weight on the device from the counter-based generator (seed, tensor id, logical
  * row-major index) -> Irwin-Hall(12) approximation of N(0,sigma); norm gains get +1. */
 int32_t lmb200_model_init_random(lmb200_model model, uint64_t seed, float sigma);
@@ -311,6 +323,10 @@ int32_t lmb200_session_kv_layer(lmb200_session session, int32_t layer, void** kv
  * built into the library (one per GPU that loads it, kept until exit) instead of session scratch.
  *  - q, out: [batch, n_kv_heads*group, head_dim] device tensors of `dtype`, heads ordered
  *    (kv head, group member); kv_layer: a tiled cache layer as lmb200_session_kv_layer returns.
+ *  - T must not exceed the capacity of the layer that the strides describe: the kernels read
+ *    ceil(T / 16) blocks of 32 * head_dim elements per (sequence, kv head).  Strides too small
+ *    for T (kv_head_stride < ceil(T / 16) * 32 * head_dim, or kv_batch_stride < n_kv_heads *
+ *    kv_head_stride) are rejected with LMB200_EINVAL; on the bf16 path group must be <= 8.
  *  - Shapes whose partial results exceed the array (more than 2 Mi floats: roughly
  *    batch * n_kv_heads * group * splits * (head_dim + 2)) are rejected with LMB200_EINVAL.
  *  - The first call on a device looks up the array's device address; make that call outside any

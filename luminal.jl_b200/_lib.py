@@ -75,14 +75,15 @@ SIGNATURES = {
     "lmb200_prefill_gemm": [_u64, _i32, _i32, _i32, _vp, _vp, _vp],
     "lmb200_whisper_encoder_create": [_u64, _i32, _i32, _i32, _i32, _i32, _i32, C.POINTER(_u64)],
     "lmb200_whisper_encoder_destroy": [_u64],
-    "lmb200_whisper_encoder_set_weight": [_u64, C.c_char_p, _vp, _i32],
+    "lmb200_whisper_encoder_set_weight": [_u64, C.c_char_p, _vp, _i32, _pi64, _i32],
     "lmb200_whisper_encoder_run": [_u64, _vp, _i32, _i32, _vp],
     "lmb200_whisper_encoder_cross_kv": [_u64, _u64],
     "lmb200_model_create": [_u64, C.POINTER(ModelConfig), C.POINTER(_u64)],
     "lmb200_shard_extent": [C.POINTER(ModelConfig), _i32, _pi32, _pi32],
     "lmb200_shard_map": [C.POINTER(ModelConfig), _i32, _i32, _i32, _pi32, _pi32, _pi32],
     "lmb200_model_destroy": [_u64],
-    "lmb200_model_set_weight": [_u64, C.c_char_p, _vp, _i32],
+    "lmb200_model_set_weight": [_u64, C.c_char_p, _vp, _i32, _pi64, _i32],
+    "lmb200_model_missing_weights": [_u64, C.c_char_p, _i64, _pi32],
     "lmb200_model_init_random": [_u64, _u64, _f32],
     "lmb200_model_weight_bytes": [_u64, _pi64],
     "lmb200_session_create": [_u64, _i32, _i32, C.POINTER(_u64)],

@@ -1,5 +1,6 @@
 // Model weights (tiled, sharded), the decode session and its CUDA graph.
 #include <math.h>
+#include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
 
@@ -806,10 +807,31 @@ extern "C" int32_t lmb200_model_init_random(lmb200_model h, uint64_t seed, float
   f.key[0] = stream_key(seed, kIdHead);
   LMB_TRY(fill_tiled_dt(M, M->lm_head, M->m_head, f));
   LMB_CUDA(cudaStreamSynchronize(ctx->stream));
+  M->all_weights_set = true;
   return LMB200_OK;
 }
 
-extern "C" int32_t lmb200_model_set_weight(lmb200_model h, const char* name, const float* host, int32_t layout) {
+// The caller states the shape of what `host` points to; it must be the logical shape the model's
+// configuration gives the tensor (matrices [out, in]; vectors [n], [1, n] or [n, 1]), so that a
+// checkpoint of another width is refused instead of being read out of bounds.
+static int32_t check_weight_shape(const char* name, int32_t rank, const int64_t* dims, int64_t rows, int64_t cols) {
+  LMB_REQUIRE(rank >= 1 && rank <= 2 && dims, "set_weight: '%s': rank %d (expected 1 or 2 with the dimensions given)", name, rank);
+  const int64_t d0 = dims[0], d1 = rank == 2 ? dims[1] : 1;
+  bool ok;
+  if (rows == 1) ok = (rank == 1 && d0 == cols) || (rank == 2 && ((d0 == 1 && d1 == cols) || (d0 == cols && d1 == 1)));
+  else ok = rank == 2 && d0 == rows && d1 == cols;
+  if (!ok) {
+    if (rows == 1)
+      return fail(LMB200_EINVAL, "set_weight: '%s' has shape [%lld%s%lld], the model expects [%lld]", name, (long long)d0,
+                  rank == 2 ? ", " : "; rank 1, ", (long long)d1, (long long)cols);
+    return fail(LMB200_EINVAL, "set_weight: '%s' has shape [%lld, %lld] (rank %d), the model expects [%lld, %lld]", name,
+                (long long)d0, (long long)d1, rank, (long long)rows, (long long)cols);
+  }
+  return LMB200_OK;
+}
+
+extern "C" int32_t lmb200_model_set_weight(lmb200_model h, const char* name, const float* host, int32_t rank,
+                                           const int64_t* dims, int32_t layout) {
   Model* M = model_from(h);
   if (!M) return LMB200_EINVAL;
   LMB_REQUIRE(name && host, "set_weight: null argument");
@@ -836,7 +858,7 @@ extern "C" int32_t lmb200_model_set_weight(lmb200_model h, const char* name, con
     else {
       int layer = -1, used = 0;
       if (sscanf(name, "model.decoder.layers.%d.%n", &layer, &used) < 1 || layer < 0 || layer >= c.n_layers)
-        return fail(LMB200_EINVAL, "set_weight: unknown tensor '%s'", name);
+        return fail(LMB200_ENOTFOUND, "set_weight: unknown tensor '%s'", name);
       const std::string tail(name + used);
       LayerWeights& L = M->layers[layer];
       auto vec = [&](float* d, int len) { dst = d; rows = 1; cols = len; plain_f32 = true; };
@@ -866,7 +888,7 @@ extern "C" int32_t lmb200_model_set_weight(lmb200_model h, const char* name, con
       else if (tail == "fc2.bias") vec(L.b_fc2, hid);
       else if (tail == "final_layer_norm.weight") vec(L.ffn_norm, hid);
       else if (tail == "final_layer_norm.bias") vec(L.ffn_norm_b, hid);
-      else return fail(LMB200_EINVAL, "set_weight: unknown tensor '%s'", name);
+      else return fail(LMB200_ENOTFOUND, "set_weight: unknown tensor '%s'", name);
     }
   } else if (n == "model.embed_tokens.weight") { dst = M->embed; rows = c.vocab; cols = c.hidden; plain_embed = true; }
   else if (n == "model.norm.weight") { dst = M->final_norm; rows = 1; cols = c.hidden; plain_f32 = true; }
@@ -874,7 +896,7 @@ extern "C" int32_t lmb200_model_set_weight(lmb200_model h, const char* name, con
   else {
     int layer = -1, used = 0;
     if (sscanf(name, "model.layers.%d.%n", &layer, &used) < 1 || layer < 0 || layer >= c.n_layers)
-      return fail(LMB200_EINVAL, "set_weight: unknown tensor '%s'", name);
+      return fail(LMB200_ENOTFOUND, "set_weight: unknown tensor '%s'", name);
     const std::string tail(name + used);
     LayerWeights& L = M->layers[layer];
     const int kvd = c.n_kv_heads * M->D;
@@ -887,8 +909,9 @@ extern "C" int32_t lmb200_model_set_weight(lmb200_model h, const char* name, con
     else if (tail == "mlp.gate_proj.weight") { dst = L.wgu; map = &M->m_gu; slot = 0; rows = c.intermediate; cols = c.hidden; }
     else if (tail == "mlp.up_proj.weight") { dst = L.wgu; map = &M->m_gu; slot = 1; rows = c.intermediate; cols = c.hidden; }
     else if (tail == "mlp.down_proj.weight") { dst = L.wdown; map = &M->m_down; rows = c.hidden; cols = c.intermediate; }
-    else return fail(LMB200_EINVAL, "set_weight: unknown tensor '%s'", name);
+    else return fail(LMB200_ENOTFOUND, "set_weight: unknown tensor '%s'", name);
   }
+  LMB_TRY(check_weight_shape(name, rank, dims, rows, cols));
   float* stage = nullptr;
   const int64_t bytes = rows * cols * 4;
   LMB_TRY(dmalloc((void**)&stage, bytes, false, ctx->stream));
@@ -922,7 +945,60 @@ extern "C" int32_t lmb200_model_set_weight(lmb200_model h, const char* name, con
   } while (0);
   cudaStreamSynchronize(ctx->stream);
   cudaFree(stage);
+  if (rc == LMB200_OK) M->weights_set.insert(n);
   return rc;
+}
+
+// Registry names of every tensor this model reads (src/NN.jl:180-225, 433-445; src/Whisper.jl:423-481).
+static std::vector<std::string> expected_weight_names(const Model* M) {
+  std::vector<std::string> v;
+  const lmb200_model_config& c = M->cfg;
+  char buf[160];
+  if (c.arch == LMB200_ARCH_WHISPER_DECODER) {
+    v = {"model.decoder.embed_tokens.weight", "model.decoder.embed_positions.weight", "model.decoder.layer_norm.weight",
+         "model.decoder.layer_norm.bias"};
+    static const char* tails[] = {"self_attn.q_proj.weight", "self_attn.k_proj.weight", "self_attn.v_proj.weight",
+                                  "self_attn.q_proj.bias", "self_attn.v_proj.bias", "self_attn.out_proj.weight",
+                                  "self_attn.out_proj.bias", "self_attn_layer_norm.weight", "self_attn_layer_norm.bias",
+                                  "encoder_attn.q_proj.weight", "encoder_attn.q_proj.bias", "encoder_attn.out_proj.weight",
+                                  "encoder_attn.out_proj.bias", "encoder_attn_layer_norm.weight", "encoder_attn_layer_norm.bias",
+                                  "fc1.weight", "fc1.bias", "fc2.weight", "fc2.bias", "final_layer_norm.weight",
+                                  "final_layer_norm.bias"};
+    for (int l = 0; l < c.n_layers; ++l)
+      for (const char* t : tails) { snprintf(buf, sizeof(buf), "model.decoder.layers.%d.%s", l, t); v.push_back(buf); }
+    return v;
+  }
+  v = {"model.embed_tokens.weight", "model.norm.weight", "lm_head.weight"};
+  static const char* tails[] = {"input_layernorm.weight", "post_attention_layernorm.weight", "self_attn.q_proj.weight",
+                                "self_attn.k_proj.weight", "self_attn.v_proj.weight", "self_attn.o_proj.weight",
+                                "mlp.gate_proj.weight", "mlp.up_proj.weight", "mlp.down_proj.weight"};
+  for (int l = 0; l < c.n_layers; ++l)
+    for (const char* t : tails) { snprintf(buf, sizeof(buf), "model.layers.%d.%s", l, t); v.push_back(buf); }
+  return v;
+}
+
+extern "C" int32_t lmb200_model_missing_weights(lmb200_model h, char* names_out, int64_t capacity, int32_t* n_missing) {
+  Model* M = model_from(h);
+  if (!M) return LMB200_EINVAL;
+  LMB_REQUIRE(n_missing && (names_out || capacity == 0) && capacity >= 0, "missing_weights: bad argument");
+  int32_t n = 0;
+  int64_t used = 0;
+  if (capacity > 0) names_out[0] = 0;
+  if (!M->all_weights_set) {
+    for (const std::string& name : expected_weight_names(M)) {
+      if (M->weights_set.count(name)) continue;
+      ++n;
+      const int64_t need = (int64_t)name.size() + 1;
+      if (used + need < capacity) {
+        memcpy(names_out + used, name.c_str(), name.size());
+        names_out[used + name.size()] = '\n';
+        used += need;
+        names_out[used] = 0;
+      }
+    }
+  }
+  *n_missing = n;
+  return LMB200_OK;
 }
 
 // =============================================================================================

@@ -1,6 +1,7 @@
 // Model (weights in the tiled layouts) and session (KV cache, activations, CUDA graph of a step).
 #pragma once
 #include <map>
+#include <set>
 #include <string>
 #include <vector>
 
@@ -67,6 +68,8 @@ struct Model {
   void* lm_head = nullptr;
   float* inv_freq = nullptr;    // [D/2]
   int64_t weight_bytes = 0;
+  std::set<std::string> weights_set;   // registry names given through lmb200_model_set_weight
+  bool all_weights_set = false;        // lmb200_model_init_random filled everything
 };
 
 struct Session {

@@ -272,20 +272,32 @@ extern "C" int32_t lmb200_whisper_encoder_destroy(uint64_t h) {
 // Names as the reference registers them (src/Whisper.jl:354-404, 809-831): model.encoder.conv{1,2}.{weight,bias},
 // model.encoder.layers.{i}.{self_attn.{q,k,v,out}_proj, self_attn_layer_norm, fc1, fc2, final_layer_norm}.{weight,bias},
 // model.encoder.layer_norm.{weight,bias}, model.decoder.layers.{i}.encoder_attn.{k,v}_proj.{weight,bias}.
-extern "C" int32_t lmb200_whisper_encoder_set_weight(uint64_t h, const char* name, const float* host, int32_t layout) {
+extern "C" int32_t lmb200_whisper_encoder_set_weight(uint64_t h, const char* name, const float* host, int32_t rank,
+                                                     const int64_t* dims, int32_t layout) {
   WhisperEncoder* E = enc_from(h);
   if (!E) return LMB200_EINVAL;
   LMB_REQUIRE(name && host, "whisper_encoder_set_weight: null argument");
+  LMB_REQUIRE(rank >= 1 && rank <= 2 && dims, "whisper_encoder_set_weight: %s: rank %d (expected 1 or 2 with the dimensions given)", name, rank);
+  // the stated shape must be the one the encoder's configuration gives the tensor: nothing is read past it
+  auto shape_is = [&](int64_t rows, int64_t cols) -> int32_t {
+    const int64_t d0 = dims[0], d1 = rank == 2 ? dims[1] : 1;
+    const bool ok = rows == 1 ? ((rank == 1 && d0 == cols) || (rank == 2 && ((d0 == 1 && d1 == cols) || (d0 == cols && d1 == 1))))
+                              : (rank == 2 && d0 == rows && d1 == cols);
+    if (!ok)
+      return fail(LMB200_EINVAL, "whisper_encoder_set_weight: %s has shape [%lld, %lld] (rank %d), the encoder expects [%lld, %lld]",
+                  name, (long long)d0, (long long)d1, rank, (long long)rows, (long long)cols);
+    return LMB200_OK;
+  };
   LMB_REQUIRE(layout == LMB200_ROWMAJOR || layout == LMB200_COLMAJOR, "whisper_encoder_set_weight: layout %d", layout);
   LMB_CUDA(cudaSetDevice(E->ctx->device));
   const std::string n(name);
   const int d = E->d;
   auto linear = [&](EncLinear& lin, const std::string& tail, int rows, int cols, int perm) -> int32_t {
-    if (tail == "weight") return upload_matrix(E, lin, host, rows, cols, layout, perm);
-    if (tail == "bias") return upload_vector(E, &lin.bias, host, rows, perm == PERM_ROWS);
-    return fail(LMB200_EINVAL, "whisper_encoder_set_weight: unknown tensor %s", name);
+    if (tail == "weight") { LMB_TRY(shape_is(rows, cols)); return upload_matrix(E, lin, host, rows, cols, layout, perm); }
+    if (tail == "bias") { LMB_TRY(shape_is(1, rows)); return upload_vector(E, &lin.bias, host, rows, perm == PERM_ROWS); }
+    return fail(LMB200_ENOTFOUND, "whisper_encoder_set_weight: unknown tensor %s", name);
   };
-  auto vec = [&](float** dst, int len) -> int32_t { return upload_vector(E, dst, host, len, false); };
+  auto vec = [&](float** dst, int len) -> int32_t { LMB_TRY(shape_is(1, len)); return upload_vector(E, dst, host, len, false); };
   const std::string enc = "model.encoder.", dec = "model.decoder.layers.";
   if (n.rfind(enc, 0) == 0) {
     const std::string r = n.substr(enc.size());
@@ -322,7 +334,7 @@ extern "C" int32_t lmb200_whisper_encoder_set_weight(uint64_t h, const char* nam
       }
     }
   }
-  return fail(LMB200_EINVAL, "whisper_encoder_set_weight: unknown tensor %s", name);
+  return fail(LMB200_ENOTFOUND, "whisper_encoder_set_weight: unknown tensor %s", name);
 }
 
 // mel: [batch, n_mels, frames] float32 row-major on the host.  out (NULL or [batch, S, d_model] float32, S =

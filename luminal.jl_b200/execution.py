@@ -179,6 +179,10 @@ def compile_fused(model, reg, inputs, device=None, batch=1, max_ctx=2048, dtype=
         if data is None:
             raise KeyError(f"weight {name} (node {t.id}) has no data")
         m.set_weight(name, data.numpy() if isinstance(data, DeviceArray) else np.asarray(data, dtype=np.float32))
+    missing = m.missing_weights()
+    if missing:
+        m.close()
+        raise KeyError(f"the registry leaves {len(missing)} model tensors unset: {missing[:6]}")
     return Session(m, batch, max_ctx)
 
 

@@ -450,6 +450,10 @@ def compile_b200(graph, output_id, inputs=None, device=None, max_ctx=2048, dtype
         if data is None:
             raise KeyError(f"{name} (node {node_id}) has no data")
         model.set_weight(name, data.numpy() if isinstance(data, DeviceArray) else np.asarray(data, dtype=np.float32))
+    missing = model.missing_weights()
+    if missing:
+        model.close()
+        raise KeyError(f"the graph leaves {len(missing)} model tensors unset: {missing[:6]}")
     return Session(model, batch or m.batch, max_ctx), m
 
 

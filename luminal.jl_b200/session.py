@@ -37,7 +37,16 @@ class Model:
     def set_weight(self, name, array, layout=ROWMAJOR):
         a = np.asarray(array, dtype=np.float32)
         host = np.asfortranarray(a) if layout == COLMAJOR else np.ascontiguousarray(a)
-        _lib.call("lmb200_model_set_weight", self.handle, name.encode(), host.ctypes.data_as(C.c_void_p), layout)
+        _lib.call("lmb200_model_set_weight", self.handle, name.encode(), host.ctypes.data_as(C.c_void_p),
+                  a.ndim, _lib.dims(a.shape), layout)
+
+    def missing_weights(self):
+        """Registry names of the model's tensors that nothing has set yet."""
+        n = C.c_int32(0)
+        buf = C.create_string_buffer(1 << 20)
+        _lib.call("lmb200_model_missing_weights", self.handle, buf, len(buf), C.byref(n))
+        names = [s for s in buf.value.decode().split("\n") if s]
+        return names if len(names) == n.value else names + [f"... and {n.value - len(names)} more"]
 
     def set_weights(self, weights, layout=ROWMAJOR):
         for name, a in weights.items():

@@ -78,9 +78,15 @@ def _files(path):
     return [path] if os.path.exists(path) else []
 
 
-def load_safetensors(model, path):
+ENOTFOUND = -7          # LMB200_ENOTFOUND: the model has no tensor of that name
+
+
+def load_safetensors(model, path, warn_missing=True):
     """Sets every tensor of the file (or of the shards in the directory) that the model knows.
-    Returns (loaded names, skipped names)."""
+    Returns (loaded names, skipped names).  Only names the model does not have are skipped; a tensor
+    of the wrong shape, a CUDA error or any other failure is raised.  Model tensors that no file
+    provided are reported with a warning, as load_weights! does for missing keys
+    (src/Weights.jl:86-91); `model.missing_weights()` returns them."""
     files = _files(path)
     if not files:
         raise FileNotFoundError(f"No safetensors files found at: {path}")
@@ -90,6 +96,14 @@ def load_safetensors(model, path):
             try:
                 model.set_weight(name, a)
                 loaded.append(name)
-            except LuminalB200Error:
+            except LuminalB200Error as e:
+                if e.code != ENOTFOUND:
+                    raise
                 skipped.append(name)
+    if warn_missing and hasattr(model, "missing_weights"):
+        missing = model.missing_weights()
+        if missing:
+            import warnings
+            warnings.warn(f"{len(missing)} model tensors were not found in {path}: " + ", ".join(missing[:8]) +
+                          (" ..." if len(missing) > 8 else ""), stacklevel=2)
     return loaded, skipped

@@ -186,7 +186,8 @@ class FusedEncoder:
             if not (name.startswith("model.encoder.") or ".encoder_attn.k_proj." in name or ".encoder_attn.v_proj." in name):
                 continue
             host = np.ascontiguousarray(np.asarray(a, dtype=np.float32))
-            self._lib.call("lmb200_whisper_encoder_set_weight", self.handle, name.encode(), host.ctypes.data_as(C.c_void_p), 0)
+            self._lib.call("lmb200_whisper_encoder_set_weight", self.handle, name.encode(), host.ctypes.data_as(C.c_void_p),
+                           host.ndim, self._lib.dims(host.shape), 0)
             used.append(name)
         return used
 

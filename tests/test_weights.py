@@ -64,3 +64,62 @@ def test_model_from_safetensors_shards_matches_arrays(tmp_path, lib_built, devic
     for s in (sa, sb):
         s.close()
     a.close(); b.close()
+
+
+class _FakeModel:
+    """Host-only stand-in for Model: knows two tensors, refuses a wrong shape like the library does."""
+    def __init__(self, L):
+        self.L, self.shapes, self.got = L, {"a.weight": (4, 8), "b.weight": (8,)}, {}
+
+    def set_weight(self, name, array):
+        if name not in self.shapes:
+            raise self.L.LuminalB200Error(-7, f"set_weight: unknown tensor '{name}'")
+        if tuple(array.shape) != self.shapes[name]:
+            raise self.L.LuminalB200Error(-1, f"set_weight: '{name}' has shape {array.shape}")
+        self.got[name] = array
+
+    def missing_weights(self):
+        return [n for n in self.shapes if n not in self.got]
+
+
+def test_loader_skips_unknown_names_only_and_reports_missing(tmp_path, lib_built):
+    """Only 'the model has no such tensor' is a skip; a wrong shape is an error, and model tensors
+    that no file provided are warned about (load_weights!, src/Weights.jl:86-91)."""
+    L = lib_built
+    W = L.weights
+    good = tmp_path / "good.safetensors"
+    W.write_safetensors(good, {"a.weight": np.ones((4, 8), np.float32), "extra": np.ones(3, np.float32)})
+    m = _FakeModel(L)
+    with pytest.warns(UserWarning, match="b.weight"):
+        loaded, skipped = W.load_safetensors(m, str(good))
+    assert loaded == ["a.weight"] and skipped == ["extra"]
+    bad = tmp_path / "bad.safetensors"
+    W.write_safetensors(bad, {"a.weight": np.ones((4, 4), np.float32)})
+    with pytest.raises(L.LuminalB200Error, match="shape"):
+        W.load_safetensors(_FakeModel(L), str(bad))
+
+
+@pytest.mark.gpu
+def test_wrong_shaped_tensor_is_refused(lib_built, device):
+    """A checkpoint of another width under a known name must not be read past its end."""
+    L = lib_built
+    cfg = O.CONFIGS["small_llama"]
+    m = L.Model(device, n_layers=cfg["n_layers"], hidden=cfg["hidden"], n_heads=cfg["n_heads"], n_kv_heads=cfg["n_kv_heads"],
+                intermediate=cfg["intermediate"], vocab=cfg["vocab"], eps=cfg["eps"], rope_base=cfg["rope_base"], dtype="f32")
+    hid = cfg["hidden"]
+    with pytest.raises(L.LuminalB200Error, match=r"expects \[256, 256\]") as e:
+        m.set_weight("model.layers.0.self_attn.q_proj.weight", np.zeros((hid // 2, hid), np.float32))
+    assert e.value.code == -1
+    with pytest.raises(L.LuminalB200Error, match="expects") as e:
+        m.set_weight("model.norm.weight", np.zeros(hid + 1, np.float32))
+    assert e.value.code == -1
+    with pytest.raises(L.LuminalB200Error) as e:
+        m.set_weight("model.layers.0.no_such.weight", np.zeros(4, np.float32))
+    assert e.value.code == -7
+    n_expected = 3 + 9 * cfg["n_layers"]
+    assert len(m.missing_weights()) == n_expected
+    m.set_weight("model.norm.weight", np.ones(hid, np.float32))
+    assert len(m.missing_weights()) == n_expected - 1 and "model.norm.weight" not in m.missing_weights()
+    m.init_random(1, 0.02)
+    assert m.missing_weights() == []
+    m.close()
