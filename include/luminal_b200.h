@@ -82,6 +82,13 @@ int32_t lmb200_launch_count(lmb200_ctx ctx, int64_t* count);
 int32_t lmb200_comm_unique_id(uint8_t id_out[128]);
 int32_t lmb200_comm_init(lmb200_ctx ctx, int32_t n_ranks, int32_t rank, const uint8_t id[128]);
 int32_t lmb200_comm_destroy(lmb200_ctx ctx);
+/* Recovery after a tensor-parallel call returned LMB200_ETIMEOUT (a peer never signalled, or its
+ * signal was invalid).  The ranks are then out of step, and prefill / decode calls of tensor-parallel
+ * sessions return LMB200_ESTATE until every rank has called this, between steps, with nothing in
+ * flight: the ranks agree on a common step number again (bounded wait for the peers) and the error
+ * marks are cleared.  Session positions are not touched: put them back with
+ * lmb200_session_set_position.  Not in the reference (single device). */
+int32_t lmb200_comm_resync(lmb200_ctx ctx);
 int32_t lmb200_allreduce_sum_f32(lmb200_ctx ctx, void* dptr, int64_t count);
 
 /* ---------------------------------------------------------------------------------------------

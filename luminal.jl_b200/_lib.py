@@ -49,6 +49,7 @@ SIGNATURES = {
     "lmb200_comm_unique_id": [C.POINTER(C.c_uint8)],
     "lmb200_comm_init": [_u64, _i32, _i32, C.POINTER(C.c_uint8)],
     "lmb200_comm_destroy": [_u64],
+    "lmb200_comm_resync": [_u64],
     "lmb200_allreduce_sum_f32": [_u64, _vp, _i64],
     "lmb200_alloc": [_u64, _i64, C.POINTER(_vp)],
     "lmb200_free": [_u64, _vp],

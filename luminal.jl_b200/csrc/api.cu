@@ -46,10 +46,20 @@ static bool g_pdl = true;
 bool pdl_enabled() { return g_pdl; }
 void pdl_set_enabled(bool on) { g_pdl = on; }
 
+// A wait that ran out inside a tensor-parallel step leaves the ranks out of step with one another
+// (this rank advanced its counters on sums it never received), so the communicator is marked broken:
+// the device word keeps every later signal of this rank marked invalid, and the session calls refuse
+// tensor-parallel work until lmb200_comm_resync.
 int32_t check_device_error(Ctx* ctx) {
-  if (ctx->dev_err && *reinterpret_cast<volatile int*>(ctx->dev_err) != 0) {
+  const int code = ctx->dev_err ? *reinterpret_cast<volatile int*>(ctx->dev_err) : 0;
+  if (code != 0) {
     *ctx->dev_err = 0;
-    return fail(LMB200_ETIMEOUT, "a kernel gave up a bounded wait (mbarrier / flag): results of the last call are invalid");
+    if (ctx->nccl_comm && ctx->tp_size > 1) ctx->comm_broken = true;
+    if (code == 2)
+      return fail(LMB200_ETIMEOUT, "a peer rank's signal was invalid (that rank had a wait run out, or the ranks' step counters "
+                                   "differ): results of the last call are invalid; call lmb200_comm_resync on every rank");
+    return fail(LMB200_ETIMEOUT, "a kernel gave up a bounded wait (mbarrier / flag): results of the last call are invalid%s",
+                ctx->comm_broken ? "; the tensor-parallel ranks are out of step, call lmb200_comm_resync on every rank" : "");
   }
   return LMB200_OK;
 }
@@ -129,7 +139,9 @@ int32_t peer_setup(Ctx* c) {
   if ((sel && strcmp(sel, "nccl") == 0) || c->tp_size < 2 || c->tp_size > 8 || !g_nccl.AllGather) return LMB200_OK;
   const int n = c->tp_size;
   const char* wms = getenv("LMB200_PEER_WAIT_MS");          // how long a kernel waits for a peer's signal
-  c->peer_wait_cycles = wms && atoll(wms) > 0 ? atoll(wms) * 1900000ll : kPeerWaitCycles;
+  int khz = 0;                                              // SM clock the limit is converted with (clock64 ticks)
+  if (cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, c->device) != cudaSuccess || khz <= 0) { cudaGetLastError(); khz = 1965000; }
+  c->peer_wait_cycles = wms && atoll(wms) > 0 ? atoll(wms) * (long long)khz : kPeerWaitCycles;
   void *region = nullptr, *dsend = nullptr, *drecv = nullptr;
   PeerHello mine, all[8];
   memset(&mine, 0, sizeof(mine));
@@ -286,6 +298,13 @@ extern "C" int32_t lmb200_init(int32_t device, lmb200_ctx* out) {
     return fail(LMB200_ECUDA, "init: pinned allocation failed");
   }
   *c->dev_err = 0;
+  if (cudaMalloc((void**)&c->dev_broken, sizeof(int)) != cudaSuccess || cudaMemset(c->dev_broken, 0, sizeof(int)) != cudaSuccess) {
+    cudaGetLastError();
+    cudaFreeHost(c->dev_err);
+    cudaStreamDestroy(c->own_stream);
+    delete c;
+    return fail(LMB200_ENOMEM, "init: device allocation failed");
+  }
   // LMB200_GEMV_KERNEL=mma selects the mma.sync bf16 GEMV (for A/B runs); default: tcgen05
   const char* pdl = getenv("LMB200_PDL");      // LMB200_PDL=0: plain stream-ordered launches
   pdl_set_enabled(!(pdl && atoi(pdl) == 0));
@@ -296,7 +315,7 @@ extern "C" int32_t lmb200_init(int32_t device, lmb200_ctx* out) {
   if (rc == LMB200_OK) rc = flash_tc_configure();
   if (rc == LMB200_OK) rc = step_kernels_configure();
   if (rc == LMB200_OK) rc = prefill_configure();
-  if (rc != LMB200_OK) { cudaFreeHost(c->dev_err); cudaStreamDestroy(c->own_stream); delete c; return rc; }
+  if (rc != LMB200_OK) { cudaFree(c->dev_broken); cudaFreeHost(c->dev_err); cudaStreamDestroy(c->own_stream); delete c; return rc; }
   *out = reinterpret_cast<lmb200_ctx>(c);
   return LMB200_OK;
 }
@@ -310,6 +329,7 @@ extern "C" int32_t lmb200_shutdown(lmb200_ctx h) {
   if (c->nccl_comm && g_nccl.CommDestroy) g_nccl.CommDestroy(c->nccl_comm);
   cudaStreamDestroy(c->own_stream);
   cudaFreeHost(c->dev_err);
+  cudaFree(c->dev_broken);
   c->magic = 0;
   delete c;
   return LMB200_OK;
@@ -378,6 +398,33 @@ extern "C" int32_t lmb200_comm_destroy(lmb200_ctx h) {
     c->tp_size = 1;
     c->tp_rank = 0;
   }
+  return LMB200_OK;
+}
+
+// After a failed tensor-parallel step (LMB200_ETIMEOUT) the ranks' step counters differ.  Collective:
+// every rank calls this between steps with nothing in flight; the ranks agree on a step number past
+// every rank's (NCCL max-reduce, bounded wait), which makes all older signals stale, and the broken
+// marks are cleared.  Session positions are the caller's to put back (lmb200_session_set_position).
+extern "C" int32_t lmb200_comm_resync(lmb200_ctx h) {
+  Ctx* c = ctx_from(h);
+  if (!c) return LMB200_EINVAL;
+  LMB_REQUIRE(c->nccl_comm && c->tp_size > 1, "comm_resync: no tensor-parallel communicator");
+  LMB_CUDA(cudaSetDevice(c->device));
+  LMB_CUDA(cudaStreamSynchronize(c->stream));
+  if (c->peer_n > 1) {
+    // ncclUint64 = 5, ncclMax = 2
+    const int r = g_nccl.AllReduce(c->peer_step, c->peer_step, 1, 5, 2, c->nccl_comm, c->own_stream);
+    if (r != 0) return fail(LMB200_ENCCL, "comm_resync: ncclAllReduce: %s", nccl_str(r));
+    if (!stream_done_within(c->own_stream, 10.0))
+      return fail(LMB200_ETIMEOUT, "comm_resync: the other ranks did not join within 10 s");
+    unsigned long long step = 0;
+    LMB_CUDA(cudaMemcpy(&step, c->peer_step, 8, cudaMemcpyDeviceToHost));
+    step += 1;
+    LMB_CUDA(cudaMemcpy(c->peer_step, &step, 8, cudaMemcpyHostToDevice));
+  }
+  LMB_CUDA(cudaMemset(c->dev_broken, 0, sizeof(int)));
+  *c->dev_err = 0;
+  c->comm_broken = false;
   return LMB200_OK;
 }
 

@@ -49,6 +49,9 @@ struct Ctx {
   cudaStream_t stream = nullptr;
   int64_t launches = 0;
   int* dev_err = nullptr;        // mapped pinned word: a kernel whose bounded wait gave up sets it
+  int* dev_broken = nullptr;     // device word: set with dev_err by a tensor-parallel wait that failed; while it is
+                                 // set every signal this rank sends to its peers is marked invalid (see PeerReduce)
+  bool comm_broken = false;      // a tensor-parallel step failed: steps are refused until lmb200_comm_resync
   // NCCL (resolved with dlopen so that the library loads on hosts without it)
   void* nccl_comm = nullptr;
   int tp_size = 1;
@@ -67,6 +70,7 @@ constexpr int64_t kPeerBufFloats = 1 << 20;
 constexpr int64_t kPeerFlagsOffset = 2 * kPeerBufFloats * 4;          // bytes
 constexpr int64_t kPeerRegionBytes = kPeerFlagsOffset + 4096;
 constexpr unsigned long long kPeerEpochStride = 4096;                 // reductions per step < this
+constexpr unsigned long long kPeerPoison = 1ull << 63;                // a signal sent by a rank whose earlier wait failed
 constexpr long long kPeerWaitCycles = 20000000000ll;                  // about 10 s of SM clock
 
 // What a kernel needs to sum the ranks' partial results of one row-parallel projection: every rank
@@ -80,32 +84,56 @@ struct PeerReduce {
   const unsigned long long* step;          // steps completed so far
   unsigned phase = 0;                      // 1 + index of the reduction inside the step
   int* dev_err = nullptr;
+  int* broken = nullptr;                   // Ctx::dev_broken
   long long wait_cycles = kPeerWaitCycles;
 };
+
+// A signal is the epoch (step * kPeerEpochStride + phase) of the reduction it announces.  A rank
+// that is one reduction ahead may already have overwritten its slot with the next epoch, which is
+// fine (its data of this epoch sits in the other buffer).  Two things are not fine and end the wait
+// with an error instead of a sum of stale partials: a signal marked kPeerPoison (its sender had a
+// wait run out earlier, so what it computed since is not the model's), and a signal a whole step or
+// more ahead (the ranks' step counters have come apart).
 
 #ifdef __CUDACC__
 // All threads of the block call this once the kernel that produced this rank's partial is complete.
 // CTA 0 publishes "rank `rank` has written reduction `epoch`" into every peer's flag array; every
 // CTA then waits until all peers have published the same epoch.  A wait that runs out (or finds an
 // earlier failure recorded) sets the error word and returns, so nothing spins forever.
+__device__ __forceinline__ bool peer_signal_ok(unsigned long long v, unsigned long long epoch, bool* bad) {
+  const unsigned long long e = v & ~kPeerPoison;
+  if (e < epoch) return false;                                   // not there yet
+  *bad = (v & kPeerPoison) != 0ull || e - epoch >= kPeerEpochStride;
+  return true;
+}
+__device__ __forceinline__ void peer_mark_failed(int* dev_err, int* broken, int code) {
+  *reinterpret_cast<volatile int*>(dev_err) = code;
+  if (broken) *reinterpret_cast<volatile int*>(broken) = 1;
+}
+
 __device__ __forceinline__ void peer_exchange_wait(const PeerReduce& pr) {
   const unsigned long long epoch = *pr.step * kPeerEpochStride + pr.phase;
   const int t = threadIdx.x;
   if (t < pr.n && t != pr.rank) {
     if (blockIdx.x == 0) {
+      const bool poisoned = pr.broken && *reinterpret_cast<volatile int*>(pr.broken) != 0;
       __threadfence_system();
-      asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(pr.remote_flag[t]), "l"(epoch) : "memory");
+      asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(pr.remote_flag[t]), "l"(epoch | (poisoned ? kPeerPoison : 0ull)) : "memory");
     }
     const long long t0 = clock64();
     unsigned spins = 0;
     for (;;) {
       unsigned long long v;
       asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(pr.local_flag + t) : "memory");
-      if (v >= epoch) break;
+      bool bad = false;
+      if (peer_signal_ok(v, epoch, &bad)) {
+        if (bad) peer_mark_failed(pr.dev_err, pr.broken, 2);
+        break;
+      }
       if ((++spins & 1023u) == 0u) {
         volatile int* err = pr.dev_err;
         if (*err != 0) break;
-        if (clock64() - t0 > pr.wait_cycles) { *err = 1; break; }
+        if (clock64() - t0 > pr.wait_cycles) { peer_mark_failed(pr.dev_err, pr.broken, 1); break; }
       }
     }
   }

@@ -1050,6 +1050,7 @@ RowParallelOut row_parallel_out(Session* S, int index) {
   r.pr.step = ctx->peer_step;
   r.pr.phase = (unsigned)index + 1;
   r.pr.dev_err = ctx->dev_err;
+  r.pr.broken = ctx->dev_broken;
   r.pr.wait_cycles = ctx->peer_wait_cycles > 0 ? ctx->peer_wait_cycles : kPeerWaitCycles;
   return r;
 }
@@ -1546,6 +1547,16 @@ extern "C" int32_t lmb200_session_read_layer_output(lmb200_session h, int32_t la
   return LMB200_OK;
 }
 
+// Tensor-parallel work is refused while the communicator is marked broken (a rank's wait ran out):
+// the ranks' counters differ, and a further step would either time out again or sum stale partials.
+static int32_t tp_guard(const Session* S, const char* what) {
+  const Ctx* ctx = S->m->ctx;
+  if (S->m->cfg.tp_size > 1 && !S->m->tp_solo && ctx->comm_broken)
+    return fail(LMB200_ESTATE, "%s: a tensor-parallel step failed earlier and the ranks are out of step; every rank must call "
+                               "lmb200_comm_resync (and put the session positions back) first", what);
+  return LMB200_OK;
+}
+
 static int32_t copy_logits_out(Session* S, float* logits_out) {
   Ctx* ctx = S->m->ctx;
   LMB_CUDA(cudaMemcpy2DAsync(logits_out, (size_t)S->m->cfg.vocab * 4, S->logits, (size_t)S->logits_pitch * 4,
@@ -1557,6 +1568,7 @@ extern "C" int32_t lmb200_prefill(lmb200_session h, const int32_t* tokens, int32
   Session* S = session_from(h);
   if (!S) return LMB200_EINVAL;
   LMB_REQUIRE(tokens && n >= 1, "prefill: null tokens or n < 1");
+  LMB_TRY(tp_guard(S, "prefill"));
   if (S->host_pos + n > S->max_ctx)
     return fail(LMB200_ESTATE, "prefill: %d + %d tokens exceed max_ctx %d", S->host_pos, n, S->max_ctx);
   Ctx* ctx = S->m->ctx;
@@ -1602,6 +1614,7 @@ extern "C" int32_t lmb200_decode_step(lmb200_session h, const int32_t* tokens_in
   Session* S = session_from(h);
   if (!S) return LMB200_EINVAL;
   LMB_REQUIRE(tokens_in, "decode_step: null tokens");
+  LMB_TRY(tp_guard(S, "decode_step"));
   if (S->host_pos + 1 > S->max_ctx)
     return fail(LMB200_ESTATE, "decode_step: position %d is past max_ctx %d", S->host_pos, S->max_ctx);
   Ctx* ctx = S->m->ctx;
@@ -1618,6 +1631,7 @@ extern "C" int32_t lmb200_decode_step(lmb200_session h, const int32_t* tokens_in
 
 static int32_t decode_n_common(Session* S, const int32_t* first, bool first_on_device, int32_t n_steps) {
   LMB_REQUIRE(n_steps >= 1, "decode_n: n_steps %d", n_steps);
+  LMB_TRY(tp_guard(S, "decode_n"));
   if (S->host_pos + n_steps > S->max_ctx)
     return fail(LMB200_ESTATE, "decode_n: %d + %d steps exceed max_ctx %d", S->host_pos, n_steps, S->max_ctx);
   Ctx* ctx = S->m->ctx;

@@ -94,6 +94,10 @@ class B200Device:
     def comm_destroy(self):
         _lib.call("lmb200_comm_destroy", self.handle)
 
+    def comm_resync(self):
+        """Collective, after a tensor-parallel call failed with LMB200_ETIMEOUT: brings the ranks back in step."""
+        _lib.call("lmb200_comm_resync", self.handle)
+
     def close(self):
         if self.handle:
             _lib.call("lmb200_shutdown", self.handle)

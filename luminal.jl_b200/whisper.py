@@ -212,5 +212,40 @@ class FusedEncoder:
             self.handle = None
 
 
-__all__ = ["FusedEncoder", "AudioEncoder", "Conv1D", "WhisperSelfAttention", "EncoderTransformerBlock", "sinusoids", "project_cross_kv",
+def registry_shapes(*, d_model, heads, enc_layers, dec_layers, ffn, vocab, n_mels, max_positions):
+    """Registry name -> logical shape of every tensor of a Whisper model of these sizes, under the names
+    AudioEncoder / TextDecoder register them with (src/Whisper.jl:354-404, 423-481): what a checkpoint
+    has to provide, and what random initialisation fills."""
+    del heads
+    d = d_model
+    s = {"model.encoder.conv1.weight": (d, n_mels * 3), "model.encoder.conv1.bias": (d,),
+         "model.encoder.conv2.weight": (d, d * 3), "model.encoder.conv2.bias": (d,),
+         "model.encoder.layer_norm.weight": (d,), "model.encoder.layer_norm.bias": (d,),
+         "model.decoder.embed_tokens.weight": (vocab, d), "model.decoder.embed_positions.weight": (max_positions, d),
+         "model.decoder.layer_norm.weight": (d,), "model.decoder.layer_norm.bias": (d,)}
+
+    def attention(p):                       # k_proj has no bias (src/Whisper.jl:249)
+        for n in ("q_proj", "v_proj", "out_proj"):
+            s[f"{p}.{n}.weight"], s[f"{p}.{n}.bias"] = (d, d), (d,)
+        s[f"{p}.k_proj.weight"] = (d, d)
+
+    def norm(p):
+        s[p + ".weight"], s[p + ".bias"] = (d,), (d,)
+
+    def mlp(p):
+        s[p + ".fc1.weight"], s[p + ".fc1.bias"] = (ffn, d), (ffn,)
+        s[p + ".fc2.weight"], s[p + ".fc2.bias"] = (d, ffn), (d,)
+
+    for i in range(enc_layers):
+        p = f"model.encoder.layers.{i}"
+        attention(p + ".self_attn"); norm(p + ".self_attn_layer_norm"); mlp(p); norm(p + ".final_layer_norm")
+    for i in range(dec_layers):
+        p = f"model.decoder.layers.{i}"
+        attention(p + ".self_attn"); norm(p + ".self_attn_layer_norm")
+        attention(p + ".encoder_attn"); norm(p + ".encoder_attn_layer_norm")
+        mlp(p); norm(p + ".final_layer_norm")
+    return s
+
+
+__all__ = ["registry_shapes", "FusedEncoder", "AudioEncoder", "Conv1D", "WhisperSelfAttention", "EncoderTransformerBlock", "sinusoids", "project_cross_kv",
            "encode_cross_kv"]

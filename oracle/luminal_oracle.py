@@ -686,6 +686,9 @@ CONFIGS = {
     # four kv heads: shards over four tensor-parallel ranks
     "mid_gqa_kv4": dict(n_layers=2, hidden=1024, n_heads=8, n_kv_heads=4, intermediate=2816,
                         vocab=4096, eps=1e-5, rope_base=500000.0),
+    # eight kv heads: shards over eight tensor-parallel ranks (one kv head and one query head each)
+    "mid_gqa_kv8": dict(n_layers=2, hidden=1024, n_heads=8, n_kv_heads=8, intermediate=2816,
+                        vocab=4096, eps=1e-5, rope_base=500000.0),
     "phi3_mini": dict(n_layers=32, hidden=3072, n_heads=32, n_kv_heads=8, intermediate=8192,
                       vocab=32064, eps=1e-5, rope_base=10000.0),
     "llama3_8b": dict(n_layers=32, hidden=4096, n_heads=32, n_kv_heads=8, intermediate=14336,
