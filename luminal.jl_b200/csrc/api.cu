@@ -131,6 +131,18 @@ int32_t gather_hello(Ctx* c, const PeerHello& mine, PeerHello* all, void* dsend,
   return LMB200_OK;
 }
 
+__global__ void fill_u32_kernel(uint32_t* p, uint32_t v, int64_t n) {
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) p[i] = v;
+}
+// This rank's push buffers back to "nothing written yet" everywhere (set-up, and after a failed step)
+int32_t peer_clear_push_buffers(Ctx* c, void* region) {
+  uint32_t* p = reinterpret_cast<uint32_t*>(reinterpret_cast<char*>(region) + kPeerPushOffset);
+  fill_u32_kernel<<<1024, 256, 0, c->own_stream>>>(p, kPeerEmptyPair, 2 * kPeerBufFloats);
+  LMB_CUDA(cudaGetLastError());
+  LMB_CUDA(cudaStreamSynchronize(c->own_stream));
+  return LMB200_OK;
+}
+
 // Maps one exchange region per rank into every rank (CUDA IPC inside one node) for the all-reduce
 // that the decode step's norm kernels do themselves.  Every decision is taken on gathered data, so
 // all ranks end up with the same answer; any failure leaves peer_n == 0 and NCCL does the sums.
@@ -148,6 +160,7 @@ int32_t peer_setup(Ctx* c) {
   bool ok = cudaMalloc(&region, kPeerRegionBytes) == cudaSuccess && cudaMemset(region, 0, kPeerRegionBytes) == cudaSuccess &&
             cudaMalloc((void**)&c->peer_step, 8) == cudaSuccess && cudaMemset(c->peer_step, 0, 8) == cudaSuccess &&
             cudaMalloc((void**)&c->peer_scratch, 4) == cudaSuccess && cudaMemset(c->peer_scratch, 0, 4) == cudaSuccess &&
+            peer_clear_push_buffers(c, region) == LMB200_OK &&
             cudaDeviceSynchronize() == cudaSuccess && cudaIpcGetMemHandle(&mine.handle, region) == cudaSuccess;
   cudaGetLastError();
   mine.ok = ok ? 1 : 0;
@@ -421,6 +434,13 @@ extern "C" int32_t lmb200_comm_resync(lmb200_ctx h) {
     LMB_CUDA(cudaMemcpy(&step, c->peer_step, 8, cudaMemcpyDeviceToHost));
     step += 1;
     LMB_CUDA(cudaMemcpy(c->peer_step, &step, 8, cudaMemcpyHostToDevice));
+    // every rank has stopped (it joined the reduction above): leftovers of the failed step out of this rank's
+    // push buffers, and nobody goes on before all ranks have done so
+    LMB_TRY(peer_clear_push_buffers(c, c->peer_base[c->tp_rank]));
+    const int r2 = g_nccl.AllReduce(c->peer_scratch, c->peer_scratch, 1, 7, 0, c->nccl_comm, c->own_stream);
+    if (r2 != 0) return fail(LMB200_ENCCL, "comm_resync: ncclAllReduce: %s", nccl_str(r2));
+    if (!stream_done_within(c->own_stream, 10.0))
+      return fail(LMB200_ETIMEOUT, "comm_resync: the other ranks did not join within 10 s");
   }
   LMB_CUDA(cudaMemset(c->dev_broken, 0, sizeof(int)));
   *c->dev_err = 0;

@@ -362,13 +362,16 @@ int32_t attn_decode_launch(Ctx* ctx, int dtype, const AttnParams& p_in, cudaStre
   // The attention kernels are launched in plain stream order: they keep their loads in flight
   // through L1, and a CTA that became resident next to a GEMV CTA (programmatic launch) would run
   // with that kernel's small-L1 / large-shared split (measured: 0.79 instead of 0.99 of the HBM rate).
+  // LMB200_ATTN_PDL=1 launches it programmatically after all (A/B runs: with few (sequence, kv head) pairs per
+  // GPU the launch gap weighs more than the L1 split).
+  static const bool attn_pdl = [] { const char* e = getenv("LMB200_ATTN_PDL"); return e && atoi(e) == 1; }();
   if (dtype == LMB200_BF16) {
     LMB_REQUIRE(p.G <= 8, "attention: %d query heads per kv head (max 8 on the bf16 path)", p.G);
     switch (p.D) {
-      case 32: LMB_CUDA(launch_k_opt(false, attn_decode_bf16_kernel<32>, grid, dim3(kAttnThreads), 0, stream, p)); break;
-      case 64: LMB_CUDA(launch_k_opt(false, attn_decode_bf16_kernel<64>, grid, dim3(kAttnThreads), 0, stream, p)); break;
-      case 96: LMB_CUDA(launch_k_opt(false, attn_decode_bf16_kernel<96>, grid, dim3(kAttnThreads), 0, stream, p)); break;
-      case 128: LMB_CUDA(launch_k_opt(false, attn_decode_bf16_kernel<128>, grid, dim3(kAttnThreads), 0, stream, p)); break;
+      case 32: LMB_CUDA(launch_k_opt(attn_pdl, attn_decode_bf16_kernel<32>, grid, dim3(kAttnThreads), 0, stream, p)); break;
+      case 64: LMB_CUDA(launch_k_opt(attn_pdl, attn_decode_bf16_kernel<64>, grid, dim3(kAttnThreads), 0, stream, p)); break;
+      case 96: LMB_CUDA(launch_k_opt(attn_pdl, attn_decode_bf16_kernel<96>, grid, dim3(kAttnThreads), 0, stream, p)); break;
+      case 128: LMB_CUDA(launch_k_opt(attn_pdl, attn_decode_bf16_kernel<128>, grid, dim3(kAttnThreads), 0, stream, p)); break;
       default: return fail(LMB200_EINVAL, "attention: head_dim %d not built for bf16", p.D);
     }
     ctx->launches++;

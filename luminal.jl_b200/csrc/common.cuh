@@ -66,9 +66,15 @@ struct Ctx {
   long long peer_wait_cycles = 0;            // SM cycles a kernel waits for a peer's signal (LMB200_PEER_WAIT_MS, default 10 s)
 };
 
+// Region layout (bytes): two 4 MiB buffers read by the peers (the norm kernels' all-reduce), two 4 MiB
+// buffers written by the peers (the projections that do their own exchange; kept at the "nothing here
+// yet" bit pattern between uses), then the flags of either protocol.
 constexpr int64_t kPeerBufFloats = 1 << 20;
-constexpr int64_t kPeerFlagsOffset = 2 * kPeerBufFloats * 4;          // bytes
-constexpr int64_t kPeerRegionBytes = kPeerFlagsOffset + 4096;
+constexpr int64_t kPeerPushOffset = 2 * kPeerBufFloats * 4;
+constexpr int64_t kPeerFlagsOffset = 4 * kPeerBufFloats * 4;
+constexpr int64_t kPeerPushFlagsOffset = kPeerFlagsOffset + 4096;    // [8 source ranks][256 CTAs] 64-bit flags
+constexpr int64_t kPeerRegionBytes = kPeerPushFlagsOffset + 8 * 256 * 8;
+constexpr uint32_t kPeerEmptyPair = 0x80008000u;                      // two bf16 -0.0: "not written yet" in a push buffer
 constexpr unsigned long long kPeerEpochStride = 4096;                 // reductions per step < this
 constexpr unsigned long long kPeerPoison = 1ull << 63;                // a signal sent by a rank whose earlier wait failed
 constexpr long long kPeerWaitCycles = 20000000000ll;                  // about 10 s of SM clock

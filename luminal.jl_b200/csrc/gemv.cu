@@ -765,10 +765,14 @@ __device__ __forceinline__ void tmem_load_row<16>(float (&v)[16], uint32_t taddr
 // The thread holds batch columns b0 .. b0+NV-1 of the row (the whole row when NV == BP); BP is the
 // batch padding of the activation buffers.
 template <int NV, int BP>
-__device__ __forceinline__ void row_epilogue(const GemvParams& p, float (&v)[NV], int row, int b0) {
+__device__ __forceinline__ void row_epilogue(const GemvParams& p, float (&v)[NV], int row, int b0, const float* s_inv) {
   typedef Layout<__nv_bfloat16> LY;
   constexpr int N = NV;
   const int rb = row >> 4, rr = row & 15, g = rr & 7, hi = rr >> 3;
+  if (s_inv) {                                   // the RMSNorm scale of the input, one per sequence (InvScale)
+#pragma unroll
+    for (int b = 0; b < N; ++b) v[b] *= s_inv[b0 + b];
+  }
   if (p.bias) {
     const float bias = row < p.rows ? p.bias[row] : 0.f;
 #pragma unroll
@@ -865,6 +869,214 @@ namespace {
 #define LMB_TRACE_NS(slot) ((void)0)
 #endif
 
+// The epilogue group (128 threads, e = 0..127) turns the producer's per-CTA sums of squares into the
+// per-sequence scale 1 / sqrt(mean(x*x) + eps) (src/HighLevelOps.jl:299-304).  Four lanes share a
+// sequence; each adds every fourth slot in ascending order and the four are combined pairwise, the
+// same arithmetic in every CTA and on every rank.
+__device__ __forceinline__ void compute_inv_scale(const InvScale& iv, float* s_inv, int e) {
+  if (!iv.ssq) return;
+  const int b = e >> 2, part = e & 3;
+  float s = 0.f;
+  for (int t = part; t < iv.tiles; t += 4) s += __ldcg(iv.ssq + t * 32 + b);
+  s += __shfl_xor_sync(0xffffffffu, s, 1);
+  s += __shfl_xor_sync(0xffffffffu, s, 2);
+  if (part == 0) s_inv[b] = 1.0f / sqrtf(s * (1.0f / (float)iv.n) + iv.eps);
+  asm volatile("bar.sync 1, 128;\n" ::: "memory");
+}
+
+__device__ __forceinline__ uint4 peer_load16(const void* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void peer_store16(void* p, uint4 v) {
+  asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+// bf16 -0.0 marks "not written yet" in a push buffer: a partial that rounds to it is sent as +0.0
+__device__ __forceinline__ uint32_t pack_bf16x2_sendable(float a, float b) {
+  uint32_t w = pack_bf16x2(a, b);
+  if ((w & 0xFFFFu) == 0x8000u) w &= 0xFFFF0000u;
+  if ((w >> 16) == 0x8000u) w &= 0x0000FFFFu;
+  return w;
+}
+__device__ __forceinline__ bool has_empty_bf16(const uint4& u) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+  bool any = false;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) any = any || (w[i] & 0xFFFFu) == 0x8000u || (w[i] >> 16) == 0x8000u;
+  return any;
+}
+__device__ __forceinline__ void unpack_bf16x8(const uint4& u, float (&v)[8]) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+}
+
+// EPI_RESID_NORM on the tile a cluster CTA finalises (rows_per = 128 / C rows of row group r, all Bp
+// batch columns), run by the 128 epilogue threads once every partial row of the cluster sits in `recv`.
+// Thread e owns rows (e >> 2) + 32 j and the 8 batch columns 8 (e & 3) .. + 7, so that a warp covers
+// 8 consecutive rows x Bp columns: its peer stores and its reads of x are contiguous 512-byte runs.
+template <int N>
+__device__ __forceinline__ void resid_norm_tile(const GemvParams& p, const unsigned char* recv_raw, int C, int c, int r,
+                                                int e, float* s_red) {
+  constexpr int BG = N / 8;
+  const int lane = e & 31, we = e >> 5;
+  const int rows_per = 128 / C;
+  const int bg = e & 3, rl0 = e >> 2;
+  const int row0 = r * 128 + c * rows_per;
+  const int iters = (rows_per + 31) >> 5;                      // 1, 1, 2, 4 for 16, 32, 64, 128 rows
+  const float4* recv = reinterpret_cast<const float4*>(recv_raw);
+  const int n = p.push.n, me = p.push.rank;
+  float acc[4][8];
+  bool valid[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int rl = rl0 + 32 * j;
+    valid[j] = j < iters && bg < BG && rl < rows_per && row0 + rl < p.rows;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[j][i] = 0.f;
+    if (valid[j]) {
+      for (int src = 0; src < C; ++src) {                      // the cluster's partials, in CTA order
+        const float4 t0 = recv[((src * rows_per + rl) * N + 8 * bg) / 4], t1 = recv[((src * rows_per + rl) * N + 8 * bg) / 4 + 1];
+        acc[j][0] += t0.x; acc[j][1] += t0.y; acc[j][2] += t0.z; acc[j][3] += t0.w;
+        acc[j][4] += t1.x; acc[j][5] += t1.y; acc[j][6] += t1.z; acc[j][7] += t1.w;
+      }
+    }
+  }
+  if (n > 1) {
+    const unsigned long long epoch = *p.push.step * kPeerEpochStride + p.push.phase;
+    // this rank's partial, rounded to bf16 (never the "not written yet" pattern), into the same place of every peer's region
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (!valid[j]) continue;
+      uint4 u;
+      u.x = pack_bf16x2_sendable(acc[j][0], acc[j][1]); u.y = pack_bf16x2_sendable(acc[j][2], acc[j][3]);
+      u.z = pack_bf16x2_sendable(acc[j][4], acc[j][5]); u.w = pack_bf16x2_sendable(acc[j][6], acc[j][7]);
+      unpack_bf16x8(u, acc[j]);                                // what this rank adds is what its peers receive
+      const size_t at = ((size_t)me * p.rows + (row0 + rl0 + 32 * j)) * N + 8 * bg;
+#pragma unroll
+      for (int rk = 0; rk < 8; ++rk)
+        if (rk < n && rk != me) peer_store16(p.push.part[rk] + at, u);
+    }
+    if (e < n && e != me) {                                    // validity channel, unordered with the data
+      const bool poisoned = *reinterpret_cast<volatile int*>(p.push.broken) != 0;
+      asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p.push.flag[e] + me * kPushMaxCtas + blockIdx.x),
+                   "l"(epoch | (poisoned ? kPeerPoison : 0ull))
+                   : "memory");
+    }
+    const uint4 empty = make_uint4(kPeerEmptyPair, kPeerEmptyPair, kPeerEmptyPair, kPeerEmptyPair);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (!valid[j]) continue;
+      __nv_bfloat16* mine = p.push.part[me] + ((size_t)(row0 + rl0 + 32 * j)) * N + 8 * bg;      // + rk * rows * N
+      const size_t src_stride = (size_t)p.rows * N;
+      uint4 got[8];
+      unsigned pending = 0;
+#pragma unroll
+      for (int rk = 0; rk < 8; ++rk)
+        if (rk < n && rk != me) pending |= 1u << rk;
+      const long long t0 = clock64();
+      unsigned spins = 0;
+      while (pending) {
+#pragma unroll
+        for (int rk = 0; rk < 8; ++rk)
+          if (pending & (1u << rk)) got[rk] = peer_load16(mine + rk * src_stride);
+#pragma unroll
+        for (int rk = 0; rk < 8; ++rk)
+          if ((pending & (1u << rk)) && !has_empty_bf16(got[rk])) pending &= ~(1u << rk);
+        if (pending && (++spins & 63u) == 0u) {
+          if (*reinterpret_cast<volatile int*>(p.push.broken) != 0) break;       // an earlier wait of this rank already failed
+          if (clock64() - t0 > p.push.wait_cycles) { peer_mark_failed(p.push.dev_err, p.push.broken, 1); break; }
+        }
+      }
+      float tot[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) tot[i] = 0.f;
+#pragma unroll
+      for (int rk = 0; rk < 8; ++rk) {                         // rank order, the same on every rank
+        if (rk >= n) continue;
+        float pv[8];
+        if (rk == me) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) pv[i] = acc[j][i];
+        } else {
+          unpack_bf16x8(got[rk], pv);
+          *reinterpret_cast<uint4*>(mine + rk * src_stride) = empty;   // ready for the reduction after the next
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) tot[i] += pv[i];
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[j][i] = tot[i];
+    }
+    if (e < n && e != me) {                                    // the senders' validity marks (normally long there)
+      const unsigned long long* flag = p.push.flag[me] + e * kPushMaxCtas + blockIdx.x;
+      const long long t0 = clock64();
+      unsigned spins = 0;
+      for (;;) {
+        unsigned long long v;
+        asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(flag) : "memory");
+        bool bad = false;
+        if (peer_signal_ok(v, epoch, &bad)) {
+          if (bad) peer_mark_failed(p.push.dev_err, p.push.broken, 2);
+          break;
+        }
+        if ((++spins & 63u) == 0u) {
+          if (*reinterpret_cast<volatile int*>(p.push.broken) != 0) break;
+          if (clock64() - t0 > p.push.wait_cycles) { peer_mark_failed(p.push.dev_err, p.push.broken, 1); break; }
+        }
+      }
+    }
+  }
+  // residual add, the next Linear's input x * gain, this tile's share of the sum of squares
+  float ssq[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) ssq[i] = 0.f;
+  __nv_bfloat16* xg = reinterpret_cast<__nv_bfloat16*>(p.rn.xg);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (!valid[j]) continue;
+    const int grow = row0 + rl0 + 32 * j;
+    float4* xr = reinterpret_cast<float4*>(p.rn.x + (size_t)grow * N + 8 * bg);
+    float4 x0 = xr[0], x1 = xr[1];
+    x0.x += acc[j][0]; x0.y += acc[j][1]; x0.z += acc[j][2]; x0.w += acc[j][3];
+    x1.x += acc[j][4]; x1.y += acc[j][5]; x1.z += acc[j][6]; x1.w += acc[j][7];
+    xr[0] = x0; xr[1] = x1;
+    const float xv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+    const float g = p.rn.gain[grow];
+    __nv_bfloat16* o = xg + (size_t)(grow >> 3) * (N * 8) + bg * 64 + (grow & 7);      // Layout::x_offset(8 bg + i, grow, N) = o + 8 i
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      o[8 * i] = __float2bfloat16_rn(xv[i] * g);
+      ssq[i] += xv[i] * xv[i];
+    }
+    if (p.rn.capture) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (8 * bg + i < p.B) p.rn.capture[(size_t)(8 * bg + i) * p.rows + grow] = xv[i];
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {                                // over the 8 rows of the warp that share these batch columns
+    ssq[i] += __shfl_xor_sync(0xffffffffu, ssq[i], 4);
+    ssq[i] += __shfl_xor_sync(0xffffffffu, ssq[i], 8);
+    ssq[i] += __shfl_xor_sync(0xffffffffu, ssq[i], 16);
+  }
+  if (lane < 4) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s_red[we * 32 + 8 * lane + i] = ssq[i];
+  }
+  asm volatile("bar.sync 1, 128;\n" ::: "memory");
+  if (e < 32) p.rn.ssq[(size_t)blockIdx.x * 32 + e] = ((s_red[e] + s_red[32 + e]) + s_red[64 + e]) + s_red[96 + e];
+}
+
 template <int N>
 __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const GemvParams p, int* err) {
   constexpr int kXStage = N * 256;
@@ -879,6 +1091,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const GemvParams
   __shared__ __align__(8) uint64_t acc_full[2];
   __shared__ __align__(8) uint64_t acc_empty[2];
   __shared__ uint32_t tmem_base_slot;
+  __shared__ float s_inv_buf[32];
+  const float* s_inv = p.inv.ssq ? s_inv_buf : nullptr;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const UnitRange ur = unit_range(p);
@@ -949,6 +1163,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const GemvParams
     pdl_wait();
     const int q = warp & 3;
     const int e = tid - 64;                      // 0..127 inside the epilogue group
+    compute_inv_scale(p.inv, s_inv_buf, e);
     int seg = 0;
     int pend_r[2], pend_first[2], pend_n[2], n_pend = 0;
     for (int u = ur.u0; u < ur.u1; ++seg) {
@@ -968,7 +1183,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const GemvParams
       int c_first, n;
       contributors(ur, r, &c_first, &n);
       if (n == 1) {
-        row_epilogue<N, N>(p, v, r * 128 + row_in_group, 0);
+        row_epilogue<N, N>(p, v, r * 128 + row_in_group, 0, s_inv);
         continue;
       }
       float4* part = reinterpret_cast<float4*>(p.partials) + (int64_t)r * p.ksplit * (128 * N / 4);
@@ -1037,7 +1252,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const GemvParams
             const float4 t = lds4(slot);
             v4[0] += t.x; v4[1] += t.y; v4[2] += t.z; v4[3] += t.w;
           }
-          row_epilogue<4, N>(p, v4, pend_r[ip] * 128 + 16 * (ci_[ip] + jj * n_[ip]) + row16, 4 * cg);
+          row_epilogue<4, N>(p, v4, pend_r[ip] * 128 + 16 * (ci_[ip] + jj * n_[ip]) + row16, 4 * cg, s_inv);
         }
         return slot;
       };
@@ -1069,7 +1284,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const GemvParams
               v4[0] += t.x; v4[1] += t.y; v4[2] += t.z; v4[3] += t.w;
             }
           }
-          row_epilogue<4, N>(p, v4, pend_r[ip] * 128 + 16 * ci_[ip] + row16, 4 * cg);
+          row_epilogue<4, N>(p, v4, pend_r[ip] * 128 + 16 * ci_[ip] + row16, 4 * cg, s_inv);
         }
       }
       if (tid == 64) LMB_TRACE(13);
@@ -1138,6 +1353,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_cl_kernel(const GemvParams
   __shared__ __align__(8) uint64_t empty_bar[kStages];
   __shared__ __align__(8) uint64_t acc_full;
   __shared__ uint32_t tmem_base_slot;
+  __shared__ float s_inv_buf[32];
+  __shared__ float s_red[128];
+  const float* s_inv = p.inv.ssq ? s_inv_buf : nullptr;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int C = (int)cluster_nctarank(), c = (int)cluster_ctarank();
@@ -1228,6 +1446,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_cl_kernel(const GemvParams
     // ---------------- epilogue warps: send every row to the CTA that finalises it ----------------
     pdl_wait();
     const int q = warp & 3;
+    compute_inv_scale(p.inv, s_inv_buf, tid - 64);
     float v[N];
     if (n_steps > 0) {
       mbar_wait(&acc_full, 0, dead, err);
@@ -1251,7 +1470,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_cl_kernel(const GemvParams
   // every partial row is in its owner's shared memory once all CTAs of the cluster are here
   cluster_sync_all();
   if (tid == 64) LMB_TRACE(7);
-  if (warp >= 2) {
+  if (warp >= 2 && p.epi == EPI_RESID_NORM) {
+    resid_norm_tile<N>(p, smem + kStages * kStage, C, c, r, tid - 64, s_red);
+  } else if (warp >= 2) {
     const int e = tid - 64;
     const int rows_per = 128 / C;
     const int row16 = lane & 15, cg = e >> 4;               // one float4 (4 batch columns) per thread
@@ -1263,7 +1484,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_cl_kernel(const GemvParams
           const float4 t = recv[((src * rows_per + 16 * j + row16) * N) / 4 + cg];
           v4[0] += t.x; v4[1] += t.y; v4[2] += t.z; v4[3] += t.w;
         }
-        row_epilogue<4, N>(p, v4, r * 128 + c * rows_per + 16 * j + row16, 4 * cg);
+        row_epilogue<4, N>(p, v4, r * 128 + c * rows_per + 16 * j + row16, 4 * cg, s_inv);
       }
     }
   }
@@ -1353,7 +1574,7 @@ template <int Bp>
 int32_t launch_bf16(Ctx* ctx, const GemvParams& p, cudaStream_t stream) {
   if (g_variant == GEMV_MMA_SYNC)
     LMB_CUDA(launch_k(gemv_mma_kernel<Bp / 8>, dim3(p.grid), dim3(kMmaThreads), stream_smem<Bp>(), stream, p, ctx->dev_err));
-  else if (p.cluster > 1)
+  else if (p.cluster >= 1)
     return launch_cluster<Bp>(ctx, p, stream);
   else
     LMB_CUDA(launch_k(gemv_tc_kernel<Bp>, dim3(p.grid), dim3(kTcThreads), stream_smem<Bp>(), stream, p, ctx->dev_err));
@@ -1376,7 +1597,7 @@ void gemv_prefetch_next(GemvParams& p, const Ctx* ctx, int dtype, const void* ne
   if (dtype != LMB200_BF16 || g_variant != GEMV_TCGEN05 || budget_mb <= 0 || !next_W) return;
   const int KS = (int)ceil_div(next_K, 128), nrbg = (int)ceil_div(next_rows, 128);
   const int64_t U = (int64_t)nrbg * KS;
-  const int parts = next_plan.cluster > 1 ? nrbg * next_plan.cluster : next_plan.grid;
+  const int parts = next_plan.cluster >= 1 ? nrbg * next_plan.cluster : next_plan.grid;
   if (parts <= 0 || U / parts < 1) return;
   int64_t chunk = ((int64_t)budget_mb * 1000000 / 32768) / parts;
   if (chunk < 1) chunk = 1;
@@ -1434,6 +1655,22 @@ GemvPlan gemv_plan(const Ctx* ctx, int dtype, int B, int rows, int K) {
   pl.partial_floats = best_ks > 1 ? (int64_t)nrbg * best_ks * RPC * Bp : 0;
   pl.n_counters = nrbg;
   return pl;
+}
+
+GemvPlan gemv_plan_resid(const Ctx* ctx, int B, int rows, int K) {
+  GemvPlan pl = gemv_plan(ctx, LMB200_BF16, B, rows, K);
+  const int Bp = Layout<__nv_bfloat16>::batch_pad(B);
+  const int nrbg = (int)ceil_div(rows, 128);
+  pl.cluster = 0;
+  if (g_variant != GEMV_TCGEN05) return pl;
+  pl.cluster = Bp == 16 ? cluster_choice<16>(ctx, rows, K) : cluster_choice<32>(ctx, rows, K);
+  if (pl.cluster == 0 && nrbg <= ctx->sm_count && nrbg <= kPushMaxCtas) pl.cluster = 1;
+  if (nrbg * pl.cluster > kPushMaxCtas) pl.cluster = 0;
+  return pl;
+}
+
+int gemv_plan_ctas(const GemvPlan& pl, int rows) {
+  return pl.cluster >= 1 ? (int)ceil_div(rows, 128) * pl.cluster : pl.grid;
 }
 
 // Raise the dynamic shared-memory limit of every instantiation once per device, outside any

@@ -479,6 +479,62 @@ __global__ void advance_kernel(int* pos, int* step_ctr, unsigned long long* peer
 }
 
 
+// First kernel of the fused step: x <- embedding rows (out-of-range ids -> zeros, as _gather_kernel! does,
+// src/Execution.jl:580-595), laid out [hidden][Bp]; xg <- bf16(x * gain) in the GEMV activation layout; one
+// slot of per-sequence sums of squares per CTA.  What add_rmsnorm_kernel does for the first layer, minus
+// the scale, which the q/k/v projection applies to its accumulators.  128 threads: thread e owns rows
+// (e >> 2) + 32 j of the CTA's rows and batch columns 8 (e & 3) .. + 7.
+template <int N>
+__global__ void __launch_bounds__(128) embed_prep_kernel(const int* __restrict__ tokens, const __nv_bfloat16* __restrict__ embed,
+                                                         int vocab, int hidden, int B, const float* __restrict__ gain,
+                                                         float* __restrict__ x, __nv_bfloat16* __restrict__ xg,
+                                                         float* __restrict__ ssq_out, int rows_per_cta) {
+  __shared__ float s_red[128];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int e = threadIdx.x, lane = e & 31, we = e >> 5;
+  const int bg = e & 3, rl0 = e >> 2;
+  int tok[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int b = 8 * bg + i;
+    const int t = (b < B && bg < N / 8) ? tokens[b] : -1;
+    tok[i] = (t >= 0 && t < vocab) ? t : -1;
+  }
+  float ssq[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) ssq[i] = 0.f;
+  for (int rl = rl0; rl < rows_per_cta; rl += 32) {
+    const int k = blockIdx.x * rows_per_cta + rl;
+    if (k >= hidden || bg >= N / 8) continue;
+    float xv[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) xv[i] = tok[i] >= 0 ? __bfloat162float(embed[(int64_t)tok[i] * hidden + k]) : 0.f;
+    float4* xr = reinterpret_cast<float4*>(x + (size_t)k * N + 8 * bg);
+    xr[0] = make_float4(xv[0], xv[1], xv[2], xv[3]);
+    xr[1] = make_float4(xv[4], xv[5], xv[6], xv[7]);
+    const float g = gain[k];
+    __nv_bfloat16* o = xg + (size_t)(k >> 3) * (N * 8) + bg * 64 + (k & 7);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      o[8 * i] = __float2bfloat16_rn(xv[i] * g);
+      ssq[i] += xv[i] * xv[i];
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    ssq[i] += __shfl_xor_sync(0xffffffffu, ssq[i], 4);
+    ssq[i] += __shfl_xor_sync(0xffffffffu, ssq[i], 8);
+    ssq[i] += __shfl_xor_sync(0xffffffffu, ssq[i], 16);
+  }
+  if (lane < 4) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s_red[we * 32 + 8 * lane + i] = ssq[i];
+  }
+  __syncthreads();
+  if (e < 32) ssq_out[(size_t)blockIdx.x * 32 + e] = ((s_red[e] + s_red[32 + e]) + s_red[64 + e]) + s_red[96 + e];
+}
+
 int32_t step_kernels_configure() {
 #define LMB_CARVE(KERN) \
   LMB_CUDA(cudaFuncSetAttribute(KERN, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared))
@@ -1159,6 +1215,116 @@ int32_t enqueue_step_t(Session* S, cudaStream_t st, bool with_head) {
   return LMB200_OK;
 }
 
+// Exchange parameters of the projection that carries reduction `index` of the step (2l: o_proj, 2l + 1:
+// down_proj) when it runs EPI_RESID_NORM under tensor parallelism.
+PeerPush peer_push(Session* S, int index) {
+  Ctx* ctx = S->m->ctx;
+  PeerPush pp;
+  const int n = S->m->cfg.tp_size;
+  if (n <= 1 || S->m->tp_solo) return pp;
+  const int64_t buf = kPeerPushOffset + (int64_t)(index & 1) * kPeerBufFloats * 4;
+  pp.n = n;
+  pp.rank = ctx->tp_rank;
+  for (int k = 0; k < n; ++k) {
+    pp.part[k] = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<char*>(ctx->peer_base[k]) + buf);
+    pp.flag[k] = reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(ctx->peer_base[k]) + kPeerPushFlagsOffset);
+  }
+  pp.step = ctx->peer_step;
+  pp.phase = (unsigned)index + 1;
+  pp.dev_err = ctx->dev_err;
+  pp.broken = ctx->dev_broken;
+  pp.wait_cycles = ctx->peer_wait_cycles > 0 ? ctx->peer_wait_cycles : kPeerWaitCycles;
+  return pp;
+}
+
+// The fused decode step of a bf16 Llama / Phi-3: five launches per layer.  The residual add and the
+// RMSNorm around every Linear (src/NN.jl:406-414, 149-161) are carried by the projections themselves:
+// o_proj and down_proj finish with EPI_RESID_NORM (under tensor parallelism including the all-reduce of
+// their partial sums), q/k/v, gate/up and the head multiply their accumulators by the norm's
+// per-sequence scale (InvScale).
+int32_t enqueue_step_fused(Session* S, cudaStream_t st, bool with_head) {
+  Model* M = S->m;
+  Ctx* ctx = M->ctx;
+  const lmb200_model_config& c = M->cfg;
+  const int dt = LMB200_BF16;
+  const int B = S->B, hid = c.hidden, L = c.n_layers;
+  {
+    const int rows_per = S->embed_rows_per_cta;
+    const int grid = (int)ceil_div(hid, rows_per);
+    if (S->Bp == 16)
+      LMB_CUDA(launch_k(embed_prep_kernel<16>, dim3(grid), dim3(128), 0, st, (const int*)S->tokens,
+                        reinterpret_cast<const __nv_bfloat16*>(M->embed), c.vocab, hid, B, (const float*)M->layers[0].attn_norm,
+                        S->xT, reinterpret_cast<__nv_bfloat16*>(S->xn), S->ssq, rows_per));
+    else
+      LMB_CUDA(launch_k(embed_prep_kernel<32>, dim3(grid), dim3(128), 0, st, (const int*)S->tokens,
+                        reinterpret_cast<const __nv_bfloat16*>(M->embed), c.vocab, hid, B, (const float*)M->layers[0].attn_norm,
+                        S->xT, reinterpret_cast<__nv_bfloat16*>(S->xn), S->ssq, rows_per));
+    ctx->launches++;
+  }
+  int tiles = (int)ceil_div(hid, S->embed_rows_per_cta);        // slots of S->ssq the last producer wrote
+  auto inv_scale = [&]() { InvScale iv; iv.ssq = S->ssq; iv.tiles = tiles; iv.n = hid; iv.eps = c.rms_eps; return iv; };
+  for (int l = 0; l < L; ++l) {
+    LayerWeights& W = M->layers[l];
+    void* kv_layer = reinterpret_cast<char*>(S->kv) + (int64_t)l * S->kv_layer_stride * M->esz;
+    {  // q/k/v projections (norm scale on the accumulators) + RoPE + KV append
+      GemvParams p = gemv_params(S, W.wqkv, M->m_qkv, S->p_qkv, S->xn);
+      p.epi = EPI_QKV_ROPE; p.inv = inv_scale();
+      p.q_out = S->qbuf; p.q_pitch = S->q_pitch;
+      p.kv_layer = kv_layer; p.kv_batch_stride = S->kv_batch_stride; p.kv_head_stride = S->kv_head_stride;
+      p.inv_freq = M->inv_freq; p.pos = S->pos; p.Hl = M->Hl; p.KVl = M->KVl; p.D = M->D;
+      LMB_TRY(gemv_launch(ctx, dt, p, st));
+    }
+    {
+      AttnParams a;
+      a.q = S->qbuf; a.q_pitch = S->q_pitch; a.kv_layer = kv_layer;
+      a.kv_batch_stride = S->kv_batch_stride; a.kv_head_stride = S->kv_head_stride;
+      a.B = B; a.KVl = M->KVl; a.G = M->G; a.D = M->D; a.pos = S->pos;
+      a.keys_per_cta = S->keys_per_cta; a.nsplit = S->nsplit;
+      a.scale = 1.0f / sqrtf((float)M->D);
+      a.part_o = S->part_o; a.part_ml = S->part_ml; a.out = S->attn_out; a.out_tiled_bp = S->Bp;
+      a.counters = S->attn_counters;
+      LMB_TRY(attn_decode_launch(ctx, dt, a, st));
+    }
+    {  // o_proj + all-reduce + residual add + what the MLP's norm needs
+      GemvParams p = gemv_params(S, W.wo, M->m_o, S->p_o, S->attn_out);
+      p.epi = EPI_RESID_NORM;
+      p.rn.x = S->xT; p.rn.gain = W.ffn_norm; p.rn.xg = S->xn; p.rn.ssq = S->ssq;
+      p.push = peer_push(S, 2 * l);
+      gemv_prefetch_next(p, ctx, dt, W.wgu, M->m_gu.rows, M->m_gu.K, S->p_gu);
+      LMB_TRY(gemv_launch(ctx, dt, p, st));
+      tiles = gemv_plan_ctas(S->p_o, M->m_o.rows);
+    }
+    {  // gate/up (norm scale on the accumulators) + SiLU gate
+      GemvParams p = gemv_params(S, W.wgu, M->m_gu, S->p_gu, S->xn);
+      p.epi = EPI_SILU_GATE; p.inv = inv_scale(); p.act = S->act; p.n_act = M->inter_l;
+      gemv_prefetch_next(p, ctx, dt, W.wdown, M->m_down.rows, M->m_down.K, S->p_down);
+      LMB_TRY(gemv_launch(ctx, dt, p, st));
+    }
+    {  // down_proj + all-reduce + residual add + what the next norm (next layer's, or the final one) needs
+      GemvParams p = gemv_params(S, W.wdown, M->m_down, S->p_down, S->act);
+      p.epi = EPI_RESID_NORM;
+      p.rn.x = S->xT; p.rn.gain = l + 1 < L ? M->layers[l + 1].attn_norm : M->final_norm; p.rn.xg = S->xn; p.rn.ssq = S->ssq;
+      p.rn.capture = S->capture_on ? S->capture + (int64_t)l * B * hid : nullptr;
+      p.push = peer_push(S, 2 * l + 1);
+      if (l + 1 < L) gemv_prefetch_next(p, ctx, dt, M->layers[l + 1].wqkv, M->m_qkv.rows, M->m_qkv.K, S->p_qkv);
+      else if (with_head) gemv_prefetch_next(p, ctx, dt, M->lm_head, M->m_head.rows, M->m_head.K, S->p_head);
+      LMB_TRY(gemv_launch(ctx, dt, p, st));
+      tiles = gemv_plan_ctas(S->p_down, M->m_down.rows);
+    }
+  }
+  if (with_head) {
+    GemvParams p = gemv_params(S, M->lm_head, M->m_head, S->p_head, S->xn);
+    p.epi = EPI_STORE_F32; p.inv = inv_scale(); p.out = S->logits; p.out_pitch = S->logits_pitch;
+    LMB_TRY(gemv_launch(ctx, dt, p, st));
+    LMB_CUDA(launch_k(argmax_step_kernel, dim3(B), dim3(kArgmaxThreads), 0, st, (const float*)S->logits, S->logits_pitch, c.vocab,
+                      S->tokens, S->tok_hist, (const int*)S->step_ctr, B));
+    ctx->launches++;
+  }
+  LMB_CUDA(launch_k(advance_kernel, dim3(1), dim3(1), 0, st, S->pos, S->step_ctr, ctx->peer_n > 1 ? ctx->peer_step : (unsigned long long*)nullptr));
+  ctx->launches++;
+  return LMB200_OK;
+}
+
 // One decode step of the Whisper TextDecoder with cached self attention and cross attention
 // (build_decode_step!, src/Whisper.jl:679-742): per layer LayerNorm -> q/k/v (bias, head_dim^-0.25
 // on q and k, no RoPE) + cache append -> attention over [0, pos] -> out_proj -> LayerNorm ->
@@ -1254,6 +1420,7 @@ int32_t enqueue_whisper_step_t(Session* S, cudaStream_t st, bool with_head) {
 }
 
 int32_t enqueue_step(Session* S, cudaStream_t st, bool with_head) {
+  if (S->fused) return enqueue_step_fused(S, st, with_head);
   if (S->m->cfg.arch == LMB200_ARCH_WHISPER_DECODER)
     return S->m->cfg.dtype == LMB200_BF16 ? enqueue_whisper_step_t<__nv_bfloat16>(S, st, with_head)
                                           : enqueue_whisper_step_t<float>(S, st, with_head);
@@ -1361,6 +1528,24 @@ extern "C" int32_t lmb200_session_create(lmb200_model hm, int32_t batch, int32_t
   };
   plan(S->p_qkv, M->m_qkv); plan(S->p_o, M->m_o); plan(S->p_gu, M->m_gu); plan(S->p_down, M->m_down);
   plan(S->p_head, M->m_head);
+  {
+    // The fused step (LMB200_FUSED_STEP=0 switches it off for A/B runs): bf16 Llama / Phi-3 on the tcgen05
+    // GEMV, every row group of the two row-parallel projections resident at once, and under tensor
+    // parallelism the peer regions mapped and large enough for n bf16 partials of [hidden][Bp].
+    const char* fe = getenv("LMB200_FUSED_STEP");
+    bool fused = !(fe && atoi(fe) == 0) && !whisper && c.dtype == LMB200_BF16 && gemv_variant() == GEMV_TCGEN05 && c.hidden % 8 == 0 &&
+                 ceil_div(c.hidden, 32 * ceil_div(c.hidden, 32 * 256)) <= 256;
+    if (fused && c.tp_size > 1 && !M->tp_solo)
+      fused = ctx->peer_n == c.tp_size && (int64_t)c.tp_size * c.hidden * S->Bp * 2 <= kPeerBufFloats * 4 &&
+              (unsigned long long)2 * c.n_layers + 1 < kPeerEpochStride;
+    if (fused) {
+      const GemvPlan po = gemv_plan_resid(ctx, batch, M->m_o.rows, M->m_o.K), pd = gemv_plan_resid(ctx, batch, M->m_down.rows, M->m_down.K);
+      if (po.cluster >= 1 && pd.cluster >= 1) { S->p_o = po; S->p_down = pd; }
+      else fused = false;
+    }
+    S->fused = fused;
+    S->embed_rows_per_cta = 32 * (int)ceil_div(c.hidden, 32 * 256);
+  }
   int64_t po, pml;
   attn_plan(ctx, batch, M->KVl, M->G, M->D, S->cap, &S->keys_per_cta, &S->nsplit, &po, &pml);
   if (whisper) {
@@ -1399,6 +1584,10 @@ extern "C" int32_t lmb200_session_create(lmb200_model hm, int32_t batch, int32_t
   alloc((void**)&S->part_o, po * 4);
   alloc((void**)&S->part_ml, pml * 4);
   alloc((void**)&S->attn_counters, (int64_t)S->B * M->KVl * 4);
+  if (S->fused) {
+    alloc((void**)&S->xT, (int64_t)round_up(c.hidden, 128) * S->Bp * 4);
+    alloc((void**)&S->ssq, (int64_t)256 * 32 * 4);
+  }
   if (rc == LMB200_OK && cudaStreamSynchronize(ctx->stream) != cudaSuccess) rc = fail(LMB200_ECUDA, "session_create: sync failed");
   if (rc != LMB200_OK) { lmb200_session_destroy(reinterpret_cast<lmb200_session>(S)); return rc; }
   *out = reinterpret_cast<lmb200_session>(S);
@@ -1416,6 +1605,7 @@ extern "C" int32_t lmb200_session_destroy(lmb200_session h) {
   cudaFree(S->attn_out); cudaFree(S->act); cudaFree(S->tokens); cudaFree(S->pos); cudaFree(S->step_ctr);
   cudaFree(S->tok_hist); cudaFree(S->prompt); cudaFree(S->gemv_partials); cudaFree(S->gemv_counters);
   cudaFree(S->part_o); cudaFree(S->part_ml); cudaFree(S->attn_counters); cudaFree(S->prefill_buf); cudaFree(S->capture);
+  cudaFree(S->xT); cudaFree(S->ssq);
   S->magic = 0;
   delete S;
   return LMB200_OK;

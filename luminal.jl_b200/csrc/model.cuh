@@ -111,6 +111,12 @@ struct Session {
   int cross_cap = 0;
   int64_t cross_head_stride = 0, cross_batch_stride = 0, cross_layer_stride = 0;
   int cross_keys_per_cta = 0, cross_nsplit = 0;
+  // fused step (bf16 Llama): the row-parallel projections do the all-reduce, the residual add and the
+  // RMSNorm preparation in their epilogue, the other projections apply the norm's scale in theirs
+  bool fused = false;
+  float* xT = nullptr;          // residual stream [hidden][Bp] float32 (batch fastest)
+  float* ssq = nullptr;         // [256][32] per-CTA sums of squares of the residual rows
+  int embed_rows_per_cta = 32;
   float* capture = nullptr;     // [L][B][hidden] when enabled
   bool capture_on = false;
   cudaGraphExec_t graph_full = nullptr;
