@@ -363,7 +363,11 @@ def run_decode(args):
                 print(json.dumps({"error": "tensor-parallel parity check failed", "tp_parity": parity}))
             raise SystemExit(3)
     cfg = dict(CFG, n_layers=args.layers or CFG["n_layers"])
-    model = L.Model(dev, dtype="bf16", tp_size=world, tp_rank=rank, **cfg)
+    tp_size = world
+    if args.solo_shard > 1 and world == 1:
+        os.environ["LMB200_TP_SOLO"] = "1"
+        tp_size = args.solo_shard
+    model = L.Model(dev, dtype="bf16", tp_size=tp_size, tp_rank=rank, **cfg)
     model.init_random(1234, 0.02)
     sess = L.Session(model, BATCH, MAX_CTX)
     sess.fill_kv_random(warm_start, seed=1234)
@@ -425,8 +429,8 @@ def run_decode(args):
     # ---- dominant kernel alone: split-KV decode attention, one launch per layer ------------------
     peaks = load_peaks()
     T_mid = ctx_start + steps // 2
-    Hl = CFG["n_heads"] // world
-    KVl = CFG["n_kv_heads"] // world
+    Hl = CFG["n_heads"] // tp_size
+    KVl = CFG["n_kv_heads"] // tp_size
     Dh = CFG["hidden"] // CFG["n_heads"]
     q = torch.randn(BATCH, Hl * Dh, device="cuda").to(torch.bfloat16)
     o = torch.empty_like(q)
@@ -456,7 +460,7 @@ def run_decode(args):
                         "max_ms_per_step": regions[-1] / steps},
             "config": {"workload": wl["workload"], "name": args.config, "batch": BATCH,
                        "context": [ctx_start, ctx_start + steps],
-                       "layers": cfg["n_layers"], "parallelism": f"tp{world}",
+                       "layers": cfg["n_layers"], "parallelism": f"tp{world}" if tp_size == world else f"rank 0 of tp{tp_size} alone (profiling)",
                        "l2": "inputs larger than L2: every step streams this rank's weights and KV cache "
                              f"({step_bytes / 1e9:.1f} GB) once"},
             "e2e": {"value": BATCH * steps / (e2e_ms * 1e-3), "unit": "tokens/s",
@@ -703,6 +707,9 @@ def main():
     ap.add_argument("--prefill", action="store_true", help="phi3_mini: also time the 2048-token prompt phase")
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (invalid as a result)")
     ap.add_argument("--batch", type=int, default=0, help="debug only: another batch size (invalid as a result)")
+    ap.add_argument("--solo-shard", type=int, default=0,
+                    help="profiling only: run rank 0's shard of an N-way tensor-parallel model alone on one GPU, without the "
+                         "exchange (kernel sizes are the rank's, the results are not the model's; invalid as a result)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

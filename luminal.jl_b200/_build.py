@@ -34,17 +34,27 @@ def _stale() -> bool:
     return any(os.path.getmtime(d) > t for d in deps if os.path.exists(d))
 
 
-def build_library(force: bool = False, verbose: bool = False) -> str:
-    """Compile every .cu under csrc/ and link the shared library.  Returns its path."""
-    if not force and not _stale():
+TRACE_LIB = os.path.join(HERE, "build_trace", "libluminal_b200_trace.so")
+
+
+def build_library(force: bool = False, verbose: bool = False, trace: bool = False) -> str:
+    """Compile every .cu under csrc/ and link the shared library.  Returns its path.
+
+    trace=True builds a second library, build_trace/libluminal_b200_trace.so, with -DLMB_GEMV_TRACE
+    -DLMB_FLASH_TRACE: the GEMV and flash kernels then stamp the SM clock at their phase boundaries
+    into a device array that lmb200_debug_gemv_trace / lmb200_debug_flash_trace copy out
+    (luminal.jl_b200/trace.py reads them).  The product library never carries the stamps."""
+    lib = TRACE_LIB if trace else LIB
+    if not trace and not force and not _stale():
         return LIB
-    objdir = os.path.join(HERE, "build")
+    objdir = os.path.join(HERE, "build_trace" if trace else "build")
     os.makedirs(objdir, exist_ok=True)
     nvcc = _nvcc()
+    extra = ["-DLMB_GEMV_TRACE", "-DLMB_FLASH_TRACE"] if trace else []
 
     def compile_one(src):
         obj = os.path.join(objdir, src.replace(".cu", ".o"))
-        cmd = [nvcc, *NVCC_FLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
+        cmd = [nvcc, *NVCC_FLAGS, *extra, "-c", os.path.join(CSRC, src), "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas")
             cmd.insert(2, "-v")
@@ -57,13 +67,13 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
 
     with ThreadPoolExecutor(max_workers=8) as pool:
         objs = list(pool.map(compile_one, _sources()))
-    cmd = [nvcc, "-shared", "-o", LIB, *objs, "-gencode", "arch=compute_100a,code=sm_100a",
+    cmd = [nvcc, "-shared", "-o", lib, *objs, "-gencode", "arch=compute_100a,code=sm_100a",
            "-Xcompiler", "-fPIC", "-lcudart_static", "-ldl", "-lpthread", "-lrt"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
-    return LIB
+    return lib
 
 
 if __name__ == "__main__":
-    print(build_library(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build_library(force="--force" in sys.argv, verbose="-v" in sys.argv, trace="--trace" in sys.argv))
