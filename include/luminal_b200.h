@@ -114,6 +114,17 @@ int32_t lmb200_ew(lmb200_ctx ctx, int32_t opcode, float* out_dptr, int32_t out_r
                   const float* a, int32_t a_rank, const int64_t* a_dims,
                   const float* b, int32_t b_rank, const int64_t* b_dims,
                   const float* c, int32_t c_rank, const int64_t* c_dims);
+/* One element-wise fusion group (what compile() makes of an element-wise node and the single-consumer
+ * element-wise nodes and constants feeding it): a postfix program over n_inputs float32 tensors,
+ * each broadcast to the output by the rule above.  ops[i] / args[i]: 0 push input (args = its index),
+ * 1 push constant (args = the value), 2 add, 3 mul, 4 mod, 5 less-than, 6 max, 7 log2, 8 exp2, 9 sin,
+ * 10 cos, 11 sqrt, 12 recip, 13 relu, 14 a*b+c, 15 max(a+b, 0).  in_dims holds the inputs' dims one after
+ * the other.  At most 8 inputs, 64 instructions, stack depth 16.  Every operation is rounded on its own,
+ * so the result equals running the nodes one by one.
+ * Replaces FusedElementwiseOp: src/Compiler.jl:196-215, 323-357, src/Execution.jl:552-563. */
+int32_t lmb200_fused_ew(lmb200_ctx ctx, float* out_dptr, int32_t out_rank, const int64_t* out_dims,
+                        int32_t n_inputs, const float* const* inputs, const int32_t* in_ranks,
+                        const int64_t* in_dims, int32_t n_instr, const int32_t* ops, const float* args);
 /* SumReduce / MaxReduce over one 0-based axis, axis dropped.  src/Execution.jl:232-233, 306-339 */
 int32_t lmb200_reduce(lmb200_ctx ctx, int32_t kind, float* out_dptr, const float* in_dptr,
                       int32_t rank, const int64_t* dims, int32_t axis);
@@ -301,6 +312,13 @@ int32_t lmb200_decode_step(lmb200_session session, const int32_t* tokens_in,
  * tokens_out [n_steps, batch] host (NULL to skip the copy back). */
 int32_t lmb200_decode_n(lmb200_session session, const int32_t* first_tokens, int32_t n_steps,
                         int32_t* tokens_out);
+/* The generation loop with the reference's two exits (src/Decoding.jl:91-130): greedy steps until
+ * every sequence has produced eot_token (:126-129) or max_steps, capped by the positions left in the
+ * session, have run (:93-95).  A sequence that is done keeps emitting eot_token while the others go
+ * on.  first_tokens [batch] host (NULL = continue); tokens_out [max_steps, batch] host receives
+ * *steps_done rows, the last of which is the step in which the last sequence finished. */
+int32_t lmb200_decode_until(lmb200_session session, const int32_t* first_tokens, int32_t max_steps,
+                            int32_t eot_token, int32_t* tokens_out, int32_t* steps_done);
 /* Same loop, asynchronous on the context's stream: tokens come from and go to device memory
  * ([batch] int32 in, [n_steps,batch] int32 out, either may be NULL), no host synchronisation. */
 int32_t lmb200_decode_n_device(lmb200_session session, const int32_t* first_tokens_dptr,

@@ -56,6 +56,7 @@ SIGNATURES = {
     "lmb200_upload": [_u64, _vp, _i32, _vp, _i32, _pi64, _i32],
     "lmb200_download": [_u64, _vp, _vp, _i32, _i32, _pi64, _i32],
     "lmb200_ew": [_u64, _i32, _vp, _i32, _pi64, _vp, _i32, _pi64, _vp, _i32, _pi64, _vp, _i32, _pi64],
+    "lmb200_fused_ew": [_u64, _vp, _i32, _pi64, _i32, C.POINTER(_vp), _pi32, _pi64, _i32, _pi32, _pf32],
     "lmb200_reduce": [_u64, _i32, _vp, _vp, _i32, _pi64, _i32],
     "lmb200_matmul": [_u64, _vp, _vp, _i32, _pi64, _vp, _i32, _pi64],
     "lmb200_permute": [_u64, _vp, _vp, _i32, _pi64, _pi32],
@@ -99,6 +100,7 @@ SIGNATURES = {
     "lmb200_prefill": [_u64, _vp, _i32, _vp],
     "lmb200_decode_step": [_u64, _vp, _vp, _vp],
     "lmb200_decode_n": [_u64, _vp, _i32, _vp],
+    "lmb200_decode_until": [_u64, _vp, _i32, _i32, _vp, _pi32],
     "lmb200_decode_n_device": [_u64, _vp, _i32, _vp],
     "lmb200_session_step_bytes": [_u64, _i32, _pi64],
     "lmb200_decode_attention_splitkv": [_u64, _i32, _vp, _vp, _i32],

@@ -93,9 +93,10 @@ def _stack_depth(code):
 
 
 # the chain silu(gate) * up as NN.Mlp builds it (src/NN.jl:246-249, src/HighLevelOps.jl:153-160):
-# gate * (1 * recip(1 + exp2((gate * -1) * (1/ln2)))) * up
-_SILU_GATE = [(PUSH_IN, 0), (PUSH_CONST, 1.0), (PUSH_CONST, 1.0), (PUSH_IN, 0), (PUSH_CONST, -1.0), (3, 0),
-              (PUSH_CONST, _INV_LN2), (3, 0), (8, 0), (2, 0), (12, 0), (3, 0), (3, 0), (PUSH_IN, 1), (3, 0)]
+# (gate * (1 * recip(exp2((gate * -1) * (1/ln2)) + 1))) * up   -- a Number on the left of + or * goes to the right
+# (src/HighLevelOps.jl:46, 56), 1 / x is constant(1) * recip(x) (:63-65)
+_SILU_GATE = [(PUSH_IN, 0), (PUSH_CONST, 1.0), (PUSH_IN, 0), (PUSH_CONST, -1.0), (3, 0), (PUSH_CONST, _INV_LN2), (3, 0),
+              (8, 0), (PUSH_CONST, 1.0), (2, 0), (12, 0), (3, 0), (3, 0), (PUSH_IN, 1), (3, 0)]
 _MUL_ADD = ([(PUSH_IN, 0), (PUSH_IN, 1), (3, 0), (PUSH_IN, 2), (2, 0)], (0, 1, 2))
 _ADD_MUL = ([(PUSH_IN, 0), (PUSH_IN, 1), (PUSH_IN, 2), (3, 0), (2, 0)], (1, 2, 0))       # c + a*b
 _ADD_RELU = [(PUSH_IN, 0), (PUSH_IN, 1), (2, 0), (13, 0)]
@@ -220,6 +221,64 @@ class CompiledGraph:
     def __init__(self, graph, device=None, fuse=True):
         self.graph, self.dev = graph, device or get_device()
         self.results, self.steps = {}, []
+        plan = plan_graph(graph, fuse)
+        for nid, what in plan:                       # buffers first: a step may read a constant planned after it
+            self.results[nid] = self.dev.empty(graph.shapes[nid - 1])
+        for nid, what in plan:
+            buf = self.results[nid]
+            if what[0] == "constant":
+                _lib.call("lmb200_upload", self.dev.handle, C.c_void_p(buf.ptr), _lib.F32,
+                          np.asarray([what[1]], np.float32).ctypes.data_as(C.c_void_p), 0, _lib.dims(()), 0)
+            elif what[0] != "input":
+                self.steps.append((what, buf))
+        # data pre-loaded into the graph (load_weights!, src/Weights.jl:60-91; the sinusoid table of the Whisper
+        # encoder) fills its input buffers once, here; the inputs of a call may still overwrite them
+        from .device import DeviceArray
+        for (node_id, out_idx), data in graph.tensors.items():
+            if out_idx == 1 and node_id in self.results:
+                a = data.numpy() if isinstance(data, DeviceArray) else np.ascontiguousarray(np.asarray(data, dtype=np.float32))
+                buf = self.results[node_id]
+                _lib.call("lmb200_upload", self.dev.handle, C.c_void_p(buf.ptr), _lib.F32, a.ctypes.data_as(C.c_void_p),
+                          len(buf.shape), _lib.dims(buf.shape), 0)
+
+    # -- execution -------------------------------------------------------------------------------
+    def __call__(self, inputs, device=None):
+        from .execution import run_op
+        for node_id, data in inputs.items():
+            buf = self.results[node_id]
+            a = np.ascontiguousarray(np.asarray(data, dtype=np.float32))
+            if a.size != buf.size:
+                raise ValueError(f"Input size mismatch for node {node_id}: expected {buf.size}, got {a.size}")
+            _lib.call("lmb200_upload", self.dev.handle, C.c_void_p(buf.ptr), _lib.F32, a.ctypes.data_as(C.c_void_p),
+                      len(buf.shape), _lib.dims(buf.shape), 0)
+        h = self.dev.handle
+        R = self.results
+        for what, out in self.steps:
+            kind = what[0]
+            if kind == "op":
+                run_op(self.dev, what[1], out, [R[i] for i in what[2]])
+            elif kind == "fused":
+                run_fused(self.dev, what[1], out, [R[i] for i in what[2]])
+            elif kind == "silu_gate":
+                _lib.call("lmb200_silu_gate", h, _p(out), _p(R[what[1]]), _p(R[what[2]]), out.size)
+            elif kind == "rmsnorm":
+                _, x, w, rows, n, eps = what
+                _lib.call("lmb200_rmsnorm_scale", h, _p(out), _p(R[x]), _p(R[w]), rows, n, eps)
+            elif kind == "layernorm":
+                _, x, w, b, rows, n, eps = what
+                _lib.call("lmb200_layernorm", h, _p(out), _p(R[x]), _p(R[w]), _p(R[b]) if b is not None else None, rows, n, eps)
+        return self.results
+
+    def kernel_count(self):
+        """Kernels one call launches (the input uploads aside)."""
+        return len(self.steps)
+
+
+class _Planner:
+    """Host-only planning of compile(): which nodes become which steps.  plan_graph() below is its entry."""
+
+    def __init__(self, graph, fuse=True):
+        self.plan = plan = []
         n = len(graph.nodes)
         edges = [0] * (n + 1)
         for node in graph.nodes:
@@ -230,7 +289,7 @@ class CompiledGraph:
         swallowed = set()             # interior nodes of a recognised norm: no step, no buffer
         if fuse:
             self._find_norms(graph, edges, absorbed, swallowed)
-        plan = []
+            fusible -= set(absorbed) | swallowed      # a recognised norm is a step of its own: a leaf for the groups around it
         for nid, node in enumerate(graph.nodes, start=1):
             op = node.op
             if nid in swallowed:
@@ -256,16 +315,6 @@ class CompiledGraph:
                             plan.append((m, ("op", mop, [i for i, _, _ in graph.nodes[m - 1].inputs])))
                 else:
                     plan.append((nid, self._specialise(code, leaves)))
-        for nid, what in plan:                       # buffers first (a step's inputs may come later in id order only for constants)
-            self.results[nid] = self.dev.empty(graph.shapes[nid - 1])
-        for nid, what in plan:
-            buf = self.results[nid]
-            if what[0] == "constant":
-                _lib.call("lmb200_upload", self.dev.handle, C.c_void_p(buf.ptr), _lib.F32,
-                          np.asarray([what[1]], np.float32).ctypes.data_as(C.c_void_p), 0, _lib.dims(()), 0)
-            elif what[0] != "input":
-                self.steps.append((what, buf))
-
     # -- planning helpers ------------------------------------------------------------------------
     @staticmethod
     def _group_nodes(graph, terminal, fusible):
@@ -341,37 +390,11 @@ class CompiledGraph:
             return None                             # RMS scale with a bias: not a layer the reference builds
         return ("rmsnorm", x, gain, int(np.prod(shape[:-1])), n, eps), interior
 
-    # -- execution -------------------------------------------------------------------------------
-    def __call__(self, inputs, device=None):
-        from .execution import run_op
-        for node_id, data in inputs.items():
-            buf = self.results[node_id]
-            a = np.ascontiguousarray(np.asarray(data, dtype=np.float32))
-            if a.size != buf.size:
-                raise ValueError(f"Input size mismatch for node {node_id}: expected {buf.size}, got {a.size}")
-            _lib.call("lmb200_upload", self.dev.handle, C.c_void_p(buf.ptr), _lib.F32, a.ctypes.data_as(C.c_void_p),
-                      len(buf.shape), _lib.dims(buf.shape), 0)
-        h = self.dev.handle
-        R = self.results
-        for what, out in self.steps:
-            kind = what[0]
-            if kind == "op":
-                run_op(self.dev, what[1], out, [R[i] for i in what[2]])
-            elif kind == "fused":
-                run_fused(self.dev, what[1], out, [R[i] for i in what[2]])
-            elif kind == "silu_gate":
-                _lib.call("lmb200_silu_gate", h, _p(out), _p(R[what[1]]), _p(R[what[2]]), out.size)
-            elif kind == "rmsnorm":
-                _, x, w, rows, n, eps = what
-                _lib.call("lmb200_rmsnorm_scale", h, _p(out), _p(R[x]), _p(R[w]), rows, n, eps)
-            elif kind == "layernorm":
-                _, x, w, b, rows, n, eps = what
-                _lib.call("lmb200_layernorm", h, _p(out), _p(R[x]), _p(R[w]), _p(R[b]) if b is not None else None, rows, n, eps)
-        return self.results
 
-    def kernel_count(self):
-        """Kernels one call launches (the input uploads aside)."""
-        return len(self.steps)
+def plan_graph(graph, fuse=True):
+    """[(node id, step)] in node order; step[0] is one of "input", "constant", "op", "fused", "silu_gate",
+    "rmsnorm", "layernorm".  Needs no GPU."""
+    return _Planner(graph, fuse).plan
 
 
 def run_fused(dev, code, out, ins):
@@ -392,4 +415,4 @@ def compile(graph, device=None, fuse=True):     # noqa: A001  (the reference's n
     return CompiledGraph(graph, device, fuse)
 
 
-__all__ = ["compile", "CompiledGraph", "fusible_intermediates", "group_program", "is_elementwise", "run_fused"]
+__all__ = ["compile", "CompiledGraph", "plan_graph", "fusible_intermediates", "group_program", "is_elementwise", "run_fused"]

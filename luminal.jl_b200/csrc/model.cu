@@ -421,8 +421,11 @@ __global__ void scatter_kv_kernel(WT* kv, int64_t batch_stride, int64_t head_str
 
 // greedy token: first maximum of the logits row; also logs it for the device-resident loop
 constexpr int kArgmaxThreads = 1024;
+// `stop` (device: [0] the end-of-text id or -1, [1] how many sequences have produced it, [2 + b] whether
+// sequence b has): once a sequence has produced the end-of-text token it keeps emitting it, the batch
+// form of the reference's `break` at EOT (src/Decoding.jl:126-129).
 __global__ void __launch_bounds__(kArgmaxThreads) argmax_step_kernel(const float* logits, int pitch, int n, int* tokens,
-                                                                     int* hist, const int* step_ctr, int B) {
+                                                                     int* hist, const int* step_ctr, int B, int* stop) {
   __shared__ float sv[kArgmaxThreads / 32];
   __shared__ int si[kArgmaxThreads / 32];
   pdl_launch_dependents();
@@ -464,6 +467,11 @@ __global__ void __launch_bounds__(kArgmaxThreads) argmax_step_kernel(const float
       take(v, i);
     }
     if (tid == 0) {
+      const int eot = stop ? stop[0] : -1;
+      if (eot >= 0) {
+        if (stop[2 + b]) bi = eot;
+        else if (bi == eot) { stop[2 + b] = 1; atomicAdd(&stop[1], 1); }
+      }
       tokens[b] = bi;
       if (hist) hist[(int64_t)(*step_ctr) * B + b] = bi;
     }
@@ -1207,7 +1215,7 @@ int32_t enqueue_step_t(Session* S, cudaStream_t st, bool with_head) {
     p.epi = EPI_STORE_F32; p.out = S->logits; p.out_pitch = S->logits_pitch;
     LMB_TRY(gemv_launch(ctx, dt, p, st));
     LMB_CUDA(launch_k(argmax_step_kernel, dim3(B), dim3(kArgmaxThreads), 0, st, (const float*)S->logits, S->logits_pitch, c.vocab,
-                      S->tokens, S->tok_hist, (const int*)S->step_ctr, B));
+                      S->tokens, S->tok_hist, (const int*)S->step_ctr, B, S->stop));
     ctx->launches++;
   }
   LMB_CUDA(launch_k(advance_kernel, dim3(1), dim3(1), 0, st, S->pos, S->step_ctr, ctx->peer_n > 1 ? ctx->peer_step : (unsigned long long*)nullptr));
@@ -1317,7 +1325,7 @@ int32_t enqueue_step_fused(Session* S, cudaStream_t st, bool with_head) {
     p.epi = EPI_STORE_F32; p.inv = inv_scale(); p.out = S->logits; p.out_pitch = S->logits_pitch;
     LMB_TRY(gemv_launch(ctx, dt, p, st));
     LMB_CUDA(launch_k(argmax_step_kernel, dim3(B), dim3(kArgmaxThreads), 0, st, (const float*)S->logits, S->logits_pitch, c.vocab,
-                      S->tokens, S->tok_hist, (const int*)S->step_ctr, B));
+                      S->tokens, S->tok_hist, (const int*)S->step_ctr, B, S->stop));
     ctx->launches++;
   }
   LMB_CUDA(launch_k(advance_kernel, dim3(1), dim3(1), 0, st, S->pos, S->step_ctr, ctx->peer_n > 1 ? ctx->peer_step : (unsigned long long*)nullptr));
@@ -1411,7 +1419,7 @@ int32_t enqueue_whisper_step_t(Session* S, cudaStream_t st, bool with_head) {
     p.epi = EPI_STORE_F32; p.out = S->logits; p.out_pitch = S->logits_pitch;
     LMB_TRY(gemv_launch(ctx, dt, p, st));
     LMB_CUDA(launch_k(argmax_step_kernel, dim3(B), dim3(kArgmaxThreads), 0, st, (const float*)S->logits, S->logits_pitch, c.vocab,
-                      S->tokens, S->tok_hist, (const int*)S->step_ctr, B));
+                      S->tokens, S->tok_hist, (const int*)S->step_ctr, B, S->stop));
     ctx->launches++;
   }
   LMB_CUDA(launch_k(advance_kernel, dim3(1), dim3(1), 0, st, S->pos, S->step_ctr, (unsigned long long*)nullptr));
@@ -1442,7 +1450,7 @@ int32_t enqueue_head_bf16(Session* S, cudaStream_t st) {
   p.epi = EPI_STORE_F32; p.out = S->logits; p.out_pitch = S->logits_pitch;
   LMB_TRY(gemv_launch(ctx, c.dtype, p, st));
   LMB_CUDA(launch_k(argmax_step_kernel, dim3(B), dim3(kArgmaxThreads), 0, st, (const float*)S->logits, S->logits_pitch, c.vocab,
-                    S->tokens, S->tok_hist, (const int*)S->step_ctr, B));
+                    S->tokens, S->tok_hist, (const int*)S->step_ctr, B, S->stop));
   ctx->launches++;
   return LMB200_OK;
 }
@@ -1578,6 +1586,7 @@ extern "C" int32_t lmb200_session_create(lmb200_model hm, int32_t batch, int32_t
   alloc((void**)&S->tokens, (int64_t)batch * 4);
   alloc((void**)&S->pos, 4);
   alloc((void**)&S->step_ctr, 4);
+  alloc((void**)&S->stop, (int64_t)(2 + batch) * 4);
   alloc((void**)&S->tok_hist, (int64_t)(S->cap + 1) * batch * 4);
   alloc((void**)&S->gemv_partials, max_part * 4);
   alloc((void**)&S->gemv_counters, (int64_t)max_cnt * 4);
@@ -1587,6 +1596,10 @@ extern "C" int32_t lmb200_session_create(lmb200_model hm, int32_t batch, int32_t
   if (S->fused) {
     alloc((void**)&S->xT, (int64_t)round_up(c.hidden, 128) * S->Bp * 4);
     alloc((void**)&S->ssq, (int64_t)256 * 32 * 4);
+  }
+  if (rc == LMB200_OK) {
+    const int no_eot = -1;                                  // end-of-text stop disabled until lmb200_decode_until sets it
+    if (cudaMemcpyAsync(S->stop, &no_eot, 4, cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess) rc = fail(LMB200_ECUDA, "session_create: copy failed");
   }
   if (rc == LMB200_OK && cudaStreamSynchronize(ctx->stream) != cudaSuccess) rc = fail(LMB200_ECUDA, "session_create: sync failed");
   if (rc != LMB200_OK) { lmb200_session_destroy(reinterpret_cast<lmb200_session>(S)); return rc; }
@@ -1605,7 +1618,7 @@ extern "C" int32_t lmb200_session_destroy(lmb200_session h) {
   cudaFree(S->attn_out); cudaFree(S->act); cudaFree(S->tokens); cudaFree(S->pos); cudaFree(S->step_ctr);
   cudaFree(S->tok_hist); cudaFree(S->prompt); cudaFree(S->gemv_partials); cudaFree(S->gemv_counters);
   cudaFree(S->part_o); cudaFree(S->part_ml); cudaFree(S->attn_counters); cudaFree(S->prefill_buf); cudaFree(S->capture);
-  cudaFree(S->xT); cudaFree(S->ssq);
+  cudaFree(S->xT); cudaFree(S->ssq); cudaFree(S->stop);
   S->magic = 0;
   delete S;
   return LMB200_OK;
@@ -1842,6 +1855,67 @@ extern "C" int32_t lmb200_decode_n(lmb200_session h, const int32_t* first_tokens
   if (tokens_out)
     LMB_CUDA(cudaMemcpyAsync(tokens_out, S->tok_hist, (size_t)n_steps * S->B * 4, cudaMemcpyDeviceToHost, ctx->stream));
   LMB_CUDA(cudaStreamSynchronize(ctx->stream));
+  return check_device_error(ctx);
+}
+
+// Greedy steps until every sequence has produced `eot_token` or max_steps (capped by the session's context) have
+// run: the generation loop of src/Decoding.jl:91-130 with its two exits (EOT :126-129, the position cap :93-95).
+// The steps are CUDA-graph replays issued in short runs; after each run the host reads how many sequences are
+// done.  A finished sequence keeps emitting eot_token.  tokens_out: [max_steps, batch], filled for *steps_done rows.
+extern "C" int32_t lmb200_decode_until(lmb200_session h, const int32_t* first_tokens, int32_t max_steps, int32_t eot_token,
+                                       int32_t* tokens_out, int32_t* steps_done) {
+  Session* S = session_from(h);
+  if (!S) return LMB200_EINVAL;
+  LMB_REQUIRE(steps_done && max_steps >= 1, "decode_until: bad argument");
+  LMB_REQUIRE(eot_token >= 0 && eot_token < S->m->cfg.vocab, "decode_until: end-of-text id %d outside the vocabulary", eot_token);
+  LMB_TRY(tp_guard(S, "decode_until"));
+  Ctx* ctx = S->m->ctx;
+  LMB_CUDA(cudaSetDevice(ctx->device));
+  const int B = S->B;
+  int budget = S->max_ctx - S->host_pos;                 // the position cap
+  if (budget > max_steps) budget = max_steps;
+  *steps_done = 0;
+  if (budget <= 0) return fail(LMB200_ESTATE, "decode_until: position %d is at max_ctx %d", S->host_pos, S->max_ctx);
+  std::vector<int> init(2 + B, 0);
+  init[0] = eot_token;
+  LMB_CUDA(cudaMemcpyAsync(S->stop, init.data(), init.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
+  if (first_tokens) LMB_CUDA(cudaMemcpyAsync(S->tokens, first_tokens, (size_t)B * 4, cudaMemcpyHostToDevice, ctx->stream));
+  LMB_CUDA(cudaMemsetAsync(S->step_ctr, 0, 4, ctx->stream));
+  int32_t rc = LMB200_OK;
+  int done = 0;
+  const int kRun = 8;                                     // replays between two looks at the count
+  while (done < budget && rc == LMB200_OK) {
+    const int n = budget - done < kRun ? budget - done : kRun;
+    for (int i = 0; i < n && rc == LMB200_OK; ++i) rc = run_step(S, true);
+    if (rc != LMB200_OK) break;
+    done += n;
+    int finished = 0;
+    if (cudaMemcpyAsync(&finished, S->stop + 1, 4, cudaMemcpyDeviceToHost, ctx->stream) != cudaSuccess ||
+        cudaStreamSynchronize(ctx->stream) != cudaSuccess) { rc = fail(LMB200_ECUDA, "decode_until: readback failed"); break; }
+    if (finished >= B) break;
+  }
+  // the rows past the step in which the last sequence finished hold only end-of-text ids: trim them
+  std::vector<int32_t> hist((size_t)done * B);
+  if (rc == LMB200_OK && done > 0) {
+    if (cudaMemcpyAsync(hist.data(), S->tok_hist, hist.size() * 4, cudaMemcpyDeviceToHost, ctx->stream) != cudaSuccess ||
+        cudaStreamSynchronize(ctx->stream) != cudaSuccess) rc = fail(LMB200_ECUDA, "decode_until: readback failed");
+  }
+  const int no_eot = -1;
+  cudaMemcpyAsync(S->stop, &no_eot, 4, cudaMemcpyHostToDevice, ctx->stream);
+  cudaStreamSynchronize(ctx->stream);
+  if (rc != LMB200_OK) return rc;
+  int keep = done;
+  while (keep > 1) {
+    bool all_eot = true;
+    for (int b = 0; b < B && all_eot; ++b) all_eot = hist[(size_t)(keep - 1) * B + b] == eot_token && hist[(size_t)(keep - 2) * B + b] == eot_token;
+    if (!all_eot) break;
+    --keep;
+  }
+  if (keep < done) {                                      // the session goes back to the step after the last useful one
+    LMB_TRY(lmb200_session_set_position(h, S->host_pos - (done - keep)));
+  }
+  if (tokens_out) memcpy(tokens_out, hist.data(), (size_t)keep * B * 4);
+  *steps_done = keep;
   return check_device_error(ctx);
 }
 

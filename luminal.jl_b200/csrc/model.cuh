@@ -93,6 +93,7 @@ struct Session {
   int* tokens = nullptr;
   int* pos = nullptr;
   int* step_ctr = nullptr;
+  int* stop = nullptr;          // [0] end-of-text id or -1, [1] sequences that produced it, [2 + b] sequence b did
   int* tok_hist = nullptr;      // [cap][B]
   int* prompt = nullptr;        // staging for prefill
   int64_t prompt_cap = 0;

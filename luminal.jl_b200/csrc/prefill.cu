@@ -32,8 +32,6 @@ bool flash_tc_supported(int64_t D);
 
 namespace {
 
-constexpr int kGemmBN = 128;
-constexpr int kGemmStages = 6;
 constexpr int kGemmThreads = 6 * 32;
 constexpr int kUnitBytes = 32768;
 constexpr float kInvLn2 = 1.4426950408889634f;
@@ -191,11 +189,25 @@ struct TileOrder {
   }
 };
 
+// Shared-memory descriptor of a K-major operand tile whose rows are 128 bytes (64 bf16) in the 128-byte
+// swizzle a tensor map with CU_TENSOR_MAP_SWIZZLE_128B writes: groups of 8 rows are 1024 bytes apart
+// (stride byte offset), the leading byte offset is not used (1), layout type 2.  The tile starts on a
+// 1024-byte boundary; a K = 16 step inside the row advances the start address by 32 bytes.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
+  return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+
+// BN tokens per tile (128 or 256).  256 halves the number of MMA instructions and barrier round trips
+// per flop and doubles the reuse of each weight byte read from shared memory; its two accumulators
+// take all 512 TMEM columns.
+template <int BN>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap,
                                                                   int* err) {
   using namespace tc;
+  constexpr int kGemmBN = BN;
+  constexpr int kGemmStages = BN == 256 ? 4 : 6;
   constexpr int kABytes = kUnitBytes / 2;                 // 128 rows x 64 k: half a weight unit (its first / last 8 k-groups)
-  constexpr int kBBytes = kGemmBN * 128;                  // 128 tokens x 64 k, bf16
+  constexpr int kBBytes = kGemmBN * 128;                  // BN tokens x 64 k, bf16: one 128-byte swizzled row per token
   constexpr int kStage = kABytes + kBBytes;
   extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ __align__(8) uint64_t full[kGemmStages], empty[kGemmStages], acc_full[2], acc_empty[2];
@@ -224,8 +236,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const GemmPara
 
   if (warp == 5) {
     // producer: per step half a weight unit (bulk copy, already in the tensor core's layout) and the
-    // activations of 128 tokens x 64 k through a 3-D tensor map over the row-major [T, K] matrix seen
-    // as [k/8][token][8]: the box {8, 128, 8} lands as K-major core matrices, rows past T as zeros
+    // activations of BN tokens x 64 k through a 2-D tensor map over the row-major [T, K] matrix: the box
+    // {64, BN} lands as BN rows of 128 bytes in the 128-byte swizzle (one request per row instead of one
+    // per 16 bytes); rows past T and columns past K arrive as zeros
     int g = 0;
     for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
       int rg, tt_;
@@ -237,9 +250,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const GemmPara
           mbar_expect_tx(&full[s], (uint32_t)kStage);
           bulk_g2s(smem + s * kStage, p.W + ((int64_t)rg * KS + (st >> 1)) * 16384 + (st & 1) * 8192, (uint32_t)kABytes, &full[s]);
           asm volatile(
-              "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n" ::"r"(
+              "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(
                   smem_u32(smem + s * kStage + kABytes)),
-              "l"(reinterpret_cast<uint64_t>(&xmap)), "r"(0), "r"(tt_ * kGemmBN), "r"(st * 8), "r"(smem_u32(&full[s]))
+              "l"(reinterpret_cast<uint64_t>(&xmap)), "r"(st * 64), "r"(tt_ * kGemmBN), "r"(smem_u32(&full[s]))
               : "memory");
         }
         __syncwarp();
@@ -259,10 +272,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const GemmPara
         if (lane == 0) {
           const uint32_t sa = smem_u32(smem + s * kStage);
           const uint64_t adesc = smem_desc(sa, 2048, 128);
-          const uint64_t bdesc = smem_desc(sa + kABytes, kGemmBN * 16, 128);
+          const uint64_t bdesc = smem_desc_sw128(sa + kABytes);
 #pragma unroll
           for (int j = 0; j < 4; ++j)
-            mma_f16(tmem + buf * kGemmBN, adesc + (uint64_t)(j * (4096 >> 4)), bdesc + (uint64_t)(j * ((2 * kGemmBN * 16) >> 4)),
+            mma_f16(tmem + buf * kGemmBN, adesc + (uint64_t)(j * (4096 >> 4)), bdesc + (uint64_t)(j * (32 >> 4)),
                     kIdesc, (st == 0 && j == 0) ? 0u : 1u);
           commit(&empty[s]);
           if (st == NS - 1) commit(&acc_full[buf]);
@@ -302,7 +315,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const GemmPara
   }
 }
 
-constexpr size_t kGemmSmem = (size_t)kGemmStages * (kUnitBytes / 2 + kGemmBN * 128) + 1024;
+template <int BN>
+constexpr size_t gemm_smem() { return (size_t)(BN == 256 ? 4 : 6) * (kUnitBytes / 2 + BN * 128) + 1024; }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -327,17 +341,22 @@ int32_t gemm_launch(Ctx* ctx, const GemmParams& p, cudaStream_t st) {
   LMB_REQUIRE(p.K % 8 == 0 && p.ldx % 8 == 0 && (reinterpret_cast<uintptr_t>(p.X) & 15) == 0, "prefill gemm: K %d, row pitch %d", p.K, p.ldx);
   EncodeTiledFn enc = encode_tiled_fn();
   if (!enc) return fail(LMB200_ECUDA, "prefill gemm: cuTensorMapEncodeTiled is not available");
+  // 256-token tiles once there are enough tokens to fill them (LMB200_GEMM_BN=128 keeps the narrow tile for A/B runs)
+  static const int forced_bn = [] { const char* e = getenv("LMB200_GEMM_BN"); return e ? atoi(e) : 0; }();
+  const int BN = forced_bn == 128 || forced_bn == 256 ? forced_bn : (p.T >= 256 ? 256 : 128);
   CUtensorMap xmap;
-  const cuuint64_t dims[3] = {8, (cuuint64_t)p.T, (cuuint64_t)(p.K / 8)};
-  const cuuint64_t strides[2] = {(cuuint64_t)p.ldx * 2, 16};          // bytes, dims 1 and 2
-  const cuuint32_t box[3] = {8, (cuuint32_t)kGemmBN, 8};
-  const cuuint32_t estr[3] = {1, 1, 1};
-  const CUresult r = enc(&xmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<__nv_bfloat16*>(p.X), dims, strides, box, estr,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+  const cuuint64_t dims[2] = {(cuuint64_t)p.K, (cuuint64_t)p.T};
+  const cuuint64_t strides[1] = {(cuuint64_t)p.ldx * 2};               // bytes, dim 1
+  const cuuint32_t box[2] = {64, (cuuint32_t)BN};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(&xmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<__nv_bfloat16*>(p.X), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(LMB200_ECUDA, "prefill gemm: cuTensorMapEncodeTiled failed (%d)", (int)r);
-  const int64_t tiles = ceil_div(p.rows, 128) * ceil_div(p.T, kGemmBN);
-  gemm_tc_kernel<<<(unsigned)std::min<int64_t>(tiles, ctx->sm_count), kGemmThreads, kGemmSmem, st>>>(p, xmap, ctx->dev_err);
+  const int64_t tiles = ceil_div(p.rows, 128) * ceil_div(p.T, BN);
+  const unsigned grid = (unsigned)std::min<int64_t>(tiles, ctx->sm_count);
+  if (BN == 256) gemm_tc_kernel<256><<<grid, kGemmThreads, gemm_smem<256>(), st>>>(p, xmap, ctx->dev_err);
+  else gemm_tc_kernel<128><<<grid, kGemmThreads, gemm_smem<128>(), st>>>(p, xmap, ctx->dev_err);
   ctx->launches++;
   LMB_CUDA(cudaGetLastError());
   return LMB200_OK;
@@ -481,7 +500,8 @@ int32_t gemm_cross_kv(Ctx* ctx, const void* W, const __nv_bfloat16* X, int ldx, 
 }
 
 int32_t prefill_configure() {
-  LMB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmem));
+  LMB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemm_smem<128>()));
+  LMB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemm_smem<256>()));
   return LMB200_OK;
 }
 

@@ -52,6 +52,76 @@ __global__ void ew_kernel(int op, float* out, const float* a, const float* b, co
   }
 }
 
+// One element-wise fusion group per launch: a postfix program over up to 8 broadcast inputs,
+// interpreted per output element with every operation rounded to float32 on its own (no
+// contraction), so the result equals running the group's nodes one by one.
+// Stands in for FusedElementwiseOp (src/Compiler.jl:323-357, executor src/Execution.jl:552-563).
+constexpr int kFusedMaxInputs = 8, kFusedMaxInstr = 64, kFusedMaxStack = 16;
+enum FusedOp { F_PUSH_IN = 0, F_PUSH_CONST = 1, F_ADD = 2, F_MUL = 3, F_MOD = 4, F_LT = 5, F_MAX = 6, F_LOG2 = 7, F_EXP2 = 8,
+               F_SIN = 9, F_COS = 10, F_SQRT = 11, F_RECIP = 12, F_RELU = 13, F_FMA = 14, F_ADD_RELU = 15 };
+struct FusedProgram {
+  int n_in, n_instr, rank;
+  int64_t out_d[kMaxRank];
+  int64_t st[kFusedMaxInputs][kMaxRank];      // input strides over the output's axes (0 = broadcast)
+  const float* in[kFusedMaxInputs];
+  int op[kFusedMaxInstr];
+  float arg[kFusedMaxInstr];                  // PUSH_IN: input index; PUSH_CONST: the value
+};
+__global__ void fused_ew_kernel(float* out, const FusedProgram pg, int64_t total) {
+  for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total; o += (int64_t)gridDim.x * blockDim.x) {
+    int64_t off[kFusedMaxInputs];
+#pragma unroll
+    for (int i = 0; i < kFusedMaxInputs; ++i) off[i] = 0;
+    int64_t rem = o;
+    for (int k = pg.rank - 1; k >= 0; --k) {
+      const int64_t idx = rem % pg.out_d[k];
+      rem /= pg.out_d[k];
+#pragma unroll
+      for (int i = 0; i < kFusedMaxInputs; ++i)
+        if (i < pg.n_in) off[i] += idx * pg.st[i][k];
+    }
+    float stack[kFusedMaxStack];
+    int sp = 0;
+    for (int pc = 0; pc < pg.n_instr; ++pc) {
+      const int op = pg.op[pc];
+      if (op == F_PUSH_IN) { const int i = (int)pg.arg[pc]; stack[sp++] = pg.in[i][off[i]]; continue; }
+      if (op == F_PUSH_CONST) { stack[sp++] = pg.arg[pc]; continue; }
+      if (op == F_FMA) {
+        const float c = stack[--sp], b = stack[--sp], a = stack[sp - 1];
+        stack[sp - 1] = __fadd_rn(__fmul_rn(a, b), c);
+        continue;
+      }
+      if (op >= F_LOG2 && op <= F_RELU) {
+        const float a = stack[sp - 1];
+        float r = a;
+        switch (op) {
+          case F_LOG2: r = log2f(a); break;
+          case F_EXP2: r = exp2f(a); break;
+          case F_SIN: r = sinf(a); break;
+          case F_COS: r = cosf(a); break;
+          case F_SQRT: r = sqrtf(a); break;
+          case F_RECIP: r = 1.0f / a; break;
+          case F_RELU: r = fmaxf(a, 0.0f); break;
+        }
+        stack[sp - 1] = r;
+        continue;
+      }
+      const float b = stack[--sp], a = stack[sp - 1];
+      float r = 0.f;
+      switch (op) {
+        case F_ADD: r = __fadd_rn(a, b); break;
+        case F_MUL: r = __fmul_rn(a, b); break;
+        case F_MOD: r = fmodf(a, b); break;
+        case F_LT: r = a < b ? 1.0f : 0.0f; break;
+        case F_MAX: r = fmaxf(a, b); break;
+        case F_ADD_RELU: r = fmaxf(__fadd_rn(a, b), 0.0f); break;
+      }
+      stack[sp - 1] = r;
+    }
+    out[o] = stack[0];
+  }
+}
+
 // out[o] = in[offset + sum idx_k * stride_k] over the OUT shape: permute / expand / slice
 struct Gather {
   int rank;
@@ -340,6 +410,47 @@ extern "C" int32_t lmb200_ew(lmb200_ctx h, int32_t opcode, float* out, int32_t o
     LMB_TRY(bcast_strides(out_rank, out_dims, c_rank, c_dims, ix.sc, "ew c"));
   }
   ew_kernel<<<grid_for(total), 256, 0, ctx->stream>>>(opcode, out, a, binary ? b : nullptr, ternary ? c : nullptr, ix, total);
+  LAUNCHED();
+  return LMB200_OK;
+}
+
+extern "C" int32_t lmb200_fused_ew(lmb200_ctx h, float* out, int32_t out_rank, const int64_t* out_dims, int32_t n_inputs,
+                                   const float* const* inputs, const int32_t* in_ranks, const int64_t* in_dims,
+                                   int32_t n_instr, const int32_t* ops, const float* args) {
+  CTX_OR_FAIL();
+  LMB_REQUIRE(out && ops && args && in_ranks && n_inputs >= 0 && (n_inputs == 0 || (inputs && in_dims)), "fused_ew: null pointer");
+  LMB_REQUIRE(n_inputs <= kFusedMaxInputs, "fused_ew: %d inputs (at most %d)", n_inputs, kFusedMaxInputs);
+  LMB_REQUIRE(n_instr >= 1 && n_instr <= kFusedMaxInstr, "fused_ew: %d instructions (1..%d)", n_instr, kFusedMaxInstr);
+  FusedProgram pg{};
+  int64_t total, tmp;
+  LMB_TRY(check_dims(out_rank, out_dims, &total));
+  pg.rank = out_rank; pg.n_in = n_inputs; pg.n_instr = n_instr;
+  for (int i = 0; i < out_rank; ++i) pg.out_d[i] = out_dims[i];
+  const int64_t* d = in_dims;
+  for (int i = 0; i < n_inputs; ++i) {
+    LMB_REQUIRE(inputs[i], "fused_ew: input %d is null", i);
+    LMB_TRY(check_dims(in_ranks[i], d, &tmp));
+    LMB_TRY(bcast_strides(out_rank, out_dims, in_ranks[i], d, pg.st[i], "fused_ew input"));
+    pg.in[i] = inputs[i];
+    d += in_ranks[i];
+  }
+  int depth = 0;                                   // the program must be well-formed postfix: checked here, not on the device
+  for (int pc = 0; pc < n_instr; ++pc) {
+    const int op = ops[pc];
+    LMB_REQUIRE(op >= F_PUSH_IN && op <= F_ADD_RELU, "fused_ew: opcode %d at %d", op, pc);
+    int need = 0, push = 1;
+    if (op == F_PUSH_IN) LMB_REQUIRE(args[pc] >= 0 && (int)args[pc] < n_inputs && (float)(int)args[pc] == args[pc], "fused_ew: input index at %d", pc);
+    if (op == F_FMA) need = 3;
+    else if (op >= F_LOG2 && op <= F_RELU) need = 1;
+    else if (op >= F_ADD) need = 2;
+    LMB_REQUIRE(depth >= need, "fused_ew: stack underflow at instruction %d", pc);
+    depth += push - need;
+    LMB_REQUIRE(depth <= kFusedMaxStack, "fused_ew: stack deeper than %d at instruction %d", kFusedMaxStack, pc);
+    pg.op[pc] = op; pg.arg[pc] = args[pc];
+  }
+  LMB_REQUIRE(depth == 1, "fused_ew: the program leaves %d values", depth);
+  if (total == 0) return LMB200_OK;
+  fused_ew_kernel<<<grid_for(total), 256, 0, ctx->stream>>>(out, pg, total);
   LAUNCHED();
   return LMB200_OK;
 }

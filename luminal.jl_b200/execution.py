@@ -120,44 +120,7 @@ def execute(graph, output_ids, initial_inputs, device=None):
     return out[output_ids] if single else out
 
 
-class CompiledGraph:
-    """compile(graph): one preallocated device buffer per node and a list of steps
-    (src/Compiler.jl:75-100, 217-361).  Calling it copies the inputs in and runs the steps;
-    it returns the per-node device buffers (index by node id, as the reference does)."""
-
-    def __init__(self, graph, device=None):
-        self.graph, self.dev = graph, device or get_device()
-        self.results = {}
-        self.steps = []
-        for node_id, node in enumerate(graph.nodes, start=1):
-            shape = graph.shapes[node_id - 1]
-            buf = self.dev.empty(shape)
-            self.results[node_id] = buf
-            op = node.op
-            if isinstance(op, G.Constant):
-                _lib.call("lmb200_upload", self.dev.handle, C.c_void_p(buf.ptr), _lib.F32,
-                          np.asarray([op.value], np.float32).ctypes.data_as(C.c_void_p), 0, _lib.dims(()), 0)
-            elif isinstance(op, G.Function) and op.name == "InputTensor":
-                pass
-            else:
-                ins = [self.results[i] for i, _, _ in node.inputs]
-                self.steps.append((op, buf, ins))
-
-    def __call__(self, inputs, device=None):
-        for node_id, data in inputs.items():
-            buf = self.results[node_id]
-            a = np.ascontiguousarray(np.asarray(data, dtype=np.float32))
-            if a.size != buf.size:
-                raise ValueError(f"Input size mismatch for node {node_id}: expected {buf.size}, got {a.size}")
-            _lib.call("lmb200_upload", self.dev.handle, C.c_void_p(buf.ptr), _lib.F32, a.ctypes.data_as(C.c_void_p),
-                      len(buf.shape), _lib.dims(buf.shape), 0)
-        for op, out, ins in self.steps:
-            run_op(self.dev, op, out, ins)
-        return self.results
-
-
-def compile(graph, device=None):     # noqa: A001  (the reference's name)
-    return CompiledGraph(graph, device)
+from .compiler import CompiledGraph, compile  # noqa: E402,F401  (compile() with fusion lives in compiler.py)
 
 
 __all__ = ["execute", "execute_op", "run_op", "compile", "CompiledGraph"]

@@ -148,6 +148,19 @@ class Session:
                   int(n_steps), out.ctypes.data_as(C.c_void_p))
         return out
 
+    def decode_until(self, first_tokens, max_steps, eot_token):
+        """Greedy steps until every sequence has produced eot_token or max_steps (or the context) run out:
+        greedy_decode's loop (src/Decoding.jl:91-130).  Returns tokens [steps_done, batch]; a sequence
+        that finished early is padded with eot_token."""
+        first = None
+        if first_tokens is not None:
+            first = np.ascontiguousarray(np.asarray(first_tokens, dtype=np.int32).reshape(self.batch))
+        out = np.empty((max_steps, self.batch), dtype=np.int32)
+        done = C.c_int32(0)
+        _lib.call("lmb200_decode_until", self.handle, first.ctypes.data_as(C.c_void_p) if first is not None else None,
+                  int(max_steps), int(eot_token), out.ctypes.data_as(C.c_void_p), C.byref(done))
+        return out[:done.value]
+
     def decode_n_device(self, first_tokens_dptr, n_steps, tokens_out_dptr=None):
         _lib.call("lmb200_decode_n_device", self.handle, C.c_void_p(first_tokens_dptr or 0), int(n_steps),
                   C.c_void_p(tokens_out_dptr or 0))

@@ -1,0 +1,65 @@
+"""A NumPy evaluator of compile()'s plan (test helper): every step kind run with the oracle's primitives, so
+the planner -- which nodes fuse, which patterns become which kernel, with which operands -- is checked
+against node-by-node evaluation without a GPU."""
+import numpy as np
+
+import luminal_jl_b200 as L
+import luminal_oracle as O
+
+G = L.graph
+
+
+def run_op(op, ins, out_shape):
+    t=type(op)
+    if t is G.Add: return O.add(*ins)
+    if t is G.Mul: return O.mul(*ins)
+    if t is G.Mod: return O.mod(*ins)
+    if t is G.LessThan: return O.less_than(*ins)
+    if t is G.Max: return np.maximum(*ins).astype(np.float32)
+    if t is G.Log2: return O.log2(ins[0])
+    if t is G.Exp2: return O.exp2(ins[0])
+    if t is G.Sin: return O.sin(ins[0])
+    if t is G.Sqrt: return O.sqrt(ins[0])
+    if t is G.Recip: return O.recip(ins[0])
+    if t is G.ReLU: return O.relu(ins[0])
+    if t is G.FusedMulAdd: return O.fused_mul_add(*ins)
+    if t is G.FusedAddReLU: return O.fused_add_relu(*ins)
+    if t is G.SumReduce: return O.sum_reduce(ins[0], op.dim)
+    if t is G.MaxReduce: return O.max_reduce(ins[0], op.dim)
+    if t is G.MatMul: return O.matmul(*ins)
+    if t is G.Permute: return O.permute(ins[0], op.dims)
+    if t is G.Reshape: return O.reshape(ins[0], op.shape)
+    if t is G.Expand: return O.expand(ins[0], op.dim, op.size)
+    if t is G.Slice:
+        a=ins[0]
+        return a[tuple(slice(s, min(e,d)) for (s,e),d in zip(op.ranges,a.shape))]
+    if t is G.Pad: return np.pad(ins[0], op.padding)
+    if t is G.Unfold: return O.unfold1d(ins[0], op.kernel_shape[0], op.stride_shape[0], op.dilation_shape[0])
+    if t is G.Function and op.name=="Gather": return O.gather(*ins)
+    if t is G.Function and op.name=="CumSum": return O.cumsum_last(ins[0])
+    raise NotImplementedError(op)
+def eval_plan(graph, plan, inputs):
+    R={}
+    for nid,w in plan:
+        k=w[0]
+        if k=='input':
+            R[nid]=np.asarray(inputs[nid] if nid in inputs else graph.tensors[(nid,1)],np.float32)
+        elif k=='constant': R[nid]=np.float32(w[1])
+    for nid,w in plan:
+        k=w[0]
+        if k=='op': R[nid]=run_op(w[1],[R[i] for i in w[2]],graph.shapes[nid-1])
+        elif k=='fused':
+            st=[]
+            for op,arg in w[1]:
+                if op==0: st.append(R[w[2][int(arg)]])
+                elif op==1: st.append(np.float32(arg))
+                else:
+                    cls={v:k2 for k2,v in L.compiler._CODE.items()}[op]
+                    ar=3 if cls is G.FusedMulAdd else (2 if cls in (G.Add,G.Mul,G.Mod,G.LessThan,G.Max,G.FusedAddReLU) else 1)
+                    args=st[-ar:]; del st[-ar:]
+                    st.append(run_op(cls(),args,None))
+            R[nid]=np.broadcast_to(st[0],graph.shapes[nid-1]).astype(np.float32)
+        elif k=='silu_gate': R[nid]=O.mul(O.swish(R[w[1]]),R[w[2]])
+        elif k=='rmsnorm': R[nid]=O.rms_norm(R[w[1]],R[w[2]],w[5])
+        elif k=='layernorm': R[nid]=O.layer_norm(R[w[1]],R[w[2]],R[w[3]] if w[3] is not None else None,w[6])
+    return R

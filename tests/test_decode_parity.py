@@ -120,3 +120,45 @@ def test_decode_past_max_ctx_is_an_error(lib_built, device):
     with pytest.raises(L.LuminalB200Error):
         L.Session(model, 33, 8)          # batch above the GEMV tile limit
     sess.close(); model.close()
+
+
+def test_decode_until_stops_at_end_of_text(lib_built, device):
+    """The generation loop's two exits (src/Decoding.jl:93-95, 126-129) for a batch: every sequence follows the
+    oracle until its first end-of-text token and emits that token from then on; the loop ends with the step in which
+    the last sequence finished, or at the position cap."""
+    L = lib_built
+    cfg = O.CONFIGS["tiny_gqa128"]
+    w = O.synth_llama_weights(cfg, seed=7)
+    batch, steps = 3, 12
+    prompt = O.synth_tokens(7, 1000, (batch, 9), cfg["vocab"])
+    ref_tok, _ = O.CachedLlama(w, cfg, batch, 64).greedy(prompt, steps + 1)     # [B, steps + 1]; column 0 comes from the prompt
+    model = make_model(L, device, cfg, w, "f32")
+    sess = L.Session(model, batch, 64)
+    first = sess.prefill(prompt).argmax(-1).astype(np.int32)
+    assert np.array_equal(first, ref_tok[:, 0])
+    free = ref_tok[:, 1:]                                                       # what an unstopped loop produces
+    # an id nobody produces: the loop runs to max_steps
+    unused = int(np.setdiff1d(np.arange(cfg["vocab"]), free)[0])
+    got = sess.decode_until(first, steps, unused)
+    assert got.shape == (steps, batch) and np.array_equal(got.T, free)
+    # the id sequence 1 produces at step 4 ends that sequence there; the others run on (or stop at their own first hit)
+    eot = int(free[1, 4])
+    want = free.copy()
+    last = 0
+    for b in range(batch):
+        hits = np.nonzero(free[b] == eot)[0]
+        if len(hits):
+            want[b, hits[0]:] = eot
+            last = max(last, hits[0])
+        else:
+            last = steps - 1
+    sess.reset()
+    sess.prefill(prompt, want_logits=False)
+    got = sess.decode_until(first, steps, eot)
+    assert got.shape[0] == last + 1 and np.array_equal(got.T, want[:, :last + 1])
+    assert sess.position() == 9 + last + 1
+    # the position cap: 64 - 9 positions are left however many steps are asked for
+    sess.reset()
+    sess.prefill(prompt, want_logits=False)
+    assert sess.decode_until(first, 1000, unused).shape[0] == 64 - 9
+    sess.close(); model.close()
