@@ -181,7 +181,7 @@ int32_t lmb200_rope(lmb200_ctx ctx, float* out, const float* x, int64_t B, int64
                     int64_t D, int64_t prev_seq, float base);
 /* One Linear on host data: out[b, o] = sum_i x[b, i] * W[o, i]; W [rows, K], x [batch <= 32, K],
  * out [batch, rows], all float32 row-major on the host.  dtype selects the float32 or the bf16
- * (float32-accumulate) decode GEMV; variant (bf16 only) 0 = tcgen05 / TMEM, 1 = mma.sync.
+ * (float32-accumulate) decode GEMV; variant is reserved (pass 0: the tcgen05 / TMEM kernel).
  * The decode session runs the same kernels on resident weights; this entry uploads, runs once and
  * downloads (tests, comparisons).  Replaces NN.Linear for a single position, src/NN.jl:22-35. */
 int32_t lmb200_linear_gemv(lmb200_ctx ctx, int32_t dtype, int32_t variant, int32_t rows, int32_t K,
@@ -283,8 +283,15 @@ int32_t lmb200_session_create(lmb200_model model, int32_t batch, int32_t max_ctx
 int32_t lmb200_session_destroy(lmb200_session session);
 int32_t lmb200_session_reset(lmb200_session session);
 int32_t lmb200_session_position(lmb200_session session, int32_t* pos);
-/* Rewind (or move) the position; cache contents at and beyond it are overwritten by later steps. */
+/* Rewind (or move) the position of every sequence; cache contents at and beyond it are overwritten by
+ * later steps.  lmb200_session_position reports the furthest position of any sequence. */
 int32_t lmb200_session_set_position(lmb200_session session, int32_t pos);
+/* One position per sequence (pos[batch] / pos_out[batch]).  The reference's [batch, seq] token tensor
+ * gives every sequence the same length (src/NN.jl:448-455); a batch of real prompts has one length
+ * each, so the session keeps a position per sequence: RoPE angle, cache slot and attention length
+ * follow it. */
+int32_t lmb200_session_set_positions(lmb200_session session, const int32_t* pos);
+int32_t lmb200_session_positions(lmb200_session session, int32_t* pos_out);
 /* Synthetic context: fill cache positions [0,n_pos) with generator values (sigma 1 for K and V)
  * and set the position to n_pos. */
 int32_t lmb200_session_fill_kv_random(lmb200_session session, int32_t n_pos, uint64_t seed);
@@ -303,6 +310,14 @@ int32_t lmb200_session_set_cross_kv(lmb200_session session, int32_t layer, const
  * (NULL or [batch, vocab] float32) receives the LAST position's logits.
  * Replaces running the model over the prompt (src/NN.jl:448-455). */
 int32_t lmb200_prefill(lmb200_session session, const int32_t* tokens, int32_t n, float* logits_out);
+/* Prompts of different lengths in one batch: tokens [batch, n_max] int32 row-major, sequence b uses its
+ * first lengths[b] ids (1 <= lengths[b] <= n_max), appended at that sequence's position.  logits_out
+ * (NULL or [batch, vocab]) receives, per sequence, the logits of ITS last prompt position; afterwards the
+ * sequences stand at different positions and lmb200_decode_step / _n / _until go on from there.
+ * Replaces running the model over a batch of prompts (src/NN.jl:448-455), which the reference can only
+ * do for equal lengths. */
+int32_t lmb200_prefill_ragged(lmb200_session session, const int32_t* tokens, const int32_t* lengths,
+                              int32_t n_max, float* logits_out);
 /* One token per sequence in, greedy next token out; host buffers, copies inside the call.
  * Replaces one iteration of the generation loop (src/Decoding.jl:91-130, examples/llama.jl:73-99). */
 int32_t lmb200_decode_step(lmb200_session session, const int32_t* tokens_in,

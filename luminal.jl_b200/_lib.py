@@ -93,6 +93,9 @@ SIGNATURES = {
     "lmb200_session_reset": [_u64],
     "lmb200_session_position": [_u64, _pi32],
     "lmb200_session_set_position": [_u64, _i32],
+    "lmb200_session_set_positions": [_u64, _pi32],
+    "lmb200_session_positions": [_u64, _pi32],
+    "lmb200_prefill_ragged": [_u64, _vp, _vp, _i32, _vp],
     "lmb200_session_fill_kv_random": [_u64, _i32, _u64],
     "lmb200_session_set_capture": [_u64, _i32],
     "lmb200_session_read_layer_output": [_u64, _i32, _vp],

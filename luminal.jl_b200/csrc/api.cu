@@ -318,11 +318,9 @@ extern "C" int32_t lmb200_init(int32_t device, lmb200_ctx* out) {
     delete c;
     return fail(LMB200_ENOMEM, "init: device allocation failed");
   }
-  // LMB200_GEMV_KERNEL=mma selects the mma.sync bf16 GEMV (for A/B runs); default: tcgen05
   const char* pdl = getenv("LMB200_PDL");      // LMB200_PDL=0: plain stream-ordered launches
   pdl_set_enabled(!(pdl && atoi(pdl) == 0));
-  const char* sel = getenv("LMB200_GEMV_KERNEL");
-  gemv_set_variant((sel && strcmp(sel, "mma") == 0) ? GEMV_MMA_SYNC : GEMV_TCGEN05);
+  gemv_set_variant(GEMV_TCGEN05);
   int32_t rc = gemv_configure();
   if (rc == LMB200_OK) rc = attn_configure();
   if (rc == LMB200_OK) rc = flash_tc_configure();

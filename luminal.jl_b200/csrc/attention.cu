@@ -57,12 +57,12 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_bf16_kernel(const At
 
   pdl_launch_dependents();
   pdl_wait();
-  const int T = p.pos ? (*p.pos + 1) : p.T_fixed;
+  const int bk = blockIdx.x;
+  const int b = bk / p.KVl, kvl = bk - b * p.KVl;
+  const int T = p.pos ? (p.pos[b] + 1) : p.T_fixed;        // every sequence has its own context length
   const int kpc = keys_per_cta_for(p, T);
   const int k_begin = blockIdx.y * kpc;
   if (k_begin >= T) return;
-  const int bk = blockIdx.x;
-  const int b = bk / p.KVl, kvl = bk - b * p.KVl;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int G = p.G;
@@ -229,14 +229,14 @@ __global__ void __launch_bounds__(kAttnThreads) attn_decode_simple_kernel(const 
   float* red = ps + p.keys_per_cta;
   pdl_launch_dependents();
   pdl_wait();
-  const int Tctx = p.pos ? (*p.pos + 1) : p.T_fixed;
+  const int bk = blockIdx.x, h = blockIdx.z;
+  const int b = bk / p.KVl, kvl = bk - b * p.KVl;
+  const int Tctx = p.pos ? (p.pos[b] + 1) : p.T_fixed;
   const int kpc = keys_per_cta_for(p, Tctx);
   const int k_begin = blockIdx.y * kpc;
   if (k_begin >= Tctx) return;
   const int k_end = min(Tctx, k_begin + kpc);
   const int n = k_end - k_begin;
-  const int bk = blockIdx.x, h = blockIdx.z;
-  const int b = bk / p.KVl, kvl = bk - b * p.KVl;
   const int tid = threadIdx.x;
   const T* q = reinterpret_cast<const T*>(p.q) + (int64_t)b * p.q_pitch + (kvl * p.G + h) * D;
   const T* kv = reinterpret_cast<const T*>(p.kv_layer) + b * p.kv_batch_stride + kvl * p.kv_head_stride;
@@ -291,10 +291,10 @@ template <typename T>
 __global__ void attn_combine_kernel(const AttnParams p) {
   pdl_launch_dependents();
   pdl_wait();
-  const int Tctx = p.pos ? (*p.pos + 1) : p.T_fixed;
+  const int b = blockIdx.x / (p.KVl * p.G);
+  const int Tctx = p.pos ? (p.pos[b] + 1) : p.T_fixed;
   const int kpc = keys_per_cta_for(p, Tctx);
   const int nvalid = (Tctx + kpc - 1) / kpc;
-  const int b = blockIdx.x / (p.KVl * p.G);
   const int hl = blockIdx.x - b * (p.KVl * p.G);
   const int kvl = hl / p.G, h = hl - kvl * p.G;
   const int64_t slot0 = (int64_t)(b * p.KVl + kvl) * p.nsplit;

@@ -14,7 +14,7 @@ struct AttnParams {
   int64_t kv_batch_stride = 0;
   int64_t kv_head_stride = 0;
   int B = 0, KVl = 0, G = 0, D = 0;
-  const int* pos = nullptr;       // device scalar; context length T = *pos + 1 (NULL -> T_fixed)
+  const int* pos = nullptr;       // device [B]; context length of sequence b is pos[b] + 1 (NULL -> T_fixed for all)
   int T_fixed = 0;
   int keys_per_cta = 0;           // multiple of 64
   int nsplit = 0;                 // gridDim.y, covers the cache capacity

@@ -4,9 +4,11 @@
 //
 // One CTA = two tiles of 128 query rows of one (batch, head) sharing the key/value stream, keys in
 // tiles of 64:
-//   2 loader warps : cp.async 16-byte chunks of Q / K / V from row-major global memory into the
-//                    canonical core-matrix layout (8 rows x 16 bytes) the tensor core reads, 3 K/V
-//                    stages in flight;
+//   2 loader warps : Q by cp.async 16-byte chunks into the canonical core-matrix layout (8 rows x 16
+//                    bytes); K and V by TMA (cp.async.bulk.tensor over a 4-D map d / key / kv head /
+//                    batch, one thread, 3 stages in flight): a key tile lands as D / W sub-tiles of
+//                    [64 keys][W head dims] in the 128-byte (W = 64) or 64-byte (W = 32, head_dim 96)
+//                    swizzle, which the tensor core reads K-major for Q K^T and MN-major for P V;
 //   1 MMA warp     : one thread issues tcgen05.mma for both query tiles -- S = Q K^T (M 128, N 64,
 //                    K = D) into a double-buffered TMEM tile, then O += P V (M 128, N = D, K 64; V
 //                    read MN-major from the same tile layout as K) accumulating in TMEM over all
@@ -19,6 +21,7 @@
 //                    tensor core busy in turn.
 // Causal: key tiles beyond a query tile's diagonal are never computed; inside the diagonal tile
 // keys j > i are masked -- the reference's `if causal && j > i continue`.
+#include <cuda.h>
 #include <math_constants.h>
 
 #include "common.cuh"
@@ -66,15 +69,33 @@ __device__ __forceinline__ uint32_t canon(int row, int c8, int rows) {
   return (uint32_t)(c8 * (rows * 16) + (row >> 3) * 128 + (row & 7) * 16);
 }
 
+// Shared-memory descriptor of a tile in the 128-byte (layout type 2) or 64-byte (type 4) swizzle a
+// tensor map writes.  K-major: lbo unused (1), sbo = bytes between groups of 8 rows.  MN-major: lbo =
+// bytes between swizzle-wide blocks along N, sbo = bytes between groups of 8 rows along K.
+__device__ __forceinline__ uint64_t smem_desc_swz(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t type) {
+  return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) | ((uint64_t)(sbo_bytes >> 4) << 32) |
+         (1ull << 46) | ((uint64_t)type << 61);
+}
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];\n" ::"r"(
+          tc::smem_u32(dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(tc::smem_u32(bar))
+      : "memory");
+}
+
 template <int D>
 __global__ void __launch_bounds__(kThreads, 1)
-flash_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
-                const __nv_bfloat16* __restrict__ v, const FlashView fv, int S, float scale, int causal, int* err) {
+flash_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ q, const __grid_constant__ CUtensorMap kmap,
+                const __grid_constant__ CUtensorMap vmap, const FlashView fv, int S, float scale, int causal, int* err) {
+  constexpr int W = D % 64 == 0 ? 64 : 32;            // head dims per swizzled sub-tile
+  constexpr int kSub = kBN * W * 2;                   // bytes of one sub-tile [64 keys][W]
+  constexpr uint32_t kSwz = W == 64 ? 2u : 4u;        // descriptor layout type: 128-byte / 64-byte swizzle
   using namespace tc;
   typedef Smem<D> SM;
   extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ __align__(8) uint64_t q_full, kv_full[kKvStages], kv_empty[kKvStages];
-  __shared__ __align__(8) uint64_t s_full[2][2], s_empty[2][2], p_full[2][2], p_empty[2][2], pv_done[2];
+  __shared__ __align__(8) uint64_t s_full[2][2], s_empty[2][2], p_full[2][2], p_empty[2][2];
   __shared__ uint32_t tmem_slot;
   constexpr uint32_t kTmemCols = 512;
   constexpr uint32_t kColS = 0, kColO = 256;                 // S: [tile][buffer] x 64 columns, O: [tile] x D columns
@@ -85,10 +106,9 @@ flash_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict
   // blockIdx.y = batch * H + head; query head h reads kv head h / G (G = 1: an op with H kv heads)
   const int bi = (int)blockIdx.y / fv.H, hi = (int)blockIdx.y - bi * fv.H;
   const __nv_bfloat16* qb = q + bi * fv.q_b + hi * fv.q_h;
-  const __nv_bfloat16* kb = k + bi * fv.k_b + (hi / fv.G) * fv.k_h;
-  const __nv_bfloat16* vb = v + bi * fv.k_b + (hi / fv.G) * fv.k_h;
+  const int kvh = hi / fv.G;
   __nv_bfloat16* ob_base = out + bi * fv.q_b + hi * fv.q_h;
-  const int64_t q_s = fv.q_s, k_s = fv.k_s;
+  const int64_t q_s = fv.q_s;
   int n_tiles[2];
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
@@ -106,7 +126,6 @@ flash_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict
         mbar_init(&s_full[t][i], 1); mbar_init(&s_empty[t][i], 4);
         mbar_init(&p_full[t][i], 4); mbar_init(&p_empty[t][i], 1);
       }
-      mbar_init(&pv_done[t], 1);
     }
     mbar_init_fence();
   }
@@ -123,7 +142,6 @@ flash_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict
     // its own tile to land before it signals it, so one warp's wait never holds back the other's
     // next issue.
     const int lw = warp - 9, lt = tid - 9 * 32;     // lt: 0..kLoaders-1
-    constexpr int kLw = kLoaders / 32;
     const uint32_t sQ = smem_u32(smem + SM::offQ);
     for (int i = lt; i < 2 * kBM * (D / 8); i += kLoaders) {
       const int row = i / (D / 8), c8 = i - row * (D / 8);      // row 0..255 over both tiles
@@ -131,51 +149,26 @@ flash_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict
       cp_async16(sQ + (row >> 7) * SM::kQ + canon(row & 127, c8, kBM), qb + (int64_t)min(qi, S - 1) * q_s + c8 * 8, qi < S ? 16u : 0u);
     }
     cp_async_commit();
-    bool q_signalled = false;
-    for (int j = lw; j < n_max; j += kLw) {
-      const int s = j % kKvStages;
-      mbar_wait(&kv_empty[s], ((j / kKvStages) & 1) ^ 1, dead, err);
-      const uint32_t sK = smem_u32(smem + SM::offK + s * SM::kKV), sV = smem_u32(smem + SM::offV + s * SM::kKV);
-      if ((32 % (D / 8)) == 0 && (j + 1) * kBN <= S) {
-        // tile inside the sequence, and a lane keeps its 16-byte column: rows advance by 32 / (D/8)
-        constexpr int kCols = D / 8, kRowStep = 32 / kCols;
-        const int c8 = lane % kCols, row0 = lane / kCols;
-        const __nv_bfloat16* ks = kb + (int64_t)(j * kBN + row0) * k_s + c8 * 8;
-        const __nv_bfloat16* vs = vb + (int64_t)(j * kBN + row0) * k_s + c8 * 8;
-#pragma unroll 8
-        for (int it = 0; it < kBN / kRowStep; ++it) {
-          const uint32_t off = canon(row0 + it * kRowStep, c8, kBN);
-          cp_async16(sK + off, ks + (int64_t)it * kRowStep * k_s, 16u);
-          cp_async16(sV + off, vs + (int64_t)it * kRowStep * k_s, 16u);
+    // Q: every loader thread waits for its own chunks, then its warp signals
+    cp_async_wait<0>();
+    fence_async_smem();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&q_full);
+    // K and V: one thread issues the tensor copies of a key tile (D / W boxes each) onto the stage's barrier
+    if (lw == 0) {
+      for (int j = 0; j < n_max; ++j) {
+        const int s = j % kKvStages;
+        mbar_wait(&kv_empty[s], ((j / kKvStages) & 1) ^ 1, dead, err);
+        if (lane == 0) {
+          mbar_expect_tx(&kv_full[s], (uint32_t)(2 * SM::kKV));
+#pragma unroll
+          for (int sub = 0; sub < D / W; ++sub) {
+            tma_load_4d(smem + SM::offK + s * SM::kKV + sub * kSub, &kmap, sub * W, j * kBN, kvh, bi, &kv_full[s]);
+            tma_load_4d(smem + SM::offV + s * SM::kKV + sub * kSub, &vmap, sub * W, j * kBN, kvh, bi, &kv_full[s]);
+          }
         }
-      } else {
-        for (int i = lane; i < kBN * (D / 8); i += 32) {
-          const int row = i / (D / 8), c8 = i - row * (D / 8);
-          const int key = j * kBN + row;
-          const int64_t src = (int64_t)min(key, S - 1) * k_s + c8 * 8;
-          const uint32_t nb = key < S ? 16u : 0u;
-          cp_async16(sK + canon(row, c8, kBN), kb + src, nb);
-          cp_async16(sV + canon(row, c8, kBN), vb + src, nb);
-        }
-      }
-      cp_async_commit();
-      if (!q_signalled) {
-        cp_async_wait<1>();                          // this warp's share of Q has landed
-        fence_async_smem();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&q_full);
-        q_signalled = true;
       }
-      cp_async_wait<0>();                            // tile j has landed
-      fence_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&kv_full[s]);
-    }
-    if (!q_signalled) {
-      cp_async_wait<0>();
-      fence_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&q_full);
     }
   } else if (warp == 8) {
     // ------------------------------ MMA issue ------------------------------
@@ -192,15 +185,14 @@ flash_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict
         if (lane == 0) FL_TRACE(j, 8 + t);
         if (lane == 0) {
           // A = P [128 x 64] K-major: lbo (between key groups of 8) = 128*16, sbo = 128
-          // B = V tile [64 keys x D] read as N = d (contiguous), K = key: sbo (between d groups) =
-          //     64*16 = 1024, lbo (between key groups) = 128
           const uint64_t adesc = smem_desc(smem_u32(smem + SM::offP + (t * 2 + pb) * SM::kP), kBM * 16, 128);
-          const uint64_t bdesc = smem_desc(smem_u32(smem + SM::offV + s * SM::kKV), 128, kBN * 16);
+          // B = V tile read MN-major: N = d runs along the swizzled rows (D / W blocks, kSub bytes apart), K = key:
+          // groups of 8 keys are 8 rows = 8 * 2 W bytes apart; a K = 16 step is two groups
+          const uint64_t bdesc = smem_desc_swz(smem_u32(smem + SM::offV + s * SM::kKV), kSub, 16 * W, kSwz);
 #pragma unroll
           for (int ks = 0; ks < kBN / 16; ++ks)
-            mma_f16(tmem + kColO + t * D, adesc + (uint64_t)(ks * ((2 * kBM * 16) >> 4)), bdesc + (uint64_t)(ks * (256 >> 4)),
+            mma_f16(tmem + kColO + t * D, adesc + (uint64_t)(ks * ((2 * kBM * 16) >> 4)), bdesc + (uint64_t)(ks * ((32 * W) >> 4)),
                     kIdescPV, (j > 0 || ks > 0) ? 1u : 0u);
-          commit(&pv_done[t]);
           commit(&p_empty[t][pb]);
         }
         __syncwarp();
@@ -219,13 +211,16 @@ flash_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict
         fence_after();
         if (lane == 0) FL_TRACE(j, 11 + t);
         if (lane == 0) {
-          // A = Q [128 x D] K-major: lbo = 128*16, sbo = 128;  B = K tile [64 x D] K-major: lbo = 64*16
+          // A = Q [128 x D] K-major, canonical: lbo = 128*16, sbo = 128
           const uint64_t adesc = smem_desc(smem_u32(smem + SM::offQ + t * SM::kQ), kBM * 16, 128);
-          const uint64_t bdesc = smem_desc(smem_u32(smem + SM::offK + s * SM::kKV), kBN * 16, 128);
+          // B = K tile, K-major in swizzled rows of W head dims: step ks covers d 16 ks .. + 15 = sub-tile (16 ks) / W,
+          // 32 bytes per step inside the row
+          const uint32_t sK = smem_u32(smem + SM::offK + s * SM::kKV);
 #pragma unroll
-          for (int ks = 0; ks < D / 16; ++ks)
-            mma_f16(tmem + kColS + (t * 2 + sb) * kBN, adesc + (uint64_t)(ks * ((2 * kBM * 16) >> 4)),
-                    bdesc + (uint64_t)(ks * ((2 * kBN * 16) >> 4)), kIdescS, ks ? 1u : 0u);
+          for (int ks = 0; ks < D / 16; ++ks) {
+            const uint64_t bdesc = smem_desc_swz(sK + ((16 * ks) / W) * kSub + ((16 * ks) % W) * 2, 16, 16 * W, kSwz);
+            mma_f16(tmem + kColS + (t * 2 + sb) * kBN, adesc + (uint64_t)(ks * ((2 * kBM * 16) >> 4)), bdesc, kIdescS, ks ? 1u : 0u);
+          }
           commit(&s_full[t][sb]);
         }
         __syncwarp();
@@ -275,7 +270,10 @@ flash_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict
       const bool raise = m > -CUDART_INF_F && mx > m + kRescaleStep;
       if (__any_sync(0xffffffffu, raise) && j > 0) {
         const float alpha = raise ? exp2f(m - mx) : 1.0f;
-        mbar_wait(&pv_done[t], (j - 1) & 1, dead, err);          // every P V issued so far has landed in O
+        // P V of key tile j - 1 (and with it every earlier one) has landed in O.  The P buffer's own barrier says
+        // so: this thread has waited every earlier phase of it, so the parity cannot be taken for an older phase
+        // (a barrier that counts every tile could be two phases behind here, and parity alone would let that pass).
+        mbar_wait(&p_empty[t][(j - 1) & 1], ((j - 1) >> 1) & 1, dead, err);
         fence_after();
 #pragma unroll
         for (int ch = 0; ch < D / 32; ++ch) {
@@ -314,7 +312,7 @@ flash_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict
       if (wq == 0 && lane == 0) FL_TRACE(j, 3 + 4 * t);
     }
     if (nt >= 1) {
-      mbar_wait(&pv_done[t], (nt - 1) & 1, dead, err);
+      mbar_wait(&p_empty[t][(nt - 1) & 1], ((nt - 1) >> 1) & 1, dead, err);     // the last P V has landed (see above)
       fence_after();
       const float inv = 1.0f / l;
       __nv_bfloat16* ob = ob_base + (int64_t)qi * q_s;
@@ -356,14 +354,56 @@ int32_t flash_tc_configure() {
 
 bool flash_tc_supported(int64_t D) { return D == 64 || D == 96 || D == 128; }
 
+namespace {
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn flash_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    else
+      cudaGetLastError();
+  }
+  return fn;
+}
+// 4-D map over K or V: dims {d, key, kv head, batch}; a box is [64 keys][W head dims], swizzled over its W * 2 bytes.
+// Keys past S arrive as zeros (the softmax masks them).
+int32_t kv_tensor_map(CUtensorMap* map, const void* base, const FlashView& fv, int64_t B, int64_t S, int64_t D) {
+  EncodeTiledFn enc = flash_encode_fn();
+  if (!enc) return fail(LMB200_ECUDA, "flash attention: cuTensorMapEncodeTiled is not available");
+  const int W = D % 64 == 0 ? 64 : 32;
+  const int64_t n_kv = fv.H / fv.G;
+  const int64_t head_stride = n_kv > 1 ? fv.k_h : S * fv.k_s;           // a dimension of extent 1 still needs a valid stride
+  const int64_t batch_stride = B > 1 ? fv.k_b : S * fv.k_s * n_kv;
+  LMB_REQUIRE((reinterpret_cast<uintptr_t>(base) & 15) == 0 && fv.k_s % 8 == 0 && head_stride % 8 == 0 && batch_stride % 8 == 0,
+              "flash attention: K / V base and strides must be multiples of 16 bytes");
+  const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)S, (cuuint64_t)n_kv, (cuuint64_t)B};
+  const cuuint64_t strides[3] = {(cuuint64_t)fv.k_s * 2, (cuuint64_t)head_stride * 2, (cuuint64_t)batch_stride * 2};
+  const cuuint32_t box[4] = {(cuuint32_t)W, (cuuint32_t)kBN, 1, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, W == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(LMB200_ECUDA, "flash attention: cuTensorMapEncodeTiled failed (%d)", (int)r);
+  return LMB200_OK;
+}
+}  // namespace
+
 // q, out: element (b, h, s, d) at b * q_b + h * q_h + s * q_s + d; k, v likewise with the k strides
 int32_t flash_tc_launch_view(Ctx* ctx, void* out, const void* q, const void* k, const void* v, const FlashView& fv, int64_t B,
                              int64_t S, int64_t D, float scale, int causal, cudaStream_t stream) {
   dim3 grid((unsigned)ceil_div(S, 2 * kBM), (unsigned)(B * fv.H));
+  CUtensorMap kmap, vmap;
+  LMB_TRY(kv_tensor_map(&kmap, k, fv, B, S, D));
+  LMB_TRY(kv_tensor_map(&vmap, v, fv, B, S, D));
 #define LMB_FLASH(DD)                                                                                                   \
   flash_tc_kernel<DD><<<grid, kThreads, Smem<DD>::total + 1024, stream>>>(                                             \
-      (__nv_bfloat16*)out, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, fv, (int)S, scale, causal, \
-      ctx->dev_err)
+      (__nv_bfloat16*)out, (const __nv_bfloat16*)q, kmap, vmap, fv, (int)S, scale, causal, ctx->dev_err)
   if (D == 128) LMB_FLASH(128);
   else if (D == 96) LMB_FLASH(96);
   else if (D == 64) LMB_FLASH(64);

@@ -6,15 +6,11 @@
 // [c*U/G, (c+1)*U/G), so every SM streams the same number of bytes in a single wave whatever the
 // matrix shape.  A producer warp keeps a ring of 5 shared-memory stages full with cp.async.bulk
 // copies (one 32 KB copy of weights, evict-first, + the matching activation slice) signalled
-// through mbarriers.  Two consumers of the ring:
-//   tcgen05 (default): one thread issues tcgen05.mma (M = 128 rows, N = batch padding, K = 16)
-//     straight from the stage through shared-memory descriptors, accumulators double-buffered in
-//     TMEM; tcgen05.commit hands the stage back to the producer; four epilogue warps read the
-//     accumulators with tcgen05.ld (one row per thread) and run the fused epilogue while the next
-//     row group is already being multiplied.
-//   mma.sync: 8 consumer warps, one 16-row block each, operands via ldmatrix.  At batch 32 this
-//     path is limited by the legacy tensor pipe (one m16n8k16 per ~9 SM cycles, ~5.5 needed);
-//     kept selectable for comparison.
+// through mbarriers.  One thread issues tcgen05.mma (M = 128 rows, N = batch padding, K = 16)
+// straight from the stage through shared-memory descriptors, accumulators double-buffered in
+// TMEM; tcgen05.commit hands the stage back to the producer; four epilogue warps read the
+// accumulators with tcgen05.ld (one row per thread) and run the fused epilogue while the next
+// row group is already being multiplied.
 // When a CTA's range leaves a row group its partial result is folded: alone -> epilogue; shared
 // -> global scratch + counter, the last contributor sums the parts in CTA order (deterministic).
 //
@@ -94,13 +90,13 @@ __device__ __forceinline__ void run_epilogue(const GemvParams& p, const float* t
     WT* q_out = reinterpret_cast<WT*>(p.q_out);
     WT* kv = reinterpret_cast<WT*>(p.kv_layer);
     const int D = p.D, tiles_per_head = D >> 4, half = D >> 1;
-    const int pos = *p.pos;
-    const float fpos = (float)pos;
     for (int i = tid; i < (RPC / 2) * Bp; i += nthreads) {
       const int b = i / (RPC / 2), j = i - b * (RPC / 2);
       const int m = j >> 3, r = j & 7;
       const int gt = row0 / 16 + m;                  // global 16-row tile
       if (b >= p.B || gt >= p.RB) continue;
+      const int pos = p.pos[b];                      // every sequence has its own position
+      const float fpos = (float)pos;
       const int hs = gt / tiles_per_head, jj = gt - hs * tiles_per_head;
       float v0 = tile[(16 * m + r) * RP + b], v1 = tile[(16 * m + r + 8) * RP + b];
       if (p.bias) { v0 += p.bias[gt * 16 + r]; v1 += p.bias[gt * 16 + r + 8]; }
@@ -478,237 +474,6 @@ __device__ __forceinline__ void produce(const GemvParams& p, const UnitRange& ur
 }
 
 // ---------------------------------------------------------------------------------------------
-// mma.sync variant: 8 consumer warps, warp w owns row block 8r + w
-// ---------------------------------------------------------------------------------------------
-constexpr int kMmaThreads = 9 * 32;
-
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-               : "r"(addr));
-}
-
-// Epilogue of one 16-row block straight from the accumulator fragments of the warp that owns it:
-// lane (g,t) holds, per batch tile nt, rows g (c0,c1) and g+8 (c2,c3) at columns 8nt+2t, +1 --
-// and rows g / g+8 are exactly the pairs the fused epilogues combine.
-template <int NB>
-__device__ __forceinline__ void fragment_epilogue(const GemvParams& p, float (&acc)[NB][4], int rb, int g, int t) {
-  constexpr int Bp = 8 * NB;
-  typedef Layout<__nv_bfloat16> LY;
-  if (p.bias) {
-    const float b0 = rb * 16 + g < p.rows ? p.bias[rb * 16 + g] : 0.f;
-    const float b1 = rb * 16 + g + 8 < p.rows ? p.bias[rb * 16 + g + 8] : 0.f;
-#pragma unroll
-    for (int nt = 0; nt < NB; ++nt) { acc[nt][0] += b0; acc[nt][1] += b0; acc[nt][2] += b1; acc[nt][3] += b1; }
-  }
-  if (p.epi == EPI_GELU_ACT) {
-    __nv_bfloat16* act = reinterpret_cast<__nv_bfloat16*>(p.act);
-    const int row = rb * 16 + g;
-#pragma unroll
-    for (int nt = 0; nt < NB; ++nt) {
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int b = 8 * nt + 2 * t + e;
-        if (b < p.B) {
-          if (row < p.n_act) act[LY::x_offset(b, row, Bp)] = __float2bfloat16_rn(gelu_ref(acc[nt][e]));
-          if (row + 8 < p.n_act) act[LY::x_offset(b, row + 8, Bp)] = __float2bfloat16_rn(gelu_ref(acc[nt][2 + e]));
-        }
-      }
-    }
-    return;
-  }
-  if (p.epi == EPI_STORE_F32) {
-    const int row = rb * 16 + g;
-#pragma unroll
-    for (int nt = 0; nt < NB; ++nt) {
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int b = 8 * nt + 2 * t + e;
-        if (b < p.B) {
-          if (row < p.rows) p.out[(int64_t)b * p.out_pitch + row] = acc[nt][e];
-          if (row + 8 < p.rows) p.out[(int64_t)b * p.out_pitch + row + 8] = acc[nt][2 + e];
-        }
-      }
-    }
-  } else if (p.epi == EPI_SILU_GATE) {
-    __nv_bfloat16* act = reinterpret_cast<__nv_bfloat16*>(p.act);
-    const int o = rb * 8 + g;
-    if (o < p.n_act) {
-#pragma unroll
-      for (int nt = 0; nt < NB; ++nt) {
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int b = 8 * nt + 2 * t + e;
-          if (b < p.B) {
-            const float a = acc[nt][e], u = acc[nt][2 + e];
-            // silu(a) = a * (1 / (1 + exp2((a * -1) * (1/ln2))))     src/HighLevelOps.jl:153-160
-            const float ex = exp2f((a * -1.0f) * kInvLn2);
-            const float sg = 1.0f / (1.0f + ex);
-            act[LY::x_offset(b, o, Bp)] = __float2bfloat16_rn((a * sg) * u);
-          }
-        }
-      }
-    }
-  } else {  // EPI_QKV_ROPE
-    __nv_bfloat16* q_out = reinterpret_cast<__nv_bfloat16*>(p.q_out);
-    __nv_bfloat16* kv = reinterpret_cast<__nv_bfloat16*>(p.kv_layer);
-    const int D = p.D, tiles_per_head = D >> 4, half = D >> 1;
-    const int pos = *p.pos;
-    const int hs = rb / tiles_per_head, jj = rb - hs * tiles_per_head;
-    float sn = 0.f, cs = 1.f;
-    const bool rope = hs < p.Hl + p.KVl;
-    const int d0 = 8 * jj + g;
-    if (rope && p.rope) {
-      // rows g / g+8 of the block are the RoPE pair (d0, d0 + D/2)      src/NN.jl:253-303
-      const float ang = (float)pos * p.inv_freq[d0];
-      sn = sinf(ang);
-      cs = sinf(kHalfPi + ang * -1.0f);   // cos(a) = sin(pi/2 - a)
-    } else if (rope) {
-      cs = p.qk_scale;                    // no rotation: q and k rows are only scaled
-    }
-#pragma unroll
-    for (int nt = 0; nt < NB; ++nt) {
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int b = 8 * nt + 2 * t + e;
-        if (b >= p.B) continue;
-        const float v0 = acc[nt][e], v1 = acc[nt][2 + e];
-        if (rope) {
-          const float o0 = v0 * cs + (v1 * sn) * -1.0f;
-          const float o1 = v0 * sn + v1 * cs;
-          if (hs < p.Hl) {
-            __nv_bfloat16* q = q_out + (int64_t)b * p.q_pitch + hs * D;
-            q[d0] = __float2bfloat16_rn(o0);
-            q[d0 + half] = __float2bfloat16_rn(o1);
-          } else {
-            __nv_bfloat16* kc = kv + b * p.kv_batch_stride + (hs - p.Hl) * p.kv_head_stride;
-            kc[kcache_offset(pos, d0, D)] = __float2bfloat16_rn(o0);
-            kc[kcache_offset(pos, d0 + half, D)] = __float2bfloat16_rn(o1);
-          }
-        } else {
-          __nv_bfloat16* vc = kv + b * p.kv_batch_stride + (hs - p.Hl - p.KVl) * p.kv_head_stride;
-          const int d = 16 * jj + g;
-          vc[vcache_offset(pos, d, D)] = __float2bfloat16_rn(v0);
-          vc[vcache_offset(pos, d + 8, D)] = __float2bfloat16_rn(v1);
-        }
-      }
-    }
-  }
-}
-
-template <int NB>
-__global__ void __launch_bounds__(kMmaThreads, 1) gemv_mma_kernel(const GemvParams p, int* err) {
-  constexpr int Bp = 8 * NB;
-  constexpr int kStage = kWStage + Bp * 256;
-  extern __shared__ __align__(1024) unsigned char smem[];
-  __shared__ __align__(8) uint64_t full_bar[kStages];
-  __shared__ __align__(8) uint64_t empty_bar[kStages];
-
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const UnitRange ur = unit_range(p);
-  if (tid == 0) {
-#pragma unroll
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], 8);
-    }
-    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-  }
-  __syncthreads();
-  pdl_launch_dependents();
-
-  if (warp == 8) {
-    produce<Bp>(p, ur, smem, full_bar, empty_bar, lane, err);
-    return;
-  }
-  pdl_wait();
-
-  const int g = lane >> 2, t = lane & 3;
-  float acc[NB][4];
-  auto zero_acc = [&]() {
-#pragma unroll
-    for (int j = 0; j < NB; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
-  };
-  // Fold the accumulators of row group r, which this CTA's unit range has just left.  Warp-local:
-  // alone -> epilogue; shared -> fragment to scratch, per-row-block counter, the last contributor
-  // sums the fragments in CTA order and runs the epilogue.
-  auto flush = [&](int r) {
-    const int rb = r * 8 + warp;
-    if (rb * 16 >= p.rows) return;
-    int c_first, n;
-    contributors(ur, r, &c_first, &n);
-    if (n > 1) {
-      float4* part = reinterpret_cast<float4*>(p.partials) + (int64_t)rb * p.ksplit * (32 * NB);
-      float4* mine = part + (int64_t)((int)blockIdx.x - c_first) * (32 * NB) + lane * NB;
-#pragma unroll
-      for (int nt = 0; nt < NB; ++nt) mine[nt] = make_float4(acc[nt][0], acc[nt][1], acc[nt][2], acc[nt][3]);
-      __threadfence();
-      __syncwarp();
-      unsigned prev = 0;
-      if (lane == 0) prev = atomicAdd(&p.counters[rb], 1u);
-      prev = __shfl_sync(0xffffffffu, prev, 0);
-      if (prev != (unsigned)n - 1u) return;
-      if (lane == 0) p.counters[rb] = 0u;          // ready for the next launch
-      __threadfence();
-      zero_acc();
-      for (int k0 = 0; k0 < n; k0 += 4) {
-        float4 v[4][NB];
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-#pragma unroll
-          for (int nt = 0; nt < NB; ++nt)
-            v[kk][nt] = (k0 + kk < n) ? __ldcg(part + (int64_t)(k0 + kk) * (32 * NB) + lane * NB + nt)
-                                      : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-#pragma unroll
-          for (int nt = 0; nt < NB; ++nt) {
-            acc[nt][0] += v[kk][nt].x; acc[nt][1] += v[kk][nt].y; acc[nt][2] += v[kk][nt].z; acc[nt][3] += v[kk][nt].w;
-          }
-      }
-    }
-    fragment_epilogue<NB>(p, acc, rb, g, t);
-  };
-
-  bool dead = false;
-  zero_acc();
-  int seg_r = ur.u0 < ur.u1 ? ur.u0 / ur.KS : -1;
-  int it = 0;
-  // ldmatrix lane addressing: matrix mi = lane/8, row lane%8
-  const int mi = lane >> 3, lr = lane & 7;
-  const uint32_t a_lane = (uint32_t)((mi >> 1) * 2048 + (2 * warp + (mi & 1)) * 128 + lr * 16);
-  const uint32_t b_lane = (uint32_t)((mi & 1) * (Bp * 16) + (mi >> 1) * 128 + lr * 16);
-  for (int u = ur.u0; u < ur.u1; ++u, ++it) {
-    const int r = u / ur.KS;
-    if (r != seg_r) {
-      flush(seg_r);
-      zero_acc();
-      seg_r = r;
-    }
-    const int s = it % kStages, k = it / kStages;
-    mbar_wait(&full_bar[s], k & 1, dead, err);
-    if ((r * 8 + warp) * 16 < p.rows) {
-      const uint32_t st = smem_u32(smem + s * kStage);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {            // 8 k-steps of 16
-        uint32_t a[4];
-        ldmatrix_x4(a, st + a_lane + j * 4096);
-#pragma unroll
-        for (int np = 0; np < NB / 2; ++np) {  // two batch tiles per ldmatrix.x4
-          uint32_t b[4];
-          ldmatrix_x4(b, st + kWStage + b_lane + j * (2 * Bp * 16) + np * 256);
-          mma_bf16(acc[2 * np], a[0], a[1], a[2], a[3], b[0], b[1]);
-          mma_bf16(acc[2 * np + 1], a[0], a[1], a[2], a[3], b[2], b[3]);
-        }
-      }
-    }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&empty_bar[s]);
-  }
-  if (seg_r >= 0) flush(seg_r);
-}
-
-// ---------------------------------------------------------------------------------------------
 // tcgen05 variant
 // ---------------------------------------------------------------------------------------------
 constexpr int kTcThreads = 6 * 32;    // warp 0 producer, warp 1 MMA issue + TMEM, warps 2..5 epilogue
@@ -819,14 +584,17 @@ __device__ __forceinline__ void row_epilogue(const GemvParams& p, float (&v)[NV]
   // EPI_QKV_ROPE
   __nv_bfloat16* kv = reinterpret_cast<__nv_bfloat16*>(p.kv_layer);
   const int D = p.D, tiles_per_head = D >> 4, half = D >> 1;
-  const int pos = *p.pos;
+  // One position per sequence.  When the host knows they are all equal (pos_uniform) the rotation's sine and
+  // cosine are computed once per row; otherwise once per batch column.
+  int pos = p.pos[0];
   const int hs = rb / tiles_per_head, jj = rb - hs * tiles_per_head;
   if (hs < p.Hl + p.KVl) {
     // rows g / g+8 of the block are the RoPE pair (d0, d0 + D/2)      src/NN.jl:253-303
     const int d0 = 8 * jj + g;
     float sn = 0.f, cs = p.qk_scale;                // no rotation: q and k rows are only scaled
+    const float inv_f = p.rope ? p.inv_freq[d0] : 0.f;
     if (p.rope) {
-      const float ang = (float)pos * p.inv_freq[d0];
+      const float ang = (float)pos * inv_f;
       sn = sinf(ang);
       cs = sinf(kHalfPi + ang * -1.0f);             // cos(a) = sin(pi/2 - a)
     }
@@ -834,6 +602,14 @@ __device__ __forceinline__ void row_epilogue(const GemvParams& p, float (&v)[NV]
 #pragma unroll
     for (int b = 0; b < N; ++b) {
       if (b0 + b < p.B) {
+        if (!p.pos_uniform) {
+          pos = p.pos[b0 + b];
+          if (p.rope) {
+            const float ang = (float)pos * inv_f;
+            sn = sinf(ang);
+            cs = sinf(kHalfPi + ang * -1.0f);
+          }
+        }
         // low row: x0*cos - x1*sin; high row: x0*sin + x1*cos (x0 = the low row's value)
         const float o = hi ? (w[b] * sn + v[b] * cs) : (v[b] * cs + (w[b] * sn) * -1.0f);
         if (hs < p.Hl) {
@@ -847,9 +623,11 @@ __device__ __forceinline__ void row_epilogue(const GemvParams& p, float (&v)[NV]
     const int d = 16 * jj + rr;
 #pragma unroll
     for (int b = 0; b < N; ++b)
-      if (b0 + b < p.B)
+      if (b0 + b < p.B) {
+        if (!p.pos_uniform) pos = p.pos[b0 + b];
         kv[(b0 + b) * p.kv_batch_stride + (hs - p.Hl - p.KVl) * p.kv_head_stride + vcache_offset(pos, d, D)] =
             __float2bfloat16_rn(v[b]);
+      }
   }
 }
 
@@ -1572,12 +1350,8 @@ constexpr size_t stream_smem() {
 
 template <int Bp>
 int32_t launch_bf16(Ctx* ctx, const GemvParams& p, cudaStream_t stream) {
-  if (g_variant == GEMV_MMA_SYNC)
-    LMB_CUDA(launch_k(gemv_mma_kernel<Bp / 8>, dim3(p.grid), dim3(kMmaThreads), stream_smem<Bp>(), stream, p, ctx->dev_err));
-  else if (p.cluster >= 1)
-    return launch_cluster<Bp>(ctx, p, stream);
-  else
-    LMB_CUDA(launch_k(gemv_tc_kernel<Bp>, dim3(p.grid), dim3(kTcThreads), stream_smem<Bp>(), stream, p, ctx->dev_err));
+  if (p.cluster >= 1) return launch_cluster<Bp>(ctx, p, stream);
+  LMB_CUDA(launch_k(gemv_tc_kernel<Bp>, dim3(p.grid), dim3(kTcThreads), stream_smem<Bp>(), stream, p, ctx->dev_err));
   ctx->launches++;
   return LMB200_OK;
 }
@@ -1587,7 +1361,7 @@ constexpr size_t kMaxXsBytes = 96 * 1024;
 
 }  // namespace
 
-void gemv_set_variant(int variant) { g_variant = variant == GEMV_MMA_SYNC ? GEMV_MMA_SYNC : GEMV_TCGEN05; }
+void gemv_set_variant(int variant) { (void)variant; g_variant = GEMV_TCGEN05; }
 int gemv_variant() { return g_variant; }
 
 void gemv_prefetch_next(GemvParams& p, const Ctx* ctx, int dtype, const void* next_W, int next_rows, int next_K,
@@ -1681,8 +1455,6 @@ int32_t gemv_configure() {
   LMB_CFG((gemv_ring_kernel<float, 1, kMtF32, 3>), kMaxSmem);
   LMB_CFG((gemv_ring_kernel<float, 2, kMtF32, 3>), kMaxSmem);
   LMB_CFG((gemv_ring_kernel<float, 4, kMtF32, 2>), kMaxSmem);
-  LMB_CFG(gemv_mma_kernel<2>, stream_smem<16>());
-  LMB_CFG(gemv_mma_kernel<4>, stream_smem<32>());
   LMB_CFG(gemv_tc_kernel<16>, stream_smem<16>());
   LMB_CFG(gemv_tc_kernel<32>, stream_smem<32>());
   LMB_CFG(gemv_cl_kernel<16>, cluster_smem<16>());

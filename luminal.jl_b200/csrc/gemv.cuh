@@ -64,11 +64,8 @@ struct InvScale {
   float eps = 0.f;
 };
 
-// bf16 kernel variants (float32 always runs the register-ring kernel)
-enum GemvVariant {
-  GEMV_TCGEN05 = 0,    // tcgen05.mma, accumulators in TMEM (default)
-  GEMV_MMA_SYNC = 1    // mma.sync m16n8k16 from ldmatrix
-};
+// bf16 kernel (float32 always runs the register-ring kernel): tcgen05.mma, accumulators in TMEM
+enum GemvVariant { GEMV_TCGEN05 = 0 };
 
 struct GemvParams {
   const void* W = nullptr;   // weights in Layout<WT>::w_offset order
@@ -99,7 +96,8 @@ struct GemvParams {
   int64_t kv_batch_stride = 0;
   int64_t kv_head_stride = 0;
   const float* inv_freq = nullptr;   // [D/2]
-  const int* pos = nullptr;          // device scalar: position the new key is written at
+  const int* pos = nullptr;          // device [B]: the position each sequence's new key is written at
+  int pos_uniform = 1;               // the host knows all B positions are equal (one sine / cosine per row)
   int Hl = 0, KVl = 0, D = 0;
   int rope = 1;                      // 0: no rotation (Whisper), q and k rows are only scaled
   float qk_scale = 1.f;              // multiplies q and k rows (Whisper: head_dim^-0.25, src/Whisper.jl:257)

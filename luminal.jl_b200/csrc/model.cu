@@ -369,7 +369,7 @@ __global__ void __launch_bounds__(kNormThreads) add_layernorm_kernel(float* __re
     const int tok = tokens[b];
     const bool ok = tok >= 0 && tok < vocab;
     const WT* er = embed + (int64_t)(ok ? tok : 0) * n;
-    const float* pr = pos_emb + (int64_t)(*pos) * n;
+    const float* pr = pos_emb + (int64_t)pos[b] * n;
     for (int i = tid; i < n; i += kNormThreads) {
       const float v = (ok ? to_f32(er[i]) : 0.f) + pr[i];
       xr[i] = v; row[i] = v; s1 += v;
@@ -478,12 +478,18 @@ __global__ void __launch_bounds__(kArgmaxThreads) argmax_step_kernel(const float
   }
 }
 
-__global__ void advance_kernel(int* pos, int* step_ctr, unsigned long long* peer_step) {
+// End of a step: every sequence whose position is below its limit moves on by one.  The limit is "never"
+// during decoding; while a ragged prompt is fed step by step it is the sequence's prompt end, so a sequence
+// whose prompt is over stays where it is (its lane of the batch then recomputes the same slot, harmlessly).
+__global__ void advance_kernel(int* pos, const int* limit, int B, int* step_ctr, unsigned long long* peer_step) {
   pdl_launch_dependents();
   pdl_wait();
-  *pos += 1;
-  *step_ctr += 1;
-  if (peer_step) *peer_step += 1;     // epoch base of the next step's in-kernel all-reduces
+  const int b = threadIdx.x;
+  if (b < B && pos[b] < limit[b]) pos[b] += 1;
+  if (b == 0) {
+    *step_ctr += 1;
+    if (peer_step) *peer_step += 1;     // epoch base of the next step's in-kernel all-reduces
+  }
 }
 
 
@@ -1166,7 +1172,7 @@ int32_t enqueue_step_t(Session* S, cudaStream_t st, bool with_head) {
       p.epi = EPI_QKV_ROPE;
       p.q_out = S->qbuf; p.q_pitch = S->q_pitch;
       p.kv_layer = kv_layer; p.kv_batch_stride = S->kv_batch_stride; p.kv_head_stride = S->kv_head_stride;
-      p.inv_freq = M->inv_freq; p.pos = S->pos; p.Hl = M->Hl; p.KVl = M->KVl; p.D = M->D;
+      p.inv_freq = M->inv_freq; p.pos = S->pos; p.pos_uniform = S->ragged ? 0 : 1; p.Hl = M->Hl; p.KVl = M->KVl; p.D = M->D;
       LMB_TRY(gemv_launch(ctx, dt, p, st));
     }
     {  // attention over the cache; the result is the tiled input of o_proj
@@ -1218,7 +1224,7 @@ int32_t enqueue_step_t(Session* S, cudaStream_t st, bool with_head) {
                       S->tokens, S->tok_hist, (const int*)S->step_ctr, B, S->stop));
     ctx->launches++;
   }
-  LMB_CUDA(launch_k(advance_kernel, dim3(1), dim3(1), 0, st, S->pos, S->step_ctr, ctx->peer_n > 1 ? ctx->peer_step : (unsigned long long*)nullptr));
+  LMB_CUDA(launch_k(advance_kernel, dim3(1), dim3(32), 0, st, S->pos, (const int*)S->limit, S->B, S->step_ctr, ctx->peer_n > 1 ? ctx->peer_step : (unsigned long long*)nullptr));
   ctx->launches++;
   return LMB200_OK;
 }
@@ -1279,7 +1285,7 @@ int32_t enqueue_step_fused(Session* S, cudaStream_t st, bool with_head) {
       p.epi = EPI_QKV_ROPE; p.inv = inv_scale();
       p.q_out = S->qbuf; p.q_pitch = S->q_pitch;
       p.kv_layer = kv_layer; p.kv_batch_stride = S->kv_batch_stride; p.kv_head_stride = S->kv_head_stride;
-      p.inv_freq = M->inv_freq; p.pos = S->pos; p.Hl = M->Hl; p.KVl = M->KVl; p.D = M->D;
+      p.inv_freq = M->inv_freq; p.pos = S->pos; p.pos_uniform = S->ragged ? 0 : 1; p.Hl = M->Hl; p.KVl = M->KVl; p.D = M->D;
       LMB_TRY(gemv_launch(ctx, dt, p, st));
     }
     {
@@ -1328,7 +1334,7 @@ int32_t enqueue_step_fused(Session* S, cudaStream_t st, bool with_head) {
                       S->tokens, S->tok_hist, (const int*)S->step_ctr, B, S->stop));
     ctx->launches++;
   }
-  LMB_CUDA(launch_k(advance_kernel, dim3(1), dim3(1), 0, st, S->pos, S->step_ctr, ctx->peer_n > 1 ? ctx->peer_step : (unsigned long long*)nullptr));
+  LMB_CUDA(launch_k(advance_kernel, dim3(1), dim3(32), 0, st, S->pos, (const int*)S->limit, S->B, S->step_ctr, ctx->peer_n > 1 ? ctx->peer_step : (unsigned long long*)nullptr));
   ctx->launches++;
   return LMB200_OK;
 }
@@ -1375,7 +1381,7 @@ int32_t enqueue_whisper_step_t(Session* S, cudaStream_t st, bool with_head) {
       p.epi = EPI_QKV_ROPE; p.rope = 0; p.qk_scale = qk_scale; p.bias = W.b_qkv;
       p.q_out = S->qbuf; p.q_pitch = S->q_pitch;
       p.kv_layer = kv_layer; p.kv_batch_stride = S->kv_batch_stride; p.kv_head_stride = S->kv_head_stride;
-      p.inv_freq = M->inv_freq; p.pos = S->pos; p.Hl = M->Hl; p.KVl = M->KVl; p.D = M->D;
+      p.inv_freq = M->inv_freq; p.pos = S->pos; p.pos_uniform = S->ragged ? 0 : 1; p.Hl = M->Hl; p.KVl = M->KVl; p.D = M->D;
       LMB_TRY(gemv_launch(ctx, dt, p, st));
     }
     LMB_TRY(attention(kv_layer, S->kv_batch_stride, S->kv_head_stride, S->pos, 0, S->keys_per_cta, S->nsplit));
@@ -1389,7 +1395,7 @@ int32_t enqueue_whisper_step_t(Session* S, cudaStream_t st, bool with_head) {
       GemvParams p = gemv_params(S, W.wq_cross, M->m_qc, S->p_qc, S->xn);
       p.epi = EPI_QKV_ROPE; p.rope = 0; p.qk_scale = qk_scale; p.bias = W.b_q_cross;
       p.q_out = S->qbuf; p.q_pitch = S->q_pitch;
-      p.kv_layer = nullptr; p.inv_freq = M->inv_freq; p.pos = S->pos; p.Hl = M->Hl; p.KVl = 0; p.D = M->D;
+      p.kv_layer = nullptr; p.inv_freq = M->inv_freq; p.pos = S->pos; p.pos_uniform = S->ragged ? 0 : 1; p.Hl = M->Hl; p.KVl = 0; p.D = M->D;
       LMB_TRY(gemv_launch(ctx, dt, p, st));
     }
     void* cross_layer = reinterpret_cast<char*>(S->cross_kv) + (int64_t)l * S->cross_layer_stride * M->esz;
@@ -1422,7 +1428,7 @@ int32_t enqueue_whisper_step_t(Session* S, cudaStream_t st, bool with_head) {
                       S->tokens, S->tok_hist, (const int*)S->step_ctr, B, S->stop));
     ctx->launches++;
   }
-  LMB_CUDA(launch_k(advance_kernel, dim3(1), dim3(1), 0, st, S->pos, S->step_ctr, (unsigned long long*)nullptr));
+  LMB_CUDA(launch_k(advance_kernel, dim3(1), dim3(32), 0, st, S->pos, (const int*)S->limit, S->B, S->step_ctr, (unsigned long long*)nullptr));
   ctx->launches++;
   return LMB200_OK;
 }
@@ -1497,12 +1503,48 @@ int32_t run_step(Session* S, bool with_head) {
   LMB_TRY(ensure_graphs(S));
   LMB_CUDA(cudaGraphLaunch(with_head ? S->graph_full : S->graph_body, ctx->stream));
   ctx->launches += with_head ? S->graph_nodes_full : S->graph_nodes_body;
-  S->host_pos += 1;
+  if (!S->in_ragged_prefill) {
+    S->host_pos += 1;
+    for (int& v : S->host_pos_v) v += 1;
+  }
   return LMB200_OK;
 }
 
 }  // namespace
 }  // namespace lmb
+
+// Positions live on the device, one per sequence; the host keeps a copy for its bounds checks.  `ragged`
+// (the positions differ) selects the per-sequence RoPE path of the kernels, so changing it drops the graphs.
+static int32_t push_positions(Session* S) {
+  Ctx* ctx = S->m->ctx;
+  bool ragged = false;
+  int mx = 0;
+  for (int b = 0; b < S->B; ++b) {
+    ragged = ragged || S->host_pos_v[b] != S->host_pos_v[0];
+    if (S->host_pos_v[b] > mx) mx = S->host_pos_v[b];
+  }
+  LMB_CUDA(cudaMemcpyAsync(S->pos, S->host_pos_v.data(), (size_t)S->B * 4, cudaMemcpyHostToDevice, ctx->stream));
+  LMB_CUDA(cudaStreamSynchronize(ctx->stream));
+  S->host_pos = mx;
+  if (ragged != S->ragged) {
+    drop_graphs(S);
+    S->ragged = ragged;
+  }
+  return LMB200_OK;
+}
+static int32_t set_all_positions(Session* S, int pos) {
+  S->host_pos_v.assign(S->B, pos);
+  return push_positions(S);
+}
+// limits == NULL: no limit (decoding)
+static int32_t set_limits(Session* S, const int* limits) {
+  Ctx* ctx = S->m->ctx;
+  std::vector<int> v(S->B, 0x7fffffff);
+  if (limits) v.assign(limits, limits + S->B);
+  LMB_CUDA(cudaMemcpyAsync(S->limit, v.data(), (size_t)S->B * 4, cudaMemcpyHostToDevice, ctx->stream));
+  LMB_CUDA(cudaStreamSynchronize(ctx->stream));
+  return LMB200_OK;
+}
 
 extern "C" int32_t lmb200_session_create(lmb200_model hm, int32_t batch, int32_t max_ctx, lmb200_session* out) {
   Model* M = model_from(hm);
@@ -1584,7 +1626,8 @@ extern "C" int32_t lmb200_session_create(lmb200_model hm, int32_t batch, int32_t
   alloc(&S->attn_out, x_elems(M->m_o.K) * M->esz);
   alloc(&S->act, x_elems(M->m_down.K) * M->esz);
   alloc((void**)&S->tokens, (int64_t)batch * 4);
-  alloc((void**)&S->pos, 4);
+  alloc((void**)&S->pos, (int64_t)batch * 4);
+  alloc((void**)&S->limit, (int64_t)batch * 4);
   alloc((void**)&S->step_ctr, 4);
   alloc((void**)&S->stop, (int64_t)(2 + batch) * 4);
   alloc((void**)&S->tok_hist, (int64_t)(S->cap + 1) * batch * 4);
@@ -1597,6 +1640,8 @@ extern "C" int32_t lmb200_session_create(lmb200_model hm, int32_t batch, int32_t
     alloc((void**)&S->xT, (int64_t)round_up(c.hidden, 128) * S->Bp * 4);
     alloc((void**)&S->ssq, (int64_t)256 * 32 * 4);
   }
+  S->host_pos_v.assign(batch, 0);
+  if (rc == LMB200_OK) rc = set_limits(S, nullptr);
   if (rc == LMB200_OK) {
     const int no_eot = -1;                                  // end-of-text stop disabled until lmb200_decode_until sets it
     if (cudaMemcpyAsync(S->stop, &no_eot, 4, cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess) rc = fail(LMB200_ECUDA, "session_create: copy failed");
@@ -1615,7 +1660,7 @@ extern "C" int32_t lmb200_session_destroy(lmb200_session h) {
   drop_graphs(S);
   cudaFree(S->cross_kv);
   cudaFree(S->kv); cudaFree(S->x); cudaFree(S->delta); cudaFree(S->logits); cudaFree(S->xn); cudaFree(S->qbuf);
-  cudaFree(S->attn_out); cudaFree(S->act); cudaFree(S->tokens); cudaFree(S->pos); cudaFree(S->step_ctr);
+  cudaFree(S->attn_out); cudaFree(S->act); cudaFree(S->tokens); cudaFree(S->pos); cudaFree(S->limit); cudaFree(S->step_ctr); cudaFree(S->ragged_logits);
   cudaFree(S->tok_hist); cudaFree(S->prompt); cudaFree(S->gemv_partials); cudaFree(S->gemv_counters);
   cudaFree(S->part_o); cudaFree(S->part_ml); cudaFree(S->attn_counters); cudaFree(S->prefill_buf); cudaFree(S->capture);
   cudaFree(S->xT); cudaFree(S->ssq); cudaFree(S->stop);
@@ -1629,11 +1674,8 @@ extern "C" int32_t lmb200_session_reset(lmb200_session h) {
   if (!S) return LMB200_EINVAL;
   Ctx* ctx = S->m->ctx;
   LMB_CUDA(cudaSetDevice(ctx->device));
-  LMB_CUDA(cudaMemsetAsync(S->pos, 0, 4, ctx->stream));
   LMB_CUDA(cudaMemsetAsync(S->step_ctr, 0, 4, ctx->stream));
-  LMB_CUDA(cudaStreamSynchronize(ctx->stream));
-  S->host_pos = 0;
-  return LMB200_OK;
+  return set_all_positions(S, 0);
 }
 
 extern "C" int32_t lmb200_session_position(lmb200_session h, int32_t* pos) {
@@ -1649,9 +1691,24 @@ extern "C" int32_t lmb200_session_set_position(lmb200_session h, int32_t pos) {
   LMB_REQUIRE(pos >= 0 && pos <= S->max_ctx, "set_position: %d outside 0..%d", pos, S->max_ctx);
   Ctx* ctx = S->m->ctx;
   LMB_CUDA(cudaSetDevice(ctx->device));
-  LMB_CUDA(cudaMemcpyAsync(S->pos, &pos, 4, cudaMemcpyHostToDevice, ctx->stream));
-  LMB_CUDA(cudaStreamSynchronize(ctx->stream));
-  S->host_pos = pos;
+  return set_all_positions(S, pos);
+}
+
+extern "C" int32_t lmb200_session_set_positions(lmb200_session h, const int32_t* pos) {
+  Session* S = session_from(h);
+  if (!S) return LMB200_EINVAL;
+  LMB_REQUIRE(pos, "set_positions: null argument");
+  for (int b = 0; b < S->B; ++b)
+    LMB_REQUIRE(pos[b] >= 0 && pos[b] <= S->max_ctx, "set_positions: sequence %d at %d, outside 0..%d", b, pos[b], S->max_ctx);
+  LMB_CUDA(cudaSetDevice(S->m->ctx->device));
+  S->host_pos_v.assign(pos, pos + S->B);
+  return push_positions(S);
+}
+
+extern "C" int32_t lmb200_session_positions(lmb200_session h, int32_t* pos_out) {
+  Session* S = session_from(h);
+  if (!S || !pos_out) return LMB200_EINVAL;
+  for (int b = 0; b < S->B; ++b) pos_out[b] = S->host_pos_v[b];
   return LMB200_OK;
 }
 
@@ -1716,10 +1773,7 @@ extern "C" int32_t lmb200_session_fill_kv_random(lmb200_session h, int32_t n_pos
       LMB_CUDA(cudaGetLastError());
     }
   }
-  LMB_CUDA(cudaMemcpyAsync(S->pos, &n_pos, 4, cudaMemcpyHostToDevice, ctx->stream));
-  LMB_CUDA(cudaStreamSynchronize(ctx->stream));
-  S->host_pos = n_pos;
-  return LMB200_OK;
+  return set_all_positions(S, n_pos);
 }
 
 extern "C" int32_t lmb200_session_set_capture(lmb200_session h, int32_t enable) {
@@ -1771,6 +1825,7 @@ extern "C" int32_t lmb200_prefill(lmb200_session h, const int32_t* tokens, int32
   Session* S = session_from(h);
   if (!S) return LMB200_EINVAL;
   LMB_REQUIRE(tokens && n >= 1, "prefill: null tokens or n < 1");
+  LMB_REQUIRE(!S->ragged, "prefill: the sequences are at different positions; use lmb200_prefill_ragged");
   LMB_TRY(tp_guard(S, "prefill"));
   if (S->host_pos + n > S->max_ctx)
     return fail(LMB200_ESTATE, "prefill: %d + %d tokens exceed max_ctx %d", S->host_pos, n, S->max_ctx);
@@ -1787,13 +1842,10 @@ extern "C" int32_t lmb200_prefill(lmb200_session h, const int32_t* tokens, int32
   if (prefill_gemm_ok(S, n)) {
     // every position at once: GEMMs + flash attention, then the head on the last position
     LMB_CUDA(cudaMemcpyAsync(S->prompt, tokens, (size_t)n * B * 4, cudaMemcpyHostToDevice, ctx->stream));
-    LMB_TRY(prefill_gemm(S, S->prompt, n, ctx->stream));
+    LMB_TRY(prefill_gemm(S, S->prompt, n, nullptr, ctx->stream));
     LMB_CUDA(cudaMemsetAsync(S->step_ctr, 0, 4, ctx->stream));
     LMB_TRY(enqueue_head_bf16(S, ctx->stream));
-    const int new_pos = S->host_pos + n;
-    LMB_CUDA(cudaMemcpyAsync(S->pos, &new_pos, 4, cudaMemcpyHostToDevice, ctx->stream));
-    LMB_CUDA(cudaStreamSynchronize(ctx->stream));
-    S->host_pos = new_pos;
+    LMB_TRY(set_all_positions(S, S->host_pos + n));
     if (logits_out) LMB_TRY(copy_logits_out(S, logits_out));
     LMB_CUDA(cudaStreamSynchronize(ctx->stream));
     return check_device_error(ctx);
@@ -1809,6 +1861,107 @@ extern "C" int32_t lmb200_prefill(lmb200_session h, const int32_t* tokens, int32
   }
   if (logits_out) LMB_TRY(copy_logits_out(S, logits_out));
   LMB_CUDA(cudaStreamSynchronize(ctx->stream));
+  return check_device_error(ctx);
+}
+
+// Prompts of different lengths in one batch (the reference's [batch, seq] token tensor, src/NN.jl:448-455, has one
+// length; a batch of real prompts does not).  tokens: [batch, n_max] row-major, sequence b uses its first lengths[b]
+// ids.  logits_out (NULL or [batch, vocab]): for every sequence the logits of ITS last prompt position.  Afterwards
+// sequence b stands at its old position + lengths[b] and decoding goes on with one position per sequence.
+// A fresh bf16 Llama / Phi-3 session runs all positions at once through the prompt GEMMs (the padding behind a short
+// prompt is computed and never read: attention is causal and later steps overwrite those cache slots); otherwise
+// the prompt goes through the decode step, a finished sequence standing still while the longer ones go on.
+extern "C" int32_t lmb200_prefill_ragged(lmb200_session h, const int32_t* tokens, const int32_t* lengths, int32_t n_max,
+                                         float* logits_out) {
+  Session* S = session_from(h);
+  if (!S) return LMB200_EINVAL;
+  LMB_REQUIRE(tokens && lengths && n_max >= 1, "prefill_ragged: null argument or n_max < 1");
+  LMB_TRY(tp_guard(S, "prefill_ragged"));
+  const int B = S->B;
+  int longest = 0;
+  for (int b = 0; b < B; ++b) {
+    LMB_REQUIRE(lengths[b] >= 1 && lengths[b] <= n_max, "prefill_ragged: sequence %d has length %d, outside 1..%d", b, lengths[b], n_max);
+    if (S->host_pos_v[b] + lengths[b] > S->max_ctx)
+      return fail(LMB200_ESTATE, "prefill_ragged: sequence %d: %d + %d tokens exceed max_ctx %d", b, S->host_pos_v[b], lengths[b], S->max_ctx);
+    if (lengths[b] > longest) longest = lengths[b];
+  }
+  Ctx* ctx = S->m->ctx;
+  LMB_CUDA(cudaSetDevice(ctx->device));
+  if ((int64_t)longest * B > S->prompt_cap) {
+    cudaFree(S->prompt);
+    S->prompt = nullptr;
+    S->prompt_cap = 0;
+    LMB_TRY(dmalloc((void**)&S->prompt, (int64_t)longest * B * 4, false, ctx->stream));
+    S->prompt_cap = (int64_t)longest * B;
+  }
+  std::vector<int> new_pos(B), limits(B);
+  for (int b = 0; b < B; ++b) new_pos[b] = limits[b] = S->host_pos_v[b] + lengths[b];
+  if (!S->ragged && prefill_gemm_ok(S, longest)) {
+    std::vector<int32_t> tk((size_t)longest * B, 0);            // [B, longest]
+    for (int b = 0; b < B; ++b)
+      for (int i = 0; i < lengths[b]; ++i) tk[(size_t)b * longest + i] = tokens[(size_t)b * n_max + i];
+    int* lens_dev = nullptr;
+    LMB_TRY(dmalloc((void**)&lens_dev, (int64_t)B * 4, false, ctx->stream));
+    int32_t rc = LMB200_OK;
+    if (cudaMemcpyAsync(S->prompt, tk.data(), tk.size() * 4, cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess ||
+        cudaMemcpyAsync(lens_dev, lengths, (size_t)B * 4, cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess)
+      rc = fail(LMB200_ECUDA, "prefill_ragged: upload failed");
+    if (rc == LMB200_OK) rc = prefill_gemm(S, S->prompt, longest, lens_dev, ctx->stream);
+    cudaStreamSynchronize(ctx->stream);
+    cudaFree(lens_dev);
+    LMB_TRY(rc);
+    LMB_CUDA(cudaMemsetAsync(S->step_ctr, 0, 4, ctx->stream));
+    LMB_TRY(enqueue_head_bf16(S, ctx->stream));
+    S->host_pos_v = new_pos;
+    LMB_TRY(push_positions(S));
+    if (logits_out) LMB_TRY(copy_logits_out(S, logits_out));
+    LMB_CUDA(cudaStreamSynchronize(ctx->stream));
+    return check_device_error(ctx);
+  }
+  // step by step: position-major token staging, the per-sequence limits stop a finished sequence
+  std::vector<int32_t> tr((size_t)longest * B, 0);              // [longest][B]
+  for (int b = 0; b < B; ++b)
+    for (int i = 0; i < lengths[b]; ++i) tr[(size_t)i * B + b] = tokens[(size_t)b * n_max + i];
+  LMB_CUDA(cudaMemcpyAsync(S->prompt, tr.data(), tr.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
+  LMB_CUDA(cudaMemsetAsync(S->step_ctr, 0, 4, ctx->stream));
+  if (logits_out && !S->ragged_logits)
+    LMB_TRY(dmalloc((void**)&S->ragged_logits, (int64_t)B * S->logits_pitch * 4, true, ctx->stream));
+  if (!S->ragged) {                                             // the steps below run with one position per sequence
+    LMB_CUDA(cudaStreamSynchronize(ctx->stream));
+    drop_graphs(S);
+    S->ragged = true;
+  }
+  LMB_TRY(set_limits(S, limits.data()));
+  S->in_ragged_prefill = true;
+  int32_t rc = LMB200_OK;
+  for (int i = 0; i < longest && rc == LMB200_OK; ++i) {
+    bool ends_here = false;
+    for (int b = 0; b < B; ++b) ends_here = ends_here || lengths[b] - 1 == i;
+    if (cudaMemcpyAsync(S->tokens, S->prompt + (int64_t)i * B, (size_t)B * 4, cudaMemcpyDeviceToDevice, ctx->stream) != cudaSuccess) {
+      rc = fail(LMB200_ECUDA, "prefill_ragged: token copy failed");
+      break;
+    }
+    rc = run_step(S, ends_here);
+    if (rc == LMB200_OK && ends_here && logits_out) {
+      for (int b = 0; b < B; ++b)
+        if (lengths[b] - 1 == i &&
+            cudaMemcpyAsync(S->ragged_logits + (int64_t)b * S->logits_pitch, S->logits + (int64_t)b * S->logits_pitch,
+                            (size_t)S->m->cfg.vocab * 4, cudaMemcpyDeviceToDevice, ctx->stream) != cudaSuccess)
+          rc = fail(LMB200_ECUDA, "prefill_ragged: logits copy failed");
+    }
+  }
+  S->in_ragged_prefill = false;
+  cudaStreamSynchronize(ctx->stream);
+  const int32_t rc2 = set_limits(S, nullptr);
+  LMB_TRY(rc);
+  LMB_TRY(rc2);
+  S->host_pos_v = new_pos;
+  LMB_TRY(push_positions(S));
+  if (logits_out) {
+    LMB_CUDA(cudaMemcpy2DAsync(logits_out, (size_t)S->m->cfg.vocab * 4, S->ragged_logits, (size_t)S->logits_pitch * 4,
+                               (size_t)S->m->cfg.vocab * 4, B, cudaMemcpyDeviceToHost, ctx->stream));
+    LMB_CUDA(cudaStreamSynchronize(ctx->stream));
+  }
   return check_device_error(ctx);
 }
 
@@ -1912,7 +2065,8 @@ extern "C" int32_t lmb200_decode_until(lmb200_session h, const int32_t* first_to
     --keep;
   }
   if (keep < done) {                                      // the session goes back to the step after the last useful one
-    LMB_TRY(lmb200_session_set_position(h, S->host_pos - (done - keep)));
+    for (int& v : S->host_pos_v) v -= done - keep;
+    LMB_TRY(push_positions(S));
   }
   if (tokens_out) memcpy(tokens_out, hist.data(), (size_t)keep * B * 4);
   *steps_done = keep;

@@ -76,7 +76,12 @@ struct Session {
   uint32_t magic = 0x53455353;
   Model* m = nullptr;
   int B = 0, max_ctx = 0, cap = 0;
-  int host_pos = 0;
+  int host_pos = 0;               // the furthest position of any sequence (bounds checks)
+  std::vector<int> host_pos_v;    // the host's copy of the per-sequence positions
+  bool ragged = false;            // the positions differ: kernels take the per-sequence RoPE path
+  bool in_ragged_prefill = false; // steps of lmb200_prefill_ragged: the host positions are set at its end
+  int* limit = nullptr;           // device [B]: a sequence at its limit does not advance
+  float* ragged_logits = nullptr; // [B][logits_pitch]: each sequence's logits at its own last prompt position
   // cache: [L][B][KVl][cap/16][32*D]
   void* kv = nullptr;
   int64_t kv_head_stride = 0, kv_batch_stride = 0, kv_layer_stride = 0;
@@ -91,7 +96,7 @@ struct Session {
   int Bp = 0;                   // batch padding of the tiled activation buffers (8, 16 or 32)
   int q_pitch = 0, logits_pitch = 0;
   int* tokens = nullptr;
-  int* pos = nullptr;
+  int* pos = nullptr;           // device [B]: one position per sequence
   int* step_ctr = nullptr;
   int* stop = nullptr;          // [0] end-of-text id or -1, [1] sequences that produced it, [2 + b] sequence b did
   int* tok_hist = nullptr;      // [cap][B]
@@ -130,7 +135,8 @@ int32_t step_kernels_configure();
 // prompt phase as GEMMs + flash attention (csrc/prefill.cu)
 int32_t prefill_configure();
 bool prefill_gemm_ok(const Session* S, int n);
-int32_t prefill_gemm(Session* S, const int* tokens_dev, int n, cudaStream_t st);
+// lens_dev: NULL (every sequence has n tokens) or device [B] prompt lengths <= n (the last-position rows are taken per sequence)
+int32_t prefill_gemm(Session* S, const int* tokens_dev, int n, const int* lens_dev, cudaStream_t st);
 int32_t prefill_linear(Ctx* ctx, const void* W, const float* x_dev, int T, int rows, int K, float* out_dev, cudaStream_t st);
 Model* model_from(lmb200_model h);
 Session* session_from(lmb200_session h);

@@ -429,9 +429,9 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(float* __restrict__ x
 
 // the residual rows of each sequence's last prompt position -> the decode step's [B, n] buffer
 __global__ void last_rows_kernel(float* __restrict__ dst, const float* __restrict__ x, const float* __restrict__ delta, int n_seq,
-                                 int n) {
+                                 int n, const int* __restrict__ lens) {
   const int b = blockIdx.x;
-  const int64_t t = (int64_t)b * n_seq + n_seq - 1;
+  const int64_t t = (int64_t)b * n_seq + (lens ? lens[b] : n_seq) - 1;
   for (int i = threadIdx.x; i < n; i += blockDim.x) dst[(int64_t)b * n + i] = x[t * n + i] + (delta ? delta[t * n + i] : 0.f);
 }
 
@@ -516,7 +516,7 @@ bool prefill_gemm_ok(const Session* S, int n) {
 
 // tokens_dev: [B, n] int32, sequence-major.  On return the cache holds positions 0..n-1 of every
 // sequence and S->x the residual rows of the last position (the caller runs the final norm + head).
-int32_t prefill_gemm(Session* S, const int* tokens_dev, int n, cudaStream_t st) {
+int32_t prefill_gemm(Session* S, const int* tokens_dev, int n, const int* lens_dev, cudaStream_t st) {
   Model* M = S->m;
   Ctx* ctx = M->ctx;
   const lmb200_model_config& c = M->cfg;
@@ -602,7 +602,7 @@ int32_t prefill_gemm(Session* S, const int* tokens_dev, int n, cudaStream_t st) 
       LMB_TRY(reduce(delta));
     }
   }
-  last_rows_kernel<<<B, 256, 0, st>>>(S->x, x, delta, n, hid);
+  last_rows_kernel<<<B, 256, 0, st>>>(S->x, x, delta, n, hid, lens_dev);
   ctx->launches++;
   LMB_CUDA(cudaGetLastError());
   LMB_CUDA(cudaStreamSynchronize(st));

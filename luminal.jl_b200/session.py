@@ -97,6 +97,31 @@ class Session:
     def set_position(self, pos):
         _lib.call("lmb200_session_set_position", self.handle, int(pos))
 
+    def positions(self):
+        """One position per sequence."""
+        p = (C.c_int32 * self.batch)()
+        _lib.call("lmb200_session_positions", self.handle, p)
+        return np.array(p[:], dtype=np.int32)
+
+    def set_positions(self, pos):
+        p = (C.c_int32 * self.batch)(*[int(v) for v in pos])
+        _lib.call("lmb200_session_set_positions", self.handle, p)
+
+    def prefill_ragged(self, prompts, want_logits=True):
+        """Prompts of different lengths, one per sequence (a list of 1-D id arrays).  Returns, per sequence,
+        the logits of its own last prompt position ([batch, vocab]); decoding then goes on with one position
+        per sequence."""
+        assert len(prompts) == self.batch
+        lens = np.array([len(p) for p in prompts], dtype=np.int32)
+        n_max = int(lens.max())
+        t = np.zeros((self.batch, n_max), dtype=np.int32)
+        for b, p in enumerate(prompts):
+            t[b, :len(p)] = np.asarray(p, dtype=np.int32)
+        logits = np.empty((self.batch, self.vocab), dtype=np.float32) if want_logits else None
+        _lib.call("lmb200_prefill_ragged", self.handle, t.ctypes.data_as(C.c_void_p), lens.ctypes.data_as(C.c_void_p), n_max,
+                  logits.ctypes.data_as(C.c_void_p) if want_logits else None)
+        return logits
+
     def fill_kv_random(self, n_pos, seed=1234):
         _lib.call("lmb200_session_fill_kv_random", self.handle, int(n_pos), int(seed))
 
@@ -245,7 +270,7 @@ def shard_layout(cfg_kwargs, matrix, tp_size=1, tp_rank=0):
 
 def linear_gemv(device, w, x, dtype="bf16", variant=0):
     """out[b, o] = sum_i x[b, i] * w[o, i] through the decode GEMV kernel (host arrays in and out).
-    variant (bf16): 0 = tcgen05/TMEM, 1 = mma.sync."""
+    variant is reserved (0)."""
     w = np.ascontiguousarray(np.asarray(w, dtype=np.float32))
     x = np.ascontiguousarray(np.asarray(x, dtype=np.float32))
     rows, K = w.shape
