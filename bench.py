@@ -477,6 +477,11 @@ def run_decode(args):
         }
         if parity is not None:
             line["tp_parity"] = parity
+            # what the 2 x layers reductions of a step move over NVLink, per GPU and direction: every rank stores its
+            # bf16 partial [hidden][32] into each of the N - 1 peers' regions (and receives as much)
+            line["nvlink"] = {"reductions_per_step": 2 * cfg["n_layers"],
+                              "bytes_out_per_step_per_gpu": 2 * cfg["n_layers"] * (world - 1) * CFG["hidden"] * 32 * 2,
+                              "protocol": "peer stores of bf16 partials + data polling inside the o_proj / down_proj kernels"}
         if args.prefill:
             line["prefill"] = None
         if not args.no_cpu_baseline and world == 1:

@@ -45,6 +45,8 @@ enum {
   LMB200_ENCCL = -4,
   LMB200_ESTATE = -5,    /* call order (e.g. decode past max_ctx) */
   LMB200_ETIMEOUT = -6,  /* a bounded device-side wait gave up */
+  LMB200_ENOMATCH = -8,  /* lmb200_match_decoder / lmb200_compile_node_list: the node list is not a decoder this
+                            backend fuses; the message names the first node that does not fit.  Run it node by node. */
   LMB200_ENOTFOUND = -7  /* a tensor name the model does not have (the reference skips tensors that
                             are not registered, src/Weights.jl:76-91) */
 };
@@ -341,6 +343,65 @@ int32_t lmb200_decode_n_device(lmb200_session session, const int32_t* first_toke
 /* Algorithmic HBM bytes of ONE decode step on this rank at context length T (weights read once
  * + KV cache read for T keys + KV written for one key). */
 int32_t lmb200_session_step_bytes(lmb200_session session, int32_t T, int64_t* bytes);
+
+/* ---------------------------------------------------------------------------------------------
+ * A graph as a backend sees it: Graph.nodes (src/Graph.jl:4-26) flattened into arrays, node n (1-based, in
+ * insertion = topological order) described by op[n-1], its inputs in_node[in_off[n-1] .. in_off[n]) (1-based
+ * ids of earlier nodes), its output shape shape[shape_off[n-1] .. shape_off[n]) and its op fields as doubles
+ * arg[arg_off[n-1] .. arg_off[n]):
+ *   SumReduce / MaxReduce: dim;  Permute: dims...;  Expand: dim, size;  Reshape: shape...;
+ *   Slice: (start, stop) per dim, 0-based half-open, an open end as any value >= 2^62;  Pad: (left, right) per dim;
+ *   Unfold: kernel..., stride..., dilation...;  Constant: value;  FlashAttentionOp: scale, causal;  others: none.
+ * Function("InputTensor" / "Gather" / "CumSum") are LMB200_NODE_INPUT / _GATHER / _CUMSUM (src/Ops.jl:4-110).
+ * ------------------------------------------------------------------------------------------ */
+enum {
+  LMB200_NODE_LOG2 = 0, LMB200_NODE_EXP2 = 1, LMB200_NODE_SIN = 2, LMB200_NODE_SQRT = 3, LMB200_NODE_COS = 4,
+  LMB200_NODE_RECIP = 5, LMB200_NODE_CONTIGUOUS = 6, LMB200_NODE_RELU = 7, LMB200_NODE_ADD = 8, LMB200_NODE_MUL = 9,
+  LMB200_NODE_MOD = 10, LMB200_NODE_MAX = 11, LMB200_NODE_LESSTHAN = 12, LMB200_NODE_FUSED_MUL_ADD = 13,
+  LMB200_NODE_FUSED_ADD_RELU = 14, LMB200_NODE_MATMUL = 15, LMB200_NODE_SUM_REDUCE = 16, LMB200_NODE_MAX_REDUCE = 17,
+  LMB200_NODE_PERMUTE = 18, LMB200_NODE_EXPAND = 19, LMB200_NODE_RESHAPE = 20, LMB200_NODE_SLICE = 21,
+  LMB200_NODE_PAD = 22, LMB200_NODE_UNFOLD = 23, LMB200_NODE_CONSTANT = 24, LMB200_NODE_INPUT = 25,
+  LMB200_NODE_GATHER = 26, LMB200_NODE_CUMSUM = 27, LMB200_NODE_FLASH_ATTENTION = 28, LMB200_NODE_OTHER = 29
+};
+typedef struct {
+  int32_t n_nodes;
+  int32_t reserved;
+  const int32_t* op;        /* [n_nodes] LMB200_NODE_* */
+  const int32_t* in_off;    /* [n_nodes + 1] */
+  const int32_t* in_node;
+  const int32_t* shape_off; /* [n_nodes + 1] */
+  const int64_t* shape;
+  const int32_t* arg_off;   /* [n_nodes + 1] */
+  const double* arg;
+} lmb200_node_list;
+typedef struct {
+  int32_t batch;        /* the shape the graph was traced for: tokens [batch, seq] */
+  int32_t seq;
+  int32_t prev_seq;     /* the position offset baked into the RoPE angles (src/NN.jl:253-262) */
+  int32_t tokens_node;  /* the input node the token ids enter through */
+  int32_t n_weights;    /* 3 + 9 * n_layers */
+  int32_t reserved;
+} lmb200_decoder_match;
+/* Recognises NN.Llama / NN.Phi3 (src/NN.jl:390-507) ending in the logits node output_id:
+ * lm_head(norm(block^L(embedding(tokens)))), every layer decomposed into primitives as src/NN.jl and
+ * src/HighLevelOps.jl build them.  No GPU is needed.  On success cfg holds the widths, head split, epsilon and
+ * RoPE base (dtype float32, tp_size 1), weight_nodes[k] (as many as fit in weight_capacity) the input node that
+ * plays the role of the k-th registry name of names_out ('\n'-separated, src/NN.jl:180-225, 433-445).  A graph
+ * that deviates anywhere returns LMB200_ENOMATCH and lmb200_last_error names the node and what was expected
+ * there; the reference has no such step: its compile() (src/Compiler.jl:181-364) runs whatever nodes it is given. */
+int32_t lmb200_match_decoder(const lmb200_node_list* list, int32_t output_id, lmb200_model_config* cfg,
+                             lmb200_decoder_match* info, int32_t* weight_nodes, int32_t weight_capacity,
+                             char* names_out, int64_t names_capacity);
+/* compile() for a graph lmb200_match_decoder recognises (replaces src/Compiler.jl:181-364 + the per-token
+ * re-execution of examples/llama.jl:39-99 for such a graph): matches, creates the model in `dtype`, sets every
+ * weight from node_data[node - 1] (host float32 in `layout`, shape = that node's; entries of other nodes may be
+ * NULL: graph.tensors filled by load_weights!, src/Weights.jl:60-114) and creates a session of `batch` sequences
+ * (0 = the graph's) with room for max_ctx positions.  The caller owns both handles.  The session starts at
+ * position 0, so a graph traced with prev_seq != 0 is refused (LMB200_ENOMATCH). */
+int32_t lmb200_compile_node_list(lmb200_ctx ctx, const lmb200_node_list* list, int32_t output_id,
+                                 const float* const* node_data, int32_t layout, int32_t dtype, int32_t batch,
+                                 int32_t max_ctx, lmb200_model* model_out, lmb200_session* session_out,
+                                 lmb200_decoder_match* info);
 
 /* Stand-alone split-KV decode attention over a cache in the session layout (tests, profiling),
  * asynchronous on the context's stream (lmb200_sync before reading the result).

@@ -312,6 +312,67 @@ function compile_b200(d::B200Device, cfg::ModelConfig, weights::Dict{String,<:Ar
     m, Session(m, cfg, batch, max_ctx)
 end
 
+# compile_b200 from the graph alone: Graph.nodes flattened into lmb200_node_list, recognised by the library's
+# structural matcher (lmb200_match_decoder) and turned into a model + session (lmb200_compile_node_list).  The
+# weights are whatever load_weights! put into graph.tensors (src/Weights.jl:60-114).  A graph the matcher does not
+# recognise raises B200Error with code -8 (LMB200_ENOMATCH): run it with compile() / execute() instead.
+struct NodeList                                     # lmb200_node_list, field for field
+    n_nodes::Int32; reserved::Int32
+    op::Ptr{Int32}; in_off::Ptr{Int32}; in_node::Ptr{Int32}; shape_off::Ptr{Int32}; shape::Ptr{Int64}
+    arg_off::Ptr{Int32}; arg::Ptr{Float64}
+end
+struct DecoderMatch                                 # lmb200_decoder_match
+    batch::Int32; seq::Int32; prev_seq::Int32; tokens_node::Int32; n_weights::Int32; reserved::Int32
+end
+const NODE_CODES = Dict{DataType,Int32}(
+    Luminal.Log2 => 0, Luminal.Exp2 => 1, Luminal.Sin => 2, Luminal.Sqrt => 3, Luminal.Cos => 4, Luminal.Recip => 5,
+    Luminal.Contiguous => 6, Luminal.ReLU => 7, Luminal.Add => 8, Luminal.Mul => 9, Luminal.Mod => 10, Luminal.Max => 11,
+    Luminal.LessThan => 12, Luminal.FusedMulAdd => 13, Luminal.FusedAddReLU => 14, Luminal.MatMul => 15,
+    Luminal.SumReduce => 16, Luminal.MaxReduce => 17, Luminal.Permute => 18, Luminal.Expand => 19, Luminal.Reshape => 20,
+    Luminal.Slice => 21, Luminal.Pad => 22, Luminal.Unfold => 23, Luminal.Constant => 24, Luminal.FlashAttentionOp => 28)
+const FUNCTION_CODES = Dict("InputTensor" => Int32(25), "Gather" => Int32(26), "CumSum" => Int32(27))
+node_code(op::Luminal.Op) = get(NODE_CODES, typeof(op), Int32(29))
+node_code(op::Luminal.Function) = get(FUNCTION_CODES, op.name, Int32(29))
+node_args(::Luminal.Op) = Float64[]
+node_args(op::Union{Luminal.SumReduce,Luminal.MaxReduce}) = Float64[op.dim]
+node_args(op::Luminal.Permute) = Float64.(op.dims)
+node_args(op::Luminal.Expand) = Float64[op.dim, op.size]
+node_args(op::Luminal.Reshape) = Float64.(op.shape)
+node_args(op::Luminal.Slice) = Float64[v for r in op.ranges for v in r]
+node_args(op::Luminal.Pad) = Float64[v for r in op.padding for v in r]
+node_args(op::Luminal.Unfold) = Float64[op.kernel_shape; op.stride_shape; op.dilation_shape]
+node_args(op::Luminal.Constant) = Float64[op.value]
+node_args(op::Luminal.FlashAttentionOp) = Float64[op.scale, op.causal]
+
+function compile_b200(d::B200Device, graph::Luminal.Graph, output_id::Integer; dtype::Integer=F32, batch::Integer=0,
+                      max_ctx::Integer=2048)
+    n = length(graph.nodes)
+    op = Int32[node_code(nd.op) for nd in graph.nodes]
+    in_off = Int32[0]; in_node = Int32[]; shape_off = Int32[0]; shape = Int64[]; arg_off = Int32[0]; arg = Float64[]
+    for (nd, st) in zip(graph.nodes, graph.shapes)
+        append!(in_node, Int32[i for (i, _, _) in nd.inputs]); push!(in_off, length(in_node))
+        append!(shape, Int64.(Luminal.realized_dims(st))); push!(shape_off, length(shape))
+        append!(arg, node_args(nd.op)); push!(arg_off, length(arg))
+    end
+    data = Ptr{Float32}[C_NULL for _ in 1:n]
+    keep = Any[]
+    for ((id, _), a) in graph.tensors
+        a isa Array{Float32} || continue
+        push!(keep, a); data[id] = pointer(a)
+    end
+    model = Ref{UInt64}(0); session = Ref{UInt64}(0); info = Ref(DecoderMatch(0, 0, 0, 0, 0, 0))
+    GC.@preserve op in_off in_node shape_off shape arg_off arg keep begin
+        nl = NodeList(n, 0, pointer(op), pointer(in_off), pointer(in_node), pointer(shape_off), pointer(shape),
+                      pointer(arg_off), pointer(arg))
+        check(ccall((:lmb200_compile_node_list, LIB), Int32,
+                    (UInt64, Ref{NodeList}, Int32, Ptr{Ptr{Float32}}, Int32, Int32, Int32, Int32, Ref{UInt64}, Ref{UInt64},
+                     Ref{DecoderMatch}),
+                    d.ctx, Ref(nl), output_id, data, COLMAJOR, dtype, batch, max_ctx, model, session, info))
+    end
+    vocab = Luminal.realized_dims(graph.shapes[output_id])[end]
+    Model(model[]), Session(session[], batch > 0 ? batch : info[].batch, vocab), info[]
+end
+
 # tensor parallelism: one process per GPU; rank 0 creates the id, the launcher broadcasts the 128 bytes
 function comm_unique_id()
     id = Vector{UInt8}(undef, 128)

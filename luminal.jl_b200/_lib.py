@@ -21,6 +21,7 @@ class LuminalB200Error(RuntimeError):
     def __init__(self, code, message):
         super().__init__(f"libluminal_b200 error {code}: {message}")
         self.code = code
+        self.message = message
 
 
 class ModelConfig(C.Structure):
@@ -106,6 +107,8 @@ SIGNATURES = {
     "lmb200_decode_until": [_u64, _vp, _i32, _i32, _vp, _pi32],
     "lmb200_decode_n_device": [_u64, _vp, _i32, _vp],
     "lmb200_session_step_bytes": [_u64, _i32, _pi64],
+    "lmb200_match_decoder": [_vp, _i32, _vp, _vp, _pi32, _i32, C.c_char_p, _i64],
+    "lmb200_compile_node_list": [_u64, _vp, _i32, _vp, _i32, _i32, _i32, _i32, C.POINTER(_u64), C.POINTER(_u64), _vp],
     "lmb200_decode_attention_splitkv": [_u64, _i32, _vp, _vp, _i32],
     "lmb200_session_kv_layer": [_u64, _i32, C.POINTER(_vp), _pi64, _pi64],
     "lmb200_decode_attention_noalloc": [_u64, _i32, _vp, _vp, _vp, _i64, _i64, _i32, _i32, _i32, _i32, _i32],

@@ -16,6 +16,7 @@
 namespace lmb {
 
 int32_t flash_tc_configure();
+int32_t flash_tc_f32_configure();
 
 static thread_local char g_err[1024] = "";
 
@@ -324,6 +325,7 @@ extern "C" int32_t lmb200_init(int32_t device, lmb200_ctx* out) {
   int32_t rc = gemv_configure();
   if (rc == LMB200_OK) rc = attn_configure();
   if (rc == LMB200_OK) rc = flash_tc_configure();
+  if (rc == LMB200_OK) rc = flash_tc_f32_configure();
   if (rc == LMB200_OK) rc = step_kernels_configure();
   if (rc == LMB200_OK) rc = prefill_configure();
   if (rc != LMB200_OK) { cudaFree(c->dev_broken); cudaFreeHost(c->dev_err); cudaStreamDestroy(c->own_stream); delete c; return rc; }

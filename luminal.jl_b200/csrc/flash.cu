@@ -14,6 +14,8 @@
 namespace lmb {
 // tensor-core kernel (flash_tc.cu)
 bool flash_tc_supported(int64_t D);
+int32_t flash_tc_f32_launch(Ctx* ctx, float* out, const float* q, const float* k, const float* v, int64_t BH, int64_t S, int64_t D,
+                            float scale, int causal);
 int32_t flash_tc_launch(Ctx* ctx, void* out, const void* q, const void* k, const void* v, int64_t BH, int64_t S, int64_t D,
                         float scale, int causal);
 namespace {
@@ -129,10 +131,15 @@ extern "C" int32_t lmb200_flash_attention(lmb200_ctx h, void* out, const void* q
   LMB_REQUIRE(out && q && k && v, "flash_attention: null pointer");
   LMB_REQUIRE(B >= 1 && H >= 1 && S >= 1 && B * H <= 65535, "flash_attention: bad shape");
   LMB_CUDA(cudaSetDevice(ctx->device));
-  if (dtype == LMB200_F32) return launch<float>(ctx, out, q, k, v, B * H, S, D, scale, causal);
+  // LMB200_FLASH_KERNEL=simple keeps the CUDA-core kernel (comparison runs)
+  const char* sel = getenv("LMB200_FLASH_KERNEL");
+  if (dtype == LMB200_F32) {
+    // float32 on the tensor cores: operands split into bf16 hi + lo, three MMAs per product (flash_tc_f32.cu)
+    if (flash_tc_supported(D) && !(sel && strcmp(sel, "simple") == 0))
+      return flash_tc_f32_launch(ctx, (float*)out, (const float*)q, (const float*)k, (const float*)v, B * H, S, D, scale, causal);
+    return launch<float>(ctx, out, q, k, v, B * H, S, D, scale, causal);
+  }
   if (dtype == LMB200_BF16) {
-    // LMB200_FLASH_KERNEL=simple keeps the CUDA-core kernel (comparison runs)
-    const char* sel = getenv("LMB200_FLASH_KERNEL");
     if (flash_tc_supported(D) && !(sel && strcmp(sel, "simple") == 0))
       return flash_tc_launch(ctx, out, q, k, v, B * H, S, D, scale, causal);
     return launch<__nv_bfloat16>(ctx, out, q, k, v, B * H, S, D, scale, causal);

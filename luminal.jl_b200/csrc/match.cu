@@ -1,0 +1,554 @@
+// Recognising a decoder-only transformer in a bare node list (host code only: no kernel here).
+//
+// The reference's only plugin seam is its graph: a backend sees Graph.nodes (src/Graph.jl:4-26), a flat,
+// topologically ordered list of primitive ops with every NN layer already decomposed (src/NN.jl,
+// src/HighLevelOps.jl).  lmb200_match_decoder walks such a list backwards from the logits node and recovers, by
+// structure alone -- no model object, no weight names -- what src/NN.jl:390-455 built: the layer count, the
+// widths, the head split, the RMSNorm epsilon, the RoPE base, and which input-tensor node plays which weight's
+// role.  lmb200_compile_node_list hands that to the fused session.  A graph that deviates anywhere (another
+// activation, a bias, a different mask) is refused with LMB200_ENOMATCH and a message naming the node; the caller
+// then runs it node by node.
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <set>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+
+namespace {
+
+struct NoMatch {
+  std::string what;
+};
+
+const char* kOpNames[] = {"Log2", "Exp2", "Sin", "Sqrt", "Cos", "Recip", "Contiguous", "ReLU", "Add", "Mul", "Mod", "Max",
+                          "LessThan", "FusedMulAdd", "FusedAddReLU", "MatMul", "SumReduce", "MaxReduce", "Permute", "Expand",
+                          "Reshape", "Slice", "Pad", "Unfold", "Constant", "InputTensor", "Gather", "CumSum",
+                          "FlashAttentionOp", "Other"};
+
+using Shape = std::vector<int64_t>;
+
+std::string shape_text(const Shape& s) {
+  std::string t = "[";
+  for (size_t i = 0; i < s.size(); ++i) t += (i ? ", " : "") + std::to_string(s[i]);
+  return t + "]";
+}
+
+[[noreturn]] void no_match(const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  throw NoMatch{buf};
+}
+
+// What one attention + MLP block resolved to: input-tensor node ids by role and the block's constants.
+struct Block {
+  int q = 0, k = 0, v = 0, o = 0, gate = 0, up = 0, down = 0, inp = 0, post = 0;
+  int64_t H = 0, KV = 0, D = 0, B = 0, S = 0;
+  double base = 0, eps = 0;
+  int64_t prev = 0;
+};
+
+struct Walker {
+  const lmb200_node_list& g;
+  explicit Walker(const lmb200_node_list& list) : g(list) {}
+
+  int op(int i) const { return g.op[i - 1]; }
+  int n_in(int i) const { return g.in_off[i] - g.in_off[i - 1]; }
+  int in(int i, int k) const { return g.in_node[g.in_off[i - 1] + k]; }
+  std::vector<int> ins(int i) const {
+    return std::vector<int>(g.in_node + g.in_off[i - 1], g.in_node + g.in_off[i]);
+  }
+  Shape shape(int i) const { return Shape(g.shape + g.shape_off[i - 1], g.shape + g.shape_off[i]); }
+  int n_arg(int i) const { return g.arg_off[i] - g.arg_off[i - 1]; }
+  double arg(int i, int k) const { return g.arg[g.arg_off[i - 1] + k]; }
+  std::vector<int64_t> iargs(int i) const {
+    std::vector<int64_t> a;
+    for (int k = 0; k < n_arg(i); ++k) {          // an open slice end arrives as typemax(Int): clamp before the cast
+      double v = arg(i, k);
+      a.push_back(v >= 4.6e18 ? (int64_t)1 << 62 : v <= -4.6e18 ? -((int64_t)1 << 62) : (int64_t)v);
+    }
+    return a;
+  }
+
+  [[noreturn]] void fail(int i, const std::string& what) const {
+    int o = op(i);
+    no_match("node %d (%s%s): expected %s", i, o >= 0 && o <= LMB200_NODE_OTHER ? kOpNames[o] : "?",
+             shape_text(shape(i)).c_str(), what.c_str());
+  }
+  std::vector<int> expect(int i, int code, const char* what = nullptr) const {
+    if (op(i) != code) fail(i, what ? what : kOpNames[code]);
+    return ins(i);
+  }
+  int expect1(int i, int code, const char* what = nullptr) const {
+    auto v = expect(i, code, what);
+    if (v.size() != 1) fail(i, what ? what : kOpNames[code]);
+    return v[0];
+  }
+  void expect2(int i, int code, const char* what, int& a, int& b) const {
+    auto v = expect(i, code, what);
+    if (v.size() != 2) fail(i, what);
+    a = v[0];
+    b = v[1];
+  }
+  bool is_input(int i) const { return op(i) == LMB200_NODE_INPUT; }
+  bool is_const(int i) const { return op(i) == LMB200_NODE_CONSTANT && n_arg(i) == 1; }
+  double cval(int i) const { return arg(i, 0); }
+  // Binary node with one Constant operand (either side) -> the other operand and the value.
+  int with_const(int i, int code, const char* what, double& value) const {
+    int a, b;
+    expect2(i, code, what, a, b);
+    if (is_const(b)) { value = cval(b); return a; }
+    if (is_const(a)) { value = cval(a); return b; }
+    fail(i, what);
+  }
+  int skip(int i, int code) const {
+    while (op(i) == code && n_in(i) >= 1) i = in(i, 0);
+    return i;
+  }
+  bool permute_is(int i, std::initializer_list<int64_t> dims) const {
+    return op(i) == LMB200_NODE_PERMUTE && iargs(i) == std::vector<int64_t>(dims);
+  }
+
+  // MatMul(x, Permute[2,1](W)) with W a rank-2 input tensor and no bias (src/NN.jl:23-35).
+  void linear(int i, int& x, int& w) const {
+    int wt;
+    expect2(i, LMB200_NODE_MATMUL, "a Linear's MatMul", x, wt);
+    if (!permute_is(wt, {2, 1})) fail(wt, "Permute[2,1] of a weight");
+    w = in(wt, 0);
+    if (!(is_input(w) && shape(w).size() == 2)) fail(w, "a [out, in] weight input");
+  }
+
+  // x * expand(recip(sqrt(sum(x*x)*(1/n) + eps))) * expand(g)   (src/NN.jl:138-173 with mean_norm off,
+  // src/HighLevelOps.jl:296-300)
+  void rmsnorm(int i, int& x, int& gain, double& eps) const {
+    int a, b;
+    expect2(i, LMB200_NODE_MUL, "RMSNorm's scale by the gain", a, b);
+    gain = skip(b, LMB200_NODE_EXPAND);
+    if (!(is_input(gain) && shape(gain).size() == 1)) {
+      std::swap(a, b);
+      gain = skip(b, LMB200_NODE_EXPAND);
+    }
+    if (!(is_input(gain) && shape(gain).size() == 1)) fail(i, "RMSNorm's scale by a [hidden] gain");
+    int inv;
+    expect2(a, LMB200_NODE_MUL, "x * inv_rms", x, inv);
+    int ex = expect1(inv, LMB200_NODE_EXPAND, "expand(inv_rms)");
+    int sq = expect1(ex, LMB200_NODE_RECIP, "recip(sqrt(...))");
+    int ms = expect1(sq, LMB200_NODE_SQRT, "sqrt(mean + eps)");
+    int mean = with_const(ms, LMB200_NODE_ADD, "mean + eps", eps);
+    double inv_n;
+    int total = with_const(mean, LMB200_NODE_MUL, "sum * (1/n)", inv_n);
+    Shape xs = shape(x);
+    if (xs.empty()) fail(x, "a tensor to normalise");
+    int64_t n = xs.back();
+    if (std::fabs(inv_n * (double)n - 1.0) > 1e-5) fail(mean, "sum * (1/" + std::to_string(n) + ")");
+    if (!(op(total) == LMB200_NODE_SUM_REDUCE && n_arg(total) == 1 && (int64_t)arg(total, 0) == (int64_t)xs.size()))
+      fail(total, "sum over the last dim");
+    int p, q;
+    expect2(in(total, 0), LMB200_NODE_MUL, "x * x", p, q);
+    if (!(p == q && p == x)) fail(in(total, 0), "x * x of the normalised tensor");
+    if (shape(gain)[0] != n) fail(gain, "a gain of length " + std::to_string(n));
+  }
+
+  // a * (1 * recip(1 + exp2(a * -1 * (1/ln 2))))   (src/HighLevelOps.jl:153-160)
+  int silu(int i) const {
+    int a, s;
+    expect2(i, LMB200_NODE_MUL, "silu(gate)", a, s);
+    double one, one2, k, m1;
+    int r = with_const(s, LMB200_NODE_MUL, "1 / (1 + exp2(..))", one);
+    int den = expect1(r, LMB200_NODE_RECIP, "recip(1 + exp2(..))");
+    int e = with_const(den, LMB200_NODE_ADD, "1 + exp2(..)", one2);
+    int ar = expect1(e, LMB200_NODE_EXP2, "exp2(-a / ln 2)");
+    int neg = with_const(ar, LMB200_NODE_MUL, "(-a) * (1/ln 2)", k);
+    int src = with_const(neg, LMB200_NODE_MUL, "a * -1", m1);
+    if (!(one == 1.0 && one2 == 1.0 && m1 == -1.0 && std::fabs(k - 1.0 / std::log(2.0)) < 1e-6 && src == a))
+      fail(i, "silu(gate) with the reference's constants");
+    return a;
+  }
+
+  // arange(n): cumsum(expand(1, n)) - 1, or expand(0, 1) for n == 1   (src/HighLevelOps.jl:336-345)
+  int64_t arange(int i) const {
+    if (op(i) == LMB200_NODE_EXPAND) {
+      if (n_in(i) == 1 && is_const(in(i, 0)) && cval(in(i, 0)) == 0.0 && shape(i) == Shape{1}) return 1;
+      fail(i, "arange(1)");
+    }
+    double m1;
+    int c = with_const(i, LMB200_NODE_ADD, "cumsum(ones) - 1", m1);
+    if (!(m1 == -1.0 && op(c) == LMB200_NODE_CUMSUM && n_in(c) == 1)) fail(i, "cumsum(ones) - 1");
+    int ones = expect1(in(c, 0), LMB200_NODE_EXPAND, "expand(1, n)");
+    if (!(is_const(ones) && cval(ones) == 1.0 && shape(c).size() == 1)) fail(c, "cumsum over expand(1, n)");
+    return shape(c)[0];
+  }
+
+  // (lo, hi) of the last dimension of a Slice / Pad node's argument list
+  bool last_pair_is(int i, int64_t lo, int64_t hi, bool others_zero) const {
+    auto a = iargs(i);
+    if (a.size() < 2 || a.size() % 2) return false;
+    if (a[a.size() - 2] != lo || a[a.size() - 1] != hi) return false;
+    if (others_zero)
+      for (size_t k = 0; k + 2 < a.size(); ++k)
+        if (a[k] != 0) return false;
+    return true;
+  }
+
+  // apply_rotary_embeddings (src/NN.jl:253-303): the half-split rotation of pairs (j, j + D/2) that the
+  // column-major reshape to [.., D/2, 2] produces.
+  void rope(int i, int& src, double& base, int64_t& prev) const {
+    Shape shp = shape(i);
+    if (shp.size() != 4 || shp[3] % 2) fail(i, "RoPE output [batch, heads, seq, head_dim]");
+    int64_t D = shp[3], half = D / 2;
+    int cat = expect1(i, LMB200_NODE_RESHAPE, "reshape of the rotated pairs");
+    int pa, pb;
+    expect2(cat, LMB200_NODE_ADD, "concat of the two halves", pa, pb);
+    int outs[2];
+    const int parts[2] = {pa, pb};
+    const int64_t want[2][2] = {{0, 1}, {1, 0}};
+    for (int h = 0; h < 2; ++h) {
+      int e = expect1(parts[h], LMB200_NODE_PAD, "pad of one half");
+      if (!last_pair_is(parts[h], want[h][0], want[h][1], true)) fail(parts[h], "pad of one slot along the pair dim");
+      outs[h] = expect1(e, LMB200_NODE_EXPAND, "expand(.., 5, 1)");
+    }
+    // x0' = x0 cos - x1 sin ; x1' = x0 sin + x1 cos
+    int t0, t1, x0, cosn, x1, sinn, u0, u1;
+    expect2(outs[0], LMB200_NODE_ADD, "x0*cos - x1*sin", t0, t1);
+    expect2(t0, LMB200_NODE_MUL, "x0 * cos", x0, cosn);
+    double neg;
+    int m = with_const(t1, LMB200_NODE_MUL, "-(x1 * sin)", neg);
+    expect2(m, LMB200_NODE_MUL, "x1 * sin", x1, sinn);
+    expect2(outs[1], LMB200_NODE_ADD, "x0*sin + x1*cos", u0, u1);
+    if (neg != -1.0 || op(u0) != LMB200_NODE_MUL || ins(u0) != std::vector<int>{x0, sinn} || op(u1) != LMB200_NODE_MUL ||
+        ins(u1) != std::vector<int>{x1, cosn})
+      fail(outs[1], "the rotation's second row over the same x0, x1, sin, cos");
+    int ang = expect1(sinn, LMB200_NODE_SIN, "sin(angle)");
+    int shifted = expect1(cosn, LMB200_NODE_SIN, "cos as sin(pi/2 - angle)");
+    double hp, m1;
+    int na = with_const(shifted, LMB200_NODE_ADD, "pi/2 - angle", hp);
+    int a2 = with_const(na, LMB200_NODE_MUL, "angle * -1", m1);
+    if (a2 != ang || m1 != -1.0 || std::fabs(hp - M_PI / 2) > 1e-6) fail(cosn, "sin(pi/2 - angle) of the same angle");
+    int srcs[2];
+    const int xs[2] = {x0, x1};
+    for (int h = 0; h < 2; ++h) {
+      int s = expect1(skip(xs[h], LMB200_NODE_CONTIGUOUS), LMB200_NODE_RESHAPE, "reshape of one pair element");
+      if (!(op(s) == LMB200_NODE_SLICE && last_pair_is(s, h, h + 1, false))) fail(s, "slice of one element of the pair dim");
+      int sp = in(s, 0);
+      Shape wantshape = {shp[0], shp[1], shp[2], half, 2};
+      if (!(op(sp) == LMB200_NODE_RESHAPE && shape(sp) == wantshape)) fail(sp, "reshape to [.., D/2, 2]");
+      srcs[h] = in(sp, 0);
+    }
+    if (srcs[0] != srcs[1]) fail(i, "both pair elements from one tensor");
+    int emb = skip(ang, LMB200_NODE_EXPAND);
+    int pcol, frow;
+    expect2(emb, LMB200_NODE_MATMUL, "positions x inverse frequencies", pcol, frow);
+    double prevd;
+    int pos = with_const(expect1(pcol, LMB200_NODE_EXPAND, "positions as a column"), LMB200_NODE_ADD, "arange(seq) + prev_seq", prevd);
+    if (arange(pos) != shp[2] || prevd != std::floor(prevd) || prevd < 0) fail(pos, "arange(seq) + a whole prev_seq");
+    int inv = expect1(expect1(frow, LMB200_NODE_EXPAND, "frequencies as a row"), LMB200_NODE_RECIP, "1 / base^(2j/D)");
+    double lb, inv_d, two;
+    int fr = with_const(expect1(inv, LMB200_NODE_EXP2, "exp2(log2(base) * 2j/D)"), LMB200_NODE_MUL, "freqs * log2(base)", lb);
+    int f2 = with_const(fr, LMB200_NODE_MUL, "(2j) / D", inv_d);
+    int ar = with_const(f2, LMB200_NODE_MUL, "2 * j", two);
+    if (two != 2.0 || std::fabs(inv_d * (double)D - 1.0) > 1e-5 || arange(ar) != half) fail(fr, "arange(D/2) * 2 / D");
+    // the graph holds log2(base) rounded to float32: snap back to the whole number it came from
+    base = std::exp2(lb);
+    if (base < std::exp2(40.0) && (double)log2f((float)std::round(base)) == lb) base = std::round(base);
+    src = srcs[0];
+    prev = (int64_t)prevd;
+  }
+
+  // expand(expand(triu(seq, 1) * -1e9))   (src/NN.jl:368-373, src/HighLevelOps.jl:347-361)
+  void causal_mask(int i, int64_t seq) const {
+    int m = skip(i, LMB200_NODE_EXPAND);
+    double big, zero;
+    int tri = with_const(m, LMB200_NODE_MUL, "triu * -1e9", big);
+    int v, hh;
+    expect2(tri, LMB200_NODE_LESSTHAN, "column index > row index", v, hh);
+    int h = with_const(hh, LMB200_NODE_ADD, "row index - 0", zero);
+    bool ok = big == -1e9 && zero == 0.0 && op(h) == LMB200_NODE_EXPAND && op(v) == LMB200_NODE_EXPAND && n_arg(h) == 2 &&
+              n_arg(v) == 2 && (int64_t)arg(h, 0) == 1 && (int64_t)arg(v, 0) == 2;
+    if (ok) ok = arange(in(h, 0)) == seq && arange(in(v, 0)) == seq && shape(tri) == Shape{seq, seq};
+    if (!ok) fail(i, "the strict upper-triangular mask of size " + std::to_string(seq));
+  }
+
+  // exp2((a - expand(max a)) / ln 2) * recip(expand(sum ..)) over dim 4   (src/HighLevelOps.jl:318-327)
+  int softmax_last(int i) const {
+    int e, r;
+    expect2(i, LMB200_NODE_MUL, "softmax's e / sum(e)", e, r);
+    int s = expect1(expect1(r, LMB200_NODE_RECIP, "1 / sum(e)"), LMB200_NODE_EXPAND, "expand(sum(e))");
+    if (!(op(s) == LMB200_NODE_SUM_REDUCE && n_arg(s) == 1 && (int64_t)arg(s, 0) == 4 && ins(s) == std::vector<int>{e}))
+      fail(s, "sum(e) over the key dim");
+    double k, m1;
+    int d = with_const(expect1(e, LMB200_NODE_EXP2, "exp2(..)"), LMB200_NODE_MUL, "(a - max) * (1/ln 2)", k);
+    int a, nm;
+    expect2(d, LMB200_NODE_ADD, "a - max", a, nm);
+    int mx = with_const(nm, LMB200_NODE_MUL, "max * -1", m1);
+    int red = expect1(mx, LMB200_NODE_EXPAND, "expand(max)");
+    if (!(std::fabs(k - 1.0 / std::log(2.0)) < 1e-6 && m1 == -1.0 && op(red) == LMB200_NODE_MAX_REDUCE && n_arg(red) == 1 &&
+          (int64_t)arg(red, 0) == 4 && ins(red) == std::vector<int>{a}))
+      fail(i, "a softmax over the key dim");
+    return a;
+  }
+
+  // permute[1,3,2,4](reshape[B,S,heads,D](Linear(x)))
+  void split_heads(int i, int& w, int64_t& heads, int64_t& D, int& x) const {
+    if (!permute_is(i, {1, 3, 2, 4})) fail(i, "permute [1,3,2,4] of the head split");
+    int rs = in(i, 0);
+    int lin = expect1(rs, LMB200_NODE_RESHAPE, "reshape to [batch, seq, heads, head_dim]");
+    linear(lin, x, w);
+    Shape s = shape(rs);
+    if (s.size() != 4) fail(rs, "reshape to [batch, seq, heads, head_dim]");
+    heads = s[2];
+    D = s[3];
+  }
+
+  // repeat_kv (src/NN.jl:305-317): reshape[B,H,S,D](expand(x, 3, groups)), or x itself when groups == 1
+  int repeated(int i, int64_t H) const {
+    Shape s = shape(i);
+    if (s.size() == 4 && s[1] == H && op(i) == LMB200_NODE_RESHAPE && op(in(i, 0)) == LMB200_NODE_EXPAND) {
+      int e = in(i, 0);
+      Shape inner = shape(in(e, 0));
+      if (!(n_arg(e) == 2 && (int64_t)arg(e, 0) == 3 && inner.size() >= 2 && (int64_t)arg(e, 1) * inner[1] == H))
+        fail(e, "expand(kv, 3, heads / kv_heads)");
+      return in(e, 0);
+    }
+    return i;
+  }
+
+  // SelfAttention's output projection and everything under it down to the tensor the q, k and v projections
+  // read (src/NN.jl:320-387)
+  int attention(int i, Block& p) const {
+    int ctx;
+    linear(i, ctx, p.o);
+    Shape cs = shape(ctx);
+    if (cs.size() != 3) fail(ctx, "attention output [batch, seq, hidden]");
+    int64_t B = cs[0], S = cs[1], hidden = cs[2];
+    int pv = expect1(ctx, LMB200_NODE_RESHAPE, "reshape to [batch, seq, hidden]");
+    if (!permute_is(pv, {1, 3, 2, 4})) fail(pv, "permute [1,3,2,4] of the attention output");
+    int probs, vals;
+    expect2(in(pv, 0), LMB200_NODE_MATMUL, "probs x values", probs, vals);
+    Shape ps = shape(probs);
+    if (ps.size() != 4) fail(probs, "probabilities [batch, heads, seq, keys]");
+    int64_t H = ps[1];
+    int scores = softmax_last(probs);
+    if (S > 1) {
+      int sc, mask;
+      expect2(scores, LMB200_NODE_ADD, "scores + causal mask", sc, mask);
+      causal_mask(mask, S);
+      scores = sc;
+    }
+    double scale;
+    int qk = with_const(scores, LMB200_NODE_MUL, "q.k * 1/sqrt(head_dim)", scale);
+    int q, kt;
+    expect2(qk, LMB200_NODE_MATMUL, "queries x keys^T", q, kt);
+    if (!permute_is(kt, {1, 2, 4, 3})) fail(kt, "permute [1,2,4,3] of the keys");
+    int q_in, k_in;
+    double base_q, base_k;
+    int64_t prev_q, prev_k;
+    rope(q, q_in, base_q, prev_q);
+    rope(repeated(in(kt, 0), H), k_in, base_k, prev_k);
+    int xq, xk, xv;
+    int64_t Hq, D, KV, Dk, KVv, Dv;
+    split_heads(q_in, p.q, Hq, D, xq);
+    split_heads(k_in, p.k, KV, Dk, xk);
+    split_heads(repeated(vals, H), p.v, KVv, Dv, xv);
+    if (!(xq == xk && xk == xv)) fail(i, "q, k and v projections of one tensor");
+    if (!(Hq == H && D == Dk && D == Dv && KV == KVv && KV > 0 && H % KV == 0 && H * D == hidden && base_q == base_k &&
+          prev_q == prev_k && std::fabs(scale * std::sqrt((double)D) - 1.0) < 1e-5))
+      fail(i, "consistent head counts, head_dim, RoPE base and 1/sqrt(head_dim) scale");
+    p.H = H; p.KV = KV; p.D = D; p.base = base_q; p.prev = prev_q; p.B = B; p.S = S;
+    return xq;
+  }
+
+  // TransformerBlock (src/NN.jl:390-414): x + attn(norm(x)), then + mlp(norm(.)) -> the block's input
+  int block(int i, Block& p) const {
+    int h, ff;
+    expect2(i, LMB200_NODE_ADD, "residual + mlp", h, ff);
+    int act;
+    linear(ff, act, p.down);
+    int sg, up;
+    expect2(act, LMB200_NODE_MUL, "silu(gate) * up", sg, up);
+    int gate = silu(sg);
+    int n2, n2b;
+    linear(gate, n2, p.gate);
+    linear(up, n2b, p.up);
+    int h2;
+    double eps2;
+    rmsnorm(n2, h2, p.post, eps2);
+    if (n2 != n2b || h2 != h) fail(ff, "gate and up projections of one normalised residual");
+    int x, at;
+    expect2(h, LMB200_NODE_ADD, "residual + attention", x, at);
+    int n1 = attention(at, p);
+    int x1;
+    double eps1;
+    rmsnorm(n1, x1, p.inp, eps1);
+    if (x1 != x || eps1 != eps2) fail(at, "attention over the normalised block input, one epsilon per block");
+    p.eps = eps1;
+    return x;
+  }
+};
+
+struct Role {
+  int Block::*node;
+  const char* name;
+};
+const Role kRoles[] = {{&Block::q, "self_attn.q_proj"},  {&Block::k, "self_attn.k_proj"}, {&Block::v, "self_attn.v_proj"},
+                       {&Block::o, "self_attn.o_proj"},  {&Block::gate, "mlp.gate_proj"}, {&Block::up, "mlp.up_proj"},
+                       {&Block::down, "mlp.down_proj"},  {&Block::inp, "input_layernorm"},
+                       {&Block::post, "post_attention_layernorm"}};
+
+void validate_list(const lmb200_node_list* g) {
+  if (!g || g->n_nodes <= 0 || !g->op || !g->in_off || !g->shape_off || !g->arg_off) no_match("empty or incomplete node list");
+  for (int n = 1; n <= g->n_nodes; ++n) {
+    if (g->in_off[n] < g->in_off[n - 1] || g->shape_off[n] < g->shape_off[n - 1] || g->arg_off[n] < g->arg_off[n - 1])
+      no_match("node %d: offsets run backwards", n);
+    if (g->op[n - 1] < 0 || g->op[n - 1] > LMB200_NODE_OTHER) no_match("node %d: unknown op code %d", n, g->op[n - 1]);
+    for (int k = g->in_off[n - 1]; k < g->in_off[n]; ++k)
+      if (g->in_node[k] < 1 || g->in_node[k] >= n) no_match("node %d: input %d is not an earlier node", n, g->in_node[k]);
+  }
+}
+
+struct Match {
+  lmb200_model_config cfg{};
+  lmb200_decoder_match info{};
+  std::vector<std::pair<std::string, int>> weights;
+};
+
+Match match_decoder(const lmb200_node_list* g, int output_id) {
+  validate_list(g);
+  Walker w(*g);
+  if (output_id < 1 || output_id > g->n_nodes) no_match("no node %d", output_id);
+  int normed, w_head, x, g_final;
+  double eps;
+  w.linear(output_id, normed, w_head);
+  w.rmsnorm(normed, x, g_final, eps);
+  std::vector<Block> layers;
+  while (w.op(x) != LMB200_NODE_GATHER) {
+    if (w.op(x) != LMB200_NODE_ADD) w.fail(x, "a transformer block's residual sum, or the embedding gather");
+    Block b;
+    x = w.block(x, b);
+    layers.push_back(b);
+  }
+  if (layers.empty()) no_match("no transformer block between the embedding and the final norm");
+  std::vector<Block> ordered(layers.rbegin(), layers.rend());
+  if (w.n_in(x) != 2) w.fail(x, "gather(embedding table input, token input)");
+  int table = w.in(x, 0), tokens = w.in(x, 1);
+  if (!(w.is_input(table) && w.shape(table).size() == 2 && w.is_input(tokens)))
+    w.fail(x, "gather(embedding table input, token input)");
+  const Block& f = ordered[0];
+  for (size_t n = 0; n < ordered.size(); ++n) {
+    const Block& p = ordered[n];
+    bool same = p.H == f.H && p.KV == f.KV && p.D == f.D && p.base == f.base && p.prev == f.prev && p.B == f.B && p.S == f.S &&
+                p.eps == eps;
+    for (const Role& r : kRoles) same = same && w.shape(p.*(r.node)) == w.shape(f.*(r.node));
+    if (!same) no_match("block %zu differs from block 0 in its head split, widths, epsilon or RoPE constants", n);
+  }
+  int64_t hidden = f.H * f.D, inter = w.shape(f.gate)[0];
+  struct { int node; Shape want; const char* role; } checks[] = {
+      {f.q, {hidden, hidden}, "q"},       {f.k, {f.KV * f.D, hidden}, "k"}, {f.v, {f.KV * f.D, hidden}, "v"},
+      {f.o, {hidden, hidden}, "o"},       {f.gate, {inter, hidden}, "gate"}, {f.up, {inter, hidden}, "up"},
+      {f.down, {hidden, inter}, "down"}};
+  for (auto& c : checks)
+    if (w.shape(c.node) != c.want) w.fail(c.node, std::string(c.role) + " weight of shape " + shape_text(c.want));
+  int64_t vocab = w.shape(w_head)[0];
+  if (w.shape(table) != Shape{vocab, hidden} || w.shape(w_head) != Shape{vocab, hidden} || w.shape(g_final) != Shape{hidden})
+    w.fail(table, "[" + std::to_string(vocab) + ", " + std::to_string(hidden) + "] embedding table, lm_head and a final gain");
+  if (w.shape(tokens) != Shape{f.B, f.S}) w.fail(tokens, "token ids of shape " + shape_text(Shape{f.B, f.S}));
+
+  Match m;
+  m.weights = {{"model.embed_tokens.weight", table}, {"model.norm.weight", g_final}, {"lm_head.weight", w_head}};
+  for (size_t n = 0; n < ordered.size(); ++n)
+    for (const Role& r : kRoles)
+      m.weights.push_back({"model.layers." + std::to_string(n) + "." + r.name + ".weight", ordered[n].*(r.node)});
+  std::set<int> distinct;
+  for (auto& kv : m.weights) distinct.insert(kv.second);
+  if (distinct.size() != m.weights.size()) no_match("one input tensor plays two weight roles");
+  m.cfg.n_layers = (int32_t)ordered.size();
+  m.cfg.hidden = (int32_t)hidden;
+  m.cfg.n_heads = (int32_t)f.H;
+  m.cfg.n_kv_heads = (int32_t)f.KV;
+  m.cfg.head_dim = (int32_t)f.D;
+  m.cfg.intermediate = (int32_t)inter;
+  m.cfg.vocab = (int32_t)vocab;
+  m.cfg.rms_eps = (float)eps;
+  m.cfg.rope_base = (float)f.base;
+  m.cfg.dtype = LMB200_F32;
+  m.cfg.tp_size = 1;
+  m.cfg.tp_rank = 0;
+  m.cfg.arch = LMB200_ARCH_LLAMA;
+  m.info.batch = (int32_t)f.B;
+  m.info.seq = (int32_t)f.S;
+  m.info.prev_seq = (int32_t)f.prev;
+  m.info.tokens_node = tokens;
+  m.info.n_weights = (int32_t)m.weights.size();
+  return m;
+}
+
+}  // namespace
+
+extern "C" int32_t lmb200_match_decoder(const lmb200_node_list* list, int32_t output_id, lmb200_model_config* cfg,
+                                        lmb200_decoder_match* info, int32_t* weight_nodes, int32_t weight_capacity,
+                                        char* names_out, int64_t names_capacity) {
+  try {
+    Match m = match_decoder(list, output_id);
+    if (cfg) *cfg = m.cfg;
+    if (info) *info = m.info;
+    if (weight_nodes)
+      for (int32_t k = 0; k < weight_capacity && k < (int32_t)m.weights.size(); ++k) weight_nodes[k] = m.weights[k].second;
+    if (names_out && names_capacity > 0) {
+      std::string all;
+      for (size_t k = 0; k < m.weights.size(); ++k) {
+        const std::string add = (k ? "\n" : "") + m.weights[k].first;
+        if ((int64_t)(all.size() + add.size()) >= names_capacity) break;
+        all += add;
+      }
+      std::memcpy(names_out, all.c_str(), all.size() + 1);
+    }
+    return LMB200_OK;
+  } catch (const NoMatch& e) {
+    return lmb::fail(LMB200_ENOMATCH, "%s", e.what.c_str());
+  } catch (const std::exception& e) {
+    return lmb::fail(LMB200_EINVAL, "node list: %s", e.what());
+  }
+}
+
+extern "C" int32_t lmb200_compile_node_list(lmb200_ctx ctx, const lmb200_node_list* list, int32_t output_id,
+                                            const float* const* node_data, int32_t layout, int32_t dtype, int32_t batch,
+                                            int32_t max_ctx, lmb200_model* model_out, lmb200_session* session_out,
+                                            lmb200_decoder_match* info) {
+  LMB_REQUIRE(model_out && session_out && node_data, "lmb200_compile_node_list: null output or node_data");
+  LMB_REQUIRE(dtype == LMB200_F32 || dtype == LMB200_BF16, "lmb200_compile_node_list: dtype must be float32 or bf16");
+  Match m;
+  try {
+    m = match_decoder(list, output_id);
+  } catch (const NoMatch& e) {
+    return lmb::fail(LMB200_ENOMATCH, "%s", e.what.c_str());
+  } catch (const std::exception& e) {
+    return lmb::fail(LMB200_EINVAL, "node list: %s", e.what());
+  }
+  if (m.info.prev_seq != 0)
+    return lmb::fail(LMB200_ENOMATCH, "the graph was traced with prev_seq = %d: a cached session starts at position 0",
+                     m.info.prev_seq);
+  for (auto& kv : m.weights)
+    if (!node_data[kv.second - 1]) return lmb::fail(LMB200_EINVAL, "%s (node %d) has no data", kv.first.c_str(), kv.second);
+  m.cfg.dtype = dtype;
+  lmb200_model model = 0;
+  int32_t rc = lmb200_model_create(ctx, &m.cfg, &model);
+  if (rc != LMB200_OK) return rc;
+  Walker w(*list);
+  for (auto& kv : m.weights) {
+    Shape s = w.shape(kv.second);
+    rc = lmb200_model_set_weight(model, kv.first.c_str(), node_data[kv.second - 1], (int32_t)s.size(), s.data(), layout);
+    if (rc != LMB200_OK) { lmb200_model_destroy(model); return rc; }
+  }
+  lmb200_session session = 0;
+  rc = lmb200_session_create(model, batch > 0 ? batch : m.info.batch, max_ctx, &session);
+  if (rc != LMB200_OK) { lmb200_model_destroy(model); return rc; }
+  *model_out = model;
+  *session_out = session;
+  if (info) *info = m.info;
+  return LMB200_OK;
+}

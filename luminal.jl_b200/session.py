@@ -34,6 +34,18 @@ class Model:
         _lib.call("lmb200_model_create", device.handle, C.byref(self.cfg), C.byref(h))
         self.handle = h
 
+    @classmethod
+    def adopt(cls, device, handle, *, n_layers, hidden, n_heads, n_kv_heads, intermediate, vocab, eps, rope_base, dtype):
+        """Wraps a model handle the library created (lmb200_compile_node_list)."""
+        self = cls.__new__(cls)
+        self.device = device
+        self.cfg = ModelConfig(n_layers=n_layers, hidden=hidden, n_heads=n_heads, n_kv_heads=n_kv_heads,
+                               head_dim=hidden // n_heads, intermediate=intermediate, vocab=vocab, rms_eps=eps,
+                               rope_base=rope_base, dtype=_dtype_code(dtype), tp_size=1, tp_rank=0, arch=0,
+                               max_positions=0, cross_len=0)
+        self.handle = C.c_uint64(int(handle))
+        return self
+
     def set_weight(self, name, array, layout=ROWMAJOR):
         a = np.asarray(array, dtype=np.float32)
         host = np.asfortranarray(a) if layout == COLMAJOR else np.ascontiguousarray(a)
@@ -81,6 +93,14 @@ class Session:
         h = C.c_uint64(0)
         _lib.call("lmb200_session_create", model.handle, self.batch, self.max_ctx, C.byref(h))
         self.handle = h
+
+    @classmethod
+    def adopt(cls, model, handle, batch, max_ctx):
+        """Wraps a session handle the library created (lmb200_compile_node_list)."""
+        self = cls.__new__(cls)
+        self.model, self.batch, self.max_ctx = model, int(batch), int(max_ctx)
+        self.handle = C.c_uint64(int(handle))
+        return self
 
     @property
     def vocab(self):

@@ -211,8 +211,11 @@ def test_fused_layer_ops(lib_built, device):
     assert np.array_equal(ids.cpu().numpy(), x.argmax(axis=1))
 
 
-@pytest.mark.parametrize("dtype,tol", [("f32", 2e-5), ("bf16", 2e-2)])
-@pytest.mark.parametrize("shape", [(2, 3, 200, 64), (1, 2, 333, 128), (1, 4, 77, 32), (1, 1, 130, 96)])
+# float32 with head_dim 64 / 96 / 128 runs on the tensor cores with bf16 hi + lo operands (three MMAs per product):
+# 1e-4 is the reference's own pin for this op (tests/test_flash_attention_verification.jl:24-50); head_dim 32 stays on
+# the CUDA-core kernel
+@pytest.mark.parametrize("dtype,tol", [("f32", 1e-4), ("bf16", 2e-2)])
+@pytest.mark.parametrize("shape", [(2, 3, 200, 64), (1, 2, 333, 128), (1, 4, 77, 32), (1, 1, 130, 96), (1, 2, 64, 128), (2, 1, 1, 64)])
 @pytest.mark.parametrize("causal", [False, True])
 def test_flash_attention_op(lib_built, device, dtype, tol, shape, causal):
     import torch

@@ -136,3 +136,33 @@ def test_full_size_flash_attention_sampled_rows(lib_built, device, causal):
             assert np.abs(got[i] - ref).max() <= 2e-2 * max(np.abs(ref).max(), 0.05), (b, h, r)
     if causal:
         assert torch.equal(out[:, :, 0], v[:, :, 0])
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_full_size_flash_attention_fp32_sampled_rows(lib_built, device, causal):
+    """The same [4, 32, 4096, 128] case with float32 tensors (the reference's own precision): tensor cores with bf16
+    hi + lo operands.  Sampled rows against float64 at rtol 1e-4 of the row's largest magnitude."""
+    import torch
+    from importlib import import_module
+    _lib = import_module("luminal_jl_b200._lib")
+    B, H, S, D = 4, 32, 4096, 128
+    gen = torch.Generator(device="cuda").manual_seed(11)
+    q, k, v = (torch.randn((B, H, S, D), device="cuda", generator=gen) for _ in range(3))
+    out = torch.empty_like(q)
+    torch.cuda.synchronize()
+    scale = 1.0 / np.sqrt(D)
+    p = lambda t: C.c_void_p(t.data_ptr())
+    _lib.call("lmb200_flash_attention", device.handle, p(out), p(q), p(k), p(v), _lib.F32, B, H, S, D, scale, int(causal))
+    device.sync()
+    rows = [0, 1, 63, 64, 127, 128, 2047, 2048, 4000, 4095]
+    for b, h in [(0, 0), (2, 17), (3, 31)]:
+        kk = k[b, h].cpu().numpy().astype(np.float64)
+        vv = v[b, h].cpu().numpy().astype(np.float64)
+        qq = q[b, h, rows].cpu().numpy().astype(np.float64)
+        got = out[b, h, rows].cpu().numpy()
+        for i, r in enumerate(rows):
+            n = r + 1 if causal else S
+            s = kk[:n] @ qq[i] * scale
+            pr = np.exp(s - s.max())
+            ref = (pr / pr.sum()) @ vv[:n]
+            assert np.abs(got[i] - ref).max() <= 1e-4 * np.abs(ref).max(), (b, h, r, float(np.abs(got[i] - ref).max() / np.abs(ref).max()))

@@ -132,3 +132,31 @@ def test_compile_b200_from_a_node_list(lib_built, device):
     assert np.abs(full - logits).max() <= 1e-3 and np.abs(ref - logits).max() <= 1e-3
     assert np.array_equal(full.argmax(-1), logits.argmax(-1))
     sess.close()
+
+
+def test_flat_node_list_and_error_code():
+    """The array form the library's matcher reads (lmb200_node_list): offsets, op codes and op fields of a small
+    graph; a refusal is LMB200_ENOMATCH (-8), a malformed list LMB200_ENOMATCH with the offending node named."""
+    import ctypes as C
+    from luminal_jl_b200 import _lib
+    g = G.Graph()
+    x = G.tensor(g, [2, 6])
+    y = G.slice_along(G.permute(x, [2, 1]), 1, 1, G.BIG) * np.float32(3.0)
+    nl = M.flatten_graph(g)
+    assert nl.n_nodes == len(g.nodes)
+    ops = [nl.op[i] for i in range(nl.n_nodes)]
+    assert ops[0] == 25 and 18 in ops and 21 in ops and 24 in ops and ops[y.id - 1] == 9
+    k = ops.index(21)
+    args = [nl.arg[i] for i in range(nl.arg_off[k], nl.arg_off[k + 1])]
+    assert args[:3] == [1.0, 6.0, 0.0] and args[3] >= 2.0
+    assert [nl.in_node[i] for i in range(nl.in_off[y.id - 1], nl.in_off[y.id])] == [i for i, _, _ in g.nodes[y.id - 1].inputs]
+    assert [nl.shape[i] for i in range(nl.shape_off[y.id - 1], nl.shape_off[y.id])] == list(g.shapes[y.id - 1])
+    with pytest.raises(_lib.LuminalB200Error) as e:
+        _lib.call("lmb200_match_decoder", C.byref(nl), y.id, None, None, None, 0, None, 0)
+    assert e.value.code == -8 and "Linear's MatMul" in str(e.value)
+    nl.in_node[nl.in_off[y.id - 1]] = y.id + 5                  # an input that is not an earlier node
+    with pytest.raises(M.MatchError, match="earlier node"):
+        try:
+            _lib.call("lmb200_match_decoder", C.byref(nl), y.id, None, None, None, 0, None, 0)
+        except _lib.LuminalB200Error as err:
+            M._raise_match(err)
