@@ -477,11 +477,14 @@ def run_decode(args):
         }
         if parity is not None:
             line["tp_parity"] = parity
-            # what the 2 x layers reductions of a step move over NVLink, per GPU and direction: every rank stores its
-            # bf16 partial [hidden][32] into each of the N - 1 peers' regions (and receives as much)
+            # what the 2 x layers reductions of a step move over NVLink, per GPU and direction.  Fused step: every rank
+            # stores its bf16 partial [hidden][32] into each of the N - 1 peers' regions; separate norm kernels
+            # (LMB200_FUSED_STEP=0): every rank loads the N - 1 peers' float32 partials [32][hidden]
+            fused = os.environ.get("LMB200_FUSED_STEP", "1") != "0"
             line["nvlink"] = {"reductions_per_step": 2 * cfg["n_layers"],
-                              "bytes_out_per_step_per_gpu": 2 * cfg["n_layers"] * (world - 1) * CFG["hidden"] * 32 * 2,
-                              "protocol": "peer stores of bf16 partials + data polling inside the o_proj / down_proj kernels"}
+                              "bytes_per_step_per_gpu": 2 * cfg["n_layers"] * (world - 1) * CFG["hidden"] * 32 * (2 if fused else 4),
+                              "protocol": ("peer stores of bf16 partials + data polling inside the o_proj / down_proj kernels" if fused
+                                           else "flag + peer loads of float32 partials inside the norm kernels")}
         if args.prefill:
             line["prefill"] = None
         if not args.no_cpu_baseline and world == 1:

@@ -375,12 +375,15 @@ typedef struct {
   const double* arg;
 } lmb200_node_list;
 typedef struct {
+  int32_t arch;         /* LMB200_ARCH_LLAMA or LMB200_ARCH_WHISPER_DECODER: which builder's graph was recognised */
   int32_t batch;        /* the shape the graph was traced for: tokens [batch, seq] */
   int32_t seq;
-  int32_t prev_seq;     /* the position offset baked into the RoPE angles (src/NN.jl:253-262) */
+  int32_t prev_seq;     /* Llama: the position offset baked into the RoPE angles (src/NN.jl:253-262); Whisper: the
+                           step_pos baked into the slice positions (src/Whisper.jl:687-742) */
   int32_t tokens_node;  /* the input node the token ids enter through */
-  int32_t n_weights;    /* 3 + 9 * n_layers */
-  int32_t reserved;
+  int32_t n_weights;    /* Llama: 3 + 9 * n_layers; Whisper: 4 + 21 * n_layers */
+  int32_t max_seq;      /* Whisper: positions of the past self K/V inputs */
+  int32_t cross_len;    /* Whisper: positions of the encoder K/V inputs */
 } lmb200_decoder_match;
 /* Recognises NN.Llama / NN.Phi3 (src/NN.jl:390-507) ending in the logits node output_id:
  * lm_head(norm(block^L(embedding(tokens)))), every layer decomposed into primitives as src/NN.jl and
@@ -392,12 +395,24 @@ typedef struct {
 int32_t lmb200_match_decoder(const lmb200_node_list* list, int32_t output_id, lmb200_model_config* cfg,
                              lmb200_decoder_match* info, int32_t* weight_nodes, int32_t weight_capacity,
                              char* names_out, int64_t names_capacity);
-/* compile() for a graph lmb200_match_decoder recognises (replaces src/Compiler.jl:181-364 + the per-token
- * re-execution of examples/llama.jl:39-99 for such a graph): matches, creates the model in `dtype`, sets every
- * weight from node_data[node - 1] (host float32 in `layout`, shape = that node's; entries of other nodes may be
- * NULL: graph.tensors filled by load_weights!, src/Weights.jl:60-114) and creates a session of `batch` sequences
- * (0 = the graph's) with room for max_ctx positions.  The caller owns both handles.  The session starts at
- * position 0, so a graph traced with prev_seq != 0 is refused (LMB200_ENOMATCH). */
+/* The same for the Whisper TextDecoder's incremental decode step (build_decode_step!, src/Whisper.jl:687-742: cached
+ * self attention with the slice-and-concat cache write of src/Whisper.jl:541-570, cross attention over encoder K/V
+ * inputs, GELU MLP, LayerNorm, tied-embedding head), ending in its logits node.  cfg comes back with
+ * LMB200_ARCH_WHISPER_DECODER; weight_nodes / names_out list the model.decoder.* tensors the session needs; cache_nodes
+ * (as many as fit) holds, n_layers of each in this order: the encoder K inputs, encoder V inputs, past self K inputs,
+ * past self V inputs, and the nodes of the updated self K and V (IncrementalDecodeGraph, src/Whisper.jl:662-672). */
+int32_t lmb200_match_whisper_step(const lmb200_node_list* list, int32_t logits_id, lmb200_model_config* cfg,
+                                  lmb200_decoder_match* info, int32_t* weight_nodes, int32_t weight_capacity,
+                                  char* names_out, int64_t names_capacity, int32_t* cache_nodes,
+                                  int32_t cache_capacity);
+/* compile() for a graph one of the two matchers recognises (replaces src/Compiler.jl:181-364 + the per-token
+ * re-execution of examples/llama.jl:39-99, or the per-position graph build + compile of src/Whisper.jl:679-801):
+ * matches, creates the model in `dtype`, sets every weight from node_data[node - 1] (host float32 in `layout`, shape =
+ * that node's; entries of other nodes may be NULL: graph.tensors filled by load_weights!, src/Weights.jl:60-114) and
+ * creates a session of `batch` sequences (0 = the graph's) with room for max_ctx positions (Whisper: 0 = the graph's
+ * max_seq).  The caller owns both handles.  The session starts at position 0: a Llama graph traced with prev_seq != 0
+ * is refused (LMB200_ENOMATCH); a Whisper step graph of any step_pos gives the same session, and encoder K/V inputs that
+ * have data are uploaded as lmb200_session_set_cross_kv does. */
 int32_t lmb200_compile_node_list(lmb200_ctx ctx, const lmb200_node_list* list, int32_t output_id,
                                  const float* const* node_data, int32_t layout, int32_t dtype, int32_t batch,
                                  int32_t max_ctx, lmb200_model* model_out, lmb200_session* session_out,

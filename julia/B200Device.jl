@@ -313,8 +313,10 @@ function compile_b200(d::B200Device, cfg::ModelConfig, weights::Dict{String,<:Ar
 end
 
 # compile_b200 from the graph alone: Graph.nodes flattened into lmb200_node_list, recognised by the library's
-# structural matcher (lmb200_match_decoder) and turned into a model + session (lmb200_compile_node_list).  The
-# weights are whatever load_weights! put into graph.tensors (src/Weights.jl:60-114).  A graph the matcher does not
+# structural matchers (lmb200_match_decoder for NN.Llama / NN.Phi3, lmb200_match_whisper_step for the graph of
+# build_decode_step!, src/Whisper.jl:687-742) and turned into a model + session (lmb200_compile_node_list).  The
+# weights are whatever load_weights! put into graph.tensors (src/Weights.jl:60-114); for a Whisper step graph the
+# encoder K/V inputs that have data there are uploaded too, and max_ctx = 0 takes the graph's max_seq.  A graph the matcher does not
 # recognise raises B200Error with code -8 (LMB200_ENOMATCH): run it with compile() / execute() instead.
 struct NodeList                                     # lmb200_node_list, field for field
     n_nodes::Int32; reserved::Int32
@@ -322,7 +324,7 @@ struct NodeList                                     # lmb200_node_list, field fo
     arg_off::Ptr{Int32}; arg::Ptr{Float64}
 end
 struct DecoderMatch                                 # lmb200_decoder_match
-    batch::Int32; seq::Int32; prev_seq::Int32; tokens_node::Int32; n_weights::Int32; reserved::Int32
+    arch::Int32; batch::Int32; seq::Int32; prev_seq::Int32; tokens_node::Int32; n_weights::Int32; max_seq::Int32; cross_len::Int32
 end
 const NODE_CODES = Dict{DataType,Int32}(
     Luminal.Log2 => 0, Luminal.Exp2 => 1, Luminal.Sin => 2, Luminal.Sqrt => 3, Luminal.Cos => 4, Luminal.Recip => 5,
@@ -360,7 +362,7 @@ function compile_b200(d::B200Device, graph::Luminal.Graph, output_id::Integer; d
         a isa Array{Float32} || continue
         push!(keep, a); data[id] = pointer(a)
     end
-    model = Ref{UInt64}(0); session = Ref{UInt64}(0); info = Ref(DecoderMatch(0, 0, 0, 0, 0, 0))
+    model = Ref{UInt64}(0); session = Ref{UInt64}(0); info = Ref(DecoderMatch(0, 0, 0, 0, 0, 0, 0, 0))
     GC.@preserve op in_off in_node shape_off shape arg_off arg keep begin
         nl = NodeList(n, 0, pointer(op), pointer(in_off), pointer(in_node), pointer(shape_off), pointer(shape),
                       pointer(arg_off), pointer(arg))

@@ -363,6 +363,168 @@ struct Walker {
     return xq;
   }
 
+  // ---- Whisper TextDecoder, one cached decode step (src/Whisper.jl:541-742) ------------------------------------
+  int sc(int i) const { return skip(i, LMB200_NODE_CONTIGUOUS); }
+
+  // Linear with an optional bias: MatMul(x, Permute[2,1](W)) [+ expand*(b)]   (src/NN.jl:22-35)
+  void linear_bias(int i, int& x, int& w, int& b) const {
+    b = 0;
+    if (op(i) == LMB200_NODE_ADD && n_in(i) == 2) {
+      int p = in(i, 0), q = in(i, 1);
+      int bq = skip(q, LMB200_NODE_EXPAND), bp = skip(p, LMB200_NODE_EXPAND);
+      if (op(p) == LMB200_NODE_MATMUL && is_input(bq) && shape(bq).size() == 1) { b = bq; i = p; }
+      else if (op(q) == LMB200_NODE_MATMUL && is_input(bp) && shape(bp).size() == 1) { b = bp; i = q; }
+      else fail(i, "a Linear's MatMul plus its [out] bias");
+    }
+    linear(i, x, w);
+    if (b && shape(b)[0] != shape(w)[0]) fail(b, "a bias as long as the weight has rows");
+  }
+
+  // LayerNorm (src/NN.jl:138-173): std_norm(mean_norm(x)) * expand(w) + expand(b), over the last dim
+  void layernorm(int i, int& x, int& gain, int& bias, double& eps) const {
+    int a, bb;
+    expect2(i, LMB200_NODE_ADD, "LayerNorm's + bias", a, bb);
+    bias = skip(bb, LMB200_NODE_EXPAND);
+    if (!(is_input(bias) && shape(bias).size() == 1)) {
+      std::swap(a, bb);
+      bias = skip(bb, LMB200_NODE_EXPAND);
+    }
+    if (!(is_input(bias) && shape(bias).size() == 1)) fail(i, "LayerNorm's + a [hidden] bias");
+    int centred;
+    rmsnorm(a, centred, gain, eps);                    // the scale part is the RMSNorm pattern over the centred tensor
+    // mean_norm: x - expand(sum(x) * (1/n))  ==  x + (expand(..) * -1)
+    int neg;
+    expect2(centred, LMB200_NODE_ADD, "x - mean(x)", x, neg);
+    double m1, inv_n;
+    int ex = with_const(neg, LMB200_NODE_MUL, "mean * -1", m1);
+    int mean = expect1(ex, LMB200_NODE_EXPAND, "expand(mean)");
+    int total = with_const(mean, LMB200_NODE_MUL, "sum * (1/n)", inv_n);
+    Shape xs = shape(x);
+    if (xs.empty()) fail(x, "a tensor to normalise");
+    if (!(m1 == -1.0 && std::fabs(inv_n * (double)xs.back() - 1.0) < 1e-5 && op(total) == LMB200_NODE_SUM_REDUCE &&
+          n_arg(total) == 1 && (int64_t)arg(total, 0) == (int64_t)xs.size() && in(total, 0) == x))
+      fail(centred, "x minus its mean over the last dim");
+    if (shape(bias)[0] != xs.back()) fail(bias, "a bias of length " + std::to_string(xs.back()));
+  }
+
+  // 1 * recip(1 + exp2(z * -1 * (1/ln 2)))   (src/HighLevelOps.jl:153-155) -> z
+  int sigmoid(int s) const {
+    double one, one2, k, m1;
+    int r = with_const(s, LMB200_NODE_MUL, "1 / (1 + exp2(..))", one);
+    int den = expect1(r, LMB200_NODE_RECIP, "recip(1 + exp2(..))");
+    int e = with_const(den, LMB200_NODE_ADD, "1 + exp2(..)", one2);
+    int ar = expect1(e, LMB200_NODE_EXP2, "exp2(-z / ln 2)");
+    int neg = with_const(ar, LMB200_NODE_MUL, "(-z) * (1/ln 2)", k);
+    int z = with_const(neg, LMB200_NODE_MUL, "z * -1", m1);
+    if (!(one == 1.0 && one2 == 1.0 && m1 == -1.0 && std::fabs(k - 1.0 / std::log(2.0)) < 1e-6))
+      fail(s, "sigmoid with the reference's constants");
+    return z;
+  }
+
+  // gelu (src/HighLevelOps.jl:162-168): a * 0.5 * (1 + tanh(0.7978845608 * a * (1 + 0.044715 * a * a))),
+  // tanh(u) = sigmoid(2u) * 2 - 1 -> a
+  int gelu(int i) const {
+    int half_a, onep;
+    expect2(i, LMB200_NODE_MUL, "gelu: (a * 0.5) * (1 + tanh(..))", half_a, onep);
+    double c_half, one, m1, two, two2, c0, one2, c1;
+    int a = with_const(half_a, LMB200_NODE_MUL, "a * 0.5", c_half);
+    int th = with_const(onep, LMB200_NODE_ADD, "1 + tanh(..)", one);
+    int sg2 = with_const(th, LMB200_NODE_ADD, "sigmoid(2u) * 2 - 1", m1);
+    int sg = with_const(sg2, LMB200_NODE_MUL, "sigmoid(2u) * 2", two);
+    int u2 = sigmoid(sg);
+    int u = with_const(u2, LMB200_NODE_MUL, "u * 2", two2);
+    int ca, poly;
+    expect2(u, LMB200_NODE_MUL, "(0.79788 * a) * (1 + 0.044715 * a * a)", ca, poly);
+    int a1 = with_const(ca, LMB200_NODE_MUL, "0.7978845608 * a", c0);
+    int cub = with_const(poly, LMB200_NODE_ADD, "1 + 0.044715 * a * a", one2);
+    int caa, a3;
+    expect2(cub, LMB200_NODE_MUL, "(0.044715 * a) * a", caa, a3);
+    int a2 = with_const(caa, LMB200_NODE_MUL, "0.044715 * a", c1);
+    if (!(c_half == 0.5 && one == 1.0 && m1 == -1.0 && two == 2.0 && two2 == 2.0 && one2 == 1.0 &&
+          std::fabs(c0 - 0.7978845608) < 1e-6 && std::fabs(c1 - 0.044715) < 1e-7 && a1 == a && a2 == a && a3 == a))
+      fail(i, "gelu of one tensor with the reference's constants");
+    return a;
+  }
+
+  // softmax over the last of four dims of MatMul(q, keys^T) -> the MatMul's operands
+  void attn_probs(int probs, int& q, int& kt) const {
+    int weights = softmax_last(probs);
+    expect2(weights, LMB200_NODE_MATMUL, "queries x keys^T", q, kt);
+  }
+
+  // permute[1,3,2,4](reshape[B,1,H,D](Linear(x) [* scale])) -> the projection's parts
+  void step_heads(int i, bool scaled, bool want_bias, int& x, int& w, int& b, int64_t& H, int64_t& D, double& scale) const {
+    i = sc(i);
+    if (!permute_is(i, {1, 3, 2, 4})) fail(i, "permute [1,3,2,4] of the head split");
+    int rs = in(i, 0);
+    int lin = expect1(rs, LMB200_NODE_RESHAPE, "reshape to [batch, 1, heads, head_dim]");
+    Shape s = shape(rs);
+    if (s.size() != 4 || s[1] != 1) fail(rs, "reshape to [batch, 1, heads, head_dim]");
+    H = s[2];
+    D = s[3];
+    scale = 1.0;
+    if (scaled) lin = with_const(lin, LMB200_NODE_MUL, "projection * head_dim^-0.25", scale);
+    linear_bias(lin, x, w, b);
+    if (want_bias != (b != 0)) fail(lin, want_bias ? "a projection with a bias" : "a projection without a bias");
+  }
+
+  // a node that is concat_along(a, b, 3) = pad(a, 3, 0, nb) + pad(b, 3, na, 0)   (src/HighLevelOps.jl:243-248)
+  bool is_concat3(int i, int& a, int& b) const {
+    if (!(op(i) == LMB200_NODE_ADD && n_in(i) == 2 && op(in(i, 0)) == LMB200_NODE_PAD && op(in(i, 1)) == LMB200_NODE_PAD)) return false;
+    int pa = in(i, 0), pb = in(i, 1);
+    a = in(pa, 0);
+    b = in(pb, 0);
+    Shape sa = shape(a), sb = shape(b);
+    if (sa.size() != 4 || sb.size() != 4) return false;
+    auto want = [&](int64_t l, int64_t r) { return std::vector<int64_t>{0, 0, 0, 0, l, r, 0, 0}; };
+    return iargs(pa) == want(0, sb[2]) && iargs(pb) == want(sa[2], 0);
+  }
+  // Slice of an input [B, H, max_seq, D] along dim 3 only -> (input, start, stop)
+  bool cache_slice(int i, int& past, int64_t& lo, int64_t& hi) const {
+    if (op(i) != LMB200_NODE_SLICE || n_in(i) != 1) return false;
+    past = in(i, 0);
+    Shape ps = shape(past);
+    auto a = iargs(i);
+    if (!is_input(past) || ps.size() != 4 || a.size() != 8) return false;
+    for (int d = 0; d < 4; ++d) {
+      if (d == 2) continue;
+      if (a[2 * d] != 0 || a[2 * d + 1] < ps[d]) return false;
+    }
+    lo = a[4];
+    hi = std::min<int64_t>(a[5], ps[2]);
+    return true;
+  }
+  // _kv_scatter (src/Whisper.jl:541-570): past[.., 0:s, :] ++ new_slot ++ past[.., s+1:, :] -> (past, new_slot, s)
+  void kv_scatter(int i, int& past, int& slot, int64_t& step) const {
+    std::vector<int> parts;
+    int cur = i, a, b;
+    while (is_concat3(cur, a, b)) {
+      parts.insert(parts.begin(), b);
+      cur = a;
+    }
+    parts.insert(parts.begin(), cur);
+    if (parts.size() < 2 || parts.size() > 3) fail(i, "a cache with one slot replaced (slice ++ new ++ slice)");
+    past = 0;
+    slot = 0;
+    int64_t at = 0, max_seq = shape(i).size() == 4 ? shape(i)[2] : 0;
+    step = -1;
+    for (int p : parts) {
+      int src;
+      int64_t lo, hi;
+      if (cache_slice(p, src, lo, hi)) {
+        if ((past && src != past) || lo != at || hi <= lo) fail(p, "consecutive slices of one past-cache input");
+        past = src;
+        at = hi;
+      } else {
+        Shape s = shape(p);
+        if (slot || s.size() != 4 || s[2] != 1) fail(p, "one new [batch, heads, 1, head_dim] slot");
+        slot = p;
+        step = at;
+        at += 1;
+      }
+    }
+    if (!past || !slot || at != max_seq || shape(past)[2] != max_seq) fail(i, "a full-length cache built from one past input and one new slot");
+  }
   // TransformerBlock (src/NN.jl:390-414): x + attn(norm(x)), then + mlp(norm(.)) -> the block's input
   int block(int i, Block& p) const {
     int h, ff;
@@ -391,6 +553,115 @@ struct Walker {
   }
 };
 
+struct WhisperLayer {
+  // input-tensor nodes by role
+  int q_w = 0, q_b = 0, k_w = 0, v_w = 0, v_b = 0, o_w = 0, o_b = 0, n1_w = 0, n1_b = 0;
+  int cq_w = 0, cq_b = 0, co_w = 0, co_b = 0, n2_w = 0, n2_b = 0, fc1_w = 0, fc1_b = 0, fc2_w = 0, fc2_b = 0, n3_w = 0, n3_b = 0;
+  int cross_k = 0, cross_v = 0, self_k = 0, self_v = 0, new_k = 0, new_v = 0;
+  int64_t H = 0, D = 0, step = 0, max_seq = 0, enc_seq = 0, B = 0;
+  double eps = 0;
+};
+
+struct WhisperWalker : Walker {
+  using Walker::Walker;
+
+  void check_scale(int at, double scale, int64_t D) const {
+    if (std::fabs(scale * scale * scale * scale * (double)D - 1.0) > 1e-4) fail(at, "the (hidden / heads)^-0.25 scale");
+  }
+
+  // whisper_self_attn_cached (src/Whisper.jl:584-625) from its out_proj -> the normalised input
+  int self_attention(int at, WhisperLayer& L) const {
+    int ctx;
+    linear_bias(at, ctx, L.o_w, L.o_b);
+    if (!L.o_b) fail(at, "out_proj with a bias");
+    int pv = expect1(ctx, LMB200_NODE_RESHAPE, "reshape to [batch, 1, hidden]");
+    if (!permute_is(pv, {1, 3, 2, 4})) fail(pv, "permute [1,3,2,4] of the attention output");
+    int probs, v_ctx, q, kt;
+    expect2(in(pv, 0), LMB200_NODE_MATMUL, "probs x values", probs, v_ctx);
+    attn_probs(probs, q, kt);
+    kt = sc(kt);
+    if (!permute_is(kt, {1, 2, 4, 3})) fail(kt, "permute [1,2,4,3] of the cached keys");
+    int k_ctx = in(kt, 0);
+    // the context is new_cache[.., 0 : step + 1, :]
+    auto context = [&](int c, int& cache) {
+      if (op(c) != LMB200_NODE_SLICE) fail(c, "slice [0, step + 1) of the updated cache");
+      auto a = iargs(c);
+      cache = in(c, 0);
+      if (a.size() != 8 || a[4] != 0) fail(c, "slice [0, step + 1) of the updated cache");
+      return a[5];
+    };
+    int64_t kn = context(k_ctx, L.new_k), vn = context(v_ctx, L.new_v);
+    int k_slot, v_slot;
+    int64_t ks, vs;
+    kv_scatter(L.new_k, L.self_k, k_slot, ks);
+    kv_scatter(L.new_v, L.self_v, v_slot, vs);
+    if (!(ks == vs && kn == ks + 1 && vn == vs + 1 && L.self_k != L.self_v)) fail(at, "keys and values written at one position and read up to it");
+    L.step = ks;
+    L.max_seq = shape(L.self_k)[2];
+    int xq, xk, xv, nob;
+    int64_t H2, D2, H3, D3;
+    double sq, sk, sv;
+    step_heads(q, true, true, xq, L.q_w, L.q_b, L.H, L.D, sq);
+    step_heads(k_slot, true, false, xk, L.k_w, nob, H2, D2, sk);
+    step_heads(v_slot, false, true, xv, L.v_w, L.v_b, H3, D3, sv);
+    if (!(xq == xk && xk == xv && L.H == H2 && L.H == H3 && L.D == D2 && L.D == D3 && sq == sk)) fail(at, "q, k and v projections of one tensor with one head split");
+    check_scale(q, sq, L.D);
+    Shape ps = shape(L.self_k);
+    if (!(ps[1] == L.H && ps[3] == L.D && shape(L.self_v) == ps)) fail(L.self_k, "past K and V of shape [batch, heads, max_seq, head_dim]");
+    L.B = ps[0];
+    return xq;
+  }
+
+  // whisper_cross_attn_cached (src/Whisper.jl:633-651)
+  int cross_attention(int at, WhisperLayer& L) const {
+    int ctx;
+    linear_bias(at, ctx, L.co_w, L.co_b);
+    if (!L.co_b) fail(at, "out_proj with a bias");
+    int pv = expect1(ctx, LMB200_NODE_RESHAPE, "reshape to [batch, 1, hidden]");
+    if (!permute_is(pv, {1, 3, 2, 4})) fail(pv, "permute [1,3,2,4] of the attention output");
+    int probs, q, kt;
+    expect2(in(pv, 0), LMB200_NODE_MATMUL, "probs x encoder values", probs, L.cross_v);
+    attn_probs(probs, q, kt);
+    kt = sc(kt);
+    if (!permute_is(kt, {1, 2, 4, 3})) fail(kt, "permute [1,2,4,3] of the encoder keys");
+    L.cross_k = in(kt, 0);
+    Shape ks = shape(L.cross_k);
+    if (!(is_input(L.cross_k) && is_input(L.cross_v) && ks.size() == 4 && shape(L.cross_v) == ks && L.cross_k != L.cross_v))
+      fail(at, "encoder K and V inputs of one [batch, heads, enc_seq, head_dim] shape");
+    int x;
+    int64_t H, D;
+    double s;
+    step_heads(q, true, true, x, L.cq_w, L.cq_b, H, D, s);
+    if (!(H == L.H && D == L.D && ks[0] == L.B && ks[1] == H && ks[3] == D)) fail(at, "the self attention's head split");
+    check_scale(q, s, D);
+    L.enc_seq = ks[2];
+    return x;
+  }
+
+  // one decoder layer of build_decode_step! (src/Whisper.jl:712-729), from its output sum -> its input
+  int layer(int i, WhisperLayer& L) const {
+    int x2, ff, x1, cr, x0, at;
+    expect2(i, LMB200_NODE_ADD, "residual + mlp", x2, ff);
+    int act, h, n3, xa, xb, xc;
+    linear_bias(ff, act, L.fc2_w, L.fc2_b);
+    h = gelu(act);
+    linear_bias(h, n3, L.fc1_w, L.fc1_b);
+    if (!(L.fc1_b && L.fc2_b)) fail(ff, "fc1 and fc2 with biases");
+    double e3, e2, e1;
+    layernorm(n3, xa, L.n3_w, L.n3_b, e3);
+    if (xa != x2) fail(ff, "the MLP over the normalised residual");
+    expect2(x2, LMB200_NODE_ADD, "residual + cross attention", x1, cr);
+    expect2(x1, LMB200_NODE_ADD, "residual + self attention", x0, at);
+    int n1 = self_attention(at, L);
+    layernorm(n1, xc, L.n1_w, L.n1_b, e1);
+    int n2 = cross_attention(cr, L);
+    layernorm(n2, xb, L.n2_w, L.n2_b, e2);
+    if (xb != x1 || xc != x0 || e1 != e2 || e2 != e3) fail(i, "three pre-norm sub-layers over one residual stream, one epsilon");
+    L.eps = e1;
+    return x0;
+  }
+};
+
 struct Role {
   int Block::*node;
   const char* name;
@@ -415,6 +686,7 @@ struct Match {
   lmb200_model_config cfg{};
   lmb200_decoder_match info{};
   std::vector<std::pair<std::string, int>> weights;
+  std::vector<int> cache;        // Whisper: cross K, cross V, past self K, past self V, new self K, new self V; n_layers of each
 };
 
 Match match_decoder(const lmb200_node_list* g, int output_id) {
@@ -479,6 +751,7 @@ Match match_decoder(const lmb200_node_list* g, int output_id) {
   m.cfg.tp_size = 1;
   m.cfg.tp_rank = 0;
   m.cfg.arch = LMB200_ARCH_LLAMA;
+  m.info.arch = LMB200_ARCH_LLAMA;
   m.info.batch = (int32_t)f.B;
   m.info.seq = (int32_t)f.S;
   m.info.prev_seq = (int32_t)f.prev;
@@ -487,27 +760,161 @@ Match match_decoder(const lmb200_node_list* g, int output_id) {
   return m;
 }
 
+// build_decode_step! (src/Whisper.jl:687-742) ending in the logits node: the tied-embedding head over
+// layer_norm(layer^L(embedding(token) + position slot)).
+Match match_whisper_step(const lmb200_node_list* g, int output_id) {
+  validate_list(g);
+  WhisperWalker w(*g);
+  if (output_id < 1 || output_id > g->n_nodes) no_match("no node %d", output_id);
+  int first, wt;
+  w.expect2(output_id, LMB200_NODE_MATMUL, "the head's MatMul", first, wt);
+  if (!w.permute_is(wt, {2, 1})) w.fail(wt, "Permute[2,1] of the embedding table");
+  int emb = w.in(wt, 0);
+  first = w.sc(first);
+  if (w.op(first) != LMB200_NODE_SLICE) w.fail(first, "slice of the first (only) position of the normalised output");
+  int out = w.in(first, 0), x, ln_w, ln_b;
+  double eps;
+  w.layernorm(out, x, ln_w, ln_b, eps);
+  std::vector<WhisperLayer> layers;
+  auto is_bottom = [&](int n) {
+    return w.op(n) == LMB200_NODE_ADD && w.n_in(n) == 2 && (w.op(w.in(n, 0)) == LMB200_NODE_GATHER || w.op(w.in(n, 1)) == LMB200_NODE_GATHER);
+  };
+  while (!is_bottom(x)) {
+    if (w.op(x) != LMB200_NODE_ADD) w.fail(x, "a decoder layer's residual sum, or embedding + position");
+    WhisperLayer L;
+    x = w.layer(x, L);
+    layers.push_back(L);
+  }
+  if (layers.empty()) no_match("no decoder layer between the embedding and the final norm");
+  std::vector<WhisperLayer> ordered(layers.rbegin(), layers.rend());
+  int ga = w.in(x, 0), pe = w.in(x, 1);
+  if (w.op(ga) != LMB200_NODE_GATHER) std::swap(ga, pe);
+  int table = w.in(ga, 0), tokens = w.in(ga, 1);
+  const WhisperLayer& f = ordered[0];
+  const int64_t hidden = f.H * f.D;
+  if (!(table == emb && w.is_input(table) && w.is_input(tokens) && w.shape(table).size() == 2 && w.shape(table)[1] == hidden &&
+        w.shape(tokens) == Shape{f.B, 1}))
+    w.fail(ga, "gather(the head's embedding table, token ids [batch, 1])");
+  // + expand(contiguous(slice(pos_embedding, 1, step, step + 1)), 1, batch)
+  int slot = w.sc(w.expect1(pe, LMB200_NODE_EXPAND, "the position slot expanded over the batch"));
+  if (w.op(slot) != LMB200_NODE_SLICE) w.fail(slot, "slice of one row of the position table");
+  int pos = w.in(slot, 0);
+  auto pr = w.iargs(slot);
+  if (!(w.is_input(pos) && w.shape(pos).size() == 2 && w.shape(pos)[1] == hidden && pr.size() == 4 && pr[1] == pr[0] + 1 && pr[0] == f.step))
+    w.fail(slot, "row `step` of a [max_positions, hidden] position table");
+  int64_t ffn = w.shape(f.fc1_w)[0];
+  for (size_t n = 0; n < ordered.size(); ++n) {
+    const WhisperLayer& p = ordered[n];
+    bool same = p.H == f.H && p.D == f.D && p.step == f.step && p.max_seq == f.max_seq && p.enc_seq == f.enc_seq && p.B == f.B &&
+                p.eps == eps;
+    for (int WhisperLayer::*r : {&WhisperLayer::q_w, &WhisperLayer::k_w, &WhisperLayer::v_w, &WhisperLayer::o_w, &WhisperLayer::cq_w,
+                                 &WhisperLayer::co_w})
+      same = same && w.shape(p.*r) == Shape{hidden, hidden};
+    same = same && w.shape(p.fc1_w) == Shape{ffn, hidden} && w.shape(p.fc2_w) == Shape{hidden, ffn};
+    if (!same) no_match("decoder layer %zu differs from layer 0 in its widths, head split, epsilon, position or cache shapes", n);
+  }
+  Match m;
+  m.weights = {{"model.decoder.embed_tokens.weight", table}, {"model.decoder.embed_positions.weight", pos},
+               {"model.decoder.layer_norm.weight", ln_w}, {"model.decoder.layer_norm.bias", ln_b}};
+  struct WRole { int WhisperLayer::*node; const char* name; };
+  static const WRole roles[] = {
+      {&WhisperLayer::q_w, "self_attn.q_proj.weight"}, {&WhisperLayer::k_w, "self_attn.k_proj.weight"},
+      {&WhisperLayer::v_w, "self_attn.v_proj.weight"}, {&WhisperLayer::q_b, "self_attn.q_proj.bias"},
+      {&WhisperLayer::v_b, "self_attn.v_proj.bias"}, {&WhisperLayer::o_w, "self_attn.out_proj.weight"},
+      {&WhisperLayer::o_b, "self_attn.out_proj.bias"}, {&WhisperLayer::n1_w, "self_attn_layer_norm.weight"},
+      {&WhisperLayer::n1_b, "self_attn_layer_norm.bias"}, {&WhisperLayer::cq_w, "encoder_attn.q_proj.weight"},
+      {&WhisperLayer::cq_b, "encoder_attn.q_proj.bias"}, {&WhisperLayer::co_w, "encoder_attn.out_proj.weight"},
+      {&WhisperLayer::co_b, "encoder_attn.out_proj.bias"}, {&WhisperLayer::n2_w, "encoder_attn_layer_norm.weight"},
+      {&WhisperLayer::n2_b, "encoder_attn_layer_norm.bias"}, {&WhisperLayer::fc1_w, "fc1.weight"},
+      {&WhisperLayer::fc1_b, "fc1.bias"}, {&WhisperLayer::fc2_w, "fc2.weight"}, {&WhisperLayer::fc2_b, "fc2.bias"},
+      {&WhisperLayer::n3_w, "final_layer_norm.weight"}, {&WhisperLayer::n3_b, "final_layer_norm.bias"}};
+  for (size_t n = 0; n < ordered.size(); ++n)
+    for (const WRole& r : roles)
+      m.weights.push_back({"model.decoder.layers." + std::to_string(n) + "." + r.name, ordered[n].*(r.node)});
+  std::set<int> distinct;
+  for (auto& kv : m.weights) distinct.insert(kv.second);
+  for (int WhisperLayer::*r : {&WhisperLayer::cross_k, &WhisperLayer::cross_v, &WhisperLayer::self_k, &WhisperLayer::self_v,
+                               &WhisperLayer::new_k, &WhisperLayer::new_v})
+    for (const WhisperLayer& p : ordered) {
+      m.cache.push_back(p.*r);
+      distinct.insert(p.*r);
+    }
+  if (distinct.size() != m.weights.size() + m.cache.size()) no_match("one input tensor plays two roles");
+  m.cfg.n_layers = (int32_t)ordered.size();
+  m.cfg.hidden = (int32_t)hidden;
+  m.cfg.n_heads = m.cfg.n_kv_heads = (int32_t)f.H;
+  m.cfg.head_dim = (int32_t)f.D;
+  m.cfg.intermediate = (int32_t)ffn;
+  m.cfg.vocab = (int32_t)w.shape(table)[0];
+  m.cfg.rms_eps = (float)eps;
+  m.cfg.rope_base = 10000.f;
+  m.cfg.dtype = LMB200_F32;
+  m.cfg.tp_size = 1;
+  m.cfg.arch = LMB200_ARCH_WHISPER_DECODER;
+  m.cfg.max_positions = (int32_t)w.shape(pos)[0];
+  m.cfg.cross_len = (int32_t)f.enc_seq;
+  m.info.arch = LMB200_ARCH_WHISPER_DECODER;
+  m.info.batch = (int32_t)f.B;
+  m.info.seq = 1;
+  m.info.prev_seq = (int32_t)f.step;
+  m.info.tokens_node = tokens;
+  m.info.n_weights = (int32_t)m.weights.size();
+  m.info.max_seq = (int32_t)f.max_seq;
+  m.info.cross_len = (int32_t)f.enc_seq;
+  return m;
+}
+
+// Which builder's graph ends here?  The Whisper step reads its head input through a slice of the first position.
+Match match_any(const lmb200_node_list* g, int output_id) {
+  validate_list(g);
+  Walker w(*g);
+  if (output_id >= 1 && output_id <= g->n_nodes && w.op(output_id) == LMB200_NODE_MATMUL && w.n_in(output_id) == 2 &&
+      w.op(w.sc(w.in(output_id, 0))) == LMB200_NODE_SLICE)
+    return match_whisper_step(g, output_id);
+  return match_decoder(g, output_id);
+}
+
+int32_t report(const Match& m, lmb200_model_config* cfg, lmb200_decoder_match* info, int32_t* weight_nodes,
+               int32_t weight_capacity, char* names_out, int64_t names_capacity) {
+  if (cfg) *cfg = m.cfg;
+  if (info) *info = m.info;
+  if (weight_nodes)
+    for (int32_t k = 0; k < weight_capacity && k < (int32_t)m.weights.size(); ++k) weight_nodes[k] = m.weights[k].second;
+  if (names_out && names_capacity > 0) {
+    std::string all;
+    for (size_t k = 0; k < m.weights.size(); ++k) {
+      const std::string add = (k ? "\n" : "") + m.weights[k].first;
+      if ((int64_t)(all.size() + add.size()) >= names_capacity) break;
+      all += add;
+    }
+    std::memcpy(names_out, all.c_str(), all.size() + 1);
+  }
+  return LMB200_OK;
+}
+
 }  // namespace
 
 extern "C" int32_t lmb200_match_decoder(const lmb200_node_list* list, int32_t output_id, lmb200_model_config* cfg,
                                         lmb200_decoder_match* info, int32_t* weight_nodes, int32_t weight_capacity,
                                         char* names_out, int64_t names_capacity) {
   try {
-    Match m = match_decoder(list, output_id);
-    if (cfg) *cfg = m.cfg;
-    if (info) *info = m.info;
-    if (weight_nodes)
-      for (int32_t k = 0; k < weight_capacity && k < (int32_t)m.weights.size(); ++k) weight_nodes[k] = m.weights[k].second;
-    if (names_out && names_capacity > 0) {
-      std::string all;
-      for (size_t k = 0; k < m.weights.size(); ++k) {
-        const std::string add = (k ? "\n" : "") + m.weights[k].first;
-        if ((int64_t)(all.size() + add.size()) >= names_capacity) break;
-        all += add;
-      }
-      std::memcpy(names_out, all.c_str(), all.size() + 1);
-    }
-    return LMB200_OK;
+    return report(match_decoder(list, output_id), cfg, info, weight_nodes, weight_capacity, names_out, names_capacity);
+  } catch (const NoMatch& e) {
+    return lmb::fail(LMB200_ENOMATCH, "%s", e.what.c_str());
+  } catch (const std::exception& e) {
+    return lmb::fail(LMB200_EINVAL, "node list: %s", e.what());
+  }
+}
+
+extern "C" int32_t lmb200_match_whisper_step(const lmb200_node_list* list, int32_t logits_id, lmb200_model_config* cfg,
+                                             lmb200_decoder_match* info, int32_t* weight_nodes, int32_t weight_capacity,
+                                             char* names_out, int64_t names_capacity, int32_t* cache_nodes,
+                                             int32_t cache_capacity) {
+  try {
+    Match m = match_whisper_step(list, logits_id);
+    if (cache_nodes)
+      for (int32_t k = 0; k < cache_capacity && k < (int32_t)m.cache.size(); ++k) cache_nodes[k] = m.cache[k];
+    return report(m, cfg, info, weight_nodes, weight_capacity, names_out, names_capacity);
   } catch (const NoMatch& e) {
     return lmb::fail(LMB200_ENOMATCH, "%s", e.what.c_str());
   } catch (const std::exception& e) {
@@ -523,13 +930,14 @@ extern "C" int32_t lmb200_compile_node_list(lmb200_ctx ctx, const lmb200_node_li
   LMB_REQUIRE(dtype == LMB200_F32 || dtype == LMB200_BF16, "lmb200_compile_node_list: dtype must be float32 or bf16");
   Match m;
   try {
-    m = match_decoder(list, output_id);
+    m = match_any(list, output_id);
   } catch (const NoMatch& e) {
     return lmb::fail(LMB200_ENOMATCH, "%s", e.what.c_str());
   } catch (const std::exception& e) {
     return lmb::fail(LMB200_EINVAL, "node list: %s", e.what());
   }
-  if (m.info.prev_seq != 0)
+  const bool whisper = m.info.arch == LMB200_ARCH_WHISPER_DECODER;
+  if (!whisper && m.info.prev_seq != 0)
     return lmb::fail(LMB200_ENOMATCH, "the graph was traced with prev_seq = %d: a cached session starts at position 0",
                      m.info.prev_seq);
   for (auto& kv : m.weights)
@@ -545,8 +953,23 @@ extern "C" int32_t lmb200_compile_node_list(lmb200_ctx ctx, const lmb200_node_li
     if (rc != LMB200_OK) { lmb200_model_destroy(model); return rc; }
   }
   lmb200_session session = 0;
-  rc = lmb200_session_create(model, batch > 0 ? batch : m.info.batch, max_ctx, &session);
+  rc = lmb200_session_create(model, batch > 0 ? batch : m.info.batch, whisper && max_ctx <= 0 ? m.info.max_seq : max_ctx, &session);
   if (rc != LMB200_OK) { lmb200_model_destroy(model); return rc; }
+  if (whisper) {
+    // the encoder K / V the step graph takes as inputs (decode_step! feeds them at every step, src/Whisper.jl:770-778)
+    // are uploaded once, where the caller has them already
+    const int L = m.cfg.n_layers;
+    for (int l = 0; l < L; ++l) {
+      const float* k = node_data[m.cache[l] - 1];
+      const float* v = node_data[m.cache[L + l] - 1];
+      if (!k && !v) continue;
+      if (!k || !v || (batch > 0 && batch != m.info.batch))
+        rc = lmb::fail(LMB200_EINVAL, "layer %d: cross K and V come as a pair, shaped for the graph's batch", l);
+      else
+        rc = lmb200_session_set_cross_kv(session, l, k, v, layout);
+      if (rc != LMB200_OK) { lmb200_session_destroy(session); lmb200_model_destroy(model); return rc; }
+    }
+  }
   *model_out = model;
   *session_out = session;
   if (info) *info = m.info;

@@ -121,7 +121,8 @@ class NodeList(C.Structure):
 
 
 class DecoderMatchInfo(C.Structure):
-    _fields_ = [(n, C.c_int32) for n in ("batch", "seq", "prev_seq", "tokens_node", "n_weights", "reserved")]
+    """lmb200_decoder_match"""
+    _fields_ = [(n, C.c_int32) for n in ("arch", "batch", "seq", "prev_seq", "tokens_node", "n_weights", "max_seq", "cross_len")]
 
 
 def flatten_graph(graph) -> NodeList:
@@ -199,44 +200,125 @@ def match_decoder(graph, output_id: int) -> DecoderMatch:
                         tokens=info.tokens_node, weights={n: int(nodes[k]) for k, n in enumerate(wnames)})
 
 
+@dataclass
+class WhisperStepMatch:
+    """What the matcher found in a build_decode_step graph (src/Whisper.jl:687-742).  `weights` maps the registry
+    names of the model.decoder.* tensors the cached session needs to input node ids; the other lists are the ids of
+    IncrementalDecodeGraph (src/Whisper.jl:662-672)."""
+    n_layers: int
+    d_model: int
+    heads: int
+    ffn: int
+    vocab: int
+    max_positions: int
+    eps: float
+    batch: int
+    step_pos: int
+    max_seq: int
+    enc_seq: int
+    tokens: int
+    weights: Dict[str, int] = field(default_factory=dict)
+    cross_k_ids: List[int] = field(default_factory=list)
+    cross_v_ids: List[int] = field(default_factory=list)
+    self_k_ids: List[int] = field(default_factory=list)
+    self_v_ids: List[int] = field(default_factory=list)
+    new_self_k_ids: List[int] = field(default_factory=list)
+    new_self_v_ids: List[int] = field(default_factory=list)
+
+
+def match_whisper_step(graph, logits_id: int) -> WhisperStepMatch:
+    """Recognises the Whisper TextDecoder's incremental decode step ending in the logits node `logits_id` --
+    lmb200_match_whisper_step; needs no GPU.  Raises MatchError at the first node that does not fit."""
+    from . import _lib
+    from .session import ModelConfig
+    nl = flatten_graph(graph)
+    cfg, info = ModelConfig(), DecoderMatchInfo()
+    cap = max(len(graph.nodes), 1)
+    nodes, cache = (C.c_int32 * cap)(), (C.c_int32 * cap)()
+    names = C.create_string_buffer(64 * cap + 256)
+    try:
+        _lib.call("lmb200_match_whisper_step", C.byref(nl), int(logits_id), C.byref(cfg), C.byref(info), nodes, cap, names,
+                  len(names), cache, cap)
+    except _lib.LuminalB200Error as e:
+        _raise_match(e)
+    wnames = names.value.decode().split("\n")
+    L = cfg.n_layers
+    part = lambda k: [int(cache[k * L + l]) for l in range(L)]
+    return WhisperStepMatch(n_layers=L, d_model=cfg.hidden, heads=cfg.n_heads, ffn=cfg.intermediate, vocab=cfg.vocab,
+                            max_positions=cfg.max_positions, eps=float(cfg.rms_eps), batch=info.batch, step_pos=info.prev_seq,
+                            max_seq=info.max_seq, enc_seq=info.cross_len, tokens=info.tokens_node,
+                            weights={n: int(nodes[k]) for k, n in enumerate(wnames)}, cross_k_ids=part(0), cross_v_ids=part(1),
+                            self_k_ids=part(2), self_v_ids=part(3), new_self_k_ids=part(4), new_self_v_ids=part(5))
+
+
 def compile_b200(graph, output_id, inputs=None, device=None, max_ctx=2048, dtype="f32", batch=None):
-    """compile() for a graph the matcher recognises (lmb200_compile_node_list): returns (Session, DecoderMatch).
+    """compile() for a graph one of the matchers recognises (lmb200_compile_node_list): returns (Session, match).
     The weights come from `inputs` (node id -> array, as execute() takes them) or from data pre-loaded into
     graph.tensors (src/Weights.jl:60-114 fills those).  The session keeps a KV cache, so the caller feeds it the
-    tokens the graph was traced for (prefill) and then one token per step, instead of re-running a longer graph
-    for every position as examples/llama.jl:39-99 does."""
+    tokens the graph was traced for (prefill) and then one token per step, instead of re-running a longer graph for
+    every position as examples/llama.jl:39-99 does -- or, for a Whisper decode-step graph, instead of building and
+    compiling one graph per position (src/Whisper.jl:679-801); encoder K/V inputs that have data are uploaded to the
+    session's cross cache."""
     from . import _lib
     from .device import DeviceArray, get_device
     from .session import Model, Session, _dtype_code
-    m = match_decoder(graph, output_id)
-    if m.prev_seq != 0:
-        raise MatchError("the graph was traced with prev_seq != 0: a cached session starts at position 0")
+    try:
+        m = match_decoder(graph, output_id)
+        if m.prev_seq != 0:
+            raise MatchError("the graph was traced with prev_seq != 0: a cached session starts at position 0")
+        whisper, needed = False, dict(m.weights)
+    except MatchError as first:
+        try:
+            m = match_whisper_step(graph, output_id)
+        except MatchError:
+            raise first from None
+        whisper, needed = True, dict(m.weights)
     dev = device or get_device()
     inputs = inputs or {}
-    host, data = [], (C.c_void_p * len(graph.nodes))()
-    for name, node_id in m.weights.items():
+
+    def data_of(node_id):
         a = inputs.get(node_id)
         if a is None:
             a = graph.tensors.get((node_id, 1))
         if a is None:
-            raise KeyError(f"{name} (node {node_id}) has no data")
+            return None
         a = np.ascontiguousarray(a.numpy() if isinstance(a, DeviceArray) else a, dtype=np.float32)
         if a.shape != tuple(graph.shapes[node_id - 1]):
-            raise ValueError(f"{name} (node {node_id}): data of shape {a.shape}, node of shape {graph.shapes[node_id - 1]}")
+            raise ValueError(f"node {node_id}: data of shape {a.shape}, node of shape {graph.shapes[node_id - 1]}")
+        return a
+
+    host, data = [], (C.c_void_p * len(graph.nodes))()
+    for name, node_id in needed.items():
+        a = data_of(node_id)
+        if a is None:
+            raise KeyError(f"{name} (node {node_id}) has no data")
         host.append(a)
         data[node_id - 1] = a.ctypes.data
+    if whisper:
+        for node_id in m.cross_k_ids + m.cross_v_ids:
+            a = data_of(node_id)
+            if a is not None:
+                host.append(a)
+                data[node_id - 1] = a.ctypes.data
     nl = flatten_graph(graph)
     model_h, session_h, info = C.c_uint64(), C.c_uint64(), DecoderMatchInfo()
+    if whisper:
+        max_ctx = m.max_seq
     try:
         _lib.call("lmb200_compile_node_list", dev.handle, C.byref(nl), int(output_id), data, _lib.ROWMAJOR,
-                  _dtype_code(dtype), int(batch or 0), int(max_ctx),
-                  C.byref(model_h), C.byref(session_h), C.byref(info))
+                  _dtype_code(dtype), int(batch or 0), int(max_ctx), C.byref(model_h), C.byref(session_h), C.byref(info))
     except _lib.LuminalB200Error as e:
         _raise_match(e)
-    model = Model.adopt(dev, model_h.value, n_layers=m.n_layers, hidden=m.hidden, n_heads=m.n_heads, n_kv_heads=m.n_kv_heads,
-                        intermediate=m.intermediate, vocab=m.vocab, eps=m.eps, rope_base=m.rope_base, dtype=dtype)
+    if whisper:
+        model = Model.adopt(dev, model_h.value, n_layers=m.n_layers, hidden=m.d_model, n_heads=m.heads, n_kv_heads=m.heads,
+                            intermediate=m.ffn, vocab=m.vocab, eps=m.eps, rope_base=10000.0, dtype=dtype, arch=1,
+                            max_positions=m.max_positions, cross_len=m.enc_seq)
+    else:
+        model = Model.adopt(dev, model_h.value, n_layers=m.n_layers, hidden=m.hidden, n_heads=m.n_heads,
+                            n_kv_heads=m.n_kv_heads, intermediate=m.intermediate, vocab=m.vocab, eps=m.eps,
+                            rope_base=m.rope_base, dtype=dtype)
     return Session.adopt(model, session_h.value, batch or m.batch, max_ctx), m
 
 
-__all__ = ["MatchError", "DecoderMatch", "NodeList", "export_graph", "import_graph", "flatten_graph", "match_decoder",
-           "compile_b200"]
+__all__ = ["MatchError", "DecoderMatch", "WhisperStepMatch", "NodeList", "export_graph", "import_graph", "flatten_graph",
+           "match_decoder", "match_whisper_step", "compile_b200"]

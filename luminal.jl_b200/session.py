@@ -35,14 +35,15 @@ class Model:
         self.handle = h
 
     @classmethod
-    def adopt(cls, device, handle, *, n_layers, hidden, n_heads, n_kv_heads, intermediate, vocab, eps, rope_base, dtype):
+    def adopt(cls, device, handle, *, n_layers, hidden, n_heads, n_kv_heads, intermediate, vocab, eps, rope_base, dtype,
+              arch=0, max_positions=0, cross_len=0):
         """Wraps a model handle the library created (lmb200_compile_node_list)."""
         self = cls.__new__(cls)
         self.device = device
         self.cfg = ModelConfig(n_layers=n_layers, hidden=hidden, n_heads=n_heads, n_kv_heads=n_kv_heads,
                                head_dim=hidden // n_heads, intermediate=intermediate, vocab=vocab, rms_eps=eps,
-                               rope_base=rope_base, dtype=_dtype_code(dtype), tp_size=1, tp_rank=0, arch=0,
-                               max_positions=0, cross_len=0)
+                               rope_base=rope_base, dtype=_dtype_code(dtype), tp_size=1, tp_rank=0, arch=arch,
+                               max_positions=max_positions, cross_len=cross_len)
         self.handle = C.c_uint64(int(handle))
         return self
 

@@ -1,6 +1,6 @@
-"""Whisper as graph builders: the Python stand-in for src/Whisper.jl:208-404, 809-831 and for
-NN.Conv1D (src/NN.jl:38-104) -- sinusoids, self attention, encoder blocks, AudioEncoder and
-project_cross_kv -- with the model sizes as arguments instead of the reference's hard-coded
+"""Whisper as graph builders: the Python stand-in for src/Whisper.jl:208-404, 406-742, 809-831 and for
+NN.Conv1D (src/NN.jl:38-104) -- sinusoids, self attention, encoder blocks, AudioEncoder,
+project_cross_kv, TextDecoder and its incremental decode-step graph -- with the model sizes as arguments instead of the reference's hard-coded
 whisper-tiny constants (src/Whisper.jl:195-206).  The encoder and the cross-K/V projection run
 once per utterance through execute() (one device call per node); the per-token decoder runs in
 the fused session (session.WhisperDecoderModel).
@@ -148,6 +148,111 @@ def project_cross_kv(graph, reg, enc_output, *, d_model, heads, layers):     # s
         v = G.permute(G.reshape(v_proj(enc_output), [batch, seq, heads, D]), [1, 3, 2, 4])
         out.append((k, v))
     return out
+
+
+# ---------------------------------------------------------------------------------------------
+# TextDecoder and its incremental decode-step graph (src/Whisper.jl:406-742)
+# ---------------------------------------------------------------------------------------------
+class WhisperCrossAttention:                     # src/Whisper.jl:282-316 (parameters; the cached call is below)
+    def __init__(self, hidden, heads, graph, reg, prefix):
+        self.q_proj = WLinear(hidden, hidden, graph, reg, f"{prefix}.q_proj", bias=True)
+        self.k_proj = WLinear(hidden, hidden, graph, reg, f"{prefix}.k_proj", bias=False)
+        self.v_proj = WLinear(hidden, hidden, graph, reg, f"{prefix}.v_proj", bias=True)
+        self.o_proj = WLinear(hidden, hidden, graph, reg, f"{prefix}.out_proj", bias=True)
+        self.heads = heads
+
+
+class DecoderTransformerBlock:                   # src/Whisper.jl:410-432
+    def __init__(self, hidden, heads, ff, graph, reg, prefix):
+        self.attn = WhisperSelfAttention(hidden, heads, graph, reg, f"{prefix}.self_attn")
+        self.attn_norm = WLayerNorm(hidden, graph, reg, f"{prefix}.self_attn_layer_norm")
+        self.cross_attn = WhisperCrossAttention(hidden, heads, graph, reg, f"{prefix}.encoder_attn")
+        self.cross_attn_norm = WLayerNorm(hidden, graph, reg, f"{prefix}.encoder_attn_layer_norm")
+        self.ff1 = WLinear(hidden, ff, graph, reg, f"{prefix}.fc1")
+        self.ff2 = WLinear(ff, hidden, graph, reg, f"{prefix}.fc2")
+        self.ff_norm = WLayerNorm(hidden, graph, reg, f"{prefix}.final_layer_norm")
+
+
+class TextDecoder:                               # src/Whisper.jl:449-486
+    def __init__(self, graph, reg, *, d_model, heads, layers, ffn, vocab, max_positions):
+        pfx = "model.decoder"
+        self.d_model, self.heads, self.max_positions = d_model, heads, max_positions
+        self.embedding = G.tensor(graph, [vocab, d_model])
+        self.pos_embedding = G.tensor(graph, [max_positions, d_model])
+        reg[f"{pfx}.embed_tokens.weight"], reg[f"{pfx}.embed_positions.weight"] = self.embedding, self.pos_embedding
+        self.layers = [DecoderTransformerBlock(d_model, heads, ffn, graph, reg, f"{pfx}.layers.{i}") for i in range(layers)]
+        self.layer_norm = WLayerNorm(d_model, graph, reg, f"{pfx}.layer_norm")
+
+
+def _kv_scatter(past, new_slot, step_pos):       # src/Whisper.jl:541-570: slice-and-concat write of one cache slot
+    max_seq = past.shape[2]
+    if step_pos == 0:
+        return G.concat_along(new_slot, G.slice_along(past, 3, 1, max_seq), 3)
+    head = G.concat_along(G.slice_along(past, 3, 0, step_pos), new_slot, 3)
+    if max_seq - step_pos - 1 == 0:
+        return head
+    return G.concat_along(head, G.slice_along(past, 3, step_pos + 1, max_seq), 3)
+
+
+def whisper_self_attn_cached(sa, x, step_pos, past_k, past_v):       # src/Whisper.jl:584-625
+    batch, _, hidden = x.shape
+    H, D = sa.heads, hidden // sa.heads
+    scale = F32(F32(F32(hidden) / F32(H)) ** F32(-0.25))
+    q = G.permute(G.reshape(sa.q_proj(x) * scale, [batch, 1, H, D]), [1, 3, 2, 4])
+    k_new = G.contiguous(G.permute(G.reshape(sa.k_proj(x) * scale, [batch, 1, H, D]), [1, 3, 2, 4]))
+    v_new = G.permute(G.reshape(sa.v_proj(x), [batch, 1, H, D]), [1, 3, 2, 4])
+    new_k, new_v = _kv_scatter(past_k, k_new, step_pos), _kv_scatter(past_v, v_new, step_pos)
+    k_ctx = G.slice_along(new_k, 3, 0, step_pos + 1)
+    v_ctx = G.slice_along(new_v, 3, 0, step_pos + 1)
+    probs = G.softmax(G.matmul(q, G.contiguous(G.permute(k_ctx, [1, 2, 4, 3]))), 4)
+    out = G.reshape(G.permute(G.matmul(probs, v_ctx), [1, 3, 2, 4]), [batch, 1, hidden])
+    return sa.o_proj(out), new_k, new_v
+
+
+def whisper_cross_attn_cached(ca, x, enc_k, enc_v):                  # src/Whisper.jl:633-651
+    batch, _, hidden = x.shape
+    H, D = ca.heads, hidden // ca.heads
+    scale = F32(F32(F32(hidden) / F32(H)) ** F32(-0.25))
+    q = G.permute(G.reshape(ca.q_proj(x) * scale, [batch, 1, H, D]), [1, 3, 2, 4])
+    probs = G.softmax(G.matmul(q, G.contiguous(G.permute(enc_k, [1, 2, 4, 3]))), 4)
+    out = G.reshape(G.permute(G.matmul(probs, enc_v), [1, 3, 2, 4]), [batch, 1, hidden])
+    return ca.o_proj(out)
+
+
+class IncrementalDecodeGraph:                    # src/Whisper.jl:662-672: node ids for driving one step
+    def __init__(self, **kw):
+        self.__dict__.update(kw)
+
+
+def build_decode_step(td, graph, enc_seq, step_pos, *, max_seq=None, batch=1):     # src/Whisper.jl:687-742
+    """One step of the incremental decode graph for position `step_pos` (baked into the slice positions, so the
+    reference builds one graph per position).  Inputs: the token [batch, 1], per layer the cross K/V [batch, heads,
+    enc_seq, head_dim] and the past self K/V [batch, heads, max_seq, head_dim]; outputs: logits [batch, 1, vocab] and
+    the updated self K/V."""
+    max_seq = max_seq or td.max_positions
+    H, D, L = td.heads, td.d_model // td.heads, len(td.layers)
+    token_in = G.tensor(graph, [batch, 1])
+    cross_k = [G.tensor(graph, [batch, H, enc_seq, D]) for _ in range(L)]
+    cross_v = [G.tensor(graph, [batch, H, enc_seq, D]) for _ in range(L)]
+    self_k = [G.tensor(graph, [batch, H, max_seq, D]) for _ in range(L)]
+    self_v = [G.tensor(graph, [batch, H, max_seq, D]) for _ in range(L)]
+    x = G.gather(td.embedding, token_in)
+    pos_slot = G.contiguous(G.slice_along(td.pos_embedding, 1, step_pos, step_pos + 1))
+    x = x + G.expand(pos_slot, 1, batch)
+    new_k, new_v = [], []
+    for i, layer in enumerate(td.layers):
+        attn_out, nk, nv = whisper_self_attn_cached(layer.attn, layer.attn_norm(x), step_pos, self_k[i], self_v[i])
+        x = x + attn_out
+        new_k.append(nk)
+        new_v.append(nv)
+        x = x + whisper_cross_attn_cached(layer.cross_attn, layer.cross_attn_norm(x), cross_k[i], cross_v[i])
+        x = x + layer.ff2(G.gelu(layer.ff1(layer.ff_norm(x))))
+    out = td.layer_norm(x)
+    logits = G.matmul(G.contiguous(G.slice_along(out, 2, 0, 1)), G.permute(td.embedding, [2, 1]))
+    ids = lambda ts: [t.id for t in ts]
+    return IncrementalDecodeGraph(token_input_id=token_in.id, cross_k_ids=ids(cross_k), cross_v_ids=ids(cross_v),
+                                  self_k_ids=ids(self_k), self_v_ids=ids(self_v), logits_id=logits.id,
+                                  new_self_k_ids=ids(new_k), new_self_v_ids=ids(new_v), step_pos=step_pos)
 
 
 def encode_cross_kv(device, weights, mel, *, d_model, heads, enc_layers, dec_layers, ffn, n_mels):
