@@ -345,8 +345,6 @@ __global__ void __launch_bounds__(kRingThreads, 1) gemv_ring_kernel(const GemvPa
 // bf16 stream-K kernels
 // =============================================================================================
 constexpr int kStages = 5;
-constexpr int kClusterLightSteps = 8;    // a cluster-GEMV CTA with at most this many k steps ...
-constexpr int kClusterLightStages = 5;   // ... allocates at most this many stages (5: no limit)
 constexpr int kWStage = 32768;                   // 128 rows x 128 k, bf16
 constexpr long long kWaitLimit = 4000000000LL;   // clock cycles (~2 s) before a wait gives up
 
@@ -1123,12 +1121,12 @@ __device__ __forceinline__ void cluster_sync_all() {
 }
 
 template <int N>
-__global__ void __launch_bounds__(kTcThreads, 2) gemv_cl_kernel(const GemvParams p, int* err) {
+__global__ void __launch_bounds__(kTcThreads, 1) gemv_cl_kernel(const GemvParams p, int* err) {
   constexpr int kXStage = N * 256;
   constexpr int kStage = kWStage + kXStage;
   constexpr uint32_t kTmemCols = N < 32 ? 32 : N;     // an allocation is at least 32 columns
   constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((128u >> 4) << 24);
-  extern __shared__ __align__(1024) unsigned char smem[];       // p.cl_stages stages, then recv[C][128 / C][N] floats
+  extern __shared__ __align__(1024) unsigned char smem[];       // kStages stages, then recv[C][128 / C][N] floats
   __shared__ __align__(8) uint64_t full_bar[kStages];
   __shared__ __align__(8) uint64_t empty_bar[kStages];
   __shared__ __align__(8) uint64_t acc_full;
@@ -1143,8 +1141,6 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemv_cl_kernel(const GemvParams
   const int KS = (p.K + 127) >> 7;
   const int ks0 = (int)((long long)c * KS / C), ks1 = (int)((long long)(c + 1) * KS / C);
   const int n_steps = ks1 - ks0;
-  const int S = p.cl_stages;                                      // stages the launch allocated (<= kStages)
-  unsigned char* const recv_buf = smem + S * kStage;
   if (tid == 0) {
     LMB_TRACE(0); LMB_TRACE_NS(10);
 #pragma unroll
@@ -1176,7 +1172,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemv_cl_kernel(const GemvParams
     asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;\n" : "=l"(pol_x));
     const __nv_bfloat16* W = reinterpret_cast<const __nv_bfloat16*>(p.W) + ((int64_t)r * KS + ks0) * 16384;
     const __nv_bfloat16* X = reinterpret_cast<const __nv_bfloat16*>(p.x) + (int64_t)ks0 * (128 * N);
-    const int n_pre = n_steps < S ? n_steps : S;
+    const int n_pre = n_steps < kStages ? n_steps : kStages;
     if (lane == 0) {
       for (int i = 0; i < n_pre; ++i) {
         mbar_expect_tx(&full_bar[i], (uint32_t)kStage);
@@ -1190,7 +1186,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemv_cl_kernel(const GemvParams
     }
     __syncwarp();
     for (int i = n_pre; i < n_steps; ++i) {
-      const int s = i % S, k = i / S;
+      const int s = i % kStages, k = i / kStages;
       mbar_wait(&empty_bar[s], (k & 1) ^ 1, dead, err);
       if (lane == 0) {
         unsigned char* sp = smem + s * kStage;
@@ -1206,7 +1202,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemv_cl_kernel(const GemvParams
     pdl_wait();
     if (lane == 0) LMB_TRACE(2);
     for (int i = 0; i < n_steps; ++i) {
-      const int s = i % S, k = i / S;
+      const int s = i % kStages, k = i / kStages;
       mbar_wait(&full_bar[s], k & 1, dead, err);
       tc_fence_after();
       if (lane == 0 && i == 0) LMB_TRACE(3);
@@ -1243,7 +1239,7 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemv_cl_kernel(const GemvParams
     const int rows_per = 128 / C;
     const int row = 32 * q + lane;
     const int owner = row / rows_per, row_local = row - owner * rows_per;
-    const uint32_t recv_local = smem_u32(recv_buf) + (uint32_t)(((c * rows_per + row_local) * N) * 4);
+    const uint32_t recv_local = smem_u32(smem + kStages * kStage) + (uint32_t)(((c * rows_per + row_local) * N) * 4);
     const uint32_t dst = dsmem_addr(recv_local, (uint32_t)owner);
 #pragma unroll
     for (int i = 0; i < N / 4; ++i) dsmem_store4(dst + 16u * i, v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
@@ -1253,13 +1249,13 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemv_cl_kernel(const GemvParams
   cluster_sync_all();
   if (tid == 64) LMB_TRACE(7);
   if (warp >= 2 && p.epi == EPI_RESID_NORM) {
-    resid_norm_tile<N>(p, recv_buf, C, c, r, tid - 64, s_red);
+    resid_norm_tile<N>(p, smem + kStages * kStage, C, c, r, tid - 64, s_red);
   } else if (warp >= 2) {
     const int e = tid - 64;
     const int rows_per = 128 / C;
     const int row16 = lane & 15, cg = e >> 4;               // one float4 (4 batch columns) per thread
     if (cg < N / 4) {
-      const float4* recv = reinterpret_cast<const float4*>(recv_buf);
+      const float4* recv = reinterpret_cast<const float4*>(smem + kStages * kStage);
       for (int j = 0; j < rows_per / 16; ++j) {
         float v4[4] = {0.f, 0.f, 0.f, 0.f};
         for (int src = 0; src < C; ++src) {
@@ -1281,26 +1277,8 @@ __global__ void __launch_bounds__(kTcThreads, 2) gemv_cl_kernel(const GemvParams
 }
 
 template <int Bp>
-constexpr size_t cluster_smem(int stages = kStages) {
-  return (size_t)stages * (kWStage + Bp * 256) + 128 * Bp * 4 + 1024;
-}
-
-// Pipeline stages of one cluster-GEMV launch: never more than the k steps a CTA has, and -- where a CTA has only a few
-// steps (a tensor-parallel shard) -- few enough that two CTAs fit one SM: the next GEMV's CTAs, launched
-// programmatically, then become resident beside this kernel's and stream their weights while this kernel is still in
-// its exchange and epilogue.  LMB200_GEMV_CL_STAGES=n overrides the limit of the second rule (A/B runs).
-inline int cluster_stages(const GemvParams& p) {
-  static const int forced = [] {
-    const char* e = getenv("LMB200_GEMV_CL_STAGES");
-    const int v = e ? atoi(e) : 0;
-    return v >= 1 && v <= kStages ? v : 0;
-  }();
-  const int KS = (int)ceil_div(p.K, 128), C = p.cluster > 0 ? p.cluster : 1;
-  const int steps = (int)ceil_div(KS, C);
-  int s = steps < kStages ? steps : kStages;
-  const int light = forced ? forced : kClusterLightStages;
-  if (steps <= kClusterLightSteps && s > light) s = light;
-  return s < 1 ? 1 : s;
+constexpr size_t cluster_smem() {
+  return (size_t)kStages * (kWStage + Bp * 256) + 128 * Bp * 4 + 1024;
 }
 
 template <int Bp>
@@ -1308,9 +1286,7 @@ int32_t launch_cluster(Ctx* ctx, const GemvParams& p, cudaStream_t stream) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(ceil_div(p.rows, 128) * p.cluster));
   cfg.blockDim = dim3(kTcThreads);
-  GemvParams q = p;
-  q.cl_stages = cluster_stages(p);
-  cfg.dynamicSmemBytes = cluster_smem<Bp>(q.cl_stages);
+  cfg.dynamicSmemBytes = cluster_smem<Bp>();
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -1321,7 +1297,7 @@ int32_t launch_cluster(Ctx* ctx, const GemvParams& p, cudaStream_t stream) {
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl_enabled() ? 2 : 1;
-  LMB_CUDA(cudaLaunchKernelEx(&cfg, gemv_cl_kernel<Bp>, q, ctx->dev_err));
+  LMB_CUDA(cudaLaunchKernelEx(&cfg, gemv_cl_kernel<Bp>, p, ctx->dev_err));
   ctx->launches++;
   return LMB200_OK;
 }

@@ -80,7 +80,6 @@ struct GemvParams {
   int kc_per_split = 0;
   int grid = 0;              // bf16 kernels: number of CTAs
   int cluster = 0;           // > 1: one thread-block cluster of this size per 128-row group (small matrices)
-  int cl_stages = 5;         // cluster kernel: pipeline stages its dynamic shared memory holds (set by the launch)
   float* partials = nullptr;     // split-K scratch
   unsigned* counters = nullptr;  // zero between launches
   int epi = EPI_STORE_F32;

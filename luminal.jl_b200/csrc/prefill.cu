@@ -34,6 +34,7 @@ namespace {
 
 constexpr int kGemmThreads = 6 * 32;
 constexpr int kUnitBytes = 32768;
+constexpr int kEpiStageBytes = 32 * 80;        // per epilogue warp: 32 tokens x 32 bf16 outputs, rows of 80 bytes
 constexpr float kInvLn2 = 1.4426950408889634f;
 constexpr float kHalfPi = 1.5707963267948966f;
 
@@ -63,6 +64,12 @@ struct GemmParams {
   void* out_any = nullptr;
   const float2* rope = nullptr;         // [n_seq, D/2]: (sin, cos) of position pos0 + s times inv_freq[d0]
   int pos0 = 0, n_seq = 1, Hl = 0, KVl = 0, D = 0;
+  // Implicit 1-D convolution (conv_taps > 0; src/NN.jl:55-104 without the unfolded buffer): X is the token-major input
+  // [conv_B][conv_rows_in][ldx] (channels contiguous, conv_rows_in a multiple of the stride conv_P, rows past the valid
+  // input zero), output position o of batch b reads input rows o * conv_P + tap - conv_pad (rows outside the tensor read
+  // as zeros: the padding), K = conv_taps * conv_cpad with W's column tap * conv_cpad + c the weight of (c, tap).  The
+  // accumulator of (b, o) is stored at token index b * conv_out_rpb + o.
+  int conv_taps = 0, conv_P = 1, conv_pad = 0, conv_C = 0, conv_cpad = 0, conv_B = 0, conv_rows_in = 0, conv_Lout = 0, conv_out_rpb = 0;
 };
 
 // GELU with the reference's tanh (src/HighLevelOps.jl:162-168): tanh z = sigmoid(2z) * 2 - 1
@@ -80,13 +87,13 @@ __device__ __forceinline__ uint32_t canon(int row, int c8, int rows) {
 
 // v[i] = accumulator of (row, token t0 + i).  Rows g and g+8 of a 16-row block, which the fused
 // epilogues combine, are 8 lanes apart.
-__device__ __forceinline__ void gemm_epilogue(const GemmParams& p, float (&v)[32], int row, int t0) {
+__device__ __forceinline__ void gemm_epilogue(const GemmParams& p, float (&v)[32], int row, int t0, int t_end, unsigned char* stage) {
   const int rb = row >> 4, rr = row & 15, g = rr & 7, hi = rr >> 3;
   if (p.epi == GEMM_STORE_F32) {
     if (row < p.rows) {
 #pragma unroll
       for (int i = 0; i < 32; ++i)
-        if (t0 + i < p.T) p.out[(int64_t)(t0 + i) * p.ldo + row] = v[i];
+        if (t0 + i < t_end) p.out[(int64_t)(t0 + i) * p.ldo + row] = v[i];
     }
     return;
   }
@@ -97,7 +104,7 @@ __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, float (&v)[32
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
       const int t = t0 + i;
-      if (t >= p.T) continue;
+      if (t >= t_end) continue;
       float y = v[i] + bias;
       if (p.gelu) y = gelu_ref(y);
       y *= p.out_scale;
@@ -113,63 +120,96 @@ __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, float (&v)[32
     }
     return;
   }
+  // The fused epilogues below give every thread (one row) 32 tokens of one column of the output: stored directly,
+  // a warp's store instruction would write 16-byte pieces of 32 different token rows.  Instead the warp turns its
+  // 32 x 32 block round through its own 2.5 KB of shared memory (rows of 80 bytes: conflict-free both ways), after
+  // which lane L holds token t0 + L's 32 outputs and writes them as 16-byte vectors.
   float w[32];
 #pragma unroll
   for (int i = 0; i < 32; ++i) w[i] = __shfl_xor_sync(0xffffffffu, v[i], 8);
-  if (row >= p.rows) return;
+  const int lane = threadIdx.x & 31;
+  const int rbl = (row >> 4) & 1;                      // which of the warp's two 16-row blocks
+  const int row0 = row & ~31;                          // the warp's first row: rows row0 .. row0 + 31 (a multiple of 32)
+  __nv_bfloat16* st = reinterpret_cast<__nv_bfloat16*>(stage);
+  constexpr int kPitch = 40;                           // bf16 elements per staged token row (80 bytes)
+  const int tL = t0 + lane;                            // the token this lane stores after the turn
   if (p.epi == GEMM_SILU_GATE) {
-    const int o = rb * 8 + g;
-    if (hi == 0 && o < p.n_act) {
+    // column of (rb, g): rbl * 8 + g, 16 outputs per token = act[t, (row0 / 16) * 8 .. + 16)
+    if (hi == 0) {
+      const int col = rbl * 8 + g;
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
-        if (t0 + i < p.T) {
-          const float a = v[i], u = w[i];
-          const float ex = exp2f((a * -1.0f) * kInvLn2);          // src/HighLevelOps.jl:153-160
-          const float sg = 1.0f / (1.0f + ex);
-          p.act[(int64_t)(t0 + i) * p.ld_act + o] = __float2bfloat16_rn((a * sg) * u);
-        }
+        const float a = v[i], u = w[i];
+        const float ex = exp2f((a * -1.0f) * kInvLn2);          // src/HighLevelOps.jl:153-160
+        const float sg = 1.0f / (1.0f + ex);
+        st[i * kPitch + col] = __float2bfloat16_rn((a * sg) * u);
       }
     }
+    __syncwarp();
+    const int o0 = (row0 >> 4) * 8;
+    if (tL < t_end && o0 < p.n_act) {
+      __nv_bfloat16* dst = p.act + (int64_t)tL * p.ld_act + o0;
+      const uint4* src = reinterpret_cast<const uint4*>(st + lane * kPitch);
+      if (o0 + 16 <= p.n_act && (p.ld_act & 7) == 0) {
+        reinterpret_cast<uint4*>(dst)[0] = src[0];
+        reinterpret_cast<uint4*>(dst)[1] = src[1];
+      } else {
+        for (int c = 0; c < 16 && o0 + c < p.n_act; ++c) dst[c] = st[lane * kPitch + c];
+      }
+    }
+    __syncwarp();
     return;
   }
   // GEMM_QKV_ROPE
   const int D = p.D, tiles_per_head = D >> 4, half = D >> 1;
   const int hs = rb / tiles_per_head, jj = rb - hs * tiles_per_head;
+  const int jj0 = jj - rbl;                            // the warp's first 16-row block inside the head (even)
+  const bool live = row0 < p.rows;                     // uniform over the warp (rows is a multiple of 32 here)
   if (hs < p.Hl + p.KVl) {
     const int d0 = 8 * jj + g;                         // rows g / g+8 are the pair (d0, d0 + D/2), src/NN.jl:253-303
-    const int d = hi ? d0 + half : d0;
-    // all table reads of the chunk first: between stores the compiler could not move them
-    float2 sc[32];
-    int sq = t0 % p.n_seq;
+    // staged columns: [0, 16) = d 8*jj0 .. + 15, [16, 32) = D/2 + the same
+    const int col = rbl * 8 + g + (hi ? 16 : 0);
+    if (live) {
+      // all table reads of the chunk first: between stores the compiler could not move them
+      float2 sc[32];
+      int sq = t0 % p.n_seq;
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      sc[i] = (t0 + i < p.T) ? __ldg(p.rope + (int64_t)sq * half + d0) : make_float2(0.f, 1.f);
-      if (++sq == p.n_seq) sq = 0;
-    }
+      for (int i = 0; i < 32; ++i) {
+        sc[i] = (t0 + i < t_end) ? __ldg(p.rope + (int64_t)sq * half + d0) : make_float2(0.f, 1.f);
+        if (++sq == p.n_seq) sq = 0;
+      }
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      const int t = t0 + i;
-      if (t < p.T) {
+      for (int i = 0; i < 32; ++i) {
         const float sn = sc[i].x, cs = sc[i].y;
         const float o = hi ? (w[i] * sn + v[i] * cs) : (v[i] * cs + (w[i] * sn) * -1.0f);
-        const __nv_bfloat16 ob = __float2bfloat16_rn(o);
-        if (hs < p.Hl) {
-          p.q[(int64_t)t * p.ldq + hs * D + d] = ob;
-        } else {
-          p.kbuf[(int64_t)t * p.ldkv + (hs - p.Hl) * D + d] = ob;
-        }
+        st[i * kPitch + col] = __float2bfloat16_rn(o);
       }
+    }
+    __syncwarp();
+    if (live && tL < t_end) {
+      __nv_bfloat16* base = hs < p.Hl ? p.q + (int64_t)tL * p.ldq + hs * D : p.kbuf + (int64_t)tL * p.ldkv + (hs - p.Hl) * D;
+      const uint4* src = reinterpret_cast<const uint4*>(st + lane * kPitch);
+      uint4* lo = reinterpret_cast<uint4*>(base + 8 * jj0);
+      uint4* up = reinterpret_cast<uint4*>(base + half + 8 * jj0);
+      lo[0] = src[0]; lo[1] = src[1];
+      up[0] = src[2]; up[1] = src[3];
     }
   } else {
-    const int kvh = hs - p.Hl - p.KVl, d = 16 * jj + rr;
+    const int kvh = hs - p.Hl - p.KVl;
+    const int col = rbl * 16 + rr;                     // d = 16 * jj0 + col
+    if (live) {
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      const int t = t0 + i;
-      if (t < p.T) {
-        p.vbuf[(int64_t)t * p.ldkv + kvh * D + d] = __float2bfloat16_rn(v[i]);
-      }
+      for (int i = 0; i < 32; ++i) st[i * kPitch + col] = __float2bfloat16_rn(v[i]);
+    }
+    __syncwarp();
+    if (live && tL < t_end) {
+      uint4* dst = reinterpret_cast<uint4*>(p.vbuf + (int64_t)tL * p.ldkv + kvh * D + 16 * jj0);
+      const uint4* src = reinterpret_cast<const uint4*>(st + lane * kPitch);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) dst[c] = src[c];
     }
   }
+  __syncwarp();
 }
 
 // Tile order: groups of `gt` token tiles (their activations, about 64 MB, stay in L2); inside a
@@ -217,7 +257,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const GemmPara
   const int NS = (p.K + 63) >> 6;                         // pipeline steps of 64 k per tile
   // Persistent CTAs walk the tiles with the token tile as the fast index: the CTAs running at one
   // time share a few weight row groups (L2 hits) and the activations fit L2 as a whole.
-  const int n_tt = (p.T + kGemmBN - 1) / kGemmBN, n_rg = (p.rows + 127) >> 7;
+  const bool conv = p.conv_taps > 0;
+  const int tpb = conv ? (p.conv_Lout + kGemmBN - 1) / kGemmBN : 0;      // convolution: token tiles per batch element
+  const int n_tt = conv ? p.conv_B * tpb : (p.T + kGemmBN - 1) / kGemmBN, n_rg = (p.rows + 127) >> 7;
   const int n_tiles = n_tt * n_rg;
   TileOrder order;
   order.n_tt = n_tt; order.n_rg = n_rg;
@@ -246,7 +288,21 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const GemmPara
       for (int st = 0; st < NS; ++st, ++g) {
         const int s = g % kGemmStages;
         mbar_wait(&empty[s], ((g / kGemmStages) & 1) ^ 1, dead, err);
-        if (lane == 0) {
+        if (lane == 0 && conv) {
+          // tap k of output rows [o0, o0 + BN): input rows o * P + k - pad = (o + shift) * P + par, i.e. the box
+          // {64 channels, parity par, BN row pairs from o0 + shift, batch b} of the [B][rows / P][P][C] view
+          const int b = tt_ / tpb, o0 = (tt_ - b * tpb) * kGemmBN;
+          const int spt = p.conv_cpad >> 6, tap = st / spt, c0 = (st - tap * spt) << 6;
+          const int j = tap - p.conv_pad;
+          const int shift = j >= 0 ? j / p.conv_P : -((-j + p.conv_P - 1) / p.conv_P), par = j - shift * p.conv_P;
+          mbar_expect_tx(&full[s], (uint32_t)kStage);
+          bulk_g2s(smem + s * kStage, p.W + ((int64_t)rg * KS + (st >> 1)) * 16384 + (st & 1) * 8192, (uint32_t)kABytes, &full[s]);
+          asm volatile(
+              "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];\n" ::"r"(
+                  smem_u32(smem + s * kStage + kABytes)),
+              "l"(reinterpret_cast<uint64_t>(&xmap)), "r"(c0), "r"(par), "r"(o0 + shift), "r"(b), "r"(smem_u32(&full[s]))
+              : "memory");
+        } else if (lane == 0) {
           mbar_expect_tx(&full[s], (uint32_t)kStage);
           bulk_g2s(smem + s * kStage, p.W + ((int64_t)rg * KS + (st >> 1)) * 16384 + (st & 1) * 8192, (uint32_t)kABytes, &full[s]);
           asm volatile(
@@ -291,7 +347,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const GemmPara
       const int buf = n & 1;
       int rg_, tt_;
       order.decode(tile, &rg_, &tt_);
-      const int t0 = tt_ * kGemmBN, row = rg_ * 128 + 32 * warp + lane;
+      int t0 = tt_ * kGemmBN, t_end = p.T;
+      if (conv) {
+        const int b = tt_ / tpb, o0 = (tt_ - b * tpb) * kGemmBN;
+        t0 = b * p.conv_out_rpb + o0;
+        t_end = b * p.conv_out_rpb + p.conv_Lout;
+      }
+      const int row = rg_ * 128 + 32 * warp + lane;
       mbar_wait(&acc_full[buf], (n >> 1) & 1, dead, err);
       fence_after();
 #pragma unroll 1
@@ -303,7 +365,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const GemmPara
           __syncwarp();
           if (lane == 0) mbar_arrive(&acc_empty[buf]);
         }
-        gemm_epilogue(p, v, row, t0 + ch * 32);
+        gemm_epilogue(p, v, row, t0 + ch * 32, t_end, smem + kGemmStages * kStage + warp * kEpiStageBytes);
       }
     }
   }
@@ -315,8 +377,173 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const GemmPara
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// The same product with two CTAs (a cluster of 2 on one TPC) on one 256-row x 256-token tile: tcgen05.mma
+// cta_group::2, M = 256.  CTA r of the pair stages ITS row group's weights and ITS half of the tokens (a plain TMA
+// box of 128 tokens, no multicast); the tensor core of each SM reads both halves of the token tile, so every byte
+// staged in shared memory is used for twice the flops: 32 KB per CTA per 64-k step instead of 48 KB, which is what
+// the single-CTA kernel is bound by (L2 -> shared memory).  One thread of CTA 0 issues the MMAs for both; its
+// commits arrive on the barriers of both CTAs; CTA 1 forwards "my stage has landed" and "my accumulator is drained"
+// to CTA 0's barriers with remote arrives.
+// ---------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_barrier() {
+  asm volatile("barrier.cluster.arrive.release;\n" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire;\n" ::: "memory");
+}
+__device__ __forceinline__ void mma_f16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrives on the barrier at this shared-memory offset in both CTAs of the pair once the MMAs issued so far are done
+__device__ __forceinline__ void commit_pair(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n" ::"r"(
+                   tc::smem_u32(bar)),
+               "h"((uint16_t)3)
+               : "memory");
+}
+
+constexpr int kPairStages = 6;
+constexpr int kPairStage = 32768;       // 128 rows x 64 k of weights + 128 tokens x 64 k of activations
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+    gemm_tc2_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap, int* err) {
+  using namespace tc;
+  constexpr int kBN = 256, kABytes = 16384;
+  extern __shared__ __align__(1024) unsigned char smem[];
+  __shared__ __align__(8) uint64_t full[kPairStages], empty[kPairStages], peer_full[kPairStages], acc_full[2], acc_empty[2];
+  __shared__ uint32_t tmem_slot;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint32_t rank = cluster_rank();
+  const int KS = (p.K + 127) >> 7, NS = (p.K + 63) >> 6;
+  const int n_tt = (p.T + kBN - 1) / kBN, n_rgp = (p.rows + 255) >> 8;
+  const int n_tiles = n_tt * n_rgp;
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  TileOrder order;
+  order.n_tt = n_tt; order.n_rg = n_rgp;
+  order.gt = max(8, min(n_tt, (64 << 20) / (kBN * p.K * 2)));
+  if (tid == 0) {
+    for (int s = 0; s < kPairStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); mbar_init(&peer_full[s], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 8); }
+    mbar_init_fence();
+  }
+  if (warp == 4) tmem_alloc(&tmem_slot, 512);          // all columns in both CTAs: the same base address in both
+  fence_before();
+  __syncthreads();
+  cluster_barrier();                                     // both CTAs' barriers exist before anything arrives on them
+  fence_after();
+  const uint32_t tmem = tmem_slot;
+  bool dead = false;
+
+  if (warp == 5) {
+    int g = 0;
+    for (int tile = pair; tile < n_tiles; tile += n_pairs) {
+      int rgp, tt_;
+      order.decode(tile, &rgp, &tt_);
+      const int rg = 2 * rgp + (int)rank;
+      for (int st = 0; st < NS; ++st, ++g) {
+        const int s = g % kPairStages;
+        mbar_wait(&empty[s], ((g / kPairStages) & 1) ^ 1, dead, err);
+        if (lane == 0) {
+          mbar_expect_tx(&full[s], (uint32_t)kPairStage);
+          bulk_g2s(smem + s * kPairStage, p.W + ((int64_t)rg * KS + (st >> 1)) * 16384 + (st & 1) * 8192, (uint32_t)kABytes, &full[s]);
+          asm volatile(
+              "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(
+                  smem_u32(smem + s * kPairStage + kABytes)),
+              "l"(reinterpret_cast<uint64_t>(&xmap)), "r"(st * 64), "r"(tt_ * kBN + (int)rank * 128), "r"(smem_u32(&full[s]))
+              : "memory");
+        }
+        __syncwarp();
+      }
+    }
+  } else if (warp == 4 && rank == 1) {
+    // CTA 1: tell CTA 0 when this CTA's half of a stage has landed
+    int g = 0;
+    for (int tile = pair; tile < n_tiles; tile += n_pairs) {
+      for (int st = 0; st < NS; ++st, ++g) {
+        const int s = g % kPairStages;
+        mbar_wait(&full[s], (g / kPairStages) & 1, dead, err);
+        if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&peer_full[s]), 0));
+        __syncwarp();
+      }
+    }
+  } else if (warp == 4) {
+    constexpr uint32_t kIdesc = idesc_bf16(256, kBN, false, false);
+    int g = 0, n = 0;
+    for (int tile = pair; tile < n_tiles; tile += n_pairs, ++n) {
+      const int buf = n & 1;
+      mbar_wait(&acc_empty[buf], ((n >> 1) & 1) ^ 1, dead, err);        // both CTAs' epilogues have drained this accumulator
+      fence_after();
+      for (int st = 0; st < NS; ++st, ++g) {
+        const int s = g % kPairStages;
+        mbar_wait(&full[s], (g / kPairStages) & 1, dead, err);
+        mbar_wait(&peer_full[s], (g / kPairStages) & 1, dead, err);
+        fence_after();
+        if (lane == 0) {
+          const uint32_t sa = smem_u32(smem + s * kPairStage);
+          const uint64_t adesc = smem_desc(sa, 2048, 128);
+          const uint64_t bdesc = smem_desc_sw128(sa + kABytes);
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            mma_f16_pair(tmem + buf * kBN, adesc + (uint64_t)(j * (4096 >> 4)), bdesc + (uint64_t)(j * (32 >> 4)), kIdesc,
+                         (st == 0 && j == 0) ? 0u : 1u);
+          commit_pair(&empty[s]);
+          if (st == NS - 1) commit_pair(&acc_full[buf]);
+        }
+        __syncwarp();
+      }
+    }
+  } else {
+    const uint32_t lane_base = (uint32_t)(32 * warp) << 16;
+    const uint32_t acc_empty_remote[2] = {map_to_cta(smem_u32(&acc_empty[0]), 0), map_to_cta(smem_u32(&acc_empty[1]), 0)};
+    int n = 0;
+    for (int tile = pair; tile < n_tiles; tile += n_pairs, ++n) {
+      const int buf = n & 1;
+      int rgp, tt_;
+      order.decode(tile, &rgp, &tt_);
+      const int t0 = tt_ * kBN, row = (2 * rgp + (int)rank) * 128 + 32 * warp + lane;
+      mbar_wait(&acc_full[buf], (n >> 1) & 1, dead, err);
+      fence_after();
+#pragma unroll 1
+      for (int ch = 0; ch < kBN / 32; ++ch) {
+        float v[32];
+        tmem_ld32(v, tmem + lane_base + buf * kBN + ch * 32);
+        if (ch == kBN / 32 - 1) {
+          fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(acc_empty_remote[buf]);
+        }
+        gemm_epilogue(p, v, row, t0 + ch * 32, p.T, smem + kPairStages * kPairStage + warp * kEpiStageBytes);
+      }
+    }
+  }
+  fence_before();
+  __syncthreads();
+  cluster_barrier();            // no CTA leaves while its partner may still arrive on its barriers or read its shared memory
+  if (warp == 4) {
+    fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+constexpr size_t gemm_pair_smem() { return (size_t)kPairStages * kPairStage + 4 * kEpiStageBytes + 1024; }
+
 template <int BN>
-constexpr size_t gemm_smem() { return (size_t)(BN == 256 ? 4 : 6) * (kUnitBytes / 2 + BN * 128) + 1024; }
+constexpr size_t gemm_smem() { return (size_t)(BN == 256 ? 4 : 6) * (kUnitBytes / 2 + BN * 128) + 4 * kEpiStageBytes + 1024; }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -343,17 +570,68 @@ int32_t gemm_launch(Ctx* ctx, const GemmParams& p, cudaStream_t st) {
   if (!enc) return fail(LMB200_ECUDA, "prefill gemm: cuTensorMapEncodeTiled is not available");
   // 256-token tiles once there are enough tokens to fill them (LMB200_GEMM_BN=128 keeps the narrow tile for A/B runs)
   static const int forced_bn = [] { const char* e = getenv("LMB200_GEMM_BN"); return e ? atoi(e) : 0; }();
-  const int BN = forced_bn == 128 || forced_bn == 256 ? forced_bn : (p.T >= 256 ? 256 : 128);
+  const bool conv = p.conv_taps > 0;
+  const int n_tok = conv ? p.conv_Lout : p.T;
+  const int BN = forced_bn == 128 || forced_bn == 256 ? forced_bn : (n_tok >= 256 ? 256 : 128);
   CUtensorMap xmap;
-  const cuuint64_t dims[2] = {(cuuint64_t)p.K, (cuuint64_t)p.T};
-  const cuuint64_t strides[1] = {(cuuint64_t)p.ldx * 2};               // bytes, dim 1
-  const cuuint32_t box[2] = {64, (cuuint32_t)BN};
-  const cuuint32_t estr[2] = {1, 1};
-  const CUresult r = enc(&xmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<__nv_bfloat16*>(p.X), dims, strides, box, estr,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CUresult r;
+  if (conv) {
+    LMB_REQUIRE(p.conv_P >= 1 && p.conv_rows_in % p.conv_P == 0 && p.conv_cpad % 64 == 0 && p.K == p.conv_taps * p.conv_cpad &&
+                    p.conv_C <= p.conv_cpad && p.conv_C <= p.ldx,
+                "implicit convolution: stride %d, rows %d, channels %d padded to %d, K %d", p.conv_P, p.conv_rows_in, p.conv_C,
+                p.conv_cpad, p.K);
+    // the input seen as [B][rows / P][P][C]: a tap of a strided convolution is one parity of consecutive row groups
+    const cuuint64_t dims[4] = {(cuuint64_t)p.conv_C, (cuuint64_t)p.conv_P, (cuuint64_t)(p.conv_rows_in / p.conv_P), (cuuint64_t)p.conv_B};
+    const cuuint64_t strides[3] = {(cuuint64_t)p.ldx * 2, (cuuint64_t)p.ldx * 2 * p.conv_P, (cuuint64_t)p.ldx * 2 * p.conv_rows_in};
+    const cuuint32_t box[4] = {64, 1, (cuuint32_t)BN, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    r = enc(&xmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<__nv_bfloat16*>(p.X), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  } else {
+    const cuuint64_t dims[2] = {(cuuint64_t)p.K, (cuuint64_t)p.T};
+    const cuuint64_t strides[1] = {(cuuint64_t)p.ldx * 2};               // bytes, dim 1
+    const cuuint32_t box[2] = {64, (cuuint32_t)BN};
+    const cuuint32_t estr[2] = {1, 1};
+    r = enc(&xmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<__nv_bfloat16*>(p.X), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
   if (r != CUDA_SUCCESS) return fail(LMB200_ECUDA, "prefill gemm: cuTensorMapEncodeTiled failed (%d)", (int)r);
-  const int64_t tiles = ceil_div(p.rows, 128) * ceil_div(p.T, BN);
+  // CTA pairs (LMB200_GEMM_PAIR=1) where the tile grid allows them.  Off by default: measured on the Phi-3 prompt the
+  // pair kernel runs at 518 TFLOP/s against the single-CTA kernel's 793 -- a stage of CTA 1 reaches the MMA thread
+  // through two more hops (its own barrier, then a remote arrive), which the six stages do not cover.
+  static const bool pair_on = [] { const char* e = getenv("LMB200_GEMM_PAIR"); return e && atoi(e) != 0; }();
+  if (pair_on && !conv && BN == 256 && p.rows % 256 == 0) {
+    CUtensorMap hmap;                                       // each CTA's half of a token tile: a box of 128 tokens
+    const cuuint64_t dims[2] = {(cuuint64_t)p.K, (cuuint64_t)p.T};
+    const cuuint64_t strides[1] = {(cuuint64_t)p.ldx * 2};
+    const cuuint32_t box[2] = {64, 128};
+    const cuuint32_t estr[2] = {1, 1};
+    r = enc(&hmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<__nv_bfloat16*>(p.X), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(LMB200_ECUDA, "prefill gemm: cuTensorMapEncodeTiled failed (%d)", (int)r);
+    const int64_t pair_tiles = (int64_t)(p.rows / 256) * ceil_div(p.T, 256);
+    // a persistent grid: as many pairs as can be resident at once (SMs whose TPC partner is fused off take none)
+    static int max_pairs = 0;
+    if (!max_pairs) {
+      cudaLaunchConfig_t qc = {};
+      qc.gridDim = dim3((unsigned)(ctx->sm_count / 2 * 2));
+      qc.blockDim = dim3(kGemmThreads);
+      qc.dynamicSmemBytes = gemm_pair_smem();
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, gemm_tc2_kernel, &qc) != cudaSuccess || n < 1) { cudaGetLastError(); n = ctx->sm_count / 2; }
+      max_pairs = n;
+      if (getenv("LMB200_DEBUG_GEMM")) fprintf(stderr, "gemm_tc2_kernel: %d pairs resident on %d SMs\n", n, ctx->sm_count);
+    }
+    const unsigned pairs = (unsigned)std::min<int64_t>(pair_tiles, max_pairs);
+    gemm_tc2_kernel<<<2 * pairs, kGemmThreads, gemm_pair_smem(), st>>>(p, hmap, ctx->dev_err);
+    ctx->launches++;
+    LMB_CUDA(cudaGetLastError());
+    return LMB200_OK;
+  }
+  const int64_t tiles = ceil_div(p.rows, 128) * (conv ? (int64_t)p.conv_B * ceil_div(p.conv_Lout, BN) : ceil_div(p.T, BN));
   const unsigned grid = (unsigned)std::min<int64_t>(tiles, ctx->sm_count);
   if (BN == 256) gemm_tc_kernel<256><<<grid, kGemmThreads, gemm_smem<256>(), st>>>(p, xmap, ctx->dev_err);
   else gemm_tc_kernel<128><<<grid, kGemmThreads, gemm_smem<128>(), st>>>(p, xmap, ctx->dev_err);
@@ -488,6 +766,20 @@ int32_t gemm_affine(Ctx* ctx, const void* W, const __nv_bfloat16* X, int ldx, in
   return gemm_launch(ctx, p, st);
 }
 
+// y[b, o, row] = act(sum_{tap, c} W[row, tap * cpad + c] * x[b, o * stride + tap - pad, c] + bias[row]) stored as bf16 at
+// out[(b * out_rpb + o) * ldo + row]: NN.Conv1D (src/NN.jl:55-104) as a GEMM whose activation tiles come straight from the
+// token-major input through a 4-D tensor map, one tap of 64 channels per pipeline step; nothing is unfolded in memory.
+int32_t gemm_conv1d(Ctx* ctx, const void* W, const __nv_bfloat16* X, int ldx, int batch, int rows_in, int C, int cpad, int taps,
+                    int stride, int pad, int Lout, int out_rpb, int rows, const float* bias, int gelu, void* out, int ldo,
+                    int out_bf16, cudaStream_t st) {
+  GemmParams p;
+  p.W = reinterpret_cast<const __nv_bfloat16*>(W); p.X = X; p.ldx = ldx; p.T = batch * out_rpb; p.rows = rows; p.K = taps * cpad;
+  p.epi = GEMM_AFFINE; p.bias = bias; p.out_scale = 1.0f; p.gelu = gelu; p.out_bf16 = out_bf16; p.out_any = out; p.ldo = ldo;
+  p.conv_taps = taps; p.conv_P = stride; p.conv_pad = pad; p.conv_C = C; p.conv_cpad = cpad; p.conv_B = batch;
+  p.conv_rows_in = rows_in; p.conv_Lout = Lout; p.conv_out_rpb = out_rpb;
+  return gemm_launch(ctx, p, st);
+}
+
 // the same product written as bf16 into a tiled cache layer (rows = heads * D in head-major order)
 int32_t gemm_cross_kv(Ctx* ctx, const void* W, const __nv_bfloat16* X, int ldx, int T, int rows, int K, const float* bias, float scale,
                       void* kv_layer, int64_t batch_stride, int64_t head_stride, int n_seq, int D, int is_v, cudaStream_t st) {
@@ -502,6 +794,7 @@ int32_t gemm_cross_kv(Ctx* ctx, const void* W, const __nv_bfloat16* X, int ldx, 
 int32_t prefill_configure() {
   LMB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemm_smem<128>()));
   LMB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemm_smem<256>()));
+  LMB_CUDA(cudaFuncSetAttribute(gemm_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemm_pair_smem()));
   return LMB200_OK;
 }
 

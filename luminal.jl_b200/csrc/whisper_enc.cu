@@ -4,8 +4,9 @@
 // reshape + matmul (src/NN.jl:55-104), attention with a materialised [B, H, S, S] score tensor
 // (src/Whisper.jl:238-276), LayerNorm, Linear, GELU (src/Whisper.jl:322-404) -- and projects the
 // encoder output to every decoder layer's cross K/V (src/Whisper.jl:809-831).  Here each Conv1D is
-// an im2col gather (the merged index c + C*k of the reference's column-major reshape) followed by
-// the prompt GEMM with a bias + GELU epilogue, the Linears are the same GEMM with bias / scale /
+// an implicit GEMM (the prompt GEMM whose activation tiles are, per pipeline step, 64 channels of one tap read
+// from the token-major input through a 4-D tensor map; the weight columns keep the reference's merged index c + C*k,
+// regrouped tap by tap) with a bias + GELU epilogue, the Linears are the same GEMM with bias / scale /
 // GELU epilogues, attention is the tensor-core flash kernel (non-causal), and the cross K/V GEMMs
 // write straight into the decode session's tiled cross cache.
 //
@@ -25,6 +26,9 @@ namespace lmb {
 
 int32_t gemm_affine(Ctx* ctx, const void* W, const __nv_bfloat16* X, int ldx, int T, int rows, int K, const float* bias, float scale,
                     int gelu, void* out, int ldo, int out_bf16, cudaStream_t st);
+int32_t gemm_conv1d(Ctx* ctx, const void* W, const __nv_bfloat16* X, int ldx, int batch, int rows_in, int C, int cpad, int taps,
+                    int stride, int pad, int Lout, int out_rpb, int rows, const float* bias, int gelu, void* out, int ldo,
+                    int out_bf16, cudaStream_t st);
 int32_t gemm_cross_kv(Ctx* ctx, const void* W, const __nv_bfloat16* X, int ldx, int T, int rows, int K, const float* bias, float scale,
                       void* kv_layer, int64_t batch_stride, int64_t head_stride, int n_seq, int D, int is_v, cudaStream_t st);
 int32_t flash_tc_launch_view(Ctx* ctx, void* out, const void* q, const void* k, const void* v, const FlashView& fv, int64_t B,
@@ -78,7 +82,7 @@ struct WhisperEncoder {
   Bufs scratch;
   int scratch_B = 0, scratch_frames = 0;
   float *mel = nullptr, *x = nullptr, *delta = nullptr;
-  __nv_bfloat16 *col1 = nullptr, *h1 = nullptr, *col2 = nullptr, *xn = nullptr, *qb = nullptr, *kb = nullptr, *vb = nullptr, *attn = nullptr,
+  __nv_bfloat16 *melt = nullptr, *h1 = nullptr, *xn = nullptr, *qb = nullptr, *kb = nullptr, *vb = nullptr, *attn = nullptr,
                 *act = nullptr;
 };
 
@@ -88,41 +92,37 @@ WhisperEncoder* enc_from(uint64_t h) {
   return e;
 }
 
-enum Perm { PERM_NONE = 0, PERM_ROWS = 1, PERM_COLS = 2 };
+enum Perm { PERM_NONE = 0, PERM_ROWS = 1, PERM_COLS = 2, PERM_CONV = 3 };
 
 // dst (tensor-core layout, zero padded) <- src [rows, cols] float32 (row- or column-major), with the
 // head permutation f = h + H*dd -> h*D + dd applied to the rows or to the columns
-__global__ void canon_fill_kernel(__nv_bfloat16* dst, const float* src, int rows, int cols, int colmajor, int perm, int H, int D,
-                                  int rows_pad, int KS) {
+__global__ void canon_fill_kernel(__nv_bfloat16* dst, const float* src, int rows, int cols, int cols_dst, int colmajor, int perm,
+                                  int H, int D, int rows_pad, int KS) {
   const int64_t total = (int64_t)rows_pad * KS * 128;
   for (int64_t o = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; o < total; o += (int64_t)gridDim.x * blockDim.x) {
     const int r = (int)(o / (KS * 128)), k = (int)(o - (int64_t)r * (KS * 128));
     float v = 0.f;
-    if (r < rows && k < cols) {
+    if (r < rows && k < cols_dst) {
       int sr = r, sk = k;
       if (perm == PERM_ROWS) sr = (r / D) + H * (r % D);
       if (perm == PERM_COLS) sk = (k / D) + H * (k % D);
-      v = colmajor ? src[(int64_t)sk * rows + sr] : src[(int64_t)sr * cols + sk];
+      // convolution weights: destination column tap * cpad + c <- the reference's merged column c + C * tap (H = C, D = cpad)
+      if (perm == PERM_CONV) sk = (k % D) < H ? (k % D) + H * (k / D) : -1;
+      if (sk >= 0) v = colmajor ? src[(int64_t)sk * rows + sr] : src[(int64_t)sr * cols + sk];
     }
     dst[wcanon_offset(r, k, KS)] = __float2bfloat16_rn(v);
   }
 }
 
-// rows of the im2col matrix of a 1-D convolution with kernel 3: out[(b * Lo + o), c + C*k] =
-// x(b, c, o * stride + k - pad), x addressed through strides (channel-major mel or token-major activations)
-template <typename TI>
-__global__ void im2col3_kernel(__nv_bfloat16* __restrict__ out, const TI* __restrict__ x, int B, int C, int Lin, int Lo, int stride,
-                               int pad, int64_t sb, int64_t sc, int64_t sl) {
-  const int64_t total = (int64_t)B * Lo * C * 3;
+// mel [B, C, L] float32 -> token-major bf16 [B, L, pitch] (channels contiguous, pitch >= C): the layout whose rows the
+// implicit convolution's tensor map reads
+__global__ void mel_tokens_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ mel, int B, int C, int L, int pitch) {
+  const int64_t total = (int64_t)B * L * pitch;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    const int j = (int)(i % (C * 3));
-    const int64_t row = i / (C * 3);
-    const int o = (int)(row % Lo), b = (int)(row / Lo);
-    const int k = j / C, c = j - k * C;
-    const int l = o * stride + k - pad;
-    float v = 0.f;
-    if (l >= 0 && l < Lin) v = to_f32(x[b * sb + c * sc + l * sl]);
-    out[i] = __float2bfloat16_rn(v);
+    const int c = (int)(i % pitch);
+    const int64_t row = i / pitch;
+    const int l = (int)(row % L), b = (int)(row / L);
+    out[i] = __float2bfloat16_rn(c < C ? mel[((int64_t)b * C + c) * L + l] : 0.f);
   }
 }
 
@@ -186,7 +186,11 @@ int32_t dev_alloc(void** p, int64_t bytes) {
 
 int32_t upload_matrix(WhisperEncoder* E, EncLinear& lin, const float* host, int rows, int cols, int layout, int perm) {
   Ctx* ctx = E->ctx;
-  const int KS = (cols + 127) / 128, rows_pad = (rows + 127) / 128 * 128;
+  // a convolution's [out, C * 3] matrix is stored tap by tap with the channels of a tap padded to a multiple of 64: a
+  // pipeline step of the implicit GEMM is then 64 channels of one tap
+  const int conv_C = cols / 3, conv_cpad = (conv_C + 63) / 64 * 64;
+  const int cols_dst = perm == PERM_CONV ? 3 * conv_cpad : cols;
+  const int KS = (cols_dst + 127) / 128, rows_pad = (rows + 127) / 128 * 128;
   float* stage = nullptr;
   LMB_TRY(dev_alloc((void**)&stage, (int64_t)rows * cols * 4));
   int32_t rc = LMB200_OK;
@@ -194,10 +198,12 @@ int32_t upload_matrix(WhisperEncoder* E, EncLinear& lin, const float* host, int 
   if (rc == LMB200_OK && cudaMemcpyAsync(stage, host, (size_t)rows * cols * 4, cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess)
     rc = fail(LMB200_ECUDA, "whisper encoder: upload failed");
   if (rc == LMB200_OK) {
+    const bool cv = perm == PERM_CONV;
     canon_fill_kernel<<<grid_for((int64_t)rows_pad * KS * 128), 256, 0, ctx->stream>>>(
-        reinterpret_cast<__nv_bfloat16*>(lin.W), stage, rows, cols, layout == LMB200_COLMAJOR, perm, E->H, E->d / E->H, rows_pad, KS);
+        reinterpret_cast<__nv_bfloat16*>(lin.W), stage, rows, cols, cols_dst, layout == LMB200_COLMAJOR, perm, cv ? conv_C : E->H,
+        cv ? conv_cpad : E->d / E->H, rows_pad, KS);
     ctx->launches++;
-    lin.rows = rows; lin.K = cols;
+    lin.rows = rows; lin.K = cols_dst;
   }
   cudaStreamSynchronize(ctx->stream);
   cudaFree(stage);
@@ -301,8 +307,8 @@ extern "C" int32_t lmb200_whisper_encoder_set_weight(uint64_t h, const char* nam
   const std::string enc = "model.encoder.", dec = "model.decoder.layers.";
   if (n.rfind(enc, 0) == 0) {
     const std::string r = n.substr(enc.size());
-    if (r.rfind("conv1.", 0) == 0) return linear(E->conv1, r.substr(6), d, E->n_mels * 3, PERM_NONE);
-    if (r.rfind("conv2.", 0) == 0) return linear(E->conv2, r.substr(6), d, d * 3, PERM_NONE);
+    if (r.rfind("conv1.", 0) == 0) return linear(E->conv1, r.substr(6), d, E->n_mels * 3, PERM_CONV);
+    if (r.rfind("conv2.", 0) == 0) return linear(E->conv2, r.substr(6), d, d * 3, PERM_CONV);
     if (r == "layer_norm.weight") return vec(&E->post_w, d);
     if (r == "layer_norm.bias") return vec(&E->post_b, d);
     if (r.rfind("layers.", 0) == 0) {
@@ -354,15 +360,18 @@ extern "C" int32_t lmb200_whisper_encoder_run(uint64_t h, const float* mel_host,
                 "whisper_encoder_run: layer weights missing");
   const int L1 = frames;                         // conv1: kernel 3, stride 1, padding 1
   const int S = (frames + 2 - 3) / 2 + 1;        // conv2: kernel 3, stride 2, padding 1
+  const int L1p = (L1 + 1) / 2 * 2;              // rows per batch element of conv1's output: even, so that a tap of the
+                                                 // stride-2 convolution is one parity of consecutive row pairs
+  const int C1p = (C1 + 7) / 8 * 8;              // channel pitch of the token-major mel (rows start on 16 bytes)
   const int64_t T1 = (int64_t)batch * L1, T = (int64_t)batch * S;
   if (E->scratch_B != batch || E->scratch_frames != frames) {
     E->scratch.release();
     E->scratch_B = E->scratch_frames = 0;
     Bufs& sc = E->scratch;
     LMB_TRY(sc.get(&E->mel, (int64_t)batch * C1 * frames));
-    LMB_TRY(sc.get(&E->col1, T1 * C1 * 3));
-    LMB_TRY(sc.get(&E->h1, T1 * d));
-    LMB_TRY(sc.get(&E->col2, T * d * 3));
+    LMB_TRY(sc.get(&E->melt, T1 * C1p));
+    LMB_TRY(sc.get(&E->h1, (int64_t)batch * L1p * d));
+    LMB_CUDA(cudaMemsetAsync(E->h1, 0, (size_t)batch * L1p * d * 2, st));      // the pad row of an odd length stays zero
     LMB_TRY(sc.get(&E->x, T * d));
     LMB_TRY(sc.get(&E->delta, T * d));
     LMB_TRY(sc.get(&E->xn, T * d));
@@ -374,7 +383,7 @@ extern "C" int32_t lmb200_whisper_encoder_run(uint64_t h, const float* mel_host,
     E->scratch_B = batch; E->scratch_frames = frames;
   }
   float *mel = E->mel, *x = E->x, *delta = E->delta;
-  __nv_bfloat16 *col1 = E->col1, *h1 = E->h1, *col2 = E->col2, *xn = E->xn, *qb = E->qb, *kb = E->kb, *vb = E->vb, *attn = E->attn,
+  __nv_bfloat16 *melt = E->melt, *h1 = E->h1, *xn = E->xn, *qb = E->qb, *kb = E->kb, *vb = E->vb, *attn = E->attn,
                 *act = E->act;
   if (E->out_B * E->out_S != T) {
     cudaFree(E->enc_b); cudaFree(E->enc_f);
@@ -384,13 +393,12 @@ extern "C" int32_t lmb200_whisper_encoder_run(uint64_t h, const float* mel_host,
   }
   E->out_B = batch; E->out_S = S;
   LMB_CUDA(cudaMemcpyAsync(mel, mel_host, (size_t)batch * C1 * frames * 4, cudaMemcpyHostToDevice, st));
-  // stem: conv1 + GELU, conv2 + GELU, positions
-  im2col3_kernel<float><<<grid_for(T1 * C1 * 3), 256, 0, st>>>(col1, mel, batch, C1, frames, L1, 1, 1, (int64_t)C1 * frames, frames, 1);
+  // stem: conv1 + GELU, conv2 + GELU (implicit GEMMs: the activation tiles of every tap come straight from the
+  // token-major input, nothing is unfolded), positions
+  mel_tokens_kernel<<<grid_for(T1 * C1p), 256, 0, st>>>(melt, mel, batch, C1, frames, C1p);
   ctx->launches++;
-  LMB_TRY(gemm_affine(ctx, E->conv1.W, col1, C1 * 3, (int)T1, d, C1 * 3, E->conv1.bias, 1.0f, 1, h1, d, 1, st));
-  im2col3_kernel<__nv_bfloat16><<<grid_for(T * d * 3), 256, 0, st>>>(col2, h1, batch, d, L1, S, 2, 1, (int64_t)L1 * d, 1, d);
-  ctx->launches++;
-  LMB_TRY(gemm_affine(ctx, E->conv2.W, col2, d * 3, (int)T, d, d * 3, E->conv2.bias, 1.0f, 1, x, d, 0, st));
+  LMB_TRY(gemm_conv1d(ctx, E->conv1.W, melt, C1p, batch, L1, C1, E->conv1.K / 3, 3, 1, 1, L1, L1p, d, E->conv1.bias, 1, h1, d, 1, st));
+  LMB_TRY(gemm_conv1d(ctx, E->conv2.W, h1, d, batch, L1p, d, E->conv2.K / 3, 3, 2, 1, S, S, d, E->conv2.bias, 1, x, d, 0, st));
   add_sinusoids_kernel<<<grid_for(T * d), 256, 0, st>>>(x, E->inv_ts, S, d, T * d);
   ctx->launches++;
   const float scale = powf((float)d / (float)H, -0.25f);          // on q and k (src/Whisper.jl:257-260)

@@ -79,7 +79,8 @@ def test_gemm_prefill_phi3_width(lib_built, device):
     sess.close(); model.close()
 
 
-@pytest.mark.parametrize("rows,K,tokens", [(128, 128, 128), (100, 72, 37), (384, 1024, 300), (1000, 2816, 129), (4608, 3072, 512)])
+@pytest.mark.parametrize("rows,K,tokens", [(128, 128, 128), (100, 72, 37), (384, 1024, 300), (1000, 2816, 129), (4608, 3072, 512),
+                                            (256, 256, 256), (512, 4096, 1000), (768, 64, 257)])
 def test_prefill_gemm_matches_float64(lib_built, device, rows, K, tokens):
     L = lib_built
     rng = np.random.default_rng(rows + tokens)
@@ -89,3 +90,29 @@ def test_prefill_gemm_matches_float64(lib_built, device, rows, K, tokens):
     ref = x.astype(np.float64) @ w.astype(np.float64).T
     assert got.shape == ref.shape
     assert np.abs(got - ref).max() <= 2e-5 * max(1.0, np.abs(ref).max()) * np.sqrt(K / 32.0)
+
+
+def test_prefill_gemm_cta_pair_kernel(lib_built, device):
+    """The two-CTA form of the prompt GEMM (tcgen05.mma cta_group::2, one 256-row x 256-token tile per pair) is an
+    option (LMB200_GEMM_PAIR=1, read once per process): run it in a child process against float64."""
+    import subprocess
+    import sys
+    code = r'''
+import numpy as np, sys
+sys.path.insert(0, "."); sys.path.insert(0, "oracle")
+import luminal_jl_b200 as L
+import luminal_oracle as O
+dev = L.get_device()
+for rows, K, tokens in [(256, 256, 256), (512, 4096, 1000), (4608, 3072, 512)]:
+    rng = np.random.default_rng(rows + tokens)
+    w = O.bf16_round(rng.standard_normal((rows, K), dtype=np.float32) * np.float32(0.05))
+    x = O.bf16_round(rng.standard_normal((tokens, K), dtype=np.float32))
+    got = L.prefill_gemm(dev, w, x)
+    ref = x.astype(np.float64) @ w.astype(np.float64).T
+    assert np.abs(got - ref).max() <= 2e-5 * max(1.0, np.abs(ref).max()) * np.sqrt(K / 32.0), (rows, K, tokens)
+print("pair ok")
+'''
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-c", code], cwd=root, env=dict(os.environ, LMB200_GEMM_PAIR="1"), capture_output=True,
+                       text=True, timeout=300)
+    assert r.returncode == 0 and "pair ok" in r.stdout, r.stdout + r.stderr
