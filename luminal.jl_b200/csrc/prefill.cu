@@ -379,12 +379,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const GemmPara
 
 // ---------------------------------------------------------------------------------------------------------------
 // The same product with two CTAs (a cluster of 2 on one TPC) on one 256-row x 256-token tile: tcgen05.mma
-// cta_group::2, M = 256.  CTA r of the pair stages ITS row group's weights and ITS half of the tokens (a plain TMA
-// box of 128 tokens, no multicast); the tensor core of each SM reads both halves of the token tile, so every byte
-// staged in shared memory is used for twice the flops: 32 KB per CTA per 64-k step instead of 48 KB, which is what
-// the single-CTA kernel is bound by (L2 -> shared memory).  One thread of CTA 0 issues the MMAs for both; its
-// commits arrive on the barriers of both CTAs; CTA 1 forwards "my stage has landed" and "my accumulator is drained"
-// to CTA 0's barriers with remote arrives.
+// cta_group::2, M = 256.  CTA r of the pair stages ITS row group's weights and ITS half of the tokens (plain TMA
+// boxes, no multicast); the tensor core of each SM reads both halves of the token tile, so every byte staged in
+// shared memory is used for twice the flops: 32 KB per CTA per 64-k step instead of 48 KB, and six stages instead of
+// four.  One thread of CTA 0 issues the MMAs for both.  Signals: both CTAs' loads complete on CTA 0's `full`
+// barrier (a cta_group::2 TMA load may count on the partner's barrier); the MMA thread's commits arrive on the
+// `empty` / `acc_full` barriers of both CTAs (multicast commit); CTA 1's epilogue warps hand its accumulator back with
+// a remote arrive on CTA 0's `acc_empty`.  (A first version forwarded CTA 1's "stage landed" through a thread doing
+// remote release-arrives: about a microsecond each, in series -- 518 TFLOP/s instead of 890.)
 // ---------------------------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t cluster_rank() {
   uint32_t r;
@@ -417,15 +419,24 @@ __device__ __forceinline__ void commit_pair(uint64_t* bar) {
                : "memory");
 }
 
+// TMA tile load whose completion is counted on a barrier given by its shared::cluster address: with cta_group::2 that
+// may be the partner CTA's barrier
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar_cluster_addr)
+      : "memory");
+}
+
 constexpr int kPairStages = 6;
 constexpr int kPairStage = 32768;       // 128 rows x 64 k of weights + 128 tokens x 64 k of activations
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
-    gemm_tc2_kernel(const GemmParams p, const __grid_constant__ CUtensorMap xmap, int* err) {
+    gemm_tc2_kernel(const GemmParams p, const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap, int* err) {
   using namespace tc;
   constexpr int kBN = 256, kABytes = 16384;
   extern __shared__ __align__(1024) unsigned char smem[];
-  __shared__ __align__(8) uint64_t full[kPairStages], empty[kPairStages], peer_full[kPairStages], acc_full[2], acc_empty[2];
+  __shared__ __align__(8) uint64_t full[kPairStages], empty[kPairStages], acc_full[2], acc_empty[2];
   __shared__ uint32_t tmem_slot;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const uint32_t rank = cluster_rank();
@@ -437,7 +448,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
   order.n_tt = n_tt; order.n_rg = n_rgp;
   order.gt = max(8, min(n_tt, (64 << 20) / (kBN * p.K * 2)));
   if (tid == 0) {
-    for (int s = 0; s < kPairStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); mbar_init(&peer_full[s], 1); }
+    for (int s = 0; s < kPairStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 8); }
     mbar_init_fence();
   }
@@ -459,28 +470,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         const int s = g % kPairStages;
         mbar_wait(&empty[s], ((g / kPairStages) & 1) ^ 1, dead, err);
         if (lane == 0) {
-          mbar_expect_tx(&full[s], (uint32_t)kPairStage);
-          bulk_g2s(smem + s * kPairStage, p.W + ((int64_t)rg * KS + (st >> 1)) * 16384 + (st & 1) * 8192, (uint32_t)kABytes, &full[s]);
-          asm volatile(
-              "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(
-                  smem_u32(smem + s * kPairStage + kABytes)),
-              "l"(reinterpret_cast<uint64_t>(&xmap)), "r"(st * 64), "r"(tt_ * kBN + (int)rank * 128), "r"(smem_u32(&full[s]))
-              : "memory");
+          // both CTAs' loads complete on CTA 0's barrier (cta_group::2 lets a TMA load signal the partner's
+          // barrier): the MMA thread waits for one barrier per stage and nothing has to be forwarded
+          const uint32_t bar0 = map_to_cta(smem_u32(&full[s]), 0);
+          if (rank == 0) mbar_expect_tx(&full[s], 2u * (uint32_t)kPairStage);
+          tma_load_2d_pair(smem_u32(smem + s * kPairStage), &wmap, 0, (int)((((int64_t)rg * KS + (st >> 1)) * 2 + (st & 1)) * 128), bar0);
+          tma_load_2d_pair(smem_u32(smem + s * kPairStage + kABytes), &xmap, st * 64, tt_ * kBN + (int)rank * 128, bar0);
         }
         __syncwarp();
       }
     }
   } else if (warp == 4 && rank == 1) {
-    // CTA 1: tell CTA 0 when this CTA's half of a stage has landed
-    int g = 0;
-    for (int tile = pair; tile < n_tiles; tile += n_pairs) {
-      for (int st = 0; st < NS; ++st, ++g) {
-        const int s = g % kPairStages;
-        mbar_wait(&full[s], (g / kPairStages) & 1, dead, err);
-        if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&peer_full[s]), 0));
-        __syncwarp();
-      }
-    }
+    // CTA 1 issues no MMAs: CTA 0's thread drives both tensor cores
   } else if (warp == 4) {
     constexpr uint32_t kIdesc = idesc_bf16(256, kBN, false, false);
     int g = 0, n = 0;
@@ -491,7 +492,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
       for (int st = 0; st < NS; ++st, ++g) {
         const int s = g % kPairStages;
         mbar_wait(&full[s], (g / kPairStages) & 1, dead, err);
-        mbar_wait(&peer_full[s], (g / kPairStages) & 1, dead, err);
         fence_after();
         if (lane == 0) {
           const uint32_t sa = smem_u32(smem + s * kPairStage);
@@ -525,7 +525,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         if (ch == kBN / 32 - 1) {
           fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(acc_empty_remote[buf]);
+          if (lane == 0) {
+            if (rank == 0) mbar_arrive(&acc_empty[buf]);
+            else mbar_arrive_cluster(acc_empty_remote[buf]);
+          }
         }
         gemm_epilogue(p, v, row, t0 + ch * 32, p.T, smem + kPairStages * kPairStage + warp * kEpiStageBytes);
       }
@@ -598,10 +601,8 @@ int32_t gemm_launch(Ctx* ctx, const GemmParams& p, cudaStream_t st) {
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   }
   if (r != CUDA_SUCCESS) return fail(LMB200_ECUDA, "prefill gemm: cuTensorMapEncodeTiled failed (%d)", (int)r);
-  // CTA pairs (LMB200_GEMM_PAIR=1) where the tile grid allows them.  Off by default: measured on the Phi-3 prompt the
-  // pair kernel runs at 518 TFLOP/s against the single-CTA kernel's 793 -- a stage of CTA 1 reaches the MMA thread
-  // through two more hops (its own barrier, then a remote arrive), which the six stages do not cover.
-  static const bool pair_on = [] { const char* e = getenv("LMB200_GEMM_PAIR"); return e && atoi(e) != 0; }();
+  // CTA pairs where the tile grid allows them (LMB200_GEMM_PAIR=0 keeps the single-CTA kernel for A/B runs)
+  static const bool pair_on = [] { const char* e = getenv("LMB200_GEMM_PAIR"); return !(e && atoi(e) == 0); }();
   if (pair_on && !conv && BN == 256 && p.rows % 256 == 0) {
     CUtensorMap hmap;                                       // each CTA's half of a token tile: a box of 128 tokens
     const cuuint64_t dims[2] = {(cuuint64_t)p.K, (cuuint64_t)p.T};
@@ -612,6 +613,15 @@ int32_t gemm_launch(Ctx* ctx, const GemmParams& p, cudaStream_t st) {
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(LMB200_ECUDA, "prefill gemm: cuTensorMapEncodeTiled failed (%d)", (int)r);
+    // the weights as rows of 128 bytes: half a canonical unit (128 rows x 64 k) is 128 consecutive rows, copied as it lies
+    CUtensorMap wmap;
+    const int64_t w_rows = (int64_t)(p.rows / 128) * ceil_div(p.K, 128) * 2 * 128;
+    const cuuint64_t wdims[2] = {64, (cuuint64_t)w_rows};
+    const cuuint64_t wstrides[1] = {128};
+    r = enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<__nv_bfloat16*>(p.W), wdims, wstrides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(LMB200_ECUDA, "prefill gemm: cuTensorMapEncodeTiled (weights) failed (%d)", (int)r);
     const int64_t pair_tiles = (int64_t)(p.rows / 256) * ceil_div(p.T, 256);
     // a persistent grid: as many pairs as can be resident at once (SMs whose TPC partner is fused off take none)
     static int max_pairs = 0;
@@ -626,7 +636,7 @@ int32_t gemm_launch(Ctx* ctx, const GemmParams& p, cudaStream_t st) {
       if (getenv("LMB200_DEBUG_GEMM")) fprintf(stderr, "gemm_tc2_kernel: %d pairs resident on %d SMs\n", n, ctx->sm_count);
     }
     const unsigned pairs = (unsigned)std::min<int64_t>(pair_tiles, max_pairs);
-    gemm_tc2_kernel<<<2 * pairs, kGemmThreads, gemm_pair_smem(), st>>>(p, hmap, ctx->dev_err);
+    gemm_tc2_kernel<<<2 * pairs, kGemmThreads, gemm_pair_smem(), st>>>(p, wmap, hmap, ctx->dev_err);
     ctx->launches++;
     LMB_CUDA(cudaGetLastError());
     return LMB200_OK;
