@@ -343,6 +343,7 @@ extern "C" int32_t lmb200_shutdown(lmb200_ctx h) {
   cudaStreamDestroy(c->own_stream);
   cudaFreeHost(c->dev_err);
   cudaFree(c->dev_broken);
+  cudaFree(c->scratch);
   c->magic = 0;
   delete c;
   return LMB200_OK;

@@ -64,6 +64,10 @@ struct Ctx {
   unsigned long long* peer_step = nullptr;   // device counter: decode steps enqueued on this communicator
   float* peer_scratch = nullptr;             // 1 float for the teardown barrier
   long long peer_wait_cycles = 0;            // SM cycles a kernel waits for a peer's signal (LMB200_PEER_WAIT_MS, default 10 s)
+  // Scratch of the stand-alone ops that need some (the float32 flash attention's bf16 halves): grows to the largest
+  // request and stays until shutdown, so that a call neither allocates nor waits for the device
+  void* scratch = nullptr;
+  size_t scratch_bytes = 0;
 };
 
 // Region layout (bytes): two 4 MiB buffers read by the peers (the norm kernels' all-reduce), two 4 MiB

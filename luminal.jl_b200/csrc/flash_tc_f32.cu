@@ -345,16 +345,26 @@ int32_t flash_tc_f32_configure() {
   return LMB200_OK;
 }
 
-// out, q, k, v: float32 [BH, S, D] contiguous on the device.  Scratch: the six bf16 halves (3 x 2 x BH x S x D x 2 bytes).
+// out, q, k, v: float32 [BH, S, D] contiguous on the device.  Scratch: the six bf16 halves (3 x 2 x BH x S x D x 2 bytes),
+// kept in the context between calls.  Asynchronous on the context's stream like the bf16 kernel.
 int32_t flash_tc_f32_launch(Ctx* ctx, float* out, const float* q, const float* k, const float* v, int64_t BH, int64_t S, int64_t D,
                             float scale, int causal) {
   const int64_t n = BH * S * D;
   LMB_REQUIRE(n % 4 == 0, "flash attention: element count must be a multiple of 4");
-  __nv_bfloat16* hl = nullptr;
-  if (cudaMalloc((void**)&hl, (size_t)n * 2 * 3 * sizeof(__nv_bfloat16)) != cudaSuccess) {
-    cudaGetLastError();
-    return fail(LMB200_ENOMEM, "flash attention: scratch allocation of %lld bytes failed", (long long)(n * 12));
+  const size_t need = (size_t)n * 2 * 3 * sizeof(__nv_bfloat16);
+  if (ctx->scratch_bytes < need) {
+    // work queued on the stream may still use the smaller block
+    LMB_CUDA(cudaStreamSynchronize(ctx->stream));
+    cudaFree(ctx->scratch);
+    ctx->scratch = nullptr;
+    ctx->scratch_bytes = 0;
+    if (cudaMalloc(&ctx->scratch, need) != cudaSuccess) {
+      cudaGetLastError();
+      return fail(LMB200_ENOMEM, "flash attention: scratch allocation of %lld bytes failed", (long long)need);
+    }
+    ctx->scratch_bytes = need;
   }
+  __nv_bfloat16* hl = reinterpret_cast<__nv_bfloat16*>(ctx->scratch);
   __nv_bfloat16 *qhl = hl, *khl = hl + 2 * n, *vhl = hl + 4 * n;
   const unsigned grid1 = (unsigned)std::min<int64_t>(ceil_div(n / 4, 256), 148 * 16);
   split_hi_lo_kernel<<<grid1, 256, 0, ctx->stream>>>(q, qhl, n);
@@ -378,9 +388,6 @@ int32_t flash_tc_f32_launch(Ctx* ctx, float* out, const float* q, const float* k
       if (cudaGetLastError() != cudaSuccess) rc = fail(LMB200_ECUDA, "flash attention: launch failed");
     }
   }
-  cudaStreamSynchronize(ctx->stream);        // the scratch is freed below
-  cudaFree(hl);
-  if (rc == LMB200_OK) rc = check_device_error(ctx);
   return rc;
 }
 
