@@ -343,12 +343,336 @@ flash_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------
+// The same operation with key tiles of 128 and P kept in tensor memory.
+//
+// Per 64-key step the kernel above issues 16 MMAs of N = 64 for the two S tiles and 8 for the two P V products,
+// every one reading both operands from shared memory (P makes a round trip through it): 160 KB of operand reads per
+// 128 keys and query tile, more than the tensor core's time for the same work.  Here a step is 128 keys: S = Q K^T is
+// one M 128 x N 128 accumulator per query tile; the softmax threads read it from tensor memory, and write P as bf16
+// back over the same columns (tcgen05.st: a thread's row is its lane); P V takes its A operand from there, so only K
+// and V are read from shared memory (96 KB per 128 keys and tile).  S and P of a tile share their columns, so a tile
+// runs S -> softmax -> P V strictly in turn, and the two query tiles of the CTA alternate on the tensor core: while
+// one is in its softmax, the other's MMAs run.  Tensor memory: S/P 2 x 128 columns, O 2 x D.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int kBN2 = 128, kStages2 = 2;
+constexpr int kMmaWarp2 = 16;                       // warps 0-15 softmax (two per query row), 16 MMA issue, 17-18 loaders
+constexpr int kThreads2 = (kMmaWarp2 + 1) * 32 + kLoaders;
+
+template <int D>
+struct Smem2 {
+  static constexpr int kQ = kBM * D * 2;
+  static constexpr int kKV = kBN2 * D * 2;
+  static constexpr int offQ = 0;                              // two query tiles
+  static constexpr int offK = offQ + 2 * kQ;
+  static constexpr int offV = offK + kStages2 * kKV;
+  static constexpr int total = offV + kStages2 * kKV;
+};
+
+__device__ __forceinline__ void mma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// 16 consecutive 32-bit columns of this thread's lane from registers (no wait: the caller waits once per step)
+__device__ __forceinline__ void tmem_st16_nowait(uint32_t taddr, const uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n" ::"r"(taddr),
+      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]),
+      "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+      : "memory");
+}
+// 16 consecutive float32 columns of this thread's lane
+__device__ __forceinline__ void tmem_ld16(float (&v)[16], uint32_t taddr) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+      "tcgen05.wait::ld.sync.aligned;\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+
+template <int D>
+__global__ void __launch_bounds__(kThreads2, 1)
+flash_tc128_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ q, const __grid_constant__ CUtensorMap kmap,
+                   const __grid_constant__ CUtensorMap vmap, const FlashView fv, int S, float scale, int causal, int* err) {
+  constexpr int W = D % 64 == 0 ? 64 : 32;            // head dims per swizzled sub-tile
+  constexpr int kSub = kBN2 * W * 2;                  // bytes of one sub-tile [128 keys][W]
+  constexpr uint32_t kSwz = W == 64 ? 2u : 4u;
+  using namespace tc;
+  typedef Smem2<D> SM;
+  extern __shared__ __align__(1024) unsigned char smem[];
+  __shared__ __align__(8) uint64_t q_full, k_full[kStages2], k_empty[kStages2], v_full[kStages2], v_empty[kStages2];
+  __shared__ __align__(8) uint64_t s_full[2], p_full[2], o_done[2];
+  __shared__ float xch[2][2][kBM];                    // [tile][column half][row]: the halves' row maxima, later their sums
+  __shared__ uint32_t tmem_slot;
+  constexpr uint32_t kTmemCols = 512;
+  constexpr uint32_t kColS = 0, kColO = 256;          // S / P: [tile] x 128 columns, O: [tile] x D columns
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int qp = (int)gridDim.x - 1 - (int)blockIdx.x;        // heavy (late) causal tiles first
+  const int q0 = qp * 2 * kBM;
+  const int bi = (int)blockIdx.y / fv.H, hi = (int)blockIdx.y - bi * fv.H;
+  const __nv_bfloat16* qb = q + bi * fv.q_b + hi * fv.q_h;
+  const int kvh = hi / fv.G;
+  __nv_bfloat16* ob_base = out + bi * fv.q_b + hi * fv.q_h;
+  const int64_t q_s = fv.q_s;
+  int n_tiles[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int qt0 = q0 + t * kBM;
+    const int k_stop = qt0 >= S ? 0 : (causal ? min(S, qt0 + kBM) : S);
+    n_tiles[t] = (k_stop + kBN2 - 1) / kBN2;
+  }
+  const int n_max = max(n_tiles[0], n_tiles[1]);
+
+  if (tid == 0) {
+    mbar_init(&q_full, kLoaders / 32);
+    for (int s = 0; s < kStages2; ++s) {
+      mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
+    }
+    for (int t = 0; t < 2; ++t) { mbar_init(&s_full[t], 1); mbar_init(&p_full[t], 8); mbar_init(&o_done[t], 1); }
+    mbar_init_fence();
+  }
+  if (warp == kMmaWarp2) tmem_alloc(&tmem_slot, kTmemCols);
+  fence_before();
+  __syncthreads();
+  fence_after();
+  const uint32_t tmem = tmem_slot;
+  bool dead = false;
+
+  if (warp > kMmaWarp2) {
+    // ------------------------------ loaders: Q by both warps, then K by one and V by the other ------------------------------
+    const int lw = warp - kMmaWarp2 - 1, lt = tid - (kMmaWarp2 + 1) * 32;
+    const uint32_t sQ = smem_u32(smem + SM::offQ);
+    for (int i = lt; i < 2 * kBM * (D / 8); i += kLoaders) {
+      const int row = i / (D / 8), c8 = i - row * (D / 8);
+      const int qi = q0 + row;
+      cp_async16(sQ + (row >> 7) * SM::kQ + canon(row & 127, c8, kBM), qb + (int64_t)min(qi, S - 1) * q_s + c8 * 8, qi < S ? 16u : 0u);
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    fence_async_smem();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&q_full);
+    uint64_t* full = lw == 0 ? k_full : v_full;
+    uint64_t* empty = lw == 0 ? k_empty : v_empty;
+    const CUtensorMap* map = lw == 0 ? &kmap : &vmap;
+    const int off = lw == 0 ? SM::offK : SM::offV;
+    for (int j = 0; j < n_max; ++j) {
+      const int s = j % kStages2;
+      mbar_wait(&empty[s], ((j / kStages2) & 1) ^ 1, dead, err);
+      if (lane == 0) {
+        mbar_expect_tx(&full[s], (uint32_t)SM::kKV);
+#pragma unroll
+        for (int sub = 0; sub < D / W; ++sub) tma_load_4d(smem + off + s * SM::kKV + sub * kSub, map, sub * W, j * kBN2, kvh, bi, &full[s]);
+      }
+      __syncwarp();
+    }
+  } else if (warp == kMmaWarp2) {
+    // ------------------------------ MMA issue ------------------------------
+    constexpr uint32_t kIdescS = idesc_bf16(kBM, kBN2, false, false);
+    constexpr uint32_t kIdescPV = idesc_bf16(kBM, D, false, true);          // V is read MN-major
+    mbar_wait(&q_full, 0, dead, err);
+    auto issue_s = [&](int j, int t) {                // S[t] = Q[t] K(j)^T
+      if (lane == 0) {
+        const uint64_t adesc = smem_desc(smem_u32(smem + SM::offQ + t * SM::kQ), kBM * 16, 128);
+        const uint32_t sK = smem_u32(smem + SM::offK + (j % kStages2) * SM::kKV);
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint64_t bdesc = smem_desc_swz(sK + ((16 * ks) / W) * kSub + ((16 * ks) % W) * 2, 16, 16 * W, kSwz);
+          mma_f16(tmem + kColS + t * kBN2, adesc + (uint64_t)(ks * ((2 * kBM * 16) >> 4)), bdesc, kIdescS, ks ? 1u : 0u);
+        }
+        commit(&s_full[t]);
+      }
+      __syncwarp();
+    };
+    auto issue_pv = [&](int j, int t) {               // O[t] += P[t] V(j), P read from tensor memory
+      if (lane == 0) {
+        const uint64_t bdesc = smem_desc_swz(smem_u32(smem + SM::offV + (j % kStages2) * SM::kKV), kSub, 16 * W, kSwz);
+#pragma unroll
+        for (int ks = 0; ks < kBN2 / 16; ++ks)
+          mma_f16_ts(tmem + kColO + t * D, tmem + kColS + t * kBN2 + ks * 8, bdesc + (uint64_t)(ks * ((32 * W) >> 4)), kIdescPV,
+                     (j > 0 || ks > 0) ? 1u : 0u);
+        if (j == n_tiles[t] - 1) commit(&o_done[t]);
+      }
+      __syncwarp();
+    };
+    if (n_max >= 1) {
+      mbar_wait(&k_full[0], 0, dead, err);
+      fence_after();
+#pragma unroll
+      for (int t = 0; t < 2; ++t)
+        if (n_tiles[t] >= 1) issue_s(0, t);
+      if (lane == 0) commit(&k_empty[0]);
+      __syncwarp();
+    }
+    for (int j = 0; j < n_max; ++j) {
+      const int s = j % kStages2, s1 = (j + 1) % kStages2;
+      mbar_wait(&v_full[s], (j / kStages2) & 1, dead, err);
+      if (j + 1 < n_max) mbar_wait(&k_full[s1], ((j + 1) / kStages2) & 1, dead, err);
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        if (j >= n_tiles[t]) continue;
+        mbar_wait(&p_full[t], j & 1, dead, err);
+        fence_after();
+        issue_pv(j, t);
+        if (j + 1 < n_tiles[t]) issue_s(j + 1, t);       // runs after P V(j) in the tensor pipe: S overwrites P's columns
+      }
+      if (lane == 0) {
+        commit(&v_empty[s]);
+        if (j + 1 < n_max) commit(&k_empty[s1]);
+      }
+      __syncwarp();
+    }
+  } else {
+    // ------------------------------ softmax + output ------------------------------
+    // Two threads per query row: warps 0-7 take keys 0-63 of a tile, warps 8-15 keys 64-127 (a warp reaches the 32
+    // tensor-memory lanes of its index modulo 4, so warp w and w + 8 see the same rows).  The two halves exchange
+    // their row maxima through shared memory and a 64-thread barrier, keep their own partial sums, and each writes
+    // its half of P -- after a second barrier, because P's columns lie over the other half's scores.
+    const int h = warp >> 3, t = (warp >> 2) & 1, wq = warp & 3;
+    const int r = 32 * wq + lane;
+    const int qi = q0 + t * kBM + r;
+    const uint32_t lane_base = (uint32_t)(32 * wq) << 16;
+    const uint32_t colS = kColS + t * kBN2 + h * 64, colP = kColS + t * kBN2 + h * 32, colO = kColO + t * D + h * (D / 2);
+    const int pair_bar = 1 + t * 4 + wq;              // named barrier of the two warps that share these rows
+    const float c = scale * kLog2e;
+    const int nt = n_tiles[t];
+    float m = -CUDART_INF_F, l = 0.f;
+    for (int j = 0; j < nt; ++j) {
+      mbar_wait(&s_full[t], j & 1, dead, err);          // S(j) is complete, and with it (pipe order) P V(j - 1): O is at rest
+      fence_after();
+      const int key0 = j * kBN2 + h * 64;
+      const bool inside = (j + 1) * kBN2 <= S && (!causal || (j + 1) * kBN2 - 1 <= q0 + t * kBM);   // no key of the tile is masked
+      // pass 1: the maximum of this thread's 64 scores
+      float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+      for (int qd = 0; qd < 2; ++qd) {
+        float sv[32];
+        tmem_ld32(sv, tmem + lane_base + colS + qd * 32);
+        if (inside) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], sv[i]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int key = key0 + qd * 32 + i;
+            if (!(key >= S || (causal && key > qi))) mx4[i & 3] = fmaxf(mx4[i & 3], sv[i]);
+          }
+        }
+      }
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      xch[t][h][r] = mx;
+      asm volatile("bar.sync %0, 64;\n" ::"r"(pair_bar) : "memory");
+      mx = fmaxf(mx, xch[t][h ^ 1][r]);
+      mx *= c;
+      const bool first = m == -CUDART_INF_F && mx > -CUDART_INF_F;
+      const bool raise = m > -CUDART_INF_F && mx > m + kRescaleStep;
+      if (__any_sync(0xffffffffu, raise) && j > 0) {      // both halves decide alike; each rescales its half of O's columns
+        const float alpha = raise ? exp2f(m - mx) : 1.0f;
+#pragma unroll
+        for (int ch = 0; ch < D / 32; ++ch) {
+          float o[16];
+          tmem_ld16(o, tmem + lane_base + colO + ch * 16);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) o[i] *= alpha;
+          uint32_t ou[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) ou[i] = __float_as_uint(o[i]);
+          tmem_st16_nowait(tmem + lane_base + colO + ch * 16, ou);
+        }
+      }
+      if (raise) { l *= exp2f(m - mx); m = mx; }
+      if (first) m = mx;
+      const float neg_m = m == -CUDART_INF_F ? 0.f : -m;
+      // pass 2: p = exp2(s c - m) as bf16 pairs, kept in registers until the other half has read its scores too
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t packed[32];
+#pragma unroll
+      for (int qd = 0; qd < 4; ++qd) {
+        float sv[16];
+        tmem_ld16(sv, tmem + lane_base + colS + qd * 16);
+#pragma unroll
+        for (int i = 0; i < 16; i += 2) {
+          float a0 = sv[i], a1 = sv[i + 1];
+          if (!inside) {
+            const int key = key0 + qd * 16 + i;
+            if (key >= S || (causal && key > qi)) a0 = -CUDART_INF_F;
+            if (key + 1 >= S || (causal && key + 1 > qi)) a1 = -CUDART_INF_F;
+          }
+          const float p0 = ex2_approx(fmaf(a0, c, neg_m)), p1 = ex2_approx(fmaf(a1, c, neg_m));
+          sum4[(i >> 1) & 3] += p0 + p1;
+          const __nv_bfloat162 pb2 = __floats2bfloat162_rn(p0, p1);
+          packed[qd * 8 + i / 2] = *reinterpret_cast<const uint32_t*>(&pb2);
+        }
+      }
+      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      asm volatile("bar.sync %0, 64;\n" ::"r"(pair_bar) : "memory");
+      {
+        uint32_t lo[16], hi2[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) { lo[i] = packed[i]; hi2[i] = packed[16 + i]; }
+        tmem_st16_nowait(tmem + lane_base + colP, lo);
+        tmem_st16_nowait(tmem + lane_base + colP + 16, hi2);
+      }
+      tmem_st_wait();
+      fence_before();                    // orders the stores (P, a rescaled O) before the MMA that the arrive releases
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[t]);
+    }
+    if (nt >= 1) {
+      xch[t][h][r] = l;
+      asm volatile("bar.sync %0, 64;\n" ::"r"(pair_bar) : "memory");
+      l += xch[t][h ^ 1][r];
+      mbar_wait(&o_done[t], 0, dead, err);            // the last P V has landed
+      fence_after();
+      const float inv = 1.0f / l;
+      __nv_bfloat16* ob = ob_base + (int64_t)qi * q_s + h * (D / 2);
+#pragma unroll
+      for (int ch = 0; ch < D / 32; ++ch) {
+        float o[16];
+        tmem_ld16(o, tmem + lane_base + colO + ch * 16);
+        if (qi < S) {
+#pragma unroll
+          for (int i = 0; i < 16; i += 8) {
+            uint4 w;
+            __nv_bfloat162 a0 = __floats2bfloat162_rn(o[i] * inv, o[i + 1] * inv), a1 = __floats2bfloat162_rn(o[i + 2] * inv, o[i + 3] * inv);
+            __nv_bfloat162 a2 = __floats2bfloat162_rn(o[i + 4] * inv, o[i + 5] * inv), a3 = __floats2bfloat162_rn(o[i + 6] * inv, o[i + 7] * inv);
+            w.x = *reinterpret_cast<uint32_t*>(&a0); w.y = *reinterpret_cast<uint32_t*>(&a1);
+            w.z = *reinterpret_cast<uint32_t*>(&a2); w.w = *reinterpret_cast<uint32_t*>(&a3);
+            *reinterpret_cast<uint4*>(ob + ch * 16 + i) = w;
+          }
+        }
+      }
+      fence_before();
+    }
+  }
+  fence_before();
+  __syncthreads();
+  if (warp == kMmaWarp2) {
+    fence_after();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
 }  // namespace
 
 int32_t flash_tc_configure() {
   LMB_CUDA(cudaFuncSetAttribute(flash_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<128>::total + 1024));
   LMB_CUDA(cudaFuncSetAttribute(flash_tc_kernel<96>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<96>::total + 1024));
   LMB_CUDA(cudaFuncSetAttribute(flash_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<64>::total + 1024));
+  LMB_CUDA(cudaFuncSetAttribute(flash_tc128_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem2<128>::total + 1024));
+  LMB_CUDA(cudaFuncSetAttribute(flash_tc128_kernel<96>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem2<96>::total + 1024));
+  LMB_CUDA(cudaFuncSetAttribute(flash_tc128_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem2<64>::total + 1024));
   return LMB200_OK;
 }
 
@@ -373,7 +697,7 @@ EncodeTiledFn flash_encode_fn() {
 }
 // 4-D map over K or V: dims {d, key, kv head, batch}; a box is [64 keys][W head dims], swizzled over its W * 2 bytes.
 // Keys past S arrive as zeros (the softmax masks them).
-int32_t kv_tensor_map(CUtensorMap* map, const void* base, const FlashView& fv, int64_t B, int64_t S, int64_t D) {
+int32_t kv_tensor_map(CUtensorMap* map, const void* base, const FlashView& fv, int64_t B, int64_t S, int64_t D, int box_keys) {
   EncodeTiledFn enc = flash_encode_fn();
   if (!enc) return fail(LMB200_ECUDA, "flash attention: cuTensorMapEncodeTiled is not available");
   const int W = D % 64 == 0 ? 64 : 32;
@@ -384,7 +708,7 @@ int32_t kv_tensor_map(CUtensorMap* map, const void* base, const FlashView& fv, i
               "flash attention: K / V base and strides must be multiples of 16 bytes");
   const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)S, (cuuint64_t)n_kv, (cuuint64_t)B};
   const cuuint64_t strides[3] = {(cuuint64_t)fv.k_s * 2, (cuuint64_t)head_stride * 2, (cuuint64_t)batch_stride * 2};
-  const cuuint32_t box[4] = {(cuuint32_t)W, (cuuint32_t)kBN, 1, 1};
+  const cuuint32_t box[4] = {(cuuint32_t)W, (cuuint32_t)box_keys, 1, 1};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
   const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, W == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
@@ -398,12 +722,20 @@ int32_t kv_tensor_map(CUtensorMap* map, const void* base, const FlashView& fv, i
 int32_t flash_tc_launch_view(Ctx* ctx, void* out, const void* q, const void* k, const void* v, const FlashView& fv, int64_t B,
                              int64_t S, int64_t D, float scale, int causal, cudaStream_t stream) {
   dim3 grid((unsigned)ceil_div(S, 2 * kBM), (unsigned)(B * fv.H));
+  // key tiles of 128 with P in tensor memory; LMB200_FLASH_KEYS=64 selects the 64-key kernel (A/B runs)
+  static const bool k64 = [] { const char* e = getenv("LMB200_FLASH_KEYS"); return e && atoi(e) == 64; }();
   CUtensorMap kmap, vmap;
-  LMB_TRY(kv_tensor_map(&kmap, k, fv, B, S, D));
-  LMB_TRY(kv_tensor_map(&vmap, v, fv, B, S, D));
+  LMB_TRY(kv_tensor_map(&kmap, k, fv, B, S, D, k64 ? kBN : kBN2));
+  LMB_TRY(kv_tensor_map(&vmap, v, fv, B, S, D, k64 ? kBN : kBN2));
 #define LMB_FLASH(DD)                                                                                                   \
-  flash_tc_kernel<DD><<<grid, kThreads, Smem<DD>::total + 1024, stream>>>(                                             \
-      (__nv_bfloat16*)out, (const __nv_bfloat16*)q, kmap, vmap, fv, (int)S, scale, causal, ctx->dev_err)
+  do {                                                                                                                  \
+    if (k64)                                                                                                            \
+      flash_tc_kernel<DD><<<grid, kThreads, Smem<DD>::total + 1024, stream>>>(                                         \
+          (__nv_bfloat16*)out, (const __nv_bfloat16*)q, kmap, vmap, fv, (int)S, scale, causal, ctx->dev_err);          \
+    else                                                                                                                \
+      flash_tc128_kernel<DD><<<grid, kThreads2, Smem2<DD>::total + 1024, stream>>>(                                     \
+          (__nv_bfloat16*)out, (const __nv_bfloat16*)q, kmap, vmap, fv, (int)S, scale, causal, ctx->dev_err);          \
+  } while (0)
   if (D == 128) LMB_FLASH(128);
   else if (D == 96) LMB_FLASH(96);
   else if (D == 64) LMB_FLASH(64);
