@@ -40,9 +40,9 @@ TRACE_LIB = os.path.join(HERE, "build_trace", "libluminal_b200_trace.so")
 def build_library(force: bool = False, verbose: bool = False, trace: bool = False) -> str:
     """Compile every .cu under csrc/ and link the shared library.  Returns its path.
 
-    trace=True builds a second library, build_trace/libluminal_b200_trace.so, with -DLMB_GEMV_TRACE
-    -DLMB_FLASH_TRACE: the GEMV and flash kernels then stamp the SM clock at their phase boundaries
-    into a device array that lmb200_debug_gemv_trace / lmb200_debug_flash_trace copy out
+    trace=True builds a second library, build_trace/libluminal_b200_trace.so, with -DLMB_GEMV_TRACE:
+    the GEMV kernels then stamp the SM clock at their phase boundaries into a device array that
+    lmb200_debug_gemv_trace copies out
     (luminal.jl_b200/trace.py reads them).  The product library never carries the stamps."""
     lib = TRACE_LIB if trace else LIB
     if not trace and not force and not _stale():
@@ -50,7 +50,7 @@ def build_library(force: bool = False, verbose: bool = False, trace: bool = Fals
     objdir = os.path.join(HERE, "build_trace" if trace else "build")
     os.makedirs(objdir, exist_ok=True)
     nvcc = _nvcc()
-    extra = ["-DLMB_GEMV_TRACE", "-DLMB_FLASH_TRACE"] if trace else []
+    extra = ["-DLMB_GEMV_TRACE"] if trace else []
 
     def compile_one(src):
         obj = os.path.join(objdir, src.replace(".cu", ".o"))

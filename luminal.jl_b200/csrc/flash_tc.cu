@@ -3,22 +3,29 @@
 // series, no tensor cores) for bf16 tensors of head_dim 64, 96 or 128.
 //
 // One CTA = two tiles of 128 query rows of one (batch, head) sharing the key/value stream, keys in
-// tiles of 64:
+// tiles of 128:
 //   2 loader warps : Q by cp.async 16-byte chunks into the canonical core-matrix layout (8 rows x 16
-//                    bytes); K and V by TMA (cp.async.bulk.tensor over a 4-D map d / key / kv head /
-//                    batch, one thread, 3 stages in flight): a key tile lands as D / W sub-tiles of
-//                    [64 keys][W head dims] in the 128-byte (W = 64) or 64-byte (W = 32, head_dim 96)
-//                    swizzle, which the tensor core reads K-major for Q K^T and MN-major for P V;
-//   1 MMA warp     : one thread issues tcgen05.mma for both query tiles -- S = Q K^T (M 128, N 64,
-//                    K = D) into a double-buffered TMEM tile, then O += P V (M 128, N = D, K 64; V
-//                    read MN-major from the same tile layout as K) accumulating in TMEM over all
-//                    key tiles; tcgen05.commit signals mbarriers;
-//   2 x 4 softmax warps, one group per query tile, one query row per thread: tcgen05.ld the S row,
-//                    exp2 with the scale folded in, write P as bf16 straight into the A-operand
-//                    layout.  The running maximum is only raised -- and O in TMEM rescaled -- when
-//                    it grows by more than 2^8 (p stays <= 256, exact in the final O / l), so in the
-//                    steady state a softmax thread never touches O and the two groups keep the
-//                    tensor core busy in turn.
+//                    bytes); then one warp streams K and the other V by TMA (cp.async.bulk.tensor over
+//                    a 4-D map d / key / kv head / batch, 2 stages each): a key tile lands as D / W
+//                    sub-tiles of [128 keys][W head dims] in the 128-byte (W = 64) or 64-byte (W = 32,
+//                    head_dim 96) swizzle, which the tensor core reads K-major for Q K^T and MN-major
+//                    for P V;
+//   1 MMA warp     : one thread issues tcgen05.mma for both query tiles -- S = Q K^T (M 128, N 128,
+//                    K = D) into the tile's 128 columns of tensor memory, and O += P V (M 128, N = D,
+//                    K 128) with P read FROM TENSOR MEMORY (the A operand), accumulating O in tensor
+//                    memory over all key tiles; tcgen05.commit signals mbarriers;
+//   16 softmax warps, two threads per query row (warps w and w + 8 reach the same 32 lanes; each takes
+//                    64 of the tile's 128 keys): tcgen05.ld the scores twice (row maximum, then
+//                    exp2 with the scale folded in), exchange the halves' maxima through shared
+//                    memory, and tcgen05.st P as bf16 pairs over the columns of S.  The running maximum
+//                    is only raised -- and O rescaled in place -- when it grows by more than 2^8 (p
+//                    stays <= 256, exact in the final O / l).
+// S and P of a tile share their columns, so a tile runs S -> softmax -> P V strictly in turn and the
+// two query tiles alternate on the tensor core.  Tensor memory: S / P 2 x 128 columns, O 2 x D.
+// (Earlier forms: keys in tiles of 64 with P through shared memory -- 16 + 8 small MMAs per 64 keys,
+// all operands from shared memory, 160 KB of operand reads per 128 keys and tile -- ran at 709
+// TFLOP/s on [4, 32, 4096, 128]; 128-key tiles with P in tensor memory 729; two softmax threads
+// per row 948; packed float32 pairs and three-input maxima in the softmax 959.)
 // Causal: key tiles beyond a query tile's diagonal are never computed; inside the diagonal tile
 // keys j > i are masked -- the reference's `if causal && j > i continue`.
 #include <cuda.h>
@@ -30,33 +37,10 @@
 namespace lmb {
 namespace {
 
-constexpr int kBM = 128, kBN = 64, kKvStages = 3;
+constexpr int kBM = 128;
 constexpr int kLoaders = 2 * 32;          // loader threads
-constexpr int kThreads = 9 * 32 + kLoaders;   // warps 0-3 / 4-7 softmax of query tile 0 / 1, 8 MMA, 9.. loaders
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleStep = 8.0f;     // log2 units the maximum may lag behind before O is rescaled
-
-// Optional phase stamps (SM clock) of CTA (0, 0) for tuning; compiled in only with -DLMB_FLASH_TRACE.
-#ifdef LMB_FLASH_TRACE
-}  // namespace
-__device__ long long g_flash_trace[64 * 16];
-namespace {
-#define FL_TRACE(tile, slot) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (tile) < 64) g_flash_trace[(tile) * 16 + (slot)] = clock64(); } while (0)
-#else
-#define FL_TRACE(tile, slot) ((void)0)
-#endif
-
-template <int D>
-struct Smem {
-  static constexpr int kQ = kBM * D * 2;
-  static constexpr int kKV = kBN * D * 2;
-  static constexpr int kP = kBM * kBN * 2;
-  static constexpr int offQ = 0;                              // two query tiles
-  static constexpr int offK = offQ + 2 * kQ;
-  static constexpr int offV = offK + kKvStages * kKV;
-  static constexpr int offP = offV + kKvStages * kKV;          // [tile][buffer]
-  static constexpr int total = offP + 4 * kP;
-};
 
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
@@ -84,290 +68,42 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, i
       : "memory");
 }
 
-template <int D>
-__global__ void __launch_bounds__(kThreads, 1)
-flash_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ q, const __grid_constant__ CUtensorMap kmap,
-                const __grid_constant__ CUtensorMap vmap, const FlashView fv, int S, float scale, int causal, int* err) {
-  constexpr int W = D % 64 == 0 ? 64 : 32;            // head dims per swizzled sub-tile
-  constexpr int kSub = kBN * W * 2;                   // bytes of one sub-tile [64 keys][W]
-  constexpr uint32_t kSwz = W == 64 ? 2u : 4u;        // descriptor layout type: 128-byte / 64-byte swizzle
-  using namespace tc;
-  typedef Smem<D> SM;
-  extern __shared__ __align__(1024) unsigned char smem[];
-  __shared__ __align__(8) uint64_t q_full, kv_full[kKvStages], kv_empty[kKvStages];
-  __shared__ __align__(8) uint64_t s_full[2][2], s_empty[2][2], p_full[2][2], p_empty[2][2];
-  __shared__ uint32_t tmem_slot;
-  constexpr uint32_t kTmemCols = 512;
-  constexpr uint32_t kColS = 0, kColO = 256;                 // S: [tile][buffer] x 64 columns, O: [tile] x D columns
-
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int qp = (int)gridDim.x - 1 - (int)blockIdx.x;        // heavy (late) causal tiles first
-  const int q0 = qp * 2 * kBM;
-  // blockIdx.y = batch * H + head; query head h reads kv head h / G (G = 1: an op with H kv heads)
-  const int bi = (int)blockIdx.y / fv.H, hi = (int)blockIdx.y - bi * fv.H;
-  const __nv_bfloat16* qb = q + bi * fv.q_b + hi * fv.q_h;
-  const int kvh = hi / fv.G;
-  __nv_bfloat16* ob_base = out + bi * fv.q_b + hi * fv.q_h;
-  const int64_t q_s = fv.q_s;
-  int n_tiles[2];
-#pragma unroll
-  for (int t = 0; t < 2; ++t) {
-    const int qt0 = q0 + t * kBM;
-    const int k_stop = qt0 >= S ? 0 : (causal ? min(S, qt0 + kBM) : S);
-    n_tiles[t] = (k_stop + kBN - 1) / kBN;
-  }
-  const int n_max = max(n_tiles[0], n_tiles[1]);
-
-  if (tid == 0) {
-    mbar_init(&q_full, kLoaders / 32);
-    for (int s = 0; s < kKvStages; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
-    for (int t = 0; t < 2; ++t) {
-      for (int i = 0; i < 2; ++i) {
-        mbar_init(&s_full[t][i], 1); mbar_init(&s_empty[t][i], 4);
-        mbar_init(&p_full[t][i], 4); mbar_init(&p_empty[t][i], 1);
-      }
-    }
-    mbar_init_fence();
-  }
-  if (warp == 8) tmem_alloc(&tmem_slot, kTmemCols);
-  fence_before();
-  __syncthreads();
-  fence_after();
-  const uint32_t tmem = tmem_slot;
-  bool dead = false;
-
-  if (warp >= 9) {
-    // ------------------------------ loaders ------------------------------
-    // The loader warps take the key tiles in turn (warp w: tiles w, w + 2, ...), each waiting for
-    // its own tile to land before it signals it, so one warp's wait never holds back the other's
-    // next issue.
-    const int lw = warp - 9, lt = tid - 9 * 32;     // lt: 0..kLoaders-1
-    const uint32_t sQ = smem_u32(smem + SM::offQ);
-    for (int i = lt; i < 2 * kBM * (D / 8); i += kLoaders) {
-      const int row = i / (D / 8), c8 = i - row * (D / 8);      // row 0..255 over both tiles
-      const int qi = q0 + row;
-      cp_async16(sQ + (row >> 7) * SM::kQ + canon(row & 127, c8, kBM), qb + (int64_t)min(qi, S - 1) * q_s + c8 * 8, qi < S ? 16u : 0u);
-    }
-    cp_async_commit();
-    // Q: every loader thread waits for its own chunks, then its warp signals
-    cp_async_wait<0>();
-    fence_async_smem();
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&q_full);
-    // K and V: one thread issues the tensor copies of a key tile (D / W boxes each) onto the stage's barrier
-    if (lw == 0) {
-      for (int j = 0; j < n_max; ++j) {
-        const int s = j % kKvStages;
-        mbar_wait(&kv_empty[s], ((j / kKvStages) & 1) ^ 1, dead, err);
-        if (lane == 0) {
-          mbar_expect_tx(&kv_full[s], (uint32_t)(2 * SM::kKV));
-#pragma unroll
-          for (int sub = 0; sub < D / W; ++sub) {
-            tma_load_4d(smem + SM::offK + s * SM::kKV + sub * kSub, &kmap, sub * W, j * kBN, kvh, bi, &kv_full[s]);
-            tma_load_4d(smem + SM::offV + s * SM::kKV + sub * kSub, &vmap, sub * W, j * kBN, kvh, bi, &kv_full[s]);
-          }
-        }
-        __syncwarp();
-      }
-    }
-  } else if (warp == 8) {
-    // ------------------------------ MMA issue ------------------------------
-    constexpr uint32_t kIdescS = idesc_bf16(kBM, kBN, false, false);
-    constexpr uint32_t kIdescPV = idesc_bf16(kBM, D, false, true);          // V is read MN-major
-    mbar_wait(&q_full, 0, dead, err);
-    auto issue_pv = [&](int j) {                     // O[t] += P[t](j) V(j) for the tiles that reach key tile j
-      const int pb = j & 1, s = j % kKvStages;
-#pragma unroll
-      for (int t = 0; t < 2; ++t) {
-        if (j >= n_tiles[t]) continue;
-        mbar_wait(&p_full[t][pb], (j >> 1) & 1, dead, err);
-        fence_after();
-        if (lane == 0) FL_TRACE(j, 8 + t);
-        if (lane == 0) {
-          // A = P [128 x 64] K-major: lbo (between key groups of 8) = 128*16, sbo = 128
-          const uint64_t adesc = smem_desc(smem_u32(smem + SM::offP + (t * 2 + pb) * SM::kP), kBM * 16, 128);
-          // B = V tile read MN-major: N = d runs along the swizzled rows (D / W blocks, kSub bytes apart), K = key:
-          // groups of 8 keys are 8 rows = 8 * 2 W bytes apart; a K = 16 step is two groups
-          const uint64_t bdesc = smem_desc_swz(smem_u32(smem + SM::offV + s * SM::kKV), kSub, 16 * W, kSwz);
-#pragma unroll
-          for (int ks = 0; ks < kBN / 16; ++ks)
-            mma_f16(tmem + kColO + t * D, adesc + (uint64_t)(ks * ((2 * kBM * 16) >> 4)), bdesc + (uint64_t)(ks * ((32 * W) >> 4)),
-                    kIdescPV, (j > 0 || ks > 0) ? 1u : 0u);
-          commit(&p_empty[t][pb]);
-        }
-        __syncwarp();
-      }
-      if (lane == 0) commit(&kv_empty[s]);
-      __syncwarp();
-    };
-    for (int j = 0; j < n_max; ++j) {
-      const int sb = j & 1, s = j % kKvStages;
-      mbar_wait(&kv_full[s], (j / kKvStages) & 1, dead, err);
-      if (lane == 0) FL_TRACE(j, 10);
-#pragma unroll
-      for (int t = 0; t < 2; ++t) {
-        if (j >= n_tiles[t]) continue;
-        mbar_wait(&s_empty[t][sb], ((j >> 1) & 1) ^ 1, dead, err);
-        fence_after();
-        if (lane == 0) FL_TRACE(j, 11 + t);
-        if (lane == 0) {
-          // A = Q [128 x D] K-major, canonical: lbo = 128*16, sbo = 128
-          const uint64_t adesc = smem_desc(smem_u32(smem + SM::offQ + t * SM::kQ), kBM * 16, 128);
-          // B = K tile, K-major in swizzled rows of W head dims: step ks covers d 16 ks .. + 15 = sub-tile (16 ks) / W,
-          // 32 bytes per step inside the row
-          const uint32_t sK = smem_u32(smem + SM::offK + s * SM::kKV);
-#pragma unroll
-          for (int ks = 0; ks < D / 16; ++ks) {
-            const uint64_t bdesc = smem_desc_swz(sK + ((16 * ks) / W) * kSub + ((16 * ks) % W) * 2, 16, 16 * W, kSwz);
-            mma_f16(tmem + kColS + (t * 2 + sb) * kBN, adesc + (uint64_t)(ks * ((2 * kBM * 16) >> 4)), bdesc, kIdescS, ks ? 1u : 0u);
-          }
-          commit(&s_full[t][sb]);
-        }
-        __syncwarp();
-      }
-      if (j >= 1) issue_pv(j - 1);
-    }
-    if (n_max >= 1) issue_pv(n_max - 1);
-  } else {
-    // ------------------------------ softmax + output: one query row per thread ------------------------------
-    const int t = warp >> 2, wq = warp & 3;
-    const int r = 32 * wq + lane;
-    const int qi = q0 + t * kBM + r;
-    const uint32_t lane_base = (uint32_t)(32 * wq) << 16;
-    const uint32_t colO = kColO + t * D;
-    const float c = scale * kLog2e;
-    const int nt = n_tiles[t];
-    float m = -CUDART_INF_F, l = 0.f;
-    for (int j = 0; j < nt; ++j) {
-      const int sb = j & 1;
-      if (wq == 0 && lane == 0) FL_TRACE(j, 0 + 4 * t);
-      mbar_wait(&s_full[t][sb], (j >> 1) & 1, dead, err);
-      fence_after();
-      if (wq == 0 && lane == 0) FL_TRACE(j, 1 + 4 * t);
-      float sv[kBN];
-      tmem_ld64(sv, tmem + lane_base + kColS + (t * 2 + sb) * kBN);
-      fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_empty[t][sb]);
-      // scores stay unscaled in registers; the scale (c > 0) enters through the exp2 argument
-      float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};     // four chains, not one of 64
-      const bool inside = (j + 1) * kBN <= S && (!causal || (j + 1) * kBN - 1 <= q0 + t * kBM);   // no key of the tile is masked
-      if (inside) {
-#pragma unroll
-        for (int i = 0; i < kBN; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], sv[i]);
-      } else {
-#pragma unroll
-        for (int i = 0; i < kBN; ++i) {
-          const int key = j * kBN + i;
-          if (key >= S || (causal && key > qi)) sv[i] = -CUDART_INF_F;
-          mx4[i & 3] = fmaxf(mx4[i & 3], sv[i]);
-        }
-      }
-      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      mx *= c;
-      // raise the reference maximum only when it lags by more than kRescaleStep; O and l follow it
-      const bool first = m == -CUDART_INF_F && mx > -CUDART_INF_F;
-      const bool raise = m > -CUDART_INF_F && mx > m + kRescaleStep;
-      if (__any_sync(0xffffffffu, raise) && j > 0) {
-        const float alpha = raise ? exp2f(m - mx) : 1.0f;
-        // P V of key tile j - 1 (and with it every earlier one) has landed in O.  The P buffer's own barrier says
-        // so: this thread has waited every earlier phase of it, so the parity cannot be taken for an older phase
-        // (a barrier that counts every tile could be two phases behind here, and parity alone would let that pass).
-        mbar_wait(&p_empty[t][(j - 1) & 1], ((j - 1) >> 1) & 1, dead, err);
-        fence_after();
-#pragma unroll
-        for (int ch = 0; ch < D / 32; ++ch) {
-          float o[32];
-          tmem_ld32(o, tmem + lane_base + colO + ch * 32);
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] *= alpha;
-          tmem_st32(tmem + lane_base + colO + ch * 32, o);
-        }
-        fence_before();
-      }
-      if (raise) { l *= exp2f(m - mx); m = mx; }
-      if (first) m = mx;
-      const float neg_m = m == -CUDART_INF_F ? 0.f : -m;             // row fully masked so far: p = exp2(-inf) = 0
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-      uint32_t packed[kBN / 2];
-#pragma unroll
-      for (int i = 0; i < kBN; i += 2) {
-        const float p0 = ex2_approx(fmaf(sv[i], c, neg_m)), p1 = ex2_approx(fmaf(sv[i + 1], c, neg_m));
-        sum4[(i >> 1) & 3] += p0 + p1;
-        const __nv_bfloat162 pb2 = __floats2bfloat162_rn(p0, p1);
-        packed[i / 2] = *reinterpret_cast<const uint32_t*>(&pb2);
-      }
-      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-      if (wq == 0 && lane == 0) FL_TRACE(j, 2 + 4 * t);
-      mbar_wait(&p_empty[t][sb], ((j >> 1) & 1) ^ 1, dead, err);
-      unsigned char* pt = smem + SM::offP + (t * 2 + sb) * SM::kP;
-#pragma unroll
-      for (int c8 = 0; c8 < kBN / 8; ++c8)
-        *reinterpret_cast<uint4*>(pt + canon(r, c8, kBM)) =
-            make_uint4(packed[4 * c8], packed[4 * c8 + 1], packed[4 * c8 + 2], packed[4 * c8 + 3]);
-      fence_async_smem();
-      fence_before();                    // orders a rescale's tcgen05.st before the MMA that the arrive releases
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full[t][sb]);
-      if (wq == 0 && lane == 0) FL_TRACE(j, 3 + 4 * t);
-    }
-    if (nt >= 1) {
-      mbar_wait(&p_empty[t][(nt - 1) & 1], ((nt - 1) >> 1) & 1, dead, err);     // the last P V has landed (see above)
-      fence_after();
-      const float inv = 1.0f / l;
-      __nv_bfloat16* ob = ob_base + (int64_t)qi * q_s;
-#pragma unroll
-      for (int ch = 0; ch < D / 32; ++ch) {
-        float o[32];
-        tmem_ld32(o, tmem + lane_base + colO + ch * 32);
-        if (qi < S) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint4 w;
-            __nv_bfloat162 a0 = __floats2bfloat162_rn(o[i] * inv, o[i + 1] * inv), a1 = __floats2bfloat162_rn(o[i + 2] * inv, o[i + 3] * inv);
-            __nv_bfloat162 a2 = __floats2bfloat162_rn(o[i + 4] * inv, o[i + 5] * inv), a3 = __floats2bfloat162_rn(o[i + 6] * inv, o[i + 7] * inv);
-            w.x = *reinterpret_cast<uint32_t*>(&a0); w.y = *reinterpret_cast<uint32_t*>(&a1);
-            w.z = *reinterpret_cast<uint32_t*>(&a2); w.w = *reinterpret_cast<uint32_t*>(&a3);
-            *reinterpret_cast<uint4*>(ob + ch * 32 + i) = w;
-          }
-        }
-      }
-      fence_before();
-    }
-  }
-  fence_before();
-  __syncthreads();
-  if (warp == 8) {
-    fence_after();
-    tmem_dealloc(tmem, kTmemCols);
-  }
+// packed float32 pairs (two lanes of one 64-bit register) and the three-input maximum of this architecture: fewer
+// instructions per score in the softmax threads, whose issue slots are as scarce as the exp2 unit
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t pack2(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
 }
 
-
-// ---------------------------------------------------------------------------------------------------------------
-// The same operation with key tiles of 128 and P kept in tensor memory.
-//
-// Per 64-key step the kernel above issues 16 MMAs of N = 64 for the two S tiles and 8 for the two P V products,
-// every one reading both operands from shared memory (P makes a round trip through it): 160 KB of operand reads per
-// 128 keys and query tile, more than the tensor core's time for the same work.  Here a step is 128 keys: S = Q K^T is
-// one M 128 x N 128 accumulator per query tile; the softmax threads read it from tensor memory, and write P as bf16
-// back over the same columns (tcgen05.st: a thread's row is its lane); P V takes its A operand from there, so only K
-// and V are read from shared memory (96 KB per 128 keys and tile).  S and P of a tile share their columns, so a tile
-// runs S -> softmax -> P V strictly in turn, and the two query tiles of the CTA alternate on the tensor core: while
-// one is in its softmax, the other's MMAs run.  Tensor memory: S/P 2 x 128 columns, O 2 x D.
-// ---------------------------------------------------------------------------------------------------------------
-constexpr int kBN2 = 128, kStages2 = 2;
-constexpr int kMmaWarp2 = 16;                       // warps 0-15 softmax (two per query row), 16 MMA issue, 17-18 loaders
-constexpr int kThreads2 = (kMmaWarp2 + 1) * 32 + kLoaders;
+constexpr int kBN = 128, kStages = 2;
+constexpr int kMmaWarp = 16;                       // warps 0-15 softmax (two per query row), 16 MMA issue, 17-18 loaders
+constexpr int kThreads = (kMmaWarp + 1) * 32 + kLoaders;
 
 template <int D>
-struct Smem2 {
+struct Smem {
   static constexpr int kQ = kBM * D * 2;
-  static constexpr int kKV = kBN2 * D * 2;
+  static constexpr int kKV = kBN * D * 2;
   static constexpr int offQ = 0;                              // two query tiles
   static constexpr int offK = offQ + 2 * kQ;
-  static constexpr int offV = offK + kStages2 * kKV;
-  static constexpr int total = offV + kStages2 * kKV;
+  static constexpr int offV = offK + kStages * kKV;
+  static constexpr int total = offV + kStages * kKV;
 };
 
 __device__ __forceinline__ void mma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
@@ -400,16 +136,16 @@ __device__ __forceinline__ void tmem_ld16(float (&v)[16], uint32_t taddr) {
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 
 template <int D>
-__global__ void __launch_bounds__(kThreads2, 1)
-flash_tc128_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ q, const __grid_constant__ CUtensorMap kmap,
+__global__ void __launch_bounds__(kThreads, 1)
+flash_tc_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ q, const __grid_constant__ CUtensorMap kmap,
                    const __grid_constant__ CUtensorMap vmap, const FlashView fv, int S, float scale, int causal, int* err) {
   constexpr int W = D % 64 == 0 ? 64 : 32;            // head dims per swizzled sub-tile
-  constexpr int kSub = kBN2 * W * 2;                  // bytes of one sub-tile [128 keys][W]
+  constexpr int kSub = kBN * W * 2;                  // bytes of one sub-tile [128 keys][W]
   constexpr uint32_t kSwz = W == 64 ? 2u : 4u;
   using namespace tc;
-  typedef Smem2<D> SM;
+  typedef Smem<D> SM;
   extern __shared__ __align__(1024) unsigned char smem[];
-  __shared__ __align__(8) uint64_t q_full, k_full[kStages2], k_empty[kStages2], v_full[kStages2], v_empty[kStages2];
+  __shared__ __align__(8) uint64_t q_full, k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
   __shared__ __align__(8) uint64_t s_full[2], p_full[2], o_done[2];
   __shared__ float xch[2][2][kBM];                    // [tile][column half][row]: the halves' row maxima, later their sums
   __shared__ uint32_t tmem_slot;
@@ -429,29 +165,29 @@ flash_tc128_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restr
   for (int t = 0; t < 2; ++t) {
     const int qt0 = q0 + t * kBM;
     const int k_stop = qt0 >= S ? 0 : (causal ? min(S, qt0 + kBM) : S);
-    n_tiles[t] = (k_stop + kBN2 - 1) / kBN2;
+    n_tiles[t] = (k_stop + kBN - 1) / kBN;
   }
   const int n_max = max(n_tiles[0], n_tiles[1]);
 
   if (tid == 0) {
     mbar_init(&q_full, kLoaders / 32);
-    for (int s = 0; s < kStages2; ++s) {
+    for (int s = 0; s < kStages; ++s) {
       mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
       mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
     }
     for (int t = 0; t < 2; ++t) { mbar_init(&s_full[t], 1); mbar_init(&p_full[t], 8); mbar_init(&o_done[t], 1); }
     mbar_init_fence();
   }
-  if (warp == kMmaWarp2) tmem_alloc(&tmem_slot, kTmemCols);
+  if (warp == kMmaWarp) tmem_alloc(&tmem_slot, kTmemCols);
   fence_before();
   __syncthreads();
   fence_after();
   const uint32_t tmem = tmem_slot;
   bool dead = false;
 
-  if (warp > kMmaWarp2) {
+  if (warp > kMmaWarp) {
     // ------------------------------ loaders: Q by both warps, then K by one and V by the other ------------------------------
-    const int lw = warp - kMmaWarp2 - 1, lt = tid - (kMmaWarp2 + 1) * 32;
+    const int lw = warp - kMmaWarp - 1, lt = tid - (kMmaWarp + 1) * 32;
     const uint32_t sQ = smem_u32(smem + SM::offQ);
     for (int i = lt; i < 2 * kBM * (D / 8); i += kLoaders) {
       const int row = i / (D / 8), c8 = i - row * (D / 8);
@@ -468,28 +204,28 @@ flash_tc128_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restr
     const CUtensorMap* map = lw == 0 ? &kmap : &vmap;
     const int off = lw == 0 ? SM::offK : SM::offV;
     for (int j = 0; j < n_max; ++j) {
-      const int s = j % kStages2;
-      mbar_wait(&empty[s], ((j / kStages2) & 1) ^ 1, dead, err);
+      const int s = j % kStages;
+      mbar_wait(&empty[s], ((j / kStages) & 1) ^ 1, dead, err);
       if (lane == 0) {
         mbar_expect_tx(&full[s], (uint32_t)SM::kKV);
 #pragma unroll
-        for (int sub = 0; sub < D / W; ++sub) tma_load_4d(smem + off + s * SM::kKV + sub * kSub, map, sub * W, j * kBN2, kvh, bi, &full[s]);
+        for (int sub = 0; sub < D / W; ++sub) tma_load_4d(smem + off + s * SM::kKV + sub * kSub, map, sub * W, j * kBN, kvh, bi, &full[s]);
       }
       __syncwarp();
     }
-  } else if (warp == kMmaWarp2) {
+  } else if (warp == kMmaWarp) {
     // ------------------------------ MMA issue ------------------------------
-    constexpr uint32_t kIdescS = idesc_bf16(kBM, kBN2, false, false);
+    constexpr uint32_t kIdescS = idesc_bf16(kBM, kBN, false, false);
     constexpr uint32_t kIdescPV = idesc_bf16(kBM, D, false, true);          // V is read MN-major
     mbar_wait(&q_full, 0, dead, err);
     auto issue_s = [&](int j, int t) {                // S[t] = Q[t] K(j)^T
       if (lane == 0) {
         const uint64_t adesc = smem_desc(smem_u32(smem + SM::offQ + t * SM::kQ), kBM * 16, 128);
-        const uint32_t sK = smem_u32(smem + SM::offK + (j % kStages2) * SM::kKV);
+        const uint32_t sK = smem_u32(smem + SM::offK + (j % kStages) * SM::kKV);
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
           const uint64_t bdesc = smem_desc_swz(sK + ((16 * ks) / W) * kSub + ((16 * ks) % W) * 2, 16, 16 * W, kSwz);
-          mma_f16(tmem + kColS + t * kBN2, adesc + (uint64_t)(ks * ((2 * kBM * 16) >> 4)), bdesc, kIdescS, ks ? 1u : 0u);
+          mma_f16(tmem + kColS + t * kBN, adesc + (uint64_t)(ks * ((2 * kBM * 16) >> 4)), bdesc, kIdescS, ks ? 1u : 0u);
         }
         commit(&s_full[t]);
       }
@@ -497,10 +233,10 @@ flash_tc128_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restr
     };
     auto issue_pv = [&](int j, int t) {               // O[t] += P[t] V(j), P read from tensor memory
       if (lane == 0) {
-        const uint64_t bdesc = smem_desc_swz(smem_u32(smem + SM::offV + (j % kStages2) * SM::kKV), kSub, 16 * W, kSwz);
+        const uint64_t bdesc = smem_desc_swz(smem_u32(smem + SM::offV + (j % kStages) * SM::kKV), kSub, 16 * W, kSwz);
 #pragma unroll
-        for (int ks = 0; ks < kBN2 / 16; ++ks)
-          mma_f16_ts(tmem + kColO + t * D, tmem + kColS + t * kBN2 + ks * 8, bdesc + (uint64_t)(ks * ((32 * W) >> 4)), kIdescPV,
+        for (int ks = 0; ks < kBN / 16; ++ks)
+          mma_f16_ts(tmem + kColO + t * D, tmem + kColS + t * kBN + ks * 8, bdesc + (uint64_t)(ks * ((32 * W) >> 4)), kIdescPV,
                      (j > 0 || ks > 0) ? 1u : 0u);
         if (j == n_tiles[t] - 1) commit(&o_done[t]);
       }
@@ -516,9 +252,9 @@ flash_tc128_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restr
       __syncwarp();
     }
     for (int j = 0; j < n_max; ++j) {
-      const int s = j % kStages2, s1 = (j + 1) % kStages2;
-      mbar_wait(&v_full[s], (j / kStages2) & 1, dead, err);
-      if (j + 1 < n_max) mbar_wait(&k_full[s1], ((j + 1) / kStages2) & 1, dead, err);
+      const int s = j % kStages, s1 = (j + 1) % kStages;
+      mbar_wait(&v_full[s], (j / kStages) & 1, dead, err);
+      if (j + 1 < n_max) mbar_wait(&k_full[s1], ((j + 1) / kStages) & 1, dead, err);
 #pragma unroll
       for (int t = 0; t < 2; ++t) {
         if (j >= n_tiles[t]) continue;
@@ -543,7 +279,7 @@ flash_tc128_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restr
     const int r = 32 * wq + lane;
     const int qi = q0 + t * kBM + r;
     const uint32_t lane_base = (uint32_t)(32 * wq) << 16;
-    const uint32_t colS = kColS + t * kBN2 + h * 64, colP = kColS + t * kBN2 + h * 32, colO = kColO + t * D + h * (D / 2);
+    const uint32_t colS = kColS + t * kBN + h * 64, colP = kColS + t * kBN + h * 32, colO = kColO + t * D + h * (D / 2);
     const int pair_bar = 1 + t * 4 + wq;              // named barrier of the two warps that share these rows
     const float c = scale * kLog2e;
     const int nt = n_tiles[t];
@@ -551,8 +287,8 @@ flash_tc128_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restr
     for (int j = 0; j < nt; ++j) {
       mbar_wait(&s_full[t], j & 1, dead, err);          // S(j) is complete, and with it (pipe order) P V(j - 1): O is at rest
       fence_after();
-      const int key0 = j * kBN2 + h * 64;
-      const bool inside = (j + 1) * kBN2 <= S && (!causal || (j + 1) * kBN2 - 1 <= q0 + t * kBM);   // no key of the tile is masked
+      const int key0 = j * kBN + h * 64;
+      const bool inside = (j + 1) * kBN <= S && (!causal || (j + 1) * kBN - 1 <= q0 + t * kBM);   // no key of the tile is masked
       // pass 1: the maximum of this thread's 64 scores
       float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
 #pragma unroll
@@ -561,7 +297,7 @@ flash_tc128_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restr
         tmem_ld32(sv, tmem + lane_base + colS + qd * 32);
         if (inside) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], sv[i]);
+          for (int i = 0; i < 32; i += 2) mx4[(i >> 1) & 3] = max3(mx4[(i >> 1) & 3], sv[i], sv[i + 1]);
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
@@ -595,7 +331,8 @@ flash_tc128_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restr
       if (first) m = mx;
       const float neg_m = m == -CUDART_INF_F ? 0.f : -m;
       // pass 2: p = exp2(s c - m) as bf16 pairs, kept in registers until the other half has read its scores too
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};           // four chains of (even, odd) partial sums
+      const uint64_t c2 = pack2(c, c), negm2 = pack2(neg_m, neg_m);
       uint32_t packed[32];
 #pragma unroll
       for (int qd = 0; qd < 4; ++qd) {
@@ -609,13 +346,19 @@ flash_tc128_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restr
             if (key >= S || (causal && key > qi)) a0 = -CUDART_INF_F;
             if (key + 1 >= S || (causal && key + 1 > qi)) a1 = -CUDART_INF_F;
           }
-          const float p0 = ex2_approx(fmaf(a0, c, neg_m)), p1 = ex2_approx(fmaf(a1, c, neg_m));
-          sum4[(i >> 1) & 3] += p0 + p1;
+          float x0, x1;
+          unpack2(fma2(pack2(a0, a1), c2, negm2), x0, x1);
+          const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+          sum2[(i >> 1) & 3] = add2(sum2[(i >> 1) & 3], pack2(p0, p1));
           const __nv_bfloat162 pb2 = __floats2bfloat162_rn(p0, p1);
           packed[qd * 8 + i / 2] = *reinterpret_cast<const uint32_t*>(&pb2);
         }
       }
-      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      {
+        float e, o;
+        unpack2(add2(add2(sum2[0], sum2[1]), add2(sum2[2], sum2[3])), e, o);
+        l += e + o;
+      }
       asm volatile("bar.sync %0, 64;\n" ::"r"(pair_bar) : "memory");
       {
         uint32_t lo[16], hi2[16];
@@ -658,7 +401,7 @@ flash_tc128_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restr
   }
   fence_before();
   __syncthreads();
-  if (warp == kMmaWarp2) {
+  if (warp == kMmaWarp) {
     fence_after();
     tmem_dealloc(tmem, kTmemCols);
   }
@@ -670,9 +413,6 @@ int32_t flash_tc_configure() {
   LMB_CUDA(cudaFuncSetAttribute(flash_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<128>::total + 1024));
   LMB_CUDA(cudaFuncSetAttribute(flash_tc_kernel<96>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<96>::total + 1024));
   LMB_CUDA(cudaFuncSetAttribute(flash_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<64>::total + 1024));
-  LMB_CUDA(cudaFuncSetAttribute(flash_tc128_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem2<128>::total + 1024));
-  LMB_CUDA(cudaFuncSetAttribute(flash_tc128_kernel<96>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem2<96>::total + 1024));
-  LMB_CUDA(cudaFuncSetAttribute(flash_tc128_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem2<64>::total + 1024));
   return LMB200_OK;
 }
 
@@ -695,7 +435,7 @@ EncodeTiledFn flash_encode_fn() {
   }
   return fn;
 }
-// 4-D map over K or V: dims {d, key, kv head, batch}; a box is [64 keys][W head dims], swizzled over its W * 2 bytes.
+// 4-D map over K or V: dims {d, key, kv head, batch}; a box is [box_keys keys][W head dims], swizzled over its W * 2 bytes.
 // Keys past S arrive as zeros (the softmax masks them).
 int32_t kv_tensor_map(CUtensorMap* map, const void* base, const FlashView& fv, int64_t B, int64_t S, int64_t D, int box_keys) {
   EncodeTiledFn enc = flash_encode_fn();
@@ -722,20 +462,12 @@ int32_t kv_tensor_map(CUtensorMap* map, const void* base, const FlashView& fv, i
 int32_t flash_tc_launch_view(Ctx* ctx, void* out, const void* q, const void* k, const void* v, const FlashView& fv, int64_t B,
                              int64_t S, int64_t D, float scale, int causal, cudaStream_t stream) {
   dim3 grid((unsigned)ceil_div(S, 2 * kBM), (unsigned)(B * fv.H));
-  // key tiles of 128 with P in tensor memory; LMB200_FLASH_KEYS=64 selects the 64-key kernel (A/B runs)
-  static const bool k64 = [] { const char* e = getenv("LMB200_FLASH_KEYS"); return e && atoi(e) == 64; }();
   CUtensorMap kmap, vmap;
-  LMB_TRY(kv_tensor_map(&kmap, k, fv, B, S, D, k64 ? kBN : kBN2));
-  LMB_TRY(kv_tensor_map(&vmap, v, fv, B, S, D, k64 ? kBN : kBN2));
+  LMB_TRY(kv_tensor_map(&kmap, k, fv, B, S, D, kBN));
+  LMB_TRY(kv_tensor_map(&vmap, v, fv, B, S, D, kBN));
 #define LMB_FLASH(DD)                                                                                                   \
-  do {                                                                                                                  \
-    if (k64)                                                                                                            \
-      flash_tc_kernel<DD><<<grid, kThreads, Smem<DD>::total + 1024, stream>>>(                                         \
-          (__nv_bfloat16*)out, (const __nv_bfloat16*)q, kmap, vmap, fv, (int)S, scale, causal, ctx->dev_err);          \
-    else                                                                                                                \
-      flash_tc128_kernel<DD><<<grid, kThreads2, Smem2<DD>::total + 1024, stream>>>(                                     \
-          (__nv_bfloat16*)out, (const __nv_bfloat16*)q, kmap, vmap, fv, (int)S, scale, causal, ctx->dev_err);          \
-  } while (0)
+  flash_tc_kernel<DD><<<grid, kThreads, Smem<DD>::total + 1024, stream>>>(                                        \
+      (__nv_bfloat16*)out, (const __nv_bfloat16*)q, kmap, vmap, fv, (int)S, scale, causal, ctx->dev_err)
   if (D == 128) LMB_FLASH(128);
   else if (D == 96) LMB_FLASH(96);
   else if (D == 64) LMB_FLASH(64);
@@ -755,9 +487,3 @@ int32_t flash_tc_launch(Ctx* ctx, void* out, const void* q, const void* k, const
 }
 
 }  // namespace lmb
-
-#ifdef LMB_FLASH_TRACE
-extern "C" int32_t lmb200_debug_flash_trace(long long* out) {
-  return cudaMemcpyFromSymbol(out, lmb::g_flash_trace, sizeof(lmb::g_flash_trace)) == cudaSuccess ? 0 : -3;
-}
-#endif
