@@ -534,9 +534,14 @@ __device__ __forceinline__ void row_epilogue(const GemvParams& p, float (&v)[NV]
   typedef Layout<__nv_bfloat16> LY;
   constexpr int N = NV;
   const int rb = row >> 4, rr = row & 15, g = rr & 7, hi = rr >> 3;
-  if (s_inv) {                                   // the RMSNorm scale of the input, one per sequence (InvScale)
+  if (s_inv) {                                   // the norm scale of the input, one per sequence (InvScale)
 #pragma unroll
     for (int b = 0; b < N; ++b) v[b] *= s_inv[b0 + b];
+    if (p.ln_wg) {                               // LayerNorm: the mean's share, inv * mu * (W g)[row]
+      const float wg = row < p.rows ? p.ln_wg[row] : 0.f;
+#pragma unroll
+      for (int b = 0; b < N; ++b) v[b] -= s_inv[32 + b0 + b] * wg;
+    }
   }
   if (p.bias) {
     const float bias = row < p.rows ? p.bias[row] : 0.f;
@@ -654,11 +659,22 @@ namespace {
 __device__ __forceinline__ void compute_inv_scale(const InvScale& iv, float* s_inv, int e) {
   if (!iv.ssq) return;
   const int b = e >> 2, part = e & 3;
-  float s = 0.f;
+  float s = 0.f, sx = 0.f;
   for (int t = part; t < iv.tiles; t += 4) s += __ldcg(iv.ssq + t * 32 + b);
   s += __shfl_xor_sync(0xffffffffu, s, 1);
   s += __shfl_xor_sync(0xffffffffu, s, 2);
-  if (part == 0) s_inv[b] = 1.0f / sqrtf(s * (1.0f / (float)iv.n) + iv.eps);
+  if (iv.sum) {
+    for (int t = part; t < iv.tiles; t += 4) sx += __ldcg(iv.sum + t * 32 + b);
+    sx += __shfl_xor_sync(0xffffffffu, sx, 1);
+    sx += __shfl_xor_sync(0xffffffffu, sx, 2);
+  }
+  if (part == 0) {
+    const float rn = 1.0f / (float)iv.n;
+    const float mu = sx * rn;                                   // 0 for RMSNorm
+    const float inv = 1.0f / sqrtf(fmaxf(s * rn - mu * mu, 0.f) + iv.eps);
+    s_inv[b] = inv;
+    s_inv[32 + b] = mu * inv;
+  }
   asm volatile("bar.sync 1, 128;\n" ::: "memory");
 }
 
@@ -813,10 +829,10 @@ __device__ __forceinline__ void resid_norm_tile(const GemvParams& p, const unsig
       }
     }
   }
-  // residual add, the next Linear's input x * gain, this tile's share of the sum of squares
-  float ssq[8];
+  // residual add, the next Linear's input x * gain, this tile's share of the sum of squares (and, for a LayerNorm, of the sum)
+  float ssq[8], sxv[8];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) ssq[i] = 0.f;
+  for (int i = 0; i < 8; ++i) { ssq[i] = 0.f; sxv[i] = 0.f; }
   __nv_bfloat16* xg = reinterpret_cast<__nv_bfloat16*>(p.rn.xg);
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
@@ -824,8 +840,9 @@ __device__ __forceinline__ void resid_norm_tile(const GemvParams& p, const unsig
     const int grow = row0 + rl0 + 32 * j;
     float4* xr = reinterpret_cast<float4*>(p.rn.x + (size_t)grow * N + 8 * bg);
     float4 x0 = xr[0], x1 = xr[1];
-    x0.x += acc[j][0]; x0.y += acc[j][1]; x0.z += acc[j][2]; x0.w += acc[j][3];
-    x1.x += acc[j][4]; x1.y += acc[j][5]; x1.z += acc[j][6]; x1.w += acc[j][7];
+    const float bias = p.bias ? p.bias[grow] : 0.f;             // the projection's own bias (Whisper)
+    x0.x += acc[j][0] + bias; x0.y += acc[j][1] + bias; x0.z += acc[j][2] + bias; x0.w += acc[j][3] + bias;
+    x1.x += acc[j][4] + bias; x1.y += acc[j][5] + bias; x1.z += acc[j][6] + bias; x1.w += acc[j][7] + bias;
     xr[0] = x0; xr[1] = x1;
     const float xv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
     const float g = p.rn.gain[grow];
@@ -834,6 +851,7 @@ __device__ __forceinline__ void resid_norm_tile(const GemvParams& p, const unsig
     for (int i = 0; i < 8; ++i) {
       o[8 * i] = __float2bfloat16_rn(xv[i] * g);
       ssq[i] += xv[i] * xv[i];
+      sxv[i] += xv[i];
     }
     if (p.rn.capture) {
 #pragma unroll
@@ -853,6 +871,21 @@ __device__ __forceinline__ void resid_norm_tile(const GemvParams& p, const unsig
   }
   asm volatile("bar.sync 1, 128;\n" ::: "memory");
   if (e < 32) p.rn.ssq[(size_t)blockIdx.x * 32 + e] = ((s_red[e] + s_red[32 + e]) + s_red[64 + e]) + s_red[96 + e];
+  if (p.rn.sum) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      sxv[i] += __shfl_xor_sync(0xffffffffu, sxv[i], 4);
+      sxv[i] += __shfl_xor_sync(0xffffffffu, sxv[i], 8);
+      sxv[i] += __shfl_xor_sync(0xffffffffu, sxv[i], 16);
+    }
+    asm volatile("bar.sync 1, 128;\n" ::: "memory");         // s_red has been read
+    if (lane < 4) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s_red[we * 32 + 8 * lane + i] = sxv[i];
+    }
+    asm volatile("bar.sync 1, 128;\n" ::: "memory");
+    if (e < 32) p.rn.sum[(size_t)blockIdx.x * 32 + e] = ((s_red[e] + s_red[32 + e]) + s_red[64 + e]) + s_red[96 + e];
+  }
 }
 
 template <int N>
@@ -869,7 +902,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_tc_kernel(const GemvParams
   __shared__ __align__(8) uint64_t acc_full[2];
   __shared__ __align__(8) uint64_t acc_empty[2];
   __shared__ uint32_t tmem_base_slot;
-  __shared__ float s_inv_buf[32];
+  __shared__ float s_inv_buf[64];        // [0, 32): inv per sequence, [32, 64): mean * inv (LayerNorm)
   const float* s_inv = p.inv.ssq ? s_inv_buf : nullptr;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -1131,7 +1164,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) gemv_cl_kernel(const GemvParams
   __shared__ __align__(8) uint64_t empty_bar[kStages];
   __shared__ __align__(8) uint64_t acc_full;
   __shared__ uint32_t tmem_base_slot;
-  __shared__ float s_inv_buf[32];
+  __shared__ float s_inv_buf[64];        // [0, 32): inv per sequence, [32, 64): mean * inv (LayerNorm)
   __shared__ float s_red[128];
   const float* s_inv = p.inv.ssq ? s_inv_buf : nullptr;
 

@@ -52,13 +52,18 @@ struct ResidNorm {
   const float* gain = nullptr;
   void* xg = nullptr;
   float* ssq = nullptr;
+  float* sum = nullptr;                    // LayerNorm: sum over this CTA's rows of x, slots like ssq (NULL: RMSNorm)
   float* capture = nullptr;                // [B][rows] float32 copy of the new residual rows (parity tests) or NULL
 };
 
 // Consumer side: inv[b] = 1 / sqrt(sum_t ssq[t][b] * (1/n) + eps) multiplies every accumulator of batch
 // column b before the rest of the epilogue.  ssq == NULL: no scaling.
+// LayerNorm (sum != NULL; src/NN.jl:138-173, src/HighLevelOps.jl:292-304): with mu = mean(x) and inv = 1 / sqrt(mean(x*x)
+// - mu*mu + eps), W ((x - mu) inv g + b) = inv (W (x g)) - inv mu (W g) + W b: the consumer multiplies its accumulators
+// by inv, subtracts inv mu wg[row] (GemvParams::ln_wg = W g) and adds a bias that already holds W b.
 struct InvScale {
   const float* ssq = nullptr;
+  const float* sum = nullptr;
   int tiles = 0;                           // slots written by the producer (its CTA count)
   int n = 0;                               // row length of the norm (hidden)
   float eps = 0.f;
@@ -104,6 +109,7 @@ struct GemvParams {
   // every epilogue: added to the accumulator first, one value per internal row (NULL: none)
   const float* bias = nullptr;
   InvScale inv;              // per-sequence RMSNorm scale applied to the accumulators (before the bias)
+  const float* ln_wg = nullptr;  // LayerNorm input: W g per internal row (see InvScale)
   ResidNorm rn;              // EPI_RESID_NORM
   PeerPush push;             // EPI_RESID_NORM under tensor parallelism (n > 1)
   // L2 prefetch for the GEMV that runs next (bf16 tensor-core kernels): once a CTA's producer has issued

@@ -549,6 +549,98 @@ __global__ void __launch_bounds__(128) embed_prep_kernel(const int* __restrict__
   if (e < 32) ssq_out[(size_t)blockIdx.x * 32 + e] = ((s_red[e] + s_red[32 + e]) + s_red[64 + e]) + s_red[96 + e];
 }
 
+// The same for the Whisper decoder: x <- embedding row + position row (src/Whisper.jl:704-707), the first
+// LayerNorm's x * gain, and per-CTA sums of x and of x^2 (mean and variance for the consumer, InvScale).
+template <int N>
+__global__ void __launch_bounds__(128) embed_prep_ln_kernel(const int* __restrict__ tokens, const __nv_bfloat16* __restrict__ embed,
+                                                            int vocab, int hidden, int B, const float* __restrict__ pos_emb,
+                                                            const int* __restrict__ pos, const float* __restrict__ gain,
+                                                            float* __restrict__ x, __nv_bfloat16* __restrict__ xg,
+                                                            float* __restrict__ ssq_out, float* __restrict__ sum_out, int rows_per_cta) {
+  __shared__ float s_red[2][128];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int e = threadIdx.x, lane = e & 31, we = e >> 5;
+  const int bg = e & 3, rl0 = e >> 2;
+  int tok[8], ps[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int b = 8 * bg + i;
+    const bool live = b < B && bg < N / 8;
+    const int t = live ? tokens[b] : -1;
+    tok[i] = (t >= 0 && t < vocab) ? t : -1;
+    ps[i] = live ? pos[b] : 0;
+  }
+  float ssq[8], sx[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { ssq[i] = 0.f; sx[i] = 0.f; }
+  for (int rl = rl0; rl < rows_per_cta; rl += 32) {
+    const int k = blockIdx.x * rows_per_cta + rl;
+    if (k >= hidden || bg >= N / 8) continue;
+    float xv[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float ev = tok[i] >= 0 ? __bfloat162float(embed[(int64_t)tok[i] * hidden + k]) : 0.f;
+      xv[i] = 8 * bg + i < B ? ev + pos_emb[(int64_t)ps[i] * hidden + k] : 0.f;
+    }
+    float4* xr = reinterpret_cast<float4*>(x + (size_t)k * N + 8 * bg);
+    xr[0] = make_float4(xv[0], xv[1], xv[2], xv[3]);
+    xr[1] = make_float4(xv[4], xv[5], xv[6], xv[7]);
+    const float g = gain[k];
+    __nv_bfloat16* o = xg + (size_t)(k >> 3) * (N * 8) + bg * 64 + (k & 7);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      o[8 * i] = __float2bfloat16_rn(xv[i] * g);
+      ssq[i] += xv[i] * xv[i];
+      sx[i] += xv[i];
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    ssq[i] += __shfl_xor_sync(0xffffffffu, ssq[i], 4);
+    ssq[i] += __shfl_xor_sync(0xffffffffu, ssq[i], 8);
+    ssq[i] += __shfl_xor_sync(0xffffffffu, ssq[i], 16);
+    sx[i] += __shfl_xor_sync(0xffffffffu, sx[i], 4);
+    sx[i] += __shfl_xor_sync(0xffffffffu, sx[i], 8);
+    sx[i] += __shfl_xor_sync(0xffffffffu, sx[i], 16);
+  }
+  if (lane < 4) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { s_red[0][we * 32 + 8 * lane + i] = ssq[i]; s_red[1][we * 32 + 8 * lane + i] = sx[i]; }
+  }
+  __syncthreads();
+  if (e < 32) {
+    ssq_out[(size_t)blockIdx.x * 32 + e] = ((s_red[0][e] + s_red[0][32 + e]) + s_red[0][64 + e]) + s_red[0][96 + e];
+    sum_out[(size_t)blockIdx.x * 32 + e] = ((s_red[1][e] + s_red[1][32 + e]) + s_red[1][64 + e]) + s_red[1][96 + e];
+  }
+}
+
+// wg[r] = sum_k W[r, k] g[k];  bf[r] = sum_k W[r, k] b[k] + bias[r]: the two vectors that fold a LayerNorm (gain g,
+// bias b) into the Linear W that follows it.  W in the tiled bf16 layout, one block per internal row.
+__global__ void __launch_bounds__(128) ln_fold_kernel(const __nv_bfloat16* __restrict__ W, int rows, int K, const float* __restrict__ g,
+                                                      const float* __restrict__ b, const float* __restrict__ bias,
+                                                      float* __restrict__ wg, float* __restrict__ bf) {
+  __shared__ float red[2][4];
+  const int r = blockIdx.x, KS = (K + 127) >> 7;
+  float sg = 0.f, sb = 0.f;
+  for (int k = threadIdx.x; k < K; k += 128) {
+    const float w = __bfloat162float(W[wcanon_offset(r, k, KS)]);
+    sg += w * g[k];
+    sb += w * b[k];
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    sg += __shfl_xor_sync(0xffffffffu, sg, off);
+    sb += __shfl_xor_sync(0xffffffffu, sb, off);
+  }
+  if ((threadIdx.x & 31) == 0) { red[0][threadIdx.x >> 5] = sg; red[1][threadIdx.x >> 5] = sb; }
+  __syncthreads();
+  if (threadIdx.x == 0 && r < rows) {
+    wg[r] = (red[0][0] + red[0][1]) + (red[0][2] + red[0][3]);
+    bf[r] = (red[1][0] + red[1][1]) + (red[1][2] + red[1][3]) + (bias ? bias[r] : 0.f);
+  }
+}
+
 int32_t step_kernels_configure() {
 #define LMB_CARVE(KERN) \
   LMB_CUDA(cudaFuncSetAttribute(KERN, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared))
@@ -825,8 +917,9 @@ extern "C" int32_t lmb200_model_destroy(lmb200_model h) {
     cudaFree(L.wq_cross); cudaFree(L.wo_cross); cudaFree(L.attn_norm_b); cudaFree(L.ffn_norm_b);
     cudaFree(L.cross_norm); cudaFree(L.cross_norm_b); cudaFree(L.b_qkv); cudaFree(L.b_o); cudaFree(L.b_q_cross);
     cudaFree(L.b_o_cross); cudaFree(L.b_fc1); cudaFree(L.b_fc2);
+    cudaFree(L.wg_qkv); cudaFree(L.bf_qkv); cudaFree(L.wg_qc); cudaFree(L.bf_qc); cudaFree(L.wg_fc1); cudaFree(L.bf_fc1);
   }
-  cudaFree(M->final_norm_b); cudaFree(M->pos_emb); cudaFree(M->embed_tiled);
+  cudaFree(M->final_norm_b); cudaFree(M->pos_emb); cudaFree(M->embed_tiled); cudaFree(M->wg_head); cudaFree(M->bf_head);
   cudaFree(M->embed); cudaFree(M->final_norm); cudaFree(M->lm_head); cudaFree(M->inv_freq);
   M->magic = 0;
   delete M;
@@ -878,6 +971,7 @@ extern "C" int32_t lmb200_model_init_random(lmb200_model h, uint64_t seed, float
   LMB_TRY(fill_tiled_dt(M, M->lm_head, M->m_head, f));
   LMB_CUDA(cudaStreamSynchronize(ctx->stream));
   M->all_weights_set = true;
+  M->fold_valid = false;
   return LMB200_OK;
 }
 
@@ -1016,6 +1110,7 @@ extern "C" int32_t lmb200_model_set_weight(lmb200_model h, const char* name, con
   cudaStreamSynchronize(ctx->stream);
   cudaFree(stage);
   if (rc == LMB200_OK) M->weights_set.insert(n);
+  M->fold_valid = false;
   return rc;
 }
 
@@ -1433,7 +1528,141 @@ int32_t enqueue_whisper_step_t(Session* S, cudaStream_t st, bool with_head) {
   return LMB200_OK;
 }
 
+// The vectors that fold every LayerNorm of the Whisper decoder into the Linear after it (LayerWeights::wg_*, bf_*):
+// computed from the bf16 weights the step multiplies with, once per set of weights.
+int32_t whisper_fold(Model* M) {
+  Ctx* ctx = M->ctx;
+  const lmb200_model_config& c = M->cfg;
+  auto fold = [&](const void* W, const WMap& m, const float* g, const float* b, const float* bias, float** wg, float** bf) -> int32_t {
+    const int rows_pad = (int)round_up(m.rows, 128);
+    if (!*wg) LMB_TRY(dmalloc((void**)wg, (int64_t)rows_pad * 4, true, ctx->stream));
+    if (!*bf) LMB_TRY(dmalloc((void**)bf, (int64_t)rows_pad * 4, true, ctx->stream));
+    ln_fold_kernel<<<m.rows, 128, 0, ctx->stream>>>(reinterpret_cast<const __nv_bfloat16*>(W), m.rows, m.K, g, b, bias, *wg, *bf);
+    ctx->launches++;
+    return LMB200_OK;
+  };
+  for (LayerWeights& W : M->layers) {
+    LMB_TRY(fold(W.wqkv, M->m_qkv, W.attn_norm, W.attn_norm_b, W.b_qkv, &W.wg_qkv, &W.bf_qkv));
+    LMB_TRY(fold(W.wq_cross, M->m_qc, W.cross_norm, W.cross_norm_b, W.b_q_cross, &W.wg_qc, &W.bf_qc));
+    LMB_TRY(fold(W.wgu, M->m_gu, W.ffn_norm, W.ffn_norm_b, W.b_fc1, &W.wg_fc1, &W.bf_fc1));
+  }
+  LMB_TRY(fold(M->embed_tiled, M->m_head, M->final_norm, M->final_norm_b, nullptr, &M->wg_head, &M->bf_head));
+  LMB_CUDA(cudaGetLastError());
+  (void)c;
+  M->fold_valid = true;
+  return LMB200_OK;
+}
+
+// The fused decode step of the bf16 Whisper decoder: eight launches per layer instead of eleven.  As in the Llama
+// step the residual add and the norm around every Linear ride on the projections: out_proj (self and cross) and fc2
+// finish with EPI_RESID_NORM (their own bias added on the way), which leaves x * gain and the per-sequence sums of x
+// and x^2; q/k/v, the cross q projection, fc1 and the tied head apply the LayerNorm to their accumulators
+// (InvScale with a mean, GemvParams::ln_wg, a bias that already holds W b).  src/Whisper.jl:584-742.
+int32_t enqueue_whisper_step_fused(Session* S, cudaStream_t st, bool with_head) {
+  Model* M = S->m;
+  Ctx* ctx = M->ctx;
+  const lmb200_model_config& c = M->cfg;
+  const int dt = c.dtype;
+  const int B = S->B, hid = c.hidden, L = c.n_layers;
+  const float qk_scale = powf((float)hid / (float)c.n_heads, -0.25f);
+  {
+    const int rows_per = S->embed_rows_per_cta;
+    const int grid = (int)ceil_div(hid, rows_per);
+    if (S->Bp == 16)
+      LMB_CUDA(launch_k(embed_prep_ln_kernel<16>, dim3(grid), dim3(128), 0, st, (const int*)S->tokens,
+                        reinterpret_cast<const __nv_bfloat16*>(M->embed), c.vocab, hid, B, (const float*)M->pos_emb, (const int*)S->pos,
+                        (const float*)M->layers[0].attn_norm, S->xT, reinterpret_cast<__nv_bfloat16*>(S->xn), S->ssq, S->sum_slots,
+                        rows_per));
+    else
+      LMB_CUDA(launch_k(embed_prep_ln_kernel<32>, dim3(grid), dim3(128), 0, st, (const int*)S->tokens,
+                        reinterpret_cast<const __nv_bfloat16*>(M->embed), c.vocab, hid, B, (const float*)M->pos_emb, (const int*)S->pos,
+                        (const float*)M->layers[0].attn_norm, S->xT, reinterpret_cast<__nv_bfloat16*>(S->xn), S->ssq, S->sum_slots,
+                        rows_per));
+    ctx->launches++;
+  }
+  int tiles = (int)ceil_div(hid, S->embed_rows_per_cta);
+  auto layer_norm = [&](GemvParams& p, const float* wg, const float* bf) {
+    p.inv.ssq = S->ssq; p.inv.sum = S->sum_slots; p.inv.tiles = tiles; p.inv.n = hid; p.inv.eps = c.rms_eps;
+    p.ln_wg = wg; p.bias = bf;
+  };
+  auto resid = [&](GemvParams& p, const float* bias, const float* next_gain, const GemvPlan& plan, int rows) {
+    p.epi = EPI_RESID_NORM; p.bias = bias;
+    p.rn.x = S->xT; p.rn.gain = next_gain; p.rn.xg = S->xn; p.rn.ssq = S->ssq; p.rn.sum = S->sum_slots;
+    tiles = gemv_plan_ctas(plan, rows);
+  };
+  auto attention = [&](void* kv_layer, int64_t bs, int64_t hs, const int* pos, int T_fixed, int kpc, int nsplit) -> int32_t {
+    AttnParams a;
+    a.q = S->qbuf; a.q_pitch = S->q_pitch; a.kv_layer = kv_layer; a.kv_batch_stride = bs; a.kv_head_stride = hs;
+    a.B = B; a.KVl = M->KVl; a.G = 1; a.D = M->D; a.pos = pos; a.T_fixed = T_fixed;
+    a.keys_per_cta = kpc; a.nsplit = nsplit;
+    a.scale = 1.0f;                      // the scale is already in q and k
+    a.part_o = S->part_o; a.part_ml = S->part_ml; a.out = S->attn_out; a.out_tiled_bp = S->Bp;
+    a.counters = S->attn_counters;
+    return attn_decode_launch(ctx, dt, a, st);
+  };
+  for (int l = 0; l < L; ++l) {
+    LayerWeights& W = M->layers[l];
+    void* kv_layer = reinterpret_cast<char*>(S->kv) + (int64_t)l * S->kv_layer_stride * M->esz;
+    {
+      GemvParams p = gemv_params(S, W.wqkv, M->m_qkv, S->p_qkv, S->xn);
+      p.epi = EPI_QKV_ROPE; p.rope = 0; p.qk_scale = qk_scale;
+      layer_norm(p, W.wg_qkv, W.bf_qkv);
+      p.q_out = S->qbuf; p.q_pitch = S->q_pitch;
+      p.kv_layer = kv_layer; p.kv_batch_stride = S->kv_batch_stride; p.kv_head_stride = S->kv_head_stride;
+      p.inv_freq = M->inv_freq; p.pos = S->pos; p.pos_uniform = S->ragged ? 0 : 1; p.Hl = M->Hl; p.KVl = M->KVl; p.D = M->D;
+      LMB_TRY(gemv_launch(ctx, dt, p, st));
+    }
+    LMB_TRY(attention(kv_layer, S->kv_batch_stride, S->kv_head_stride, S->pos, 0, S->keys_per_cta, S->nsplit));
+    {
+      GemvParams p = gemv_params(S, W.wo, M->m_o, S->p_o, S->attn_out);
+      resid(p, W.b_o, W.cross_norm, S->p_o, M->m_o.rows);
+      LMB_TRY(gemv_launch(ctx, dt, p, st));
+    }
+    {  // cross-attention query: q rows only, nothing is appended to a cache
+      GemvParams p = gemv_params(S, W.wq_cross, M->m_qc, S->p_qc, S->xn);
+      p.epi = EPI_QKV_ROPE; p.rope = 0; p.qk_scale = qk_scale;
+      layer_norm(p, W.wg_qc, W.bf_qc);
+      p.q_out = S->qbuf; p.q_pitch = S->q_pitch;
+      p.kv_layer = nullptr; p.inv_freq = M->inv_freq; p.pos = S->pos; p.pos_uniform = S->ragged ? 0 : 1; p.Hl = M->Hl; p.KVl = 0; p.D = M->D;
+      LMB_TRY(gemv_launch(ctx, dt, p, st));
+    }
+    void* cross_layer = reinterpret_cast<char*>(S->cross_kv) + (int64_t)l * S->cross_layer_stride * M->esz;
+    LMB_TRY(attention(cross_layer, S->cross_batch_stride, S->cross_head_stride, nullptr, c.cross_len, S->cross_keys_per_cta,
+                      S->cross_nsplit));
+    {
+      GemvParams p = gemv_params(S, W.wo_cross, M->m_o, S->p_o, S->attn_out);
+      resid(p, W.b_o_cross, W.ffn_norm, S->p_o, M->m_o.rows);
+      LMB_TRY(gemv_launch(ctx, dt, p, st));
+    }
+    {
+      GemvParams p = gemv_params(S, W.wgu, M->m_gu, S->p_gu, S->xn);
+      p.epi = EPI_GELU_ACT; p.act = S->act; p.n_act = c.intermediate;
+      layer_norm(p, W.wg_fc1, W.bf_fc1);
+      LMB_TRY(gemv_launch(ctx, dt, p, st));
+    }
+    {
+      GemvParams p = gemv_params(S, W.wdown, M->m_down, S->p_down, S->act);
+      resid(p, W.b_fc2, l + 1 < L ? M->layers[l + 1].attn_norm : M->final_norm, S->p_down, M->m_down.rows);
+      p.rn.capture = S->capture_on ? S->capture + (int64_t)l * B * hid : nullptr;
+      LMB_TRY(gemv_launch(ctx, dt, p, st));
+    }
+  }
+  if (with_head) {
+    GemvParams p = gemv_params(S, M->embed_tiled, M->m_head, S->p_head, S->xn);     // logits = LayerNorm(x) * E^T
+    p.epi = EPI_STORE_F32; p.out = S->logits; p.out_pitch = S->logits_pitch;
+    layer_norm(p, M->wg_head, M->bf_head);
+    LMB_TRY(gemv_launch(ctx, dt, p, st));
+    LMB_CUDA(launch_k(argmax_step_kernel, dim3(B), dim3(kArgmaxThreads), 0, st, (const float*)S->logits, S->logits_pitch, c.vocab,
+                      S->tokens, S->tok_hist, (const int*)S->step_ctr, B, S->stop));
+    ctx->launches++;
+  }
+  LMB_CUDA(launch_k(advance_kernel, dim3(1), dim3(32), 0, st, S->pos, (const int*)S->limit, S->B, S->step_ctr, (unsigned long long*)nullptr));
+  ctx->launches++;
+  return LMB200_OK;
+}
+
 int32_t enqueue_step(Session* S, cudaStream_t st, bool with_head) {
+  if (S->fused && S->m->cfg.arch == LMB200_ARCH_WHISPER_DECODER) return enqueue_whisper_step_fused(S, st, with_head);
   if (S->fused) return enqueue_step_fused(S, st, with_head);
   if (S->m->cfg.arch == LMB200_ARCH_WHISPER_DECODER)
     return S->m->cfg.dtype == LMB200_BF16 ? enqueue_whisper_step_t<__nv_bfloat16>(S, st, with_head)
@@ -1500,6 +1729,7 @@ int32_t ensure_graphs(Session* S) {
 
 int32_t run_step(Session* S, bool with_head) {
   Ctx* ctx = S->m->ctx;
+  if (S->fused && S->m->cfg.arch == LMB200_ARCH_WHISPER_DECODER && !S->m->fold_valid) LMB_TRY(whisper_fold(S->m));
   LMB_TRY(ensure_graphs(S));
   LMB_CUDA(cudaGraphLaunch(with_head ? S->graph_full : S->graph_body, ctx->stream));
   ctx->launches += with_head ? S->graph_nodes_full : S->graph_nodes_body;
@@ -1579,11 +1809,11 @@ extern "C" int32_t lmb200_session_create(lmb200_model hm, int32_t batch, int32_t
   plan(S->p_qkv, M->m_qkv); plan(S->p_o, M->m_o); plan(S->p_gu, M->m_gu); plan(S->p_down, M->m_down);
   plan(S->p_head, M->m_head);
   {
-    // The fused step (LMB200_FUSED_STEP=0 switches it off for A/B runs): bf16 Llama / Phi-3 on the tcgen05
-    // GEMV, every row group of the two row-parallel projections resident at once, and under tensor
+    // The fused step (LMB200_FUSED_STEP=0 switches it off for A/B runs): bf16 Llama / Phi-3 / Whisper decoder on the
+    // tcgen05 GEMV, every row group of the two row-parallel projections resident at once, and under tensor
     // parallelism the peer regions mapped and large enough for n bf16 partials of [hidden][Bp].
     const char* fe = getenv("LMB200_FUSED_STEP");
-    bool fused = !(fe && atoi(fe) == 0) && !whisper && c.dtype == LMB200_BF16 && gemv_variant() == GEMV_TCGEN05 && c.hidden % 8 == 0 &&
+    bool fused = !(fe && atoi(fe) == 0) && c.dtype == LMB200_BF16 && gemv_variant() == GEMV_TCGEN05 && c.hidden % 8 == 0 &&
                  ceil_div(c.hidden, 32 * ceil_div(c.hidden, 32 * 256)) <= 256;
     if (fused && c.tp_size > 1 && !M->tp_solo)
       fused = ctx->peer_n == c.tp_size && (int64_t)c.tp_size * c.hidden * S->Bp * 2 <= kPeerBufFloats * 4 &&
@@ -1639,6 +1869,7 @@ extern "C" int32_t lmb200_session_create(lmb200_model hm, int32_t batch, int32_t
   if (S->fused) {
     alloc((void**)&S->xT, (int64_t)round_up(c.hidden, 128) * S->Bp * 4);
     alloc((void**)&S->ssq, (int64_t)256 * 32 * 4);
+    if (whisper) alloc((void**)&S->sum_slots, (int64_t)256 * 32 * 4);
   }
   S->host_pos_v.assign(batch, 0);
   if (rc == LMB200_OK) rc = set_limits(S, nullptr);
@@ -1663,7 +1894,7 @@ extern "C" int32_t lmb200_session_destroy(lmb200_session h) {
   cudaFree(S->attn_out); cudaFree(S->act); cudaFree(S->tokens); cudaFree(S->pos); cudaFree(S->limit); cudaFree(S->step_ctr); cudaFree(S->ragged_logits);
   cudaFree(S->tok_hist); cudaFree(S->prompt); cudaFree(S->gemv_partials); cudaFree(S->gemv_counters);
   cudaFree(S->part_o); cudaFree(S->part_ml); cudaFree(S->attn_counters); cudaFree(S->prefill_buf); cudaFree(S->capture);
-  cudaFree(S->xT); cudaFree(S->ssq); cudaFree(S->stop);
+  cudaFree(S->xT); cudaFree(S->ssq); cudaFree(S->sum_slots); cudaFree(S->stop);
   S->magic = 0;
   delete S;
   return LMB200_OK;

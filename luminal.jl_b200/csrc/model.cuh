@@ -48,6 +48,9 @@ struct LayerWeights {
   float* b_o_cross = nullptr;
   float* b_fc1 = nullptr;
   float* b_fc2 = nullptr;
+  // Whisper, fused step: what folding a LayerNorm into the Linear that follows it needs (InvScale): W g and W b + bias
+  // per internal row of q/k/v, of the cross-attention q projection and of fc1
+  float *wg_qkv = nullptr, *bf_qkv = nullptr, *wg_qc = nullptr, *bf_qc = nullptr, *wg_fc1 = nullptr, *bf_fc1 = nullptr;
 };
 
 struct Model {
@@ -62,6 +65,8 @@ struct Model {
   float* final_norm_b = nullptr;
   float* pos_emb = nullptr;     // Whisper: [max_positions, hidden] float32
   void* embed_tiled = nullptr;  // Whisper: the embedding table in GEMV layout (tied head)
+  float *wg_head = nullptr, *bf_head = nullptr;   // Whisper, fused step: the final LayerNorm folded into the head
+  bool fold_valid = false;      // the folded vectors match the weights (set_weight / init_random clear it)
   std::vector<LayerWeights> layers;
   void* embed = nullptr;        // [vocab, hidden] row-major, model dtype
   float* final_norm = nullptr;
@@ -108,6 +113,7 @@ struct Session {
   float* part_o = nullptr;
   float* part_ml = nullptr;
   unsigned* attn_counters = nullptr;   // [B*KVl], zero between launches
+  float* sum_slots = nullptr;          // fused Whisper step: per-CTA sums of x beside ssq (LayerNorm's mean)
   void* prefill_buf = nullptr;         // scratch of the GEMM prompt phase, kept between prompts
   int64_t prefill_bytes = 0;
   int keys_per_cta = 0, nsplit = 0;
