@@ -31,15 +31,6 @@ constexpr size_t kMaxSmem = 224 * 1024;
 
 int g_variant = GEMV_TCGEN05;
 
-__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
-                                         uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-      "{%0,%1,%2,%3};\n"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
 // gelu(a) = a*0.5*(1 + tanh(0.7978845608*a*(1 + 0.044715*a*a))), tanh(z) = sigmoid(2z)*2 - 1,
 // sigmoid through exp2 -- the reference's decomposition, src/HighLevelOps.jl:153-168
 __device__ __forceinline__ float gelu_ref(float a) {

@@ -663,7 +663,7 @@ struct WhisperWalker : Walker {
 };
 
 struct Role {
-  int Block::*node;
+  int Block::* node;
   const char* name;
 };
 const Role kRoles[] = {{&Block::q, "self_attn.q_proj"},  {&Block::k, "self_attn.k_proj"}, {&Block::v, "self_attn.v_proj"},
@@ -807,7 +807,7 @@ Match match_whisper_step(const lmb200_node_list* g, int output_id) {
     const WhisperLayer& p = ordered[n];
     bool same = p.H == f.H && p.D == f.D && p.step == f.step && p.max_seq == f.max_seq && p.enc_seq == f.enc_seq && p.B == f.B &&
                 p.eps == eps;
-    for (int WhisperLayer::*r : {&WhisperLayer::q_w, &WhisperLayer::k_w, &WhisperLayer::v_w, &WhisperLayer::o_w, &WhisperLayer::cq_w,
+    for (int WhisperLayer::* r : {&WhisperLayer::q_w, &WhisperLayer::k_w, &WhisperLayer::v_w, &WhisperLayer::o_w, &WhisperLayer::cq_w,
                                  &WhisperLayer::co_w})
       same = same && w.shape(p.*r) == Shape{hidden, hidden};
     same = same && w.shape(p.fc1_w) == Shape{ffn, hidden} && w.shape(p.fc2_w) == Shape{hidden, ffn};
@@ -816,7 +816,7 @@ Match match_whisper_step(const lmb200_node_list* g, int output_id) {
   Match m;
   m.weights = {{"model.decoder.embed_tokens.weight", table}, {"model.decoder.embed_positions.weight", pos},
                {"model.decoder.layer_norm.weight", ln_w}, {"model.decoder.layer_norm.bias", ln_b}};
-  struct WRole { int WhisperLayer::*node; const char* name; };
+  struct WRole { int WhisperLayer::* node; const char* name; };
   static const WRole roles[] = {
       {&WhisperLayer::q_w, "self_attn.q_proj.weight"}, {&WhisperLayer::k_w, "self_attn.k_proj.weight"},
       {&WhisperLayer::v_w, "self_attn.v_proj.weight"}, {&WhisperLayer::q_b, "self_attn.q_proj.bias"},

@@ -81,10 +81,6 @@ __device__ __forceinline__ float gelu_ref(float a) {
   return (a * 0.5f) * (1.0f + th);
 }
 
-__device__ __forceinline__ uint32_t canon(int row, int c8, int rows) {
-  return (uint32_t)(c8 * (rows * 16) + (row >> 3) * 128 + (row & 7) * 16);
-}
-
 // v[i] = accumulator of (row, token t0 + i).  Rows g and g+8 of a 16-row block, which the fused
 // epilogues combine, are 8 lanes apart.
 __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, float (&v)[32], int row, int t0, int t_end, unsigned char* stage) {
@@ -754,7 +750,7 @@ __global__ void f32_to_bf16_kernel(__nv_bfloat16* __restrict__ dst, const float*
 int32_t prefill_linear(Ctx* ctx, const void* W, const float* x_dev, int T, int rows, int K, float* out_dev, cudaStream_t st) {
   LMB_REQUIRE(K % 8 == 0, "prefill_gemm: K %d must be a multiple of 8", K);
   Scratch sc;
-  __nv_bfloat16* xb;
+  __nv_bfloat16* xb = nullptr;
   LMB_TRY(sc.get(&xb, (int64_t)T * K));
   const int64_t n = (int64_t)T * K;
   f32_to_bf16_kernel<<<(unsigned)std::min<int64_t>(ceil_div(n, 256), 4096), 256, 0, st>>>(xb, x_dev, n);

@@ -248,7 +248,6 @@ __global__ void cumsum_kernel(float* out, const float* in, int64_t rows, int64_t
 __global__ void __launch_bounds__(256) norm_kernel(float* y, const float* x, const float* w, const float* bias,
                                                    int64_t n, float eps, int mean_centre) {
   __shared__ float red[8];
-  __shared__ float s_mean;
   const int tid = threadIdx.x;
   const float* xr = x + blockIdx.x * n;
   float* yr = y + blockIdx.x * n;
@@ -273,7 +272,6 @@ __global__ void __launch_bounds__(256) norm_kernel(float* y, const float* x, con
   for (int64_t i = tid; i < n; i += 256) { const float v = xr[i] + mean * -1.0f; ss += v * v; }
   const float var = block_sum(ss) * (1.0f / (float)n);
   const float inv = 1.0f / sqrtf(var + eps);
-  (void)s_mean;
   for (int64_t i = tid; i < n; i += 256) {
     float v = (xr[i] + mean * -1.0f) * inv;
     if (w) v = v * w[i];

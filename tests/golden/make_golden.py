@@ -6,6 +6,9 @@ synth_golden.json  -- bit patterns of the counter-based generator (seed, tensor 
 small_llama_golden.npz -- greedy tokens and first-step logits of BASELINE config 1 (4 layers,
     hidden 256, 8 heads, MLP 688, vocab 1024; 32-token prompt, 64 steps) from the oracle, so the
     GPU parity test also has a committed reference that does not depend on re-running the oracle.
+
+Both files are written by this repository's own oracle: they are regression fixtures (they catch a change of
+the oracle or of the generator), not vectors of the reference, which cannot run here.
 """
 import json
 import os
