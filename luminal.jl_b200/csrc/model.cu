@@ -493,6 +493,72 @@ __global__ void advance_kernel(int* pos, const int* limit, int B, int* step_ctr,
 }
 
 
+// Tensor-parallel head: the best (logit, id) of this rank's slice of the vocabulary, per sequence, written where the
+// peers can read it (this rank's exchange buffer): pairs[2 b] = value, pairs[2 b + 1] = the id's bits.
+__global__ void __launch_bounds__(kArgmaxThreads) argmax_pairs_kernel(const float* logits, int pitch, int n, int id0, float* pairs) {
+  __shared__ float sv[kArgmaxThreads / 32];
+  __shared__ int si[kArgmaxThreads / 32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int b = blockIdx.x, tid = threadIdx.x;
+  const float* row = logits + (int64_t)b * pitch;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  auto take = [&](float v, int i) {
+    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+  };
+  for (int i = tid; i < n; i += kArgmaxThreads) take(row[i], i);
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    const float v = __shfl_xor_sync(0xffffffffu, best, off);
+    const int i = __shfl_xor_sync(0xffffffffu, bi, off);
+    take(v, i);
+  }
+  if ((tid & 31) == 0) { sv[tid >> 5] = best; si[tid >> 5] = bi; }
+  __syncthreads();
+  if (tid < 32) {
+    best = sv[tid];
+    bi = si[tid];
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      const float v = __shfl_xor_sync(0xffffffffu, best, off);
+      const int i = __shfl_xor_sync(0xffffffffu, bi, off);
+      take(v, i);
+    }
+    if (tid == 0) {
+      pairs[2 * b] = best;
+      pairs[2 * b + 1] = __int_as_float(bi == 0x7fffffff ? bi : bi + id0);
+    }
+  }
+}
+
+// ... and the choice among the ranks' pairs: the flag exchange of the float32 all-reduce (every rank announces the epoch,
+// waits -- bounded -- for the others', then reads their pairs with peer loads), the largest logit wins and the lowest id
+// among equals, exactly what argmax_step_kernel does over the whole row; then the same bookkeeping.  One block.
+__global__ void __launch_bounds__(256) argmax_tp_select_kernel(const PeerReduce pr, int B, int* tokens, int* hist, const int* step_ctr,
+                                                               int* stop) {
+  pdl_launch_dependents();
+  pdl_wait();
+  peer_exchange_wait(pr);
+  const int b = threadIdx.x;
+  if (b >= B) return;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int r = 0; r < pr.n; ++r) {
+    float v, f;
+    asm volatile("ld.relaxed.sys.global.v2.f32 {%0,%1}, [%2];" : "=f"(v), "=f"(f) : "l"(pr.part[r] + 2 * b) : "memory");
+    const int i = __float_as_int(f);
+    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+  }
+  const int eot = stop ? stop[0] : -1;
+  if (eot >= 0) {
+    if (stop[2 + b]) bi = eot;
+    else if (bi == eot) { stop[2 + b] = 1; atomicAdd(&stop[1], 1); }
+  }
+  tokens[b] = bi;
+  if (hist) hist[(int64_t)(*step_ctr) * B + b] = bi;
+}
+
 // First kernel of the fused step: x <- embedding rows (out-of-range ids -> zeros, as _gather_kernel! does,
 // src/Execution.jl:580-595), laid out [hidden][Bp]; xg <- bf16(x * gain) in the GEMV activation layout; one
 // slot of per-sequence sums of squares per CTA.  What add_rmsnorm_kernel does for the first layer, minus
@@ -1351,7 +1417,9 @@ PeerPush peer_push(Session* S, int index) {
 // o_proj and down_proj finish with EPI_RESID_NORM (under tensor parallelism including the all-reduce of
 // their partial sums), q/k/v, gate/up and the head multiply their accumulators by the norm's
 // per-sequence scale (InvScale).
-int32_t enqueue_step_fused(Session* S, cudaStream_t st, bool with_head) {
+// head: 0 no head, 1 head with the full logits, 2 tokens only (the sliced head, where the session has one)
+int32_t enqueue_step_fused(Session* S, cudaStream_t st, int head) {
+  const bool with_head = head != 0;
   Model* M = S->m;
   Ctx* ctx = M->ctx;
   const lmb200_model_config& c = M->cfg;
@@ -1421,7 +1489,30 @@ int32_t enqueue_step_fused(Session* S, cudaStream_t st, bool with_head) {
       tiles = gemv_plan_ctas(S->p_down, M->m_down.rows);
     }
   }
-  if (with_head) {
+  if (with_head && S->head_sliced) {
+    // this rank's rows of the head, its best (logit, id) per sequence, the exchange; the full logits only on request
+    {
+      WMap ms = M->m_head;
+      ms.rows = S->head_rows;
+      ms.RB = (int)ceil_div(S->head_rows, 16);
+      const int64_t KS = ceil_div(M->m_head.K, 128);
+      const __nv_bfloat16* Ws = reinterpret_cast<const __nv_bfloat16*>(M->lm_head) + (int64_t)S->head_rg0 * KS * 16384;
+      GemvParams p = gemv_params(S, Ws, ms, S->p_head_slice, S->xn);
+      p.epi = EPI_STORE_F32; p.inv = inv_scale(); p.out = S->logits_slice; p.out_pitch = S->head_pitch;
+      LMB_TRY(gemv_launch(ctx, dt, p, st));
+    }
+    RowParallelOut ex = row_parallel_out(S, 2 * L);       // the buffers and flags of the float32 exchange, phase 2 L + 1
+    LMB_CUDA(launch_k(argmax_pairs_kernel, dim3(B), dim3(kArgmaxThreads), 0, st, (const float*)S->logits_slice, S->head_pitch,
+                      S->head_rows, S->head_rg0 * 128, ex.out));
+    LMB_CUDA(launch_k(argmax_tp_select_kernel, dim3(1), dim3(256), 0, st, ex.pr, B, S->tokens, S->tok_hist, (const int*)S->step_ctr,
+                      S->stop));
+    ctx->launches += 2;
+    if (head == 1) {
+      GemvParams p = gemv_params(S, M->lm_head, M->m_head, S->p_head, S->xn);
+      p.epi = EPI_STORE_F32; p.inv = inv_scale(); p.out = S->logits; p.out_pitch = S->logits_pitch;
+      LMB_TRY(gemv_launch(ctx, dt, p, st));
+    }
+  } else if (with_head) {
     GemvParams p = gemv_params(S, M->lm_head, M->m_head, S->p_head, S->xn);
     p.epi = EPI_STORE_F32; p.inv = inv_scale(); p.out = S->logits; p.out_pitch = S->logits_pitch;
     LMB_TRY(gemv_launch(ctx, dt, p, st));
@@ -1661,9 +1752,10 @@ int32_t enqueue_whisper_step_fused(Session* S, cudaStream_t st, bool with_head) 
   return LMB200_OK;
 }
 
-int32_t enqueue_step(Session* S, cudaStream_t st, bool with_head) {
+int32_t enqueue_step(Session* S, cudaStream_t st, int head) {
+  const bool with_head = head != 0;
   if (S->fused && S->m->cfg.arch == LMB200_ARCH_WHISPER_DECODER) return enqueue_whisper_step_fused(S, st, with_head);
-  if (S->fused) return enqueue_step_fused(S, st, with_head);
+  if (S->fused) return enqueue_step_fused(S, st, head);
   if (S->m->cfg.arch == LMB200_ARCH_WHISPER_DECODER)
     return S->m->cfg.dtype == LMB200_BF16 ? enqueue_whisper_step_t<__nv_bfloat16>(S, st, with_head)
                                           : enqueue_whisper_step_t<float>(S, st, with_head);
@@ -1693,15 +1785,16 @@ int32_t enqueue_head_bf16(Session* S, cudaStream_t st) {
 void drop_graphs(Session* S) {
   if (S->graph_full) cudaGraphExecDestroy(S->graph_full);
   if (S->graph_body) cudaGraphExecDestroy(S->graph_body);
-  S->graph_full = S->graph_body = nullptr;
+  if (S->graph_tok) cudaGraphExecDestroy(S->graph_tok);
+  S->graph_full = S->graph_body = S->graph_tok = nullptr;
   S->graph_stream = nullptr;
 }
 
-int32_t capture_one(Session* S, cudaStream_t st, bool with_head, cudaGraphExec_t* exec, int* nodes) {
+int32_t capture_one(Session* S, cudaStream_t st, int head, cudaGraphExec_t* exec, int* nodes) {
   Ctx* ctx = S->m->ctx;
   const int64_t before = ctx->launches;
   LMB_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
-  int32_t rc = enqueue_step(S, st, with_head);
+  int32_t rc = enqueue_step(S, st, head);
   cudaGraph_t graph = nullptr;
   cudaError_t e = cudaStreamEndCapture(st, &graph);
   ctx->launches = before;            // captured, not run
@@ -1721,18 +1814,22 @@ int32_t ensure_graphs(Session* S) {
   Ctx* ctx = S->m->ctx;
   if (S->graph_full && S->graph_stream == ctx->stream) return LMB200_OK;
   drop_graphs(S);
-  LMB_TRY(capture_one(S, ctx->stream, true, &S->graph_full, &S->graph_nodes_full));
-  LMB_TRY(capture_one(S, ctx->stream, false, &S->graph_body, &S->graph_nodes_body));
+  LMB_TRY(capture_one(S, ctx->stream, 1, &S->graph_full, &S->graph_nodes_full));
+  LMB_TRY(capture_one(S, ctx->stream, 0, &S->graph_body, &S->graph_nodes_body));
+  if (S->head_sliced) LMB_TRY(capture_one(S, ctx->stream, 2, &S->graph_tok, &S->graph_nodes_tok));
   S->graph_stream = ctx->stream;
   return LMB200_OK;
 }
 
-int32_t run_step(Session* S, bool with_head) {
+// with_head: the step ends in the head and the greedy token; want_logits: a caller will read the full logits after it
+// (under tensor parallelism the step otherwise computes only this rank's slice of them)
+int32_t run_step(Session* S, bool with_head, bool want_logits = true) {
   Ctx* ctx = S->m->ctx;
   if (S->fused && S->m->cfg.arch == LMB200_ARCH_WHISPER_DECODER && !S->m->fold_valid) LMB_TRY(whisper_fold(S->m));
   LMB_TRY(ensure_graphs(S));
-  LMB_CUDA(cudaGraphLaunch(with_head ? S->graph_full : S->graph_body, ctx->stream));
-  ctx->launches += with_head ? S->graph_nodes_full : S->graph_nodes_body;
+  const bool tok_only = with_head && !want_logits && S->graph_tok;
+  LMB_CUDA(cudaGraphLaunch(tok_only ? S->graph_tok : with_head ? S->graph_full : S->graph_body, ctx->stream));
+  ctx->launches += tok_only ? S->graph_nodes_tok : with_head ? S->graph_nodes_full : S->graph_nodes_body;
   if (!S->in_ragged_prefill) {
     S->host_pos += 1;
     for (int& v : S->host_pos_v) v += 1;
@@ -1825,6 +1922,24 @@ extern "C" int32_t lmb200_session_create(lmb200_model hm, int32_t batch, int32_t
     }
     S->fused = fused;
     S->embed_rows_per_cta = 32 * (int)ceil_div(c.hidden, 32 * 256);
+    // The head is replicated; under tensor parallelism every rank multiplies only its share of the rows and the ranks
+    // exchange their best (logit, id) pairs (LMB200_TP_HEAD=replicated keeps every rank on the whole head, A/B runs).
+    const char* he = getenv("LMB200_TP_HEAD");
+    if (fused && !whisper && c.tp_size > 1 && !M->tp_solo && ctx->peer_n == c.tp_size && !(he && strcmp(he, "replicated") == 0)) {
+      const int n_rg = (int)ceil_div(M->m_head.rows, 128), per = (int)ceil_div(n_rg, c.tp_size);
+      const int rg0 = per * c.tp_rank;
+      const int rows = (int)std::min<int64_t>((int64_t)per * 128, (int64_t)M->m_head.rows - (int64_t)rg0 * 128);
+      if ((int64_t)per * 128 * (c.tp_size - 1) < M->m_head.rows && rows > 0 && (int64_t)batch * c.hidden <= kPeerBufFloats &&
+          (unsigned long long)2 * c.n_layers + 2 < kPeerEpochStride) {
+        S->head_sliced = true;
+        S->head_rg0 = rg0;
+        S->head_rows = rows;
+        S->head_pitch = per * 128;
+        WMap ms = M->m_head;
+        ms.rows = rows;
+        plan(S->p_head_slice, ms);
+      }
+    }
   }
   int64_t po, pml;
   attn_plan(ctx, batch, M->KVl, M->G, M->D, S->cap, &S->keys_per_cta, &S->nsplit, &po, &pml);
@@ -1871,6 +1986,7 @@ extern "C" int32_t lmb200_session_create(lmb200_model hm, int32_t batch, int32_t
     alloc((void**)&S->ssq, (int64_t)256 * 32 * 4);
     if (whisper) alloc((void**)&S->sum_slots, (int64_t)256 * 32 * 4);
   }
+  if (S->head_sliced) alloc((void**)&S->logits_slice, (int64_t)batch * S->head_pitch * 4);
   S->host_pos_v.assign(batch, 0);
   if (rc == LMB200_OK) rc = set_limits(S, nullptr);
   if (rc == LMB200_OK) {
@@ -1894,7 +2010,7 @@ extern "C" int32_t lmb200_session_destroy(lmb200_session h) {
   cudaFree(S->attn_out); cudaFree(S->act); cudaFree(S->tokens); cudaFree(S->pos); cudaFree(S->limit); cudaFree(S->step_ctr); cudaFree(S->ragged_logits);
   cudaFree(S->tok_hist); cudaFree(S->prompt); cudaFree(S->gemv_partials); cudaFree(S->gemv_counters);
   cudaFree(S->part_o); cudaFree(S->part_ml); cudaFree(S->attn_counters); cudaFree(S->prefill_buf); cudaFree(S->capture);
-  cudaFree(S->xT); cudaFree(S->ssq); cudaFree(S->sum_slots); cudaFree(S->stop);
+  cudaFree(S->xT); cudaFree(S->ssq); cudaFree(S->sum_slots); cudaFree(S->logits_slice); cudaFree(S->stop);
   S->magic = 0;
   delete S;
   return LMB200_OK;
@@ -2088,7 +2204,7 @@ extern "C" int32_t lmb200_prefill(lmb200_session h, const int32_t* tokens, int32
   LMB_CUDA(cudaMemsetAsync(S->step_ctr, 0, 4, ctx->stream));
   for (int i = 0; i < n; ++i) {
     LMB_CUDA(cudaMemcpyAsync(S->tokens, S->prompt + (int64_t)i * B, (size_t)B * 4, cudaMemcpyDeviceToDevice, ctx->stream));
-    LMB_TRY(run_step(S, i == n - 1));
+    LMB_TRY(run_step(S, i == n - 1, logits_out != nullptr));
   }
   if (logits_out) LMB_TRY(copy_logits_out(S, logits_out));
   LMB_CUDA(cudaStreamSynchronize(ctx->stream));
@@ -2172,7 +2288,7 @@ extern "C" int32_t lmb200_prefill_ragged(lmb200_session h, const int32_t* tokens
       rc = fail(LMB200_ECUDA, "prefill_ragged: token copy failed");
       break;
     }
-    rc = run_step(S, ends_here);
+    rc = run_step(S, ends_here, logits_out != nullptr);
     if (rc == LMB200_OK && ends_here && logits_out) {
       for (int b = 0; b < B; ++b)
         if (lengths[b] - 1 == i &&
@@ -2208,7 +2324,7 @@ extern "C" int32_t lmb200_decode_step(lmb200_session h, const int32_t* tokens_in
   LMB_CUDA(cudaSetDevice(ctx->device));
   LMB_CUDA(cudaMemcpyAsync(S->tokens, tokens_in, (size_t)S->B * 4, cudaMemcpyHostToDevice, ctx->stream));
   LMB_CUDA(cudaMemsetAsync(S->step_ctr, 0, 4, ctx->stream));
-  LMB_TRY(run_step(S, true));
+  LMB_TRY(run_step(S, true, logits_out != nullptr));
   if (next_tokens_out)
     LMB_CUDA(cudaMemcpyAsync(next_tokens_out, S->tokens, (size_t)S->B * 4, cudaMemcpyDeviceToHost, ctx->stream));
   if (logits_out) LMB_TRY(copy_logits_out(S, logits_out));
@@ -2227,7 +2343,7 @@ static int32_t decode_n_common(Session* S, const int32_t* first, bool first_on_d
     LMB_CUDA(cudaMemcpyAsync(S->tokens, first, (size_t)S->B * 4,
                              first_on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, ctx->stream));
   LMB_CUDA(cudaMemsetAsync(S->step_ctr, 0, 4, ctx->stream));
-  for (int i = 0; i < n_steps; ++i) LMB_TRY(run_step(S, true));
+  for (int i = 0; i < n_steps; ++i) LMB_TRY(run_step(S, true, false));
   return LMB200_OK;
 }
 
@@ -2270,7 +2386,7 @@ extern "C" int32_t lmb200_decode_until(lmb200_session h, const int32_t* first_to
   const int kRun = 8;                                     // replays between two looks at the count
   while (done < budget && rc == LMB200_OK) {
     const int n = budget - done < kRun ? budget - done : kRun;
-    for (int i = 0; i < n && rc == LMB200_OK; ++i) rc = run_step(S, true);
+    for (int i = 0; i < n && rc == LMB200_OK; ++i) rc = run_step(S, true, false);
     if (rc != LMB200_OK) break;
     done += n;
     int finished = 0;

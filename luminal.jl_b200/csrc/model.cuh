@@ -131,10 +131,18 @@ struct Session {
   int embed_rows_per_cta = 32;
   float* capture = nullptr;     // [L][B][hidden] when enabled
   bool capture_on = false;
-  cudaGraphExec_t graph_full = nullptr;
-  cudaGraphExec_t graph_body = nullptr;
+  // Tensor parallelism, fused step: every rank multiplies only its slice of the (replicated) head's rows and the ranks
+  // exchange their (best logit, token id) pairs; the full logits are computed only when a caller asks for them
+  bool head_sliced = false;
+  int head_rg0 = 0, head_rows = 0;      // this rank's first 128-row group and its valid rows
+  GemvPlan p_head_slice;
+  float* logits_slice = nullptr;        // [B][head_pitch] float32
+  int head_pitch = 0;
+  cudaGraphExec_t graph_full = nullptr;   // head and logits
+  cudaGraphExec_t graph_body = nullptr;   // no head
+  cudaGraphExec_t graph_tok = nullptr;    // sliced head, tokens only (head_sliced)
   cudaStream_t graph_stream = nullptr;
-  int graph_nodes_full = 0, graph_nodes_body = 0;
+  int graph_nodes_full = 0, graph_nodes_body = 0, graph_nodes_tok = 0;
 };
 
 int32_t step_kernels_configure();
