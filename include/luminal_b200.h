@@ -341,7 +341,8 @@ int32_t lmb200_decode_until(lmb200_session session, const int32_t* first_tokens,
 int32_t lmb200_decode_n_device(lmb200_session session, const int32_t* first_tokens_dptr,
                                int32_t n_steps, int32_t* tokens_out_dptr);
 /* Algorithmic HBM bytes of ONE decode step on this rank at context length T (weights read once
- * + KV cache read for T keys + KV written for one key). */
+ * + KV cache read for T keys + KV written for one key; of the replicated head only the rows this
+ * rank multiplies in a token-only step under tensor parallelism). */
 int32_t lmb200_session_step_bytes(lmb200_session session, int32_t T, int64_t* bytes);
 
 /* ---------------------------------------------------------------------------------------------

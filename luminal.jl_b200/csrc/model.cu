@@ -2439,7 +2439,9 @@ extern "C" int32_t lmb200_session_step_bytes(lmb200_session h, int32_t T, int64_
   int64_t per_layer = ((int64_t)M->m_qkv.rows * c.hidden + (int64_t)c.hidden * M->Hl * M->D +
                        (int64_t)2 * M->inter_l * c.hidden + (int64_t)c.hidden * M->inter_l) * e +
                       (int64_t)2 * c.hidden * 4;
-  int64_t w = per_layer * c.n_layers + (int64_t)c.vocab * c.hidden * e + (int64_t)c.hidden * 4 +
+  // the head: every row, or under tensor parallelism this rank's slice of the rows (the token-only step)
+  const int64_t head_rows = S->head_sliced ? S->head_rows : c.vocab;
+  int64_t w = per_layer * c.n_layers + head_rows * c.hidden * e + (int64_t)c.hidden * 4 +
               (int64_t)S->B * c.hidden * e;
   int64_t kv_read = (int64_t)c.n_layers * S->B * M->KVl * T * M->D * 2 * e;
   int64_t kv_write = (int64_t)c.n_layers * S->B * M->KVl * M->D * 2 * e;
