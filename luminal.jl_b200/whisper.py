@@ -161,6 +161,17 @@ class WhisperCrossAttention:                     # src/Whisper.jl:282-316 (param
         self.o_proj = WLinear(hidden, hidden, graph, reg, f"{prefix}.out_proj", bias=True)
         self.heads = heads
 
+    def __call__(self, queries_t, keys_t, values_t):      # src/Whisper.jl:297-316: projects the encoder output itself
+        batch, dec_seq, hidden = queries_t.shape
+        enc_seq = keys_t.shape[1]
+        H, D = self.heads, hidden // self.heads
+        scale = F32(F32(F32(hidden) / F32(H)) ** F32(-0.25))
+        q = G.permute(G.reshape(self.q_proj(queries_t) * scale, [batch, dec_seq, H, D]), [1, 3, 2, 4])
+        k = G.contiguous(G.permute(G.reshape(self.k_proj(keys_t) * scale, [batch, enc_seq, H, D]), [1, 3, 4, 2]))
+        v = G.permute(G.reshape(self.v_proj(values_t), [batch, enc_seq, H, D]), [1, 3, 2, 4])
+        out = G.matmul(G.softmax(G.matmul(q, k), 4), v)
+        return self.o_proj(G.reshape(G.permute(out, [1, 3, 2, 4]), [batch, dec_seq, hidden]))
+
 
 class DecoderTransformerBlock:                   # src/Whisper.jl:410-432
     def __init__(self, hidden, heads, ff, graph, reg, prefix):
@@ -172,6 +183,11 @@ class DecoderTransformerBlock:                   # src/Whisper.jl:410-432
         self.ff2 = WLinear(ff, hidden, graph, reg, f"{prefix}.fc2")
         self.ff_norm = WLayerNorm(hidden, graph, reg, f"{prefix}.final_layer_norm")
 
+    def __call__(self, x, encoded):                       # src/Whisper.jl:433-443: no cache, causal mask
+        x = x + self.attn(self.attn_norm(x), True)
+        x = x + self.cross_attn(self.cross_attn_norm(x), encoded, encoded)
+        return x + self.ff2(G.gelu(self.ff1(self.ff_norm(x))))
+
 
 class TextDecoder:                               # src/Whisper.jl:449-486
     def __init__(self, graph, reg, *, d_model, heads, layers, ffn, vocab, max_positions):
@@ -182,6 +198,49 @@ class TextDecoder:                               # src/Whisper.jl:449-486
         reg[f"{pfx}.embed_tokens.weight"], reg[f"{pfx}.embed_positions.weight"] = self.embedding, self.pos_embedding
         self.layers = [DecoderTransformerBlock(d_model, heads, ffn, graph, reg, f"{pfx}.layers.{i}") for i in range(layers)]
         self.layer_norm = WLayerNorm(d_model, graph, reg, f"{pfx}.layer_norm")
+
+    def __call__(self, enc_output, tokens):               # src/Whisper.jl:488-505: the whole prefix at once
+        x = G.gather(self.embedding, tokens)
+        cur_seq = tokens.shape[1]
+        pos = G.contiguous(G.slice_along(self.pos_embedding, 1, 0, cur_seq))
+        x = x + G.expand(pos, 1, x.shape[0])
+        for layer in self.layers:
+            x = layer(x, enc_output)
+        return G.matmul(self.layer_norm(x), G.permute(self.embedding, [2, 1]))
+
+
+class KVCacheState:                              # src/Whisper.jl:519-541
+    """Host-side state of one decode session driven graph by graph: the position and, per layer, the self K/V
+    [batch, heads, max_seq, head_dim] (zeroed) and the cross K/V [batch, heads, enc_seq, head_dim]."""
+
+    def __init__(self, batch, n_layers, n_heads, head_dim, enc_seq, max_seq):
+        z = lambda s: np.zeros((batch, n_heads, s, head_dim), F32)
+        self.step_pos, self.max_seq = 0, max_seq
+        self.self_cache = [(z(max_seq), z(max_seq)) for _ in range(n_layers)]
+        self.cross_cache = [(z(enc_seq), z(enc_seq)) for _ in range(n_layers)]
+
+
+def decode_step(exec_obj, idg, cache, token_ids, cross_kv_arrays, device=None):      # src/Whisper.jl:760-801
+    """One step of the incremental decode graph `idg` (built for cache.step_pos): exec_obj is the Graph (run through
+    execute) or its CompiledGraph; the cache's self K/V are replaced by the step's updated ones and its position
+    advances.  Returns the logits [batch, 1, vocab].  The cached session (Session.decode_step) is the fast form of the
+    same step; this one is the reference's host loop kept call for call."""
+    from .execution import execute
+    inputs = {idg.token_input_id: np.asarray(token_ids, F32)}
+    for i, (ck, cv) in enumerate(cross_kv_arrays):
+        inputs[idg.cross_k_ids[i]], inputs[idg.cross_v_ids[i]] = ck, cv
+    for i in range(len(idg.self_k_ids)):
+        inputs[idg.self_k_ids[i]], inputs[idg.self_v_ids[i]] = cache.self_cache[i]
+    want = [idg.logits_id] + list(idg.new_self_k_ids) + list(idg.new_self_v_ids)
+    if isinstance(exec_obj, G.Graph):
+        result = execute(exec_obj, want, inputs, device)
+    else:
+        bufs = exec_obj(inputs, device)
+        result = {i: bufs[i].numpy() for i in want}
+    for i in range(len(idg.new_self_k_ids)):
+        cache.self_cache[i] = (result[idg.new_self_k_ids[i]], result[idg.new_self_v_ids[i]])
+    cache.step_pos += 1
+    return result[idg.logits_id]
 
 
 def _kv_scatter(past, new_slot, step_pos):       # src/Whisper.jl:541-570: slice-and-concat write of one cache slot
@@ -353,4 +412,5 @@ def registry_shapes(*, d_model, heads, enc_layers, dec_layers, ffn, vocab, n_mel
 
 
 __all__ = ["registry_shapes", "FusedEncoder", "AudioEncoder", "Conv1D", "WhisperSelfAttention", "EncoderTransformerBlock", "sinusoids", "project_cross_kv",
-           "encode_cross_kv"]
+           "encode_cross_kv", "WhisperCrossAttention", "DecoderTransformerBlock", "TextDecoder", "KVCacheState", "decode_step", "build_decode_step",
+           "IncrementalDecodeGraph", "whisper_self_attn_cached", "whisper_cross_attn_cached"]

@@ -38,6 +38,23 @@ def run_op(op, ins, out_shape):
     if t is G.Function and op.name=="Gather": return O.gather(*ins)
     if t is G.Function and op.name=="CumSum": return O.cumsum_last(ins[0])
     raise NotImplementedError(op)
+def eval_graph(g, inputs, want):
+    """Node-by-node evaluation of a graph with the oracle's primitives: the CPU counterpart of execute()."""
+    vals = {}
+    for n, (node, shp) in enumerate(zip(g.nodes, g.shapes), start=1):
+        op = node.op
+        if isinstance(op, G.Function) and op.name == "InputTensor":
+            if n in inputs:
+                vals[n] = np.asarray(inputs[n], np.float32)
+            elif (n, 1) in g.tensors:
+                vals[n] = np.asarray(g.tensors[(n, 1)], np.float32)
+        elif isinstance(op, G.Constant):
+            vals[n] = np.float32(op.value)
+        else:
+            vals[n] = run_op(op, [vals[i] for i, _, _ in node.inputs], shp)
+    return [vals[i] for i in want]
+
+
 def eval_plan(graph, plan, inputs):
     R={}
     for nid,w in plan:

@@ -1,0 +1,278 @@
+"""The reference's own component tests restated on this backend, testset for testset, with the reference's sizes:
+tests/test_llama.jl:23-113 (RMSNorm, Mlp, RoPE, Attention, top-level Llama), tests/test_whisper_components.jl:47-118
+(Conv1D, AudioEncoder, TextDecoder at the whisper-tiny constants of src/Whisper.jl:195-206) and tests/test_kv_cache.jl
+(KVCacheState, IncrementalDecodeGraph, _kv_scatter, the cached attention graphs, decode_step! over three steps).
+
+The reference asserts shapes, the absence of NaNs and one RoPE property on random inputs.  Here each graph is built
+by the graph builders, evaluated node by node with the oracle's primitives on the CPU (the reference's assertions,
+plus the values against the oracle's direct restatement of the layer), and, on the GPU, run through execute() and
+compile() against that CPU evaluation."""
+import numpy as np
+import pytest
+
+import luminal_jl_b200 as L
+import luminal_oracle as O
+import whisper_oracle as W
+from luminal_jl_b200 import graph as G, nn as NN, whisper as WG
+from plan_eval import eval_graph
+
+TINY = dict(d_model=384, heads=6, enc_layers=4, dec_layers=4, ffn=1536, vocab=51864, n_mels=80, max_positions=448)
+TOL = 2e-4          # float32 graphs, device against the CPU evaluation (relative to the largest magnitude)
+
+
+def fill_inputs(graph, given, seed):
+    """execute_with_random_inputs of tests/test_llama.jl:7-21: random data for every input tensor not given."""
+    inputs = dict(given)
+    for nid, node in enumerate(graph.nodes, start=1):
+        if isinstance(node.op, G.Function) and node.op.name == "InputTensor" and nid not in inputs and (nid, 1) not in graph.tensors:
+            inputs[nid] = O.synth_normal(seed, nid, graph.shapes[nid - 1], 0.05)
+    return inputs
+
+
+def close(a, b, tol=TOL):
+    a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
+    return a.shape == b.shape and np.abs(a - b).max() <= tol * max(1.0, np.abs(b).max())
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# graphs of tests/test_llama.jl; each returns (graph, output id, inputs, the oracle's value)
+# ----------------------------------------------------------------------------------------------------------------
+def case_rmsnorm():
+    g = G.Graph()
+    ln = NN.RMSNorm(128, g, epsilon=1e-5)
+    x = G.tensor(g, [2, 128])
+    out = ln(x)
+    inputs = fill_inputs(g, {x.id: O.synth_normal(1, 900, (2, 128), 1.0)}, 1)
+    return g, out.id, inputs, O.rms_norm(inputs[x.id], inputs[ln.weight.id], 1e-5), (2, 128)
+
+
+def case_mlp():
+    g = G.Graph()
+    mlp = NN.Mlp(128, 256, g)
+    x = G.tensor(g, [2, 128])
+    out = mlp(x)
+    inputs = fill_inputs(g, {x.id: O.synth_normal(2, 900, (2, 128), 1.0)}, 2)
+    want = O.mlp(inputs[x.id], inputs[mlp.gate_proj.weight.id], inputs[mlp.up_proj.weight.id], inputs[mlp.down_proj.weight.id])
+    return g, out.id, inputs, want, (2, 128)
+
+
+def case_rope():
+    g = G.Graph()
+    x = G.tensor(g, [1, 4, 10, 32])
+    out = NN.apply_rotary_embeddings(x, 0)
+    inputs = {x.id: O.synth_normal(3, 900, (1, 4, 10, 32), 1.0)}
+    return g, out.id, inputs, O.apply_rotary_embeddings(inputs[x.id], 0), (1, 4, 10, 32)
+
+
+def case_attention():
+    g = G.Graph()
+    sa = NN.SelfAttention(128, 4, 4, g)
+    x = G.tensor(g, [1, 8, 128])
+    out = sa(x, 0)
+    inputs = fill_inputs(g, {x.id: O.synth_normal(4, 900, (1, 8, 128), 1.0)}, 4)
+    want = O.self_attention(inputs[x.id], inputs[sa.q_proj.weight.id], inputs[sa.k_proj.weight.id], inputs[sa.v_proj.weight.id],
+                            inputs[sa.o_proj.weight.id], 4, 4, 0)
+    return g, out.id, inputs, want, (1, 8, 128)
+
+
+def case_llama():
+    g, reg = G.Graph(), {}
+    cfg = dict(n_layers=2, hidden=64, n_heads=4, n_kv_heads=4, intermediate=128, vocab=1000, eps=1e-5, rope_base=NN.Llama.ROPE_BASE)
+    llama = NN.Llama(g, reg, vocab_size=1000, hidden=64, n_layers=2, n_heads=4, n_kv_heads=4, intermediate=128)
+    x = G.tensor(g, [1, 8])
+    out = llama(x, 0)
+    tokens = O.synth_tokens(5, 900, (1, 8), 1000)
+    w = O.synth_llama_weights(cfg, seed=5)
+    inputs = {t.id: w[name] for name, t in reg.items()}
+    inputs[x.id] = tokens.astype(np.float32)
+    return g, out.id, inputs, O.llama_forward(tokens, w, cfg, 0), (1, 8, 1000)
+
+
+LLAMA_CASES = dict(rmsnorm=case_rmsnorm, mlp=case_mlp, rope=case_rope, attention=case_attention, llama=case_llama)
+
+
+@pytest.mark.parametrize("name", list(LLAMA_CASES))
+def test_llama_components_on_the_cpu(name):
+    g, out_id, inputs, want, shape = LLAMA_CASES[name]()
+    (res,) = eval_graph(g, inputs, [out_id])
+    assert res.shape == shape                                    # @test size(result) == ...
+    assert not np.isnan(res).any()                               # @test all(!isnan, result)
+    assert close(res, want, 1e-5)
+    if name == "rope":                                           # tests/test_llama.jl:69-72: the pair keeps its norm
+        x = next(iter(inputs.values()))
+        assert abs(np.hypot(x[0, 0, 0, 0], x[0, 0, 0, 1]) - np.hypot(res[0, 0, 0, 0], res[0, 0, 0, 1])) <= 1e-5
+        # ... and, at every position, the pair the column-major split really rotates: (d, d + head_dim / 2)
+        assert np.allclose(np.hypot(x[..., :16], x[..., 16:]), np.hypot(res[..., :16], res[..., 16:]), atol=1e-5)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", list(LLAMA_CASES))
+def test_llama_components_on_the_device(lib_built, device, name):
+    g, out_id, inputs, _, shape = LLAMA_CASES[name]()
+    (want,) = eval_graph(g, inputs, [out_id])
+    res = L.execute(g, out_id, inputs, device)
+    assert res.shape == shape and not np.isnan(res).any()
+    assert close(res, want)
+    cg = L.compile(g, device)
+    assert close(cg(inputs)[out_id].numpy(), want)
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# tests/test_whisper_components.jl:47-118
+# ----------------------------------------------------------------------------------------------------------------
+def conv1d_case():
+    g, reg = G.Graph(), {}
+    a = G.tensor(g, [1, 2, 7])
+    conv = WG.Conv1D(2, 3, 3, g, reg, "conv", stride=2, padding=1)
+    out = conv(a)
+    a_data = np.array([[1, 2, 3, 4, 5, 6, 7], [8, 9, 10, 11, 12, 13, 14]], np.float32).reshape(1, 2, 7)
+    inputs = {a.id: a_data, conv.weight.id: np.ones((3, 6), np.float32), conv.bias.id: np.full(3, 0.5, np.float32)}
+    return g, out.id, inputs
+
+
+def test_conv1d_on_the_cpu():
+    g, out_id, inputs = conv1d_case()
+    (res,) = eval_graph(g, inputs, [out_id])
+    assert res.shape == (1, 3, 4)                                # @test size(res) == (1, 3, 4)
+    # all-ones weights: every output channel is the sum of the zero-padded stride-2 windows of both rows + 0.5
+    assert np.array_equal(res, np.broadcast_to(np.array([20.5, 39.5, 51.5, 40.5], np.float32), (1, 3, 4)))
+
+
+def encoder_case():
+    g, reg = G.Graph(), {}
+    enc = WG.AudioEncoder(g, reg, d_model=TINY["d_model"], heads=TINY["heads"], layers=TINY["enc_layers"], ffn=TINY["ffn"],
+                          n_mels=TINY["n_mels"])
+    a = G.tensor(g, [1, 80, 50])
+    out = enc(a)
+    w = W.synth_weights(TINY, seed=6)
+    inputs = {t.id: w[name] for name, t in reg.items()}
+    inputs[a.id] = O.synth_normal(6, 900, (1, 80, 50), 1.0)
+    return g, out.id, inputs, w, a.id
+
+
+def decoder_case():
+    g, reg = G.Graph(), {}
+    dec = WG.TextDecoder(g, reg, d_model=TINY["d_model"], heads=TINY["heads"], layers=TINY["dec_layers"], ffn=TINY["ffn"],
+                         vocab=TINY["vocab"], max_positions=TINY["max_positions"])
+    enc_out = G.tensor(g, [1, 25, 384])
+    tokens = G.tensor(g, [1, 10])
+    out = dec(enc_out, tokens)
+    w = W.synth_weights(TINY, seed=7)
+    inputs = {t.id: w[name] for name, t in reg.items()}
+    inputs[enc_out.id] = O.synth_normal(7, 900, (1, 25, 384), 1.0)
+    inputs[tokens.id] = np.ones((1, 10), np.float32)             # "dummy tokens", tests/test_whisper_components.jl:102
+    return g, out.id, inputs, w, enc_out.id, tokens.id
+
+
+def test_audio_encoder_on_the_cpu():
+    g, out_id, inputs, w, a_id = encoder_case()
+    (res,) = eval_graph(g, inputs, [out_id])
+    assert res.shape == (1, 25, 384)                             # @test size(res) == (1, 25, 384)
+    assert close(res, W.encoder(inputs[a_id], w, TINY), 1e-5)
+
+
+def test_text_decoder_on_the_cpu():
+    g, out_id, inputs, w, enc_id, tok_id = decoder_case()
+    (res,) = eval_graph(g, inputs, [out_id])
+    assert res.shape == (1, 10, 51864)                           # @test size(res) == (1, 10, 51864)
+    assert close(res, W.decoder_full(inputs[tok_id].astype(np.int64), inputs[enc_id], w, TINY), 1e-5)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("which", ["conv1d", "encoder", "decoder"])
+def test_whisper_components_on_the_device(lib_built, device, which):
+    g, out_id, inputs = {"conv1d": conv1d_case, "encoder": encoder_case, "decoder": decoder_case}[which]()[:3]
+    (want,) = eval_graph(g, inputs, [out_id])
+    res = L.execute(g, out_id, inputs, device)
+    assert res.shape == want.shape and close(res, want)
+    assert close(L.compile(g, device)(inputs)[out_id].numpy(), want)
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# tests/test_kv_cache.jl (TEST_BATCH 1, TEST_ENC_SEQ 8, TEST_MAX_SEQ 10, TEST_STEPS 3)
+# ----------------------------------------------------------------------------------------------------------------
+BATCH, ENC_SEQ, MAX_SEQ, STEPS = 1, 8, 10, 3
+HEADS, HEAD_DIM, D_MODEL = TINY["heads"], TINY["d_model"] // TINY["heads"], TINY["d_model"]
+
+
+def test_kv_cache_state_allocation():                            # tests/test_kv_cache.jl:12-27
+    cache = WG.KVCacheState(BATCH, 1, HEADS, HEAD_DIM, ENC_SEQ, max_seq=MAX_SEQ)
+    assert cache.step_pos == 0 and cache.max_seq == MAX_SEQ
+    assert len(cache.self_cache) == 1 and len(cache.cross_cache) == 1
+    sk, sv = cache.self_cache[0]
+    assert sk.shape == (BATCH, HEADS, MAX_SEQ, HEAD_DIM) and not sk.any() and sv.shape == sk.shape
+    ck, cv = cache.cross_cache[0]
+    assert ck.shape == (BATCH, HEADS, ENC_SEQ, HEAD_DIM) and cv.shape == ck.shape
+
+
+def tiny_decoder(g, reg, layers=None):
+    return WG.TextDecoder(g, reg, d_model=D_MODEL, heads=HEADS, layers=layers or TINY["dec_layers"], ffn=TINY["ffn"], vocab=TINY["vocab"],
+                          max_positions=TINY["max_positions"])
+
+
+def test_incremental_decode_graph_structure():                   # tests/test_kv_cache.jl:29-53
+    g = G.Graph()
+    idg = WG.build_decode_step(tiny_decoder(g, {}), g, ENC_SEQ, 0, max_seq=MAX_SEQ, batch=BATCH)
+    assert idg.token_input_id > 0 and idg.logits_id > 0 and idg.step_pos == 0
+    assert len(idg.cross_k_ids) == len(idg.self_k_ids) == len(idg.new_self_k_ids) == TINY["dec_layers"]
+    assert g.shapes[idg.logits_id - 1] == (BATCH, 1, TINY["vocab"])
+
+
+@pytest.mark.parametrize("step_pos", [0, 1, 3])
+def test_kv_scatter_places_the_slot(step_pos):                   # tests/test_kv_cache.jl:55-72
+    g = G.Graph()
+    past, new = G.tensor(g, [1, 1, 4, 2]), G.tensor(g, [1, 1, 1, 2])
+    upd = WG._kv_scatter(past, new, step_pos)
+    assert upd.shape[2] == 4                                     # @test realized_dims(updated.shape)[3] == 4
+    p = np.arange(8, dtype=np.float32).reshape(1, 1, 4, 2) + 1
+    n = np.array([-1, -2], np.float32).reshape(1, 1, 1, 2)
+    (res,) = eval_graph(g, {past.id: p, new.id: n}, [upd.id])
+    want = p.copy()
+    want[0, 0, step_pos] = n[0, 0, 0]
+    assert np.array_equal(res, want)
+
+
+def test_cached_attention_graph_shapes():                        # tests/test_kv_cache.jl:74-115
+    g, reg = G.Graph(), {}
+    sa = WG.WhisperSelfAttention(D_MODEL, HEADS, g, reg, "test.attn")
+    x = G.tensor(g, [BATCH, 1, D_MODEL])
+    past_k, past_v = (G.tensor(g, [BATCH, HEADS, MAX_SEQ, HEAD_DIM]) for _ in range(2))
+    out, new_k, new_v = WG.whisper_self_attn_cached(sa, x, 0, past_k, past_v)
+    assert all(isinstance(t, G.GraphTensor) for t in (out, new_k, new_v))
+    assert out.shape == (BATCH, 1, D_MODEL)
+    assert new_k.shape[2] == MAX_SEQ and new_k.shape[3] == HEAD_DIM and new_v.shape == new_k.shape
+    ca = WG.WhisperCrossAttention(D_MODEL, HEADS, g, reg, "test.cross_attn")
+    enc_k, enc_v = (G.tensor(g, [BATCH, HEADS, ENC_SEQ, HEAD_DIM]) for _ in range(2))
+    assert WG.whisper_cross_attn_cached(ca, x, enc_k, enc_v).shape == (BATCH, 1, D_MODEL)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("compiled", [False, True])
+def test_decode_step_host_loop(lib_built, device, compiled):
+    """decode_step! (src/Whisper.jl:760-801) over TEST_STEPS positions, through execute() and through compile(): one
+    graph per position, the cache's self K/V replaced by each step's outputs; the logits against the oracle's cached
+    decoder and, at the last step, against the un-cached TextDecoder over the whole prefix."""
+    cfg = dict(TINY, dec_layers=1, vocab=2048)
+    w = W.synth_weights(cfg, seed=8)
+    enc_out = O.synth_normal(8, 900, (BATCH, ENC_SEQ, D_MODEL), 1.0)
+    cross = W.project_cross_kv(enc_out, w, cfg)
+    ref = W.CachedDecoder(w, cfg, BATCH, cross)
+    cache = WG.KVCacheState(BATCH, 1, HEADS, HEAD_DIM, ENC_SEQ, max_seq=MAX_SEQ)
+    tok = np.array([[3.0]], np.float32)
+    fed = []
+    for step in range(STEPS):
+        g, reg = G.Graph(), {}
+        td = WG.TextDecoder(g, reg, d_model=D_MODEL, heads=HEADS, layers=1, ffn=cfg["ffn"], vocab=cfg["vocab"], max_positions=cfg["max_positions"])
+        idg = WG.build_decode_step(td, g, ENC_SEQ, step, max_seq=MAX_SEQ, batch=BATCH)
+        for name, t in reg.items():
+            g.tensors[(t.id, 1)] = w[name]                       # load_weights!, src/Weights.jl:60-91
+        assert cache.step_pos == step
+        logits = WG.decode_step(L.compile(g, device) if compiled else g, idg, cache, tok, cross, device)
+        fed.append(int(tok[0, 0]))
+        want = ref.step(np.array([fed[-1]]))
+        assert logits.shape == (BATCH, 1, cfg["vocab"])
+        assert close(logits[:, 0], want)
+        tok = np.array([[float(np.argmax(want[0]))]], np.float32)
+    assert cache.step_pos == STEPS
+    full = W.decoder_full(np.array([fed]), enc_out, w, cfg)
+    assert close(logits[:, 0], full[:, -1], 1e-3)
