@@ -330,6 +330,62 @@ def encode_cross_kv(device, weights, mel, *, d_model, heads, enc_layers, dec_lay
     return res[enc.id], [(res[k.id], res[v.id]) for k, v in kv]
 
 
+def greedy_decode(weights, enc_output, sot_sequence, eot_id, *, d_model, heads, layers, ffn, vocab, max_positions=448,
+                  max_len=448, dtype="f32", device=None):
+    """greedy_decode of src/Decoding.jl:33-136 on the cached session.  The tokenizer stays with the caller: it gives
+    `sot_sequence` (the start-of-transcript ids, Decoding.jl:89) and `eot_id`, and turns the returned ids into text.
+
+    As in the reference, the cross K/V are projected once from `enc_output` [batch, enc_seq, d_model] (Decoding.jl:
+    52-78), the self cache starts zeroed at max_positions slots, and the loop feeds only the LAST id of the start
+    sequence at position len(sot_sequence) - 1 (Decoding.jl:92, 112): the earlier start ids never enter the cache, whose
+    first slots stay zero rows that the attention still reads.  Each step takes the argmax, the loop ends after the
+    step that produced eot_id, after max_len steps, or when the position reaches max_positions - 1 (Decoding.jl:93-95,
+    126-129).  What the reference does with one compiled graph per position runs here as one device-resident loop.
+
+    Returns one id list per sequence (the start sequence included, ending with eot_id if it was produced)."""
+    from .device import get_device
+    from .execution import execute
+    from .session import Session, WhisperDecoderModel
+    dev = device or get_device()
+    enc_output = np.asarray(enc_output, dtype=F32)
+    batch, enc_seq, _ = enc_output.shape
+    start = [int(t) for t in sot_sequence]
+    assert start, "greedy_decode: empty start sequence"
+    g, reg = G.Graph(), {}
+    enc_in = G.tensor(g, enc_output.shape)
+    kv = project_cross_kv(g, reg, enc_in, d_model=d_model, heads=heads, layers=layers)
+    inputs = {t.id: weights[name] for name, t in reg.items()}
+    inputs[enc_in.id] = enc_output
+    res = execute(g, [t.id for pair in kv for t in pair], inputs, dev)
+    pos = len(start) - 1
+    steps = min(int(max_len), (max_positions - 1) - pos)
+    if steps <= 0:
+        return [list(start) for _ in range(batch)]
+    model = WhisperDecoderModel(dev, d_model=d_model, heads=heads, layers=layers, ffn=ffn, vocab=vocab, max_positions=max_positions,
+                                cross_len=enc_seq, dtype=dtype)
+    sess = None
+    try:
+        for name, a in weights.items():
+            if name.startswith("model.decoder."):
+                model.set_weight(name, a)
+        sess = Session(model, batch, max_positions - 1)
+        for i, (k, v) in enumerate(kv):
+            sess.set_cross_kv(i, res[k.id], res[v.id])
+        sess.set_position(pos)
+        out = sess.decode_until(np.full(batch, start[-1], np.int32), steps, int(eot_id))      # [steps done, batch]
+    finally:
+        if sess is not None:
+            sess.close()
+        model.close()
+    ids = []
+    for b in range(batch):
+        seq = [int(t) for t in out[:, b]]
+        if int(eot_id) in seq:
+            seq = seq[:seq.index(int(eot_id)) + 1]
+        ids.append(start + seq)
+    return ids
+
+
 class FusedEncoder:
     """AudioEncoder + project_cross_kv on the tensor cores (bf16): the fused counterpart of
     encode_cross_kv.  Weights by the reference's registry names; names it does not use are skipped."""
@@ -412,5 +468,5 @@ def registry_shapes(*, d_model, heads, enc_layers, dec_layers, ffn, vocab, n_mel
 
 
 __all__ = ["registry_shapes", "FusedEncoder", "AudioEncoder", "Conv1D", "WhisperSelfAttention", "EncoderTransformerBlock", "sinusoids", "project_cross_kv",
-           "encode_cross_kv", "WhisperCrossAttention", "DecoderTransformerBlock", "TextDecoder", "KVCacheState", "decode_step", "build_decode_step",
+           "encode_cross_kv", "WhisperCrossAttention", "DecoderTransformerBlock", "TextDecoder", "KVCacheState", "decode_step", "greedy_decode", "build_decode_step",
            "IncrementalDecodeGraph", "whisper_self_attn_cached", "whisper_cross_attn_cached"]

@@ -276,3 +276,83 @@ def test_decode_step_host_loop(lib_built, device, compiled):
     assert cache.step_pos == STEPS
     full = W.decoder_full(np.array([fed]), enc_out, w, cfg)
     assert close(logits[:, 0], full[:, -1], 1e-3)
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# tests/test_greedy_decode.jl: the greedy loop of src/Decoding.jl:33-136 (the tokenizer replaced by its ids)
+# ----------------------------------------------------------------------------------------------------------------
+TEST_CFG = W.CONFIGS["whisper_test"]
+SOT_SEQUENCE = [301, 302, 303, 304]        # stand-ins for <|startoftranscript|><|en|><|transcribe|><|notimestamps|>
+
+
+def reference_loop(w, cfg, enc_out, start, eot, max_len):
+    """The loop of src/Decoding.jl:91-130 on the oracle's cached decoder: only the last start id is fed, at position
+    len(start) - 1, over a zeroed cache."""
+    ref = W.CachedDecoder(w, cfg, enc_out.shape[0], W.project_cross_kv(enc_out, w, cfg))
+    tokens = list(start)
+    for _ in range(max_len):
+        pos = len(tokens) - 1
+        if pos >= cfg["max_positions"] - 1:
+            break
+        ref.pos = pos
+        tokens.append(int(np.argmax(ref.step(np.array([tokens[-1]]))[0])))
+        if tokens[-1] == eot:
+            break
+    return tokens
+
+
+def test_greedy_loop_start_matches_the_step_graphs():
+    """The loop's first steps graph by graph (build_decode_step! at position len(start) - 1 over zeroed self K/V,
+    evaluated with the oracle's primitives) against the cached oracle started at that position."""
+    cfg, batch, enc_seq = TEST_CFG, 1, 8
+    w = W.synth_weights(cfg, seed=12)
+    enc_out = O.synth_normal(12, 900, (batch, enc_seq, cfg["d_model"]), 1.0)
+    cross = W.project_cross_kv(enc_out, w, cfg)
+    want = reference_loop(w, cfg, enc_out, SOT_SEQUENCE, -1, 3)
+    H, D = cfg["heads"], cfg["d_model"] // cfg["heads"]
+    cache = WG.KVCacheState(batch, cfg["dec_layers"], H, D, enc_seq, max_seq=cfg["max_positions"])
+    tokens = list(SOT_SEQUENCE)
+    for _ in range(3):
+        pos = len(tokens) - 1
+        g, reg = G.Graph(), {}
+        td = WG.TextDecoder(g, reg, d_model=cfg["d_model"], heads=H, layers=cfg["dec_layers"], ffn=cfg["ffn"], vocab=cfg["vocab"],
+                            max_positions=cfg["max_positions"])
+        idg = WG.build_decode_step(td, g, enc_seq, pos, batch=batch)
+        inputs = {t.id: w[name] for name, t in reg.items()}
+        inputs[idg.token_input_id] = np.array([[tokens[-1]]], np.float32)
+        for l in range(cfg["dec_layers"]):
+            inputs[idg.cross_k_ids[l]], inputs[idg.cross_v_ids[l]] = cross[l]
+            inputs[idg.self_k_ids[l]], inputs[idg.self_v_ids[l]] = cache.self_cache[l]
+        out = eval_graph(g, inputs, [idg.logits_id] + idg.new_self_k_ids + idg.new_self_v_ids)
+        L_ = cfg["dec_layers"]
+        cache.self_cache = list(zip(out[1:1 + L_], out[1 + L_:]))
+        tokens.append(int(np.argmax(out[0][0, 0])))
+    assert tokens == want
+
+
+@pytest.mark.gpu
+def test_greedy_decode_flow(lib_built, device):
+    cfg, enc_seq = TEST_CFG, 8
+    w = W.synth_weights(cfg, seed=12)
+    enc_out = O.synth_normal(12, 900, (1, enc_seq, cfg["d_model"]), 1.0)
+    kw = dict(d_model=cfg["d_model"], heads=cfg["heads"], layers=cfg["dec_layers"], ffn=cfg["ffn"], vocab=cfg["vocab"],
+              max_positions=cfg["max_positions"], device=device)
+    longest = reference_loop(w, cfg, enc_out, SOT_SEQUENCE, -1, 1000)
+    never = next(i for i in range(cfg["vocab"]) if i not in longest)          # an end-of-text id nobody produces
+    # "Using a very small max_len for speed": max_len 5
+    (ids,) = WG.greedy_decode(w, enc_out, SOT_SEQUENCE, never, max_len=5, **kw)
+    assert len(ids) > 0 and ids[0] == SOT_SEQUENCE[0]            # tests/test_greedy_decode.jl:88-89
+    assert ids == longest[:len(SOT_SEQUENCE) + 5]
+    # the end-of-text exit: the loop stops with the step that produced it
+    eot = longest[len(SOT_SEQUENCE) + 6]
+    stop = longest.index(eot, len(SOT_SEQUENCE)) + 1
+    (ids,) = WG.greedy_decode(w, enc_out, SOT_SEQUENCE, eot, max_len=12, **kw)
+    assert ids == longest[:stop] == reference_loop(w, cfg, enc_out, SOT_SEQUENCE, eot, 12)
+    # the position cap: the loop ends when the position reaches max_positions - 1
+    (ids,) = WG.greedy_decode(w, enc_out, SOT_SEQUENCE, never, max_len=1000, **kw)
+    assert len(longest) == cfg["max_positions"] and ids == longest
+    # a batch: every sequence runs the same loop on its own encoder output
+    enc2 = O.synth_normal(13, 900, (2, enc_seq, cfg["d_model"]), 1.0)
+    both = WG.greedy_decode(w, enc2, SOT_SEQUENCE, never, max_len=6, **kw)
+    for b in range(2):
+        assert both[b] == reference_loop(w, cfg, enc2[b:b + 1], SOT_SEQUENCE, never, 6)
