@@ -280,6 +280,11 @@ int32_t lmb200_model_missing_weights(lmb200_model model, char* names_out, int64_
 int32_t lmb200_model_init_random(lmb200_model model, uint64_t seed, float sigma);
 int32_t lmb200_model_weight_bytes(lmb200_model model, int64_t* bytes);
 
+/* A session: `batch` sequences with a preallocated cache of max_ctx positions each (the cache the reference lacks for
+ * Llama, examples/llama.jl:39-99, and keeps per graph for Whisper, src/Whisper.jl:519-541).  The model's forward takes
+ * any batch (src/NN.jl:448-455): up to 32 sequences share one pass over the weights; a larger batch (Llama / Phi-3, one
+ * GPU) runs as sub-sessions of at most 32 sequences, one weight pass each, behind the same handle and entry points.
+ * Not offered above 32: lmb200_session_kv_layer, lmb200_decode_attention_splitkv, lmb200_decode_n_device. */
 int32_t lmb200_session_create(lmb200_model model, int32_t batch, int32_t max_ctx,
                               lmb200_session* session);
 int32_t lmb200_session_destroy(lmb200_session session);

@@ -9,7 +9,7 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libluminal_b200.so")
-SOURCES = ["api.cu", "gemv.cu", "attention.cu", "model.cu", "prims.cu", "flash.cu", "flash_tc.cu", "flash_tc_f32.cu", "prefill.cu", "whisper_enc.cu", "noalloc.cu", "match.cu"]
+SOURCES = ["api.cu", "gemv.cu", "attention.cu", "model.cu", "prims.cu", "flash.cu", "flash_tc.cu", "flash_tc_f32.cu", "prefill.cu", "whisper_enc.cu", "noalloc.cu", "match.cu", "wide.cu"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
               "-Xcompiler", "-fPIC"]
 

@@ -1877,8 +1877,9 @@ extern "C" int32_t lmb200_session_create(lmb200_model hm, int32_t batch, int32_t
   Model* M = model_from(hm);
   if (!M) return LMB200_EINVAL;
   LMB_REQUIRE(out, "session_create: null argument");
-  LMB_REQUIRE(batch >= 1 && batch <= 32, "session_create: batch %d outside 1..32", batch);
+  LMB_REQUIRE(batch >= 1, "session_create: batch %d", batch);
   LMB_REQUIRE(max_ctx >= 1, "session_create: max_ctx %d", max_ctx);
+  if (batch > 32) return wide_create(M, batch, max_ctx, out);
   Ctx* ctx = M->ctx;
   LMB_CUDA(cudaSetDevice(ctx->device));
   const lmb200_model_config& c = M->cfg;
@@ -2002,6 +2003,7 @@ extern "C" int32_t lmb200_session_create(lmb200_model hm, int32_t batch, int32_t
 extern "C" int32_t lmb200_session_destroy(lmb200_session h) {
   Session* S = session_from(h);
   if (!S) return LMB200_EINVAL;
+  if (!S->parts.empty()) return wide_destroy(S);
   cudaSetDevice(S->m->ctx->device);
   cudaStreamSynchronize(S->m->ctx->stream);
   drop_graphs(S);
@@ -2019,6 +2021,7 @@ extern "C" int32_t lmb200_session_destroy(lmb200_session h) {
 extern "C" int32_t lmb200_session_reset(lmb200_session h) {
   Session* S = session_from(h);
   if (!S) return LMB200_EINVAL;
+  if (!S->parts.empty()) return wide_reset(S);
   Ctx* ctx = S->m->ctx;
   LMB_CUDA(cudaSetDevice(ctx->device));
   LMB_CUDA(cudaMemsetAsync(S->step_ctr, 0, 4, ctx->stream));
@@ -2028,6 +2031,7 @@ extern "C" int32_t lmb200_session_reset(lmb200_session h) {
 extern "C" int32_t lmb200_session_position(lmb200_session h, int32_t* pos) {
   Session* S = session_from(h);
   if (!S || !pos) return LMB200_EINVAL;
+  if (!S->parts.empty()) return wide_position(S, pos);
   *pos = S->host_pos;
   return LMB200_OK;
 }
@@ -2036,6 +2040,7 @@ extern "C" int32_t lmb200_session_set_position(lmb200_session h, int32_t pos) {
   Session* S = session_from(h);
   if (!S) return LMB200_EINVAL;
   LMB_REQUIRE(pos >= 0 && pos <= S->max_ctx, "set_position: %d outside 0..%d", pos, S->max_ctx);
+  if (!S->parts.empty()) return wide_set_position(S, pos);
   Ctx* ctx = S->m->ctx;
   LMB_CUDA(cudaSetDevice(ctx->device));
   return set_all_positions(S, pos);
@@ -2045,6 +2050,7 @@ extern "C" int32_t lmb200_session_set_positions(lmb200_session h, const int32_t*
   Session* S = session_from(h);
   if (!S) return LMB200_EINVAL;
   LMB_REQUIRE(pos, "set_positions: null argument");
+  if (!S->parts.empty()) return wide_set_positions(S, pos);
   for (int b = 0; b < S->B; ++b)
     LMB_REQUIRE(pos[b] >= 0 && pos[b] <= S->max_ctx, "set_positions: sequence %d at %d, outside 0..%d", b, pos[b], S->max_ctx);
   LMB_CUDA(cudaSetDevice(S->m->ctx->device));
@@ -2055,6 +2061,7 @@ extern "C" int32_t lmb200_session_set_positions(lmb200_session h, const int32_t*
 extern "C" int32_t lmb200_session_positions(lmb200_session h, int32_t* pos_out) {
   Session* S = session_from(h);
   if (!S || !pos_out) return LMB200_EINVAL;
+  if (!S->parts.empty()) return wide_positions(S, pos_out);
   for (int b = 0; b < S->B; ++b) pos_out[b] = S->host_pos_v[b];
   return LMB200_OK;
 }
@@ -2099,6 +2106,7 @@ extern "C" int32_t lmb200_session_set_cross_kv(lmb200_session h, int32_t layer, 
 extern "C" int32_t lmb200_session_fill_kv_random(lmb200_session h, int32_t n_pos, uint64_t seed) {
   Session* S = session_from(h);
   if (!S) return LMB200_EINVAL;
+  if (!S->parts.empty()) return wide_fill_kv_random(S, n_pos, seed);
   Model* M = S->m;
   Ctx* ctx = M->ctx;
   LMB_REQUIRE(n_pos >= 0 && n_pos <= S->max_ctx, "fill_kv_random: n_pos %d outside 0..%d", n_pos, S->max_ctx);
@@ -2126,6 +2134,7 @@ extern "C" int32_t lmb200_session_fill_kv_random(lmb200_session h, int32_t n_pos
 extern "C" int32_t lmb200_session_set_capture(lmb200_session h, int32_t enable) {
   Session* S = session_from(h);
   if (!S) return LMB200_EINVAL;
+  if (!S->parts.empty()) return wide_set_capture(S, enable);
   Ctx* ctx = S->m->ctx;
   LMB_CUDA(cudaSetDevice(ctx->device));
   if (enable && !S->capture)
@@ -2141,6 +2150,7 @@ extern "C" int32_t lmb200_session_set_capture(lmb200_session h, int32_t enable) 
 extern "C" int32_t lmb200_session_read_layer_output(lmb200_session h, int32_t layer, float* host) {
   Session* S = session_from(h);
   if (!S) return LMB200_EINVAL;
+  if (!S->parts.empty()) return wide_read_layer_output(S, layer, host);
   LMB_REQUIRE(S->capture && host, "read_layer_output: capture is not enabled");
   LMB_REQUIRE(layer >= 0 && layer < S->m->cfg.n_layers, "read_layer_output: layer %d", layer);
   Ctx* ctx = S->m->ctx;
@@ -2172,6 +2182,7 @@ extern "C" int32_t lmb200_prefill(lmb200_session h, const int32_t* tokens, int32
   Session* S = session_from(h);
   if (!S) return LMB200_EINVAL;
   LMB_REQUIRE(tokens && n >= 1, "prefill: null tokens or n < 1");
+  if (!S->parts.empty()) return wide_prefill(S, tokens, n, logits_out);
   LMB_REQUIRE(!S->ragged, "prefill: the sequences are at different positions; use lmb200_prefill_ragged");
   LMB_TRY(tp_guard(S, "prefill"));
   if (S->host_pos + n > S->max_ctx)
@@ -2223,6 +2234,7 @@ extern "C" int32_t lmb200_prefill_ragged(lmb200_session h, const int32_t* tokens
   Session* S = session_from(h);
   if (!S) return LMB200_EINVAL;
   LMB_REQUIRE(tokens && lengths && n_max >= 1, "prefill_ragged: null argument or n_max < 1");
+  if (!S->parts.empty()) return wide_prefill_ragged(S, tokens, lengths, n_max, logits_out);
   LMB_TRY(tp_guard(S, "prefill_ragged"));
   const int B = S->B;
   int longest = 0;
@@ -2317,6 +2329,7 @@ extern "C" int32_t lmb200_decode_step(lmb200_session h, const int32_t* tokens_in
   Session* S = session_from(h);
   if (!S) return LMB200_EINVAL;
   LMB_REQUIRE(tokens_in, "decode_step: null tokens");
+  if (!S->parts.empty()) return wide_decode_step(S, tokens_in, next_tokens_out, logits_out);
   LMB_TRY(tp_guard(S, "decode_step"));
   if (S->host_pos + 1 > S->max_ctx)
     return fail(LMB200_ESTATE, "decode_step: position %d is past max_ctx %d", S->host_pos, S->max_ctx);
@@ -2350,6 +2363,7 @@ static int32_t decode_n_common(Session* S, const int32_t* first, bool first_on_d
 extern "C" int32_t lmb200_decode_n(lmb200_session h, const int32_t* first_tokens, int32_t n_steps, int32_t* tokens_out) {
   Session* S = session_from(h);
   if (!S) return LMB200_EINVAL;
+  if (!S->parts.empty()) return wide_decode_n(S, first_tokens, n_steps, tokens_out);
   LMB_TRY(decode_n_common(S, first_tokens, false, n_steps));
   Ctx* ctx = S->m->ctx;
   if (tokens_out)
@@ -2367,6 +2381,7 @@ extern "C" int32_t lmb200_decode_until(lmb200_session h, const int32_t* first_to
   Session* S = session_from(h);
   if (!S) return LMB200_EINVAL;
   LMB_REQUIRE(steps_done && max_steps >= 1, "decode_until: bad argument");
+  if (!S->parts.empty()) return wide_decode_until(S, first_tokens, max_steps, eot_token, tokens_out, steps_done);
   LMB_REQUIRE(eot_token >= 0 && eot_token < S->m->cfg.vocab, "decode_until: end-of-text id %d outside the vocabulary", eot_token);
   LMB_TRY(tp_guard(S, "decode_until"));
   Ctx* ctx = S->m->ctx;
@@ -2423,6 +2438,7 @@ extern "C" int32_t lmb200_decode_until(lmb200_session h, const int32_t* first_to
 extern "C" int32_t lmb200_decode_n_device(lmb200_session h, const int32_t* first_dptr, int32_t n_steps, int32_t* out_dptr) {
   Session* S = session_from(h);
   if (!S) return LMB200_EINVAL;
+  LMB_REQUIRE(S->parts.empty(), "decode_n_device: not built for a session of more than 32 sequences");
   LMB_TRY(decode_n_common(S, first_dptr, true, n_steps));
   Ctx* ctx = S->m->ctx;
   if (out_dptr)
@@ -2433,6 +2449,7 @@ extern "C" int32_t lmb200_decode_n_device(lmb200_session h, const int32_t* first
 extern "C" int32_t lmb200_session_step_bytes(lmb200_session h, int32_t T, int64_t* bytes) {
   Session* S = session_from(h);
   if (!S || !bytes) return LMB200_EINVAL;
+  if (!S->parts.empty()) return wide_step_bytes(S, T, bytes);
   Model* M = S->m;
   const lmb200_model_config& c = M->cfg;
   const int64_t e = M->esz;
@@ -2574,6 +2591,7 @@ extern "C" int32_t lmb200_session_kv_layer(lmb200_session h, int32_t layer, void
   Session* S = session_from(h);
   if (!S) return LMB200_EINVAL;
   LMB_REQUIRE(kv_dptr && batch_stride && head_stride, "session_kv_layer: null argument");
+  LMB_REQUIRE(S->parts.empty(), "session_kv_layer: a session of more than 32 sequences has one cache per 32 sequences");
   LMB_REQUIRE(layer >= 0 && layer < S->m->cfg.n_layers, "session_kv_layer: layer %d", layer);
   *kv_dptr = reinterpret_cast<char*>(S->kv) + (int64_t)layer * S->kv_layer_stride * S->m->esz;
   *batch_stride = S->kv_batch_stride;
@@ -2587,6 +2605,7 @@ extern "C" int32_t lmb200_decode_attention_splitkv(lmb200_session h, int32_t lay
   if (!S) return LMB200_EINVAL;
   Model* M = S->m;
   LMB_REQUIRE(q_dptr && out_dptr, "decode_attention: null pointer");
+  LMB_REQUIRE(S->parts.empty(), "decode_attention: not built for a session of more than 32 sequences");
   LMB_REQUIRE(layer >= 0 && layer < M->cfg.n_layers, "decode_attention: layer %d", layer);
   LMB_REQUIRE(T >= 1 && T <= S->max_ctx, "decode_attention: T %d outside 1..%d", T, S->max_ctx);
   Ctx* ctx = M->ctx;

@@ -143,7 +143,28 @@ struct Session {
   cudaGraphExec_t graph_tok = nullptr;    // sliced head, tokens only (head_sliced)
   cudaStream_t graph_stream = nullptr;
   int graph_nodes_full = 0, graph_nodes_body = 0, graph_nodes_tok = 0;
+  // a batch above 32: this session owns nothing on the device, it is a row of sub-sessions of at most 32 sequences
+  std::vector<uint64_t> parts;
 };
+
+// the entry points of a session of more than 32 sequences (csrc/wide.cu): each runs the sub-sessions in turn
+int32_t wide_create(Model* M, int batch, int max_ctx, lmb200_session* out);
+int32_t wide_destroy(Session* S);
+int32_t wide_reset(Session* S);
+int32_t wide_position(Session* S, int32_t* pos);
+int32_t wide_set_position(Session* S, int32_t pos);
+int32_t wide_set_positions(Session* S, const int32_t* pos);
+int32_t wide_positions(Session* S, int32_t* pos_out);
+int32_t wide_fill_kv_random(Session* S, int32_t n_pos, uint64_t seed);
+int32_t wide_set_capture(Session* S, int32_t enable);
+int32_t wide_read_layer_output(Session* S, int32_t layer, float* host);
+int32_t wide_prefill(Session* S, const int32_t* tokens, int32_t n, float* logits_out);
+int32_t wide_prefill_ragged(Session* S, const int32_t* tokens, const int32_t* lengths, int32_t n_max, float* logits_out);
+int32_t wide_decode_step(Session* S, const int32_t* tokens_in, int32_t* next_tokens_out, float* logits_out);
+int32_t wide_decode_n(Session* S, const int32_t* first_tokens, int32_t n_steps, int32_t* tokens_out);
+int32_t wide_decode_until(Session* S, const int32_t* first_tokens, int32_t max_steps, int32_t eot_token, int32_t* tokens_out,
+                          int32_t* steps_done);
+int32_t wide_step_bytes(Session* S, int32_t T, int64_t* bytes);
 
 int32_t step_kernels_configure();
 // prompt phase as GEMMs + flash attention (csrc/prefill.cu)

@@ -118,7 +118,7 @@ def test_decode_past_max_ctx_is_an_error(lib_built, device):
     with pytest.raises(L.LuminalB200Error):
         sess.decode_step(np.zeros(1, dtype=np.int32))
     with pytest.raises(L.LuminalB200Error):
-        L.Session(model, 33, 8)          # batch above the GEMV tile limit
+        L.Session(model, 0, 8)
     sess.close(); model.close()
 
 
