@@ -77,6 +77,18 @@ int32_t lmb200_set_stream(lmb200_ctx ctx, void* cuda_stream);
 int32_t lmb200_sync(lmb200_ctx ctx);
 /* number of kernels this context has launched so far (graph replays count their nodes) */
 int32_t lmb200_launch_count(lmb200_ctx ctx, int64_t* count);
+/* Recording a sequence of op-level calls into a CUDA graph and replaying it: what execute_with_capture is for
+ * (src/Device.jl:106-121; the reference's CUDA method runs f() uncaptured, CompiledGraph keeps the `cache` it would
+ * fill, src/Compiler.jl:75-100).  Between capture_begin and capture_end the primitive, fused and flash-attention entry
+ * points on device tensors record their launches instead of running them (same pointers on every replay: the caller
+ * keeps those buffers alive and unchanged in place); calls that copy to or from the host, allocate, free, wait, or
+ * belong to a model or session are refused with an error and leave the device untouched.  capture_end returns the
+ * instantiated graph, or an error if something recorded cannot be replayed; graph_launch enqueues one replay on the
+ * context's stream. */
+int32_t lmb200_capture_begin(lmb200_ctx ctx);
+int32_t lmb200_capture_end(lmb200_ctx ctx, uint64_t* graph_out);
+int32_t lmb200_graph_launch(lmb200_ctx ctx, uint64_t graph);
+int32_t lmb200_graph_destroy(lmb200_ctx ctx, uint64_t graph);
 
 /* Tensor-parallel communicator: one rank per process, NCCL over NVLink.  Not in the reference
  * (single device only, README.md:150-158); defined by the multi-GPU row of the hot-path scope.

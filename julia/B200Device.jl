@@ -90,6 +90,28 @@ function Luminal.from_device(a::B200Array{N}) where {N}
     out
 end
 
+# execute_with_capture (src/Device.jl:106-121; CompiledGraph hands it its steps and its cache, src/Compiler.jl:91-98):
+# the first call runs f() as it is and then records it into a CUDA graph, every later call is one replay of
+# cache[:cuda_exec].  If f() makes a call that cannot be recorded, cache[:cuda_exec] is `nothing` and f() keeps running
+# call by call.
+function Luminal.execute_with_capture(d::B200Device, f, cache::Dict)
+    g = get(cache, :cuda_exec, nothing)
+    if g !== nothing
+        check(ccall((:lmb200_graph_launch, LIB), Int32, (UInt64, UInt64), d.ctx, g))
+        return
+    end
+    f()
+    haskey(cache, :cuda_exec) && return
+    check(ccall((:lmb200_capture_begin, LIB), Int32, (UInt64,), d.ctx))
+    h = Ref{UInt64}(0)
+    recorded = try f(); true catch; false end
+    rc = ccall((:lmb200_capture_end, LIB), Int32, (UInt64, Ref{UInt64}), d.ctx, h)
+    cache[:cuda_exec] = (recorded && rc == 0) ? h[] : nothing
+    if !recorded && rc == 0
+        check(ccall((:lmb200_graph_destroy, LIB), Int32, (UInt64, UInt64), d.ctx, h[]))
+    end
+end
+
 # ---------------------------------------------------------------------------------------------
 # execute_op!: one method per op type (src/Execution.jl:274-371, 481-618), selected by the array type
 # ---------------------------------------------------------------------------------------------

@@ -47,6 +47,10 @@ SIGNATURES = {
     "lmb200_set_stream": [_u64, _vp],
     "lmb200_sync": [_u64],
     "lmb200_launch_count": [_u64, _pi64],
+    "lmb200_capture_begin": [_u64],
+    "lmb200_capture_end": [_u64, C.POINTER(_u64)],
+    "lmb200_graph_launch": [_u64, _u64],
+    "lmb200_graph_destroy": [_u64, _u64],
     "lmb200_comm_unique_id": [C.POINTER(C.c_uint8)],
     "lmb200_comm_init": [_u64, _i32, _i32, C.POINTER(C.c_uint8)],
     "lmb200_comm_destroy": [_u64],

@@ -218,9 +218,12 @@ class CompiledGraph:
     buffers indexed by node id, as the reference does.  Nodes that vanished into a fused step have no
     buffer (the reference leaves theirs at zero)."""
 
-    def __init__(self, graph, device=None, fuse=True):
+    def __init__(self, graph, device=None, fuse=True, capture=True):
         self.graph, self.dev = graph, device or get_device()
         self.results, self.steps = {}, []
+        # execute_with_capture's cache (src/Compiler.jl:75-79, 97): after the first call "cuda_exec" holds the CUDA
+        # graph of the steps, and every later call is one replay; capture=False runs the steps call by call
+        self.cache, self.capture = {}, bool(capture)
         plan = plan_graph(graph, fuse)
         for nid, what in plan:                       # buffers first: a step may read a constant planned after it
             self.results[nid] = self.dev.empty(graph.shapes[nid - 1])
@@ -243,7 +246,6 @@ class CompiledGraph:
 
     # -- execution -------------------------------------------------------------------------------
     def __call__(self, inputs, device=None):
-        from .execution import run_op
         for node_id, data in inputs.items():
             buf = self.results[node_id]
             a = np.ascontiguousarray(np.asarray(data, dtype=np.float32))
@@ -251,6 +253,16 @@ class CompiledGraph:
                 raise ValueError(f"Input size mismatch for node {node_id}: expected {buf.size}, got {a.size}")
             _lib.call("lmb200_upload", self.dev.handle, C.c_void_p(buf.ptr), _lib.F32, a.ctypes.data_as(C.c_void_p),
                       len(buf.shape), _lib.dims(buf.shape), 0)
+        if self.capture:
+            from .device import execute_with_capture
+            execute_with_capture(self.dev, self.run_steps, self.cache)
+        else:
+            self.run_steps()
+        return self.results
+
+    def run_steps(self):
+        """The steps, one library call each, on the device's stream."""
+        from .execution import run_op
         h = self.dev.handle
         R = self.results
         for what, out in self.steps:
@@ -272,6 +284,11 @@ class CompiledGraph:
     def kernel_count(self):
         """Kernels one call launches (the input uploads aside)."""
         return len(self.steps)
+
+    def close(self):
+        g = self.cache.pop("cuda_exec", None)
+        if g is not None:
+            self.dev.graph_destroy(g)
 
 
 class _Planner:
@@ -411,8 +428,8 @@ def run_fused(dev, code, out, ins):
               len(code), ops, args)
 
 
-def compile(graph, device=None, fuse=True):     # noqa: A001  (the reference's name)
-    return CompiledGraph(graph, device, fuse)
+def compile(graph, device=None, fuse=True, capture=True):     # noqa: A001  (the reference's name)
+    return CompiledGraph(graph, device, fuse, capture)
 
 
 __all__ = ["compile", "CompiledGraph", "plan_graph", "fusible_intermediates", "group_program", "is_elementwise", "run_fused"]

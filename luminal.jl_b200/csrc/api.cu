@@ -344,6 +344,7 @@ extern "C" int32_t lmb200_shutdown(lmb200_ctx h) {
   cudaFreeHost(c->dev_err);
   cudaFree(c->dev_broken);
   cudaFree(c->scratch);
+  for (void* p : c->retired_scratch) cudaFree(p);
   c->magic = 0;
   delete c;
   return LMB200_OK;
@@ -359,9 +360,98 @@ extern "C" int32_t lmb200_set_stream(lmb200_ctx h, void* stream) {
 extern "C" int32_t lmb200_sync(lmb200_ctx h) {
   Ctx* c = ctx_from(h);
   if (!c) return LMB200_EINVAL;
+  LMB_REQUIRE(!c->capturing, "sync: not between capture_begin and capture_end");
   LMB_CUDA(cudaSetDevice(c->device));
   LMB_CUDA(cudaStreamSynchronize(c->stream));
   return check_device_error(c);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Capture of a sequence of op-level calls into a CUDA graph (execute_with_capture, src/Device.jl:106-121)
+// ---------------------------------------------------------------------------------------------
+namespace {
+struct HostGraph {
+  uint32_t magic = 0x47525048;
+  Ctx* ctx = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  int64_t nodes = 0;                 // kernels one replay launches
+};
+HostGraph* graph_from(uint64_t h) {
+  HostGraph* g = reinterpret_cast<HostGraph*>(h);
+  if (!g || g->magic != 0x47525048) { set_error("invalid graph handle"); return nullptr; }
+  return g;
+}
+}  // namespace
+
+extern "C" int32_t lmb200_capture_begin(lmb200_ctx h) {
+  Ctx* c = ctx_from(h);
+  if (!c) return LMB200_EINVAL;
+  if (c->capturing) return fail(LMB200_ESTATE, "capture_begin: a capture is already open on this context");
+  LMB_CUDA(cudaSetDevice(c->device));
+  LMB_CUDA(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
+  c->capturing = true;
+  c->capture_launches0 = c->launches;
+  return LMB200_OK;
+}
+
+extern "C" int32_t lmb200_capture_end(lmb200_ctx h, uint64_t* graph_out) {
+  Ctx* c = ctx_from(h);
+  if (!c) return LMB200_EINVAL;
+  if (!c->capturing) return fail(LMB200_ESTATE, "capture_end: no capture is open on this context");
+  cudaSetDevice(c->device);
+  cudaGraph_t g = nullptr;
+  const cudaError_t e = cudaStreamEndCapture(c->stream, &g);
+  c->capturing = false;
+  const int64_t nodes = c->launches - c->capture_launches0;
+  c->launches = c->capture_launches0;                      // recorded, not run
+  if (e != cudaSuccess || !g) {
+    cudaGetLastError();
+    if (g) cudaGraphDestroy(g);
+    return fail(LMB200_ECUDA, "capture_end: the recorded calls cannot be replayed (%s)", cudaGetErrorString(e));
+  }
+  if (!graph_out) { cudaGraphDestroy(g); return fail(LMB200_EINVAL, "capture_end: null argument"); }
+  HostGraph* G = new HostGraph();
+  G->ctx = c; G->nodes = nodes;
+  const cudaError_t ei = cudaGraphInstantiate(&G->exec, g, 0);
+  cudaGraphDestroy(g);
+  if (ei != cudaSuccess) {
+    cudaGetLastError();
+    delete G;
+    return fail(LMB200_ECUDA, "capture_end: cudaGraphInstantiate failed (%s)", cudaGetErrorString(ei));
+  }
+  c->live_graphs++;
+  *graph_out = reinterpret_cast<uint64_t>(G);
+  return LMB200_OK;
+}
+
+extern "C" int32_t lmb200_graph_launch(lmb200_ctx h, uint64_t graph) {
+  Ctx* c = ctx_from(h);
+  HostGraph* G = graph_from(graph);
+  if (!c || !G) return LMB200_EINVAL;
+  LMB_REQUIRE(G->ctx == c, "graph_launch: the graph belongs to another context");
+  LMB_REQUIRE(!c->capturing, "graph_launch: not between capture_begin and capture_end");
+  LMB_CUDA(cudaSetDevice(c->device));
+  LMB_CUDA(cudaGraphLaunch(G->exec, c->stream));
+  c->launches += G->nodes;
+  return LMB200_OK;
+}
+
+extern "C" int32_t lmb200_graph_destroy(lmb200_ctx h, uint64_t graph) {
+  Ctx* c = ctx_from(h);
+  HostGraph* G = graph_from(graph);
+  if (!c || !G) return LMB200_EINVAL;
+  cudaSetDevice(c->device);
+  cudaStreamSynchronize(c->stream);
+  cudaGraphExecDestroy(G->exec);
+  G->magic = 0;
+  delete G;
+  if (--c->live_graphs <= 0) {                 // nothing can replay a read of the retired scratch blocks any more
+    c->live_graphs = 0;
+    for (void* p : c->retired_scratch) cudaFree(p);
+    c->retired_scratch.clear();
+    c->scratch_in_graph = false;
+  }
+  return LMB200_OK;
 }
 
 extern "C" int32_t lmb200_launch_count(lmb200_ctx h, int64_t* count) {
@@ -462,6 +552,7 @@ extern "C" int32_t lmb200_allreduce_sum_f32(lmb200_ctx h, void* dptr, int64_t co
 extern "C" int32_t lmb200_alloc(lmb200_ctx h, int64_t bytes, void** out) {
   Ctx* c = ctx_from(h);
   if (!c) return LMB200_EINVAL;
+  LMB_REQUIRE(!c->capturing, "alloc: not between capture_begin and capture_end");
   LMB_REQUIRE(out && bytes >= 0, "alloc: bad argument");
   LMB_CUDA(cudaSetDevice(c->device));
   void* p = nullptr;
@@ -477,6 +568,7 @@ extern "C" int32_t lmb200_alloc(lmb200_ctx h, int64_t bytes, void** out) {
 extern "C" int32_t lmb200_free(lmb200_ctx h, void* dptr) {
   Ctx* c = ctx_from(h);
   if (!c) return LMB200_EINVAL;
+  LMB_REQUIRE(!c->capturing, "free: not between capture_begin and capture_end");
   LMB_CUDA(cudaSetDevice(c->device));
   LMB_CUDA(cudaStreamSynchronize(c->stream));
   LMB_CUDA(cudaFree(dptr));
@@ -500,6 +592,7 @@ extern "C" int32_t lmb200_upload(lmb200_ctx h, void* dptr, int32_t dtype, const 
                                  const int64_t* dims, int32_t layout) {
   Ctx* c = ctx_from(h);
   if (!c) return LMB200_EINVAL;
+  LMB_REQUIRE(!c->capturing, "upload: not between capture_begin and capture_end");
   LMB_REQUIRE(dptr && host, "upload: null pointer");
   LMB_REQUIRE(dtype == LMB200_F32 || dtype == LMB200_BF16, "upload: dtype %d", dtype);
   Shape8 s;
@@ -534,6 +627,7 @@ extern "C" int32_t lmb200_download(lmb200_ctx h, float* host, const void* dptr, 
                                    const int64_t* dims, int32_t layout) {
   Ctx* c = ctx_from(h);
   if (!c) return LMB200_EINVAL;
+  LMB_REQUIRE(!c->capturing, "download: not between capture_begin and capture_end");
   LMB_REQUIRE(dptr && host, "download: null pointer");
   LMB_REQUIRE(dtype == LMB200_F32 || dtype == LMB200_BF16, "download: dtype %d", dtype);
   Shape8 s;

@@ -68,6 +68,13 @@ struct Ctx {
   // request and stays until shutdown, so that a call neither allocates nor waits for the device
   void* scratch = nullptr;
   size_t scratch_bytes = 0;
+  // lmb200_capture_begin .. lmb200_capture_end: the op-level launches of this context are recorded into a CUDA graph
+  // instead of run; calls that copy to or from the host, allocate, free or wait are refused meanwhile
+  bool capturing = false;
+  int64_t capture_launches0 = 0;
+  bool scratch_in_graph = false;   // a recorded graph reads `scratch`: when it must grow, the old block is retired, not freed
+  std::vector<void*> retired_scratch;   // blocks recorded graphs may still read; freed with the last graph or at shutdown
+  int live_graphs = 0;
 };
 
 // Region layout (bytes): two 4 MiB buffers read by the peers (the norm kernels' all-reduce), two 4 MiB

@@ -353,9 +353,17 @@ int32_t flash_tc_f32_launch(Ctx* ctx, float* out, const float* q, const float* k
   LMB_REQUIRE(n % 4 == 0, "flash attention: element count must be a multiple of 4");
   const size_t need = (size_t)n * 2 * 3 * sizeof(__nv_bfloat16);
   if (ctx->scratch_bytes < need) {
+    if (ctx->capturing)
+      return fail(LMB200_ESTATE, "flash attention: the scratch must grow to %lld bytes, which a capture cannot record: run the call once before capture_begin",
+                  (long long)need);
     // work queued on the stream may still use the smaller block
     LMB_CUDA(cudaStreamSynchronize(ctx->stream));
-    cudaFree(ctx->scratch);
+    if (ctx->scratch_in_graph) {                // a recorded graph reads it on every replay: keep it
+      ctx->retired_scratch.push_back(ctx->scratch);
+      ctx->scratch_in_graph = false;
+    } else {
+      cudaFree(ctx->scratch);
+    }
     ctx->scratch = nullptr;
     ctx->scratch_bytes = 0;
     if (cudaMalloc(&ctx->scratch, need) != cudaSuccess) {
@@ -364,6 +372,7 @@ int32_t flash_tc_f32_launch(Ctx* ctx, float* out, const float* q, const float* k
     }
     ctx->scratch_bytes = need;
   }
+  if (ctx->capturing) ctx->scratch_in_graph = true;
   __nv_bfloat16* hl = reinterpret_cast<__nv_bfloat16*>(ctx->scratch);
   __nv_bfloat16 *qhl = hl, *khl = hl + 2 * n, *vhl = hl + 4 * n;
   const unsigned grid1 = (unsigned)std::min<int64_t>(ceil_div(n / 4, 256), 148 * 16);

@@ -726,11 +726,13 @@ int32_t step_kernels_configure() {
 Model* model_from(lmb200_model h) {
   Model* m = reinterpret_cast<Model*>(h);
   if (!m || m->magic != 0x4D4F444C) { set_error("invalid model handle"); return nullptr; }
+  if (m->ctx && m->ctx->capturing) { set_error("model and session calls cannot be recorded between capture_begin and capture_end"); return nullptr; }
   return m;
 }
 Session* session_from(lmb200_session h) {
   Session* s = reinterpret_cast<Session*>(h);
   if (!s || s->magic != 0x53455353) { set_error("invalid session handle"); return nullptr; }
+  if (s->m && s->m->ctx && s->m->ctx->capturing) { set_error("model and session calls cannot be recorded between capture_begin and capture_end"); return nullptr; }
   return s;
 }
 

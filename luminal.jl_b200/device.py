@@ -80,6 +80,30 @@ class B200Device:
                   a.ndim, _lib.dims(a.shape), layout)
         return out
 
+    # CUDA-graph capture of op-level calls
+    def capture(self, f):
+        """Records the op-level calls f() makes into a CUDA graph (nothing runs) and returns its handle."""
+        _lib.call("lmb200_capture_begin", self.handle)
+        h = C.c_uint64(0)
+        try:
+            f()
+        except BaseException:
+            try:
+                _lib.call("lmb200_capture_end", self.handle, C.byref(h))
+            except _lib.LuminalB200Error:
+                pass
+            else:
+                _lib.call("lmb200_graph_destroy", self.handle, h)
+            raise
+        _lib.call("lmb200_capture_end", self.handle, C.byref(h))
+        return h
+
+    def graph_launch(self, graph):
+        _lib.call("lmb200_graph_launch", self.handle, graph)
+
+    def graph_destroy(self, graph):
+        _lib.call("lmb200_graph_destroy", self.handle, graph)
+
     # tensor-parallel communicator (one rank per process)
     @staticmethod
     def comm_unique_id():
@@ -134,5 +158,23 @@ def from_device(data):
     return data.numpy() if isinstance(data, DeviceArray) else data
 
 
-__all__ = ["B200Device", "DeviceArray", "get_device", "to_device", "from_device", "device_count",
+def execute_with_capture(device, f, cache):
+    """execute_with_capture(device, f, cache) of src/Device.jl:106-121: runs f() on the device; "if supported, it
+    captures the execution into a graph stored in cache and replays it on subsequent calls".  The first call runs f()
+    as it is (kernels that size a scratch buffer on first use do so here) and then records it; every later call is one
+    replay of cache["cuda_exec"].  If f() makes a call that cannot be recorded, cache["cuda_exec"] is None, the reason
+    is kept in cache["cuda_exec_error"], and f() keeps running call by call."""
+    graph = cache.get("cuda_exec")
+    if graph is not None:
+        device.graph_launch(graph)
+        return
+    f()
+    if "cuda_exec" not in cache:
+        try:
+            cache["cuda_exec"] = device.capture(f)
+        except _lib.LuminalB200Error as e:
+            cache["cuda_exec"], cache["cuda_exec_error"] = None, str(e)
+
+
+__all__ = ["B200Device", "DeviceArray", "get_device", "to_device", "from_device", "execute_with_capture", "device_count",
            "LuminalB200Error", "F32", "BF16", "ROWMAJOR", "COLMAJOR"]

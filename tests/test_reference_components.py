@@ -356,3 +356,85 @@ def test_greedy_decode_flow(lib_built, device):
     both = WG.greedy_decode(w, enc2, SOT_SEQUENCE, never, max_len=6, **kw)
     for b in range(2):
         assert both[b] == reference_loop(w, cfg, enc2[b:b + 1], SOT_SEQUENCE, never, 6)
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# tests/test_compilation.jl: compile(), the captured CUDA graph in the compiled graph's cache, replays
+# ----------------------------------------------------------------------------------------------------------------
+@pytest.mark.gpu
+def test_graph_compilation_and_capture(lib_built, device):
+    rng = np.random.default_rng(0)
+    g = G.Graph()
+    a, b = G.tensor(g, [3, 3]), G.tensor(g, [3, 3])
+    c = a + b
+    exec_fn = L.compile(g, device)
+    a_val, b_val = rng.random((3, 3), np.float32), rng.random((3, 3), np.float32)
+    assert np.allclose(exec_fn({a.id: a_val, b.id: b_val}, device)[c.id].numpy(), a_val + b_val)
+    assert exec_fn.cache.get("cuda_exec") is not None            # @test haskey(exec_fn.cache, :cuda_exec)
+    # every later call is one replay of that graph, on the new inputs
+    before = device.launch_count()
+    a2, b2 = rng.random((3, 3), np.float32), rng.random((3, 3), np.float32)
+    assert np.allclose(exec_fn({a.id: a2, b.id: b2}, device)[c.id].numpy(), a2 + b2)
+    assert device.launch_count() - before == exec_fn.kernel_count() == 1
+    exec_fn.close()
+    # Mul + Add + ReLU
+    g2 = G.Graph()
+    x, w, bias = (G.tensor(g2, [2, 2]) for _ in range(3))
+    z = G.relu((x * w) + bias)
+    exec_fn2 = L.compile(g2, device)
+    for _ in range(3):
+        xv, wv, bv = rng.random((2, 2), np.float32), rng.random((2, 2), np.float32), rng.random((2, 2), np.float32) - 0.5
+        got = exec_fn2({x.id: xv, w.id: wv, bias.id: bv}, device)[z.id].numpy()
+        assert np.allclose(got, np.maximum(xv * wv + bv, 0))
+    exec_fn2.close()
+
+
+@pytest.mark.gpu
+def test_captured_llama_graph_replays_on_new_tokens(lib_built, device):
+    """The 2-layer Llama of tests/test_llama_compiled.jl: the first call runs step by step, the later ones replay the
+    recorded graph; each against execute() on the same inputs, and against an uncaptured compile()."""
+    g, out_id, inputs, _, shape = case_llama()
+    tok_id = next(i for i, v in inputs.items() if v.shape == (1, 8))
+    cg, plain = L.compile(g, device), L.compile(g, device, capture=False)
+    for seed in range(3):
+        inputs[tok_id] = O.synth_tokens(40 + seed, 900, (1, 8), 1000).astype(np.float32)
+        want = L.execute(g, out_id, inputs, device)
+        got = cg(inputs)[out_id].numpy()
+        assert got.shape == shape and np.array_equal(got, plain(inputs)[out_id].numpy())
+        assert close(got, want)
+        assert cg.cache.get("cuda_exec") is not None and "cuda_exec" not in plain.cache
+    cg.close()
+
+
+@pytest.mark.gpu
+def test_capture_with_flash_attention_and_refused_calls(lib_built, device):
+    """A graph with the float32 FlashAttentionOp (its scratch is sized by the first, unrecorded call) replays; calls
+    that cannot be recorded are refused with an error during a capture and the context works on afterwards."""
+    g = G.Graph()
+    q, k, v = (G.tensor(g, [1, 2, 128, 64]) for _ in range(3))
+    out = G.flash_attention(q, k, v, causal=True) * np.float32(2.0)
+    cg = L.compile(g, device)
+    for seed in range(3):
+        vals = {t.id: O.synth_normal(50 + seed, t.id, t.shape, 1.0) for t in (q, k, v)}
+        want = 2.0 * O.flash_attn_fast(vals[q.id], vals[k.id], vals[v.id], 1.0 / 8.0, True)
+        assert np.abs(cg(vals)[out.id].numpy() - want).max() <= 1e-3
+    assert cg.cache.get("cuda_exec") is not None
+    # a larger call makes the scratch grow while the recorded graph still reads the old block: both keep working
+    g2 = G.Graph()
+    q2, k2, v2 = (G.tensor(g2, [1, 2, 256, 64]) for _ in range(3))
+    out2 = G.flash_attention(q2, k2, v2, causal=False)
+    vals2 = {t.id: O.synth_normal(60, t.id, t.shape, 1.0) for t in (q2, k2, v2)}
+    want2 = O.flash_attn_fast(vals2[q2.id], vals2[k2.id], vals2[v2.id], 1.0 / 8.0, False)
+    assert np.abs(L.execute(g2, out2.id, vals2, device) - want2).max() <= 1e-3
+    assert np.abs(cg(vals)[out.id].numpy() - want).max() <= 1e-3
+    cg.close()
+
+    def bad():
+        device.upload(np.zeros(4, np.float32))                   # a host copy: cannot be recorded
+    with pytest.raises(L.LuminalB200Error):
+        device.capture(bad)
+    cache = {}
+    L.device.execute_with_capture(device, bad, cache)            # runs it, then finds it cannot be recorded
+    assert cache["cuda_exec"] is None and "capture" in cache["cuda_exec_error"]
+    x = device.upload(np.arange(6, dtype=np.float32))
+    assert np.array_equal(x.numpy(), np.arange(6, dtype=np.float32))
