@@ -438,3 +438,23 @@ def test_capture_with_flash_attention_and_refused_calls(lib_built, device):
     assert cache["cuda_exec"] is None and "capture" in cache["cuda_exec_error"]
     x = device.upload(np.arange(6, dtype=np.float32))
     assert np.array_equal(x.numpy(), np.arange(6, dtype=np.float32))
+    # a session call inside a recording is refused too, and the session is usable afterwards
+    cfg = O.CONFIGS["tiny_gqa128"]
+    model = L.Model(device, n_layers=cfg["n_layers"], hidden=cfg["hidden"], n_heads=cfg["n_heads"], n_kv_heads=cfg["n_kv_heads"],
+                    intermediate=cfg["intermediate"], vocab=cfg["vocab"], eps=cfg["eps"], rope_base=cfg["rope_base"], dtype="f32")
+    model.init_random(1, 0.02)
+    sess = L.Session(model, 1, 8)
+    with pytest.raises(L.LuminalB200Error, match="cannot be recorded"):
+        device.capture(lambda: sess.decode_step(np.zeros(1, np.int32)))
+    assert sess.position() == 0
+    sess.decode_step(np.zeros(1, np.int32))
+    assert sess.position() == 1
+    sess.close(); model.close()
+    # misuse of the entry points is an error, not a fault
+    import ctypes as C
+    from luminal_jl_b200 import _lib
+    h = C.c_uint64(0)
+    with pytest.raises(L.LuminalB200Error, match="no capture is open"):
+        _lib.call("lmb200_capture_end", device.handle, C.byref(h))
+    with pytest.raises(L.LuminalB200Error, match="invalid graph handle"):
+        _lib.call("lmb200_graph_launch", device.handle, C.c_uint64(0))
