@@ -190,3 +190,38 @@ def test_plans_evaluate_to_the_same_values_on_the_host(lib_built):
     for fuse in (False, True):
         got = eval_plan(g, L.compiler.plan_graph(g, fuse), inputs)[out.id]
         assert np.abs(got - ref).max() <= 1e-5, fuse
+
+
+def test_execute_with_capture_host_logic():
+    """execute_with_capture's bookkeeping (src/Device.jl:106-121) against a stand-in device: the first call runs f()
+    and records it, later calls only replay; a recording that fails leaves f() running call by call."""
+    from luminal_jl_b200 import _lib
+    from luminal_jl_b200.device import execute_with_capture
+
+    class FakeDevice:
+        def __init__(self, fail=False):
+            self.fail, self.recorded, self.replays = fail, 0, 0
+
+        def capture(self, f):
+            if self.fail:
+                raise _lib.LuminalB200Error(-5, "upload: not between capture_begin and capture_end")
+            f()
+            self.recorded += 1
+            return 7
+
+        def graph_launch(self, graph):
+            assert graph == 7
+            self.replays += 1
+
+    runs = []
+    dev, cache = FakeDevice(), {}
+    for _ in range(4):
+        execute_with_capture(dev, lambda: runs.append(1), cache)
+    assert cache["cuda_exec"] == 7 and dev.recorded == 1 and dev.replays == 3
+    assert len(runs) == 2                         # once for real, once while recording
+    runs.clear()
+    dev, cache = FakeDevice(fail=True), {}
+    for _ in range(3):
+        execute_with_capture(dev, lambda: runs.append(1), cache)
+    assert cache["cuda_exec"] is None and "capture_begin" in cache["cuda_exec_error"]
+    assert len(runs) == 3 and dev.replays == 0
