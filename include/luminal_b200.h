@@ -436,6 +436,30 @@ int32_t lmb200_compile_node_list(lmb200_ctx ctx, const lmb200_node_list* list, i
                                  int32_t max_ctx, lmb200_model* model_out, lmb200_session* session_out,
                                  lmb200_decoder_match* info);
 
+/* The Whisper AudioEncoder's graph (src/Whisper.jl:354-404: the Conv1D stem of src/NN.jl:55-104 with GELU, the
+ * sinusoid table of src/Whisper.jl:208-231, pre-norm blocks of unmasked self attention and a GELU MLP, a final
+ * LayerNorm), ending in its output node. */
+typedef struct {
+  int32_t d_model, heads, layers, ffn, n_mels;
+  int32_t batch, frames;   /* the mel input the graph was traced for: [batch, n_mels, frames] */
+  int32_t mel_node;        /* the input node the mel enters through */
+  int32_t rates_node;      /* the input node holding the sinusoid rates exp(-log(10000) / (d_model/2 - 1) * i) */
+  int32_t n_weights;       /* 6 + 15 * layers */
+  float eps;               /* LayerNorm epsilon */
+} lmb200_encoder_match;
+/* Recognises that graph.  No GPU is needed.  weight_nodes / names_out as for lmb200_match_decoder, with the
+ * model.encoder.* registry names; a graph that deviates anywhere returns LMB200_ENOMATCH naming the node. */
+int32_t lmb200_match_whisper_encoder(const lmb200_node_list* list, int32_t output_id, lmb200_encoder_match* info,
+                                     int32_t* weight_nodes, int32_t weight_capacity, char* names_out,
+                                     int64_t names_capacity);
+/* compile() for it: matches, creates the tensor-core encoder (lmb200_whisper_encoder_create with no decoder layers) and
+ * sets every weight from node_data[node - 1] (host float32 in `layout`).  The sinusoid rates the graph holds must be
+ * sinusoids()'s and the epsilon 1e-5, which the fused encoder has built in; lmb200_whisper_encoder_run then takes a mel
+ * of any batch and length.  Replaces running the ~280 nodes of that graph one kernel each (src/Compiler.jl:181-364). */
+int32_t lmb200_compile_encoder_node_list(lmb200_ctx ctx, const lmb200_node_list* list, int32_t output_id,
+                                         const float* const* node_data, int32_t layout,
+                                         lmb200_whisper_encoder* encoder_out, lmb200_encoder_match* info);
+
 /* Stand-alone split-KV decode attention over a cache in the session layout (tests, profiling),
  * asynchronous on the context's stream (lmb200_sync before reading the result).
  * q: [batch, n_heads_local, head_dim] in the session dtype (device); out: same shape.

@@ -368,8 +368,8 @@ node_args(op::Luminal.Unfold) = Float64[op.kernel_shape; op.stride_shape; op.dil
 node_args(op::Luminal.Constant) = Float64[op.value]
 node_args(op::Luminal.FlashAttentionOp) = Float64[op.scale, op.causal]
 
-function compile_b200(d::B200Device, graph::Luminal.Graph, output_id::Integer; dtype::Integer=F32, batch::Integer=0,
-                      max_ctx::Integer=2048)
+# Graph.nodes and graph.tensors as the arrays lmb200_node_list and node_data point into; the caller keeps the result alive
+function flatten(graph::Luminal.Graph)
     n = length(graph.nodes)
     op = Int32[node_code(nd.op) for nd in graph.nodes]
     in_off = Int32[0]; in_node = Int32[]; shape_off = Int32[0]; shape = Int64[]; arg_off = Int32[0]; arg = Float64[]
@@ -384,8 +384,15 @@ function compile_b200(d::B200Device, graph::Luminal.Graph, output_id::Integer; d
         a isa Array{Float32} || continue
         push!(keep, a); data[id] = pointer(a)
     end
+    (n, op, in_off, in_node, shape_off, shape, arg_off, arg, data, keep)
+end
+
+function compile_b200(d::B200Device, graph::Luminal.Graph, output_id::Integer; dtype::Integer=F32, batch::Integer=0,
+                      max_ctx::Integer=2048)
+    flat = flatten(graph)
+    n, op, in_off, in_node, shape_off, shape, arg_off, arg, data, _ = flat
     model = Ref{UInt64}(0); session = Ref{UInt64}(0); info = Ref(DecoderMatch(0, 0, 0, 0, 0, 0, 0, 0))
-    GC.@preserve op in_off in_node shape_off shape arg_off arg keep begin
+    GC.@preserve flat begin
         nl = NodeList(n, 0, pointer(op), pointer(in_off), pointer(in_node), pointer(shape_off), pointer(shape),
                       pointer(arg_off), pointer(arg))
         check(ccall((:lmb200_compile_node_list, LIB), Int32,
@@ -396,6 +403,42 @@ function compile_b200(d::B200Device, graph::Luminal.Graph, output_id::Integer; d
     vocab = Luminal.realized_dims(graph.shapes[output_id])[end]
     Model(model[]), Session(session[], batch > 0 ? batch : info[].batch, vocab), info[]
 end
+
+# The Whisper AudioEncoder (src/Whisper.jl:354-404) on the tensor cores.  compile_encoder_b200 recognises its graph
+# (lmb200_compile_encoder_node_list; weights from graph.tensors as above) and returns the fused encoder; encode! runs a
+# mel (batch, n_mels, frames) of any batch and length through it, cross_kv! projects the last output to every decoder
+# layer's cross K/V inside a bf16 Whisper session (project_cross_kv, src/Whisper.jl:809-831, without the host).
+struct EncoderMatch                                 # lmb200_encoder_match
+    d_model::Int32; heads::Int32; layers::Int32; ffn::Int32; n_mels::Int32; batch::Int32; frames::Int32
+    mel_node::Int32; rates_node::Int32; n_weights::Int32; eps::Float32
+end
+struct Encoder
+    h::UInt64
+    d_model::Int
+end
+function compile_encoder_b200(d::B200Device, graph::Luminal.Graph, output_id::Integer)
+    flat = flatten(graph)
+    n, op, in_off, in_node, shape_off, shape, arg_off, arg, data, _ = flat
+    enc = Ref{UInt64}(0); info = Ref(EncoderMatch(0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0f0))
+    GC.@preserve flat begin
+        nl = NodeList(n, 0, pointer(op), pointer(in_off), pointer(in_node), pointer(shape_off), pointer(shape),
+                      pointer(arg_off), pointer(arg))
+        check(ccall((:lmb200_compile_encoder_node_list, LIB), Int32,
+                    (UInt64, Ref{NodeList}, Int32, Ptr{Ptr{Float32}}, Int32, Ref{UInt64}, Ref{EncoderMatch}),
+                    d.ctx, Ref(nl), output_id, data, COLMAJOR, enc, info))
+    end
+    Encoder(enc[], info[].d_model), info[]
+end
+function encode!(e::Encoder, mel::Array{Float32,3})
+    batch, n_mels, frames = size(mel)
+    rowmajor = permutedims(mel, (3, 2, 1))           # the entry takes the mel row-major: frames fastest
+    out = Array{Float32}(undef, e.d_model, (frames - 1) ÷ 2 + 1, batch)
+    check(ccall((:lmb200_whisper_encoder_run, LIB), Int32, (UInt64, Ptr{Float32}, Int32, Int32, Ptr{Float32}),
+                e.h, rowmajor, batch, frames, out))
+    permutedims(out, (3, 2, 1))                      # (batch, seq, d_model) as AudioEncoder returns it
+end
+cross_kv!(e::Encoder, s::Session) = check(ccall((:lmb200_whisper_encoder_cross_kv, LIB), Int32, (UInt64, UInt64), e.h, s.h))
+destroy!(e::Encoder) = check(ccall((:lmb200_whisper_encoder_destroy, LIB), Int32, (UInt64,), e.h))
 
 # tensor parallelism: one process per GPU; rank 0 creates the id, the launcher broadcasts the 128 bytes
 function comm_unique_id()

@@ -113,6 +113,8 @@ SIGNATURES = {
     "lmb200_session_step_bytes": [_u64, _i32, _pi64],
     "lmb200_match_decoder": [_vp, _i32, _vp, _vp, _pi32, _i32, C.c_char_p, _i64],
     "lmb200_match_whisper_step": [_vp, _i32, _vp, _vp, _pi32, _i32, C.c_char_p, _i64, _pi32, _i32],
+    "lmb200_match_whisper_encoder": [_vp, _i32, _vp, _pi32, _i32, C.c_char_p, _i64],
+    "lmb200_compile_encoder_node_list": [_u64, _vp, _i32, _vp, _i32, C.POINTER(_u64), _vp],
     "lmb200_compile_node_list": [_u64, _vp, _i32, _vp, _i32, _i32, _i32, _i32, C.POINTER(_u64), C.POINTER(_u64), _vp],
     "lmb200_decode_attention_splitkv": [_u64, _i32, _vp, _vp, _i32],
     "lmb200_session_kv_layer": [_u64, _i32, C.POINTER(_vp), _pi64, _pi64],

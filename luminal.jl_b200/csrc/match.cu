@@ -662,6 +662,221 @@ struct WhisperWalker : Walker {
   }
 };
 
+// ---- Whisper AudioEncoder (src/Whisper.jl:354-404) ---------------------------------------------------------------
+struct EncoderLayer {
+  int q_w = 0, q_b = 0, k_w = 0, v_w = 0, v_b = 0, o_w = 0, o_b = 0, n1_w = 0, n1_b = 0;
+  int fc1_w = 0, fc1_b = 0, fc2_w = 0, fc2_b = 0, n2_w = 0, n2_b = 0;
+  int64_t H = 0, D = 0, B = 0, S = 0;
+  double eps = 0;
+};
+
+struct ConvStem {
+  int w = 0, b = 0;
+  int64_t c_in = 0, c_out = 0, kernel = 0, stride = 0, pad = 0, len_in = 0, len_out = 0, B = 0;
+};
+
+struct EncoderWalker : WhisperWalker {
+  using WhisperWalker::WhisperWalker;
+
+  // permute[perm](reshape[B, S, H, D](Linear(x) [* scale])) -> the projection's parts
+  void seq_heads(int i, std::initializer_list<int64_t> perm, bool scaled, bool want_bias, int& x, int& w, int& b, int64_t& B,
+                 int64_t& S, int64_t& H, int64_t& D, double& scale) const {
+    i = sc(i);
+    if (!permute_is(i, perm)) fail(i, "the permute of the head split");
+    int rs = in(i, 0);
+    int lin = expect1(rs, LMB200_NODE_RESHAPE, "reshape to [batch, seq, heads, head_dim]");
+    Shape s = shape(rs);
+    if (s.size() != 4) fail(rs, "reshape to [batch, seq, heads, head_dim]");
+    B = s[0]; S = s[1]; H = s[2]; D = s[3];
+    scale = 1.0;
+    if (scaled) lin = with_const(lin, LMB200_NODE_MUL, "projection * head_dim^-0.25", scale);
+    linear_bias(lin, x, w, b);
+    if (want_bias != (b != 0)) fail(lin, want_bias ? "a projection with a bias" : "a projection without a bias");
+  }
+
+  // WhisperSelfAttention without a mask (src/Whisper.jl:253-276), from its out_proj -> the normalised input
+  int enc_attention(int at, EncoderLayer& L) const {
+    int ctx;
+    linear_bias(at, ctx, L.o_w, L.o_b);
+    if (!L.o_b) fail(at, "out_proj with a bias");
+    int pv = expect1(ctx, LMB200_NODE_RESHAPE, "reshape to [batch, seq, hidden]");
+    if (!permute_is(pv, {1, 3, 2, 4})) fail(pv, "permute [1,3,2,4] of the attention output");
+    int probs, v, q, kt;
+    expect2(in(pv, 0), LMB200_NODE_MATMUL, "probs x values", probs, v);
+    attn_probs(probs, q, kt);
+    int xq, xk, xv, nob;
+    int64_t B2, S2, H2, D2, B3, S3, H3, D3;
+    double sq, sk, sv;
+    seq_heads(q, {1, 3, 2, 4}, true, true, xq, L.q_w, L.q_b, L.B, L.S, L.H, L.D, sq);
+    seq_heads(kt, {1, 3, 4, 2}, true, false, xk, L.k_w, nob, B2, S2, H2, D2, sk);
+    seq_heads(v, {1, 3, 2, 4}, false, true, xv, L.v_w, L.v_b, B3, S3, H3, D3, sv);
+    if (!(xq == xk && xk == xv && L.H == H2 && L.H == H3 && L.D == D2 && L.D == D3 && L.S == S2 && L.S == S3 && L.B == B2 && L.B == B3 &&
+          sq == sk))
+      fail(at, "q, k and v projections of one tensor with one head split");
+    check_scale(q, sq, L.D);
+    return xq;
+  }
+
+  // EncoderTransformerBlock (src/Whisper.jl:343-352), from its output sum -> its input
+  int enc_layer(int i, EncoderLayer& L) const {
+    int x1, ff, x0, at;
+    expect2(i, LMB200_NODE_ADD, "residual + mlp", x1, ff);
+    int act, n2, xa, xb;
+    linear_bias(ff, act, L.fc2_w, L.fc2_b);
+    int h = gelu(act);
+    linear_bias(h, n2, L.fc1_w, L.fc1_b);
+    if (!(L.fc1_b && L.fc2_b)) fail(ff, "fc1 and fc2 with biases");
+    double e1, e2;
+    layernorm(n2, xa, L.n2_w, L.n2_b, e2);
+    if (xa != x1) fail(ff, "the MLP over the normalised residual");
+    expect2(x1, LMB200_NODE_ADD, "residual + self attention", x0, at);
+    int n1 = enc_attention(at, L);
+    layernorm(n1, xb, L.n1_w, L.n1_b, e1);
+    if (xb != x0 || e1 != e2) fail(i, "two pre-norm sub-layers over one residual stream, one epsilon");
+    L.eps = e1;
+    return x0;
+  }
+
+  // NN.Conv1D (src/NN.jl:55-104): pad, Unfold, permute, column-major merge of (channel, tap), MatMul with the
+  // [ch_out, ch_in * kernel] weight, permute back, + bias -> its input
+  int conv1d(int i, ConvStem& c) const {
+    int out, be;
+    expect2(i, LMB200_NODE_ADD, "conv output + bias", out, be);
+    c.b = skip(be, LMB200_NODE_EXPAND);
+    if (!(is_input(c.b) && shape(c.b).size() == 1)) fail(i, "a [ch_out] bias expanded over batch and length");
+    if (!permute_is(out, {1, 3, 2})) fail(out, "permute [1,3,2] back to [batch, ch_out, length]");
+    int merged;
+    linear(in(out, 0), merged, c.w);
+    int perm = expect1(merged, LMB200_NODE_RESHAPE, "reshape to [batch, length, ch_in * kernel]");
+    if (!permute_is(perm, {1, 3, 2, 4})) fail(perm, "permute [1,3,2,4] of the unfolded windows");
+    int unf = in(perm, 0);
+    auto ua = op(unf) == LMB200_NODE_UNFOLD ? iargs(unf) : std::vector<int64_t>();
+    if (!(n_in(unf) == 1 && ua.size() == 3 && ua[0] >= 1 && ua[1] >= 1 && ua[2] == 1)) fail(unf, "Unfold over the last dim, dilation 1");
+    c.kernel = ua[0];
+    c.stride = ua[1];
+    int src = in(unf, 0);
+    c.pad = 0;
+    if (op(src) == LMB200_NODE_PAD) {
+      auto pa = iargs(src);
+      if (!(pa.size() == 6 && pa[0] == 0 && pa[1] == 0 && pa[2] == 0 && pa[3] == 0 && pa[4] == pa[5] && pa[4] > 0))
+        fail(src, "the same padding on both ends of the last dim");
+      c.pad = pa[4];
+      src = in(src, 0);
+    }
+    Shape xs = shape(src), us = shape(unf), ws = shape(c.w);
+    if (xs.size() != 3 || us.size() != 4) fail(unf, "windows [batch, ch_in, length, kernel] of a [batch, ch_in, length] tensor");
+    c.B = xs[0]; c.c_in = xs[1]; c.len_in = xs[2]; c.len_out = us[2];
+    c.c_out = ws[0];
+    if (!(ws == Shape{c.c_out, c.c_in * c.kernel} && shape(c.b)[0] == c.c_out && us == Shape{c.B, c.c_in, c.len_out, c.kernel} &&
+          c.len_out == (c.len_in + 2 * c.pad - c.kernel) / c.stride + 1 && shape(merged) == Shape{c.B, c.len_out, c.c_in * c.kernel}))
+      fail(i, "a Conv1D with a [ch_out, ch_in * kernel] weight and a [ch_out] bias");
+    return src;
+  }
+
+  // sinusoids(channels, length) (src/Whisper.jl:208-231): concat(sin(t), cos(t), 2) with t = arange(length) x rates
+  void sinusoid_table(int i, int64_t length, int64_t channels, int& rates) const {
+    const int64_t half = channels / 2;
+    int pa, pb;
+    expect2(i, LMB200_NODE_ADD, "concat(sin(t), cos(t)) along dim 2", pa, pb);
+    int s = expect1(pa, LMB200_NODE_PAD, "sin(t) padded to the full width");
+    int c = expect1(pb, LMB200_NODE_PAD, "cos(t) padded to the full width");
+    if (iargs(pa) != std::vector<int64_t>{0, 0, 0, half} || iargs(pb) != std::vector<int64_t>{0, 0, half, 0})
+      fail(i, "two halves of " + std::to_string(half) + " columns each");
+    int t = expect1(s, LMB200_NODE_SIN, "sin(t)");
+    int shifted = expect1(c, LMB200_NODE_SIN, "cos as sin(pi/2 - t)");
+    double hp, m1;
+    int na = with_const(shifted, LMB200_NODE_ADD, "pi/2 - t", hp);
+    int t2 = with_const(na, LMB200_NODE_MUL, "t * -1", m1);
+    if (t2 != t || m1 != -1.0 || std::fabs(hp - M_PI / 2) > 1e-6) fail(c, "sin(pi/2 - t) of the same t");
+    int ea, eb;
+    expect2(t, LMB200_NODE_MUL, "positions x rates", ea, eb);
+    int ar = expect1(ea, LMB200_NODE_EXPAND, "positions as a column");
+    rates = expect1(eb, LMB200_NODE_EXPAND, "rates as a row");
+    if (!(arange(ar) == length && is_input(rates) && shape(rates) == Shape{half} && shape(i) == Shape{length, channels}))
+      fail(t, "arange(" + std::to_string(length) + ") x a [" + std::to_string(half) + "] input of rates");
+  }
+};
+
+void validate_list(const lmb200_node_list* g);
+
+struct EncoderMatch {
+  lmb200_encoder_match info{};
+  std::vector<std::pair<std::string, int>> weights;
+};
+
+// AudioEncoder(mel) (src/Whisper.jl:379-404) ending in its output node: layer_norm(block^L(permute(gelu(conv2(gelu(
+// conv1(mel))))) + sinusoids)).
+EncoderMatch match_whisper_encoder(const lmb200_node_list* g, int output_id) {
+  validate_list(g);
+  EncoderWalker w(*g);
+  if (output_id < 1 || output_id > g->n_nodes) no_match("no node %d", output_id);
+  int x, ln_w, ln_b;
+  double eps;
+  w.layernorm(output_id, x, ln_w, ln_b, eps);
+  std::vector<EncoderLayer> layers;
+  auto is_bottom = [&](int n) { return w.op(n) == LMB200_NODE_ADD && w.n_in(n) == 2 && w.permute_is(w.in(n, 0), {1, 3, 2}); };
+  while (!is_bottom(x)) {
+    if (w.op(x) != LMB200_NODE_ADD) w.fail(x, "an encoder layer's residual sum, or the conv stem + sinusoids");
+    EncoderLayer L;
+    x = w.enc_layer(x, L);
+    layers.push_back(L);
+  }
+  if (layers.empty()) no_match("no encoder layer between the conv stem and the final norm");
+  std::vector<EncoderLayer> ordered(layers.rbegin(), layers.rend());
+  const int table = w.expect1(w.in(x, 1), LMB200_NODE_EXPAND, "the sinusoid table expanded over the batch");
+  ConvStem c1, c2;
+  const int g2 = w.gelu(w.in(w.in(x, 0), 0));
+  const int g1 = w.gelu(w.conv1d(g2, c2));
+  const int mel = w.conv1d(g1, c1);
+  const EncoderLayer& f = ordered[0];
+  const int64_t d = f.H * f.D, ffn = w.shape(f.fc1_w)[0];
+  if (!w.is_input(mel)) w.fail(mel, "the mel input [batch, n_mels, frames]");
+  if (!(c1.kernel == 3 && c1.stride == 1 && c1.pad == 1 && c2.kernel == 3 && c2.stride == 2 && c2.pad == 1 && c1.c_out == d &&
+        c2.c_in == d && c2.c_out == d && c2.len_in == c1.len_out && c2.len_out == f.S && c1.B == f.B && c2.B == f.B))
+    w.fail(x, "the stem conv1 (kernel 3, stride 1, padding 1) and conv2 (kernel 3, stride 2, padding 1) into width " + std::to_string(d));
+  int rates;
+  w.sinusoid_table(table, f.S, d, rates);
+  for (size_t n = 0; n < ordered.size(); ++n) {
+    const EncoderLayer& p = ordered[n];
+    bool same = p.H == f.H && p.D == f.D && p.B == f.B && p.S == f.S && p.eps == eps;
+    for (int EncoderLayer::* r : {&EncoderLayer::q_w, &EncoderLayer::k_w, &EncoderLayer::v_w, &EncoderLayer::o_w})
+      same = same && w.shape(p.*r) == Shape{d, d};
+    same = same && w.shape(p.fc1_w) == Shape{ffn, d} && w.shape(p.fc2_w) == Shape{d, ffn};
+    if (!same) no_match("encoder layer %zu differs from layer 0 in its widths, head split, epsilon or sequence length", n);
+  }
+  if (w.shape(ln_w) != Shape{d}) w.fail(ln_w, "a final gain of length " + std::to_string(d));
+  EncoderMatch m;
+  m.weights = {{"model.encoder.conv1.weight", c1.w}, {"model.encoder.conv1.bias", c1.b}, {"model.encoder.conv2.weight", c2.w},
+               {"model.encoder.conv2.bias", c2.b}, {"model.encoder.layer_norm.weight", ln_w}, {"model.encoder.layer_norm.bias", ln_b}};
+  struct ERole { int EncoderLayer::* node; const char* name; };
+  static const ERole roles[] = {
+      {&EncoderLayer::q_w, "self_attn.q_proj.weight"}, {&EncoderLayer::q_b, "self_attn.q_proj.bias"},
+      {&EncoderLayer::k_w, "self_attn.k_proj.weight"}, {&EncoderLayer::v_w, "self_attn.v_proj.weight"},
+      {&EncoderLayer::v_b, "self_attn.v_proj.bias"}, {&EncoderLayer::o_w, "self_attn.out_proj.weight"},
+      {&EncoderLayer::o_b, "self_attn.out_proj.bias"}, {&EncoderLayer::n1_w, "self_attn_layer_norm.weight"},
+      {&EncoderLayer::n1_b, "self_attn_layer_norm.bias"}, {&EncoderLayer::fc1_w, "fc1.weight"}, {&EncoderLayer::fc1_b, "fc1.bias"},
+      {&EncoderLayer::fc2_w, "fc2.weight"}, {&EncoderLayer::fc2_b, "fc2.bias"}, {&EncoderLayer::n2_w, "final_layer_norm.weight"},
+      {&EncoderLayer::n2_b, "final_layer_norm.bias"}};
+  for (size_t n = 0; n < ordered.size(); ++n)
+    for (const ERole& r : roles)
+      m.weights.push_back({"model.encoder.layers." + std::to_string(n) + "." + r.name, ordered[n].*(r.node)});
+  std::set<int> distinct{mel, rates};
+  for (auto& kv : m.weights) distinct.insert(kv.second);
+  if (distinct.size() != m.weights.size() + 2) no_match("one input tensor plays two roles");
+  m.info.d_model = (int32_t)d;
+  m.info.heads = (int32_t)f.H;
+  m.info.layers = (int32_t)ordered.size();
+  m.info.ffn = (int32_t)ffn;
+  m.info.n_mels = (int32_t)c1.c_in;
+  m.info.batch = (int32_t)f.B;
+  m.info.frames = (int32_t)c1.len_in;
+  m.info.mel_node = mel;
+  m.info.rates_node = rates;
+  m.info.n_weights = (int32_t)m.weights.size();
+  m.info.eps = (float)eps;
+  return m;
+}
+
 struct Role {
   int Block::* node;
   const char* name;
@@ -920,6 +1135,63 @@ extern "C" int32_t lmb200_match_whisper_step(const lmb200_node_list* list, int32
   } catch (const std::exception& e) {
     return lmb::fail(LMB200_EINVAL, "node list: %s", e.what());
   }
+}
+
+extern "C" int32_t lmb200_match_whisper_encoder(const lmb200_node_list* list, int32_t output_id, lmb200_encoder_match* info,
+                                                int32_t* weight_nodes, int32_t weight_capacity, char* names_out,
+                                                int64_t names_capacity) {
+  try {
+    EncoderMatch m = match_whisper_encoder(list, output_id);
+    Match names;
+    names.weights = m.weights;
+    if (info) *info = m.info;
+    return report(names, nullptr, nullptr, weight_nodes, weight_capacity, names_out, names_capacity);
+  } catch (const NoMatch& e) {
+    return lmb::fail(LMB200_ENOMATCH, "%s", e.what.c_str());
+  } catch (const std::exception& e) {
+    return lmb::fail(LMB200_EINVAL, "node list: %s", e.what());
+  }
+}
+
+extern "C" int32_t lmb200_compile_encoder_node_list(lmb200_ctx ctx, const lmb200_node_list* list, int32_t output_id,
+                                                    const float* const* node_data, int32_t layout,
+                                                    lmb200_whisper_encoder* encoder_out, lmb200_encoder_match* info) {
+  LMB_REQUIRE(encoder_out && node_data, "lmb200_compile_encoder_node_list: null output or node_data");
+  EncoderMatch m;
+  try {
+    m = match_whisper_encoder(list, output_id);
+  } catch (const NoMatch& e) {
+    return lmb::fail(LMB200_ENOMATCH, "%s", e.what.c_str());
+  } catch (const std::exception& e) {
+    return lmb::fail(LMB200_EINVAL, "node list: %s", e.what());
+  }
+  for (auto& kv : m.weights)
+    if (!node_data[kv.second - 1]) return lmb::fail(LMB200_EINVAL, "%s (node %d) has no data", kv.first.c_str(), kv.second);
+  // the fused encoder computes the sinusoid table itself, at the reference's rates, and normalises with eps 1e-5:
+  // a graph with other constants is not the graph it stands for
+  const float* rates = node_data[m.info.rates_node - 1];
+  if (!rates) return lmb::fail(LMB200_EINVAL, "the sinusoid rates (node %d) have no data", m.info.rates_node);
+  const int half = m.info.d_model / 2;
+  const double inc = std::log(10000.0) / (half - 1);
+  for (int i = 0; i < half; ++i) {
+    const double want = std::exp(-inc * i);
+    if (std::fabs((double)rates[i] - want) > 1e-6 * want + 1e-12)
+      return lmb::fail(LMB200_ENOMATCH, "node %d: rate %d is %g, sinusoids() gives %g", m.info.rates_node, i, (double)rates[i], want);
+  }
+  if (std::fabs(m.info.eps - 1e-5f) > 1e-9f)
+    return lmb::fail(LMB200_ENOMATCH, "LayerNorm epsilon %g: the fused encoder is built for 1e-5", (double)m.info.eps);
+  lmb200_whisper_encoder enc = 0;
+  int32_t rc = lmb200_whisper_encoder_create(ctx, m.info.d_model, m.info.heads, m.info.layers, m.info.ffn, m.info.n_mels, 0, &enc);
+  if (rc != LMB200_OK) return rc;
+  Walker w(*list);
+  for (auto& kv : m.weights) {
+    Shape s = w.shape(kv.second);
+    rc = lmb200_whisper_encoder_set_weight(enc, kv.first.c_str(), node_data[kv.second - 1], (int32_t)s.size(), s.data(), layout);
+    if (rc != LMB200_OK) { lmb200_whisper_encoder_destroy(enc); return rc; }
+  }
+  *encoder_out = enc;
+  if (info) *info = m.info;
+  return LMB200_OK;
 }
 
 extern "C" int32_t lmb200_compile_node_list(lmb200_ctx ctx, const lmb200_node_list* list, int32_t output_id,

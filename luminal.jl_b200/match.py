@@ -251,6 +251,81 @@ def match_whisper_step(graph, logits_id: int) -> WhisperStepMatch:
                             self_k_ids=part(2), self_v_ids=part(3), new_self_k_ids=part(4), new_self_v_ids=part(5))
 
 
+class EncoderMatchInfo(C.Structure):
+    """lmb200_encoder_match"""
+    _fields_ = [(n, C.c_int32) for n in ("d_model", "heads", "layers", "ffn", "n_mels", "batch", "frames", "mel_node", "rates_node",
+                                         "n_weights")] + [("eps", C.c_float)]
+
+
+@dataclass
+class WhisperEncoderMatch:
+    """What the matcher found in an AudioEncoder graph (src/Whisper.jl:354-404).  `weights` maps the model.encoder.*
+    registry names to input node ids; `mel` is the node the mel enters through, `rates` the input holding the
+    sinusoid rates."""
+    d_model: int
+    heads: int
+    layers: int
+    ffn: int
+    n_mels: int
+    batch: int
+    frames: int
+    eps: float
+    mel: int
+    rates: int
+    weights: Dict[str, int] = field(default_factory=dict)
+
+
+def match_whisper_encoder(graph, output_id: int) -> WhisperEncoderMatch:
+    """Recognises the Whisper AudioEncoder ending in the node `output_id` -- lmb200_match_whisper_encoder; needs no
+    GPU.  Raises MatchError at the first node that does not fit."""
+    from . import _lib
+    nl = flatten_graph(graph)
+    info = EncoderMatchInfo()
+    cap = max(len(graph.nodes), 1)
+    nodes = (C.c_int32 * cap)()
+    names = C.create_string_buffer(64 * cap + 256)
+    try:
+        _lib.call("lmb200_match_whisper_encoder", C.byref(nl), int(output_id), C.byref(info), nodes, cap, names, len(names))
+    except _lib.LuminalB200Error as e:
+        _raise_match(e)
+    wnames = names.value.decode().split("\n")
+    return WhisperEncoderMatch(d_model=info.d_model, heads=info.heads, layers=info.layers, ffn=info.ffn, n_mels=info.n_mels,
+                               batch=info.batch, frames=info.frames, eps=float(info.eps), mel=info.mel_node, rates=info.rates_node,
+                               weights={n: int(nodes[k]) for k, n in enumerate(wnames)})
+
+
+def compile_encoder_b200(graph, output_id, inputs=None, device=None):
+    """compile() for an AudioEncoder graph (lmb200_compile_encoder_node_list): returns (whisper.FusedEncoder, match).
+    The weights come from `inputs` or from graph.tensors, as for compile_b200.  The encoder then takes a mel of any
+    batch and length (FusedEncoder.run), on the tensor cores, instead of one kernel per node of the graph."""
+    from . import _lib
+    from .device import DeviceArray, get_device
+    from .whisper import FusedEncoder
+    m = match_whisper_encoder(graph, output_id)
+    dev = device or get_device()
+    inputs = inputs or {}
+    host, data = [], (C.c_void_p * len(graph.nodes))()
+    for name, node_id in list(m.weights.items()) + [("the sinusoid rates", m.rates)]:
+        a = inputs.get(node_id)
+        if a is None:
+            a = graph.tensors.get((node_id, 1))
+        if a is None:
+            raise KeyError(f"{name} (node {node_id}) has no data")
+        a = np.ascontiguousarray(a.numpy() if isinstance(a, DeviceArray) else a, dtype=np.float32)
+        if a.shape != tuple(graph.shapes[node_id - 1]):
+            raise ValueError(f"node {node_id}: data of shape {a.shape}, node of shape {graph.shapes[node_id - 1]}")
+        host.append(a)
+        data[node_id - 1] = a.ctypes.data
+    nl = flatten_graph(graph)
+    handle, info = C.c_uint64(), EncoderMatchInfo()
+    try:
+        _lib.call("lmb200_compile_encoder_node_list", dev.handle, C.byref(nl), int(output_id), data, _lib.ROWMAJOR, C.byref(handle),
+                  C.byref(info))
+    except _lib.LuminalB200Error as e:
+        _raise_match(e)
+    return FusedEncoder.adopt(dev, handle.value, m.d_model), m
+
+
 def compile_b200(graph, output_id, inputs=None, device=None, max_ctx=2048, dtype="f32", batch=None):
     """compile() for a graph one of the matchers recognises (lmb200_compile_node_list): returns (Session, match).
     The weights come from `inputs` (node id -> array, as execute() takes them) or from data pre-loaded into
@@ -321,4 +396,4 @@ def compile_b200(graph, output_id, inputs=None, device=None, max_ctx=2048, dtype
 
 
 __all__ = ["MatchError", "DecoderMatch", "WhisperStepMatch", "NodeList", "export_graph", "import_graph", "flatten_graph",
-           "match_decoder", "match_whisper_step", "compile_b200"]
+           "match_decoder", "match_whisper_step", "compile_b200", "WhisperEncoderMatch", "match_whisper_encoder", "compile_encoder_b200"]

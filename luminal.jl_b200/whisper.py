@@ -399,6 +399,16 @@ class FusedEncoder:
         _lib.call("lmb200_whisper_encoder_create", device.handle, d_model, heads, enc_layers, ffn, n_mels, dec_layers, C.byref(h))
         self.handle = h
 
+    @classmethod
+    def adopt(cls, device, handle, d_model):
+        """Wraps an encoder handle the library created (lmb200_compile_encoder_node_list)."""
+        import ctypes as C
+        from . import _lib
+        self = cls.__new__(cls)
+        self._lib, self._C, self.device, self.d_model = _lib, C, device, int(d_model)
+        self.handle = C.c_uint64(int(handle))
+        return self
+
     def set_weights(self, weights):
         C = self._C
         used = []
