@@ -286,9 +286,17 @@ class CompiledGraph:
         return len(self.steps)
 
     def close(self):
+        """Drops the recorded CUDA graph (the buffers go with their DeviceArrays)."""
         g = self.cache.pop("cuda_exec", None)
         if g is not None:
             self.dev.graph_destroy(g)
+
+    def __del__(self):
+        try:
+            if getattr(self.dev, "handle", None):
+                self.close()
+        except Exception:
+            pass
 
 
 class _Planner:
