@@ -440,6 +440,7 @@ extern "C" int32_t lmb200_graph_destroy(lmb200_ctx h, uint64_t graph) {
   Ctx* c = ctx_from(h);
   HostGraph* G = graph_from(graph);
   if (!c || !G) return LMB200_EINVAL;
+  LMB_REQUIRE(!c->capturing, "graph_destroy: not between capture_begin and capture_end");   // it waits for the stream
   cudaSetDevice(c->device);
   cudaStreamSynchronize(c->stream);
   cudaGraphExecDestroy(G->exec);
