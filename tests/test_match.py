@@ -160,3 +160,52 @@ def test_flat_node_list_and_error_code():
             _lib.call("lmb200_match_decoder", C.byref(nl), y.id, None, None, None, 0, None, 0)
         except _lib.LuminalB200Error as err:
             M._raise_match(err)
+
+
+def test_matchers_over_a_sweep_of_shapes():
+    """Seeded sweep over widths, head splits, batches, sequence lengths and positions: whatever the builders build, the
+    three matchers give back exactly the configuration and the weight roles it was built with, and each refuses the
+    other two builders' graphs."""
+    from luminal_jl_b200 import whisper as WG
+    rng = np.random.default_rng(20240)
+    for _ in range(12):
+        heads = int(rng.choice([1, 2, 4, 6, 8]))
+        kv = int(rng.choice([k for k in (1, 2, 3, 4, 6, 8) if heads % k == 0]))
+        D = int(rng.choice([2, 4, 8, 16]))
+        layers, batch, seq = int(rng.integers(1, 4)), int(rng.integers(1, 5)), int(rng.integers(1, 7))
+        inter, vocab, prev = int(rng.integers(3, 40)), int(rng.integers(5, 90)), int(rng.choice([0, 0, 3]))
+        cls = nn.Llama if rng.integers(2) else nn.Phi3
+        g, reg, tok, out = build(cls, seq=seq, batch=batch, kv=kv, layers=layers, prev_seq=prev, hidden=heads * D, heads=heads,
+                                 inter=inter, vocab=vocab)
+        m = M.match_decoder(g, out.id)
+        assert (m.n_layers, m.hidden, m.n_heads, m.n_kv_heads, m.head_dim, m.intermediate, m.vocab) == (
+            layers, heads * D, heads, kv, D, inter, vocab)
+        assert (m.batch, m.seq, m.prev_seq, m.tokens, m.rope_base) == (batch, seq, prev, tok.id, cls.ROPE_BASE)
+        assert m.weights == {name: t.id for name, t in reg.items()}
+        for other in (M.match_whisper_step, M.match_whisper_encoder):
+            with pytest.raises(M.MatchError):
+                other(g, out.id)
+    for _ in range(8):
+        heads, D = int(rng.choice([1, 2, 4])), int(rng.choice([8, 16, 64]))
+        d, layers, ffn = heads * D, int(rng.integers(1, 4)), int(rng.integers(2, 9)) * 8
+        batch, enc_seq, max_seq = int(rng.integers(1, 4)), int(rng.integers(3, 30)), int(rng.integers(4, 20))
+        step = int(rng.integers(0, max_seq))
+        vocab, n_mels, frames = int(rng.integers(10, 80)), int(rng.integers(1, 5)) * 8, int(rng.integers(4, 50))
+        g, reg = G.Graph(), {}
+        td = WG.TextDecoder(g, reg, d_model=d, heads=heads, layers=layers, ffn=ffn, vocab=vocab, max_positions=max_seq + 3)
+        idg = WG.build_decode_step(td, g, enc_seq, step, max_seq=max_seq, batch=batch)
+        m = M.match_whisper_step(g, idg.logits_id)
+        assert (m.n_layers, m.d_model, m.heads, m.ffn, m.vocab, m.max_positions) == (layers, d, heads, ffn, vocab, max_seq + 3)
+        assert (m.batch, m.step_pos, m.max_seq, m.enc_seq, m.tokens) == (batch, step, max_seq, enc_seq, idg.token_input_id)
+        assert m.weights == {n: t.id for n, t in reg.items() if "encoder_attn.k_proj" not in n and "encoder_attn.v_proj" not in n}
+        assert (m.self_k_ids, m.new_self_v_ids) == (idg.self_k_ids, idg.new_self_v_ids)
+        g, reg = G.Graph(), {}
+        enc = WG.AudioEncoder(g, reg, d_model=d, heads=heads, layers=layers, ffn=ffn, n_mels=n_mels)
+        mel = G.tensor(g, [batch, n_mels, frames])
+        out = enc(mel)
+        e = M.match_whisper_encoder(g, out.id)
+        assert (e.d_model, e.heads, e.layers, e.ffn, e.n_mels, e.batch, e.frames, e.mel) == (d, heads, layers, ffn, n_mels, batch, frames, mel.id)
+        assert e.weights == {n: t.id for n, t in reg.items()}
+        for other in (M.match_decoder, M.match_whisper_step):
+            with pytest.raises(M.MatchError):
+                other(g, out.id)
