@@ -895,6 +895,40 @@ void validate_list(const lmb200_node_list* g) {
     for (int k = g->in_off[n - 1]; k < g->in_off[n]; ++k)
       if (g->in_node[k] < 1 || g->in_node[k] >= n) no_match("node %d: input %d is not an earlier node", n, g->in_node[k]);
   }
+  // The movement ops carry their result shape twice, in their fields and in the shape recorded for the node
+  // (src/Graph.jl:4-26 keeps both): a list in which the two disagree is not a traced graph.
+  Walker w(*g);
+  for (int n = 1; n <= g->n_nodes; ++n) {
+    const int o = w.op(n);
+    if (o != LMB200_NODE_PERMUTE && o != LMB200_NODE_EXPAND && o != LMB200_NODE_RESHAPE && o != LMB200_NODE_SLICE && o != LMB200_NODE_PAD) continue;
+    if (w.n_in(n) != 1) no_match("node %d: a movement op takes one input", n);
+    const Shape in = w.shape(w.in(n, 0)), out = w.shape(n);
+    const std::vector<int64_t> a = w.iargs(n);
+    Shape want;
+    bool ok = true;
+    if (o == LMB200_NODE_RESHAPE) {
+      want = Shape(a.begin(), a.end());
+    } else if (o == LMB200_NODE_PERMUTE) {
+      ok = a.size() == in.size();
+      for (size_t k = 0; ok && k < a.size(); ++k) {
+        ok = a[k] >= 1 && a[k] <= (int64_t)in.size();
+        if (ok) want.push_back(in[a[k] - 1]);
+      }
+    } else if (o == LMB200_NODE_EXPAND) {
+      ok = a.size() == 2 && a[0] >= 1 && a[0] <= (int64_t)in.size() + 1;
+      if (ok) {
+        want = in;
+        want.insert(want.begin() + (a[0] - 1), a[1]);
+      }
+    } else {
+      ok = a.size() == 2 * in.size();
+      for (size_t d = 0; ok && d < in.size(); ++d)
+        want.push_back(o == LMB200_NODE_PAD ? in[d] + a[2 * d] + a[2 * d + 1]
+                                            : std::min<int64_t>(a[2 * d + 1], in[d]) - std::max<int64_t>(a[2 * d], 0));
+    }
+    if (!ok || want != out) no_match("node %d (%s): its fields give %s from an input of %s, the node records %s", n, kOpNames[o],
+                                     ok ? shape_text(want).c_str() : "no shape", shape_text(in).c_str(), shape_text(out).c_str());
+  }
 }
 
 struct Match {

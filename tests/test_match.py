@@ -209,3 +209,17 @@ def test_matchers_over_a_sweep_of_shapes():
         for other in (M.match_decoder, M.match_whisper_step):
             with pytest.raises(M.MatchError):
                 other(g, out.id)
+
+
+def test_corrupted_node_lists_get_a_status_not_a_fault():
+    """tests/fuzz_node_lists.py in a child process: 3 graphs x 150 random corruptions x 3 matchers."""
+    import os
+    import subprocess
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    env = dict(os.environ, PYTHONPATH=os.pathsep.join([os.path.dirname(here), here, os.environ.get("PYTHONPATH", "")]))
+    r = subprocess.run([sys.executable, os.path.join(here, "fuzz_node_lists.py"), "7", "150"], capture_output=True, text=True, env=env,
+                       timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    accepted, refused = (int(x) for x in r.stdout.split()[1::2])
+    assert accepted + refused == 3 * 150 * 3 and refused > accepted          # a changed list is, as a rule, not the graph
