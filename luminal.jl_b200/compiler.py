@@ -218,15 +218,30 @@ class CompiledGraph:
     buffers indexed by node id, as the reference does.  Nodes that vanished into a fused step have no
     buffer (the reference leaves theirs at zero)."""
 
-    def __init__(self, graph, device=None, fuse=True, capture=True):
+    def __init__(self, graph, device=None, fuse=True, capture=True, outputs=None):
         self.graph, self.dev = graph, device or get_device()
         self.results, self.steps = {}, []
+        self.outputs = None if outputs is None else [int(i) for i in outputs]
         # execute_with_capture's cache (src/Compiler.jl:75-79, 97): after the first call "cuda_exec" holds the CUDA
         # graph of the steps, and every later call is one replay; capture=False runs the steps call by call
         self.cache, self.capture = {}, bool(capture)
         plan = plan_graph(graph, fuse)
-        for nid, what in plan:                       # buffers first: a step may read a constant planned after it
-            self.results[nid] = self.dev.empty(graph.shapes[nid - 1])
+        if self.outputs is None:
+            for nid, what in plan:                   # buffers first: a step may read a constant planned after it
+                self.results[nid] = self.dev.empty(graph.shapes[nid - 1])
+        else:
+            # only `outputs` are read after a call: the other step outputs share blocks by liveness (plan_buffers)
+            from .device import DeviceArray
+            missing = [i for i in self.outputs if i not in dict(plan)]
+            if missing:
+                raise KeyError(f"compile: output nodes {missing} have no buffer (they vanished into a fused step)")
+            slot_of, capacity = plan_buffers(graph, plan, self.outputs)
+            self.blocks = [self.dev.empty((n,)) for n in capacity]
+            for nid, what in plan:
+                if nid in slot_of:
+                    self.results[nid] = DeviceArray(self.dev, self.blocks[slot_of[nid]].ptr, graph.shapes[nid - 1], owned=False)
+                else:
+                    self.results[nid] = self.dev.empty(graph.shapes[nid - 1])
         for nid, what in plan:
             buf = self.results[nid]
             if what[0] == "constant":
@@ -284,6 +299,12 @@ class CompiledGraph:
     def kernel_count(self):
         """Kernels one call launches (the input uploads aside)."""
         return len(self.steps)
+
+    def buffer_bytes(self):
+        """Device memory behind the step outputs (inputs and constants aside)."""
+        if self.outputs is not None:
+            return 4 * sum(b.size for b in self.blocks)
+        return 4 * sum(out.size for _, out in self.steps)
 
     def close(self):
         """Drops the recorded CUDA graph (the buffers go with their DeviceArrays)."""
@@ -422,6 +443,52 @@ def plan_graph(graph, fuse=True):
     return _Planner(graph, fuse).plan
 
 
+def step_reads(what):
+    """The node ids a planned step reads."""
+    kind = what[0]
+    if kind in ("op", "fused"):
+        return list(what[2])
+    if kind in ("silu_gate", "rmsnorm"):
+        return [what[1], what[2]]
+    if kind == "layernorm":
+        return [i for i in what[1:4] if i is not None]
+    return []
+
+
+def plan_buffers(graph, plan, keep, slack=2.0):
+    """Which step outputs may share device memory when only the nodes in `keep` are read after a call.  The reference
+    gives every node a buffer of its own for the graph's lifetime (src/Compiler.jl:217-235); here a step's output
+    takes over the block of a tensor whose last reader has run, if that block is large enough and at most `slack`
+    times too large.  Inputs, constants and `keep` never share.  A step's output never takes a block one of its own
+    inputs still occupies (the kernels are not in-place).  Returns ({node id: slot}, [slot capacity in floats]); needs
+    no GPU."""
+    keep = set(keep)
+    steps = [(nid, what) for nid, what in plan if what[0] not in ("input", "constant")]
+    produced = {nid for nid, _ in steps}
+    last_use = {}
+    for idx, (_, what) in enumerate(steps):
+        for i in step_reads(what):
+            last_use[i] = idx
+    slot_of, capacity, free = {}, [], []
+    for idx, (nid, what) in enumerate(steps):
+        size = max(1, int(np.prod(graph.shapes[nid - 1])) if graph.shapes[nid - 1] else 1)
+        fits = [s for s in free if size <= capacity[s] <= slack * size]
+        if nid in keep or not fits:
+            slot = len(capacity)
+            capacity.append(size)
+        else:
+            slot = min(fits, key=lambda s: capacity[s])
+            free.remove(slot)
+        slot_of[nid] = slot
+        released = {i for i in step_reads(what) if last_use.get(i) == idx and i in produced and i not in keep}
+        if nid not in last_use and nid not in keep:
+            released.add(nid)                      # nobody reads it: its block is free again at once
+        for i in sorted(released):
+            if slot_of[i] not in free:
+                free.append(slot_of[i])
+    return slot_of, capacity
+
+
 def run_fused(dev, code, out, ins):
     """One fusion group through lmb200_fused_ew: inputs broadcast to the output's shape by the
     reference's rule (1-dims prepended, src/Execution.jl:207-214)."""
@@ -436,8 +503,11 @@ def run_fused(dev, code, out, ins):
               len(code), ops, args)
 
 
-def compile(graph, device=None, fuse=True, capture=True):     # noqa: A001  (the reference's name)
-    return CompiledGraph(graph, device, fuse, capture)
+def compile(graph, device=None, fuse=True, capture=True, outputs=None):     # noqa: A001  (the reference's name)
+    """compile(graph) of src/Compiler.jl:181-364.  fuse: form the fusion groups; capture: replay a CUDA graph from the
+    second call on; outputs: the node ids the caller reads after a call -- given them, the other intermediate tensors
+    share device memory by liveness instead of holding one buffer each for the graph's lifetime."""
+    return CompiledGraph(graph, device, fuse, capture, outputs)
 
 
-__all__ = ["compile", "CompiledGraph", "plan_graph", "fusible_intermediates", "group_program", "is_elementwise", "run_fused"]
+__all__ = ["compile", "CompiledGraph", "plan_graph", "plan_buffers", "step_reads", "fusible_intermediates", "group_program", "is_elementwise", "run_fused"]

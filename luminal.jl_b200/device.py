@@ -29,8 +29,11 @@ class DeviceArray:
 
     def free(self):
         if self._owned and self.ptr:
-            _lib.call("lmb200_free", self.device.handle, C.c_void_p(self.ptr))
-            self.ptr = 0
+            ptr, self.ptr = self.ptr, 0
+            if getattr(self.device, "recording", False):
+                self.device.deferred_free.append(ptr)          # a free waits for the stream: not while calls are recorded
+            else:
+                _lib.call("lmb200_free", self.device.handle, C.c_void_p(ptr))
 
     def __del__(self):
         try:
@@ -47,6 +50,7 @@ class B200Device:
         _lib.call("lmb200_init", int(ordinal), C.byref(h))
         self.handle = h
         self.ordinal = int(ordinal)
+        self.recording, self.deferred_free = False, []     # see capture()
         if stream is not None:
             self.set_stream(stream)
 
@@ -84,18 +88,24 @@ class B200Device:
     def capture(self, f):
         """Records the op-level calls f() makes into a CUDA graph (nothing runs) and returns its handle."""
         _lib.call("lmb200_capture_begin", self.handle)
+        self.recording = True
         h = C.c_uint64(0)
         try:
-            f()
-        except BaseException:
             try:
-                _lib.call("lmb200_capture_end", self.handle, C.byref(h))
-            except _lib.LuminalB200Error:
-                pass
-            else:
-                _lib.call("lmb200_graph_destroy", self.handle, h)
-            raise
-        _lib.call("lmb200_capture_end", self.handle, C.byref(h))
+                f()
+            except BaseException:
+                try:
+                    _lib.call("lmb200_capture_end", self.handle, C.byref(h))
+                except _lib.LuminalB200Error:
+                    pass
+                else:
+                    _lib.call("lmb200_graph_destroy", self.handle, h)
+                raise
+            _lib.call("lmb200_capture_end", self.handle, C.byref(h))
+        finally:
+            self.recording = False
+            while self.deferred_free:                              # arrays collected while the calls were recorded
+                _lib.call("lmb200_free", self.handle, C.c_void_p(self.deferred_free.pop()))
         return h
 
     def graph_launch(self, graph):

@@ -55,28 +55,61 @@ def eval_graph(g, inputs, want):
     return [vals[i] for i in want]
 
 
-def eval_plan(graph, plan, inputs):
+def eval_step(graph, nid, w, R):
+    """The value of one planned step from the values R of the nodes it reads."""
+    k=w[0]
+    if k=='op': return run_op(w[1],[R[i] for i in w[2]],graph.shapes[nid-1])
+    if k=='fused':
+        st=[]
+        for op,arg in w[1]:
+            if op==0: st.append(R[w[2][int(arg)]])
+            elif op==1: st.append(np.float32(arg))
+            else:
+                cls={v:k2 for k2,v in L.compiler._CODE.items()}[op]
+                ar=3 if cls is G.FusedMulAdd else (2 if cls in (G.Add,G.Mul,G.Mod,G.LessThan,G.Max,G.FusedAddReLU) else 1)
+                args=st[-ar:]; del st[-ar:]
+                st.append(run_op(cls(),args,None))
+        return np.broadcast_to(st[0],graph.shapes[nid-1]).astype(np.float32)
+    if k=='silu_gate': return O.mul(O.swish(R[w[1]]),R[w[2]])
+    if k=='rmsnorm': return O.rms_norm(R[w[1]],R[w[2]],w[5])
+    if k=='layernorm': return O.layer_norm(R[w[1]],R[w[2]],R[w[3]] if w[3] is not None else None,w[6])
+    raise NotImplementedError(k)
+
+
+def _leaves(graph, plan, inputs):
     R={}
     for nid,w in plan:
         k=w[0]
         if k=='input':
             R[nid]=np.asarray(inputs[nid] if nid in inputs else graph.tensors[(nid,1)],np.float32)
         elif k=='constant': R[nid]=np.float32(w[1])
-    for nid,w in plan:
-        k=w[0]
-        if k=='op': R[nid]=run_op(w[1],[R[i] for i in w[2]],graph.shapes[nid-1])
-        elif k=='fused':
-            st=[]
-            for op,arg in w[1]:
-                if op==0: st.append(R[w[2][int(arg)]])
-                elif op==1: st.append(np.float32(arg))
-                else:
-                    cls={v:k2 for k2,v in L.compiler._CODE.items()}[op]
-                    ar=3 if cls is G.FusedMulAdd else (2 if cls in (G.Add,G.Mul,G.Mod,G.LessThan,G.Max,G.FusedAddReLU) else 1)
-                    args=st[-ar:]; del st[-ar:]
-                    st.append(run_op(cls(),args,None))
-            R[nid]=np.broadcast_to(st[0],graph.shapes[nid-1]).astype(np.float32)
-        elif k=='silu_gate': R[nid]=O.mul(O.swish(R[w[1]]),R[w[2]])
-        elif k=='rmsnorm': R[nid]=O.rms_norm(R[w[1]],R[w[2]],w[5])
-        elif k=='layernorm': R[nid]=O.layer_norm(R[w[1]],R[w[2]],R[w[3]] if w[3] is not None else None,w[6])
     return R
+
+
+def eval_plan(graph, plan, inputs):
+    R=_leaves(graph, plan, inputs)
+    for nid,w in plan:
+        if w[0] not in ('input','constant'): R[nid]=eval_step(graph, nid, w, R)
+    return R
+
+
+def eval_plan_shared(graph, plan, inputs, keep):
+    """The plan run with the block sharing plan_buffers() decides: every step output is written into its block, and a
+    step reads its operands out of the blocks as they are at that moment -- so a block handed on too early shows as a
+    wrong value.  Returns ({node: value} for `keep`, the slot map, the capacities)."""
+    slot_of, capacity = L.compiler.plan_buffers(graph, plan, keep)
+    blocks=[np.full(n, np.nan, np.float32) for n in capacity]
+    leaves=_leaves(graph, plan, inputs)
+    shape_of=lambda nid: tuple(graph.shapes[nid-1])
+
+    class View(dict):
+        def __missing__(self, nid):
+            if nid in leaves: return leaves[nid]
+            n=int(np.prod(shape_of(nid))) if shape_of(nid) else 1
+            return blocks[slot_of[nid]][:n].reshape(shape_of(nid))
+    R=View()
+    for nid,w in plan:
+        if w[0] in ('input','constant'): continue
+        val=np.ascontiguousarray(eval_step(graph, nid, w, R), np.float32)
+        blocks[slot_of[nid]][:val.size]=val.reshape(-1)
+    return {nid: R[nid].copy() for nid in keep}, slot_of, capacity

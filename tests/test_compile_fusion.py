@@ -225,3 +225,73 @@ def test_execute_with_capture_host_logic():
         execute_with_capture(dev, lambda: runs.append(1), cache)
     assert cache["cuda_exec"] is None and "capture_begin" in cache["cuda_exec_error"]
     assert len(runs) == 3 and dev.replays == 0
+
+
+def test_buffer_sharing_plan_keeps_every_value_alive(lib_built):
+    """plan_buffers(): with the blocks shared as planned, the kept outputs of a 2-layer Llama graph, of the Whisper
+    encoder graph and of a graph with two outputs equal the unshared evaluation; the shared plan needs a
+    fraction of the memory; no step's output shares a block with one of its own operands."""
+    from luminal_jl_b200 import nn, whisper as WG
+    from plan_eval import eval_plan, eval_plan_shared
+    L = lib_built
+    G = L.graph
+    cases = []
+    g, reg = G.Graph(), {}
+    model = nn.Llama(g, reg, vocab_size=50, hidden=32, n_layers=2, n_heads=4, n_kv_heads=2, intermediate=48)
+    tok = G.tensor(g, [2, 5])
+    out = model(tok, 0)
+    inputs = {t.id: O.synth_normal(3, t.id, t.shape, 0.3) for t in reg.values()}
+    inputs[tok.id] = O.synth_tokens(3, 999, (2, 5), 50).astype(np.float32)
+    cases.append((g, inputs, [out.id]))
+    g, reg = G.Graph(), {}
+    enc = WG.AudioEncoder(g, reg, d_model=32, heads=2, layers=2, ffn=48, n_mels=8)
+    mel = G.tensor(g, [2, 8, 21])
+    out = enc(mel)
+    inputs = {t.id: O.synth_normal(4, t.id, t.shape, 0.3) for t in reg.values()}
+    inputs[mel.id] = O.synth_normal(4, 999, (2, 8, 21), 1.0)
+    cases.append((g, inputs, [out.id]))
+    g = G.Graph()
+    a, b = G.tensor(g, [4, 6]), G.tensor(g, [4, 6])
+    c = G.relu(a * b + a)
+    d = G.sum_(c * c, 2)
+    e = G.exp2(c) + G.expand(d, 2, 6)
+    cases.append((g, {a.id: O.synth_normal(5, 1, (4, 6), 1.0), b.id: O.synth_normal(5, 2, (4, 6), 1.0)}, [d.id, e.id]))
+    for g, inputs, keep in cases:
+        for fuse in (True, False):
+            plan = L.compiler.plan_graph(g, fuse)
+            want = eval_plan(g, plan, inputs)
+            got, slot_of, capacity = eval_plan_shared(g, plan, inputs, keep)
+            for nid in keep:
+                # (not bit for bit: NumPy's matmul takes another path for the blocks' contiguous views)
+                assert np.allclose(got[nid], want[nid], rtol=1e-4, atol=1e-5), (nid, fuse)
+            for nid, what in plan:
+                if nid in slot_of:
+                    assert all(slot_of.get(i) != slot_of[nid] for i in L.compiler.step_reads(what)), nid
+            assert len({slot_of[n] for n in keep}) == len(keep)
+            own = sum(int(np.prod(g.shapes[n - 1])) if g.shapes[n - 1] else 1 for n in slot_of)
+            if len(slot_of) > 20:
+                assert sum(capacity) < 0.35 * own, (sum(capacity), own)
+
+
+@pytest.mark.gpu
+def test_compile_with_outputs_shares_buffers(lib_built, device):
+    """compile(graph, outputs=[...]): the intermediate tensors share blocks by liveness; the kept outputs equal those
+    of the graph compiled with one buffer per node, on the first (step by step) call and on the replays."""
+    from luminal_jl_b200 import nn
+    L = lib_built
+    G = L.graph
+    g, reg = G.Graph(), {}
+    model = nn.Llama(g, reg, vocab_size=200, hidden=64, n_layers=2, n_heads=4, n_kv_heads=2, intermediate=96)
+    tok = G.tensor(g, [2, 16])
+    out = model(tok, 0)
+    inputs = {t.id: O.synth_normal(3, t.id, t.shape, 0.3) for t in reg.values()}
+    own, shared = L.compile(g, device), L.compile(g, device, outputs=[out.id])
+    assert shared.buffer_bytes() < 0.35 * own.buffer_bytes()
+    for seed in range(3):
+        inputs[tok.id] = O.synth_tokens(seed, 999, (2, 16), 200).astype(np.float32)
+        assert np.array_equal(shared(inputs)[out.id].numpy(), own(inputs)[out.id].numpy())
+    assert shared.cache.get("cuda_exec") is not None
+    own.close(); shared.close()
+    with pytest.raises(KeyError):
+        interior = next(n for n in range(len(g.nodes), 0, -1) if n not in dict(L.compiler.plan_graph(g)))
+        L.compile(g, device, outputs=[interior])
