@@ -214,6 +214,11 @@ int32_t lmb200_whisper_encoder_create(lmb200_ctx ctx, int32_t d_model, int32_t h
 int32_t lmb200_whisper_encoder_destroy(lmb200_whisper_encoder enc);
 int32_t lmb200_whisper_encoder_set_weight(lmb200_whisper_encoder enc, const char* name, const float* host, int32_t rank,
                                           const int64_t* dims, int32_t layout);
+/* The reference registers its encoder blocks' tensors as model.encoder.layers.{i}.attn.*, .attn_layer_norm.*, .mlp.fc1.*,
+ * .mlp.fc2.* (src/Whisper.jl:330-336); checkpoints and the reference's decoder blocks (src/Whisper.jl:424-431) spell them
+ * .self_attn.*, .self_attn_layer_norm.*, .fc1.*, .fc2.*.  set_weight takes either; this writes the checkpoint's spelling
+ * of `name` (any other name unchanged) into out.  No GPU is needed. */
+int32_t lmb200_whisper_canonical_name(const char* name, char* out, int64_t capacity);
 /* mel [batch, n_mels, frames] float32 row-major on the host; out_host NULL or [batch, (frames - 1) / 2 + 1, d_model].
  * The output also stays on the device for lmb200_whisper_encoder_cross_kv. */
 int32_t lmb200_whisper_encoder_run(lmb200_whisper_encoder enc, const float* mel_host, int32_t batch, int32_t frames,

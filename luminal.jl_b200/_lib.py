@@ -83,6 +83,7 @@ SIGNATURES = {
     "lmb200_whisper_encoder_create": [_u64, _i32, _i32, _i32, _i32, _i32, _i32, C.POINTER(_u64)],
     "lmb200_whisper_encoder_destroy": [_u64],
     "lmb200_whisper_encoder_set_weight": [_u64, C.c_char_p, _vp, _i32, _pi64, _i32],
+    "lmb200_whisper_canonical_name": [C.c_char_p, C.c_char_p, _i64],
     "lmb200_whisper_encoder_run": [_u64, _vp, _i32, _i32, _vp],
     "lmb200_whisper_encoder_cross_kv": [_u64, _u64],
     "lmb200_model_create": [_u64, C.POINTER(ModelConfig), C.POINTER(_u64)],

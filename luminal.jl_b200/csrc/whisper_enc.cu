@@ -278,6 +278,31 @@ extern "C" int32_t lmb200_whisper_encoder_destroy(uint64_t h) {
 // Names as the reference registers them (src/Whisper.jl:354-404, 809-831): model.encoder.conv{1,2}.{weight,bias},
 // model.encoder.layers.{i}.{self_attn.{q,k,v,out}_proj, self_attn_layer_norm, fc1, fc2, final_layer_norm}.{weight,bias},
 // model.encoder.layer_norm.{weight,bias}, model.decoder.layers.{i}.encoder_attn.{k,v}_proj.{weight,bias}.
+// The reference registers the tensors of its encoder blocks as layers.{i}.attn.{q,k,v,out}_proj.*, attn_layer_norm.*,
+// mlp.fc1.* and mlp.fc2.* (src/Whisper.jl:330-336), while checkpoints -- and the reference's own decoder blocks
+// (src/Whisper.jl:424-431) -- spell them self_attn.*, self_attn_layer_norm.*, fc1.* and fc2.*.  Both spellings name the
+// same tensor; this gives the checkpoint's.
+static std::string canonical_encoder_name(const std::string& n) {
+  const std::string pre = "model.encoder.layers.";
+  if (n.rfind(pre, 0) != 0) return n;
+  const size_t dot = n.find('.', pre.size());
+  if (dot == std::string::npos) return n;
+  const std::string head = n.substr(0, dot + 1), t = n.substr(dot + 1);
+  static const char* const kAlias[][2] = {{"attn.", "self_attn."}, {"attn_layer_norm.", "self_attn_layer_norm."},
+                                          {"mlp.fc1.", "fc1."}, {"mlp.fc2.", "fc2."}};
+  for (const auto& a : kAlias)
+    if (t.rfind(a[0], 0) == 0) return head + a[1] + t.substr(strlen(a[0]));
+  return n;
+}
+
+extern "C" int32_t lmb200_whisper_canonical_name(const char* name, char* out, int64_t capacity) {
+  LMB_REQUIRE(name && out && capacity > 0, "whisper_canonical_name: null argument");
+  const std::string c = canonical_encoder_name(name);
+  LMB_REQUIRE((int64_t)c.size() < capacity, "whisper_canonical_name: %lld bytes do not hold %s", (long long)capacity, c.c_str());
+  memcpy(out, c.c_str(), c.size() + 1);
+  return LMB200_OK;
+}
+
 extern "C" int32_t lmb200_whisper_encoder_set_weight(uint64_t h, const char* name, const float* host, int32_t rank,
                                                      const int64_t* dims, int32_t layout) {
   WhisperEncoder* E = enc_from(h);
@@ -296,7 +321,7 @@ extern "C" int32_t lmb200_whisper_encoder_set_weight(uint64_t h, const char* nam
   };
   LMB_REQUIRE(layout == LMB200_ROWMAJOR || layout == LMB200_COLMAJOR, "whisper_encoder_set_weight: layout %d", layout);
   LMB_CUDA(cudaSetDevice(E->ctx->device));
-  const std::string n(name);
+  const std::string n = canonical_encoder_name(name);
   const int d = E->d;
   auto linear = [&](EncLinear& lin, const std::string& tail, int rows, int cols, int perm) -> int32_t {
     if (tail == "weight") { LMB_TRY(shape_is(rows, cols)); return upload_matrix(E, lin, host, rows, cols, layout, perm); }

@@ -107,3 +107,52 @@ def load_safetensors(model, path, warn_missing=True):
             warnings.warn(f"{len(missing)} model tensors were not found in {path}: " + ", ".join(missing[:8]) +
                           (" ..." if len(missing) > 8 else ""), stacklevel=2)
     return loaded, skipped
+
+
+class WeightRegistry(dict):
+    """WeightRegistry of src/Weights.jl:28-42: registry name -> graph node id.  The graph builders of this package
+    take any dict and store the GraphTensor itself; this class stores ids, as the reference's `mapping` does, and
+    accepts either when written to."""
+
+    def __setitem__(self, name, t):
+        super().__setitem__(str(name), int(getattr(t, "id", t)))
+
+    @property
+    def mapping(self):
+        return self
+
+
+def register_weight(reg, name, t):            # register_weight!, src/Weights.jl:38-42
+    reg[name] = t
+    return t
+
+
+def load_weights(graph, reg, source, device=None):
+    """load_weights!(graph, reg, path | tensors) of src/Weights.jl:60-114: every tensor of the `.safetensors` file, of
+    the shards of a directory, or of a dict of arrays whose name is registered goes, as float32, into
+    graph.tensors[(node id, 1)] -- where execute(), compile() and the node-list compilers look for weights; other
+    tensors are ignored.  With a device the arrays are uploaded (to_device), otherwise they stay on the host and are
+    uploaded by whoever runs the graph.  Registered names no source provided are warned about and returned."""
+    ids = {name: int(getattr(t, "id", t)) for name, t in reg.items()}
+    if isinstance(source, dict):
+        sources = [source]
+    else:
+        files = _files(source)
+        if not files:
+            raise FileNotFoundError(f"No safetensors files found at: {source}")
+        sources = (read_safetensors(f) for f in files)
+    for tensors in sources:
+        for name, node_id in ids.items():
+            if name in tensors:
+                a = np.ascontiguousarray(np.asarray(tensors[name], dtype=np.float32))
+                want = tuple(graph.shapes[node_id - 1])
+                if a.shape != want:
+                    raise ValueError(f"{name}: tensor of shape {a.shape}, node {node_id} of shape {want}")
+                graph.tensors[(node_id, 1)] = device.upload(a) if device is not None else a
+    missing = [name for name, node_id in ids.items() if (node_id, 1) not in graph.tensors]
+    if missing:
+        import warnings
+        warnings.warn(f"Missing weights: {len(missing)} of {len(ids)} registered tensors: " + ", ".join(sorted(missing)[:8]) +
+                      (" ..." if len(missing) > 8 else ""), stacklevel=2)
+    return missing
+

@@ -103,11 +103,17 @@ class WhisperSelfAttention:                      # src/Whisper.jl:238-276
 
 
 class EncoderTransformerBlock:                   # src/Whisper.jl:322-352
-    def __init__(self, hidden, heads, ff, graph, reg, prefix):
-        self.attn = WhisperSelfAttention(hidden, heads, graph, reg, f"{prefix}.self_attn")
-        self.attn_norm = WLayerNorm(hidden, graph, reg, f"{prefix}.self_attn_layer_norm")
-        self.ff1 = WLinear(hidden, ff, graph, reg, f"{prefix}.fc1")
-        self.ff2 = WLinear(ff, hidden, graph, reg, f"{prefix}.fc2")
+    """Registry names: the checkpoint's (self_attn.*, self_attn_layer_norm.*, fc1.*, fc2.*) by default; with
+    reference_names the ones the reference's encoder block registers (attn.*, attn_layer_norm.*, mlp.fc1.*, mlp.fc2.*,
+    src/Whisper.jl:330-336).  The library takes either spelling."""
+
+    def __init__(self, hidden, heads, ff, graph, reg, prefix, reference_names=False):
+        attn, norm, fc1, fc2 = (("attn", "attn_layer_norm", "mlp.fc1", "mlp.fc2") if reference_names else
+                                ("self_attn", "self_attn_layer_norm", "fc1", "fc2"))
+        self.attn = WhisperSelfAttention(hidden, heads, graph, reg, f"{prefix}.{attn}")
+        self.attn_norm = WLayerNorm(hidden, graph, reg, f"{prefix}.{norm}")
+        self.ff1 = WLinear(hidden, ff, graph, reg, f"{prefix}.{fc1}")
+        self.ff2 = WLinear(ff, hidden, graph, reg, f"{prefix}.{fc2}")
         self.ff_norm = WLayerNorm(hidden, graph, reg, f"{prefix}.final_layer_norm")
 
     def __call__(self, x):
@@ -116,12 +122,13 @@ class EncoderTransformerBlock:                   # src/Whisper.jl:322-352
 
 
 class AudioEncoder:                              # src/Whisper.jl:354-404
-    def __init__(self, graph, reg, *, d_model, heads, layers, ffn, n_mels):
+    def __init__(self, graph, reg, *, d_model, heads, layers, ffn, n_mels, reference_names=False):
         pfx = "model.encoder"
         self.d_model = d_model
         self.conv1 = Conv1D(n_mels, d_model, 3, graph, reg, f"{pfx}.conv1", stride=1, padding=1)
         self.conv2 = Conv1D(d_model, d_model, 3, graph, reg, f"{pfx}.conv2", stride=2, padding=1)
-        self.layers = [EncoderTransformerBlock(d_model, heads, ffn, graph, reg, f"{pfx}.layers.{i}") for i in range(layers)]
+        self.layers = [EncoderTransformerBlock(d_model, heads, ffn, graph, reg, f"{pfx}.layers.{i}", reference_names)
+                       for i in range(layers)]
         self.post_ln = WLayerNorm(d_model, graph, reg, f"{pfx}.layer_norm")
 
     def __call__(self, x):                       # x: [batch, n_mels, frames]
@@ -330,6 +337,17 @@ def encode_cross_kv(device, weights, mel, *, d_model, heads, enc_layers, dec_lay
     return res[enc.id], [(res[k.id], res[v.id]) for k, v in kv]
 
 
+def canonical_name(name):
+    """The checkpoint's spelling of a Whisper registry name (lmb200_whisper_canonical_name): the reference's encoder
+    blocks register attn.* / attn_layer_norm.* / mlp.fc1.* / mlp.fc2.* for what checkpoints call self_attn.* /
+    self_attn_layer_norm.* / fc1.* / fc2.* (src/Whisper.jl:330-336)."""
+    import ctypes as C
+    from . import _lib
+    out = C.create_string_buffer(len(name) + 64)
+    _lib.call("lmb200_whisper_canonical_name", name.encode(), out, len(out))
+    return out.value.decode()
+
+
 def greedy_decode(weights, enc_output, sot_sequence, eot_id, *, d_model, heads, layers, ffn, vocab, max_positions=448,
                   max_len=448, dtype="f32", device=None):
     """greedy_decode of src/Decoding.jl:33-136 on the cached session.  The tokenizer stays with the caller: it gives
@@ -416,8 +434,13 @@ class FusedEncoder:
             if not (name.startswith("model.encoder.") or ".encoder_attn.k_proj." in name or ".encoder_attn.v_proj." in name):
                 continue
             host = np.ascontiguousarray(np.asarray(a, dtype=np.float32))
-            self._lib.call("lmb200_whisper_encoder_set_weight", self.handle, name.encode(), host.ctypes.data_as(C.c_void_p),
-                           host.ndim, self._lib.dims(host.shape), 0)
+            try:
+                self._lib.call("lmb200_whisper_encoder_set_weight", self.handle, name.encode(), host.ctypes.data_as(C.c_void_p),
+                               host.ndim, self._lib.dims(host.shape), 0)
+            except self._lib.LuminalB200Error as e:
+                if e.code != -7:                 # LMB200_ENOTFOUND (a decoder layer this encoder was not built for): skipped
+                    raise
+                continue
             used.append(name)
         return used
 
@@ -478,5 +501,5 @@ def registry_shapes(*, d_model, heads, enc_layers, dec_layers, ffn, vocab, n_mel
 
 
 __all__ = ["registry_shapes", "FusedEncoder", "AudioEncoder", "Conv1D", "WhisperSelfAttention", "EncoderTransformerBlock", "sinusoids", "project_cross_kv",
-           "encode_cross_kv", "WhisperCrossAttention", "DecoderTransformerBlock", "TextDecoder", "KVCacheState", "decode_step", "greedy_decode", "build_decode_step",
+           "encode_cross_kv", "WhisperCrossAttention", "DecoderTransformerBlock", "TextDecoder", "KVCacheState", "decode_step", "greedy_decode", "canonical_name", "build_decode_step",
            "IncrementalDecodeGraph", "whisper_self_attn_cached", "whisper_cross_attn_cached"]

@@ -123,3 +123,101 @@ def test_wrong_shaped_tensor_is_refused(lib_built, device):
     m.init_random(1, 0.02)
     assert m.missing_weights() == []
     m.close()
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# tests/test_weight_loading.jl restated: the registry, the names the Whisper builders register, load_weights!
+# ----------------------------------------------------------------------------------------------------------------
+TINY = dict(d_model=384, heads=6, layers=4, ffn=1536)
+
+
+def test_weight_registry_basic(lib_built):                   # tests/test_weight_loading.jl:5-15
+    L = lib_built
+    g, reg = L.Graph(), L.weights.WeightRegistry()
+    t = L.tensor(g, [4, 4])
+    assert L.weights.register_weight(reg, "layer.weight", t) is t
+    assert len(reg.mapping) == 1 and reg.mapping["layer.weight"] == t.id
+
+
+def test_whisper_registries(lib_built):                      # tests/test_weight_loading.jl:17-71
+    L = lib_built
+    WG = L.whisper
+    g, reg = L.Graph(), L.weights.WeightRegistry()
+    WG.AudioEncoder(g, reg, n_mels=80, reference_names=True, **TINY)
+    keys = list(reg.mapping)
+    for part in ("conv1.weight", "conv2.weight", "layer_norm.weight", "layers.0", "layers.0.attn.q_proj.weight", "layers.0.mlp.fc1.weight"):
+        assert any(part in k for k in keys), part
+    n_enc = len(keys)
+    WG.TextDecoder(g, reg, vocab=51864, max_positions=448, **TINY)
+    keys = list(reg.mapping)
+    for part in ("embed_tokens.weight", "embed_positions.weight", "layers.0.self_attn.q_proj.weight", "layers.0.encoder_attn.q_proj.weight",
+                 "layer_norm.weight"):
+        assert any(part in k for k in keys), part
+    enc_keys = [k for k in keys if k.startswith("model.encoder")]
+    dec_keys = [k for k in keys if k.startswith("model.decoder")]
+    assert len(enc_keys) == n_enc > 0 and len(dec_keys) > 0 and len(keys) > 50
+    # the same encoder under the checkpoint's spelling: one canonical name per reference name, and nothing else differs
+    g2, reg2 = L.Graph(), {}
+    WG.AudioEncoder(g2, reg2, n_mels=80, **TINY)
+    assert sorted(WG.canonical_name(k) for k in enc_keys) == sorted(reg2)
+    assert WG.canonical_name("model.decoder.layers.0.self_attn.q_proj.weight") == "model.decoder.layers.0.self_attn.q_proj.weight"
+
+
+def test_load_weights_into_the_graph(tmp_path, lib_built):   # tests/test_weight_loading.jl:73-115
+    L = lib_built
+    g, reg = L.Graph(), L.weights.WeightRegistry()
+    lin = L.nn.Linear(4, 8, g, bias=False)
+    L.weights.register_weight(reg, "test.weight", lin.weight)
+    dummy = np.arange(1, 33, dtype=np.float32).reshape(8, 4)       # row-major [8, 4], as the file stores it
+    path = str(tmp_path / "dummy.safetensors")
+    L.weights.write_safetensors(path, {"test.weight": dummy, "not.registered": np.zeros(3, np.float32)})
+    assert L.weights.load_weights(g, reg, path) == []
+    loaded = g.tensors[(lin.weight.id, 1)]                          # @test haskey(g.tensors, (l.weight.id, 1))
+    assert loaded.size == 32 and np.array_equal(loaded, dummy)
+    # from a dict, from a directory of shards, a missing key (warned about), a wrong shape (refused)
+    g2, reg2 = L.Graph(), {}
+    a, b = L.tensor(g2, [2, 3]), L.tensor(g2, [5])
+    reg2["a"], reg2["b"] = a, b
+    with pytest.warns(UserWarning, match="Missing weights: 1 of 2"):
+        assert L.weights.load_weights(g2, reg2, {"a": np.ones((2, 3))}) == ["b"]
+    shard_dir = tmp_path / "shards"
+    shard_dir.mkdir()
+    L.weights.write_safetensors(str(shard_dir / "model-00001.safetensors"), {"a": np.full((2, 3), 2.0, np.float32)})
+    L.weights.write_safetensors(str(shard_dir / "model-00002.safetensors"), {"b": np.arange(5, dtype=np.float32)}, dtype="BF16")
+    assert L.weights.load_weights(g2, reg2, str(shard_dir)) == []
+    assert np.array_equal(g2.tensors[(a.id, 1)], np.full((2, 3), 2.0, np.float32)) and np.array_equal(g2.tensors[(b.id, 1)], np.arange(5))
+    with pytest.raises(ValueError, match="shape"):
+        L.weights.load_weights(g2, reg2, {"a": np.ones((3, 2))})
+    with pytest.raises(FileNotFoundError):
+        L.weights.load_weights(g2, reg2, str(tmp_path / "nothing"))
+
+
+@pytest.mark.gpu
+def test_fused_encoder_takes_the_reference_spelling(lib_built, device):
+    """The tensor-core encoder fed under the names the reference's encoder blocks register (attn.*, attn_layer_norm.*,
+    mlp.fc1.*, mlp.fc2.*) gives the output it gives under the checkpoint's names; so does the compiled graph whose
+    weights load_weights placed by those names."""
+    import luminal_oracle as O
+    import whisper_oracle as W
+    L = lib_built
+    WG, M = L.whisper, L.match
+    cfg = W.CONFIGS["whisper_test"]
+    w = W.synth_weights(cfg, seed=31)
+    kw = dict(d_model=cfg["d_model"], heads=cfg["heads"], ffn=cfg["ffn"], n_mels=cfg["n_mels"])
+    g, reg = L.Graph(), L.weights.WeightRegistry()
+    enc = WG.AudioEncoder(g, reg, layers=cfg["enc_layers"], reference_names=True, **kw)
+    mel = L.tensor(g, [2, cfg["n_mels"], 40])
+    out = enc(mel)
+    by_reference_name = {name: w[WG.canonical_name(name)] for name in reg}
+    assert any(".attn." in n for n in by_reference_name) and not any("self_attn" in n for n in by_reference_name)
+    x = O.synth_normal(31, 5, (2, cfg["n_mels"], 40), 1.0)
+    a = WG.FusedEncoder(device, enc_layers=cfg["enc_layers"], dec_layers=0, **kw)
+    b = WG.FusedEncoder(device, enc_layers=cfg["enc_layers"], dec_layers=0, **kw)
+    assert len(a.set_weights(by_reference_name)) == len(by_reference_name)
+    b.set_weights({k: v for k, v in w.items() if k.startswith("model.encoder.")})
+    want = b.run(x)
+    assert np.array_equal(a.run(x), want)
+    assert L.weights.load_weights(g, reg, by_reference_name) == []
+    c, m = M.compile_encoder_b200(g, out.id, device=device)
+    assert np.array_equal(c.run(x), want)
+    a.close(); b.close(); c.close()
