@@ -221,3 +221,26 @@ def test_fused_encoder_takes_the_reference_spelling(lib_built, device):
     c, m = M.compile_encoder_b200(g, out.id, device=device)
     assert np.array_equal(c.run(x), want)
     a.close(); b.close(); c.close()
+
+
+def test_phi3_weight_loading(lib_built):                     # tests/test_phi3_loading.jl
+    L = lib_built
+    g, reg = L.Graph(), L.weights.WeightRegistry()
+    L.nn.Phi3(g, reg, vocab_size=100, hidden=64, n_layers=1, n_heads=4, n_kv_heads=1, intermediate=128)
+    for key in ("model.embed_tokens.weight", "model.layers.0.self_attn.q_proj.weight", "model.layers.0.mlp.gate_proj.weight",
+                "model.norm.weight", "lm_head.weight"):
+        assert key in reg.mapping
+    tensors = {key: O.synth_normal(9, node_id, g.shapes[node_id - 1], 1.0) for key, node_id in reg.mapping.items()}
+    assert L.weights.load_weights(g, reg, tensors) == []
+    for key, node_id in reg.mapping.items():
+        data = g.tensors[(node_id, 1)]
+        assert data.shape == tuple(g.shapes[node_id - 1]) and not np.isnan(data).any()
+    # with a forward pass traced, the graph carries everything the node-list compiler asks for: the matcher's weight
+    # roles are the registry
+    g2, reg2 = L.Graph(), L.weights.WeightRegistry()
+    model = L.nn.Phi3(g2, reg2, vocab_size=100, hidden=64, n_layers=1, n_heads=4, n_kv_heads=1, intermediate=128)
+    out = model(L.tensor(g2, [1, 4]), 0)
+    L.weights.load_weights(g2, reg2, tensors)
+    m = L.match_decoder(g2, out.id)
+    assert m.weights == dict(reg2.mapping) and all((node_id, 1) in g2.tensors for node_id in m.weights.values())
+    assert m.rope_base == 10000.0
