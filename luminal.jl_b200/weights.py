@@ -146,6 +146,9 @@ def load_weights(graph, reg, source, device=None):
             if name in tensors:
                 a = np.ascontiguousarray(np.asarray(tensors[name], dtype=np.float32))
                 want = tuple(graph.shapes[node_id - 1])
+                if a.ndim == 3 and len(want) == 2 and a.shape[0] == want[0] and a.shape[1] * a.shape[2] == want[1]:
+                    from .whisper import conv_weight_from_checkpoint      # a checkpoint's [out, in, kernel] Conv1D weight
+                    a = conv_weight_from_checkpoint(a)
                 if a.shape != want:
                     raise ValueError(f"{name}: tensor of shape {a.shape}, node {node_id} of shape {want}")
                 graph.tensors[(node_id, 1)] = device.upload(a) if device is not None else a

@@ -337,6 +337,17 @@ def encode_cross_kv(device, weights, mel, *, d_model, heads, enc_layers, dec_lay
     return res[enc.id], [(res[k.id], res[v.id]) for k, v in kv]
 
 
+def conv_weight_from_checkpoint(a):
+    """A Conv1D weight as checkpoints store it, [ch_out, ch_in, kernel], as the [ch_out, ch_in * kernel] matrix NN.Conv1D
+    multiplies by (src/NN.jl:55-104): column c + ch_in * k, which is what the reference gets when SafeTensors.jl hands it
+    the tensor column-major and load_weights! copies it into the 2-D node by length.  2-D input is returned as it is."""
+    a = np.asarray(a, dtype=F32)
+    if a.ndim != 3:
+        return a
+    ch_out, ch_in, kernel = a.shape
+    return np.ascontiguousarray(a.transpose(0, 2, 1).reshape(ch_out, kernel * ch_in))
+
+
 def canonical_name(name):
     """The checkpoint's spelling of a Whisper registry name (lmb200_whisper_canonical_name): the reference's encoder
     blocks register attn.* / attn_layer_norm.* / mlp.fc1.* / mlp.fc2.* for what checkpoints call self_attn.* /
@@ -433,7 +444,7 @@ class FusedEncoder:
         for name, a in weights.items():
             if not (name.startswith("model.encoder.") or ".encoder_attn.k_proj." in name or ".encoder_attn.v_proj." in name):
                 continue
-            host = np.ascontiguousarray(np.asarray(a, dtype=np.float32))
+            host = np.ascontiguousarray(conv_weight_from_checkpoint(a))
             try:
                 self._lib.call("lmb200_whisper_encoder_set_weight", self.handle, name.encode(), host.ctypes.data_as(C.c_void_p),
                                host.ndim, self._lib.dims(host.shape), 0)
@@ -501,5 +512,5 @@ def registry_shapes(*, d_model, heads, enc_layers, dec_layers, ffn, vocab, n_mel
 
 
 __all__ = ["registry_shapes", "FusedEncoder", "AudioEncoder", "Conv1D", "WhisperSelfAttention", "EncoderTransformerBlock", "sinusoids", "project_cross_kv",
-           "encode_cross_kv", "WhisperCrossAttention", "DecoderTransformerBlock", "TextDecoder", "KVCacheState", "decode_step", "greedy_decode", "canonical_name", "build_decode_step",
+           "encode_cross_kv", "WhisperCrossAttention", "DecoderTransformerBlock", "TextDecoder", "KVCacheState", "decode_step", "greedy_decode", "canonical_name", "conv_weight_from_checkpoint", "build_decode_step",
            "IncrementalDecodeGraph", "whisper_self_attn_cached", "whisper_cross_attn_cached"]

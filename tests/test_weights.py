@@ -244,3 +244,28 @@ def test_phi3_weight_loading(lib_built):                     # tests/test_phi3_l
     m = L.match_decoder(g2, out.id)
     assert m.weights == dict(reg2.mapping) and all((node_id, 1) in g2.tensors for node_id in m.weights.values())
     assert m.rope_base == 10000.0
+
+
+def test_conv_weight_from_a_checkpoint(lib_built):
+    """A checkpoint stores a Conv1D weight as [ch_out, ch_in, kernel]; NN.Conv1D multiplies by [ch_out, ch_in * kernel]
+    with column c + ch_in * k.  The converted matrix in the oracle's Conv1D gives the plain convolution."""
+    import whisper_oracle as W
+    L = lib_built
+    rng = np.random.default_rng(3)
+    ch_out, ch_in, kernel, length = 5, 4, 3, 11
+    w3 = rng.standard_normal((ch_out, ch_in, kernel)).astype(np.float32)
+    bias = rng.standard_normal(ch_out).astype(np.float32)
+    x = rng.standard_normal((2, ch_in, length)).astype(np.float32)
+    for stride in (1, 2):
+        got = W.conv1d(x, L.whisper.conv_weight_from_checkpoint(w3), bias, kernel, stride, 1)
+        xp = np.pad(x, ((0, 0), (0, 0), (1, 1)))
+        n_out = (length + 2 - kernel) // stride + 1
+        want = np.stack([np.einsum("bck,ock->bo", xp[:, :, o * stride:o * stride + kernel], w3) for o in range(n_out)], axis=2) + bias[None, :, None]
+        assert got.shape == want.shape and np.allclose(got, want, atol=1e-5)
+    w2 = L.whisper.conv_weight_from_checkpoint(w3)
+    assert L.whisper.conv_weight_from_checkpoint(w2) is not None and np.array_equal(L.whisper.conv_weight_from_checkpoint(w2), w2)
+    # load_weights places a checkpoint-shaped conv weight into the 2-D node
+    g, reg = L.Graph(), L.weights.WeightRegistry()
+    conv = L.whisper.Conv1D(ch_in, ch_out, kernel, g, reg, "model.encoder.conv1", stride=1, padding=1)
+    assert L.weights.load_weights(g, reg, {"model.encoder.conv1.weight": w3, "model.encoder.conv1.bias": bias}) == []
+    assert np.array_equal(g.tensors[(conv.weight.id, 1)], w2)
