@@ -244,9 +244,57 @@ def cpu_baseline(name="llama3_8b", layers=2, steps=1, ctx=None):
             "sample_seconds": t_sample, "ms_per_step_extrapolated": t_full * 1e3}
 
 
+def run_reference_small_llama(args):
+    """configs[0], the reference's own CPU-runnable case, with nothing extrapolated: the oracle runs the whole job the
+    way the reference's generation loop does -- no KV cache for Llama, the whole prefix re-run for every token
+    (examples/llama.jl:39-99) -- and, beside it, the cached form of the same function the GPU session is compared with."""
+    import numpy as np
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import luminal_oracle as O
+    try:
+        from threadpoolctl import threadpool_limits
+        threadpool_limits(limits=N_CORES)
+    except Exception:
+        pass
+    cfg = O.CONFIGS["small_llama"]
+    w = O.synth_llama_weights(cfg, seed=1234)
+    gold = np.load(os.path.join(ROOT, "tests", "golden", "small_llama_golden.npz"))
+    prompt, steps = gold["prompt"], 64
+    recompute, cached, toks = [], [], None
+    for r in range(1 + max(1, min(args.steps, 3))):            # the first pass warms BLAS up and is not counted
+        t0 = time.perf_counter()
+        toks, _ = O.greedy_generate_recompute(prompt, w, cfg, steps)
+        t1 = time.perf_counter()
+        toks_c, _ = O.CachedLlama(w, cfg, 1, 128).greedy(prompt, steps)
+        t2 = time.perf_counter()
+        if r:
+            recompute.append((t1 - t0) * 1e3)
+            cached.append((t2 - t1) * 1e3)
+    ms, ms_c = median(sorted(recompute)), median(sorted(cached))
+    identical = bool(np.array_equal(toks, gold["tokens"]) and np.array_equal(toks_c, gold["tokens"]))
+    val = steps / (ms * 1e-3)
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "tokens/s", "n_gpus": args.gpus, "steps": steps,
+        "warmup": 1, "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": "small llama (4 layers, hidden 256, 8 heads x 32, MLP 688, vocab 1024), float32, batch 1, "
+                               "32-token prompt + 64 greedy steps; the time includes the prompt", "name": "small_llama",
+                   "note": "CPU oracle port run as the reference generates: the whole prefix re-run per token, no KV cache"},
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": N_CORES, "kind": "port",
+                         "sample": "the whole job, nothing extrapolated", "sample_seconds": ms * 1e-3,
+                         "with_kv_cache_tokens_per_s": steps / (ms_c * 1e-3)},
+        "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "parity": {"tokens_identical_to_golden": identical},
+    }))
+    if not identical:
+        raise SystemExit(3)
+
+
 def run_reference(args):
     if int(os.environ.get("RANK", "0")) != 0:
         return
+    if args.config == "small_llama":
+        return run_reference_small_llama(args)
     name = args.config if args.config in DECODE else "llama3_8b"
     wl = DECODE[name]
     samples, base = [], None
