@@ -312,6 +312,23 @@ function decode_until!(s::Session, first::Vector{Int32}, max_steps::Integer, eot
                 s.h, first, max_steps, eot, out, done))
     out[:, 1:done[]]
 end
+# greedy_decode's loop (src/Decoding.jl:85-130) on a Whisper session created with max_ctx = MAX_TARGET_POSITION - 1 whose
+# cross K/V are set: as in the reference only the LAST id of the start sequence is fed, at position length(tokens) - 1,
+# over a cache whose earlier slots are still the zero rows of a fresh KVCacheState (a fresh session's cache is zeroed);
+# the loop ends with the step that produced eot_id, after max_len steps, or at the position cap.  Returns the ids, the
+# start sequence included; the tokenizer calls around the loop stay in Decoding.jl.
+function greedy_decode!(s::Session, tokens::Vector{Int}, eot_id::Integer; max_len::Integer=448, max_positions::Integer=448)
+    pos = length(tokens) - 1
+    steps = min(max_len, (max_positions - 1) - pos)
+    steps <= 0 && return tokens
+    set_position!(s, pos)
+    out = decode_until!(s, fill(Int32(tokens[end]), s.batch), steps, eot_id)
+    for t in out[1, :]
+        push!(tokens, Int(t))
+        t == eot_id && break
+    end
+    tokens
+end
 # Whisper: cross K/V of one layer, (B, H, T, D) Julia arrays as project_cross_kv returns them (src/Whisper.jl:809-831)
 function set_cross_kv!(s::Session, layer::Integer, k::Array{Float32,4}, v::Array{Float32,4})
     check(ccall((:lmb200_session_set_cross_kv, LIB), Int32, (UInt64, Int32, Ptr{Float32}, Ptr{Float32}, Int32),
