@@ -269,3 +269,37 @@ def test_conv_weight_from_a_checkpoint(lib_built):
     conv = L.whisper.Conv1D(ch_in, ch_out, kernel, g, reg, "model.encoder.conv1", stride=1, padding=1)
     assert L.weights.load_weights(g, reg, {"model.encoder.conv1.weight": w3, "model.encoder.conv1.bias": bias}) == []
     assert np.array_equal(g.tensors[(conv.weight.id, 1)], w2)
+
+
+def test_fused_encoder_set_weights_host_logic(lib_built):
+    """FusedEncoder.set_weights against a stand-in library: names outside the encoder are left out, a checkpoint-shaped
+    conv weight goes down as the 2-D matrix, a name the encoder does not have (LMB200_ENOTFOUND) is skipped, any other
+    failure is raised."""
+    import ctypes as C
+    L = lib_built
+    _lib = L._lib
+
+    class FakeLib:
+        LuminalB200Error = _lib.LuminalB200Error
+        dims = staticmethod(_lib.dims)
+
+        def __init__(self):
+            self.seen = {}
+
+        def call(self, fn, handle, name, ptr, ndim, dims, layout):
+            n = name.decode()
+            if "decoder" in n:
+                raise _lib.LuminalB200Error(-7, "unknown tensor")
+            if "bad" in n:
+                raise _lib.LuminalB200Error(-1, "shape")
+            self.seen[n] = [dims[i] for i in range(ndim)]
+
+    enc = L.whisper.FusedEncoder.__new__(L.whisper.FusedEncoder)
+    enc._lib, enc._C, enc.handle = FakeLib(), C, None
+    used = enc.set_weights({"model.encoder.conv1.bias": np.zeros(3), "model.encoder.conv1.weight": np.zeros((5, 4, 3)),
+                            "model.encoder.layers.0.attn.q_proj.weight": np.zeros((4, 4), np.float64),
+                            "model.decoder.layers.0.encoder_attn.k_proj.weight": np.zeros((2, 2)), "lm_head.weight": np.zeros(2)})
+    assert used == ["model.encoder.conv1.bias", "model.encoder.conv1.weight", "model.encoder.layers.0.attn.q_proj.weight"]
+    assert enc._lib.seen["model.encoder.conv1.weight"] == [5, 12]
+    with pytest.raises(_lib.LuminalB200Error):
+        enc.set_weights({"model.encoder.bad": np.zeros(3)})
