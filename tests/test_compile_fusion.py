@@ -295,3 +295,53 @@ def test_compile_with_outputs_shares_buffers(lib_built, device):
     with pytest.raises(KeyError):
         interior = next(n for n in range(len(g.nodes), 0, -1) if n not in dict(L.compiler.plan_graph(g)))
         L.compile(g, device, outputs=[interior])
+
+
+def test_buffer_sharing_on_random_graphs(lib_built):
+    """plan_buffers() on seeded random graphs (element-wise chains, reductions, expands, permutes, matmuls, values read
+    many steps after they were made, several kept outputs): the shared run equals the unshared one and no step's output
+    shares a block with an operand."""
+    from plan_eval import eval_plan, eval_plan_shared
+    L = lib_built
+    G = L.graph
+    rng = np.random.default_rng(77)
+    for trial in range(40):
+        g = G.Graph()
+        n = int(rng.choice([3, 4, 6]))
+        pool = [G.tensor(g, [n, n]) for _ in range(int(rng.integers(1, 4)))]
+        inputs = {t.id: rng.standard_normal((n, n)).astype(np.float32) for t in pool}
+        for _ in range(int(rng.integers(5, 40))):
+            a = pool[int(rng.integers(len(pool)))] if rng.random() < 0.4 else pool[-1 - int(rng.integers(min(3, len(pool))))]
+            b = pool[int(rng.integers(len(pool)))]
+            kind = int(rng.integers(8))
+            if kind == 0:
+                t = a + b
+            elif kind == 1:
+                t = a * b * np.float32(0.5)
+            elif kind == 2:
+                t = G.relu(a) + np.float32(0.25)
+            elif kind == 3:
+                t = G.sin(a)
+            elif kind == 4:
+                t = G.expand(G.sum_(a, 2), 2, n) * np.float32(1.0 / n)
+            elif kind == 5:
+                t = G.permute(a, [2, 1])
+            elif kind == 6:
+                t = G.matmul(a, b) * np.float32(1.0 / n)
+            else:
+                t = G.expand(G.max_reduce(a, 1), 1, n)
+            pool.append(t)
+        made = [t.id for t in pool if t.id not in inputs]
+        for fuse in (True, False):
+            plan = L.compiler.plan_graph(g, fuse)
+            planned = {nid for nid, what in plan if what[0] not in ("input", "constant")}
+            candidates = [i for i in made if i in planned]
+            keep = sorted(set(int(i) for i in rng.choice(candidates, size=min(len(candidates), int(rng.integers(1, 4))), replace=False)))
+            want = eval_plan(g, plan, inputs)
+            got, slot_of, capacity = eval_plan_shared(g, plan, inputs, keep)
+            for nid in keep:
+                assert np.allclose(got[nid], want[nid], rtol=1e-4, atol=1e-5, equal_nan=True), (trial, fuse, nid)
+            for nid, what in plan:
+                if nid in slot_of:
+                    assert all(slot_of.get(i) != slot_of[nid] for i in L.compiler.step_reads(what)), (trial, nid)
+            assert len({slot_of[i] for i in keep}) == len(keep)
