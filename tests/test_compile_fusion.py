@@ -332,6 +332,11 @@ def test_buffer_sharing_on_random_graphs(lib_built):
                 t = G.expand(G.max_reduce(a, 1), 1, n)
             pool.append(t)
         made = [t.id for t in pool if t.id not in inputs]
+        # the fusion groups change which nodes are materialised, never a value
+        fused, plain = eval_plan(g, L.compiler.plan_graph(g, True), inputs), eval_plan(g, L.compiler.plan_graph(g, False), inputs)
+        assert set(fused) <= set(plain) and set(made) <= set(plain)
+        for nid in fused:
+            assert np.array_equal(np.asarray(fused[nid]), np.asarray(plain[nid]), equal_nan=True), (trial, nid)
         for fuse in (True, False):
             plan = L.compiler.plan_graph(g, fuse)
             planned = {nid for nid, what in plan if what[0] not in ("input", "constant")}
