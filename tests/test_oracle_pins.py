@@ -134,3 +134,19 @@ def test_generator_golden_values():
     got = O.synth_normal(g["seed"], g["tensor_id"], (g["n"],), g["sigma"])
     assert got.view(np.uint32).tolist() == g["bits"]
     assert O.synth_tokens(g["seed"], g["tensor_id"], (8,), 1024).tolist() == g["tokens"]
+
+
+def test_readme_quick_start():
+    # README.md:10-34: c = matmul(a [3,1], b [1,4]) with a = [1;2;3], b = [1 2 3 4] -- the outer product, through the
+    # oracle's batch_matmul and through the graph builders evaluated node by node
+    import luminal_jl_b200 as L
+    from plan_eval import eval_graph
+    a_val = np.array([[1.0], [2.0], [3.0]], np.float32)
+    b_val = np.array([[1.0, 2.0, 3.0, 4.0]], np.float32)
+    want = np.array([[1, 2, 3, 4], [2, 4, 6, 8], [3, 6, 9, 12]], np.float32)
+    assert np.array_equal(O.matmul(a_val, b_val), want)
+    g = L.Graph()
+    a, b = L.tensor(g, (3, 1)), L.tensor(g, (1, 4))
+    c = L.graph.matmul(a, b)
+    (res,) = eval_graph(g, {a.id: a_val, b.id: b_val}, [c.id])
+    assert res.shape == (3, 4) and np.array_equal(res, want)
